@@ -1,0 +1,272 @@
+/*
+ * mantle_cuda.h -- C ABI of libmantle_cuda.so, the B200 (sm_100a) execution backend for
+ * Mantle's operator registry.
+ *
+ * Mantle dispatches every graph node through
+ *     forward_op [op, shapes..., attrs](res, t1[, t2[, t3]])        mantle/autograd/ops/ops.mojo:243-352
+ *     backward_op[tensor_id, op, ug_shape, shapes..., attrs](ug, t1[, t2[, t3]], grad)
+ *                                                                    mantle/autograd/ops/ops.mojo:355-528
+ * and updates weights with Adam.step / Adam.zero_grad               mantle/nn/optim.mojo:90-140.
+ * Each arm of those dispatchers maps to exactly one entry point below; the comment above an entry
+ * point names the reference function it replaces.  Op ids are the reference's OP.* ids
+ * (mantle/autograd/ops/ops.mojo:57-83).
+ *
+ * Conventions
+ *   - every function returns an int32 status (MTL_OK == 0); the text of the last error of a
+ *     context is available through mtl_last_error().  Nothing aborts and no kernel traps.
+ *   - all tensor pointers are DEVICE pointers to dense row-major fp32 data unless the parameter
+ *     is documented as host memory; shapes are host integers.
+ *   - calls on one context are enqueued on that context's stream in call order and return
+ *     without waiting for the GPU (mtl_d2h and mtl_sync wait).
+ *   - one context is driven by one host thread at a time; different contexts are independent.
+ *   - backward entry points take `accumulate`: non-zero adds the contribution to `grad`
+ *     (the reference's accumulate_grad, mantle/core/tensorutils.mojo:443-487), zero overwrites.
+ *   - there is no CPU fallback: without a usable CUDA device mtl_ctx_create fails.
+ */
+#ifndef MANTLE_CUDA_H_
+#define MANTLE_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define MTL_API __attribute__((visibility("default")))
+#else
+#define MTL_API
+#endif
+
+typedef struct mtl_ctx mtl_ctx;
+typedef struct mtl_graph mtl_graph;
+
+#define MTL_MAX_RANK 8 /* TensorShape rank limit, mantle/core/tensor.mojo */
+
+enum mtl_status {
+    MTL_OK = 0,
+    MTL_ERR_INVALID = 1,     /* bad argument: null pointer, bad shape, unknown op id        */
+    MTL_ERR_CUDA = 2,        /* a CUDA runtime / driver call failed                          */
+    MTL_ERR_UNSUPPORTED = 3, /* valid in the reference but outside this backend's coverage   */
+    MTL_ERR_NOMEM = 4,       /* device allocation failed, or workspace growth while capturing */
+    MTL_ERR_TIMEOUT = 5,     /* a bounded device-side wait ran out (kernel returned cleanly)  */
+    MTL_ERR_COMM = 6         /* collective library error                                     */
+};
+
+/* Arithmetic used by OP.DOT and OP.CONV2D.
+ *   MTL_MATH_FP32   CUDA-core fp32 FMA chains in ascending k, bit-identical to the reference's
+ *                   per-element accumulation in matmul.mojo:50-62 for DOT.
+ *   MTL_MATH_TF32   tcgen05 kind::tf32 tensor-core GEMM, fp32 accumulate in TMEM.
+ *   MTL_MATH_TF32X3 each operand split into tf32 hi + lo parts, three tensor-core products
+ *                   (hi*hi + hi*lo + lo*hi); fp32-faithful results.
+ * Shapes the tensor-core kernels cannot take (unaligned strides, tiny extents) run on the
+ * CUDA-core kernels in every mode. */
+enum mtl_math_mode { MTL_MATH_FP32 = 0, MTL_MATH_TF32 = 1, MTL_MATH_TF32X3 = 2 };
+
+/* OP.* ids accepted by the generic entry points (mantle/autograd/ops/ops.mojo:57-83). */
+enum mtl_op {
+    MTL_OP_ADD = 0, MTL_OP_SUB = 1, MTL_OP_MUL = 2, MTL_OP_DIV = 3,
+    MTL_OP_EXP = 4, MTL_OP_LOG = 5, MTL_OP_POW = 6, MTL_OP_DOT = 7,
+    MTL_OP_SUM = 8, MTL_OP_MEAN = 9, MTL_OP_MAX = 10,
+    MTL_OP_FLATTEN = 11, MTL_OP_RESHAPE = 12,
+    MTL_OP_SIGMOID = 13, MTL_OP_RELU = 14, MTL_OP_TANH = 15,
+    MTL_OP_CONV2D = 16, MTL_OP_TRANSPOSE = 17, MTL_OP_MAXPOOL2D = 18, MTL_OP_FMA = 19,
+    MTL_OP_CLIP = 20, MTL_OP_SQUEEZE = 21, MTL_OP_UNSQUEEZE = 22,
+    MTL_OP_LEAKYRELU = 28
+};
+
+/* ---------------------------------------------------------------- lifecycle ------------- */
+
+/* Creates a context on CUDA device `device` with its own non-blocking stream.
+ * Replaces nothing in the reference (which has no device); it is the handle every op needs. */
+MTL_API int32_t mtl_ctx_create(int32_t device, mtl_ctx** out);
+MTL_API int32_t mtl_ctx_destroy(mtl_ctx* ctx);
+/* Use an existing cudaStream_t (passed as void*) instead of the context's own stream. */
+MTL_API int32_t mtl_ctx_set_stream(mtl_ctx* ctx, void* cuda_stream);
+MTL_API void*   mtl_ctx_stream(mtl_ctx* ctx);
+MTL_API int32_t mtl_ctx_set_math_mode(mtl_ctx* ctx, int32_t mode);
+MTL_API int32_t mtl_ctx_math_mode(mtl_ctx* ctx);
+/* Pre-sizes the internal scratch workspace (operand splits, channels-last staging, split-K
+ * partials).  It grows on demand outside stream capture; growth during capture is an error. */
+MTL_API int32_t mtl_ctx_reserve_workspace(mtl_ctx* ctx, size_t bytes);
+MTL_API int32_t mtl_sync(mtl_ctx* ctx);
+MTL_API const char* mtl_last_error(mtl_ctx* ctx);
+/* Number of kernels this library launched on the context since creation (memsets and copies
+ * are not counted). */
+MTL_API int64_t mtl_launch_count(mtl_ctx* ctx);
+/* Reads and clears the device-side status word that bounded waits write on time-out. */
+MTL_API int32_t mtl_device_status(mtl_ctx* ctx, int32_t* out_status);
+MTL_API const char* mtl_version(void);
+
+/* ---------------------------------------------------------------- memory ---------------- */
+
+/* Device storage behind Collection / Parameters (mantle/autograd/collection.mojo:175-222). */
+MTL_API int32_t mtl_malloc(mtl_ctx* ctx, size_t bytes, void** out_dptr);
+MTL_API int32_t mtl_free(mtl_ctx* ctx, void* dptr);
+/* Model.execute step 1, inputs into the arena (mantle/nn/model.mojo:117-119); src is host. */
+MTL_API int32_t mtl_h2d(mtl_ctx* ctx, void* dst, const void* src_host, size_t bytes);
+/* Model.forward's return / Model.inference's copies (model.mojo:99,108-110); dst is host;
+ * waits for the stream. */
+MTL_API int32_t mtl_d2h(mtl_ctx* ctx, void* dst_host, const void* src, size_t bytes);
+/* Asynchronous variants for pinned host memory (see mtl_host_alloc). */
+MTL_API int32_t mtl_h2d_async(mtl_ctx* ctx, void* dst, const void* src_host, size_t bytes);
+MTL_API int32_t mtl_d2h_async(mtl_ctx* ctx, void* dst_host, const void* src, size_t bytes);
+MTL_API int32_t mtl_host_alloc(mtl_ctx* ctx, size_t bytes, void** out_hptr);
+MTL_API int32_t mtl_host_free(mtl_ctx* ctx, void* hptr);
+/* Collection.set_zero (collection.mojo:222) and fill (mantle/core/tensorutils.mojo:30-44). */
+MTL_API int32_t mtl_zero(mtl_ctx* ctx, void* dptr, size_t bytes);
+MTL_API int32_t mtl_fill_f32(mtl_ctx* ctx, float* dptr, int64_t n, float value);
+/* RESHAPE / FLATTEN / SQUEEZE / UNSQUEEZE forward and backward are copies
+ * (mantle/autograd/ops/basics.mojo:706-756, mlops.mojo:302-373). accumulate != 0: dst += src. */
+MTL_API int32_t mtl_copy_f32(mtl_ctx* ctx, float* dst, const float* src, int64_t n,
+                             int32_t accumulate);
+
+/* ---------------------------------------------------------------- DOT ------------------- */
+
+/* DOT.forward -> dot (basics.mojo:230-237, matmul.mojo:80-153): C[M,N] = A[M,K] . B[K,N]. */
+MTL_API int32_t mtl_dot_fwd(mtl_ctx* ctx, float* C, const float* A, const float* B,
+                            int64_t M, int64_t K, int64_t N);
+/* DOT.backward (basics.mojo:240-257): tensor_id 0: grad[M,K] (+)= ug[M,N] . B^T
+ * (dot_transpose_t2, matmul.mojo:175-182); tensor_id 1: grad[K,N] (+)= A^T . ug
+ * (dot_transpose_t1, matmul.mojo:203-210).  The operand not needed may be null. */
+MTL_API int32_t mtl_dot_bwd(mtl_ctx* ctx, int32_t tensor_id, float* grad, const float* ug,
+                            const float* A, const float* B, int64_t M, int64_t K, int64_t N,
+                            int32_t accumulate);
+
+/* ---------------------------------------------------------------- CONV2D ---------------- */
+
+/* Geometry shared by the convolution and pooling entry points; the index lists are the
+ * reference's "padding", "stride", "dilation" attributes (x = dim -2, y = dim -1). */
+typedef struct mtl_conv2d_desc {
+    int32_t N, C, H, W; /* inputs  [N, C, H, W]                                   */
+    int32_t K, R, S;    /* kernel  [K, C, R, S]; for pooling K is ignored, R,S = kernel_size */
+    int32_t pad[2], stride[2], dilation[2];
+} mtl_conv2d_desc;
+
+/* get_result_shape (mantle/autograd/ops/conv.mojo:25-58). Host-only helper. */
+MTL_API int32_t mtl_conv2d_out_shape(const mtl_conv2d_desc* d, int32_t* OH, int32_t* OW);
+/* CONV2D.forward (conv.mojo:81-226): Y[N,K,OH,OW] = conv(X, Wt) + bias[K]. */
+MTL_API int32_t mtl_conv2d_fwd(mtl_ctx* ctx, float* Y, const float* X, const float* Wt,
+                               const float* bias, const mtl_conv2d_desc* d);
+/* CONV2D.backward (conv.mojo:229-425): tensor_id 0 -> grad = dX, 1 -> dW, 2 -> dbias. */
+MTL_API int32_t mtl_conv2d_bwd(mtl_ctx* ctx, int32_t tensor_id, float* grad, const float* ug,
+                               const float* X, const float* Wt, const mtl_conv2d_desc* d,
+                               int32_t accumulate);
+
+/* ---------------------------------------------------------------- MAXPOOL2D ------------- */
+
+/* MAXPOOL2D.forward (mantle/autograd/ops/pool.mojo:44-100).  `idx` (may be null) receives for
+ * every output element the plane-local input offset ih*W+iw of the first maximum in the
+ * reference's (kx, ky) scan order under its strict `>` update; -1 when the window holds no
+ * value greater than -inf. */
+MTL_API int32_t mtl_maxpool2d_fwd(mtl_ctx* ctx, float* Y, int32_t* idx, const float* X,
+                                  const mtl_conv2d_desc* d);
+/* MAXPOOL2D.backward (pool.mojo:103-165): recomputes the argmax from X like the reference and
+ * adds ug into dX at it.  Windows with no argmax (-1) contribute nothing; the reference writes
+ * out of bounds there (pool.mojo:128,163). */
+MTL_API int32_t mtl_maxpool2d_bwd(mtl_ctx* ctx, float* dX, const float* ug, const float* X,
+                                  const mtl_conv2d_desc* d, int32_t accumulate);
+/* Same result from the indices mtl_maxpool2d_fwd stored, without re-reading X. */
+MTL_API int32_t mtl_maxpool2d_bwd_idx(mtl_ctx* ctx, float* dX, const float* ug,
+                                      const int32_t* idx, const mtl_conv2d_desc* d,
+                                      int32_t accumulate);
+
+/* ---------------------------------------------------------------- elementwise ----------- */
+
+/* ADD/SUB/MUL/DIV.forward -> elwise_op / broadcast_elwise_op (tensorutils.mojo:243-357):
+ * scalar path when a shape is [1], NumPy broadcasting otherwise. out has the broadcast shape. */
+MTL_API int32_t mtl_binary_fwd(mtl_ctx* ctx, int32_t op, float* out, const float* a,
+                               const float* b, int32_t a_rank, const int64_t* a_shape,
+                               int32_t b_rank, const int64_t* b_shape);
+/* ADD/SUB/MUL/DIV.backward + un-broadcasting accumulate_grad (basics.mojo:46-219,
+ * ops.mojo:457-463, tensorutils.mojo:455-487). ug has the broadcast shape. */
+MTL_API int32_t mtl_binary_bwd(mtl_ctx* ctx, int32_t op, int32_t tensor_id, float* grad,
+                               const float* ug, const float* a, const float* b,
+                               int32_t a_rank, const int64_t* a_shape, int32_t b_rank,
+                               const int64_t* b_shape, int32_t accumulate);
+/* EXP, LOG, POW, SIGMOID, RELU, TANH, CLIP, LEAKYRELU forward (basics.mojo:260-327,
+ * mlops.mojo:27-299).  p0/p1: POW exponent (truncated to int like elwise_pow) / unused;
+ * LEAKYRELU negative_slope / unused; CLIP min / max. */
+MTL_API int32_t mtl_unary_fwd(mtl_ctx* ctx, int32_t op, float* out, const float* in, int64_t n,
+                              float p0, float p1);
+/* Their backward arms; `in` is the forward INPUT (the reference differentiates at the input,
+ * e.g. relu_bw mlops.mojo:94-100; POW uses a*(x+1e-12)^(a-1), basics.mojo:350-355). */
+MTL_API int32_t mtl_unary_bwd(mtl_ctx* ctx, int32_t op, float* grad, const float* ug,
+                              const float* in, int64_t n, float p0, float p1,
+                              int32_t accumulate);
+/* FMA.forward/backward (basics.mojo:759-817): out = a*b + c, all the same shape. */
+MTL_API int32_t mtl_fma_fwd(mtl_ctx* ctx, float* out, const float* a, const float* b,
+                            const float* c, int64_t n);
+MTL_API int32_t mtl_fma_bwd(mtl_ctx* ctx, int32_t tensor_id, float* grad, const float* ug,
+                            const float* a, const float* b, int64_t n, int32_t accumulate);
+
+/* ---------------------------------------------------------------- reductions ------------ */
+
+/* SUM/MEAN/MAX.forward -> tsum/tmean/tmax (basics.mojo:381-534, tensorutils.mojo:565-876).
+ * axis < 0 reduces everything to shape [1]; otherwise the axis keeps size 1. */
+MTL_API int32_t mtl_reduce_fwd(mtl_ctx* ctx, int32_t op, float* out, const float* in,
+                               int32_t rank, const int64_t* shape, int32_t axis);
+/* SUM/MEAN/MAX.backward (basics.mojo:409-425, 455-506, 537-615); MAX splits the gradient
+ * 1/n between n tied maxima. */
+MTL_API int32_t mtl_reduce_bwd(mtl_ctx* ctx, int32_t op, float* grad, const float* ug,
+                               const float* in, int32_t rank, const int64_t* shape,
+                               int32_t axis, int32_t accumulate);
+
+/* ---------------------------------------------------------------- optimizer ------------- */
+
+/* Adam.step (mantle/nn/optim.mojo:94-140) over one flat fp32 span of n parameters:
+ *   m = b1*m + (1-b1)*g;  v = b2*v + (1-b2)*g*g;
+ *   p -= lr * (m / (1 - b1^t)) / (sqrt(v / (1 - b2^t)) + eps)
+ * with g = grad_scale * grads[i] (grad_scale = 1/world for data-parallel sums). `t` is the
+ * 1-based iteration count after the increment at optim.mojo:96. */
+MTL_API int32_t mtl_adam_step(mtl_ctx* ctx, float* params, const float* grads, float* m,
+                              float* v, int64_t n, float lr, float beta1, float beta2,
+                              float eps, int32_t t, float grad_scale);
+
+/* Same step with the iteration count kept in device memory: `t_dev` (one int32, start it at 0)
+ * is incremented on the stream before the update reads it, so the call can sit inside a captured
+ * step that is replayed many times (Adam.iter, optim.mojo:59,96). */
+MTL_API int32_t mtl_adam_step_dev(mtl_ctx* ctx, float* params, const float* grads, float* m,
+                                  float* v, int64_t n, float lr, float beta1, float beta2,
+                                  float eps, int32_t* t_dev, float grad_scale);
+
+/* ---------------------------------------------------------------- stream capture -------- */
+
+/* Records every call made on the context between begin and end into a CUDA graph; launching it
+ * replays a whole training step with one submission.  Shapes in Mantle graphs are compile-time
+ * constants (model.mojo:113-171), so a step never changes between replays. */
+MTL_API int32_t mtl_graph_begin(mtl_ctx* ctx);
+MTL_API int32_t mtl_graph_end(mtl_ctx* ctx, mtl_graph** out);
+MTL_API int32_t mtl_graph_launch(mtl_ctx* ctx, mtl_graph* g);
+MTL_API int32_t mtl_graph_destroy(mtl_ctx* ctx, mtl_graph* g);
+
+/* ---------------------------------------------------------------- timing ---------------- */
+
+/* CUDA-event stopwatch on the context's stream (replaces the unhooked PerfMetrics table,
+ * mantle/autograd/perf_utils.mojo:60-236). slot in [0, 64). */
+MTL_API int32_t mtl_timer_start(mtl_ctx* ctx, int32_t slot);
+MTL_API int32_t mtl_timer_stop(mtl_ctx* ctx, int32_t slot);
+/* Waits for the stop event and returns milliseconds. */
+MTL_API int32_t mtl_timer_elapsed_ms(mtl_ctx* ctx, int32_t slot, float* out_ms);
+
+/* ---------------------------------------------------------------- data parallel --------- */
+
+/* Data-parallel training is new in this backend (the reference is single-process).  One process
+ * per GPU; rank 0 obtains an id, the launcher distributes its 128 bytes, every rank joins. */
+#define MTL_DP_ID_BYTES 128
+MTL_API int32_t mtl_dp_get_unique_id(uint8_t* out_id /* host, MTL_DP_ID_BYTES */);
+MTL_API int32_t mtl_dp_init(mtl_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world);
+/* Sum-allreduce of `n` floats in place on a communication stream, ordered after everything
+ * enqueued on the context's stream so far; overlaps with later launches until mtl_dp_wait. */
+MTL_API int32_t mtl_dp_allreduce_async(mtl_ctx* ctx, float* buf, int64_t n);
+/* Makes the context's stream wait for all outstanding allreduces. */
+MTL_API int32_t mtl_dp_wait(mtl_ctx* ctx);
+/* Broadcast `n` floats from `root` (initial parameters). */
+MTL_API int32_t mtl_dp_broadcast(mtl_ctx* ctx, float* buf, int64_t n, int32_t root);
+MTL_API int32_t mtl_dp_destroy(mtl_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MANTLE_CUDA_H_ */

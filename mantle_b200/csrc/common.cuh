@@ -1,0 +1,99 @@
+// Internal declarations shared by the translation units of libmantle_cuda.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+#include <string>
+#include <vector>
+
+#include "../../include/mantle_cuda.h"
+
+#define MTL_NUM_TIMERS 64
+
+struct mtl_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int math_mode = MTL_MATH_TF32X3;
+    int sm_count = 148;
+    // scratch workspace, grown on demand outside capture
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    bool capturing = false;
+    int64_t launches = 0;
+    int64_t launches_at_capture = 0;
+    int32_t* dev_status = nullptr;  // one word written by bounded device waits
+    char err[512] = {0};
+    cudaEvent_t t0[MTL_NUM_TIMERS] = {0};
+    cudaEvent_t t1[MTL_NUM_TIMERS] = {0};
+    // data parallel state (dp.cu)
+    void* dp = nullptr;
+    // cached driver entry point for tensor-map encoding (tma.cuh)
+    void* encode_tiled = nullptr;
+};
+
+struct mtl_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int64_t launches = 0;  // kernels recorded in the graph
+};
+
+int32_t mtl_set_error(mtl_ctx* ctx, int32_t code, const char* fmt, ...);
+// Returns a device pointer to at least `bytes` of scratch, 256-byte aligned.
+int32_t mtl_workspace(mtl_ctx* ctx, size_t bytes, void** out);
+
+#define MTL_CHECK_CTX(ctx) \
+    do {                   \
+        if (!(ctx)) return MTL_ERR_INVALID; \
+    } while (0)
+
+#define MTL_REQUIRE(ctx, cond, ...)                                  \
+    do {                                                             \
+        if (!(cond)) return mtl_set_error(ctx, MTL_ERR_INVALID, __VA_ARGS__); \
+    } while (0)
+
+#define MTL_CUDA(ctx, call)                                                              \
+    do {                                                                                 \
+        cudaError_t e__ = (call);                                                        \
+        if (e__ != cudaSuccess)                                                          \
+            return mtl_set_error(ctx, MTL_ERR_CUDA, "%s failed: %s (%s:%d)", #call,      \
+                                 cudaGetErrorString(e__), __FILE__, __LINE__);           \
+    } while (0)
+
+// After a kernel launch: count it and surface launch-configuration errors.
+#define MTL_LAUNCHED(ctx)                                                                \
+    do {                                                                                 \
+        (ctx)->launches++;                                                               \
+        cudaError_t e__ = cudaPeekAtLastError();                                         \
+        if (e__ != cudaSuccess) {                                                        \
+            cudaGetLastError();                                                          \
+            return mtl_set_error(ctx, MTL_ERR_CUDA, "kernel launch failed: %s (%s:%d)",  \
+                                 cudaGetErrorString(e__), __FILE__, __LINE__);           \
+        }                                                                                \
+    } while (0)
+
+static inline int64_t mtl_numel(int32_t rank, const int64_t* shape) {
+    int64_t n = 1;
+    for (int i = 0; i < rank; ++i) n *= shape[i];
+    return n;
+}
+
+static inline int mtl_grid_for(int64_t work_items, int block, int sm_count, int ctas_per_sm) {
+    int64_t g = (work_items + block - 1) / block;
+    int64_t cap = (int64_t)sm_count * ctas_per_sm;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+// ---- entry points implemented across translation units (internal linkage names) ----------
+int32_t mtl_gemm_simt(mtl_ctx* ctx, float* C, const float* A, const float* B, int64_t M,
+                      int64_t N, int64_t K, int transA, int transB, int accumulate);
+// Returns MTL_ERR_UNSUPPORTED when the shape cannot run on the tensor-core kernel.
+int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int64_t M,
+                    int64_t N, int64_t K, int transA, int transB, int accumulate, int x3);
+bool mtl_gemm_tc_supported(int64_t M, int64_t N, int64_t K, int transA, int transB,
+                           const float* A, const float* B, const float* C);

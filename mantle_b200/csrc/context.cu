@@ -1,0 +1,305 @@
+// Context, memory, stream-capture and timing entry points of libmantle_cuda.so.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+int32_t mtl_set_error(mtl_ctx* ctx, int32_t code, const char* fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+        va_end(ap);
+        const char* log = getenv("MANTLE_CUDA_LOG");
+        if (log && log[0] == '1') fprintf(stderr, "[mantle_cuda] error %d: %s\n", code, ctx->err);
+    }
+    return code;
+}
+
+int32_t mtl_workspace(mtl_ctx* ctx, size_t bytes, void** out) {
+    if (bytes > ctx->ws_bytes) {
+        if (ctx->capturing)
+            return mtl_set_error(ctx, MTL_ERR_NOMEM,
+                                 "workspace of %zu bytes needed during stream capture but only %zu "
+                                 "reserved; call mtl_ctx_reserve_workspace first",
+                                 bytes, ctx->ws_bytes);
+        // Growth is rare (first call of each shape): drain the stream, then replace the block.
+        MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->ws) MTL_CUDA(ctx, cudaFree(ctx->ws));
+        ctx->ws = nullptr;
+        ctx->ws_bytes = 0;
+        size_t want = (bytes + (size_t)(1 << 20) - 1) & ~((size_t)(1 << 20) - 1);
+        cudaError_t e = cudaMalloc(&ctx->ws, want);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return mtl_set_error(ctx, MTL_ERR_NOMEM, "cudaMalloc of %zu workspace bytes failed: %s",
+                                 want, cudaGetErrorString(e));
+        }
+        ctx->ws_bytes = want;
+    }
+    *out = ctx->ws;
+    return MTL_OK;
+}
+
+extern "C" {
+
+const char* mtl_version(void) { return "mantle_cuda 0.1 (sm_100a)"; }
+
+int32_t mtl_ctx_create(int32_t device, mtl_ctx** out) {
+    if (!out) return MTL_ERR_INVALID;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count <= 0 || device < 0 || device >= count) {
+        cudaGetLastError();
+        return MTL_ERR_CUDA;  // no CPU fallback: without a device there is no context
+    }
+    if (cudaSetDevice(device) != cudaSuccess) return MTL_ERR_CUDA;
+    mtl_ctx* ctx = new mtl_ctx();
+    ctx->device = device;
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        delete ctx;
+        return MTL_ERR_CUDA;
+    }
+    ctx->owns_stream = true;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
+    if (cudaMalloc((void**)&ctx->dev_status, 256) != cudaSuccess ||
+        cudaMemset(ctx->dev_status, 0, 256) != cudaSuccess) {
+        cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return MTL_ERR_CUDA;
+    }
+    const char* mode = getenv("MANTLE_CUDA_MATH");
+    if (mode) {
+        if (!strcmp(mode, "fp32")) ctx->math_mode = MTL_MATH_FP32;
+        else if (!strcmp(mode, "tf32")) ctx->math_mode = MTL_MATH_TF32;
+        else if (!strcmp(mode, "tf32x3")) ctx->math_mode = MTL_MATH_TF32X3;
+    }
+    *out = ctx;
+    return MTL_OK;
+}
+
+int32_t mtl_ctx_destroy(mtl_ctx* ctx) {
+    MTL_CHECK_CTX(ctx);
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->dp) mtl_dp_destroy(ctx);
+    for (int i = 0; i < MTL_NUM_TIMERS; ++i) {
+        if (ctx->t0[i]) cudaEventDestroy(ctx->t0[i]);
+        if (ctx->t1[i]) cudaEventDestroy(ctx->t1[i]);
+    }
+    if (ctx->ws) cudaFree(ctx->ws);
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return MTL_OK;
+}
+
+int32_t mtl_ctx_set_stream(mtl_ctx* ctx, void* cuda_stream) {
+    MTL_CHECK_CTX(ctx);
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    ctx->stream = (cudaStream_t)cuda_stream;
+    ctx->owns_stream = false;
+    return MTL_OK;
+}
+
+void* mtl_ctx_stream(mtl_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+int32_t mtl_ctx_set_math_mode(mtl_ctx* ctx, int32_t mode) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, mode >= MTL_MATH_FP32 && mode <= MTL_MATH_TF32X3, "unknown math mode %d", mode);
+    ctx->math_mode = mode;
+    return MTL_OK;
+}
+
+int32_t mtl_ctx_math_mode(mtl_ctx* ctx) { return ctx ? ctx->math_mode : -1; }
+
+int32_t mtl_ctx_reserve_workspace(mtl_ctx* ctx, size_t bytes) {
+    MTL_CHECK_CTX(ctx);
+    void* p;
+    return mtl_workspace(ctx, bytes, &p);
+}
+
+int32_t mtl_sync(mtl_ctx* ctx) {
+    MTL_CHECK_CTX(ctx);
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return MTL_OK;
+}
+
+const char* mtl_last_error(mtl_ctx* ctx) { return ctx ? ctx->err : "null context"; }
+
+int64_t mtl_launch_count(mtl_ctx* ctx) { return ctx ? ctx->launches : -1; }
+
+int32_t mtl_device_status(mtl_ctx* ctx, int32_t* out_status) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, out_status, "null out_status");
+    MTL_CUDA(ctx, cudaMemcpyAsync(out_status, ctx->dev_status, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (*out_status != 0) MTL_CUDA(ctx, cudaMemsetAsync(ctx->dev_status, 0, 4, ctx->stream));
+    return MTL_OK;
+}
+
+// ------------------------------------------------------------------ memory ---------------
+
+int32_t mtl_malloc(mtl_ctx* ctx, size_t bytes, void** out_dptr) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, out_dptr, "null out pointer");
+    *out_dptr = nullptr;
+    if (bytes == 0) bytes = 4;
+    cudaError_t e = cudaMalloc(out_dptr, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return mtl_set_error(ctx, MTL_ERR_NOMEM, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+    }
+    return MTL_OK;
+}
+
+int32_t mtl_free(mtl_ctx* ctx, void* dptr) {
+    MTL_CHECK_CTX(ctx);
+    if (!dptr) return MTL_OK;
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    MTL_CUDA(ctx, cudaFree(dptr));
+    return MTL_OK;
+}
+
+int32_t mtl_h2d(mtl_ctx* ctx, void* dst, const void* src_host, size_t bytes) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, (dst && src_host) || bytes == 0, "null pointer in mtl_h2d");
+    if (bytes == 0) return MTL_OK;
+    MTL_CUDA(ctx, cudaMemcpyAsync(dst, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    // pageable sources are staged by the runtime before the call returns; pinned ones are not,
+    // so wait: the caller may reuse the buffer as soon as this returns.
+    if (!ctx->capturing) MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return MTL_OK;
+}
+
+int32_t mtl_d2h(mtl_ctx* ctx, void* dst_host, const void* src, size_t bytes) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, (dst_host && src) || bytes == 0, "null pointer in mtl_d2h");
+    MTL_REQUIRE(ctx, !ctx->capturing, "mtl_d2h waits for the stream and cannot be captured");
+    if (bytes) MTL_CUDA(ctx, cudaMemcpyAsync(dst_host, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return MTL_OK;
+}
+
+int32_t mtl_h2d_async(mtl_ctx* ctx, void* dst, const void* src_host, size_t bytes) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, (dst && src_host) || bytes == 0, "null pointer in mtl_h2d_async");
+    if (bytes) MTL_CUDA(ctx, cudaMemcpyAsync(dst, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return MTL_OK;
+}
+
+int32_t mtl_d2h_async(mtl_ctx* ctx, void* dst_host, const void* src, size_t bytes) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, (dst_host && src) || bytes == 0, "null pointer in mtl_d2h_async");
+    if (bytes) MTL_CUDA(ctx, cudaMemcpyAsync(dst_host, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return MTL_OK;
+}
+
+int32_t mtl_host_alloc(mtl_ctx* ctx, size_t bytes, void** out_hptr) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, out_hptr, "null out pointer");
+    cudaError_t e = cudaHostAlloc(out_hptr, bytes ? bytes : 4, cudaHostAllocDefault);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return mtl_set_error(ctx, MTL_ERR_NOMEM, "cudaHostAlloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+    }
+    return MTL_OK;
+}
+
+int32_t mtl_host_free(mtl_ctx* ctx, void* hptr) {
+    MTL_CHECK_CTX(ctx);
+    if (hptr) MTL_CUDA(ctx, cudaFreeHost(hptr));
+    return MTL_OK;
+}
+
+int32_t mtl_zero(mtl_ctx* ctx, void* dptr, size_t bytes) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, dptr || bytes == 0, "null pointer in mtl_zero");
+    if (bytes) MTL_CUDA(ctx, cudaMemsetAsync(dptr, 0, bytes, ctx->stream));
+    return MTL_OK;
+}
+
+// ------------------------------------------------------------------ capture --------------
+
+int32_t mtl_graph_begin(mtl_ctx* ctx) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, !ctx->capturing, "capture already in progress");
+    MTL_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    ctx->launches_at_capture = ctx->launches;
+    return MTL_OK;
+}
+
+int32_t mtl_graph_end(mtl_ctx* ctx, mtl_graph** out) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, ctx->capturing, "no capture in progress");
+    MTL_REQUIRE(ctx, out, "null out pointer");
+    ctx->capturing = false;
+    cudaGraph_t g = nullptr;
+    MTL_CUDA(ctx, cudaStreamEndCapture(ctx->stream, &g));
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, g, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(g);
+        cudaGetLastError();
+        return mtl_set_error(ctx, MTL_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+    }
+    mtl_graph* mg = new mtl_graph();
+    mg->graph = g;
+    mg->exec = exec;
+    mg->launches = ctx->launches - ctx->launches_at_capture;
+    // captured launches did not run: they are counted each time the graph is launched
+    ctx->launches = ctx->launches_at_capture;
+    *out = mg;
+    return MTL_OK;
+}
+
+int32_t mtl_graph_launch(mtl_ctx* ctx, mtl_graph* g) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, g && g->exec, "null graph");
+    MTL_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+    ctx->launches += g->launches;
+    return MTL_OK;
+}
+
+int32_t mtl_graph_destroy(mtl_ctx* ctx, mtl_graph* g) {
+    MTL_CHECK_CTX(ctx);
+    if (!g) return MTL_OK;
+    cudaStreamSynchronize(ctx->stream);
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
+    return MTL_OK;
+}
+
+// ------------------------------------------------------------------ timing ---------------
+
+int32_t mtl_timer_start(mtl_ctx* ctx, int32_t slot) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, slot >= 0 && slot < MTL_NUM_TIMERS, "timer slot %d out of range", slot);
+    if (!ctx->t0[slot]) {
+        MTL_CUDA(ctx, cudaEventCreate(&ctx->t0[slot]));
+        MTL_CUDA(ctx, cudaEventCreate(&ctx->t1[slot]));
+    }
+    MTL_CUDA(ctx, cudaEventRecord(ctx->t0[slot], ctx->stream));
+    return MTL_OK;
+}
+
+int32_t mtl_timer_stop(mtl_ctx* ctx, int32_t slot) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, slot >= 0 && slot < MTL_NUM_TIMERS && ctx->t1[slot], "timer slot %d not started", slot);
+    MTL_CUDA(ctx, cudaEventRecord(ctx->t1[slot], ctx->stream));
+    return MTL_OK;
+}
+
+int32_t mtl_timer_elapsed_ms(mtl_ctx* ctx, int32_t slot, float* out_ms) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, slot >= 0 && slot < MTL_NUM_TIMERS && ctx->t1[slot] && out_ms, "bad timer query");
+    MTL_CUDA(ctx, cudaEventSynchronize(ctx->t1[slot]));
+    MTL_CUDA(ctx, cudaEventElapsedTime(out_ms, ctx->t0[slot], ctx->t1[slot]));
+    return MTL_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,61 @@
+// CONV2D entry points: argument checks and the choice between the tensor-core implicit-GEMM
+// kernels and the CUDA-core kernels.
+#include "conv.cuh"
+
+namespace {
+
+int32_t make_geom(mtl_ctx* ctx, const mtl_conv2d_desc* d, ConvGeom* g) {
+    MTL_REQUIRE(ctx, d, "null descriptor");
+    MTL_REQUIRE(ctx, d->K >= 1, "CONV2D needs at least one output channel");
+    int32_t OH, OW;
+    if (mtl_conv2d_out_shape(d, &OH, &OW) != MTL_OK)
+        return mtl_set_error(ctx, MTL_ERR_INVALID, "convolution geometry gives an empty or invalid output");
+    g->N = d->N; g->C = d->C; g->H = d->H; g->W = d->W; g->K = d->K; g->R = d->R; g->S = d->S;
+    g->OH = OH; g->OW = OW;
+    g->ph = d->pad[0]; g->pw = d->pad[1]; g->sh = d->stride[0]; g->sw = d->stride[1];
+    g->dh = d->dilation[0]; g->dw = d->dilation[1];
+    return MTL_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t mtl_conv2d_fwd(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
+                       const mtl_conv2d_desc* d) {
+    MTL_CHECK_CTX(ctx);
+    ConvGeom g;
+    int32_t rc = make_geom(ctx, d, &g);
+    if (rc) return rc;
+    MTL_REQUIRE(ctx, Y && X && Wt, "null pointer in mtl_conv2d_fwd");
+    if (ctx->math_mode != MTL_MATH_FP32 && mtl_conv_fwd_tc_supported(g, X, Wt, Y))
+        return mtl_conv_fwd_tc(ctx, Y, X, Wt, bias, g, ctx->math_mode == MTL_MATH_TF32X3);
+    return mtl_conv_fwd_simt(ctx, Y, X, Wt, bias, g);
+}
+
+int32_t mtl_conv2d_bwd(mtl_ctx* ctx, int32_t tensor_id, float* grad, const float* ug, const float* X,
+                       const float* Wt, const mtl_conv2d_desc* d, int32_t accumulate) {
+    MTL_CHECK_CTX(ctx);
+    ConvGeom g;
+    int32_t rc = make_geom(ctx, d, &g);
+    if (rc) return rc;
+    MTL_REQUIRE(ctx, tensor_id >= 0 && tensor_id <= 2, "tensor_id must be 0, 1 or 2");
+    MTL_REQUIRE(ctx, grad && ug, "null pointer in mtl_conv2d_bwd");
+    const bool tc = ctx->math_mode != MTL_MATH_FP32;
+    const int x3 = ctx->math_mode == MTL_MATH_TF32X3;
+    if (tensor_id == 0) {
+        MTL_REQUIRE(ctx, Wt, "input gradient needs the kernel");
+        if (tc && mtl_conv_dgrad_tc_supported(g, ug, Wt, grad))
+            return mtl_conv_dgrad_tc(ctx, grad, ug, Wt, g, accumulate, x3);
+        return mtl_conv_dgrad_simt(ctx, grad, ug, Wt, g, accumulate);
+    }
+    if (tensor_id == 1) {
+        MTL_REQUIRE(ctx, X, "kernel gradient needs the input");
+        if (tc && mtl_conv_wgrad_tc_supported(g, ug, X, grad))
+            return mtl_conv_wgrad_tc(ctx, grad, ug, X, g, accumulate, x3);
+        return mtl_conv_wgrad_simt(ctx, grad, ug, X, g, accumulate);
+    }
+    return mtl_conv_bgrad(ctx, grad, ug, g, accumulate);
+}
+
+}  // extern "C"

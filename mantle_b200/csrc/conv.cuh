@@ -1,0 +1,33 @@
+// Geometry and internal entry points shared by the CONV2D translation units.
+#pragma once
+
+#include "common.cuh"
+
+struct ConvGeom {
+    int N, C, H, W;  // input
+    int K, R, S;     // kernel [K, C, R, S]
+    int OH, OW;      // output spatial extent
+    int ph, pw, sh, sw, dh, dw;
+};
+
+int32_t mtl_sum_partials(mtl_ctx* ctx, float* out, const float* partial, int64_t n, int nsplit, int accumulate);
+
+// CUDA-core kernels (conv_simt.cu)
+int32_t mtl_conv_fwd_simt(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
+                          const ConvGeom& g);
+int32_t mtl_conv_dgrad_simt(mtl_ctx* ctx, float* dX, const float* ug, const float* Wt, const ConvGeom& g,
+                            int accumulate);
+int32_t mtl_conv_wgrad_simt(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,
+                            int accumulate);
+int32_t mtl_conv_bgrad(mtl_ctx* ctx, float* db, const float* ug, const ConvGeom& g, int accumulate);
+
+// Tensor-core implicit-GEMM kernels (conv_tc.cu); *_supported says whether a geometry qualifies.
+bool mtl_conv_fwd_tc_supported(const ConvGeom& g, const float* X, const float* Wt, const float* Y);
+bool mtl_conv_dgrad_tc_supported(const ConvGeom& g, const float* ug, const float* Wt, const float* dX);
+bool mtl_conv_wgrad_tc_supported(const ConvGeom& g, const float* ug, const float* X, const float* dW);
+int32_t mtl_conv_fwd_tc(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
+                        const ConvGeom& g, int x3);
+int32_t mtl_conv_dgrad_tc(mtl_ctx* ctx, float* dX, const float* ug, const float* Wt, const ConvGeom& g,
+                          int accumulate, int x3);
+int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,
+                          int accumulate, int x3);

@@ -1,0 +1,281 @@
+// CUDA-core CONV2D kernels: every padding / stride / dilation the reference accepts, and the
+// layers whose GEMM view is too thin for the tensor cores (e.g. one input channel with a 5x5
+// kernel: 25 multiply-adds per output, bound by writing the output).
+//   forward      one thread per output element, weights staged in shared memory when they fit
+//   input grad   gather form: one thread per input element, no atomics
+//   kernel grad  per (out_ch, in_ch) block, taps accumulated in registers, deterministic
+//                two-pass reduction over batch splits
+//   bias grad    per out_ch block, two-pass
+// Formulas: mantle/autograd/ops/conv.mojo:81-226 (forward), :284-338 (dX), :340-393 (dW),
+// :395-423 (db).
+#include "common.cuh"
+#include "conv.cuh"
+
+namespace {
+
+constexpr int kBlock = 256;
+
+__global__ void __launch_bounds__(kBlock) k_conv_fwd(float* __restrict__ Y, const float* __restrict__ X,
+                                                     const float* __restrict__ Wt, const float* __restrict__ bias,
+                                                     ConvGeom g, int64_t n_out, int w_in_smem) {
+    extern __shared__ float w_s[];
+    const int crs = g.C * g.R * g.S;
+    if (w_in_smem) {
+        for (int i = threadIdx.x; i < g.K * crs; i += blockDim.x) w_s[i] = Wt[i];
+        __syncthreads();
+    }
+    const float* wsrc = w_in_smem ? w_s : Wt;
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int plane = g.OH * g.OW;
+    for (int64_t o = tid; o < n_out; o += stride) {
+        int64_t nk = o / plane;
+        int rem = (int)(o - nk * plane);
+        int oh = rem / g.OW, ow = rem - oh * g.OW;
+        int n = (int)(nk / g.K), k = (int)(nk - (int64_t)n * g.K);
+        const float* xn = X + (int64_t)n * g.C * g.H * g.W;
+        const float* wk = wsrc + (int64_t)k * crs;
+        int ih0 = oh * g.sh - g.ph, iw0 = ow * g.sw - g.pw;
+        float acc = 0.0f;
+        for (int c = 0; c < g.C; ++c) {
+            const float* xc = xn + (int64_t)c * g.H * g.W;
+            for (int r = 0; r < g.R; ++r) {
+                int ih = ih0 + r * g.dh;
+                if (ih < 0 || ih >= g.H) continue;
+                for (int s = 0; s < g.S; ++s) {
+                    int iw = iw0 + s * g.dw;
+                    if (iw < 0 || iw >= g.W) continue;
+                    acc = fmaf(__ldg(xc + ih * g.W + iw), wk[(c * g.R + r) * g.S + s], acc);
+                }
+            }
+        }
+        Y[o] = acc + (bias ? __ldg(bias + k) : 0.0f);
+    }
+}
+
+__global__ void __launch_bounds__(kBlock) k_conv_dgrad(float* __restrict__ dX, const float* __restrict__ ug,
+                                                       const float* __restrict__ Wt, ConvGeom g, int64_t n_in,
+                                                       int accumulate) {
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int plane = g.H * g.W;
+    for (int64_t i = tid; i < n_in; i += stride) {
+        int64_t nc = i / plane;
+        int rem = (int)(i - nc * plane);
+        int ih = rem / g.W, iw = rem - ih * g.W;
+        int n = (int)(nc / g.C), c = (int)(nc - (int64_t)n * g.C);
+        float acc = 0.0f;
+        for (int r = 0; r < g.R; ++r) {
+            int th = ih + g.ph - r * g.dh;
+            if (th < 0 || th % g.sh) continue;
+            int oh = th / g.sh;
+            if (oh >= g.OH) continue;
+            for (int s = 0; s < g.S; ++s) {
+                int tw = iw + g.pw - s * g.dw;
+                if (tw < 0 || tw % g.sw) continue;
+                int ow = tw / g.sw;
+                if (ow >= g.OW) continue;
+                const float* up = ug + ((int64_t)n * g.K * g.OH + oh) * g.OW + ow;
+                const float* wp = Wt + ((int64_t)c * g.R + r) * g.S + s;
+                for (int k = 0; k < g.K; ++k)
+                    acc = fmaf(__ldg(up + (int64_t)k * g.OH * g.OW), __ldg(wp + (int64_t)k * g.C * g.R * g.S), acc);
+            }
+        }
+        dX[i] = accumulate ? dX[i] + acc : acc;
+    }
+}
+
+__device__ __forceinline__ float block_sum(float v, float* smem) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.0f;
+    if (threadIdx.x < 32) {
+        t = threadIdx.x < (kBlock >> 5) ? smem[threadIdx.x] : 0.0f;
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    }
+    __syncthreads();
+    return t;
+}
+
+// Kernel gradient, taps in registers.  grid = (K*C, nsplit); partial[split][kc][tap].
+template <int R, int S>
+__global__ void __launch_bounds__(kBlock) k_conv_wgrad_taps(float* __restrict__ partial, const float* __restrict__ ug,
+                                                            const float* __restrict__ X, ConvGeom g, int n_per_split) {
+    __shared__ float smem[32];
+    const int kc = blockIdx.x;
+    const int k = kc / g.C, c = kc - k * g.C;
+    const int n_begin = blockIdx.y * n_per_split;
+    const int n_end = min(g.N, n_begin + n_per_split);
+    const int plane = g.OH * g.OW;
+    float acc[R * S];
+#pragma unroll
+    for (int t = 0; t < R * S; ++t) acc[t] = 0.0f;
+    const int64_t total = (int64_t)(n_end - n_begin) * plane;
+    for (int64_t e = threadIdx.x; e < total; e += kBlock) {
+        int n = n_begin + (int)(e / plane);
+        int rem = (int)(e % plane);
+        int oh = rem / g.OW, ow = rem - oh * g.OW;
+        float u = __ldg(ug + ((int64_t)n * g.K + k) * plane + rem);
+        const float* xc = X + ((int64_t)n * g.C + c) * g.H * g.W;
+        int ih0 = oh * g.sh - g.ph, iw0 = ow * g.sw - g.pw;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            int ih = ih0 + r * g.dh;
+            bool rok = ih >= 0 && ih < g.H;
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                int iw = iw0 + s * g.dw;
+                float x = (rok && iw >= 0 && iw < g.W) ? __ldg(xc + ih * g.W + iw) : 0.0f;
+                acc[r * S + s] = fmaf(x, u, acc[r * S + s]);
+            }
+        }
+    }
+    float* out = partial + ((int64_t)blockIdx.y * g.K * g.C + kc) * (R * S);
+#pragma unroll
+    for (int t = 0; t < R * S; ++t) {
+        float v = block_sum(acc[t], smem);
+        if (threadIdx.x == 0) out[t] = v;
+    }
+}
+
+// Any kernel size: one tap at a time.
+__global__ void __launch_bounds__(kBlock) k_conv_wgrad_generic(float* __restrict__ partial, const float* __restrict__ ug,
+                                                               const float* __restrict__ X, ConvGeom g,
+                                                               int n_per_split) {
+    __shared__ float smem[32];
+    const int kc = blockIdx.x;
+    const int k = kc / g.C, c = kc - k * g.C;
+    const int n_begin = blockIdx.y * n_per_split;
+    const int n_end = min(g.N, n_begin + n_per_split);
+    const int plane = g.OH * g.OW;
+    const int64_t total = (int64_t)(n_end - n_begin) * plane;
+    float* out = partial + ((int64_t)blockIdx.y * g.K * g.C + kc) * (g.R * g.S);
+    for (int r = 0; r < g.R; ++r)
+        for (int s = 0; s < g.S; ++s) {
+            float acc = 0.0f;
+            for (int64_t e = threadIdx.x; e < total; e += kBlock) {
+                int n = n_begin + (int)(e / plane);
+                int rem = (int)(e % plane);
+                int oh = rem / g.OW, ow = rem - oh * g.OW;
+                int ih = oh * g.sh - g.ph + r * g.dh, iw = ow * g.sw - g.pw + s * g.dw;
+                if (ih < 0 || ih >= g.H || iw < 0 || iw >= g.W) continue;
+                acc = fmaf(__ldg(X + (((int64_t)n * g.C + c) * g.H + ih) * g.W + iw),
+                           __ldg(ug + ((int64_t)n * g.K + k) * plane + rem), acc);
+            }
+            float v = block_sum(acc, smem);
+            if (threadIdx.x == 0) out[r * g.S + s] = v;
+        }
+}
+
+// grid = (K, nsplit); partial[split][k]
+__global__ void __launch_bounds__(kBlock) k_conv_bgrad(float* __restrict__ partial, const float* __restrict__ ug,
+                                                       int N, int K, int plane, int n_per_split) {
+    __shared__ float smem[32];
+    const int k = blockIdx.x;
+    const int n_begin = blockIdx.y * n_per_split;
+    const int n_end = min(N, n_begin + n_per_split);
+    float acc = 0.0f;
+    const bool vec = (plane % 4 == 0) && ((reinterpret_cast<uintptr_t>(ug) & 15u) == 0);
+    for (int n = n_begin; n < n_end; ++n) {
+        const float* p = ug + ((int64_t)n * K + k) * plane;
+        if (vec) {
+            const float4* p4 = reinterpret_cast<const float4*>(p);
+            for (int i = threadIdx.x; i < plane / 4; i += kBlock) {
+                float4 v = __ldg(p4 + i);
+                acc += (v.x + v.y) + (v.z + v.w);
+            }
+        } else {
+            for (int i = threadIdx.x; i < plane; i += kBlock) acc += __ldg(p + i);
+        }
+    }
+    float v = block_sum(acc, smem);
+    if (threadIdx.x == 0) partial[(int64_t)blockIdx.y * K + k] = v;
+}
+
+}  // namespace
+
+// out[i] (+)= sum over splits of partial[s][i]
+__global__ void __launch_bounds__(256) k_sum_partials(float* __restrict__ out, const float* __restrict__ partial,
+                                                      int64_t n, int nsplit, int accumulate) {
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = tid; i < n; i += stride) {
+        float s = 0.0f;
+        for (int j = 0; j < nsplit; ++j) s += partial[(int64_t)j * n + i];
+        out[i] = accumulate ? out[i] + s : s;
+    }
+}
+
+int32_t mtl_sum_partials(mtl_ctx* ctx, float* out, const float* partial, int64_t n, int nsplit, int accumulate) {
+    int grid = mtl_grid_for(n, 256, ctx->sm_count, 8);
+    k_sum_partials<<<grid, 256, 0, ctx->stream>>>(out, partial, n, nsplit, accumulate);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
+int32_t mtl_conv_fwd_simt(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
+                          const ConvGeom& g) {
+    int64_t n_out = (int64_t)g.N * g.K * g.OH * g.OW;
+    size_t wbytes = (size_t)g.K * g.C * g.R * g.S * 4;
+    int w_in_smem = wbytes <= 40 * 1024;
+    int grid = mtl_grid_for(n_out, kBlock, ctx->sm_count, 8);
+    k_conv_fwd<<<grid, kBlock, w_in_smem ? wbytes : 0, ctx->stream>>>(Y, X, Wt, bias, g, n_out, w_in_smem);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
+int32_t mtl_conv_dgrad_simt(mtl_ctx* ctx, float* dX, const float* ug, const float* Wt, const ConvGeom& g,
+                            int accumulate) {
+    int64_t n_in = (int64_t)g.N * g.C * g.H * g.W;
+    int grid = mtl_grid_for(n_in, kBlock, ctx->sm_count, 8);
+    k_conv_dgrad<<<grid, kBlock, 0, ctx->stream>>>(dX, ug, Wt, g, n_in, accumulate);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
+static int pick_nsplit(const mtl_ctx* ctx, int blocks_x, int N) {
+    // enough blocks to fill the machine about four times over, never more splits than samples
+    int want = (ctx->sm_count * 4 + blocks_x - 1) / blocks_x;
+    if (want < 1) want = 1;
+    if (want > N) want = N;
+    if (want > 64) want = 64;
+    return want;
+}
+
+int32_t mtl_conv_wgrad_simt(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,
+                            int accumulate) {
+    const int kc = g.K * g.C;
+    const int taps = g.R * g.S;
+    int nsplit = pick_nsplit(ctx, kc, g.N);
+    int n_per_split = (g.N + nsplit - 1) / nsplit;
+    nsplit = (g.N + n_per_split - 1) / n_per_split;
+    void* ws;
+    int32_t rc = mtl_workspace(ctx, (size_t)nsplit * kc * taps * 4, &ws);
+    if (rc) return rc;
+    float* partial = (float*)ws;
+    dim3 grid((unsigned)kc, (unsigned)nsplit);
+    MTL_REQUIRE(ctx, nsplit <= 65535, "too many batch splits");
+    if (g.R == 5 && g.S == 5) k_conv_wgrad_taps<5, 5><<<grid, kBlock, 0, ctx->stream>>>(partial, ug, X, g, n_per_split);
+    else if (g.R == 3 && g.S == 3) k_conv_wgrad_taps<3, 3><<<grid, kBlock, 0, ctx->stream>>>(partial, ug, X, g, n_per_split);
+    else if (g.R == 1 && g.S == 1) k_conv_wgrad_taps<1, 1><<<grid, kBlock, 0, ctx->stream>>>(partial, ug, X, g, n_per_split);
+    else k_conv_wgrad_generic<<<grid, kBlock, 0, ctx->stream>>>(partial, ug, X, g, n_per_split);
+    MTL_LAUNCHED(ctx);
+    return mtl_sum_partials(ctx, dW, partial, (int64_t)kc * taps, nsplit, accumulate);
+}
+
+int32_t mtl_conv_bgrad(mtl_ctx* ctx, float* db, const float* ug, const ConvGeom& g, int accumulate) {
+    int nsplit = pick_nsplit(ctx, g.K, g.N);
+    int n_per_split = (g.N + nsplit - 1) / nsplit;
+    nsplit = (g.N + n_per_split - 1) / n_per_split;
+    void* ws;
+    int32_t rc = mtl_workspace(ctx, (size_t)nsplit * g.K * 4, &ws);
+    if (rc) return rc;
+    float* partial = (float*)ws;
+    dim3 grid((unsigned)g.K, (unsigned)nsplit);
+    k_conv_bgrad<<<grid, kBlock, 0, ctx->stream>>>(partial, ug, g.N, g.K, g.OH * g.OW, n_per_split);
+    MTL_LAUNCHED(ctx);
+    return mtl_sum_partials(ctx, db, partial, g.K, nsplit, accumulate);
+}

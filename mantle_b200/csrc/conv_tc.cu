@@ -1,0 +1,434 @@
+// OP.CONV2D on the tensor cores as implicit GEMM (stride 1, dilation 1):
+//   forward      Y[(n,oh,ow), k]   = sum over (r,s,c) of X[n, oh+r-ph, ow+s-pw, c] * W[k, c, r, s]
+//   input grad   dX[(n,ih,iw), c]  = the same form on ug with spatially flipped, transposed weights
+// The activation tensor is first re-laid out channels-last (one pass, fused with the tf32 hi/lo
+// split), so that one TMA box {32 channels, bw, bh, bn pixels} is a K-major 128-byte-swizzled
+// operand tile; shifting the box origin by (r, s) walks the filter taps and the TMA zero fill
+// outside the tensor is the convolution's zero padding.  Weights are re-laid out as [tap][out][in].
+// Pipeline and warp roles are those of the DOT kernel: TMA producer warp, MMA issuer warp, four
+// epilogue warps, two accumulators in tensor memory; the epilogue adds the bias and writes NCHW.
+#include "conv.cuh"
+#include "sm100.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;
+constexpr int kThreads = 192;
+constexpr uint64_t kWaitBudgetNs = 4000000000ull;
+
+template <int BN>
+struct Cfg {
+    static constexpr int kStages = BN == 128 ? 6 : 8;
+    static constexpr int kABytes = BM * BK * 4;
+    static constexpr int kBBytes = BN * BK * 4;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+struct ConvTcParams {
+    int N, OH, OW, Kout;  // output [N, Kout, OH, OW]
+    int Cin;              // channels reduced per tap
+    int R, S, ph, pw;     // input pixel = output pixel + (r - ph, s - pw)
+    int bw, bh, bn;       // pixel box of one tile, bw*bh*bn <= 128
+    int tiles_w, tiles_h, tiles_nb, tiles_k;
+    int nseg, segA[3], segB[3];
+    uint32_t a_bytes;     // bytes one activation box delivers
+    float* out;
+    const float* bias;
+    int accumulate;
+    int32_t* status;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+k_conv_igemm(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
+             const __grid_constant__ CUtensorMap mapB0, const __grid_constant__ CUtensorMap mapB1, ConvTcParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + C::kStages;
+    uint64_t* tmem_full = bars + 2 * C::kStages;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles_m = p.tiles_w * p.tiles_h * p.tiles_nb;
+    const int num_tiles = tiles_m * p.tiles_k;
+    const int cblocks = (p.Cin + BK - 1) / BK;
+    const int kb_per_seg = p.R * p.S * cblocks;
+    const int kb_total = kb_per_seg * p.nseg;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tmem_full[a], 1);
+            mbar_init(&tmem_empty[a], 128);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&mapA0);
+        prefetch_tensormap(&mapB0);
+        if (p.nseg > 1) {
+            prefetch_tensormap(&mapA1);
+            prefetch_tensormap(&mapB1);
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int kt = t % p.tiles_k;
+                int mt = t / p.tiles_k;
+                const int tw = mt % p.tiles_w;
+                mt /= p.tiles_w;
+                const int th = mt % p.tiles_h;
+                const int tnb = mt / p.tiles_h;
+                const int ow0 = tw * p.bw, oh0 = th * p.bh, n0 = tnb * p.bn;
+                for (int kb = 0; kb < kb_total; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+                    const int seg = kb / kb_per_seg;
+                    int rem = kb - seg * kb_per_seg;
+                    const int rs = rem / cblocks;
+                    const int cb = rem - rs * cblocks;
+                    const int r = rs / p.S, s = rs - r * p.S;
+                    const CUtensorMap* ma = p.segA[seg] ? &mapA1 : &mapA0;
+                    const CUtensorMap* mb = p.segB[seg] ? &mapB1 : &mapB0;
+                    uint8_t* sa = tiles + stage * C::kStageBytes;
+                    uint8_t* sb = sa + C::kABytes;
+                    mbar_arrive_expect_tx(&full[stage], p.a_bytes + C::kBBytes);
+                    tma_load_4d(sa, ma, &full[stage], cb * BK, ow0 + s - p.pw, oh0 + r - p.ph, n0);
+                    tma_load_3d(sb, mb, &full[stage], cb * BK, kt * BN, rs);
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) atomicExch(p.status, MTL_ERR_TIMEOUT);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_tf32(BN, false, false);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int local = 0;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+                const int acc = local & 1;
+                const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < kb_total; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(tiles + stage * C::kStageBytes);
+                    const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+                    for (int kk = 0; kk < BK / 8; ++kk) {
+                        const uint64_t da = make_smem_desc(sa + kk * 32, 16, 1024);
+                        const uint64_t db = make_smem_desc(sb + kk * 32, 16, 1024);
+                        mma_tf32(tmem_d, da, db, idesc, (kb | kk) ? 1u : 0u);
+                    }
+                    mma_commit(&empty[stage]);
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) mma_commit(&tmem_full[acc]);
+            }
+            if (!ok) atomicExch(p.status, MTL_ERR_TIMEOUT);
+        }
+    } else {
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;  // pixel slot inside the tile's box
+        const int w_i = row % p.bw;
+        const int h_i = (row / p.bw) % p.bh;
+        const int n_i = row / (p.bw * p.bh);
+        const int plane = p.OH * p.OW;
+        bool ok = true;
+        int local = 0;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+            const int kt = t % p.tiles_k;
+            int mt = t / p.tiles_k;
+            const int tw = mt % p.tiles_w;
+            mt /= p.tiles_w;
+            const int th = mt % p.tiles_h;
+            const int tnb = mt / p.tiles_h;
+            const int ow = tw * p.bw + w_i, oh = th * p.bh + h_i, n = tnb * p.bn + n_i;
+            const bool valid = n_i < p.bn && ow < p.OW && oh < p.OH && n < p.N;
+            const int acc = local & 1;
+            const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+            if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+            tc_fence_after_sync();
+            float* obase = p.out + ((int64_t)n * p.Kout) * plane + (int64_t)oh * p.OW + ow;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
+                tmem_ld_wait();
+                const int k0 = kt * BN + c * 32;
+                if (valid) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int k = k0 + j;
+                        if (k < p.Kout) {
+                            float v = __uint_as_float(r[j]);
+                            if (p.bias) v += __ldg(p.bias + k);
+                            float* dst = obase + (int64_t)k * plane;
+                            *dst = p.accumulate ? *dst + v : v;
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tmem_empty[acc]);
+        }
+        if (!ok && lane == 0) atomicExch(p.status, MTL_ERR_TIMEOUT);
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+__device__ __forceinline__ void split_tf32(float v, float& h, float& l) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+    h = __uint_as_float(u);
+    l = v - h;
+}
+
+// [N, C, HW] -> [N, HW, C] through a 32x32 shared-memory tile; optionally also writes the residual.
+template <bool SPLIT>
+__global__ void __launch_bounds__(256) k_nchw_to_nhwc(float* __restrict__ hi, float* __restrict__ lo,
+                                                      const float* __restrict__ X, int C, int HW) {
+    __shared__ float tile[32][33];
+    const int n = blockIdx.z;
+    const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    const float* xin = X + (int64_t)n * C * HW;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int c = c0 + ty + 8 * i, pp = p0 + tx;
+        tile[ty + 8 * i][tx] = (c < C && pp < HW) ? xin[(int64_t)c * HW + pp] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int pp = p0 + ty + 8 * i, c = c0 + tx;
+        if (pp < HW && c < C) {
+            float v = tile[tx][ty + 8 * i];
+            int64_t o = ((int64_t)n * HW + pp) * C + c;
+            if (SPLIT) {
+                float h, l;
+                split_tf32(v, h, l);
+                hi[o] = h;
+                lo[o] = l;
+            } else {
+                hi[o] = v;
+            }
+        }
+    }
+}
+
+// Weights [K, C, R, S] -> forward layout [tap][K][C], or (flip) input-gradient layout
+// [flipped tap][C][K].
+template <bool SPLIT>
+__global__ void __launch_bounds__(256) k_weights_relayout(float* __restrict__ hi, float* __restrict__ lo,
+                                                          const float* __restrict__ Wt, int K, int C, int R, int S,
+                                                          int flip) {
+    int64_t total = (int64_t)K * C * R * S;
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t o = tid; o < total; o += stride) {
+        int inner = flip ? K : C, mid = flip ? C : K;
+        int i0 = (int)(o % inner);
+        int64_t q = o / inner;
+        int i1 = (int)(q % mid);
+        int rs = (int)(q / mid);
+        int r = rs / S, s = rs - r * S;
+        int k = flip ? i0 : i1, c = flip ? i1 : i0;
+        if (flip) { r = R - 1 - r; s = S - 1 - s; }
+        float v = Wt[(((int64_t)k * C + c) * R + r) * S + s];
+        if (SPLIT) {
+            float h, l;
+            split_tf32(v, h, l);
+            hi[o] = h;
+            lo[o] = l;
+        } else {
+            hi[o] = v;
+        }
+    }
+}
+
+// Picks the pixel box {bw, bh, bn} (product <= 128) that wastes the fewest accumulator rows.
+void choose_box(int OW, int OH, int N, int* bw_, int* bh_, int* bn_) {
+    double best = -1.0;
+    int bbw = 1, bbh = 1, bbn = 1;
+    for (int bw = 1; bw <= OW && bw <= 128; ++bw) {
+        for (int bh = 1; bh <= OH && bw * bh <= 128; ++bh) {
+            int bn = 128 / (bw * bh);
+            if (bn > N) bn = N;
+            if (bn > 128) bn = 128;
+            int64_t tiles = (int64_t)((OW + bw - 1) / bw) * ((OH + bh - 1) / bh) * ((N + bn - 1) / bn);
+            double eff = (double)OW * OH * N / ((double)tiles * 128.0);
+            // prefer long contiguous output runs at equal efficiency
+            double score = eff + 1e-4 * bw;
+            if (score > best) { best = score; bbw = bw; bbh = bh; bbn = bn; }
+        }
+    }
+    *bw_ = bbw; *bh_ = bbh; *bn_ = bbn;
+}
+
+struct IgemmCall {
+    // logical problem: out[N, Kout, OH, OW] from act[N, Cin, IH, IW] (NCHW in memory)
+    int N, Cin, IH, IW, Kout, OH, OW, R, S, ph, pw;
+    const float* act;   // NCHW activations (X or ug)
+    const float* wt;    // [K, C, R, S] weights as the reference stores them
+    int wK, wC;         // the K and C extents of `wt`
+    int flip;           // 0 forward, 1 input gradient
+    float* out;
+    const float* bias;
+    int accumulate;
+};
+
+template <int BN>
+int32_t launch_igemm(mtl_ctx* ctx, const CUtensorMap* maps, const ConvTcParams& p) {
+    using C = Cfg<BN>;
+    auto kern = k_conv_igemm<BN>;
+    MTL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    int tiles = p.tiles_w * p.tiles_h * p.tiles_nb * p.tiles_k;
+    int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    kern<<<grid, kThreads, C::kSmemBytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
+int32_t run_igemm(mtl_ctx* ctx, const IgemmCall& c, int x3) {
+    const int HW = c.IH * c.IW;
+    const size_t n_act = (size_t)c.N * c.Cin * HW;
+    const size_t n_wt = (size_t)c.wK * c.wC * c.R * c.S;
+    const size_t act_pad = (n_act + 63) & ~(size_t)63, wt_pad = (n_wt + 63) & ~(size_t)63;
+    const int parts = x3 ? 2 : 1;
+    void* ws;
+    int32_t rc = mtl_workspace(ctx, (size_t)parts * (act_pad + wt_pad) * 4, &ws);
+    if (rc) return rc;
+    float* a_hi = (float*)ws;
+    float* a_lo = x3 ? a_hi + act_pad : nullptr;
+    float* w_hi = a_hi + (size_t)parts * act_pad;
+    float* w_lo = x3 ? w_hi + wt_pad : nullptr;
+
+    dim3 tgrid((unsigned)((HW + 31) / 32), (unsigned)((c.Cin + 31) / 32), (unsigned)c.N);
+    MTL_REQUIRE(ctx, c.N <= 65535 && tgrid.y <= 65535u, "batch too large for the layout pass");
+    if (x3) k_nchw_to_nhwc<true><<<tgrid, 256, 0, ctx->stream>>>(a_hi, a_lo, c.act, c.Cin, HW);
+    else k_nchw_to_nhwc<false><<<tgrid, 256, 0, ctx->stream>>>(a_hi, a_lo, c.act, c.Cin, HW);
+    MTL_LAUNCHED(ctx);
+    int wgrid = mtl_grid_for((int64_t)n_wt, 256, ctx->sm_count, 8);
+    if (x3) k_weights_relayout<true><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
+    else k_weights_relayout<false><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
+    MTL_LAUNCHED(ctx);
+
+    ConvTcParams p;
+    p.N = c.N; p.OH = c.OH; p.OW = c.OW; p.Kout = c.Kout; p.Cin = c.Cin;
+    p.R = c.R; p.S = c.S; p.ph = c.ph; p.pw = c.pw;
+    choose_box(c.OW, c.OH, c.N, &p.bw, &p.bh, &p.bn);
+    p.tiles_w = (c.OW + p.bw - 1) / p.bw;
+    p.tiles_h = (c.OH + p.bh - 1) / p.bh;
+    p.tiles_nb = (c.N + p.bn - 1) / p.bn;
+    const int BN = c.Kout > 64 ? 128 : 64;
+    p.tiles_k = (c.Kout + BN - 1) / BN;
+    p.nseg = x3 ? 3 : 1;
+    if (x3) { p.segA[0] = 1; p.segB[0] = 0; p.segA[1] = 0; p.segB[1] = 1; p.segA[2] = 0; p.segB[2] = 0; }
+    else    { p.segA[0] = p.segA[1] = p.segA[2] = 0; p.segB[0] = p.segB[1] = p.segB[2] = 0; }
+    p.a_bytes = (uint32_t)(p.bw * p.bh * p.bn) * 128u;
+    p.out = c.out; p.bias = c.bias; p.accumulate = c.accumulate; p.status = ctx->dev_status;
+
+    CUtensorMap maps[4];
+    for (int i = 0; i < 2; ++i) {
+        const float* a = (i == 1 && x3) ? a_lo : a_hi;
+        const float* w = (i == 1 && x3) ? w_lo : w_hi;
+        uint64_t adims[4] = {(uint64_t)c.Cin, (uint64_t)c.IW, (uint64_t)c.IH, (uint64_t)c.N};
+        uint64_t astr[3] = {(uint64_t)c.Cin * 4, (uint64_t)c.IW * c.Cin * 4, (uint64_t)c.IH * c.IW * c.Cin * 4};
+        uint32_t abox[4] = {BK, (uint32_t)p.bw, (uint32_t)p.bh, (uint32_t)p.bn};
+        rc = mtl_encode_tmap(ctx, &maps[i], a, 4, adims, astr, abox);
+        if (rc) return rc;
+        uint64_t wdims[3] = {(uint64_t)c.Cin, (uint64_t)c.Kout, (uint64_t)(c.R * c.S)};
+        uint64_t wstr[2] = {(uint64_t)c.Cin * 4, (uint64_t)c.Kout * c.Cin * 4};
+        uint32_t wbox[3] = {BK, (uint32_t)BN, 1};
+        rc = mtl_encode_tmap(ctx, &maps[2 + i], w, 3, wdims, wstr, wbox);
+        if (rc) return rc;
+    }
+    if (BN == 128) return launch_igemm<128>(ctx, maps, p);
+    return launch_igemm<64>(ctx, maps, p);
+}
+
+bool igemm_geometry_ok(const ConvGeom& g) {
+    return g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1;
+}
+
+}  // namespace
+
+bool mtl_conv_fwd_tc_supported(const ConvGeom& g, const float* X, const float* Wt, const float* Y) {
+    if (!igemm_geometry_ok(g)) return false;
+    if (g.C < 16 || (g.C % 4) || g.K < 16) return false;
+    if ((int64_t)g.N * g.OH * g.OW < 128) return false;
+    if ((((uintptr_t)X) | ((uintptr_t)Wt) | ((uintptr_t)Y)) & 15u) return false;
+    return true;
+}
+
+bool mtl_conv_dgrad_tc_supported(const ConvGeom& g, const float* ug, const float* Wt, const float* dX) {
+    if (!igemm_geometry_ok(g)) return false;
+    if (g.K < 16 || (g.K % 4) || g.C < 16) return false;
+    if ((int64_t)g.N * g.H * g.W < 128) return false;
+    if (g.ph > g.R - 1 || g.pw > g.S - 1) return false;
+    if ((((uintptr_t)ug) | ((uintptr_t)Wt) | ((uintptr_t)dX)) & 15u) return false;
+    return true;
+}
+
+int32_t mtl_conv_fwd_tc(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
+                        const ConvGeom& g, int x3) {
+    IgemmCall c;
+    c.N = g.N; c.Cin = g.C; c.IH = g.H; c.IW = g.W; c.Kout = g.K; c.OH = g.OH; c.OW = g.OW;
+    c.R = g.R; c.S = g.S; c.ph = g.ph; c.pw = g.pw;
+    c.act = X; c.wt = Wt; c.wK = g.K; c.wC = g.C; c.flip = 0;
+    c.out = Y; c.bias = bias; c.accumulate = 0;
+    return run_igemm(ctx, c, x3);
+}
+
+int32_t mtl_conv_dgrad_tc(mtl_ctx* ctx, float* dX, const float* ug, const float* Wt, const ConvGeom& g,
+                          int accumulate, int x3) {
+    IgemmCall c;
+    c.N = g.N; c.Cin = g.K; c.IH = g.OH; c.IW = g.OW; c.Kout = g.C; c.OH = g.H; c.OW = g.W;
+    c.R = g.R; c.S = g.S; c.ph = g.R - 1 - g.ph; c.pw = g.S - 1 - g.pw;
+    c.act = ug; c.wt = Wt; c.wK = g.K; c.wC = g.C; c.flip = 1;
+    c.out = dX; c.bias = nullptr; c.accumulate = accumulate;
+    return run_igemm(ctx, c, x3);
+}
+
+bool mtl_conv_wgrad_tc_supported(const ConvGeom&, const float*, const float*, const float*) { return false; }
+int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float*, const float*, const float*, const ConvGeom&, int, int) {
+    return mtl_set_error(ctx, MTL_ERR_UNSUPPORTED, "tensor-core kernel gradient not available");
+}

@@ -1,0 +1,171 @@
+// Data-parallel gradient exchange: one process per GPU, sum-allreduce of the flat gradient arena
+// over NVLink through NCCL on a separate communication stream, event-ordered against the compute
+// stream so that the exchange of a finished gradient bucket overlaps the backward pass of earlier
+// layers.  NCCL is bound at run time (dlopen) so that single-GPU use needs no NCCL at all.
+#include <dlfcn.h>
+
+#include "common.cuh"
+
+namespace {
+
+// Minimal NCCL ABI (stable across 2.x): only the calls used here.
+typedef struct ncclComm* ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+enum { ncclSuccess = 0 };
+enum { ncclFloat32 = 7 };
+enum { ncclSum = 0 };
+
+struct NcclApi {
+    void* lib = nullptr;
+    int (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    int (*CommDestroy)(ncclComm_t) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*Broadcast)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+};
+
+NcclApi g_nccl;
+
+bool load_nccl(char* why, size_t why_len) {
+    if (g_nccl.lib) return true;
+    const char* names[] = {getenv("MANTLE_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
+    void* lib = nullptr;
+    for (const char* n : names) {
+        if (!n || !n[0]) continue;
+        lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (lib) break;
+    }
+    if (!lib) {
+        snprintf(why, why_len, "cannot load libnccl.so.2: %s", dlerror());
+        return false;
+    }
+#define MTL_SYM(field, name)                                         \
+    *(void**)(&g_nccl.field) = dlsym(lib, name);                     \
+    if (!g_nccl.field) {                                             \
+        snprintf(why, why_len, "libnccl lacks symbol %s", name);     \
+        return false;                                                \
+    }
+    MTL_SYM(GetUniqueId, "ncclGetUniqueId")
+    MTL_SYM(CommInitRank, "ncclCommInitRank")
+    MTL_SYM(CommDestroy, "ncclCommDestroy")
+    MTL_SYM(AllReduce, "ncclAllReduce")
+    MTL_SYM(Broadcast, "ncclBroadcast")
+    MTL_SYM(GetErrorString, "ncclGetErrorString")
+#undef MTL_SYM
+    g_nccl.lib = lib;
+    return true;
+}
+
+struct DpState {
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+    cudaStream_t comm_stream = nullptr;
+    cudaEvent_t ready = nullptr;  // compute -> comm
+    cudaEvent_t done = nullptr;   // comm -> compute
+    bool pending = false;
+};
+
+#define MTL_NCCL(ctx, call)                                                                      \
+    do {                                                                                         \
+        int r__ = (call);                                                                        \
+        if (r__ != ncclSuccess)                                                                  \
+            return mtl_set_error(ctx, MTL_ERR_COMM, "%s failed: %s", #call, g_nccl.GetErrorString(r__)); \
+    } while (0)
+
+}  // namespace
+
+extern "C" {
+
+int32_t mtl_dp_get_unique_id(uint8_t* out_id) {
+    if (!out_id) return MTL_ERR_INVALID;
+    char why[256];
+    if (!load_nccl(why, sizeof(why))) {
+        fprintf(stderr, "[mantle_cuda] %s\n", why);
+        return MTL_ERR_COMM;
+    }
+    ncclUniqueId id;
+    if (g_nccl.GetUniqueId(&id) != ncclSuccess) return MTL_ERR_COMM;
+    static_assert(sizeof(id) == MTL_DP_ID_BYTES, "unique id size");
+    memcpy(out_id, &id, MTL_DP_ID_BYTES);
+    return MTL_OK;
+}
+
+int32_t mtl_dp_init(mtl_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, id && world >= 1 && rank >= 0 && rank < world, "bad arguments to mtl_dp_init");
+    MTL_REQUIRE(ctx, !ctx->dp, "data-parallel group already initialised on this context");
+    char why[256];
+    if (!load_nccl(why, sizeof(why))) return mtl_set_error(ctx, MTL_ERR_COMM, "%s", why);
+    MTL_CUDA(ctx, cudaSetDevice(ctx->device));
+    DpState* st = new DpState();
+    st->rank = rank;
+    st->world = world;
+    ncclUniqueId uid;
+    memcpy(&uid, id, MTL_DP_ID_BYTES);
+    int r = g_nccl.CommInitRank(&st->comm, world, uid, rank);
+    if (r != ncclSuccess) {
+        delete st;
+        return mtl_set_error(ctx, MTL_ERR_COMM, "ncclCommInitRank failed: %s", g_nccl.GetErrorString(r));
+    }
+    if (cudaStreamCreateWithFlags(&st->comm_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&st->ready, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&st->done, cudaEventDisableTiming) != cudaSuccess) {
+        g_nccl.CommDestroy(st->comm);
+        delete st;
+        return mtl_set_error(ctx, MTL_ERR_CUDA, "could not create the communication stream");
+    }
+    ctx->dp = st;
+    return MTL_OK;
+}
+
+int32_t mtl_dp_allreduce_async(mtl_ctx* ctx, float* buf, int64_t n) {
+    MTL_CHECK_CTX(ctx);
+    DpState* st = (DpState*)ctx->dp;
+    MTL_REQUIRE(ctx, st, "mtl_dp_init has not been called");
+    MTL_REQUIRE(ctx, buf && n >= 0, "bad arguments to mtl_dp_allreduce_async");
+    if (n == 0 || st->world == 1) return MTL_OK;
+    MTL_CUDA(ctx, cudaEventRecord(st->ready, ctx->stream));
+    MTL_CUDA(ctx, cudaStreamWaitEvent(st->comm_stream, st->ready, 0));
+    MTL_NCCL(ctx, g_nccl.AllReduce(buf, buf, (size_t)n, ncclFloat32, ncclSum, st->comm, st->comm_stream));
+    st->pending = true;
+    return MTL_OK;
+}
+
+int32_t mtl_dp_wait(mtl_ctx* ctx) {
+    MTL_CHECK_CTX(ctx);
+    DpState* st = (DpState*)ctx->dp;
+    MTL_REQUIRE(ctx, st, "mtl_dp_init has not been called");
+    if (!st->pending) return MTL_OK;
+    MTL_CUDA(ctx, cudaEventRecord(st->done, st->comm_stream));
+    MTL_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, st->done, 0));
+    st->pending = false;
+    return MTL_OK;
+}
+
+int32_t mtl_dp_broadcast(mtl_ctx* ctx, float* buf, int64_t n, int32_t root) {
+    MTL_CHECK_CTX(ctx);
+    DpState* st = (DpState*)ctx->dp;
+    MTL_REQUIRE(ctx, st, "mtl_dp_init has not been called");
+    MTL_REQUIRE(ctx, buf && n >= 0 && root >= 0 && root < st->world, "bad arguments to mtl_dp_broadcast");
+    if (n == 0 || st->world == 1) return MTL_OK;
+    MTL_NCCL(ctx, g_nccl.Broadcast(buf, buf, (size_t)n, ncclFloat32, root, st->comm, ctx->stream));
+    return MTL_OK;
+}
+
+int32_t mtl_dp_destroy(mtl_ctx* ctx) {
+    MTL_CHECK_CTX(ctx);
+    DpState* st = (DpState*)ctx->dp;
+    if (!st) return MTL_OK;
+    cudaStreamSynchronize(st->comm_stream);
+    cudaStreamSynchronize(ctx->stream);
+    if (st->comm) g_nccl.CommDestroy(st->comm);
+    cudaEventDestroy(st->ready);
+    cudaEventDestroy(st->done);
+    cudaStreamDestroy(st->comm_stream);
+    delete st;
+    ctx->dp = nullptr;
+    return MTL_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,424 @@
+// OP.DOT on the 5th-generation tensor cores: C[M,N] (+)= op(A) . op(B) with tcgen05.mma
+// kind::tf32, fp32 accumulators in tensor memory, operands staged by TMA into 128-byte-swizzled
+// shared memory.  One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer (one lane), ring of STAGES operand buffers
+//   warp 1      MMA issuer (one lane); owns the tensor-memory allocation
+//   warps 2-5   epilogue: tcgen05.ld -> registers -> global, overlapped with the next tile's
+//               main loop through two accumulator buffers in tensor memory
+// The same kernel serves the three products of DOT: forward (A row-major = K-major,
+// B row-major = N-major), dA = ug . B^T (both K-major) and dB = A^T . ug (both MN-major); no
+// transpose pass is needed (the reference transposes physically, matmul.mojo:175-210).
+// 3xTF32: the operands are split beforehand into tf32-exact hi and residual lo arrays and the K
+// loop runs over the three products lo*hi, hi*lo, hi*hi into the same accumulator.
+#include "common.cuh"
+#include "sm100.cuh"
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;  // 32 fp32 = one 128-byte swizzle row
+constexpr int kThreads = 192;
+constexpr uint64_t kWaitBudgetNs = 4000000000ull;  // 4 s: far beyond any legitimate wait
+
+template <int BN>
+struct Cfg {
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kABytes = BM * BK * 4;
+    static constexpr int kBBytes = BN * BK * 4;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTmemCols = 2 * BN;  // two accumulators
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+struct GemmParams {
+    int M, N, K;
+    int nseg;           // 1 (plain tf32) or 3 (hi/lo split products)
+    int segA[3], segB[3];  // which map (0 = hi, 1 = lo) each K segment reads
+    float* C;
+    int accumulate;
+    int32_t* status;
+};
+
+// Tile order: groups of 16 tile-rows; inside a group the tile-column changes slowest so that
+// CTAs running at the same time share B tiles and a bounded set of A tiles in L2.
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+    constexpr int G = 16;
+    int per_group = G * tiles_n;
+    int g = t / per_group;
+    int r = t - g * per_group;
+    int rows = min(G, tiles_m - g * G);
+    tm = g * G + r % rows;
+    tn = r / rows;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
+            const __grid_constant__ CUtensorMap mapB0, const __grid_constant__ CUtensorMap mapB1, GemmParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzle needs 1024-byte aligned tiles
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+    uint64_t* full = bars;                       // [kStages]
+    uint64_t* empty = bars + C::kStages;         // [kStages]
+    uint64_t* tmem_full = bars + 2 * C::kStages;  // [2]
+    uint64_t* tmem_empty = tmem_full + 2;         // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int tiles_m = (p.M + BM - 1) / BM;
+    const int tiles_n = (p.N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int kb_per_seg = (p.K + BK - 1) / BK;
+    const int kb_total = kb_per_seg * p.nseg;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tmem_full[a], 1);
+            mbar_init(&tmem_empty[a], 128);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&mapA0);
+        prefetch_tensormap(&mapB0);
+        if (p.nseg > 1) {
+            prefetch_tensormap(&mapA1);
+            prefetch_tensormap(&mapB1);
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer ----------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                int tm, tn;
+                tile_coords(t, tiles_m, tiles_n, tm, tn);
+                const int m0 = tm * BM, n0 = tn * BN;
+                for (int kb = 0; kb < kb_total; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+                    const int seg = kb / kb_per_seg;
+                    const int k0 = (kb - seg * kb_per_seg) * BK;
+                    const CUtensorMap* ma = p.segA[seg] ? &mapA1 : &mapA0;
+                    const CUtensorMap* mb = p.segB[seg] ? &mapB1 : &mapB0;
+                    uint8_t* sa = tiles + stage * C::kStageBytes;
+                    uint8_t* sb = sa + C::kABytes;
+                    mbar_arrive_expect_tx(&full[stage], C::kStageBytes);
+                    if (A_MN) {
+                        // A stored [K, M]: chunks of 32 m x 32 k, 4 KB each
+#pragma unroll
+                        for (int c = 0; c < BM / 32; ++c) tma_load_2d(sa + c * 4096, ma, &full[stage], m0 + c * 32, k0);
+                    } else {
+                        tma_load_2d(sa, ma, &full[stage], k0, m0);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int c = 0; c < BN / 32; ++c) tma_load_2d(sb + c * 4096, mb, &full[stage], n0 + c * 32, k0);
+                    } else {
+                        tma_load_2d(sb, mb, &full[stage], k0, n0);
+                    }
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) atomicExch(p.status, MTL_ERR_TIMEOUT);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer ------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_tf32(BN, A_MN, B_MN);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int local = 0;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+                const int acc = local & 1;
+                const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < kb_total; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(tiles + stage * C::kStageBytes);
+                    const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+                    for (int kk = 0; kk < BK / 8; ++kk) {
+                        // K-major: rows of 128 B, 8-row groups 1024 B apart, step 32 B along K.
+                        // MN-major: 32-wide chunks 4096 B apart, 8-row K groups 1024 B apart.
+                        const uint64_t da = A_MN ? make_smem_desc(sa + kk * 1024, 4096, 1024)
+                                                 : make_smem_desc(sa + kk * 32, 16, 1024);
+                        const uint64_t db = B_MN ? make_smem_desc(sb + kk * 1024, 4096, 1024)
+                                                 : make_smem_desc(sb + kk * 32, 16, 1024);
+                        mma_tf32(tmem_d, da, db, idesc, (kb | kk) ? 1u : 0u);
+                    }
+                    mma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
+                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) mma_commit(&tmem_full[acc]);
+            }
+            if (!ok) atomicExch(p.status, MTL_ERR_TIMEOUT);
+        }
+    } else {
+        // ------------------------------------------------------------- epilogue --------------
+        const int quad = warp & 3;  // tensor-memory lanes [32*quad, 32*quad + 32)
+        const bool vec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
+        bool ok = true;
+        int local = 0;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+            int tm, tn;
+            tile_coords(t, tiles_m, tiles_n, tm, tn);
+            const int acc = local & 1;
+            const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+            if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+            tc_fence_after_sync();
+            const int m = tm * BM + quad * 32 + lane;
+            const int n_base = tn * BN;
+            float* crow = p.C + (int64_t)m * p.N;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
+                tmem_ld_wait();
+                const int n0 = n_base + c * 32;
+                if (m < p.M) {
+                    if (vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            if (n0 + j < p.N) {
+                                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                                float4* dst = reinterpret_cast<float4*>(crow + n0 + j);
+                                if (p.accumulate) {
+                                    float4 o = *dst;
+                                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                                }
+                                *dst = v;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (n0 + j < p.N) {
+                                float v = __uint_as_float(r[j]);
+                                crow[n0 + j] = p.accumulate ? crow[n0 + j] + v : v;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tmem_empty[acc]);
+        }
+        if (!ok && lane == 0) atomicExch(p.status, MTL_ERR_TIMEOUT);
+    }
+
+    // teardown: everyone meets here, then the allocating warp returns the tensor memory
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// hi = x rounded to tf32 (low 13 mantissa bits zero), lo = x - hi (exact in fp32)
+__global__ void __launch_bounds__(256) k_split_tf32(float* __restrict__ hi, float* __restrict__ lo,
+                                                    const float* __restrict__ x, int64_t n) {
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    int64_t n4 = n >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    float4* h4 = reinterpret_cast<float4*>(hi);
+    float4* l4 = reinterpret_cast<float4*>(lo);
+    auto split = [](float v, float& h, float& l) {
+        uint32_t u;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+        h = __uint_as_float(u);
+        l = v - h;
+    };
+    for (int64_t i = tid; i < n4; i += stride) {
+        float4 v = x4[i], h, l;
+        split(v.x, h.x, l.x); split(v.y, h.y, l.y); split(v.z, h.z, l.z); split(v.w, h.w, l.w);
+        h4[i] = h;
+        l4[i] = l;
+    }
+    for (int64_t i = (n4 << 2) + tid; i < n; i += stride) split(x[i], hi[i], lo[i]);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int32_t launch_gemm(mtl_ctx* ctx, const CUtensorMap* maps, const GemmParams& p) {
+    using C = Cfg<BN>;
+    auto kern = k_gemm_tf32<BN, A_MN, B_MN>;
+    MTL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    kern<<<grid, kThreads, C::kSmemBytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
+}  // namespace
+
+int32_t mtl_encode_tmap(mtl_ctx* ctx, CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                        const uint64_t* strides_bytes, const uint32_t* box) {
+    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    if (!ctx->encode_tiled) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+            cudaGetLastError();
+            return mtl_set_error(ctx, MTL_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+        }
+        ctx->encode_tiled = fn;
+    }
+    cuuint64_t gdim[5];
+    cuuint64_t gstr[4];
+    cuuint32_t gbox[5];
+    cuuint32_t estr[5];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        gbox[i] = box[i];
+        estr[i] = 1;
+        if (i > 0) gstr[i - 1] = strides_bytes[i - 1];
+    }
+    CUresult r = ((encode_fn)ctx->encode_tiled)(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank,
+                                               const_cast<void*>(base), gdim, gstr, gbox, estr,
+                                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return mtl_set_error(ctx, MTL_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d)", (int)r, rank);
+    return MTL_OK;
+}
+
+bool mtl_gemm_tc_supported(int64_t M, int64_t N, int64_t K, int transA, int transB, const float* A,
+                           const float* B, const float* C) {
+    if (M < 128 || N < 128 || K < 32) return false;
+    if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return false;
+    if ((((uintptr_t)A) | ((uintptr_t)B) | ((uintptr_t)C)) & 15u) return false;
+    // global strides of a tensor map must be multiples of 16 bytes
+    int64_t lda = transA ? M : K;  // contiguous extent of A's rows
+    int64_t ldb = transB ? K : N;
+    if ((lda % 4) || (ldb % 4)) return false;
+    return true;
+}
+
+int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int64_t M, int64_t N, int64_t K,
+                    int transA, int transB, int accumulate, int x3) {
+    if (!mtl_gemm_tc_supported(M, N, K, transA, transB, A, B, C))
+        return mtl_set_error(ctx, MTL_ERR_UNSUPPORTED, "shape not supported by the tensor-core DOT kernel");
+    const int BN = N >= 256 ? 256 : 128;
+    const float* a_src[2] = {A, nullptr};
+    const float* b_src[2] = {B, nullptr};
+    if (x3) {
+        size_t na = (size_t)M * K, nb = (size_t)K * N;
+        size_t na_pad = (na + 63) & ~(size_t)63, nb_pad = (nb + 63) & ~(size_t)63;
+        void* ws;
+        int32_t rc = mtl_workspace(ctx, (2 * na_pad + 2 * nb_pad) * sizeof(float), &ws);
+        if (rc) return rc;
+        float* w = (float*)ws;
+        float *ahi = w, *alo = w + na_pad, *bhi = w + 2 * na_pad, *blo = w + 2 * na_pad + nb_pad;
+        int g1 = mtl_grid_for((int64_t)(na + 3) / 4, 256, ctx->sm_count, 8);
+        k_split_tf32<<<g1, 256, 0, ctx->stream>>>(ahi, alo, A, (int64_t)na);
+        MTL_LAUNCHED(ctx);
+        int g2 = mtl_grid_for((int64_t)(nb + 3) / 4, 256, ctx->sm_count, 8);
+        k_split_tf32<<<g2, 256, 0, ctx->stream>>>(bhi, blo, B, (int64_t)nb);
+        MTL_LAUNCHED(ctx);
+        a_src[0] = ahi; a_src[1] = alo;
+        b_src[0] = bhi; b_src[1] = blo;
+    }
+    CUtensorMap maps[4];
+    for (int i = 0; i < 2; ++i) {
+        const float* a = a_src[i] ? a_src[i] : a_src[0];
+        const float* b = b_src[i] ? b_src[i] : b_src[0];
+        uint64_t dims[2], strides[1];
+        uint32_t box[2];
+        if (transA) { dims[0] = (uint64_t)M; dims[1] = (uint64_t)K; box[0] = 32; box[1] = BK; }
+        else        { dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = BK; box[1] = BM; }
+        strides[0] = dims[0] * 4;
+        int32_t rc = mtl_encode_tmap(ctx, &maps[i], a, 2, dims, strides, box);
+        if (rc) return rc;
+        if (transB) { dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = BK; box[1] = (uint32_t)BN; }
+        else        { dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 32; box[1] = BK; }
+        strides[0] = dims[0] * 4;
+        rc = mtl_encode_tmap(ctx, &maps[2 + i], b, 2, dims, strides, box);
+        if (rc) return rc;
+    }
+    GemmParams p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.nseg = x3 ? 3 : 1;
+    // small terms first: lo*hi, hi*lo, then hi*hi
+    if (x3) { p.segA[0] = 1; p.segB[0] = 0; p.segA[1] = 0; p.segB[1] = 1; p.segA[2] = 0; p.segB[2] = 0; }
+    else    { p.segA[0] = p.segA[1] = p.segA[2] = 0; p.segB[0] = p.segB[1] = p.segB[2] = 0; }
+    p.C = C;
+    p.accumulate = accumulate ? 1 : 0;
+    p.status = ctx->dev_status;
+    const bool a_mn = transA != 0, b_mn = transB == 0;
+#define MTL_DISPATCH(BN_)                                                                     \
+    if (a_mn && b_mn) return launch_gemm<BN_, true, true>(ctx, maps, p);                     \
+    if (a_mn && !b_mn) return launch_gemm<BN_, true, false>(ctx, maps, p);                   \
+    if (!a_mn && b_mn) return launch_gemm<BN_, false, true>(ctx, maps, p);                   \
+    return launch_gemm<BN_, false, false>(ctx, maps, p);
+    if (BN == 256) { MTL_DISPATCH(256) }
+    MTL_DISPATCH(128)
+#undef MTL_DISPATCH
+}
+
+extern "C" {
+
+int32_t mtl_dot_fwd(mtl_ctx* ctx, float* C, const float* A, const float* B, int64_t M, int64_t K, int64_t N) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, C && A && B, "null pointer in mtl_dot_fwd");
+    MTL_REQUIRE(ctx, M >= 1 && K >= 1 && N >= 1, "DOT extents must be positive");
+    if (ctx->math_mode != MTL_MATH_FP32 && mtl_gemm_tc_supported(M, N, K, 0, 0, A, B, C))
+        return mtl_gemm_tc(ctx, C, A, B, M, N, K, 0, 0, 0, ctx->math_mode == MTL_MATH_TF32X3);
+    return mtl_gemm_simt(ctx, C, A, B, M, N, K, 0, 0, 0);
+}
+
+int32_t mtl_dot_bwd(mtl_ctx* ctx, int32_t tensor_id, float* grad, const float* ug, const float* A,
+                    const float* B, int64_t M, int64_t K, int64_t N, int32_t accumulate) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, tensor_id == 0 || tensor_id == 1, "tensor_id must be 0 or 1");
+    MTL_REQUIRE(ctx, grad && ug, "null pointer in mtl_dot_bwd");
+    MTL_REQUIRE(ctx, M >= 1 && K >= 1 && N >= 1, "DOT extents must be positive");
+    const bool tc = ctx->math_mode != MTL_MATH_FP32;
+    const int x3 = ctx->math_mode == MTL_MATH_TF32X3;
+    if (tensor_id == 0) {
+        // grad[M,K] = ug[M,N] . B[K,N]^T : product extents (M, K, N)
+        MTL_REQUIRE(ctx, B, "dA needs B");
+        if (tc && mtl_gemm_tc_supported(M, K, N, 0, 1, ug, B, grad))
+            return mtl_gemm_tc(ctx, grad, ug, B, M, K, N, 0, 1, accumulate, x3);
+        return mtl_gemm_simt(ctx, grad, ug, B, M, K, N, 0, 1, accumulate);
+    }
+    // grad[K,N] = A[M,K]^T . ug[M,N] : product extents (K, N, M)
+    MTL_REQUIRE(ctx, A, "dB needs A");
+    if (tc && mtl_gemm_tc_supported(K, N, M, 1, 0, A, ug, grad))
+        return mtl_gemm_tc(ctx, grad, A, ug, K, N, M, 1, 0, accumulate, x3);
+    return mtl_gemm_simt(ctx, grad, A, ug, K, N, M, 1, 0, accumulate);
+}
+
+}  // extern "C"
