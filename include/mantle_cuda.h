@@ -265,6 +265,8 @@ MTL_API int32_t mtl_dp_wait(mtl_ctx* ctx);
 /* Broadcast `n` floats from `root` (initial parameters). */
 MTL_API int32_t mtl_dp_broadcast(mtl_ctx* ctx, float* buf, int64_t n, int32_t root);
 MTL_API int32_t mtl_dp_destroy(mtl_ctx* ctx);
+/* Number of ranks joined by mtl_dp_init, 1 when the context is not part of a group. */
+MTL_API int32_t mtl_dp_world_size(mtl_ctx* ctx);
 
 #ifdef __cplusplus
 }

@@ -153,6 +153,11 @@ int32_t mtl_dp_broadcast(mtl_ctx* ctx, float* buf, int64_t n, int32_t root) {
     return MTL_OK;
 }
 
+int32_t mtl_dp_world_size(mtl_ctx* ctx) {
+    if (!ctx || !ctx->dp) return 1;
+    return ((DpState*)ctx->dp)->world;
+}
+
 int32_t mtl_dp_destroy(mtl_ctx* ctx) {
     MTL_CHECK_CTX(ctx);
     DpState* st = (DpState*)ctx->dp;

@@ -1,0 +1,495 @@
+// Graph shape rules, the executor and Adam on top of the C ABI (see model.hpp).
+#include "model.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+namespace mantle {
+
+// ------------------------------------------------------------------ shapes -----------------
+
+// broadcast_shapes, mantle/core/tensorutils.mojo:89-127
+TensorShape Graph::broadcast_shapes(const TensorShape& s1, const TensorShape& s2) {
+    int ndim = std::max(s1.rank, s2.rank);
+    int diff = std::abs(s1.rank - s2.rank);
+    const TensorShape& big = s1.rank > s2.rank ? s1 : s2;
+    const TensorShape& small = s1.rank > s2.rank ? s2 : s1;
+    TensorShape res;
+    res.rank = ndim;
+    for (int i = ndim - 1; i >= diff; --i) {
+        int64_t a = big.dims[i], b = small.dims[i - diff];
+        if (a == b) res.dims[i] = a;
+        else if (a == 1 || b == 1) res.dims[i] = a * b;
+        else throw Error(MTL_ERR_INVALID, "shapes cannot be broadcast together");
+    }
+    for (int i = diff - 1; i >= 0; --i) res.dims[i] = big.dims[i];
+    return res;
+}
+
+// get_reduce_shape, tensorutils.mojo:601-619; no axis -> [1] (basics.mojo:383-391)
+TensorShape Graph::reduce_shape(const TensorShape& t, const Attributes& a) {
+    if (!a.axis) return TensorShape{1};
+    int axis = *a.axis;
+    if (axis < 0 || axis >= t.rank) throw Error(MTL_ERR_INVALID, "reduction axis out of range");
+    TensorShape r = t;
+    r.dims[axis] = 1;
+    return r;
+}
+
+// get_result_shape, mantle/autograd/ops/conv.mojo:25-58
+void Graph::conv_out(const TensorShape& in, int R, int S, const Attributes& a, int64_t* oh, int64_t* ow) {
+    auto fd = [](int64_t x, int64_t y) {
+        int64_t q = x / y;
+        if ((x % y != 0) && ((x < 0) != (y < 0))) --q;
+        return q;
+    };
+    *oh = fd(in[-2] + 2 * a.padding[0] - (int64_t)a.dilation[0] * (R - 1) - 1, a.stride[0]) + 1;
+    *ow = fd(in[-1] + 2 * a.padding[1] - (int64_t)a.dilation[1] * (S - 1) - 1, a.stride[1]) + 1;
+}
+
+TensorShape Graph::static_result_shape(int op, const std::vector<Symbol>& o, const Attributes& a) {
+    auto need = [&](size_t n) {
+        if (o.size() != n) throw Error(MTL_ERR_INVALID, "wrong number of operands for operator");
+    };
+    switch (op) {
+        case MTL_OP_ADD: case MTL_OP_SUB: case MTL_OP_MUL: case MTL_OP_DIV:
+            need(2);
+            return broadcast_shapes(o[0].shape, o[1].shape);
+        case MTL_OP_POW:
+            need(2);
+            return o[0].shape;
+        case MTL_OP_DOT:
+            need(2);
+            if (o[0].shape.rank != 2 || o[1].shape.rank != 2 || o[0].shape[1] != o[1].shape[0])
+                throw Error(MTL_ERR_INVALID, "DOT needs [M,K] . [K,N]");
+            return TensorShape{o[0].shape[0], o[1].shape[1]};
+        case MTL_OP_EXP: case MTL_OP_LOG: case MTL_OP_SIGMOID: case MTL_OP_RELU: case MTL_OP_LEAKYRELU:
+        case MTL_OP_TANH: case MTL_OP_CLIP:
+            need(1);
+            return o[0].shape;
+        case MTL_OP_SUM: case MTL_OP_MEAN: case MTL_OP_MAX:
+            need(1);
+            return reduce_shape(o[0].shape, a);
+        case MTL_OP_FLATTEN:
+            need(1);
+            return TensorShape{o[0].shape[0], o[0].shape.num_elements() / o[0].shape[0]};
+        case MTL_OP_RESHAPE:
+            need(1);
+            if (!a.shape || a.shape->num_elements() != o[0].shape.num_elements())
+                throw Error(MTL_ERR_INVALID, "RESHAPE needs a shape attribute with the same number of elements");
+            return *a.shape;
+        case MTL_OP_SQUEEZE: {  // mlops.mojo:302-316
+            need(1);
+            TensorShape r;
+            for (int i = 0; i < o[0].shape.rank; ++i) {
+                bool listed = std::find(a.dims.begin(), a.dims.end(), i) != a.dims.end();
+                if ((a.dims.empty() && o[0].shape[i] == 1) || (listed && o[0].shape[i] == 1)) continue;
+                r.dims[r.rank++] = o[0].shape[i];
+            }
+            return r;
+        }
+        case MTL_OP_UNSQUEEZE: {  // mlops.mojo:336-353
+            need(1);
+            int new_rank = o[0].shape.rank + (int)a.dims.size();
+            if (new_rank > MTL_MAX_RANK) throw Error(MTL_ERR_INVALID, "rank above 8");
+            TensorShape r;
+            int j = 0;
+            for (int i = 0; i < new_rank; ++i) {
+                bool listed = std::find(a.dims.begin(), a.dims.end(), i) != a.dims.end() ||
+                              std::find(a.dims.begin(), a.dims.end(), i - new_rank) != a.dims.end();
+                r.dims[r.rank++] = listed ? 1 : o[0].shape[j++];
+            }
+            return r;
+        }
+        case MTL_OP_CONV2D: {  // conv.mojo:63-78
+            need(3);
+            if (o[0].shape.rank != 4 || o[1].shape.rank != 4 || o[0].shape[1] != o[1].shape[1])
+                throw Error(MTL_ERR_INVALID, "CONV2D needs [N,C,H,W] and [K,C,R,S]");
+            int64_t oh, ow;
+            conv_out(o[0].shape, (int)o[1].shape[2], (int)o[1].shape[3], a, &oh, &ow);
+            return TensorShape{o[0].shape[0], o[1].shape[0], oh, ow};
+        }
+        case MTL_OP_MAXPOOL2D: {  // pool.mojo:25-41
+            need(1);
+            if (o[0].shape.rank != 4) throw Error(MTL_ERR_INVALID, "MAXPOOL2D needs [N,C,H,W]");
+            int64_t oh, ow;
+            conv_out(o[0].shape, a.kernel_size[0], a.kernel_size[1], a, &oh, &ow);
+            return TensorShape{o[0].shape[0], o[0].shape[1], oh, ow};
+        }
+        case MTL_OP_FMA:
+            need(3);
+            return o[0].shape;
+        default:
+            throw Error(MTL_ERR_UNSUPPORTED, "operator id " + std::to_string(op) + " is not on the GPU path");
+    }
+}
+
+// ------------------------------------------------------------------ Model ------------------
+
+namespace {
+constexpr int64_t kAlign = 64;  // floats: 256-byte alignment of every tensor in the arenas
+int64_t align_up(int64_t n) { return (n + kAlign - 1) / kAlign * kAlign; }
+
+struct SplitMix {
+    uint64_t s;
+    explicit SplitMix(uint64_t seed) : s(seed) {}
+    uint64_t next() {
+        uint64_t z = (s += 0x9E3779B97F4A7C15ull);
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        return z ^ (z >> 31);
+    }
+    float uniform(float lo, float hi) { return lo + (hi - lo) * (float)((next() >> 40) * (1.0 / 16777216.0)); }
+};
+}  // namespace
+
+void Model::check(int rc, const char* what) const {
+    if (rc != MTL_OK) throw Error(rc, std::string(what) + ": " + mtl_last_error(ctx_));
+}
+
+Model::Model(mtl_ctx* ctx, const Graph& g, uint64_t init_seed) : ctx_(ctx), g_(g) {
+    if (!ctx) throw Error(MTL_ERR_INVALID, "null context");
+    // get_trainable_parameters order (optim.mojo:27-44) first, so that the span is contiguous
+    int64_t off = 0;
+    for (size_t i = 0; i < g_.params.size(); ++i) {
+        const Symbol& p = g_.params[i];
+        if (!p.trainable) continue;
+        trainable_.push_back(p);
+        trainable_off_.push_back(off);
+        tensor_off_[p.id] = off;
+        grad_off_[p.id] = off;
+        shapes_[p.id] = p.shape;
+        off += align_up(p.shape.num_elements());
+    }
+    n_trainable_ = off;
+    int64_t toff = off, goff = off;
+    auto add_tensor = [&](const Symbol& s) {
+        shapes_[s.id] = s.shape;
+        if (!tensor_off_.count(s.id)) {
+            tensor_off_[s.id] = toff;
+            toff += align_up(s.shape.num_elements());
+        }
+        if (s.trainable && !grad_off_.count(s.id)) {
+            grad_off_[s.id] = goff;
+            goff += align_up(s.shape.num_elements());
+        }
+    };
+    // allocate_tensor_memory / allocate_grad_memory walk order (model.mojo:332-395)
+    for (auto& s : g_.inputs) add_tensor(s);
+    for (auto& s : g_.params) add_tensor(s);
+    for (auto& n : g_.nodes)
+        for (auto& s : n.outputs) add_tensor(s);
+    n_tensor_floats_ = std::max<int64_t>(toff, kAlign);
+    n_grad_floats_ = std::max<int64_t>(goff, kAlign);
+    check(mtl_malloc(ctx_, (size_t)n_tensor_floats_ * 4, (void**)&tensors_), "tensor arena");
+    check(mtl_malloc(ctx_, (size_t)n_grad_floats_ * 4, (void**)&grads_), "gradient arena");
+    check(mtl_zero(ctx_, tensors_, (size_t)n_tensor_floats_ * 4), "zero tensors");
+    check(mtl_zero(ctx_, grads_, (size_t)n_grad_floats_ * 4), "zero grads");
+
+    // parameter initialisation (model.mojo:337-367)
+    for (size_t i = 0; i < g_.params.size(); ++i) {
+        const Symbol& p = g_.params[i];
+        const Param& v = g_.param_values[i];
+        int64_t n = p.shape.num_elements();
+        if (v.kind == Param::ZERO) continue;
+        std::vector<float> host((size_t)n, 0.0f);
+        if (v.kind == Param::DATA) {
+            for (size_t j = 0; j < v.data.size() && (int64_t)j < n; ++j) host[j] = v.data[j];
+            if (p.shape.is_scalar() && !v.data.empty()) scalar_values_[p.id] = v.data[0];
+        } else {
+            SplitMix rng(init_seed * 0x100000001B3ull + (uint64_t)p.id);
+            for (auto& x : host) x = rng.uniform(v.lo, v.hi);
+        }
+        check(mtl_h2d(ctx_, T(p), host.data(), (size_t)n * 4), "parameter upload");
+    }
+
+    // hidden argmax buffers for MAXPOOL2D nodes
+    for (size_t i = 0; i < g_.nodes.size(); ++i) {
+        if (g_.nodes[i].op != MTL_OP_MAXPOOL2D) continue;
+        int32_t* idx = nullptr;
+        check(mtl_malloc(ctx_, (size_t)g_.nodes[i].outputs[0].shape.num_elements() * 4, (void**)&idx), "pool indices");
+        pool_idx_[(int)i] = idx;
+    }
+
+    // n_inference_nodes (model.mojo:47-59)
+    n_inference_nodes_ = 0;
+    for (int i = (int)g_.nodes.size() - 1; i >= 0 && !n_inference_nodes_; --i)
+        for (auto& o : g_.nodes[i].outputs)
+            for (auto& go : g_.outputs)
+                if (go.id == o.id) n_inference_nodes_ = i + 1;
+    check(mtl_sync(ctx_), "model setup");
+}
+
+Model::~Model() {
+    for (auto& kv : pool_idx_) mtl_free(ctx_, kv.second);
+    mtl_free(ctx_, tensors_);
+    mtl_free(ctx_, grads_);
+}
+
+float* Model::T(const Symbol& s) const {
+    auto it = tensor_off_.find(s.id);
+    if (it == tensor_off_.end()) throw Error(MTL_ERR_INVALID, "unknown symbol " + std::to_string(s.id));
+    return tensors_ + it->second;
+}
+float* Model::G(const Symbol& s) const {
+    auto it = grad_off_.find(s.id);
+    if (it == grad_off_.end()) throw Error(MTL_ERR_INVALID, "symbol " + std::to_string(s.id) + " has no gradient");
+    return grads_ + it->second;
+}
+
+TensorShape Model::shape_of(int id) const {
+    auto it = shapes_.find(id);
+    if (it == shapes_.end()) throw Error(MTL_ERR_INVALID, "unknown symbol " + std::to_string(id));
+    return it->second;
+}
+
+void Model::get_tensor(int id, float* out) const {
+    Symbol s{id, shape_of(id), false};
+    check(mtl_d2h(ctx_, out, T(s), (size_t)s.shape.num_elements() * 4), "get_tensor");
+}
+void Model::set_tensor(int id, const float* in) {
+    Symbol s{id, shape_of(id), false};
+    check(mtl_h2d(ctx_, T(s), in, (size_t)s.shape.num_elements() * 4), "set_tensor");
+    if (s.shape.is_scalar() && scalar_values_.count(id)) scalar_values_[id] = in[0];
+}
+void Model::get_grad(int id, float* out) const {
+    Symbol s{id, shape_of(id), true};
+    check(mtl_d2h(ctx_, out, G(s), (size_t)s.shape.num_elements() * 4), "get_grad");
+}
+
+void Model::zero_grads() {
+    if (!overwrite_first_) check(mtl_zero(ctx_, grads_, (size_t)n_grad_floats_ * 4), "zero_grad");
+    // with overwrite_first the first writer of each buffer replaces its contents and buffers that
+    // no node writes still hold the zeros they were created with
+}
+
+void Model::copy_inputs_async(const std::vector<const float*>& in) {
+    if (in.size() != g_.inputs.size()) throw Error(MTL_ERR_INVALID, "wrong number of inputs");
+    for (size_t i = 0; i < in.size(); ++i)
+        check(mtl_h2d_async(ctx_, T(g_.inputs[i]), in[i], (size_t)g_.inputs[i].shape.num_elements() * 4), "input copy");
+}
+
+float* Model::loss_device() const {
+    if (!g_.loss_out) throw Error(MTL_ERR_INVALID, "no loss defined: Model.forward unavailable");
+    return T(*g_.loss_out);
+}
+
+float Model::forward(const std::vector<const float*>& in) {
+    if (!g_.loss_out) throw Error(MTL_ERR_INVALID, "no loss defined: Model.forward unavailable");
+    if (in.size() != g_.inputs.size()) throw Error(MTL_ERR_INVALID, "wrong number of inputs");
+    for (size_t i = 0; i < in.size(); ++i)
+        check(mtl_h2d(ctx_, T(g_.inputs[i]), in[i], (size_t)g_.inputs[i].shape.num_elements() * 4), "input copy");
+    execute((int)g_.nodes.size());
+    float loss = 0.0f;
+    check(mtl_d2h(ctx_, &loss, T(*g_.loss_out), 4), "loss read-back");
+    return loss;
+}
+
+void Model::inference(const std::vector<const float*>& in, const std::vector<float*>& out) {
+    if (!n_inference_nodes_) throw Error(MTL_ERR_INVALID, "no graph out defined: Model.inference unavailable");
+    if (in.size() != g_.inputs.size() || out.size() != g_.outputs.size())
+        throw Error(MTL_ERR_INVALID, "wrong number of inputs or outputs");
+    for (size_t i = 0; i < in.size(); ++i)
+        check(mtl_h2d(ctx_, T(g_.inputs[i]), in[i], (size_t)g_.inputs[i].shape.num_elements() * 4), "input copy");
+    execute(n_inference_nodes_);
+    for (size_t i = 0; i < out.size(); ++i)
+        check(mtl_d2h(ctx_, out[i], T(g_.outputs[i]), (size_t)g_.outputs[i].shape.num_elements() * 4), "output copy");
+}
+
+void Model::execute(int num_nodes) {
+    for (int i = 0; i < num_nodes; ++i) forward_op(g_.nodes[i]);
+}
+
+static mtl_conv2d_desc conv_desc(const TensorShape& in, int K, int R, int S, const Attributes& a) {
+    mtl_conv2d_desc d;
+    d.N = (int32_t)in[0]; d.C = (int32_t)in[1]; d.H = (int32_t)in[2]; d.W = (int32_t)in[3];
+    d.K = K; d.R = R; d.S = S;
+    for (int i = 0; i < 2; ++i) { d.pad[i] = a.padding[i]; d.stride[i] = a.stride[i]; d.dilation[i] = a.dilation[i]; }
+    return d;
+}
+
+static void unary_params(const Node& n, const std::map<int, float>& scalars, float* p0, float* p1) {
+    *p0 = 0.0f;
+    *p1 = 0.0f;
+    if (n.op == MTL_OP_POW) {
+        auto it = scalars.find(n.inputs[1].id);
+        if (it == scalars.end()) throw Error(MTL_ERR_UNSUPPORTED, "POW exponent must be a graph scalar");
+        *p0 = it->second;
+    } else if (n.op == MTL_OP_LEAKYRELU) {
+        *p0 = n.attrs.negative_slope;
+    } else if (n.op == MTL_OP_CLIP) {
+        *p0 = n.attrs.clip_min ? *n.attrs.clip_min : -3.402823466e38f;  // min_finite / max_finite
+        *p1 = n.attrs.clip_max ? *n.attrs.clip_max : 3.402823466e38f;
+    }
+}
+
+// forward_op, ops.mojo:243-352
+void Model::forward_op(const Node& n) {
+    const Symbol& out = n.outputs[0];
+    const Symbol& t1 = n.inputs[0];
+    float p0, p1;
+    switch (n.op) {
+        case MTL_OP_ADD: case MTL_OP_SUB: case MTL_OP_MUL: case MTL_OP_DIV:
+            check(mtl_binary_fwd(ctx_, n.op, T(out), T(t1), T(n.inputs[1]), t1.shape.rank, t1.shape.dims,
+                                 n.inputs[1].shape.rank, n.inputs[1].shape.dims), "binary forward");
+            break;
+        case MTL_OP_POW: case MTL_OP_EXP: case MTL_OP_LOG: case MTL_OP_SIGMOID: case MTL_OP_RELU:
+        case MTL_OP_LEAKYRELU: case MTL_OP_TANH: case MTL_OP_CLIP:
+            unary_params(n, scalar_values_, &p0, &p1);
+            check(mtl_unary_fwd(ctx_, n.op, T(out), T(t1), t1.shape.num_elements(), p0, p1), "unary forward");
+            break;
+        case MTL_OP_DOT:
+            check(mtl_dot_fwd(ctx_, T(out), T(t1), T(n.inputs[1]), t1.shape[0], t1.shape[1], n.inputs[1].shape[1]),
+                  "DOT forward");
+            break;
+        case MTL_OP_SUM: case MTL_OP_MEAN: case MTL_OP_MAX:
+            check(mtl_reduce_fwd(ctx_, n.op, T(out), T(t1), t1.shape.rank, t1.shape.dims,
+                                 n.attrs.axis ? *n.attrs.axis : -1), "reduce forward");
+            break;
+        case MTL_OP_FLATTEN: case MTL_OP_RESHAPE: case MTL_OP_SQUEEZE: case MTL_OP_UNSQUEEZE:
+            check(mtl_copy_f32(ctx_, T(out), T(t1), t1.shape.num_elements(), 0), "copy forward");
+            break;
+        case MTL_OP_CONV2D: {
+            const Symbol& w = n.inputs[1];
+            mtl_conv2d_desc d = conv_desc(t1.shape, (int)w.shape[0], (int)w.shape[2], (int)w.shape[3], n.attrs);
+            check(mtl_conv2d_fwd(ctx_, T(out), T(t1), T(w), T(n.inputs[2]), &d), "CONV2D forward");
+            break;
+        }
+        case MTL_OP_MAXPOOL2D: {
+            mtl_conv2d_desc d = conv_desc(t1.shape, 1, n.attrs.kernel_size[0], n.attrs.kernel_size[1], n.attrs);
+            int node_index = (int)(&n - &g_.nodes[0]);
+            check(mtl_maxpool2d_fwd(ctx_, T(out), pool_idx_.at(node_index), T(t1), &d), "MAXPOOL2D forward");
+            break;
+        }
+        case MTL_OP_FMA:
+            check(mtl_fma_fwd(ctx_, T(out), T(t1), T(n.inputs[1]), T(n.inputs[2]), t1.shape.num_elements()), "FMA forward");
+            break;
+        default:
+            throw Error(MTL_ERR_UNSUPPORTED, "operator id " + std::to_string(n.op) + " is not on the GPU path");
+    }
+}
+
+int Model::acc_flag(const Symbol& s) {
+    if (!overwrite_first_) return 1;
+    bool& w = grad_written_[s.id];
+    if (w) return 1;
+    w = true;
+    return 0;
+}
+
+// backward_op, ops.mojo:355-528: grad(operand tensor_id) += local gradient
+void Model::backward_op(const Node& n, int tensor_id) {
+    const Symbol& out = n.outputs[0];
+    const Symbol& t1 = n.inputs[0];
+    const Symbol& tj = n.inputs[tensor_id];
+    float* ug = G(out);
+    float* grad = G(tj);
+    int acc = acc_flag(tj);
+    float p0, p1;
+    switch (n.op) {
+        case MTL_OP_ADD: case MTL_OP_SUB: case MTL_OP_MUL: case MTL_OP_DIV:
+            check(mtl_binary_bwd(ctx_, n.op, tensor_id, grad, ug, T(t1), T(n.inputs[1]), t1.shape.rank, t1.shape.dims,
+                                 n.inputs[1].shape.rank, n.inputs[1].shape.dims, acc), "binary backward");
+            break;
+        case MTL_OP_POW:
+            if (tensor_id != 0) throw Error(MTL_ERR_UNSUPPORTED, "gradient of the POW exponent is not on the GPU path");
+            // fallthrough
+        case MTL_OP_EXP: case MTL_OP_LOG: case MTL_OP_SIGMOID: case MTL_OP_RELU: case MTL_OP_LEAKYRELU:
+        case MTL_OP_TANH: case MTL_OP_CLIP:
+            unary_params(n, scalar_values_, &p0, &p1);
+            check(mtl_unary_bwd(ctx_, n.op, grad, ug, T(t1), t1.shape.num_elements(), p0, p1, acc), "unary backward");
+            break;
+        case MTL_OP_DOT:
+            check(mtl_dot_bwd(ctx_, tensor_id, grad, ug, T(t1), T(n.inputs[1]), t1.shape[0], t1.shape[1],
+                              n.inputs[1].shape[1], acc), "DOT backward");
+            break;
+        case MTL_OP_SUM: case MTL_OP_MEAN: case MTL_OP_MAX:
+            check(mtl_reduce_bwd(ctx_, n.op, grad, ug, T(t1), t1.shape.rank, t1.shape.dims,
+                                 n.attrs.axis ? *n.attrs.axis : -1, acc), "reduce backward");
+            break;
+        case MTL_OP_FLATTEN: case MTL_OP_RESHAPE: case MTL_OP_SQUEEZE: case MTL_OP_UNSQUEEZE:
+            check(mtl_copy_f32(ctx_, grad, ug, t1.shape.num_elements(), acc), "copy backward");
+            break;
+        case MTL_OP_CONV2D: {
+            const Symbol& w = n.inputs[1];
+            mtl_conv2d_desc d = conv_desc(t1.shape, (int)w.shape[0], (int)w.shape[2], (int)w.shape[3], n.attrs);
+            check(mtl_conv2d_bwd(ctx_, tensor_id, grad, ug, T(t1), T(w), &d, acc), "CONV2D backward");
+            break;
+        }
+        case MTL_OP_MAXPOOL2D: {
+            mtl_conv2d_desc d = conv_desc(t1.shape, 1, n.attrs.kernel_size[0], n.attrs.kernel_size[1], n.attrs);
+            int node_index = (int)(&n - &g_.nodes[0]);
+            // the indices stored by this step's forward pass select the same elements the
+            // reference finds by re-scanning the input (pool.mojo:123-163)
+            check(mtl_maxpool2d_bwd_idx(ctx_, grad, ug, pool_idx_.at(node_index), &d, acc), "MAXPOOL2D backward");
+            break;
+        }
+        case MTL_OP_FMA:
+            check(mtl_fma_bwd(ctx_, tensor_id, grad, ug, T(t1), T(n.inputs[1]), t1.shape.num_elements(), acc), "FMA backward");
+            break;
+        default:
+            throw Error(MTL_ERR_UNSUPPORTED, "operator id " + std::to_string(n.op) + " is not on the GPU path");
+    }
+}
+
+void Model::backward_enqueue() {
+    if (!g_.loss_out) throw Error(MTL_ERR_INVALID, "no loss defined");
+    grad_written_.clear();
+    // fill(grads[loss], 1.0), model.mojo:180
+    check(mtl_fill_f32(ctx_, G(*g_.loss_out), g_.loss_out->shape.num_elements(), 1.0f), "seed loss gradient");
+    grad_written_[g_.loss_out->id] = true;
+    for (int i = (int)g_.nodes.size() - 1; i >= 0; --i) {
+        const Node& n = g_.nodes[i];
+        for (int j = 0; j < (int)n.inputs.size(); ++j)
+            if (n.inputs[j].trainable) backward_op(n, j);
+        if (after_backward_node) after_backward_node(after_backward_user, i);
+    }
+}
+
+void Model::backward() { backward_enqueue(); }
+
+// ------------------------------------------------------------------ Adam -------------------
+
+Adam::Adam(Model& model, float lr, float beta1, float beta2, float epsilon)
+    : model_(model), lr_(lr), beta1_(beta1), beta2_(beta2), eps_(epsilon) {
+    mtl_ctx* ctx = model_.ctx();
+    size_t bytes = (size_t)std::max<int64_t>(model_.n_trainable(), 1) * 4;
+    auto ck = [&](int rc, const char* w) {
+        if (rc != MTL_OK) throw Error(rc, std::string(w) + ": " + mtl_last_error(ctx));
+    };
+    // allocate_rms_and_momentum (optim.mojo:142-149): zero-initialised
+    ck(mtl_malloc(ctx, bytes, (void**)&m_), "Adam momentum");
+    ck(mtl_malloc(ctx, bytes, (void**)&v_), "Adam rms");
+    ck(mtl_malloc(ctx, 4, (void**)&t_dev_), "Adam counter");
+    ck(mtl_zero(ctx, m_, bytes), "zero momentum");
+    ck(mtl_zero(ctx, v_, bytes), "zero rms");
+    ck(mtl_zero(ctx, t_dev_, 4), "zero counter");
+}
+
+Adam::~Adam() {
+    mtl_free(model_.ctx(), m_);
+    mtl_free(model_.ctx(), v_);
+    mtl_free(model_.ctx(), t_dev_);
+}
+
+void Adam::step() {
+    iter_ += 1;  // optim.mojo:96
+    int rc = mtl_adam_step(model_.ctx(), model_.params_flat(), model_.grads_flat(), m_, v_, model_.n_trainable(), lr_,
+                           beta1_, beta2_, eps_, iter_, grad_scale_);
+    if (rc != MTL_OK) throw Error(rc, std::string("Adam.step: ") + mtl_last_error(model_.ctx()));
+}
+
+void Adam::step_captured() {
+    iter_ += 1;
+    int rc = mtl_adam_step_dev(model_.ctx(), model_.params_flat(), model_.grads_flat(), m_, v_, model_.n_trainable(),
+                               lr_, beta1_, beta2_, eps_, t_dev_, grad_scale_);
+    if (rc != MTL_OK) throw Error(rc, std::string("Adam.step: ") + mtl_last_error(model_.ctx()));
+}
+
+void Adam::get_state(int which, float* host_out) const {
+    int rc = mtl_d2h(model_.ctx(), host_out, which == 0 ? m_ : v_, (size_t)model_.n_trainable() * 4);
+    if (rc != MTL_OK) throw Error(rc, std::string("Adam state read-back: ") + mtl_last_error(model_.ctx()));
+}
+
+}  // namespace mantle

@@ -1,0 +1,126 @@
+// Host-side mirror of Mantle's graph executor and optimizer on top of the C ABI:
+//   Model   mantle/nn/model.mojo:61-395   (allocate, forward/inference/execute, backward)
+//   Adam    mantle/nn/optim.mojo:51-149   (zero_grad, step, m/v state)
+//   forward_op / backward_op              mantle/autograd/ops/ops.mojo:243-528
+// Storage differs from the reference on purpose: instead of one host allocation per symbol
+// (collection.mojo:175-200) all tensors live in one device arena, and the trainable parameters,
+// their gradients and both Adam moments are each ONE contiguous fp32 span in the order of
+// get_trainable_parameters (optim.mojo:27-44), so that the optimizer is a single kernel and the
+// data-parallel gradient exchange is a single buffer.
+#pragma once
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "graph.hpp"
+
+namespace mantle {
+
+struct Error : std::runtime_error {
+    int code;
+    Error(int c, const std::string& m) : std::runtime_error(m), code(c) {}
+};
+
+class Model {
+   public:
+    Model(mtl_ctx* ctx, const Graph& g, uint64_t init_seed = 42);
+    ~Model();
+    Model(const Model&) = delete;
+    Model& operator=(const Model&) = delete;
+
+    // model.mojo:82-99: inputs are HOST pointers in graph-declaration order; returns the loss.
+    float forward(const std::vector<const float*>& host_inputs);
+    // model.mojo:101-111: runs nodes up to the last graph output; copies outputs to host.
+    void inference(const std::vector<const float*>& host_inputs, const std::vector<float*>& host_outputs);
+    // model.mojo:173-330 with no upper gradients: seeds d(loss) = 1.
+    void backward();
+
+    // Split form used by the training pipeline: everything enqueued, nothing waited for.
+    void copy_inputs_async(const std::vector<const float*>& pinned_inputs);
+    void execute(int num_nodes);
+    void backward_enqueue();
+    float* loss_device() const;
+
+    // Parameters.tensors / Parameters.grads access (host copies).
+    void get_tensor(int symbol_id, float* host_out) const;
+    void set_tensor(int symbol_id, const float* host_in);
+    void get_grad(int symbol_id, float* host_out) const;
+    bool has_grad(int symbol_id) const { return grad_off_.count(symbol_id) != 0; }
+    TensorShape shape_of(int symbol_id) const;
+    // Collection.set_zero on every gradient (optim.mojo:90-92).
+    void zero_grads();
+
+    // When on (default), the first gradient contribution a buffer receives in a backward pass
+    // overwrites it and later ones add, which equals zero_grad() followed by accumulation without
+    // touching the buffers twice; zero_grads() then only zeroes buffers no node writes.
+    // Off: every contribution accumulates, exactly like backward_op (ops.mojo:405,463,498).
+    void set_overwrite_first(bool on) { overwrite_first_ = on; }
+
+    // flat trainable spans (device pointers) for the optimizer and the gradient exchange
+    float* params_flat() const { return tensors_; }
+    float* grads_flat() const { return grads_; }
+    int64_t n_trainable() const { return n_trainable_; }
+    const std::vector<Symbol>& trainable_parameters() const { return trainable_; }
+    // Offsets (in floats) inside the flat spans, in trainable_parameters() order.
+    const std::vector<int64_t>& trainable_offsets() const { return trainable_off_; }
+
+    mtl_ctx* ctx() const { return ctx_; }
+    const Graph& graph() const { return g_; }
+    int n_inference_nodes() const { return n_inference_nodes_; }
+
+    // Called between backward nodes by the data-parallel trainer: node index (reverse order) done.
+    void (*after_backward_node)(void* user, int node_index) = nullptr;
+    void* after_backward_user = nullptr;
+
+   private:
+    void forward_op(const Node& n);
+    void backward_op(const Node& n, int tensor_id);
+    float* T(const Symbol& s) const;
+    float* G(const Symbol& s) const;
+    int acc_flag(const Symbol& s);
+    void check(int rc, const char* what) const;
+
+    mtl_ctx* ctx_;
+    Graph g_;
+    float* tensors_ = nullptr;  // arena: [trainable params | everything else]
+    float* grads_ = nullptr;    // arena: [trainable param grads | other trainable symbols]
+    int64_t n_tensor_floats_ = 0, n_grad_floats_ = 0, n_trainable_ = 0;
+    std::map<int, int64_t> tensor_off_, grad_off_;
+    std::map<int, TensorShape> shapes_;
+    std::map<int, float> scalar_values_;      // host copies of [1]-shaped literals (POW exponent)
+    std::map<int, int32_t*> pool_idx_;         // hidden argmax buffers, keyed by node index
+    std::vector<Symbol> trainable_;
+    std::vector<int64_t> trainable_off_;
+    std::map<int, bool> grad_written_;
+    std::vector<int> never_written_;           // trainable symbols no backward node writes
+    bool overwrite_first_ = true;
+    int n_inference_nodes_ = 0;
+};
+
+class Adam {
+   public:
+    // optim.mojo:66-88
+    Adam(Model& model, float lr = 0.001f, float beta1 = 0.9f, float beta2 = 0.999f, float epsilon = 1e-8f);
+    ~Adam();
+    void zero_grad() { model_.zero_grads(); }  // optim.mojo:90-92
+    void step();                               // optim.mojo:94-140
+    // Variant whose iteration counter lives on the device, for captured steps.
+    void step_captured();
+    // A captured step that is replayed advances the device counter; this keeps the host copy equal.
+    void note_replayed_step() { iter_ += 1; }
+    int iter() const { return iter_; }
+    void set_grad_scale(float s) { grad_scale_ = s; }
+    void get_state(int which /*0 m, 1 v*/, float* host_out) const;
+
+   private:
+    Model& model_;
+    float lr_, beta1_, beta2_, eps_;
+    int iter_ = 0;
+    float grad_scale_ = 1.0f;
+    float* m_ = nullptr;
+    float* v_ = nullptr;
+    int32_t* t_dev_ = nullptr;
+};
+
+}  // namespace mantle

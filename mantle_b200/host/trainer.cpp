@@ -1,0 +1,125 @@
+#include "trainer.hpp"
+
+#include <algorithm>
+
+namespace mantle {
+
+namespace {
+void ck(mtl_ctx* ctx, int rc, const char* what) {
+    if (rc != MTL_OK) throw Error(rc, std::string(what) + ": " + mtl_last_error(ctx));
+}
+}  // namespace
+
+Trainer::Trainer(Model& model, Adam& adam, bool use_graph, int64_t bucket_bytes)
+    : model_(model), adam_(adam), use_graph_(use_graph), bucket_bytes_(bucket_bytes) {
+    mtl_ctx* ctx = model_.ctx();
+    world_ = mtl_dp_world_size(ctx);
+    ck(ctx, mtl_host_alloc(ctx, 64, (void**)&own_loss_), "pinned loss word");
+    if (world_ > 1) adam_.set_grad_scale(1.0f / (float)world_);
+    // A parameter's gradient is final after the lowest-numbered node that reads it (nodes run in
+    // reverse order during backward).
+    const Graph& g = model_.graph();
+    final_at_node_.assign(g.nodes.size(), {});
+    const auto& tr = model_.trainable_parameters();
+    for (size_t p = 0; p < tr.size(); ++p) {
+        int first = -1;
+        for (size_t i = 0; i < g.nodes.size() && first < 0; ++i)
+            for (auto& in : g.nodes[i].inputs)
+                if (in.id == tr[p].id) first = (int)i;
+        if (first >= 0) final_at_node_[first].push_back((int)p);
+    }
+    model_.after_backward_node = &Trainer::node_done_thunk;
+    model_.after_backward_user = this;
+}
+
+Trainer::~Trainer() {
+    model_.after_backward_node = nullptr;
+    model_.after_backward_user = nullptr;
+    if (graph_) mtl_graph_destroy(model_.ctx(), graph_);
+    mtl_host_free(model_.ctx(), own_loss_);
+}
+
+void Trainer::node_done_thunk(void* self, int node) { static_cast<Trainer*>(self)->node_done(node); }
+
+void Trainer::flush_bucket() {
+    if (pending_lo_ < 0) return;
+    ck(model_.ctx(), mtl_dp_allreduce_async(model_.ctx(), model_.grads_flat() + pending_lo_, pending_hi_ - pending_lo_),
+       "gradient allreduce");
+    pending_lo_ = pending_hi_ = -1;
+}
+
+void Trainer::node_done(int node) {
+    if (world_ <= 1) return;
+    const auto& tr = model_.trainable_parameters();
+    const auto& off = model_.trainable_offsets();
+    for (int p : final_at_node_[node]) {
+        int64_t lo = off[p];
+        int64_t hi = (size_t)p + 1 < off.size() ? off[p + 1] : model_.n_trainable();
+        (void)tr;
+        if (pending_lo_ < 0) {
+            pending_lo_ = lo;
+            pending_hi_ = hi;
+        } else if (hi == pending_lo_) {
+            pending_lo_ = lo;  // grows downwards: backward visits parameters from last to first
+        } else if (lo == pending_hi_) {
+            pending_hi_ = hi;
+        } else {
+            flush_bucket();
+            pending_lo_ = lo;
+            pending_hi_ = hi;
+        }
+    }
+    if (pending_lo_ >= 0 && (pending_hi_ - pending_lo_) * 4 >= bucket_bytes_) flush_bucket();
+    if (node == 0) {
+        flush_bucket();
+        ck(model_.ctx(), mtl_dp_wait(model_.ctx()), "gradient allreduce wait");
+    }
+}
+
+void Trainer::enqueue_body(float* pinned_loss) {
+    mtl_ctx* ctx = model_.ctx();
+    model_.execute((int)model_.graph().nodes.size());
+    ck(ctx, mtl_d2h_async(ctx, pinned_loss, model_.loss_device(), 4), "loss read-back");
+    adam_.zero_grad();
+    model_.backward_enqueue();
+    adam_.step_captured();
+}
+
+void Trainer::step_async(const std::vector<const float*>& host_inputs, float* pinned_loss) {
+    mtl_ctx* ctx = model_.ctx();
+    model_.copy_inputs_async(host_inputs);
+    ++steps_;
+    if (!use_graph_ || steps_ == 1) {
+        // the first step also sizes the scratch workspace, which must not grow during capture
+        enqueue_body(pinned_loss);
+        return;
+    }
+    if (!graph_ || graph_loss_slot_ != pinned_loss) {
+        if (graph_) {
+            ck(ctx, mtl_graph_destroy(ctx, graph_), "graph destroy");
+            graph_ = nullptr;
+        }
+        ck(ctx, mtl_graph_begin(ctx), "graph capture begin");
+        try {
+            enqueue_body(pinned_loss);
+        } catch (...) {
+            mtl_graph* dead = nullptr;
+            mtl_graph_end(ctx, &dead);
+            if (dead) mtl_graph_destroy(ctx, dead);
+            throw;
+        }
+        ck(ctx, mtl_graph_end(ctx, &graph_), "graph capture end");
+        graph_loss_slot_ = pinned_loss;
+    } else {
+        adam_.note_replayed_step();
+    }
+    ck(ctx, mtl_graph_launch(ctx, graph_), "graph launch");
+}
+
+float Trainer::step(const std::vector<const float*>& host_inputs) {
+    step_async(host_inputs, own_loss_);
+    ck(model_.ctx(), mtl_sync(model_.ctx()), "step wait");
+    return *own_loss_;
+}
+
+}  // namespace mantle

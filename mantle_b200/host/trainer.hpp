@@ -1,0 +1,49 @@
+// One training step as the reference's examples write it (examples/mnist.mojo:92-104):
+//     loss = model.forward(x, y); optim.zero_grad(); model.backward(); optim.step()
+// enqueued without intermediate waits, optionally replayed from a captured CUDA graph, and with
+// the data-parallel gradient exchange started per bucket as soon as a layer's parameter gradients
+// are final, so that it overlaps the backward pass of the earlier layers.
+#pragma once
+
+#include "model.hpp"
+
+namespace mantle {
+
+class Trainer {
+   public:
+    // use_graph: capture the step on its second call and replay it afterwards.
+    // bucket_bytes: gradient spans are exchanged once this many bytes are final (data parallel).
+    Trainer(Model& model, Adam& adam, bool use_graph, int64_t bucket_bytes = 256 * 1024);
+    ~Trainer();
+
+    // Inputs are host pointers (pinned memory keeps the copy asynchronous).  Returns the loss of
+    // this step after waiting for it.
+    float step(const std::vector<const float*>& host_inputs);
+    // Same, but only enqueues; the loss lands in *pinned_loss once the stream reaches it.
+    void step_async(const std::vector<const float*>& host_inputs, float* pinned_loss);
+
+    int64_t steps() const { return steps_; }
+    bool graph_active() const { return graph_ != nullptr; }
+
+   private:
+    void enqueue_body(float* pinned_loss);
+    static void node_done_thunk(void* self, int node);
+    void node_done(int node);
+    void flush_bucket();
+
+    Model& model_;
+    Adam& adam_;
+    bool use_graph_;
+    int64_t bucket_bytes_;
+    int world_ = 1;
+    mtl_graph* graph_ = nullptr;
+    float* graph_loss_slot_ = nullptr;  // the pinned slot the captured copy writes to
+    float* own_loss_ = nullptr;         // pinned word used by step()
+    int64_t steps_ = 0;
+    // data-parallel bucketing: for every node, the trainable parameters whose gradient is final
+    // once that node's backward has run
+    std::vector<std::vector<int>> final_at_node_;
+    int64_t pending_lo_ = -1, pending_hi_ = -1;  // pending span [lo, hi) in floats
+};
+
+}  // namespace mantle
