@@ -250,6 +250,20 @@ MTL_API int32_t mtl_timer_stop(mtl_ctx* ctx, int32_t slot);
 /* Waits for the stop event and returns milliseconds. */
 MTL_API int32_t mtl_timer_elapsed_ms(mtl_ctx* ctx, int32_t slot, float* out_ms);
 
+/* Per-kernel device timing of the tensor-core kernels (the dominant launches of a training
+ * step): while enabled, and outside stream capture, each launch of the kernel `which` is bracketed
+ * by CUDA events on the context's stream.  mtl_prof_get waits for them and returns the summed
+ * duration and the launch count since the last reset. */
+enum mtl_prof_kernel {
+    MTL_PROF_DOT_TC = 0,       /* tcgen05 GEMM behind OP.DOT                          */
+    MTL_PROF_CONV_IGEMM = 1,   /* tcgen05 implicit GEMM: CONV2D forward / input grad  */
+    MTL_PROF_CONV_WGRAD = 2,   /* tcgen05 implicit GEMM: CONV2D kernel gradient       */
+    MTL_PROF_KERNELS = 3
+};
+MTL_API int32_t mtl_prof_enable(mtl_ctx* ctx, int32_t on);
+MTL_API int32_t mtl_prof_reset(mtl_ctx* ctx);
+MTL_API int32_t mtl_prof_get(mtl_ctx* ctx, int32_t which, float* total_ms, int32_t* launches);
+
 /* ---------------------------------------------------------------- data parallel --------- */
 
 /* Data-parallel training is new in this backend (the reference is single-process).  One process

@@ -102,6 +102,9 @@ SIGNATURES = {
     "mtl_timer_start": (_i32, [_vp, _i32]),
     "mtl_timer_stop": (_i32, [_vp, _i32]),
     "mtl_timer_elapsed_ms": (_i32, [_vp, _i32, C.POINTER(_f32)]),
+    "mtl_prof_enable": (_i32, [_vp, _i32]),
+    "mtl_prof_reset": (_i32, [_vp]),
+    "mtl_prof_get": (_i32, [_vp, _i32, C.POINTER(_f32), C.POINTER(_i32)]),
     "mtl_dp_get_unique_id": (_i32, [C.POINTER(C.c_uint8)]),
     "mtl_dp_init": (_i32, [_vp, C.POINTER(C.c_uint8), _i32, _i32]),
     "mtl_dp_allreduce_async": (_i32, [_vp, _vp, _i64]),

@@ -7,6 +7,7 @@
 #include <stdio.h>
 #include <string.h>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/mantle_cuda.h"
@@ -33,6 +34,28 @@ struct mtl_ctx {
     void* dp = nullptr;
     // cached driver entry point for tensor-map encoding (tma.cuh)
     void* encode_tiled = nullptr;
+    // per-kernel event timing (mtl_prof_*)
+    bool prof_on = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events[MTL_PROF_KERNELS];
+};
+
+// Brackets one launch of a profiled kernel with events when profiling is on.
+struct mtl_prof_scope {
+    mtl_ctx* ctx;
+    int which;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    mtl_prof_scope(mtl_ctx* c, int w) : ctx(c), which(w) {
+        if (ctx->prof_on && !ctx->capturing && cudaEventCreate(&e0) == cudaSuccess && cudaEventCreate(&e1) == cudaSuccess)
+            cudaEventRecord(e0, ctx->stream);
+        else
+            e0 = e1 = nullptr;
+    }
+    ~mtl_prof_scope() {
+        if (e0 && e1) {
+            cudaEventRecord(e1, ctx->stream);
+            ctx->prof_events[which].push_back({e0, e1});
+        }
+    }
 };
 
 struct mtl_graph {

@@ -84,6 +84,11 @@ int32_t mtl_ctx_destroy(mtl_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->dp) mtl_dp_destroy(ctx);
+    for (int k = 0; k < MTL_PROF_KERNELS; ++k)
+        for (auto& ev : ctx->prof_events[k]) {
+            cudaEventDestroy(ev.first);
+            cudaEventDestroy(ev.second);
+        }
     for (int i = 0; i < MTL_NUM_TIMERS; ++i) {
         if (ctx->t0[i]) cudaEventDestroy(ctx->t0[i]);
         if (ctx->t1[i]) cudaEventDestroy(ctx->t1[i]);
@@ -271,6 +276,46 @@ int32_t mtl_graph_destroy(mtl_ctx* ctx, mtl_graph* g) {
     if (g->exec) cudaGraphExecDestroy(g->exec);
     if (g->graph) cudaGraphDestroy(g->graph);
     delete g;
+    return MTL_OK;
+}
+
+// ------------------------------------------------------------------ kernel profile -------
+
+static void prof_clear(mtl_ctx* ctx) {
+    for (int k = 0; k < MTL_PROF_KERNELS; ++k) {
+        for (auto& ev : ctx->prof_events[k]) {
+            cudaEventDestroy(ev.first);
+            cudaEventDestroy(ev.second);
+        }
+        ctx->prof_events[k].clear();
+    }
+}
+
+int32_t mtl_prof_enable(mtl_ctx* ctx, int32_t on) {
+    MTL_CHECK_CTX(ctx);
+    ctx->prof_on = on != 0;
+    return MTL_OK;
+}
+
+int32_t mtl_prof_reset(mtl_ctx* ctx) {
+    MTL_CHECK_CTX(ctx);
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    prof_clear(ctx);
+    return MTL_OK;
+}
+
+int32_t mtl_prof_get(mtl_ctx* ctx, int32_t which, float* total_ms, int32_t* launches) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, which >= 0 && which < MTL_PROF_KERNELS && total_ms && launches, "bad profile query");
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    float sum = 0.0f;
+    for (auto& ev : ctx->prof_events[which]) {
+        float ms = 0.0f;
+        MTL_CUDA(ctx, cudaEventElapsedTime(&ms, ev.first, ev.second));
+        sum += ms;
+    }
+    *total_ms = sum;
+    *launches = (int32_t)ctx->prof_events[which].size();
     return MTL_OK;
 }
 

@@ -146,8 +146,8 @@ k_conv_igemm(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ 
                     const uint32_t sb = sa + C::kABytes;
 #pragma unroll
                     for (int kk = 0; kk < BK / 8; ++kk) {
-                        const uint64_t da = make_smem_desc(sa + kk * 32, 16, 1024);
-                        const uint64_t db = make_smem_desc(sb + kk * 32, 16, 1024);
+                        const uint64_t da = desc_k_major(sa, kk);
+                        const uint64_t db = desc_k_major(sb, kk);
                         mma_tf32(tmem_d, da, db, idesc, (kb | kk) ? 1u : 0u);
                     }
                     mma_commit(&empty[stage]);
@@ -322,7 +322,10 @@ int32_t launch_igemm(mtl_ctx* ctx, const CUtensorMap* maps, const ConvTcParams& 
     MTL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     int tiles = p.tiles_w * p.tiles_h * p.tiles_nb * p.tiles_k;
     int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    kern<<<grid, kThreads, C::kSmemBytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+    {
+        mtl_prof_scope prof(ctx, MTL_PROF_CONV_IGEMM);
+        kern<<<grid, kThreads, C::kSmemBytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+    }
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }

@@ -164,12 +164,8 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                     const uint32_t sb = sa + C::kABytes;
 #pragma unroll
                     for (int kk = 0; kk < BK / 8; ++kk) {
-                        // K-major: rows of 128 B, 8-row groups 1024 B apart, step 32 B along K.
-                        // MN-major: 32-wide chunks 4096 B apart, 8-row K groups 1024 B apart.
-                        const uint64_t da = A_MN ? make_smem_desc(sa + kk * 1024, 4096, 1024)
-                                                 : make_smem_desc(sa + kk * 32, 16, 1024);
-                        const uint64_t db = B_MN ? make_smem_desc(sb + kk * 1024, 4096, 1024)
-                                                 : make_smem_desc(sb + kk * 32, 16, 1024);
+                        const uint64_t da = A_MN ? desc_mn_major(sa, kk) : desc_k_major(sa, kk);
+                        const uint64_t db = B_MN ? desc_mn_major(sb, kk) : desc_k_major(sb, kk);
                         mma_tf32(tmem_d, da, db, idesc, (kb | kk) ? 1u : 0u);
                     }
                     mma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
@@ -274,7 +270,10 @@ int32_t launch_gemm(mtl_ctx* ctx, const CUtensorMap* maps, const GemmParams& p) 
     MTL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
     int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    kern<<<grid, kThreads, C::kSmemBytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+    {
+        mtl_prof_scope prof(ctx, MTL_PROF_DOT_TC);
+        kern<<<grid, kThreads, C::kSmemBytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+    }
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -282,7 +281,7 @@ int32_t launch_gemm(mtl_ctx* ctx, const CUtensorMap* maps, const GemmParams& p) 
 }  // namespace
 
 int32_t mtl_encode_tmap(mtl_ctx* ctx, CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                        const uint64_t* strides_bytes, const uint32_t* box) {
+                        const uint64_t* strides_bytes, const uint32_t* box, bool atom32) {
     typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -308,7 +307,8 @@ int32_t mtl_encode_tmap(mtl_ctx* ctx, CUtensorMap* out, const void* base, int ra
     }
     CUresult r = ((encode_fn)ctx->encode_tiled)(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank,
                                                const_cast<void*>(base), gdim, gstr, gbox, estr,
-                                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                               CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                               atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return mtl_set_error(ctx, MTL_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d)", (int)r, rank);
@@ -360,12 +360,12 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
         if (transA) { dims[0] = (uint64_t)M; dims[1] = (uint64_t)K; box[0] = 32; box[1] = BK; }
         else        { dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = BK; box[1] = BM; }
         strides[0] = dims[0] * 4;
-        int32_t rc = mtl_encode_tmap(ctx, &maps[i], a, 2, dims, strides, box);
+        int32_t rc = mtl_encode_tmap(ctx, &maps[i], a, 2, dims, strides, box, transA != 0);
         if (rc) return rc;
         if (transB) { dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = BK; box[1] = (uint32_t)BN; }
         else        { dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 32; box[1] = BK; }
         strides[0] = dims[0] * 4;
-        rc = mtl_encode_tmap(ctx, &maps[2 + i], b, 2, dims, strides, box);
+        rc = mtl_encode_tmap(ctx, &maps[2 + i], b, 2, dims, strides, box, transB == 0);
         if (rc) return rc;
     }
     GemmParams p;

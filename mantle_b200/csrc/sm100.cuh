@@ -126,13 +126,31 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 
 // ---------------------------------------------------------------- tcgen05.mma --------------
 
-constexpr uint64_t kDescVersion = 1ull << 46;    // descriptor version field for sm_100
-constexpr uint64_t kDescSwizzle128 = 2ull << 61;  // 128-byte swizzle
+constexpr uint64_t kDescVersion = 1ull << 46;  // descriptor version field for sm_100
+// Swizzle modes of a shared-memory operand tile (descriptor bits 61-63).  K-major tf32 tiles use
+// the ordinary 128-byte swizzle (16-byte chunks); MN-major tf32 tiles must use the 128-byte
+// swizzle with 32-byte chunks, the only MN-major layout the tensor core accepts for 32-bit
+// operands.  The TMA map that fills the tile has to use the matching mode.
+constexpr uint64_t kSwizzle128 = 2ull << 61;
+constexpr uint64_t kSwizzle128Atom32 = 1ull << 61;
 
 // Shared-memory matrix descriptor; addresses and offsets in bytes (multiples of 16).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint64_t swizzle = kSwizzle128) {
     return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | kDescVersion | kDescSwizzle128;
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | kDescVersion | swizzle;
+}
+
+// Operand tile stored K-major: rows (one per M/N index) of 32 floats = 128 bytes, 8-row groups
+// 1024 bytes apart; one MMA (K = 8) starts 32 bytes further along the row.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t tile, int kk) {
+    return make_smem_desc(tile + kk * 32, 16, 1024, kSwizzle128);
+}
+// Operand tile stored MN-major as chunks of {32 M/N indices x 32 K rows}: rows of 128 bytes, one
+// per K index, 4-row swizzle groups 512 bytes apart, chunks 4096 bytes apart; one MMA (K = 8)
+// starts 8 rows = 1024 bytes further.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t tile, int kk) {
+    return make_smem_desc(tile + kk * 1024, 4096, 512, kSwizzle128Atom32);
 }
 
 // Instruction descriptor for kind::tf32, fp32 accumulate, M = 128.
@@ -186,7 +204,8 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 struct mtl_ctx;
 
-// Encodes a tiled fp32 tensor map with 128-byte swizzle and zero fill outside the tensor.
+// Encodes a tiled fp32 tensor map with 128-byte swizzle (16-byte chunks, or 32-byte chunks when
+// atom32 is set) and zero fill outside the tensor.
 // dims/box: innermost first; strides_bytes: rank-1 entries for dims 1..rank-1.
 int32_t mtl_encode_tmap(mtl_ctx* ctx, CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                        const uint64_t* strides_bytes, const uint32_t* box);
+                        const uint64_t* strides_bytes, const uint32_t* box, bool atom32 = false);

@@ -265,6 +265,7 @@ void Model::zero_grads() {
 }
 
 void Model::copy_inputs_async(const std::vector<const float*>& in) {
+    if (in.empty()) return;  // keep the inputs already resident in the arena
     if (in.size() != g_.inputs.size()) throw Error(MTL_ERR_INVALID, "wrong number of inputs");
     for (size_t i = 0; i < in.size(); ++i)
         check(mtl_h2d_async(ctx_, T(g_.inputs[i]), in[i], (size_t)g_.inputs[i].shape.num_elements() * 4), "input copy");

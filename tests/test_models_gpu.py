@@ -1,0 +1,162 @@
+"""Model-level parity: the host mirror of Mantle's executor (Model.forward / backward, Adam.step)
+driving the CUDA kernels, against the CPU oracle's executor and the PyTorch fixtures, on the
+BASELINE configurations' graphs with identical injected weights.  Loss trajectories are held to
+1e-3 relative (1e-4 for the two regression networks, as tests/python/test_models_*.mojo do)."""
+import numpy as np
+import pytest
+
+import mantle_b200 as mb
+import oracle
+from mantle_b200 import OP, host_api
+from helpers import assert_close, golden
+from test_oracle_kat import TRAJ, _train, build_cnn, load_weights
+
+pytestmark = pytest.mark.gpu
+
+
+class GpuNs:
+    OP = OP
+    nn = host_api.nn
+    Graph = host_api.Graph
+
+
+def make_pair(ctx, builder, weights=None, seed=0):
+    """The same graph on the GPU mirror and on the oracle, with the same parameter values."""
+    g, og = host_api.Graph(), oracle.Graph()
+    builder(GpuNs, g)
+    builder(oracle, og)
+    m, om = host_api.Model(ctx, g), oracle.Model(og)
+    tr, otr = [s for s in g.params() if s.trainable], [s for s in og.params() if s.trainable]
+    if weights is None:
+        rng = np.random.default_rng(seed)
+        weights = []
+        for s in otr:
+            fan_in = s.shape[0] if len(s.shape) <= 2 else int(np.prod(s.shape[1:]))
+            if len(s.shape) == 1:
+                fan_in = 64
+            weights.append(rng.uniform(-1, 1, s.shape).astype(np.float32) / np.float32(np.sqrt(fan_in)))
+    for s, os_, w in zip(tr, otr, weights):
+        m.set_tensor(s, w)
+        om.set_tensor(os_, w)
+    return (g, m), (og, om)
+
+
+@pytest.mark.parametrize("name,builder,lr,rtol,steps", TRAJ)
+def test_loss_trajectories(ctx, name, builder, lr, rtol, steps):
+    z = golden("models")
+    n_tr = {"reg": 2}.get(name, 6)
+    (g, m), (og, om) = make_pair(ctx, builder, load_weights(z, name, n_tr))
+    inputs = (z[name + "__x"], z[name + "__y"])
+    got = _train(m, host_api.Adam(m, lr=lr), inputs, steps)
+    want = _train(om, oracle.Adam(om, lr=lr), inputs, steps)
+    assert_close(got, want, rtol, 1e-6, name + " vs oracle")
+    assert_close(got, z[name + "__losses"][:steps], max(rtol, 1e-3) if name.startswith("cnn") else rtol, 1e-6,
+                 name + " vs torch fixture")
+    # final parameters agree as well
+    # final parameters agree as well (Adam's per-element normalisation amplifies rounding on
+    # elements with tiny gradients, so the comparison is per tensor, in the L2 norm)
+    for s, os_ in zip([s for s in g.params() if s.trainable], [s for s in og.params() if s.trainable]):
+        a, b = m.tensor(s).astype(np.float64), om.tensor(os_).astype(np.float64)
+        assert np.linalg.norm(a - b) <= 2e-2 * np.linalg.norm(b) + 1e-6, name + " final parameters"
+
+
+def test_single_step_gradients_match_oracle(ctx):
+    """One forward/backward of the CNN: every parameter gradient and the activations' gradients."""
+    (g, m), (og, om) = make_pair(ctx, lambda ns, gg: build_cnn(ns, gg, 8), seed=3)
+    rng = np.random.default_rng(4)
+    x = rng.uniform(0, 1, (8, 1, 28, 28)).astype(np.float32)
+    y = np.eye(10, dtype=np.float32)[rng.integers(0, 10, 8)]
+    for strict in (True, False):
+        m.set_overwrite_first(not strict)
+        loss, oloss = m.forward(x, y), om.forward(x, y)
+        assert abs(loss - oloss) <= 1e-5 * abs(oloss) + 1e-6
+        m.zero_grads(); om.zero_grads()
+        m.backward(); om.backward()
+        for s, os_ in zip(g.params(), og.params()):
+            if s.trainable:
+                assert_close(m.grad(s), om.grad(os_), 1e-4, 1e-6, "grad of param %d (strict=%s)" % (s.id, strict))
+        for i in range(g.counts()["nodes"]):  # activations: outputs and their gradients
+            sid = g.node(i)["output"]
+            s, os_ = host_api.Symbol(g, sid), og.nodes[i].outputs[0]
+            assert_close(m.tensor(s), om.tensor(os_), 1e-4, 1e-5, "output of node %d" % i)
+            if s.trainable:
+                assert_close(m.grad(s), om.grad(os_), 1e-4, 1e-6, "grad of node %d output" % i)
+
+
+def test_accumulation_across_backward_calls_in_strict_mode(ctx):
+    """Without zero_grad a second backward() adds to the gradients (ops.mojo:405,463,498)."""
+    from test_oracle_kat import build_sin
+    (g, m), (og, om) = make_pair(ctx, build_sin, seed=5)
+    m.set_overwrite_first(False)
+    rng = np.random.default_rng(6)
+    x = rng.uniform(-3, 3, (32, 1)).astype(np.float32)
+    y = np.sin(x)
+    m.forward(x, y); om.forward(x, y)
+    m.zero_grads(); om.zero_grads()
+    m.backward(); om.backward()
+    first = [om.grad(s) for s in og.params() if s.trainable]
+    m.backward(); om.backward()
+    for s, os_, f in zip([s for s in g.params() if s.trainable], [s for s in og.params() if s.trainable], first):
+        assert_close(m.grad(s), om.grad(os_), 1e-4, 1e-5, "accumulated grad")
+        assert not np.allclose(om.grad(os_), f) or np.allclose(f, 0)
+
+
+def test_inference_outputs(ctx):
+    (g, m), (og, om) = make_pair(ctx, lambda ns, gg: build_cnn(ns, gg, 4), seed=7)
+    rng = np.random.default_rng(8)
+    x = rng.uniform(0, 1, (4, 1, 28, 28)).astype(np.float32)
+    y = np.zeros((4, 10), np.float32)
+    out_sym = host_api.Symbol(g, g.node(8)["output"])  # the logits (g.out)
+    got = m.inference(x, y, outputs=[out_sym])[0]
+    want = om.inference(x, y)[0]
+    assert got.shape == (4, 10)
+    assert_close(got, want, 1e-4, 1e-5, "logits")
+
+
+def test_widened_cnn_uses_tensor_cores_and_matches(ctx):
+    """BASELINE config 4's network (Conv 1->64, 64->128, Linear 6272->10) at a small batch: conv2's
+    forward and input gradient run on the tcgen05 implicit-GEMM kernels."""
+    B = 8
+    build = lambda ns, gg: build_cnn(ns, gg, B, 64, 128)
+    (g, m), (og, om) = make_pair(ctx, build, seed=9)
+    rng = np.random.default_rng(10)
+    x = rng.uniform(0, 1, (B, 1, 28, 28)).astype(np.float32)
+    y = np.eye(10, dtype=np.float32)[rng.integers(0, 10, B)]
+    got = _train(m, host_api.Adam(m, lr=1e-3), (x, y), 20)
+    want = _train(om, oracle.Adam(om, lr=1e-3), (x, y), 20)
+    assert_close(got, want, 1e-3, 1e-6, "widened CNN, 3xTF32")
+    assert ctx.device_status() == 0
+    # plain TF32: same trajectory within the looser tolerance
+    (g2, m2), _ = make_pair(ctx, build, seed=9)
+    ctx.set_math_mode(mb.MATH_TF32)
+    try:
+        got2 = _train(m2, host_api.Adam(m2, lr=1e-3), (x, y), 20)
+    finally:
+        ctx.set_math_mode(mb.MATH_TF32X3)
+    assert_close(got2, want, 5e-2, 1e-4, "widened CNN, TF32")
+
+
+def test_trainer_graph_replay_equals_eager(ctx):
+    """The captured-and-replayed step produces the same losses as step-by-step execution."""
+    B = 8
+    build = lambda ns, gg: build_cnn(ns, gg, B, 64, 128)
+    rng = np.random.default_rng(11)
+    xs = rng.uniform(0, 1, (6, B, 1, 28, 28)).astype(np.float32)
+    ys = np.eye(10, dtype=np.float32)[rng.integers(0, 10, (6, B))]
+    losses = {}
+    for use_graph in (False, True):
+        (g, m), _ = make_pair(ctx, build, seed=12)
+        adam = host_api.Adam(m, lr=1e-3)
+        tr = host_api.Trainer(m, adam, use_graph=use_graph)
+        losses[use_graph] = [tr.step(xs[i], ys[i]) for i in range(6)]
+        assert tr.graph_active() == use_graph
+        assert adam.iter == 6
+        tr.close()
+    assert_close(np.array(losses[True]), np.array(losses[False]), 1e-6, 1e-7, "graph vs eager")
+    # and the eager trainer equals the reference's loop order forward / zero_grad / backward / step
+    (g, m), (og, om) = make_pair(ctx, build, seed=12)
+    oad = oracle.Adam(om, lr=1e-3)
+    want = []
+    for i in range(6):
+        want.append(om.forward(xs[i], ys[i])); oad.zero_grad(); om.backward(); oad.step()
+    assert_close(np.array(losses[False]), np.array(want, np.float32), 1e-3, 1e-6, "trainer vs oracle loop")

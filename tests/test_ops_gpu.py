@@ -1,0 +1,397 @@
+"""Parity of every CUDA entry point with the CPU oracle on the same seeded inputs, called through
+the C ABI (mantle_b200.Context.forward_op / backward_op are thin ctypes wrappers).
+
+Tolerances: the reference's own `almost` comparison is rtol = atol = 1e-5
+(tests/testing_utils.mojo:16-27); that is used for everything computed in fp32 on CUDA cores.
+Tensor-core results are held to rtol 1e-4 / atol 1e-5 in 3xTF32 mode and rtol 5e-3 in plain TF32
+mode; for long reductions the absolute part is scaled by the largest output magnitude, because the
+tensor core's fp32 accumulation truncates and its error grows with the reduction length
+(normalised max error < 3e-5 in 3xTF32 mode, < 4e-3 in TF32 mode, both checked).  Max-pool values, argmax
+indices and shapes are compared exactly; MTL_MATH_FP32 DOT is compared bit-for-bit."""
+import numpy as np
+import pytest
+
+import mantle_b200 as mb
+import oracle
+from mantle_b200 import OP
+from helpers import assert_close, cases, golden
+
+pytestmark = pytest.mark.gpu
+
+
+def run_fwd(ctx, op, out_shape, *ts, **attrs):
+    d = [ctx.array(t) for t in ts]
+    res = ctx.empty(out_shape)
+    ctx.forward_op(op, res, *d, **attrs)
+    return res.numpy()
+
+
+def run_bwd(ctx, tensor_id, op, ug, *ts, grad_shape, init=None, accumulate=True, **attrs):
+    d = [ctx.array(t) for t in ts]
+    grad = ctx.zeros(grad_shape) if init is None else ctx.array(init)
+    dug = ctx.array(ug)
+    ctx.backward_op(tensor_id, op, dug, *d, grad=grad, accumulate=accumulate, **attrs)
+    return grad.numpy()
+
+
+# ------------------------------------------------------------------ elementwise ----------------
+
+BIN = {"add": OP.ADD, "sub": OP.SUB, "mul": OP.MUL, "div": OP.DIV}
+
+
+def test_binary_forward_backward(ctx):
+    z = golden("ops")
+    rng = np.random.default_rng(1)
+    for name in cases(z, "bin_"):
+        f = lambda k: z["bin_%s__%s" % (name, k)]
+        op = BIN[name[:3]]
+        a, b, ug = f("a"), f("b"), f("ug")
+        want = oracle.binary_fwd(op, a, b)
+        assert_close(run_fwd(ctx, op, want.shape, a, b), want, what=name)
+        assert_close(want, f("c"), what=name + " (torch)")
+        for tid, t in ((0, a), (1, b)):
+            init = rng.normal(0, 1, t.shape).astype(np.float32)
+            want_g = oracle.binary_bwd(op, tid, ug, a, b, grad=init.copy())
+            got = run_bwd(ctx, tid, op, ug, a, b, grad_shape=t.shape, init=init)
+            assert_close(got, want_g, 1e-5, 1e-4, "%s d%d accumulate" % (name, tid))
+            got = run_bwd(ctx, tid, op, ug, a, b, grad_shape=t.shape, init=init, accumulate=False)
+            assert_close(got, oracle.binary_bwd(op, tid, ug, a, b), 1e-5, 1e-4, "%s d%d overwrite" % (name, tid))
+
+
+def test_scalar_operand_paths(ctx):
+    # a [1]-shaped operand selects the tensor-scalar path (tensorutils.mojo:266-269)
+    rng = np.random.default_rng(2)
+    t = rng.normal(0, 1, (33, 7)).astype(np.float32)  # odd size: exercises the non-vector tail
+    s = np.array([1.7], np.float32)
+    for op in BIN.values():
+        assert_close(run_fwd(ctx, op, t.shape, t, s), oracle.binary_fwd(op, t, s))
+        assert_close(run_fwd(ctx, op, t.shape, s, t), oracle.binary_fwd(op, s, t))
+    ug = rng.normal(0, 1, t.shape).astype(np.float32)
+    # gradient of a trainable [1] operand: everything sums into one element
+    assert_close(run_bwd(ctx, 1, OP.ADD, ug, t, s, grad_shape=(1,)), oracle.binary_bwd(OP.ADD, 1, ug, t, s), 1e-5, 1e-4)
+    assert_close(run_bwd(ctx, 1, OP.DIV, ug, t, s, grad_shape=(1,)), oracle.binary_bwd(OP.DIV, 1, ug, t, s), 1e-4, 1e-4)
+
+
+UNARY = {"exp": (OP.EXP, {}), "log": (OP.LOG, {}), "sigmoid": (OP.SIGMOID, {}), "relu": (OP.RELU, {}),
+         "tanh": (OP.TANH, {}), "pow2": (OP.POW, {"exponent": 2}), "pow3": (OP.POW, {"exponent": 3}),
+         "leakyrelu": (OP.LEAKYRELU, {"negative_slope": 0.1}), "clip": (OP.CLIP, {"min": -0.3, "max": 0.4})}
+
+
+def test_unary_forward_backward(ctx):
+    z = golden("ops")
+    for name, (op, kw) in UNARY.items():
+        x, ug = z["un_%s__x" % name], z["un_%s__ug" % name]
+        assert_close(run_fwd(ctx, op, x.shape, x, **kw), oracle.forward_op(op, x, **kw), what=name)
+        init = np.full(x.shape, 0.5, np.float32)
+        want = oracle.backward_op(0, op, ug, x, grad=init.copy(), **kw)
+        assert_close(run_bwd(ctx, 0, op, ug, x, grad_shape=x.shape, init=init, **kw), want, what=name + " bwd")
+        assert_close(run_bwd(ctx, 0, op, ug, x, grad_shape=x.shape, init=init, accumulate=False, **kw),
+                     oracle.backward_op(0, op, ug, x, **kw), what=name + " bwd overwrite")
+
+
+def test_relu_large_vectorised(ctx):
+    rng = np.random.default_rng(3)
+    x = rng.normal(0, 1, (8, 16, 28, 28)).astype(np.float32)
+    ug = rng.normal(0, 1, x.shape).astype(np.float32)
+    got = run_fwd(ctx, OP.RELU, x.shape, x)
+    assert np.array_equal(got, np.maximum(x, 0) * (x > 0))
+    assert np.array_equal(run_bwd(ctx, 0, OP.RELU, ug, x, grad_shape=x.shape), oracle.backward_op(0, OP.RELU, ug, x))
+
+
+def test_copy_ops_and_fill(ctx):
+    rng = np.random.default_rng(4)
+    x = rng.normal(0, 1, (3, 32, 7, 7)).astype(np.float32)
+    assert np.array_equal(run_fwd(ctx, OP.RESHAPE, (3, 1568), x).ravel(), x.ravel())
+    assert np.array_equal(run_fwd(ctx, OP.FLATTEN, (3, 1568), x).ravel(), x.ravel())
+    ug = rng.normal(0, 1, (3, 1568)).astype(np.float32)
+    init = rng.normal(0, 1, x.shape).astype(np.float32)
+    got = run_bwd(ctx, 0, OP.RESHAPE, ug, x, grad_shape=x.shape, init=init)
+    assert_close(got.ravel(), init.ravel() + ug.ravel())
+    d = ctx.empty((1001,))
+    ctx._check(ctx.lib.mtl_fill_f32(ctx.handle, d.ptr, 1001, 2.5))
+    assert np.array_equal(d.numpy(), np.full(1001, 2.5, np.float32))
+
+
+# ------------------------------------------------------------------ reductions -----------------
+
+RED = {"sum": OP.SUM, "mean": OP.MEAN, "max": OP.MAX}
+
+
+def test_reductions(ctx):
+    z = golden("ops")
+    x = z["red__x"]
+    for rname, op in RED.items():
+        for axis in (None, 0, 1, 2):
+            key = "red_%s_%s" % (rname, "all" if axis is None else axis)
+            want = oracle.reduce_fwd(op, x, axis)
+            assert_close(run_fwd(ctx, op, want.shape, x, axis=axis), want, 1e-5, 1e-5, key)
+            ug = z[key + "__ug"]
+            init = np.full(x.shape, 0.25, np.float32)
+            want_g = oracle.reduce_bwd(op, ug, x, axis, grad=init.copy())
+            assert_close(run_bwd(ctx, 0, op, ug, x, grad_shape=x.shape, init=init, axis=axis), want_g, 1e-5, 1e-6, key + " bwd")
+
+
+def test_reduce_large_and_long_axis(ctx):
+    rng = np.random.default_rng(5)
+    x = rng.normal(0, 1, (300001,)).astype(np.float32)
+    for op in (OP.SUM, OP.MEAN, OP.MAX):
+        want = oracle.reduce_fwd(op, x)
+        assert_close(run_fwd(ctx, op, (1,), x), want, 1e-4, 1e-3, "all %d" % op)  # summation order differs
+    x = rng.normal(0, 1, (3, 2048, 5)).astype(np.float32)
+    for op in (OP.SUM, OP.MAX):
+        want = oracle.reduce_fwd(op, x, 1)
+        assert_close(run_fwd(ctx, op, want.shape, x, axis=1), want, 1e-4, 1e-4, "long axis %d" % op)
+
+
+def test_max_backward_ties(ctx):
+    # test_backward.mojo:222-309
+    t = np.ones((2, 3), np.float32)
+    t[0, 0] = t[0, 1] = 2
+    got = run_bwd(ctx, 0, OP.MAX, np.array([9], np.float32), t, grad_shape=t.shape)
+    assert_close(got, oracle.backward_op(0, OP.MAX, np.array([9], np.float32), t))
+    assert got[0, 0] == 4.5 and got[0, 1] == 4.5
+    base = np.arange(1, 13, dtype=np.float32).reshape(2, 3, 2)
+    for axis, first, ug_shape in ((0, 7, (1, 3, 2)), (1, 5, (2, 1, 2)), (2, 2, (2, 3, 1))):
+        t = base.copy()
+        t.ravel()[0] = first
+        ug = np.full(ug_shape, 2, np.float32)
+        assert_close(run_bwd(ctx, 0, OP.MAX, ug, t, grad_shape=t.shape, axis=axis), oracle.backward_op(0, OP.MAX, ug, t, axis=axis))
+
+
+# ------------------------------------------------------------------ DOT ------------------------
+
+def dot_all(ctx, a, b, ug):
+    M, K = a.shape
+    N = b.shape[1]
+    c = run_fwd(ctx, OP.DOT, (M, N), a, b)
+    da = run_bwd(ctx, 0, OP.DOT, ug, a, b, grad_shape=a.shape, accumulate=False)
+    db = run_bwd(ctx, 1, OP.DOT, ug, a, b, grad_shape=b.shape, accumulate=False)
+    return c, da, db
+
+
+def test_dot_fp32_bit_exact(ctx):
+    """MTL_MATH_FP32: ascending-k fmaf chains, identical bits to the reference's accumulation order."""
+    z = golden("ops")
+    ctx.set_math_mode(mb.MATH_FP32)
+    try:
+        for name in cases(z, "dot"):
+            a, b, ug = z["dot%s__a" % name], z["dot%s__b" % name], z["dot%s__ug" % name]
+            c, da, db = dot_all(ctx, a, b, ug)
+            assert np.array_equal(c, oracle.dot(a, b)), name
+            assert np.array_equal(da, oracle.dot_transpose_t2(ug, b)), name
+            assert np.array_equal(db, oracle.dot_transpose_t1(a, ug)), name
+            assert_close(c, z["dot%s__c" % name], 1e-5, 1e-5, "torch")
+        # KAT: tests/mojo/test_ops.mojo:69-80 and test_backward.mojo:96-113
+        c, da, db = dot_all(ctx, np.full((2, 3), 1, np.float32), np.full((3, 2), 2, np.float32), np.ones((2, 2), np.float32))
+        assert np.all(c == 6) and np.all(da == 4) and np.all(db == 2)
+    finally:
+        ctx.set_math_mode(mb.MATH_TF32X3)
+
+
+def rel_err(got, want):
+    return float(np.max(np.abs(got.astype(np.float64) - want)) / np.max(np.abs(want)))
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 32, 128), (256, 96, 128), (384, 256, 256), (200, 136, 264), (512, 1024, 384)])
+def test_dot_tensor_core(ctx, M, K, N):
+    """tcgen05 path (all four operand major-ness combinations via fwd / dA / dB), both modes."""
+    rng = np.random.default_rng(M + K + N)
+    a = rng.normal(0, 1, (M, K)).astype(np.float32)
+    b = rng.normal(0, 1, (K, N)).astype(np.float32)
+    ug = rng.normal(0, 1, (M, N)).astype(np.float32)
+    want = (a.astype(np.float64) @ b, ug.astype(np.float64) @ b.T.astype(np.float64), a.T.astype(np.float64) @ ug)
+    for mode, tol in ((mb.MATH_TF32X3, 3e-5), (mb.MATH_TF32, 4e-3)):
+        ctx.set_math_mode(mode)
+        try:
+            got = dot_all(ctx, a, b, ug)
+        finally:
+            ctx.set_math_mode(mb.MATH_TF32X3)
+        assert ctx.device_status() == 0
+        for g, w, what in zip(got, want, ("C", "dA", "dB")):
+            e = rel_err(g, w)
+            assert e < tol, "%s mode %d: normalised max error %.3e" % (what, mode, e)
+    # element-wise tolerance of the 3xTF32 mode on unit-scale data: rtol 1e-4 / atol 1e-5
+    a1 = rng.uniform(0, 1, (M, K)).astype(np.float32) / np.float32(K)
+    b1 = rng.uniform(0, 1, (K, N)).astype(np.float32)
+    assert_close(run_fwd(ctx, OP.DOT, (M, N), a1, b1), oracle.dot(a1, b1), 1e-4, 1e-5, "x3 elementwise")
+    got_c = run_fwd(ctx, OP.DOT, (M, N), a, b)
+    assert_close(got_c, want[0].astype(np.float32), 1e-4, 1e-5 * float(np.abs(want[0]).max()), "x3 elementwise, N(0,1) data")
+    # accumulate into an existing gradient
+    init = rng.normal(0, 1, (K, N)).astype(np.float32)
+    got = run_bwd(ctx, 1, OP.DOT, ug, a, b, grad_shape=(K, N), init=init)
+    assert rel_err(got, init + want[2]) < 3e-5
+
+
+def test_dot_shapes_of_the_models(ctx):
+    # Linear layers of the benchmark networks: tiny and skinny products take the CUDA-core path
+    rng = np.random.default_rng(9)
+    for M, K, N in ((32, 13, 1), (32, 1, 32), (32, 32, 32), (32, 32, 1), (64, 1568, 10), (16, 6272, 10)):
+        a = rng.normal(0, 1, (M, K)).astype(np.float32)
+        b = rng.normal(0, 1, (K, N)).astype(np.float32)
+        ug = rng.normal(0, 1, (M, N)).astype(np.float32)
+        c, da, db = dot_all(ctx, a, b, ug)
+        assert np.array_equal(c, oracle.dot(a, b))
+        assert np.array_equal(da, oracle.dot_transpose_t2(ug, b))
+        assert np.array_equal(db, oracle.dot_transpose_t1(a, ug))
+
+
+# ------------------------------------------------------------------ CONV2D ---------------------
+
+def conv_all(ctx, x, w, b, ug, **kw):
+    y = run_fwd(ctx, OP.CONV2D, ug.shape, x, w, b, **kw)
+    bd = np.zeros_like(b)
+    dx = run_bwd(ctx, 0, OP.CONV2D, ug, x, w, bd, grad_shape=x.shape, accumulate=False, **kw)
+    dw = run_bwd(ctx, 1, OP.CONV2D, ug, x, w, bd, grad_shape=w.shape, accumulate=False, **kw)
+    db = run_bwd(ctx, 2, OP.CONV2D, ug, x, w, bd, grad_shape=b.shape, accumulate=False, **kw)
+    return y, dx, dw, db
+
+
+def test_conv_reference_cases(ctx):
+    """The padding / stride / dilation cases of tests/python/test_conv.mojo and the CNN layers."""
+    z = golden("conv_pool")
+    for name in cases(z, "conv_"):
+        f = lambda k: z["conv_%s__%s" % (name, k)]
+        a = f("attrs")
+        kw = dict(padding=tuple(int(v) for v in a[0:2]), stride=tuple(int(v) for v in a[2:4]),
+                  dilation=tuple(int(v) for v in a[4:6]))
+        x, w, b, ug = f("x"), f("w"), f("b"), f("ug")
+        y, dx, dw, db = conv_all(ctx, x, w, b, ug, **kw)
+        assert y.shape == f("y").shape
+        assert_close(y, oracle.conv2d_fwd(x, w, b, **kw), 1e-4, 1e-5, name + " y")
+        assert_close(dx, oracle.conv2d_bwd(0, ug, x, w, **kw), 1e-4, 1e-4, name + " dx")
+        assert_close(dw, oracle.conv2d_bwd(1, ug, x, w, **kw), 1e-4, 1e-3, name + " dw")
+        assert_close(db, oracle.conv2d_bwd(2, ug, x, w, **kw), 1e-4, 1e-3, name + " db")
+        assert_close(y, f("y"), 1e-4, 1e-5, name + " y (torch)")
+        assert_close(dw, f("dw"), 1e-4, 1e-3, name + " dw (torch)")
+        # accumulate semantics of backward_op (ops.mojo:498)
+        init = np.full(w.shape, 0.5, np.float32)
+        got = run_bwd(ctx, 1, OP.CONV2D, ug, x, w, np.zeros_like(b), grad_shape=w.shape, init=init, **kw)
+        assert_close(got, init + oracle.conv2d_bwd(1, ug, x, w, **kw), 1e-4, 1e-3, name + " dw accumulate")
+
+
+TC_CONV = [  # (N, C, H, W, K, R, S, pad): stride 1, dilation 1 -> implicit GEMM on tensor cores
+    (4, 32, 8, 8, 64, 3, 3, 1),
+    (6, 64, 14, 14, 128, 5, 5, 2),
+    (3, 64, 12, 10, 64, 3, 3, 0),
+    (5, 16, 14, 14, 32, 5, 5, 2),
+    (2, 64, 56, 56, 64, 3, 3, 1),
+]
+
+
+@pytest.mark.parametrize("case", TC_CONV)
+def test_conv_tensor_core(ctx, case):
+    N, C, H, W, K, R, S, p = case
+    rng = np.random.default_rng(sum(case))
+    x = rng.normal(0, 1, (N, C, H, W)).astype(np.float32)
+    w = (rng.normal(0, 1, (K, C, R, S)) / np.sqrt(C * R * S)).astype(np.float32)
+    b = rng.normal(0, 1, K).astype(np.float32)
+    kw = dict(padding=(p, p), stride=(1, 1), dilation=(1, 1))
+    want_y = oracle.conv2d_fwd(x, w, b, **kw)
+    ug = rng.normal(0, 1, want_y.shape).astype(np.float32)
+    want = (want_y, oracle.conv2d_bwd(0, ug, x, w, **kw), oracle.conv2d_bwd(1, ug, x, w, **kw),
+            oracle.conv2d_bwd(2, ug, x, w, **kw))
+    for mode, tol in ((mb.MATH_TF32X3, 3e-5), (mb.MATH_TF32, 4e-3), (mb.MATH_FP32, 5e-6)):
+        ctx.set_math_mode(mode)
+        try:
+            got = conv_all(ctx, x, w, b, ug, **kw)
+        finally:
+            ctx.set_math_mode(mb.MATH_TF32X3)
+        assert ctx.device_status() == 0
+        for g, wv, what in zip(got, want, ("y", "dx", "dw", "db")):
+            e = rel_err(g, wv.astype(np.float64))
+            assert e < tol, "%s mode %d: normalised max error %.3e" % (what, mode, e)
+    # element-wise tolerance in 3xTF32 mode
+    got = conv_all(ctx, x, w, b, ug, **kw)
+    assert_close(got[0], want[0], 1e-4, 1e-5 * float(np.abs(want[0]).max()), "y x3 elementwise")
+    init = rng.normal(0, 1, x.shape).astype(np.float32)
+    acc = run_bwd(ctx, 0, OP.CONV2D, ug, x, w, np.zeros_like(b), grad_shape=x.shape, init=init, **kw)
+    assert rel_err(acc, (init + want[1]).astype(np.float64)) < 3e-5
+
+
+# ------------------------------------------------------------------ MAXPOOL2D ------------------
+
+def test_maxpool_reference_cases(ctx):
+    z = golden("conv_pool")
+    for name in cases(z, "pool_"):
+        f = lambda k: z["pool_%s__%s" % (name, k)]
+        a = [int(v) for v in f("attrs")]
+        kw = dict(kernel_size=tuple(a[0:2]), padding=tuple(a[2:4]), stride=tuple(a[4:6]), dilation=tuple(a[6:8]))
+        x, ug = f("x"), f("ug")
+        want_y, want_idx = oracle.maxpool2d_fwd(x, return_indices=True, **kw)
+        dx_d = ctx.array(x)
+        y_d, idx_d = ctx.empty(want_y.shape), ctx.empty(want_y.shape, np.int32)
+        ctx.forward_op(OP.MAXPOOL2D, y_d, dx_d, indices=idx_d, **kw)
+        assert np.array_equal(y_d.numpy(), want_y), name          # bit-exact values
+        assert np.array_equal(idx_d.numpy(), want_idx), name      # bit-exact argmax indices
+        assert np.array_equal(idx_d.numpy(), f("idx")), name      # and the indices torch reports
+        want_dx = oracle.maxpool2d_bwd(ug, x, **kw)
+        got = run_bwd(ctx, 0, OP.MAXPOOL2D, ug, x, grad_shape=x.shape, accumulate=False, **kw)
+        assert_close(got, want_dx, 1e-6, 1e-6, name + " dx (recompute)")
+        g = ctx.zeros(x.shape)
+        ctx.backward_op(0, OP.MAXPOOL2D, ctx.array(ug), dx_d, grad=g, indices=idx_d, accumulate=True, **kw)
+        assert_close(g.numpy(), want_dx, 1e-6, 1e-6, name + " dx (indices)")
+        assert_close(want_dx, f("dx"), 1e-6, 1e-6, name + " dx (torch)")
+
+
+def test_maxpool_ties_nan_and_empty_windows(ctx):
+    kw = dict(kernel_size=(2, 2), stride=(2, 2))
+    x = np.ones((1, 1, 4, 4), np.float32)  # ties: the first element in (kx, ky) scan order wins
+    y, idx = ctx.empty((1, 1, 2, 2)), ctx.empty((1, 1, 2, 2), np.int32)
+    ctx.forward_op(OP.MAXPOOL2D, y, ctx.array(x), indices=idx, **kw)
+    assert idx.numpy().ravel().tolist() == [0, 2, 8, 10]
+    x[0, 0, 0, 0] = np.nan                # NaN never wins the strict `>` comparison
+    x[0, 0, 2:, 2:] = -np.inf             # a window with nothing above -inf selects nothing
+    ctx.forward_op(OP.MAXPOOL2D, y, ctx.array(x), indices=idx, **kw)
+    want_y, want_idx = oracle.maxpool2d_fwd(x, return_indices=True, **kw)
+    assert np.array_equal(idx.numpy(), want_idx) and idx.numpy().ravel()[0] == 1 and idx.numpy().ravel()[3] == -1
+    assert np.array_equal(y.numpy(), want_y)
+    ug = np.arange(1, 5, dtype=np.float32).reshape(1, 1, 2, 2)
+    got = run_bwd(ctx, 0, OP.MAXPOOL2D, ug, x, grad_shape=x.shape, accumulate=False, **kw)
+    assert np.array_equal(got, oracle.maxpool2d_bwd(ug, x, **kw))  # the empty window routes nothing
+
+
+def test_maxpool_overlapping_windows_accumulate(ctx):
+    rng = np.random.default_rng(11)
+    x = rng.normal(0, 1, (2, 3, 9, 11)).astype(np.float32)
+    kw = dict(kernel_size=(3, 3), stride=(1, 2), padding=(1, 1))
+    want_y = oracle.maxpool2d_fwd(x, **kw)
+    ug = rng.normal(0, 1, want_y.shape).astype(np.float32)
+    init = rng.normal(0, 1, x.shape).astype(np.float32)
+    got = run_bwd(ctx, 0, OP.MAXPOOL2D, ug, x, grad_shape=x.shape, init=init, **kw)
+    assert_close(got, init + oracle.maxpool2d_bwd(ug, x, **kw), 1e-5, 1e-5)
+
+
+# ------------------------------------------------------------------ Adam -----------------------
+
+def test_adam_matches_oracle(ctx):
+    rng = np.random.default_rng(12)
+    n = 28938 + 3  # the CNN's parameter count plus an unaligned tail
+    p = rng.normal(0, 1, n).astype(np.float32)
+    m = np.zeros(n, np.float32)
+    v = np.zeros(n, np.float32)
+    dp, dm, dv = ctx.array(p), ctx.array(m), ctx.array(v)
+    for t in range(1, 6):
+        g = rng.normal(0, 0.1, n).astype(np.float32)
+        oracle.adam_step(p, g, m, v, 1e-3, 0.9, 0.999, 1e-8, t)
+        ctx.adam_step(dp, ctx.array(g), dm, dv, n, 1e-3, 0.9, 0.999, 1e-8, t)
+        assert_close(dp.numpy(), p, 1e-5, 1e-6, "params step %d" % t)
+        assert_close(dm.numpy(), m, 1e-5, 1e-7, "m step %d" % t)
+        assert_close(dv.numpy(), v, 1e-5, 1e-9, "v step %d" % t)
+
+
+# ------------------------------------------------------------------ error behaviour ------------
+
+def test_invalid_arguments_return_status(ctx):
+    L, h = ctx.lib, ctx.handle
+    a = ctx.zeros((4, 4))
+    assert L.mtl_dot_fwd(h, a.ptr, a.ptr, None, 4, 4, 4) == 1
+    assert L.mtl_unary_fwd(h, OP.DOT, a.ptr, a.ptr, 16, 0.0, 0.0) == 1
+    assert b"not a unary" in L.mtl_last_error(h)
+    assert L.mtl_adam_step(h, a.ptr, a.ptr, a.ptr, a.ptr, 16, 1e-3, 0.9, 0.999, 1e-8, 0, 1.0) == 1
+    s2 = (2 * np.ones(1)).astype(np.int64)
+    with pytest.raises(mb.MantleError):
+        ctx.forward_op(OP.ADD, a, ctx.zeros((3,)), ctx.zeros((4,)))
+    with pytest.raises(mb.MantleError):
+        ctx.forward_op(25, a, a)  # SLICE
+    assert ctx.device_status() == 0
+    assert ctx.launch_count() > 0
