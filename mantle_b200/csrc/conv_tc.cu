@@ -392,6 +392,217 @@ bool igemm_geometry_ok(const ConvGeom& g) {
     return g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1;
 }
 
+// ------------------------------------------------------------------ kernel gradient -----------
+// dW[k, c, r, s] = sum over pixels (n, oh, ow) of ug[n, k, oh, ow] * X[n, c, oh + r - ph, ow + s - pw].
+// GEMM view per filter tap: D_tap[k, c] with the pixels as the reduction axis.  Both operands are
+// channels-last copies, so the channel axis (k of ug, c of X) is contiguous = MN-major tiles:
+//   A  {128 out-channels x 32 pixels}  from ug,  one TMA box {32 ch, bw, bh, bn} per 32 channels
+//   B  {C in-channels x 32 pixels} per tap, from X, box origin shifted by the tap, zero fill = padding
+// One CTA owns a group of T taps (T*C <= 512 accumulator columns), one 128-wide slice of the
+// output channels and a contiguous range of pixel chunks; the A tile of a stage is shared by all
+// taps of the group.  Partial sums go to scratch [split][tap][k][c] and are folded by a second
+// kernel in a fixed order (deterministic).
+
+constexpr int kWgradPix = 32;  // pixels per pipeline stage = reduction extent of 4 MMAs
+
+struct WgradParams {
+    int N, OH, OW, Kout, C;
+    int R, S, ph, pw;
+    int bw, bh, bn;             // pixel box, bw*bh*bn == 32
+    int tiles_w, tiles_h, tiles_nb;
+    int T, ngroups, ktiles, nsplit, chunks_per_split;
+    int stages, stage_bytes;
+    int nseg, segA[3], segB[3];
+    uint32_t tmem_cols;
+    float* partial;             // [nsplit][R*S][Kout][C]
+    int32_t* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+k_conv_wgrad_tc(const __grid_constant__ CUtensorMap mapU0, const __grid_constant__ CUtensorMap mapU1,
+                const __grid_constant__ CUtensorMap mapX0, const __grid_constant__ CUtensorMap mapX1, WgradParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.stages * p.stage_bytes);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + 8;
+    uint64_t* acc_full = bars + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    // work item: (tap group, out-channel tile, pixel split)
+    int item = blockIdx.x;
+    const int split = item % p.nsplit;
+    item /= p.nsplit;
+    const int kt = item % p.ktiles;
+    const int grp = item / p.ktiles;
+    const int tap0 = grp * p.T;
+    const int ntaps = min(p.T, p.R * p.S - tap0);
+    const int cchunks = p.C / 32;
+    const int total_chunks = p.tiles_w * p.tiles_h * p.tiles_nb;
+    const int chunk_begin = split * p.chunks_per_split;
+    const int chunk_end = min(total_chunks, chunk_begin + p.chunks_per_split);
+    const int n_chunks = max(0, chunk_end - chunk_begin);
+    const int kb_total = n_chunks * p.nseg;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&mapU0);
+        prefetch_tensormap(&mapX0);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, p.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t a_bytes = 4u * 4096u;
+    const uint32_t tx_bytes = a_bytes + (uint32_t)(ntaps * cchunks) * 4096u;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; kb < kb_total && ok; ++kb) {
+                if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+                const int seg = kb / n_chunks;
+                int pc = chunk_begin + (kb - seg * n_chunks);
+                const int tw = pc % p.tiles_w;
+                pc /= p.tiles_w;
+                const int th = pc % p.tiles_h;
+                const int tnb = pc / p.tiles_h;
+                const int ow0 = tw * p.bw, oh0 = th * p.bh, n0 = tnb * p.bn;
+                const CUtensorMap* mu = p.segA[seg] ? &mapU1 : &mapU0;
+                const CUtensorMap* mx = p.segB[seg] ? &mapX1 : &mapX0;
+                uint8_t* sa = tiles + stage * p.stage_bytes;
+                uint8_t* sb = sa + a_bytes;
+                mbar_arrive_expect_tx(&full[stage], tx_bytes);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) tma_load_4d(sa + j * 4096, mu, &full[stage], kt * BM + j * 32, ow0, oh0, n0);
+                for (int t = 0; t < ntaps; ++t) {
+                    const int rs = tap0 + t;
+                    const int r = rs / p.S, s = rs - r * p.S;
+                    for (int jc = 0; jc < cchunks; ++jc)
+                        tma_load_4d(sb + (t * cchunks + jc) * 4096, mx, &full[stage], jc * 32, ow0 + s - p.pw,
+                                    oh0 + r - p.ph, n0);
+                }
+                if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+            }
+            if (!ok) atomicExch(p.status, MTL_ERR_TIMEOUT);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // taps are multiplied in groups of up to 256 / C so that one instruction covers several
+            const int taps_per_mma = max(1, 256 / p.C);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; kb < kb_total && ok; ++kb) {
+                if (!mbar_wait(&full[stage], phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t sa = smem_u32(tiles + stage * p.stage_bytes);
+                const uint32_t sb = sa + a_bytes;
+                for (int t0 = 0; t0 < ntaps; t0 += taps_per_mma) {
+                    const int nt = min(taps_per_mma, ntaps - t0);
+                    const uint32_t idesc = make_idesc_tf32(nt * p.C, true, true);
+                    const uint32_t sbt = sb + (uint32_t)(t0 * cchunks) * 4096u;
+#pragma unroll
+                    for (int kk = 0; kk < kWgradPix / 8; ++kk)
+                        mma_tf32(tmem_base + (uint32_t)(t0 * p.C), desc_mn_major(sa, kk), desc_mn_major(sbt, kk), idesc,
+                                 (kb | kk) ? 1u : 0u);
+                }
+                mma_commit(&empty[stage]);
+                if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+            }
+            if (ok) mma_commit(acc_full);
+            else atomicExch(p.status, MTL_ERR_TIMEOUT);
+        }
+    } else {
+        const int quad = warp & 3;
+        const int k = kt * BM + quad * 32 + lane;
+        bool ok = true;
+        if (kb_total > 0) {
+            ok = mbar_wait(acc_full, 0, abort_flag, kWaitBudgetNs);
+            tc_fence_after_sync();
+        }
+        if (ok) {
+            for (int t = 0; t < ntaps; ++t) {
+                float* dst = p.partial + (((int64_t)split * p.R * p.S + tap0 + t) * p.Kout + k) * p.C;
+                for (int jc = 0; jc < cchunks; ++jc) {
+                    uint32_t r[32];
+                    if (kb_total > 0) {
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(t * p.C + jc * 32), r);
+                        tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = 0u;
+                    }
+                    if (k < p.Kout) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4*>(dst + jc * 32 + j) =
+                                make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                            __uint_as_float(r[j + 3]));
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            atomicExch(p.status, MTL_ERR_TIMEOUT);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, p.tmem_cols);
+    }
+}
+
+// dW[k][c][r][s] (+)= sum over splits of partial[split][rs][k][c]
+__global__ void __launch_bounds__(256) k_wgrad_fold(float* __restrict__ dW, const float* __restrict__ partial, int K,
+                                                    int C, int RS, int nsplit, int accumulate) {
+    int64_t total = (int64_t)K * C * RS;
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = tid; i < total; i += stride) {
+        // i enumerates the scratch layout [rs][k][c] so that reads are coalesced
+        int c = (int)(i % C);
+        int64_t q = i / C;
+        int k = (int)(q % K);
+        int rs = (int)(q / K);
+        float s = 0.0f;
+        for (int j = 0; j < nsplit; ++j) s += partial[(int64_t)j * total + i];
+        int64_t o = ((int64_t)k * C + c) * RS + rs;
+        dW[o] = accumulate ? dW[o] + s : s;
+    }
+}
+
+// A 32-pixel box {bw, bh, bn} (powers of two) covering the output with the least overhang.
+void choose_box32(int OW, int OH, int N, int* bw_, int* bh_, int* bn_) {
+    double best = -1.0;
+    for (int bw = 1; bw <= 32; bw *= 2)
+        for (int bh = 1; bw * bh <= 32; bh *= 2) {
+            int bn = 32 / (bw * bh);
+            int64_t tiles = (int64_t)((OW + bw - 1) / bw) * ((OH + bh - 1) / bh) * ((N + bn - 1) / bn);
+            double eff = (double)OW * OH * N / ((double)tiles * 32.0) + 1e-4 * bw;
+            if (eff > best) { best = eff; *bw_ = bw; *bh_ = bh; *bn_ = bn; }
+        }
+}
+
 }  // namespace
 
 bool mtl_conv_fwd_tc_supported(const ConvGeom& g, const float* X, const float* Wt, const float* Y) {
@@ -431,7 +642,101 @@ int32_t mtl_conv_dgrad_tc(mtl_ctx* ctx, float* dX, const float* ug, const float*
     return run_igemm(ctx, c, x3);
 }
 
-bool mtl_conv_wgrad_tc_supported(const ConvGeom&, const float*, const float*, const float*) { return false; }
-int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float*, const float*, const float*, const ConvGeom&, int, int) {
-    return mtl_set_error(ctx, MTL_ERR_UNSUPPORTED, "tensor-core kernel gradient not available");
+bool mtl_conv_wgrad_tc_supported(const ConvGeom& g, const float* ug, const float* X, const float* dW) {
+    if (!igemm_geometry_ok(g)) return false;
+    if (g.C < 32 || (g.C % 32) || g.C > 256 || g.K < 32 || (g.K % 4)) return false;
+    if ((int64_t)g.N * g.OH * g.OW < 4096) return false;  // too little reduction work to split
+    if ((((uintptr_t)ug) | ((uintptr_t)X) | ((uintptr_t)dW)) & 15u) return false;
+    return true;
+}
+
+int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,
+                          int accumulate, int x3) {
+    WgradParams p;
+    p.N = g.N; p.OH = g.OH; p.OW = g.OW; p.Kout = g.K; p.C = g.C;
+    p.R = g.R; p.S = g.S; p.ph = g.ph; p.pw = g.pw;
+    choose_box32(g.OW, g.OH, g.N, &p.bw, &p.bh, &p.bn);
+    p.tiles_w = (g.OW + p.bw - 1) / p.bw;
+    p.tiles_h = (g.OH + p.bh - 1) / p.bh;
+    p.tiles_nb = (g.N + p.bn - 1) / p.bn;
+    const int RS = g.R * g.S;
+    // taps per CTA: fit the accumulator columns, then balance the groups
+    int tmax = 512 / g.C;
+    if (tmax > RS) tmax = RS;
+    int best_t = 1, best_cost = 1 << 30;
+    for (int t = 1; t <= tmax; ++t) {
+        int cost = ((RS + t - 1) / t) * t;
+        if (cost < best_cost || (cost == best_cost && t > best_t)) { best_cost = cost; best_t = t; }
+    }
+    p.T = best_t;
+    p.ngroups = (RS + p.T - 1) / p.T;
+    p.ktiles = (g.K + BM - 1) / BM;
+    const int total_chunks = p.tiles_w * p.tiles_h * p.tiles_nb;
+    int nsplit = ctx->sm_count / (p.ngroups * p.ktiles);
+    if (nsplit < 1) nsplit = 1;
+    if (nsplit > total_chunks) nsplit = total_chunks;
+    p.chunks_per_split = (total_chunks + nsplit - 1) / nsplit;
+    p.nsplit = (total_chunks + p.chunks_per_split - 1) / p.chunks_per_split;
+    p.stage_bytes = 4 * 4096 + p.T * (g.C / 32) * 4096;
+    p.stages = (232448 - 2048) / p.stage_bytes;
+    if (p.stages > 8) p.stages = 8;
+    if (p.stages < 2) return mtl_set_error(ctx, MTL_ERR_UNSUPPORTED, "kernel-gradient tile does not fit shared memory");
+    uint32_t cols = 32;
+    while ((int)cols < p.T * g.C) cols *= 2;
+    p.tmem_cols = cols;
+    p.nseg = x3 ? 3 : 1;
+    if (x3) { p.segA[0] = 1; p.segB[0] = 0; p.segA[1] = 0; p.segB[1] = 1; p.segA[2] = 0; p.segB[2] = 0; }
+    else    { p.segA[0] = p.segA[1] = p.segA[2] = 0; p.segB[0] = p.segB[1] = p.segB[2] = 0; }
+    p.status = ctx->dev_status;
+
+    // scratch: channels-last copies of ug and X (hi [, lo]) and the per-split partial sums
+    const size_t n_u = (size_t)g.N * g.K * g.OH * g.OW, n_x = (size_t)g.N * g.C * g.H * g.W;
+    const size_t u_pad = (n_u + 63) & ~(size_t)63, x_pad = (n_x + 63) & ~(size_t)63;
+    const size_t n_part = (size_t)p.nsplit * RS * g.K * g.C;
+    const int parts = x3 ? 2 : 1;
+    void* ws;
+    int32_t rc = mtl_workspace(ctx, ((size_t)parts * (u_pad + x_pad) + n_part) * 4, &ws);
+    if (rc) return rc;
+    float* u_hi = (float*)ws;
+    float* u_lo = x3 ? u_hi + u_pad : nullptr;
+    float* x_hi = u_hi + (size_t)parts * u_pad;
+    float* x_lo = x3 ? x_hi + x_pad : nullptr;
+    p.partial = x_hi + (size_t)parts * x_pad;
+    MTL_REQUIRE(ctx, g.N <= 65535, "batch too large for the layout pass");
+    {
+        dim3 tg((unsigned)((g.OH * g.OW + 31) / 32), (unsigned)((g.K + 31) / 32), (unsigned)g.N);
+        if (x3) k_nchw_to_nhwc<true><<<tg, 256, 0, ctx->stream>>>(u_hi, u_lo, ug, g.K, g.OH * g.OW);
+        else k_nchw_to_nhwc<false><<<tg, 256, 0, ctx->stream>>>(u_hi, u_lo, ug, g.K, g.OH * g.OW);
+        MTL_LAUNCHED(ctx);
+        dim3 tx((unsigned)((g.H * g.W + 31) / 32), (unsigned)((g.C + 31) / 32), (unsigned)g.N);
+        if (x3) k_nchw_to_nhwc<true><<<tx, 256, 0, ctx->stream>>>(x_hi, x_lo, X, g.C, g.H * g.W);
+        else k_nchw_to_nhwc<false><<<tx, 256, 0, ctx->stream>>>(x_hi, x_lo, X, g.C, g.H * g.W);
+        MTL_LAUNCHED(ctx);
+    }
+    CUtensorMap maps[4];
+    for (int i = 0; i < 2; ++i) {
+        const float* u = (i == 1 && x3) ? u_lo : u_hi;
+        const float* x = (i == 1 && x3) ? x_lo : x_hi;
+        uint32_t box[4] = {32, (uint32_t)p.bw, (uint32_t)p.bh, (uint32_t)p.bn};
+        uint64_t udims[4] = {(uint64_t)g.K, (uint64_t)g.OW, (uint64_t)g.OH, (uint64_t)g.N};
+        uint64_t ustr[3] = {(uint64_t)g.K * 4, (uint64_t)g.OW * g.K * 4, (uint64_t)g.OH * g.OW * g.K * 4};
+        rc = mtl_encode_tmap(ctx, &maps[i], u, 4, udims, ustr, box, true);
+        if (rc) return rc;
+        uint64_t xdims[4] = {(uint64_t)g.C, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.N};
+        uint64_t xstr[3] = {(uint64_t)g.C * 4, (uint64_t)g.W * g.C * 4, (uint64_t)g.H * g.W * g.C * 4};
+        rc = mtl_encode_tmap(ctx, &maps[2 + i], x, 4, xdims, xstr, box, true);
+        if (rc) return rc;
+    }
+    const int smem_bytes = p.stages * p.stage_bytes + 1024 + 256;
+    MTL_CUDA(ctx, cudaFuncSetAttribute(k_conv_wgrad_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    const int grid = p.ngroups * p.ktiles * p.nsplit;
+    {
+        mtl_prof_scope prof(ctx, MTL_PROF_CONV_WGRAD);
+        k_conv_wgrad_tc<<<grid, kThreads, smem_bytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+    }
+    MTL_LAUNCHED(ctx);
+    int fgrid = mtl_grid_for((int64_t)g.K * g.C * RS, 256, ctx->sm_count, 8);
+    k_wgrad_fold<<<fgrid, 256, 0, ctx->stream>>>(dW, p.partial, g.K, g.C, RS, p.nsplit, accumulate);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
 }
