@@ -213,6 +213,23 @@ MTL_API int32_t mtl_reduce_bwd(mtl_ctx* ctx, int32_t op, float* grad, const floa
                                const float* in, int32_t rank, const int64_t* shape,
                                int32_t axis, int32_t accumulate);
 
+/* Whole-tensor SUM / MEAN / MAX that performs no allocation of any kind.
+ * No counterpart in the reference: it exists for hosts that must not allocate device memory at
+ * the moment they reduce -- for example an embedding whose GPU memory has been handed out in full
+ * to another pool at start-up, so that a cudaMalloc would fail, or a service loop that may not
+ * take the implicit device-wide wait an allocation can bring.  mtl_reduce_fwd keeps its per-block
+ * partial results in the context's growable workspace; this variant keeps them in a fixed array
+ * compiled into the library (4 KB, held by every GPU that loads the library until exit) and
+ * therefore accepts at most MTL_REDUCE_STATIC_MAX_ELEMENTS elements; larger sizes are rejected
+ * with MTL_ERR_INVALID.  Results equal mtl_reduce_fwd(op, out, in, 1, {n}, -1).
+ * The first call on a device looks up the array's device address (no allocation); make that call
+ * before starting a stream capture.  All calls on a device share the one array: two calls whose
+ * kernels overlap on the GPU (different streams or contexts) race and give wrong results; calls
+ * on one stream are ordered and safe. */
+#define MTL_REDUCE_STATIC_MAX_ELEMENTS (1ll << 28)
+MTL_API int32_t mtl_reduce_all_static(mtl_ctx* ctx, int32_t op, float* out, const float* in,
+                                      int64_t n);
+
 /* ---------------------------------------------------------------- optimizer ------------- */
 
 /* Adam.step (mantle/nn/optim.mojo:94-140) over one flat fp32 span of n parameters:

@@ -271,4 +271,49 @@ int32_t mtl_reduce_bwd(mtl_ctx* ctx, int32_t op, float* grad, const float* ug, c
     return MTL_OK;
 }
 
+// ------------------------------------------------------------------ no-allocation variant ----
+// Scratch for mtl_reduce_all_static: one partial per block of the first pass.  It lives in the
+// library image, so every GPU that loads the library carries these 4 KB until the process exits.
+#define MTL_STATIC_REDUCE_BLOCKS 1024
+static __device__ __align__(256) float g_static_reduce_partials[MTL_STATIC_REDUCE_BLOCKS];
+
+// Device address of the array above for each device ordinal, resolved on first use.  In host code
+// the array's name only stands for the symbol; a kernel must be handed the address that
+// cudaGetSymbolAddress reports for the device that is current.
+static float* g_static_reduce_addr[64] = {nullptr};
+
+int32_t mtl_reduce_all_static(mtl_ctx* ctx, int32_t op, float* out, const float* in, int64_t n) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, op == MTL_OP_SUM || op == MTL_OP_MEAN || op == MTL_OP_MAX,
+                "mtl_reduce_all_static: op id %d is not SUM/MEAN/MAX", op);
+    MTL_REQUIRE(ctx, out && in, "null pointer in mtl_reduce_all_static");
+    MTL_REQUIRE(ctx, n >= 1 && n <= MTL_REDUCE_STATIC_MAX_ELEMENTS,
+                "mtl_reduce_all_static handles 1..%lld elements, got %lld; use mtl_reduce_fwd for larger tensors",
+                (long long)MTL_REDUCE_STATIC_MAX_ELEMENTS, (long long)n);
+    MTL_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "device ordinal %d out of range", ctx->device);
+    float* partial = g_static_reduce_addr[ctx->device];
+    if (!partial) {
+        // one-time set-up for this device: make it current, then ask where the array lives on it
+        MTL_CUDA(ctx, cudaSetDevice(ctx->device));
+        void* p = nullptr;
+        MTL_CUDA(ctx, cudaGetSymbolAddress(&p, g_static_reduce_partials));
+        partial = g_static_reduce_addr[ctx->device] = (float*)p;
+    }
+    int blocks = mtl_grid_for((n + 3) / 4, kBlock, ctx->sm_count, 4);
+    if (blocks > MTL_STATIC_REDUCE_BLOCKS) blocks = MTL_STATIC_REDUCE_BLOCKS;
+    // every partial[0..blocks) is written by the first pass before the second reads it, so nothing
+    // left over from an earlier call has to be cleared
+    if (op == MTL_OP_MAX) {
+        k_reduce_partial<R_MAX><<<blocks, kBlock, 0, ctx->stream>>>(partial, in, n, nullptr);
+        MTL_LAUNCHED(ctx);
+        k_reduce_final<R_MAX><<<1, kBlock, 0, ctx->stream>>>(out, partial, blocks, 1.0f, 0);
+    } else {
+        k_reduce_partial<R_SUM><<<blocks, kBlock, 0, ctx->stream>>>(partial, in, n, nullptr);
+        MTL_LAUNCHED(ctx);
+        k_reduce_final<R_SUM><<<1, kBlock, 0, ctx->stream>>>(out, partial, blocks, (float)n, op == MTL_OP_MEAN);
+    }
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
 }  // extern "C"
