@@ -118,5 +118,9 @@ int32_t mtl_gemm_simt(mtl_ctx* ctx, float* C, const float* A, const float* B, in
 // Returns MTL_ERR_UNSUPPORTED when the shape cannot run on the tensor-core kernel.
 int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int64_t M,
                     int64_t N, int64_t K, int transA, int transB, int accumulate, int x3);
+// Thin products (N <= 16) bound by reading A; re-associates the k sum.
+bool mtl_gemm_thin_supported(int64_t M, int64_t N, int64_t K, int transA, int transB);
+int32_t mtl_gemm_thin(mtl_ctx* ctx, float* C, const float* A, const float* B, int64_t M, int64_t N, int64_t K,
+                      int transA, int accumulate);
 bool mtl_gemm_tc_supported(int64_t M, int64_t N, int64_t K, int transA, int transB,
                            const float* A, const float* B, const float* C);

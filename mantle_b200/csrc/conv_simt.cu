@@ -53,6 +53,62 @@ __global__ void __launch_bounds__(kBlock) k_conv_fwd(float* __restrict__ Y, cons
     }
 }
 
+// Forward for thin inputs (C*R*S <= 75, e.g. one input channel with a 5x5 kernel): one thread per
+// output pixel keeps its input patch in registers and produces every output channel, reading the
+// weights as 128-bit broadcasts from shared memory; stores of one channel are coalesced across the
+// warp.  Bound by writing Y.
+template <int R, int S, int C>
+__global__ void __launch_bounds__(kBlock) k_conv_fwd_patch(float* __restrict__ Y, const float* __restrict__ X,
+                                                           const float* __restrict__ Wt,
+                                                           const float* __restrict__ bias, ConvGeom g, int64_t n_pix) {
+    constexpr int CRS = C * R * S;
+    constexpr int CRS4 = (CRS + 3) / 4 * 4;
+    extern __shared__ float w_s[];  // [K][CRS4] zero padded, then bias[K]
+    float* b_s = w_s + g.K * CRS4;
+    for (int i = threadIdx.x; i < g.K * CRS4; i += blockDim.x) {
+        int k = i / CRS4, j = i - k * CRS4;
+        w_s[i] = j < CRS ? Wt[k * CRS + j] : 0.0f;
+    }
+    for (int i = threadIdx.x; i < g.K; i += blockDim.x) b_s[i] = bias ? bias[i] : 0.0f;
+    __syncthreads();
+    const int plane = g.OH * g.OW;
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t p = tid; p < n_pix; p += stride) {
+        int n = (int)(p / plane);
+        int rem = (int)(p - (int64_t)n * plane);
+        int oh = rem / g.OW, ow = rem - oh * g.OW;
+        int ih0 = oh * g.sh - g.ph, iw0 = ow * g.sw - g.pw;
+        float patch[CRS4];
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int s2 = 0; s2 < S; ++s2) {
+                    int ih = ih0 + r * g.dh, iw = iw0 + s2 * g.dw;
+                    bool ok = ih >= 0 && ih < g.H && iw >= 0 && iw < g.W;
+                    patch[(c * R + r) * S + s2] = ok ? __ldg(X + (((int64_t)n * C + c) * g.H + ih) * g.W + iw) : 0.0f;
+                }
+#pragma unroll
+        for (int j = CRS; j < CRS4; ++j) patch[j] = 0.0f;
+        float* yp = Y + (int64_t)n * g.K * plane + rem;
+        for (int k = 0; k < g.K; ++k) {
+            const float4* wk = reinterpret_cast<const float4*>(w_s + k * CRS4);
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < CRS4 / 4; ++j) {
+                float4 w = wk[j];
+                acc = fmaf(patch[4 * j], w.x, acc);
+                acc = fmaf(patch[4 * j + 1], w.y, acc);
+                acc = fmaf(patch[4 * j + 2], w.z, acc);
+                acc = fmaf(patch[4 * j + 3], w.w, acc);
+            }
+            yp[(int64_t)k * plane] = acc + b_s[k];
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kBlock) k_conv_dgrad(float* __restrict__ dX, const float* __restrict__ ug,
                                                        const float* __restrict__ Wt, ConvGeom g, int64_t n_in,
                                                        int accumulate) {
@@ -141,6 +197,73 @@ __global__ void __launch_bounds__(kBlock) k_conv_wgrad_taps(float* __restrict__ 
     }
 }
 
+// Kernel gradient with the input plane staged in shared memory (zero halo included, so taps need
+// no bounds checks) and KB output channels per block: per pixel R*S shared loads feed KB*R*S FMAs,
+// and every element of ug is read exactly once.  grid = ((K/KB)*C, nsplit); partial[split][kc][tap].
+template <int R, int S, int KB>
+__global__ void __launch_bounds__(kBlock) k_conv_wgrad_staged(float* __restrict__ partial,
+                                                              const float* __restrict__ ug,
+                                                              const float* __restrict__ X, ConvGeom g,
+                                                              int n_per_split, int PH, int PW) {
+    extern __shared__ float x_s[];                 // [PH][PW] padded plane
+    __shared__ float red[kBlock / 32][KB * R * S];
+    const int kgroups = (g.K + KB - 1) / KB;
+    const int kg = blockIdx.x % kgroups, c = blockIdx.x / kgroups;
+    const int k0 = kg * KB;
+    const int n_begin = blockIdx.y * n_per_split;
+    const int n_end = min(g.N, n_begin + n_per_split);
+    const int plane = g.OH * g.OW;
+    float acc[KB][R * S];
+#pragma unroll
+    for (int a = 0; a < KB; ++a)
+#pragma unroll
+        for (int t = 0; t < R * S; ++t) acc[a][t] = 0.0f;
+    for (int n = n_begin; n < n_end; ++n) {
+        const float* xc = X + ((int64_t)n * g.C + c) * g.H * g.W;
+        __syncthreads();
+        for (int i = threadIdx.x; i < PH * PW; i += kBlock) {
+            int ih = i / PW - g.ph, iw = i % PW - g.pw;
+            x_s[i] = (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? __ldg(xc + ih * g.W + iw) : 0.0f;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < plane; e += kBlock) {
+            int oh = e / g.OW, ow = e - oh * g.OW;
+            float u[KB];
+#pragma unroll
+            for (int a = 0; a < KB; ++a)
+                u[a] = (k0 + a < g.K) ? __ldg(ug + ((int64_t)n * g.K + k0 + a) * plane + e) : 0.0f;
+            const float* xp = x_s + (oh * g.sh) * PW + ow * g.sw;
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int s2 = 0; s2 < S; ++s2) {
+                    float x = xp[r * g.dh * PW + s2 * g.dw];
+#pragma unroll
+                    for (int a = 0; a < KB; ++a) acc[a][r * S + s2] = fmaf(x, u[a], acc[a][r * S + s2]);
+                }
+        }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int a = 0; a < KB; ++a)
+#pragma unroll
+        for (int t = 0; t < R * S; ++t) {
+            float v = acc[a][t];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) red[warp][a * R * S + t] = v;
+        }
+    __syncthreads();
+    for (int i = threadIdx.x; i < KB * R * S; i += kBlock) {
+        int a = i / (R * S), t = i - a * (R * S);
+        if (k0 + a >= g.K) continue;
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kBlock / 32; ++w) v += red[w][i];
+        partial[((int64_t)blockIdx.y * g.K * g.C + (int64_t)(k0 + a) * g.C + c) * (R * S) + t] = v;
+    }
+}
+
 // Any kernel size: one tap at a time.
 __global__ void __launch_bounds__(kBlock) k_conv_wgrad_generic(float* __restrict__ partial, const float* __restrict__ ug,
                                                                const float* __restrict__ X, ConvGeom g,
@@ -179,15 +302,19 @@ __global__ void __launch_bounds__(kBlock) k_conv_bgrad(float* __restrict__ parti
     const int n_end = min(N, n_begin + n_per_split);
     float acc = 0.0f;
     const bool vec = (plane % 4 == 0) && ((reinterpret_cast<uintptr_t>(ug) & 15u) == 0);
-    for (int n = n_begin; n < n_end; ++n) {
-        const float* p = ug + ((int64_t)n * K + k) * plane;
-        if (vec) {
-            const float4* p4 = reinterpret_cast<const float4*>(p);
-            for (int i = threadIdx.x; i < plane / 4; i += kBlock) {
-                float4 v = __ldg(p4 + i);
-                acc += (v.x + v.y) + (v.z + v.w);
-            }
-        } else {
+    if (vec) {
+        // one flat index over (image, float4) keeps every thread busy with independent loads
+        const int p4n = plane / 4;
+        const int total = (n_end - n_begin) * p4n;
+#pragma unroll 4
+        for (int i = threadIdx.x; i < total; i += kBlock) {
+            int n = n_begin + i / p4n, j = i - (i / p4n) * p4n;
+            float4 v = __ldg(reinterpret_cast<const float4*>(ug + ((int64_t)n * K + k) * plane) + j);
+            acc += (v.x + v.y) + (v.z + v.w);
+        }
+    } else {
+        for (int n = n_begin; n < n_end; ++n) {
+            const float* p = ug + ((int64_t)n * K + k) * plane;
             for (int i = threadIdx.x; i < plane; i += kBlock) acc += __ldg(p + i);
         }
     }
@@ -216,8 +343,25 @@ int32_t mtl_sum_partials(mtl_ctx* ctx, float* out, const float* partial, int64_t
     return MTL_OK;
 }
 
+template <int R, int S, int C>
+static int32_t launch_fwd_patch(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
+                                const ConvGeom& g) {
+    constexpr int CRS4 = (C * R * S + 3) / 4 * 4;
+    int64_t n_pix = (int64_t)g.N * g.OH * g.OW;
+    size_t smem = ((size_t)g.K * CRS4 + g.K) * 4;
+    int grid = mtl_grid_for(n_pix, kBlock, ctx->sm_count, 4);
+    k_conv_fwd_patch<R, S, C><<<grid, kBlock, smem, ctx->stream>>>(Y, X, Wt, bias, g, n_pix);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
 int32_t mtl_conv_fwd_simt(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
                           const ConvGeom& g) {
+    if ((size_t)g.K * (g.C * g.R * g.S + 4) * 4 <= 40 * 1024 && (int64_t)g.N * g.OH * g.OW >= 4096) {
+        if (g.R == 5 && g.S == 5 && g.C == 1) return launch_fwd_patch<5, 5, 1>(ctx, Y, X, Wt, bias, g);
+        if (g.R == 3 && g.S == 3 && g.C == 1) return launch_fwd_patch<3, 3, 1>(ctx, Y, X, Wt, bias, g);
+        if (g.R == 3 && g.S == 3 && g.C == 3) return launch_fwd_patch<3, 3, 3>(ctx, Y, X, Wt, bias, g);
+    }
     int64_t n_out = (int64_t)g.N * g.K * g.OH * g.OW;
     size_t wbytes = (size_t)g.K * g.C * g.R * g.S * 4;
     int w_in_smem = wbytes <= 40 * 1024;
@@ -256,8 +400,29 @@ int32_t mtl_conv_wgrad_simt(mtl_ctx* ctx, float* dW, const float* ug, const floa
     int32_t rc = mtl_workspace(ctx, (size_t)nsplit * kc * taps * 4, &ws);
     if (rc) return rc;
     float* partial = (float*)ws;
-    dim3 grid((unsigned)kc, (unsigned)nsplit);
     MTL_REQUIRE(ctx, nsplit <= 65535, "too many batch splits");
+    // staged variant: padded input plane in shared memory, 4 output channels per block
+    const int PH = (g.OH - 1) * g.sh + (g.R - 1) * g.dh + 1 + 0, PW = (g.OW - 1) * g.sw + (g.S - 1) * g.dw + 1;
+    const bool staged_ok = (size_t)PH * PW * 4 <= 40 * 1024 && ((g.R == 5 && g.S == 5) || (g.R == 3 && g.S == 3)) &&
+                           g.OH * g.OW >= 64;
+    if (staged_ok) {
+        constexpr int KB = 4;
+        const int kgroups = (g.K + KB - 1) / KB;
+        int ns = pick_nsplit(ctx, kgroups * g.C, g.N);
+        int nps = (g.N + ns - 1) / ns;
+        ns = (g.N + nps - 1) / nps;
+        void* ws2;
+        int32_t rc2 = mtl_workspace(ctx, (size_t)ns * kc * taps * 4, &ws2);
+        if (rc2) return rc2;
+        float* part = (float*)ws2;
+        dim3 sgrid((unsigned)(kgroups * g.C), (unsigned)ns);
+        size_t smem = (size_t)PH * PW * 4;
+        if (g.R == 5) k_conv_wgrad_staged<5, 5, KB><<<sgrid, kBlock, smem, ctx->stream>>>(part, ug, X, g, nps, PH, PW);
+        else k_conv_wgrad_staged<3, 3, KB><<<sgrid, kBlock, smem, ctx->stream>>>(part, ug, X, g, nps, PH, PW);
+        MTL_LAUNCHED(ctx);
+        return mtl_sum_partials(ctx, dW, part, (int64_t)kc * taps, ns, accumulate);
+    }
+    dim3 grid((unsigned)kc, (unsigned)nsplit);
     if (g.R == 5 && g.S == 5) k_conv_wgrad_taps<5, 5><<<grid, kBlock, 0, ctx->stream>>>(partial, ug, X, g, n_per_split);
     else if (g.R == 3 && g.S == 3) k_conv_wgrad_taps<3, 3><<<grid, kBlock, 0, ctx->stream>>>(partial, ug, X, g, n_per_split);
     else if (g.R == 1 && g.S == 1) k_conv_wgrad_taps<1, 1><<<grid, kBlock, 0, ctx->stream>>>(partial, ug, X, g, n_per_split);

@@ -74,7 +74,125 @@ k_gemm_simt(float* __restrict__ C, const float* __restrict__ A, const float* __r
     }
 }
 
+// ---- thin products (N <= 16), e.g. the classifier of the CNNs: [B, 6272] . [6272, 10] -------------
+// These are bound by reading A once.  They re-associate the k sum (lane / split partials), so they
+// are used only outside MTL_MATH_FP32; results differ from the ascending chain by fp32 rounding.
+
+// C[M,N] = A[M,K] . B[K,N], A row-major: one warp per ROWS rows, lanes stride over k.
+template <int ROWS>
+__global__ void __launch_bounds__(128) k_gemm_thin_n(float* __restrict__ C, const float* __restrict__ A,
+                                                     const float* __restrict__ B, int M, int N, int K,
+                                                     int accumulate) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const int m0 = warp * ROWS;
+    if (m0 >= M) return;
+    float acc[ROWS][16];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[r][j] = 0.0f;
+    for (int k = lane; k < K; k += 32) {
+        float b[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) b[j] = j < N ? __ldg(B + (int64_t)k * N + j) : 0.0f;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            float a = (m0 + r < M) ? __ldg(A + (int64_t)(m0 + r) * K + k) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[r][j] = fmaf(a, b[j], acc[r][j]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            float v = acc[r][j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && j < N && m0 + r < M) {
+                int64_t idx = (int64_t)(m0 + r) * N + j;
+                C[idx] = accumulate ? C[idx] + v : v;
+            }
+        }
+}
+
+// partial[split][M,N] = A^T . B over a slice of k, A stored [K, M] (m contiguous): one thread per
+// output row, rows of B staged in shared memory.
+__global__ void __launch_bounds__(256) k_gemm_thin_n_ta(float* __restrict__ partial, const float* __restrict__ A,
+                                                        const float* __restrict__ B, int M, int N, int K,
+                                                        int k_per_split) {
+    __shared__ float b_s[64][16];
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    const int k_begin = blockIdx.y * k_per_split;
+    const int k_end = min(K, k_begin + k_per_split);
+    float acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+    for (int k0 = k_begin; k0 < k_end; k0 += 64) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < 64 * 16; i += blockDim.x) {
+            int kk = i >> 4, j = i & 15;
+            b_s[kk][j] = (k0 + kk < k_end && j < N) ? __ldg(B + (int64_t)(k0 + kk) * N + j) : 0.0f;
+        }
+        __syncthreads();
+        if (m < M) {
+            const int kn = min(64, k_end - k0);
+            for (int kk = 0; kk < kn; ++kk) {
+                float a = __ldg(A + (int64_t)(k0 + kk) * M + m);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j] = fmaf(a, b_s[kk][j], acc[j]);
+            }
+        }
+    }
+    if (m < M) {
+        float* out = partial + ((int64_t)blockIdx.y * M + m) * N;
+        for (int j = 0; j < N; ++j) out[j] = acc[j];
+    }
+}
+
+__global__ void __launch_bounds__(256) k_fold_partials(float* __restrict__ out, const float* __restrict__ partial,
+                                                       int64_t n, int nsplit, int accumulate) {
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = tid; i < n; i += stride) {
+        float s = 0.0f;
+        for (int j = 0; j < nsplit; ++j) s += partial[(int64_t)j * n + i];
+        out[i] = accumulate ? out[i] + s : s;
+    }
+}
+
 }  // namespace
+
+bool mtl_gemm_thin_supported(int64_t M, int64_t N, int64_t K, int transA, int transB) {
+    return N <= 16 && !transB && M * K >= (1 << 16) && M < (1ll << 31) && K < (1ll << 31);
+}
+
+int32_t mtl_gemm_thin(mtl_ctx* ctx, float* C, const float* A, const float* B, int64_t M, int64_t N, int64_t K,
+                      int transA, int accumulate) {
+    if (!transA) {
+        constexpr int ROWS = 4;
+        int64_t warps = (M + ROWS - 1) / ROWS;
+        int grid = (int)((warps * 32 + 127) / 128);
+        k_gemm_thin_n<ROWS><<<grid, 128, 0, ctx->stream>>>(C, A, B, (int)M, (int)N, (int)K, accumulate);
+        MTL_LAUNCHED(ctx);
+        return MTL_OK;
+    }
+    int gx = (int)((M + 255) / 256);
+    int nsplit = (ctx->sm_count * 4 + gx - 1) / gx;
+    int64_t kps = (K + nsplit - 1) / nsplit;
+    kps = (kps + 63) / 64 * 64;
+    nsplit = (int)((K + kps - 1) / kps);
+    void* ws;
+    int32_t rc = mtl_workspace(ctx, (size_t)nsplit * M * N * 4, &ws);
+    if (rc) return rc;
+    dim3 grid((unsigned)gx, (unsigned)nsplit);
+    k_gemm_thin_n_ta<<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
+    MTL_LAUNCHED(ctx);
+    int fg = mtl_grid_for(M * N, 256, ctx->sm_count, 8);
+    k_fold_partials<<<fg, 256, 0, ctx->stream>>>(C, (const float*)ws, M * N, nsplit, accumulate);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
 
 int32_t mtl_gemm_simt(mtl_ctx* ctx, float* C, const float* A, const float* B, int64_t M, int64_t N, int64_t K,
                       int transA, int transB, int accumulate) {

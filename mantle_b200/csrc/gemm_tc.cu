@@ -396,6 +396,8 @@ int32_t mtl_dot_fwd(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
     MTL_REQUIRE(ctx, M >= 1 && K >= 1 && N >= 1, "DOT extents must be positive");
     if (ctx->math_mode != MTL_MATH_FP32 && mtl_gemm_tc_supported(M, N, K, 0, 0, A, B, C))
         return mtl_gemm_tc(ctx, C, A, B, M, N, K, 0, 0, 0, ctx->math_mode == MTL_MATH_TF32X3);
+    if (ctx->math_mode != MTL_MATH_FP32 && mtl_gemm_thin_supported(M, N, K, 0, 0))
+        return mtl_gemm_thin(ctx, C, A, B, M, N, K, 0, 0);
     return mtl_gemm_simt(ctx, C, A, B, M, N, K, 0, 0, 0);
 }
 
@@ -418,6 +420,7 @@ int32_t mtl_dot_bwd(mtl_ctx* ctx, int32_t tensor_id, float* grad, const float* u
     MTL_REQUIRE(ctx, A, "dB needs A");
     if (tc && mtl_gemm_tc_supported(K, N, M, 1, 0, A, ug, grad))
         return mtl_gemm_tc(ctx, grad, A, ug, K, N, M, 1, 0, accumulate, x3);
+    if (tc && mtl_gemm_thin_supported(K, N, M, 1, 0)) return mtl_gemm_thin(ctx, grad, A, ug, K, N, M, 1, accumulate);
     return mtl_gemm_simt(ctx, grad, A, ug, K, N, M, 1, 0, accumulate);
 }
 
