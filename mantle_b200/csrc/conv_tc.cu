@@ -489,14 +489,13 @@ k_conv_wgrad_tc(const __grid_constant__ CUtensorMap mapU0, const __grid_constant
                 uint8_t* sa = tiles + stage * p.stage_bytes;
                 uint8_t* sb = sa + a_bytes;
                 mbar_arrive_expect_tx(&full[stage], tx_bytes);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) tma_load_4d(sa + j * 4096, mu, &full[stage], kt * BM + j * 32, ow0, oh0, n0);
+                // one 5-D box per operand tile: {32 channels, bw, bh, bn pixels, channel chunks}; TMA
+                // instructions are costly to issue, so fewer and larger ones keep the ring full
+                tma_load_5d(sa, mu, &full[stage], 0, ow0, oh0, n0, kt * (BM / 32));
                 for (int t = 0; t < ntaps; ++t) {
                     const int rs = tap0 + t;
                     const int r = rs / p.S, s = rs - r * p.S;
-                    for (int jc = 0; jc < cchunks; ++jc)
-                        tma_load_4d(sb + (t * cchunks + jc) * 4096, mx, &full[stage], jc * 32, ow0 + s - p.pw,
-                                    oh0 + r - p.ph, n0);
+                    tma_load_5d(sb + t * cchunks * 4096, mx, &full[stage], 0, ow0 + s - p.pw, oh0 + r - p.ph, n0, 0);
                 }
                 if (++stage == p.stages) { stage = 0; phase ^= 1u; }
             }
@@ -644,7 +643,7 @@ int32_t mtl_conv_dgrad_tc(mtl_ctx* ctx, float* dX, const float* ug, const float*
 
 bool mtl_conv_wgrad_tc_supported(const ConvGeom& g, const float* ug, const float* X, const float* dW) {
     if (!igemm_geometry_ok(g)) return false;
-    if (g.C < 32 || (g.C % 32) || g.C > 256 || g.K < 32 || (g.K % 4)) return false;
+    if (g.C < 32 || (g.C % 32) || g.C > 256 || g.K < 32 || (g.K % 32)) return false;
     if ((int64_t)g.N * g.OH * g.OW < 4096) return false;  // too little reduction work to split
     if ((((uintptr_t)ug) | ((uintptr_t)X) | ((uintptr_t)dW)) & 15u) return false;
     return true;
@@ -717,14 +716,16 @@ int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float*
     for (int i = 0; i < 2; ++i) {
         const float* u = (i == 1 && x3) ? u_lo : u_hi;
         const float* x = (i == 1 && x3) ? x_lo : x_hi;
-        uint32_t box[4] = {32, (uint32_t)p.bw, (uint32_t)p.bh, (uint32_t)p.bn};
-        uint64_t udims[4] = {(uint64_t)g.K, (uint64_t)g.OW, (uint64_t)g.OH, (uint64_t)g.N};
-        uint64_t ustr[3] = {(uint64_t)g.K * 4, (uint64_t)g.OW * g.K * 4, (uint64_t)g.OH * g.OW * g.K * 4};
-        rc = mtl_encode_tmap(ctx, &maps[i], u, 4, udims, ustr, box, true);
+        // channels-last [N, H, W, Ch] viewed as {32, W, H, N, Ch/32}: the last axis steps 128 bytes
+        uint32_t ubox[5] = {32, (uint32_t)p.bw, (uint32_t)p.bh, (uint32_t)p.bn, (uint32_t)(BM / 32)};
+        uint64_t udims[5] = {32, (uint64_t)g.OW, (uint64_t)g.OH, (uint64_t)g.N, (uint64_t)(g.K / 32)};
+        uint64_t ustr[4] = {(uint64_t)g.K * 4, (uint64_t)g.OW * g.K * 4, (uint64_t)g.OH * g.OW * g.K * 4, 128};
+        rc = mtl_encode_tmap(ctx, &maps[i], u, 5, udims, ustr, ubox, true);
         if (rc) return rc;
-        uint64_t xdims[4] = {(uint64_t)g.C, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.N};
-        uint64_t xstr[3] = {(uint64_t)g.C * 4, (uint64_t)g.W * g.C * 4, (uint64_t)g.H * g.W * g.C * 4};
-        rc = mtl_encode_tmap(ctx, &maps[2 + i], x, 4, xdims, xstr, box, true);
+        uint32_t xbox[5] = {32, (uint32_t)p.bw, (uint32_t)p.bh, (uint32_t)p.bn, (uint32_t)(g.C / 32)};
+        uint64_t xdims[5] = {32, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.N, (uint64_t)(g.C / 32)};
+        uint64_t xstr[4] = {(uint64_t)g.C * 4, (uint64_t)g.W * g.C * 4, (uint64_t)g.H * g.W * g.C * 4, 128};
+        rc = mtl_encode_tmap(ctx, &maps[2 + i], x, 5, xdims, xstr, xbox, true);
         if (rc) return rc;
     }
     const int smem_bytes = p.stages * p.stage_bytes + 1024 + 256;

@@ -39,6 +39,9 @@ struct GemmParams {
     float* C;
     int accumulate;
     int32_t* status;
+    int a3d, b3d;     // MN-major operand fetched as one 3-D box {32, BK, chunks} instead of one box per chunk
+    int stages;       // ring depth actually used (<= the configuration's maximum)
+    int skip_store;   // tuning aid: run the epilogue without writing C
 };
 
 // Tile order: groups of 16 tile-rows; inside a group the tile-column changes slowest so that
@@ -80,7 +83,7 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
     const int kb_total = kb_per_seg * p.nseg;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::kStages; ++s) {
+        for (int s = 0; s < p.stages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -127,18 +130,28 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                     mbar_arrive_expect_tx(&full[stage], C::kStageBytes);
                     if (A_MN) {
                         // A stored [K, M]: chunks of 32 m x 32 k, 4 KB each
+                        if (p.a3d) {
+                            tma_load_3d(sa, ma, &full[stage], 0, k0, m0 / 32);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < BM / 32; ++c) tma_load_2d(sa + c * 4096, ma, &full[stage], m0 + c * 32, k0);
+                            for (int c = 0; c < BM / 32; ++c)
+                                tma_load_2d(sa + c * 4096, ma, &full[stage], m0 + c * 32, k0);
+                        }
                     } else {
                         tma_load_2d(sa, ma, &full[stage], k0, m0);
                     }
                     if (B_MN) {
+                        if (p.b3d) {
+                            tma_load_3d(sb, mb, &full[stage], 0, k0, n0 / 32);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < BN / 32; ++c) tma_load_2d(sb + c * 4096, mb, &full[stage], n0 + c * 32, k0);
+                            for (int c = 0; c < BN / 32; ++c)
+                                tma_load_2d(sb + c * 4096, mb, &full[stage], n0 + c * 32, k0);
+                        }
                     } else {
                         tma_load_2d(sb, mb, &full[stage], k0, n0);
                     }
-                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                 }
             }
             if (!ok) atomicExch(p.status, MTL_ERR_TIMEOUT);
@@ -169,7 +182,7 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                         mma_tf32(tmem_d, da, db, idesc, (kb | kk) ? 1u : 0u);
                     }
                     mma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
-                    if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) mma_commit(&tmem_full[acc]);
             }
@@ -197,7 +210,7 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
                 tmem_ld_wait();
                 const int n0 = n_base + c * 32;
-                if (m < p.M) {
+                if (m < p.M && !p.skip_store) {
                     if (vec_ok) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
@@ -331,7 +344,8 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
                     int transA, int transB, int accumulate, int x3) {
     if (!mtl_gemm_tc_supported(M, N, K, transA, transB, A, B, C))
         return mtl_set_error(ctx, MTL_ERR_UNSUPPORTED, "shape not supported by the tensor-core DOT kernel");
-    const int BN = N >= 256 ? 256 : 128;
+    int BN = N >= 256 ? 256 : 128;
+    if (const char* e = getenv("MANTLE_GEMM_BN")) { int b = atoi(e); if (b == 128 || (b == 256 && N >= 256)) BN = b; }
     const float* a_src[2] = {A, nullptr};
     const float* b_src[2] = {B, nullptr};
     if (x3) {
@@ -351,21 +365,30 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
         a_src[0] = ahi; a_src[1] = alo;
         b_src[0] = bhi; b_src[1] = blo;
     }
+    // An MN-major operand stored [K, MN] can be fetched with ONE 3-D box per stage when MN is a
+    // multiple of 32: dims {32, K, MN/32} with strides {row, 128 B}, box {32, BK, chunks}; its
+    // shared-memory image [chunk][k][32] is exactly the chunked layout the descriptors expect.
+    const bool no3d = getenv("MANTLE_GEMM_NO3D") != nullptr;
+    const int a3d = transA && (M % 32 == 0) && !no3d, b3d = !transB && (N % 32 == 0) && !no3d;
     CUtensorMap maps[4];
     for (int i = 0; i < 2; ++i) {
         const float* a = a_src[i] ? a_src[i] : a_src[0];
         const float* b = b_src[i] ? b_src[i] : b_src[0];
-        uint64_t dims[2], strides[1];
-        uint32_t box[2];
-        if (transA) { dims[0] = (uint64_t)M; dims[1] = (uint64_t)K; box[0] = 32; box[1] = BK; }
-        else        { dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = BK; box[1] = BM; }
-        strides[0] = dims[0] * 4;
-        int32_t rc = mtl_encode_tmap(ctx, &maps[i], a, 2, dims, strides, box, transA != 0);
+        uint64_t dims[3], strides[2];
+        uint32_t box[3];
+        int rank = 2;
+        if (a3d) { dims[0] = 32; dims[1] = (uint64_t)K; dims[2] = (uint64_t)(M / 32); strides[0] = (uint64_t)M * 4; strides[1] = 128;
+                   box[0] = 32; box[1] = BK; box[2] = BM / 32; rank = 3; }
+        else if (transA) { dims[0] = (uint64_t)M; dims[1] = (uint64_t)K; box[0] = 32; box[1] = BK; strides[0] = dims[0] * 4; }
+        else             { dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = BK; box[1] = BM; strides[0] = dims[0] * 4; }
+        int32_t rc = mtl_encode_tmap(ctx, &maps[i], a, rank, dims, strides, box, transA != 0);
         if (rc) return rc;
-        if (transB) { dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = BK; box[1] = (uint32_t)BN; }
-        else        { dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 32; box[1] = BK; }
-        strides[0] = dims[0] * 4;
-        rc = mtl_encode_tmap(ctx, &maps[2 + i], b, 2, dims, strides, box, transB == 0);
+        rank = 2;
+        if (b3d) { dims[0] = 32; dims[1] = (uint64_t)K; dims[2] = (uint64_t)(N / 32); strides[0] = (uint64_t)N * 4; strides[1] = 128;
+                   box[0] = 32; box[1] = BK; box[2] = (uint32_t)(BN / 32); rank = 3; }
+        else if (transB) { dims[0] = (uint64_t)K; dims[1] = (uint64_t)N; box[0] = BK; box[1] = (uint32_t)BN; strides[0] = dims[0] * 4; }
+        else             { dims[0] = (uint64_t)N; dims[1] = (uint64_t)K; box[0] = 32; box[1] = BK; strides[0] = dims[0] * 4; }
+        rc = mtl_encode_tmap(ctx, &maps[2 + i], b, rank, dims, strides, box, transB == 0);
         if (rc) return rc;
     }
     GemmParams p;
@@ -377,6 +400,12 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
     p.C = C;
     p.accumulate = accumulate ? 1 : 0;
     p.status = ctx->dev_status;
+    p.stages = BN == 256 ? 4 : 6;
+    p.a3d = a3d;
+    p.b3d = b3d;
+    p.skip_store = 0;
+    if (const char* e = getenv("MANTLE_GEMM_STAGES")) { int s = atoi(e); if (s >= 1 && s <= p.stages) p.stages = s; }
+    if (const char* e = getenv("MANTLE_GEMM_SKIP_STORE")) p.skip_store = atoi(e) != 0;
     const bool a_mn = transA != 0, b_mn = transB == 0;
 #define MTL_DISPATCH(BN_)                                                                     \
     if (a_mn && b_mn) return launch_gemm<BN_, true, true>(ctx, maps, p);                     \
