@@ -192,6 +192,10 @@ def run_ours(args):
             raise SystemExit("launch with torch.distributed.run --nproc-per-node %d for --gpus %d" % (args.gpus, args.gpus))
     dist = None
     if world > 1:
+        # the collective library's banner and debug lines must not reach stdout: rank 0 prints
+        # exactly one JSON line there
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE"):
+            os.environ["NCCL_DEBUG_FILE"] = os.environ.get("NCCL_DEBUG_FILE", "/dev/stderr")
         import torch.distributed as dist
         dist.init_process_group("gloo", rank=rank, world_size=world)  # control plane only
 
