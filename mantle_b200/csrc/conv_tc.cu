@@ -315,6 +315,268 @@ struct IgemmCall {
     int accumulate;
 };
 
+// ------------------------------------------------------------------ channel-major variant -----
+// Measured on B200: one tcgen05.mma kind::tf32 with M = 128 costs about 71 ns + 0.164 ns * N, i.e.
+// fetching the A operand is a large fixed cost and the instruction only reaches the tensor peak
+// near N = 256.  Output channels (64..128 per layer here) therefore go on the M axis and the
+// PIXELS on the N axis: A = one weight tile {128 out-ch x 32 in-ch}, B = up to 256 pixels x 32
+// in-ch fetched by one TMA box {32, bw, bh, bn}.  Accumulator D[out-ch, pixel]: a thread of the
+// epilogue owns one output channel and walks the tile's pixels, which are contiguous in NCHW.
+constexpr int kTStages = 4;
+constexpr int kTABytes = BM * BK * 4;        // weights tile
+constexpr int kTBBytes = 256 * BK * 4;       // pixel tile (maximum)
+constexpr int kTStageBytes = kTABytes + kTBBytes;
+constexpr int kTSmemBytes = kTStages * kTStageBytes + 1024 + 256 + 256 * 4 + 64 * 4 + 4 * 32 * 36 * 4;
+
+struct ConvTParams {
+    int N, OH, OW, Kout, Cin;
+    int R, S, ph, pw;
+    int bw, bh, bn, npix;   // pixel box, npix = bw*bh*bn <= 256
+    int n_mma;              // npix rounded up to a multiple of 16: the N extent of the instruction
+    int tiles_w, tiles_h, tiles_nb, tiles_k;
+    int nseg, segA[3], segB[3];
+    float* out;
+    const float* bias;
+    int accumulate;
+    int vec_ok;             // channel planes are 16-byte aligned: four adjacent pixels may leave as a float4
+    int32_t* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant__ CUtensorMap mapX1,
+               const __grid_constant__ CUtensorMap mapW0, const __grid_constant__ CUtensorMap mapW1, ConvTParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kTStages * kTStageBytes);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kTStages;
+    uint64_t* tmem_full = bars + 2 * kTStages;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* col_off = reinterpret_cast<int*>(smem + kTStages * kTStageBytes + 256);
+    int* col_vec = col_off + 256;
+    float* stage_buf = reinterpret_cast<float*>(col_vec + 64);  // 4 warps x 32 x 36 floats
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles_m = p.tiles_w * p.tiles_h * p.tiles_nb;
+    const int num_tiles = tiles_m * p.tiles_k;
+    const int cblocks = (p.Cin + BK - 1) / BK;
+    const int kb_per_seg = p.R * p.S * cblocks;
+    const int kb_total = kb_per_seg * p.nseg;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 128); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&mapX0);
+        prefetch_tensormap(&mapW0);
+        if (p.nseg > 1) { prefetch_tensormap(&mapX1); prefetch_tensormap(&mapW1); }
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            const uint32_t tx = (uint32_t)kTABytes + (uint32_t)p.npix * 128u;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int kt = t % p.tiles_k;
+                int mt = t / p.tiles_k;
+                const int tw = mt % p.tiles_w;
+                mt /= p.tiles_w;
+                const int th = mt % p.tiles_h;
+                const int tnb = mt / p.tiles_h;
+                const int ow0 = tw * p.bw, oh0 = th * p.bh, n0 = tnb * p.bn;
+                for (int seg = 0; seg < p.nseg && ok; ++seg) {
+                    const CUtensorMap* mx = p.segA[seg] ? &mapX1 : &mapX0;
+                    const CUtensorMap* mw = p.segB[seg] ? &mapW1 : &mapW0;
+                    for (int r = 0; r < p.R && ok; ++r)
+                        for (int s = 0; s < p.S && ok; ++s)
+                            for (int cb = 0; cb < cblocks; ++cb) {
+                                if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+                                uint8_t* sa = tiles + stage * kTStageBytes;
+                                uint8_t* sb = sa + kTABytes;
+                                mbar_arrive_expect_tx(&full[stage], tx);
+                                tma_load_3d(sa, mw, &full[stage], cb * BK, kt * BM, r * p.S + s);
+                                tma_load_4d(sb, mx, &full[stage], cb * BK, ow0 + s - p.pw, oh0 + r - p.ph, n0);
+                                if (++stage == kTStages) { stage = 0; phase ^= 1u; }
+                            }
+                }
+            }
+            if (!ok) atomicExch(p.status, MTL_ERR_TIMEOUT);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_tf32(p.n_mma, false, false);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int local = 0;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+                const int acc = local & 1;
+                const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * 256);
+                for (int kb = 0; kb < kb_total; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(tiles + stage * kTStageBytes);
+                    const uint32_t sb = sa + kTABytes;
+#pragma unroll
+                    for (int kk = 0; kk < BK / 8; ++kk)
+                        mma_tf32(tmem_d, desc_k_major(sa, kk), desc_k_major(sb, kk), idesc, (kb | kk) ? 1u : 0u);
+                    mma_commit(&empty[stage]);
+                    if (++stage == kTStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) mma_commit(&tmem_full[acc]);
+            }
+            if (!ok) atomicExch(p.status, MTL_ERR_TIMEOUT);
+        }
+    } else {
+        const int quad = warp & 3;
+        const int krow = quad * 32 + lane;  // output channel inside the tile
+        const int plane = p.OH * p.OW;
+        bool ok = true;
+        int local = 0;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+            const int kt = t % p.tiles_k;
+            int mt = t / p.tiles_k;
+            const int tw = mt % p.tiles_w;
+            mt /= p.tiles_w;
+            const int th = mt % p.tiles_h;
+            const int tnb = mt / p.tiles_h;
+            const int ow0 = tw * p.bw, oh0 = th * p.bh, n0 = tnb * p.bn;
+            const int k = kt * BM + krow;
+            const bool kvalid = k < p.Kout;
+            const float bv = (kvalid && p.bias) ? __ldg(p.bias + k) : 0.0f;
+            const int acc = local & 1;
+            const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+            if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+            tc_fence_after_sync();
+            // Column j of the accumulator is pixel (j % bw, (j / bw) % bh, j / (bw*bh)) of the box.
+            // The 128 epilogue threads first tabulate, per column, the offset of that pixel inside
+            // one channel plane set (-1 = outside the tensor) and, per group of four columns,
+            // whether the four are contiguous and 16-byte aligned; the store loop then costs a few
+            // instructions per column, which matters because only four warps drain 256 columns.
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            for (int j = (int)threadIdx.x - 64; j < 256; j += 128) {
+                int o = -1;
+                if (j < p.npix) {
+                    const int w_i = j % p.bw, h_i = (j / p.bw) % p.bh, n_i = j / (p.bw * p.bh);
+                    const int ow = ow0 + w_i, oh = oh0 + h_i, n = n0 + n_i;
+                    if (ow < p.OW && oh < p.OH && n < p.N) o = n * p.Kout * plane + oh * p.OW + ow;
+                }
+                col_off[j] = o;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if ((int)threadIdx.x - 64 < 64) {
+                const int g = (int)threadIdx.x - 64;
+                const int o0 = col_off[g * 4], o1 = col_off[g * 4 + 1], o2 = col_off[g * 4 + 2], o3 = col_off[g * 4 + 3];
+                col_vec[g] = (o0 >= 0 && o1 == o0 + 1 && o2 == o0 + 2 && o3 == o0 + 3 && (o0 & 3) == 0 && p.vec_ok) ? 1 : 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            // A thread of the accumulator owns one channel, but channels are a whole plane apart in
+            // NCHW: storing from that layout scatters every warp store over 32 lines (measured: the
+            // stores then take as long as the whole main loop).  Each warp therefore turns its
+            // 32 channels x 32 pixels block through shared memory so that eight lanes write 32
+            // adjacent pixels of one channel.
+            float* stg = stage_buf + (warp - 2) * (32 * 36);
+            const int sub = lane & 7, chl = lane >> 3;
+#pragma unroll 1
+            for (int c = 0; c * 32 < p.npix; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * 256 + c * 32), r);
+                tmem_ld_wait();
+                __syncwarp();
+#pragma unroll
+                for (int g = 0; g < 8; ++g)
+                    *reinterpret_cast<float4*>(stg + lane * 36 + g * 4) =
+                        make_float4(__uint_as_float(r[g * 4]) + bv, __uint_as_float(r[g * 4 + 1]) + bv,
+                                    __uint_as_float(r[g * 4 + 2]) + bv, __uint_as_float(r[g * 4 + 3]) + bv);
+                __syncwarp();
+                const int j0 = c * 32 + sub * 4;
+                const int vec = col_vec[j0 >> 2];
+                const int o0 = col_off[j0], o1 = col_off[j0 + 1], o2 = col_off[j0 + 2], o3 = col_off[j0 + 3];
+                {
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int ch = it * 4 + chl;
+                        const int kk = kt * BM + quad * 32 + ch;
+                        if (kk < p.Kout) {
+                            const float4 val = *reinterpret_cast<const float4*>(stg + ch * 36 + sub * 4);
+                            float* base = p.out + (int64_t)kk * plane;
+                            if (vec) {
+                                float4* dst = reinterpret_cast<float4*>(base + o0);
+                                float4 o = val;
+                                if (p.accumulate) {
+                                    float4 old = *dst;
+                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                }
+                                *dst = o;
+                            } else {
+                                if (o0 >= 0) base[o0] = p.accumulate ? base[o0] + val.x : val.x;
+                                if (o1 >= 0) base[o1] = p.accumulate ? base[o1] + val.y : val.y;
+                                if (o2 >= 0) base[o2] = p.accumulate ? base[o2] + val.z : val.z;
+                                if (o3 >= 0) base[o3] = p.accumulate ? base[o3] + val.w : val.w;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tmem_empty[acc]);
+        }
+        if (!ok && lane == 0) atomicExch(p.status, MTL_ERR_TIMEOUT);
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// Pixel box {bw, bh, bn} with at most `limit` pixels.  Among the boxes within 8 % of the best
+// column utilisation, take the one whose pixels form the longest contiguous run in an NCHW plane
+// (whole rows, then adjacent rows), because the epilogue stores runs; then the fuller one.
+void choose_box_n(int OW, int OH, int N, int limit, int* bw_, int* bh_, int* bn_) {
+    double best_eff = 0.0;
+    for (int pass = 0; pass < 2; ++pass) {
+        double best_score = -1.0;
+        for (int bw = 1; bw <= OW && bw <= limit; ++bw)
+            for (int bh = 1; bh <= OH && bw * bh <= limit; ++bh) {
+                int bn = limit / (bw * bh);
+                if (bn > N) bn = N;
+                if (bn > 256) bn = 256;
+                int64_t tiles = (int64_t)((OW + bw - 1) / bw) * ((OH + bh - 1) / bh) * ((N + bn - 1) / bn);
+                double eff = (double)OW * OH * N / ((double)tiles * limit);
+                if (pass == 0) {
+                    if (eff > best_eff) best_eff = eff;
+                    continue;
+                }
+                if (eff < 0.92 * best_eff) continue;
+                int run = (bw == OW) ? bw * bh : bw;
+                double score = run + eff;
+                if (score > best_score) { best_score = score; *bw_ = bw; *bh_ = bh; *bn_ = bn; }
+            }
+    }
+}
+
 template <int BN>
 int32_t launch_igemm(mtl_ctx* ctx, const CUtensorMap* maps, const ConvTcParams& p) {
     using C = Cfg<BN>;
@@ -353,6 +615,52 @@ int32_t run_igemm(mtl_ctx* ctx, const IgemmCall& c, int x3) {
     if (x3) k_weights_relayout<true><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
     else k_weights_relayout<false><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
     MTL_LAUNCHED(ctx);
+
+    const bool channel_major = c.Kout >= 64 && (int64_t)c.N * c.OH * c.OW >= 1024 &&
+                               (int64_t)c.N * c.Kout * c.OH * c.OW < (1ll << 31) &&
+                               !(getenv("MANTLE_CONV_CHANNEL_MAJOR") && atoi(getenv("MANTLE_CONV_CHANNEL_MAJOR")) == 0);
+    if (channel_major) {
+        ConvTParams q;
+        q.N = c.N; q.OH = c.OH; q.OW = c.OW; q.Kout = c.Kout; q.Cin = c.Cin;
+        q.R = c.R; q.S = c.S; q.ph = c.ph; q.pw = c.pw;
+        choose_box_n(c.OW, c.OH, c.N, 256, &q.bw, &q.bh, &q.bn);
+        q.npix = q.bw * q.bh * q.bn;
+        q.n_mma = (q.npix + 15) / 16 * 16;
+        q.tiles_w = (c.OW + q.bw - 1) / q.bw;
+        q.tiles_h = (c.OH + q.bh - 1) / q.bh;
+        q.tiles_nb = (c.N + q.bn - 1) / q.bn;
+        q.tiles_k = (c.Kout + BM - 1) / BM;
+        q.nseg = x3 ? 3 : 1;
+        // segA selects the activation map, segB the weight map: lo*hi, hi*lo, hi*hi
+        if (x3) { q.segA[0] = 1; q.segB[0] = 0; q.segA[1] = 0; q.segB[1] = 1; q.segA[2] = 0; q.segB[2] = 0; }
+        else    { q.segA[0] = q.segA[1] = q.segA[2] = 0; q.segB[0] = q.segB[1] = q.segB[2] = 0; }
+        q.out = c.out; q.bias = c.bias; q.accumulate = c.accumulate; q.status = ctx->dev_status;
+        q.vec_ok = ((c.OH * c.OW) % 4 == 0) && ((reinterpret_cast<uintptr_t>(c.out) & 15) == 0);
+        CUtensorMap tm[4];
+        for (int i = 0; i < 2; ++i) {
+            const float* a = (i == 1 && x3) ? a_lo : a_hi;
+            const float* w = (i == 1 && x3) ? w_lo : w_hi;
+            uint64_t adims[4] = {(uint64_t)c.Cin, (uint64_t)c.IW, (uint64_t)c.IH, (uint64_t)c.N};
+            uint64_t astr[3] = {(uint64_t)c.Cin * 4, (uint64_t)c.IW * c.Cin * 4, (uint64_t)c.IH * c.IW * c.Cin * 4};
+            uint32_t abox[4] = {BK, (uint32_t)q.bw, (uint32_t)q.bh, (uint32_t)q.bn};
+            rc = mtl_encode_tmap(ctx, &tm[i], a, 4, adims, astr, abox);
+            if (rc) return rc;
+            uint64_t wdims[3] = {(uint64_t)c.Cin, (uint64_t)c.Kout, (uint64_t)(c.R * c.S)};
+            uint64_t wstr[2] = {(uint64_t)c.Cin * 4, (uint64_t)c.Kout * c.Cin * 4};
+            uint32_t wbox[3] = {BK, (uint32_t)BM, 1};
+            rc = mtl_encode_tmap(ctx, &tm[2 + i], w, 3, wdims, wstr, wbox);
+            if (rc) return rc;
+        }
+        MTL_CUDA(ctx, cudaFuncSetAttribute(k_conv_igemm_t, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmemBytes));
+        int tiles = q.tiles_w * q.tiles_h * q.tiles_nb * q.tiles_k;
+        int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+        {
+            mtl_prof_scope prof(ctx, MTL_PROF_CONV_IGEMM);
+            k_conv_igemm_t<<<grid, kThreads, kTSmemBytes, ctx->stream>>>(tm[0], tm[1], tm[2], tm[3], q);
+        }
+        MTL_LAUNCHED(ctx);
+        return MTL_OK;
+    }
 
     ConvTcParams p;
     p.N = c.N; p.OH = c.OH; p.OW = c.OW; p.Kout = c.Kout; p.Cin = c.Cin;
