@@ -109,6 +109,97 @@ __global__ void __launch_bounds__(kBlock) k_conv_fwd_patch(float* __restrict__ Y
     }
 }
 
+// Forward for few input channels and rows of at most 32 - (S - 1) pixels: a warp owns one output
+// row, a lane one output channel with its R*S*C weights in registers.  Input rows come out of a
+// zero-padded plane in shared memory as broadcast float4 loads (8*R*C loads for OW*R*S*C FMAs);
+// the finished 32 channels x OW block is turned through shared memory so that OW/4 lanes store one
+// channel's row as consecutive float4s.  Bound by writing Y.
+template <int R, int S, int C, int OW, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 2) k_conv_fwd_rows(float* __restrict__ Y, const float* __restrict__ X,
+                                                                  const float* __restrict__ Wt,
+                                                                  const float* __restrict__ bias, ConvGeom g) {
+    constexpr int PW = 32, NT = WARPS * 32, SST = OW + ((OW / 4) % 2 == 0 ? 4 : 8);  // odd multiple of 4 floats
+    constexpr int LPC = OW / 4, CPI = 32 / LPC;  // lanes per channel row, channel rows per store instruction
+    extern __shared__ __align__(16) float rows_smem[];
+    const int PH = g.OH + R - 1;
+    float* xs = rows_smem;                         // [2][C][PH][PW]
+    float* stg = rows_smem + 2 * C * PH * PW;      // [WARPS][32][SST]
+    const int kgroups = (g.K + 31) / 32;
+    const int kg = blockIdx.x % kgroups;
+    const int k0 = kg * 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k = k0 + lane;
+    float w[C * R * S];
+#pragma unroll
+    for (int i = 0; i < C * R * S; ++i) w[i] = k < g.K ? __ldg(Wt + (int64_t)k * C * R * S + i) : 0.0f;
+    const float bv = (bias && k < g.K) ? __ldg(bias + k) : 0.0f;
+
+    for (int i = threadIdx.x; i < 2 * C * PH * PW; i += NT) xs[i] = 0.0f;
+    __syncthreads();
+    const int n_first = blockIdx.x / kgroups, n_step = gridDim.x / kgroups;
+    auto issue = [&](int n, int buf) {
+        float* xb = xs + buf * C * PH * PW;
+        const float* xn = X + (int64_t)n * C * g.H * g.W;
+        for (int i = threadIdx.x; i < C * g.H * g.W; i += NT) {
+            const int c = i / (g.H * g.W), rem = i - c * g.H * g.W;
+            const int ih = rem / g.W, iw = rem - ih * g.W;
+            uint32_t dst = (uint32_t)__cvta_generic_to_shared(xb + (c * PH + ih + g.ph) * PW + iw + g.pw);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(xn + i) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (n_first < g.N) issue(n_first, 0);
+    int buf = 0;
+    float* sw = stg + warp * 32 * SST;
+    const int chl = lane / LPC, sub = lane - chl * LPC;
+    for (int n = n_first; n < g.N; n += n_step, buf ^= 1) {
+        if (n + n_step < g.N) {
+            issue(n + n_step, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const float* xb = xs + buf * C * PH * PW;
+        for (int oh = warp; oh < g.OH; oh += WARPS) {
+            float out[OW];
+#pragma unroll
+            for (int i = 0; i < OW; ++i) out[i] = bv;
+#pragma unroll
+            for (int c = 0; c < C; ++c)
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    float xr[PW];
+#pragma unroll
+                    for (int i = 0; i < PW / 4; ++i) {
+                        const float4 q = *reinterpret_cast<const float4*>(xb + (c * PH + oh + r) * PW + 4 * i);
+                        xr[4 * i] = q.x; xr[4 * i + 1] = q.y; xr[4 * i + 2] = q.z; xr[4 * i + 3] = q.w;
+                    }
+#pragma unroll
+                    for (int ow = 0; ow < OW; ++ow)
+#pragma unroll
+                        for (int s2 = 0; s2 < S; ++s2) out[ow] = fmaf(w[(c * R + r) * S + s2], xr[ow + s2], out[ow]);
+                }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < OW / 4; ++i)
+                *reinterpret_cast<float4*>(sw + lane * SST + 4 * i) = make_float4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+            __syncwarp();
+            if (chl < CPI) {
+#pragma unroll
+                for (int it = 0; it < (32 + CPI - 1) / CPI; ++it) {
+                    const int ch = it * CPI + chl;
+                    if (ch < 32 && k0 + ch < g.K) {
+                        const float4 q = *reinterpret_cast<const float4*>(sw + ch * SST + 4 * sub);
+                        *reinterpret_cast<float4*>(Y + (((int64_t)n * g.K + k0 + ch) * g.OH + oh) * OW + 4 * sub) = q;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
 __global__ void __launch_bounds__(kBlock) k_conv_dgrad(float* __restrict__ dX, const float* __restrict__ ug,
                                                        const float* __restrict__ Wt, ConvGeom g, int64_t n_in,
                                                        int accumulate) {
@@ -264,6 +355,117 @@ __global__ void __launch_bounds__(kBlock) k_conv_wgrad_staged(float* __restrict_
     }
 }
 
+// Few input channels, stride 1, rows of at most 32 - (S - 1) pixels (the first layer of the CNNs).
+// This layer is bound by reading ug once, so ug streams through shared memory with cp.async
+// (two buffers) while the previous chunk is multiplied.  A warp owns one output row, a lane one
+// output channel: the input row comes out of shared memory as broadcast float4 loads and the ug
+// row as one float4 per four pixels (row stride 4 mod 32 floats keeps those conflict free), so
+// one output row costs 8*R + OW/4 shared loads for OW*R*S FMAs per thread.
+template <int R, int S, int OW, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 3) k_conv_wgrad_rows(float* __restrict__ partial,
+                                                                const float* __restrict__ ug,
+                                                                const float* __restrict__ X, ConvGeom g,
+                                                                int n_per_split, int ustride) {
+    constexpr int PW = 32, RS = R * S, NT = WARPS * 32;
+    extern __shared__ __align__(16) float rows_smem[];
+    const int PH = g.OH + R - 1;
+    float* xs = rows_smem;                       // [2][PH][PW] zero-padded input planes
+    float* us = rows_smem + 2 * PH * PW;         // [2][32][ustride] chunks of ug
+    const int kgroups = (g.K + 31) / 32;
+    const int kg = blockIdx.x % kgroups, c = blockIdx.x / kgroups;
+    const int k0 = kg * 32;
+    const int n_begin = blockIdx.y * n_per_split;
+    const int n_end = min(g.N, n_begin + n_per_split);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nchunks = (g.OH + WARPS - 1) / WARPS;
+    const int steps = (n_end - n_begin) * nchunks;
+
+    for (int i = threadIdx.x; i < 2 * PH * PW; i += NT) xs[i] = 0.0f;
+    __syncthreads();
+
+    auto issue = [&](int step) {
+        const int n = n_begin + step / nchunks, chunk = step % nchunks;
+        const int oh0 = chunk * WARPS;
+        constexpr int pieces = WARPS * OW / 4;  // 16-byte pieces per channel (OH is a multiple of WARPS)
+        float* ub = us + (step & 1) * 32 * ustride;
+        const float* ubase = ug + (((int64_t)n * g.K + k0) * g.OH + oh0) * OW;
+        const int plane = g.OH * OW;
+#pragma unroll
+        for (int i = threadIdx.x; i < 32 * pieces; i += NT) {
+            const int kk = i / pieces, pc = i - kk * pieces;
+            if (k0 + kk < g.K) {
+                const float* src = ubase + kk * plane + pc * 4;
+                uint32_t dst = (uint32_t)__cvta_generic_to_shared(ub + kk * ustride + pc * 4);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+            }
+        }
+        if (chunk == 0) {
+            float* xb = xs + ((step / nchunks) & 1) * PH * PW;
+            const float* xc = X + ((int64_t)n * g.C + c) * g.H * g.W;
+            for (int i = threadIdx.x; i < g.H * g.W; i += NT) {
+                const int ih = i / g.W, iw = i - ih * g.W;
+                uint32_t dst = (uint32_t)__cvta_generic_to_shared(xb + (ih + g.ph) * PW + iw + g.pw);
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(xc + i) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    float acc[RS];
+#pragma unroll
+    for (int t = 0; t < RS; ++t) acc[t] = 0.0f;
+
+    if (steps > 0) issue(0);
+    for (int step = 0; step < steps; ++step) {
+        if (step + 1 < steps) {
+            issue(step + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const int chunk = step % nchunks;
+        const int oh = chunk * WARPS + warp;
+        if (oh < g.OH) {
+            const float* ub = us + (step & 1) * 32 * ustride + lane * ustride + warp * OW;
+            const float* xb = xs + ((step / nchunks) & 1) * PH * PW + oh * PW;
+            float u[OW];
+#pragma unroll
+            for (int i = 0; i < OW / 4; ++i) {
+                const float4 q = *reinterpret_cast<const float4*>(ub + 4 * i);
+                u[4 * i] = q.x; u[4 * i + 1] = q.y; u[4 * i + 2] = q.z; u[4 * i + 3] = q.w;
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                float xr[PW];
+#pragma unroll
+                for (int i = 0; i < PW / 4; ++i) {
+                    const float4 q = *reinterpret_cast<const float4*>(xb + r * PW + 4 * i);
+                    xr[4 * i] = q.x; xr[4 * i + 1] = q.y; xr[4 * i + 2] = q.z; xr[4 * i + 3] = q.w;
+                }
+#pragma unroll
+                for (int ow = 0; ow < OW; ++ow)
+#pragma unroll
+                    for (int s2 = 0; s2 < S; ++s2) acc[r * S + s2] = fmaf(u[ow], xr[ow + s2], acc[r * S + s2]);
+            }
+        }
+        __syncthreads();
+    }
+    // fold the WARPS row partials of every channel in a fixed order
+    float* red = us;  // [WARPS][32][RS]
+#pragma unroll
+    for (int t = 0; t < RS; ++t) red[(warp * 32 + lane) * RS + t] = acc[t];
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * RS; i += NT) {
+        const int kk = i / RS, t = i - kk * RS;
+        if (k0 + kk >= g.K) continue;
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) v += red[w * 32 * RS + i];
+        partial[((int64_t)blockIdx.y * g.K * g.C + (int64_t)(k0 + kk) * g.C + c) * RS + t] = v;
+    }
+}
+
 // Any kernel size: one tap at a time.
 __global__ void __launch_bounds__(kBlock) k_conv_wgrad_generic(float* __restrict__ partial, const float* __restrict__ ug,
                                                                const float* __restrict__ X, ConvGeom g,
@@ -355,8 +557,32 @@ static int32_t launch_fwd_patch(mtl_ctx* ctx, float* Y, const float* X, const fl
     return MTL_OK;
 }
 
+template <int R, int S, int C>
+static int32_t launch_fwd_rows(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
+                               const ConvGeom& g) {
+    constexpr int WARPS = 7, OWc = 28, SST = 36;
+    const int kgroups = (g.K + 31) / 32;
+    const int PH = g.OH + R - 1;
+    size_t smem = (size_t)(2 * C * PH * 32 + WARPS * 32 * SST) * 4;
+    int per_group = (ctx->sm_count * 2 + kgroups - 1) / kgroups;
+    if (per_group > g.N) per_group = g.N;
+    auto kern = k_conv_fwd_rows<R, S, C, OWc, WARPS>;
+    MTL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<per_group * kgroups, WARPS * 32, smem, ctx->stream>>>(Y, X, Wt, bias, g);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
 int32_t mtl_conv_fwd_simt(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
                           const ConvGeom& g) {
+    const bool rows_ok = g.OW == 28 && g.K >= 16 && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1 &&
+                         g.W + 2 * g.pw == g.OW + g.S - 1 && g.H + 2 * g.ph == g.OH + g.R - 1 && g.OH <= 64 &&
+                         ((reinterpret_cast<uintptr_t>(Y) & 15) == 0) && g.N >= 64;
+    if (rows_ok) {
+        if (g.R == 5 && g.S == 5 && g.C == 1) return launch_fwd_rows<5, 5, 1>(ctx, Y, X, Wt, bias, g);
+        if (g.R == 3 && g.S == 3 && g.C == 1) return launch_fwd_rows<3, 3, 1>(ctx, Y, X, Wt, bias, g);
+        if (g.R == 3 && g.S == 3 && g.C == 3) return launch_fwd_rows<3, 3, 3>(ctx, Y, X, Wt, bias, g);
+    }
     if ((size_t)g.K * (g.C * g.R * g.S + 4) * 4 <= 40 * 1024 && (int64_t)g.N * g.OH * g.OW >= 4096) {
         if (g.R == 5 && g.S == 5 && g.C == 1) return launch_fwd_patch<5, 5, 1>(ctx, Y, X, Wt, bias, g);
         if (g.R == 3 && g.S == 3 && g.C == 1) return launch_fwd_patch<3, 3, 1>(ctx, Y, X, Wt, bias, g);
@@ -405,6 +631,40 @@ int32_t mtl_conv_wgrad_simt(mtl_ctx* ctx, float* dW, const float* ug, const floa
     const int PH = (g.OH - 1) * g.sh + (g.R - 1) * g.dh + 1 + 0, PW = (g.OW - 1) * g.sw + (g.S - 1) * g.dw + 1;
     const bool staged_ok = (size_t)PH * PW * 4 <= 40 * 1024 && ((g.R == 5 && g.S == 5) || (g.R == 3 && g.S == 3)) &&
                            g.OH * g.OW >= 64;
+    // row-streaming variant: few input channels, 28-pixel rows, 'same'-style geometry
+    const bool rows_ok = g.C <= 4 && g.K >= 16 && g.OW == 28 && g.OH % 7 == 0 && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1 &&
+                         ((g.R == 5 && g.S == 5) || (g.R == 3 && g.S == 3)) && g.W + 2 * g.pw == g.OW + g.S - 1 &&
+                         g.H + 2 * g.ph == g.OH + g.R - 1 && ((reinterpret_cast<uintptr_t>(ug) & 15) == 0) && g.N >= 64;
+    if (rows_ok) {
+        constexpr int WARPS = 7, OWc = 28;
+        const int kgroups = (g.K + 31) / 32;
+        int ustride = WARPS * OWc;
+        while ((ustride / 4) % 2 == 0) ustride += 4;     // odd multiple of 4 floats
+        const int PH = g.OH + g.R - 1;
+        size_t smem = (size_t)(2 * PH * 32 + 2 * 32 * ustride) * 4;
+        size_t red_bytes = (size_t)WARPS * 32 * taps * 4;
+        if (red_bytes > (size_t)2 * 32 * ustride * 4) smem += red_bytes - (size_t)2 * 32 * ustride * 4;
+        int ns = (ctx->sm_count * 3 + kgroups * g.C - 1) / (kgroups * g.C);
+        if (ns > g.N / 4) ns = g.N / 4;
+        if (ns < 1) ns = 1;
+        int nps = (g.N + ns - 1) / ns;
+        ns = (g.N + nps - 1) / nps;
+        MTL_REQUIRE(ctx, ns <= 65535, "too many batch splits");
+        void* ws2;
+        int32_t rc2 = mtl_workspace(ctx, (size_t)ns * kc * taps * 4, &ws2);
+        if (rc2) return rc2;
+        float* part = (float*)ws2;
+        dim3 rgrid((unsigned)(kgroups * g.C), (unsigned)ns);
+        if (g.R == 5) {
+            MTL_CUDA(ctx, cudaFuncSetAttribute(k_conv_wgrad_rows<5, 5, OWc, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            k_conv_wgrad_rows<5, 5, OWc, WARPS><<<rgrid, WARPS * 32, smem, ctx->stream>>>(part, ug, X, g, nps, ustride);
+        } else {
+            MTL_CUDA(ctx, cudaFuncSetAttribute(k_conv_wgrad_rows<3, 3, OWc, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            k_conv_wgrad_rows<3, 3, OWc, WARPS><<<rgrid, WARPS * 32, smem, ctx->stream>>>(part, ug, X, g, nps, ustride);
+        }
+        MTL_LAUNCHED(ctx);
+        return mtl_sum_partials(ctx, dW, part, (int64_t)kc * taps, ns, accumulate);
+    }
     if (staged_ok) {
         constexpr int KB = 4;
         const int kgroups = (g.K + KB - 1) / KB;

@@ -116,6 +116,57 @@ __global__ void __launch_bounds__(128) k_gemm_thin_n(float* __restrict__ C, cons
         }
 }
 
+// partial[split][M,N] = A[M, k-slice] . B[k-slice, N]: a block stages its slice of B in shared
+// memory (rows padded to 20 floats so that the four float4 reads of a row are conflict free), each
+// warp streams four rows of A with coalesced loads and keeps 4 x 16 partial sums per lane.
+// Splitting k gives enough blocks to fill the machine when M is only a few thousand rows.
+constexpr int kThinKC = 512;  // k extent of one block
+__global__ void __launch_bounds__(256) k_gemm_thin_tile(float* __restrict__ partial, const float* __restrict__ A,
+                                                        const float* __restrict__ B, int M, int N, int K) {
+    __shared__ __align__(16) float b_s[kThinKC * 20];
+    const int k_begin = blockIdx.y * kThinKC;
+    const int kn = min(kThinKC, K - k_begin);
+    for (int i = threadIdx.x; i < kn * 16; i += 256) {
+        const int kk = i >> 4, j = i & 15;
+        b_s[kk * 20 + j] = j < N ? __ldg(B + (int64_t)(k_begin + kk) * N + j) : 0.0f;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = (blockIdx.x * 8 + warp) * 4;
+    if (m0 >= M) return;
+    float acc[4][16];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[r][j] = 0.0f;
+    const float* a0 = A + (int64_t)m0 * K + k_begin;
+    for (int kk = lane; kk < kn; kk += 32) {
+        float a[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) a[r] = (m0 + r < M) ? __ldg(a0 + (int64_t)r * K + kk) : 0.0f;
+        float b[16];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 t = *reinterpret_cast<const float4*>(b_s + kk * 20 + q * 4);
+            b[q * 4] = t.x; b[q * 4 + 1] = t.y; b[q * 4 + 2] = t.z; b[q * 4 + 3] = t.w;
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[r][j] = fmaf(a[r], b[j], acc[r][j]);
+    }
+    float* out = partial + (int64_t)blockIdx.y * M * N;
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            float v = acc[r][j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && j < N && m0 + r < M) out[(int64_t)(m0 + r) * N + j] = v;
+        }
+}
+
 // partial[split][M,N] = A^T . B over a slice of k, A stored [K, M] (m contiguous): one thread per
 // output row, rows of B staged in shared memory.
 __global__ void __launch_bounds__(256) k_gemm_thin_n_ta(float* __restrict__ partial, const float* __restrict__ A,
@@ -169,6 +220,19 @@ bool mtl_gemm_thin_supported(int64_t M, int64_t N, int64_t K, int transA, int tr
 
 int32_t mtl_gemm_thin(mtl_ctx* ctx, float* C, const float* A, const float* B, int64_t M, int64_t N, int64_t K,
                       int transA, int accumulate) {
+    if (!transA && K >= 2 * kThinKC) {
+        const int nsplit = (int)((K + kThinKC - 1) / kThinKC);
+        void* ws;
+        int32_t rc = mtl_workspace(ctx, (size_t)nsplit * M * N * 4, &ws);
+        if (rc) return rc;
+        dim3 grid((unsigned)((M + 31) / 32), (unsigned)nsplit);
+        k_gemm_thin_tile<<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K);
+        MTL_LAUNCHED(ctx);
+        int fg = mtl_grid_for(M * N, 256, ctx->sm_count, 8);
+        k_fold_partials<<<fg, 256, 0, ctx->stream>>>(C, (const float*)ws, M * N, nsplit, accumulate);
+        MTL_LAUNCHED(ctx);
+        return MTL_OK;
+    }
     if (!transA) {
         constexpr int ROWS = 4;
         int64_t warps = (M + ROWS - 1) / ROWS;

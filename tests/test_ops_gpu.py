@@ -324,6 +324,35 @@ def test_conv_tensor_core(ctx, case):
     assert rel_err(acc, (init + want[1]).astype(np.float64)) < 3e-5
 
 
+FIRST_LAYER_CONV = [  # few input channels, 28-pixel rows: the CUDA-core kernels written for conv1 of the CNNs
+    (70, 1, 28, 28, 64, 5, 5, 2),
+    (65, 3, 28, 28, 40, 3, 3, 1),
+    (64, 1, 28, 28, 16, 5, 5, 2),
+    (9, 1, 28, 28, 64, 5, 5, 2),       # batch below the threshold of the row-streaming kernel
+]
+
+
+@pytest.mark.parametrize("case", FIRST_LAYER_CONV)
+def test_conv_first_layer(ctx, case):
+    N, C, H, W, K, R, S, p = case
+    rng = np.random.default_rng(sum(case))
+    x = rng.normal(0, 1, (N, C, H, W)).astype(np.float32)
+    w = (rng.normal(0, 1, (K, C, R, S)) / np.sqrt(C * R * S)).astype(np.float32)
+    b = rng.normal(0, 1, K).astype(np.float32)
+    kw = dict(padding=(p, p), stride=(1, 1), dilation=(1, 1))
+    want_y = oracle.conv2d_fwd(x, w, b, **kw)
+    ug = rng.normal(0, 1, want_y.shape).astype(np.float32)
+    want = (want_y, oracle.conv2d_bwd(0, ug, x, w, **kw), oracle.conv2d_bwd(1, ug, x, w, **kw),
+            oracle.conv2d_bwd(2, ug, x, w, **kw))
+    got = conv_all(ctx, x, w, b, ug, **kw)
+    for g, wv, what in zip(got, want, ("y", "dx", "dw", "db")):
+        e = rel_err(g, wv.astype(np.float64))
+        assert e < 1e-5, "%s: normalised max error %.3e" % (what, e)   # fp32 CUDA-core paths, re-associated sums
+    init = rng.normal(0, 1, w.shape).astype(np.float32)
+    acc = run_bwd(ctx, 1, OP.CONV2D, ug, x, w, np.zeros_like(b), grad_shape=w.shape, init=init, **kw)
+    assert rel_err(acc, (init + want[2]).astype(np.float64)) < 1e-5
+
+
 # ------------------------------------------------------------------ MAXPOOL2D ------------------
 
 def test_maxpool_reference_cases(ctx):
