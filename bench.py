@@ -357,6 +357,7 @@ def run_ours(args):
 
 
 def main():
+    global GLOBAL_BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -364,8 +365,11 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--math", choices=("tf32", "tf32x3", "fp32"), default="tf32")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
+                    help="diagnostic only: the headline number is quoted at the default")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    GLOBAL_BATCH = args.global_batch
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
