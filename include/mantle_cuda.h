@@ -172,6 +172,22 @@ MTL_API int32_t mtl_maxpool2d_bwd_idx(mtl_ctx* ctx, float* dX, const float* ug,
                                       const int32_t* idx, const mtl_conv2d_desc* d,
                                       int32_t accumulate);
 
+/* Fused forms for a CONV2D -> RELU -> MAXPOOL2D chain.  Neither has a single counterpart in the
+ * reference: each gives exactly the result of two of its operator calls and lets the caller skip
+ * one full-size tensor.  act_op is MTL_OP_RELU, or negative for "no activation".
+ *   mtl_conv2d_fwd_act         Y = RELU.forward(CONV2D.forward(X, Wt, bias))  (conv.mojo:81-226 then
+ *                              mlops.mojo RELU): the pre-activation tensor is never written.
+ *   mtl_maxpool2d_bwd_idx_act  dX (+)= RELU.backward(MAXPOOL2D.backward(ug)), where dX is the gradient of
+ *                              the RELU's INPUT and `pooled` the pooling output of the forward pass: the
+ *                              element a window selected is the pooled value itself, so (pooled > 0) is
+ *                              the RELU mask of the only element that receives a gradient. */
+MTL_API int32_t mtl_conv2d_fwd_act(mtl_ctx* ctx, float* Y, const float* X, const float* Wt,
+                                   const float* bias, const mtl_conv2d_desc* d, int32_t act_op);
+MTL_API int32_t mtl_maxpool2d_bwd_idx_act(mtl_ctx* ctx, float* dX, const float* ug,
+                                          const int32_t* idx, const float* pooled,
+                                          const mtl_conv2d_desc* d, int32_t act_op,
+                                          int32_t accumulate);
+
 /* ---------------------------------------------------------------- elementwise ----------- */
 
 /* ADD/SUB/MUL/DIV.forward -> elwise_op / broadcast_elwise_op (tensorutils.mojo:243-357):

@@ -21,16 +21,28 @@ int32_t make_geom(mtl_ctx* ctx, const mtl_conv2d_desc* d, ConvGeom* g) {
 
 extern "C" {
 
-int32_t mtl_conv2d_fwd(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
-                       const mtl_conv2d_desc* d) {
+static int32_t conv2d_fwd(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
+                          const mtl_conv2d_desc* d, int relu) {
     MTL_CHECK_CTX(ctx);
     ConvGeom g;
     int32_t rc = make_geom(ctx, d, &g);
     if (rc) return rc;
-    MTL_REQUIRE(ctx, Y && X && Wt, "null pointer in mtl_conv2d_fwd");
+    MTL_REQUIRE(ctx, Y && X && Wt, "null pointer in CONV2D forward");
     if (ctx->math_mode != MTL_MATH_FP32 && mtl_conv_fwd_tc_supported(g, X, Wt, Y))
-        return mtl_conv_fwd_tc(ctx, Y, X, Wt, bias, g, ctx->math_mode == MTL_MATH_TF32X3);
-    return mtl_conv_fwd_simt(ctx, Y, X, Wt, bias, g);
+        return mtl_conv_fwd_tc(ctx, Y, X, Wt, bias, g, ctx->math_mode == MTL_MATH_TF32X3, relu);
+    return mtl_conv_fwd_simt(ctx, Y, X, Wt, bias, g, relu);
+}
+
+int32_t mtl_conv2d_fwd(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
+                       const mtl_conv2d_desc* d) {
+    return conv2d_fwd(ctx, Y, X, Wt, bias, d, 0);
+}
+
+int32_t mtl_conv2d_fwd_act(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
+                           const mtl_conv2d_desc* d, int32_t act_op) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, act_op == MTL_OP_RELU || act_op < 0, "mtl_conv2d_fwd_act fuses RELU only (act_op %d)", act_op);
+    return conv2d_fwd(ctx, Y, X, Wt, bias, d, act_op == MTL_OP_RELU ? 1 : 0);
 }
 
 int32_t mtl_conv2d_bwd(mtl_ctx* ctx, int32_t tensor_id, float* grad, const float* ug, const float* X,

@@ -13,8 +13,10 @@ struct ConvGeom {
 int32_t mtl_sum_partials(mtl_ctx* ctx, float* out, const float* partial, int64_t n, int nsplit, int accumulate);
 
 // CUDA-core kernels (conv_simt.cu)
+// relu != 0: Y = relu(conv + bias), applied in the kernel's epilogue where the kernel has one and by an
+// in-place pass otherwise
 int32_t mtl_conv_fwd_simt(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
-                          const ConvGeom& g);
+                          const ConvGeom& g, int relu);
 int32_t mtl_conv_dgrad_simt(mtl_ctx* ctx, float* dX, const float* ug, const float* Wt, const ConvGeom& g,
                             int accumulate);
 int32_t mtl_conv_wgrad_simt(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,
@@ -26,7 +28,7 @@ bool mtl_conv_fwd_tc_supported(const ConvGeom& g, const float* X, const float* W
 bool mtl_conv_dgrad_tc_supported(const ConvGeom& g, const float* ug, const float* Wt, const float* dX);
 bool mtl_conv_wgrad_tc_supported(const ConvGeom& g, const float* ug, const float* X, const float* dW);
 int32_t mtl_conv_fwd_tc(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
-                        const ConvGeom& g, int x3);
+                        const ConvGeom& g, int x3, int relu);
 int32_t mtl_conv_dgrad_tc(mtl_ctx* ctx, float* dX, const float* ug, const float* Wt, const ConvGeom& g,
                           int accumulate, int x3);
 int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,

@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(kBlock) k_conv_fwd_patch(float* __restrict__ Y
 template <int R, int S, int C, int OW, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 2) k_conv_fwd_rows(float* __restrict__ Y, const float* __restrict__ X,
                                                                   const float* __restrict__ Wt,
-                                                                  const float* __restrict__ bias, ConvGeom g) {
+                                                                  const float* __restrict__ bias, ConvGeom g, int relu) {
     constexpr int PW = 32, NT = WARPS * 32, SST = OW + ((OW / 4) % 2 == 0 ? 4 : 8);  // odd multiple of 4 floats
     constexpr int LPC = OW / 4, CPI = 32 / LPC;  // lanes per channel row, channel rows per store instruction
     extern __shared__ __align__(16) float rows_smem[];
@@ -180,6 +180,10 @@ __global__ void __launch_bounds__(WARPS * 32, 2) k_conv_fwd_rows(float* __restri
 #pragma unroll
                         for (int s2 = 0; s2 < S; ++s2) out[ow] = fmaf(w[(c * R + r) * S + s2], xr[ow + s2], out[ow]);
                 }
+            if (relu) {  // RELU.forward: x > 0 ? x : 0
+#pragma unroll
+                for (int i = 0; i < OW; ++i) out[i] = out[i] > 0.0f ? out[i] : 0.0f;
+            }
             __syncwarp();
 #pragma unroll
             for (int i = 0; i < OW / 4; ++i)
@@ -559,7 +563,7 @@ static int32_t launch_fwd_patch(mtl_ctx* ctx, float* Y, const float* X, const fl
 
 template <int R, int S, int C>
 static int32_t launch_fwd_rows(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
-                               const ConvGeom& g) {
+                               const ConvGeom& g, int relu) {
     constexpr int WARPS = 7, OWc = 28, SST = 36;
     const int kgroups = (g.K + 31) / 32;
     const int PH = g.OH + R - 1;
@@ -568,21 +572,13 @@ static int32_t launch_fwd_rows(mtl_ctx* ctx, float* Y, const float* X, const flo
     if (per_group > g.N) per_group = g.N;
     auto kern = k_conv_fwd_rows<R, S, C, OWc, WARPS>;
     MTL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<per_group * kgroups, WARPS * 32, smem, ctx->stream>>>(Y, X, Wt, bias, g);
+    kern<<<per_group * kgroups, WARPS * 32, smem, ctx->stream>>>(Y, X, Wt, bias, g, relu);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
 
-int32_t mtl_conv_fwd_simt(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
+static int32_t conv_fwd_simt_plain(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
                           const ConvGeom& g) {
-    const bool rows_ok = g.OW == 28 && g.K >= 16 && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1 &&
-                         g.W + 2 * g.pw == g.OW + g.S - 1 && g.H + 2 * g.ph == g.OH + g.R - 1 && g.OH <= 64 &&
-                         ((reinterpret_cast<uintptr_t>(Y) & 15) == 0) && g.N >= 64;
-    if (rows_ok) {
-        if (g.R == 5 && g.S == 5 && g.C == 1) return launch_fwd_rows<5, 5, 1>(ctx, Y, X, Wt, bias, g);
-        if (g.R == 3 && g.S == 3 && g.C == 1) return launch_fwd_rows<3, 3, 1>(ctx, Y, X, Wt, bias, g);
-        if (g.R == 3 && g.S == 3 && g.C == 3) return launch_fwd_rows<3, 3, 3>(ctx, Y, X, Wt, bias, g);
-    }
     if ((size_t)g.K * (g.C * g.R * g.S + 4) * 4 <= 40 * 1024 && (int64_t)g.N * g.OH * g.OW >= 4096) {
         if (g.R == 5 && g.S == 5 && g.C == 1) return launch_fwd_patch<5, 5, 1>(ctx, Y, X, Wt, bias, g);
         if (g.R == 3 && g.S == 3 && g.C == 1) return launch_fwd_patch<3, 3, 1>(ctx, Y, X, Wt, bias, g);
@@ -595,6 +591,21 @@ int32_t mtl_conv_fwd_simt(mtl_ctx* ctx, float* Y, const float* X, const float* W
     k_conv_fwd<<<grid, kBlock, w_in_smem ? wbytes : 0, ctx->stream>>>(Y, X, Wt, bias, g, n_out, w_in_smem);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
+}
+
+int32_t mtl_conv_fwd_simt(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
+                          const ConvGeom& g, int relu) {
+    const bool rows_ok = g.OW == 28 && g.K >= 16 && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1 &&
+                         g.W + 2 * g.pw == g.OW + g.S - 1 && g.H + 2 * g.ph == g.OH + g.R - 1 && g.OH <= 64 &&
+                         ((reinterpret_cast<uintptr_t>(Y) & 15) == 0) && g.N >= 64;
+    if (rows_ok) {
+        if (g.R == 5 && g.S == 5 && g.C == 1) return launch_fwd_rows<5, 5, 1>(ctx, Y, X, Wt, bias, g, relu);
+        if (g.R == 3 && g.S == 3 && g.C == 1) return launch_fwd_rows<3, 3, 1>(ctx, Y, X, Wt, bias, g, relu);
+        if (g.R == 3 && g.S == 3 && g.C == 3) return launch_fwd_rows<3, 3, 3>(ctx, Y, X, Wt, bias, g, relu);
+    }
+    int32_t rc = conv_fwd_simt_plain(ctx, Y, X, Wt, bias, g);
+    if (rc || !relu) return rc;
+    return mtl_unary_fwd(ctx, MTL_OP_RELU, Y, Y, (int64_t)g.N * g.K * g.OH * g.OW, 0.0f, 0.0f);
 }
 
 int32_t mtl_conv_dgrad_simt(mtl_ctx* ctx, float* dX, const float* ug, const float* Wt, const ConvGeom& g,

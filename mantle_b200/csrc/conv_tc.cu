@@ -313,6 +313,7 @@ struct IgemmCall {
     float* out;
     const float* bias;
     int accumulate;
+    int relu;           // clamp the result at zero after the bias (forward with a fused RELU)
 };
 
 // ------------------------------------------------------------------ channel-major variant -----
@@ -338,6 +339,7 @@ struct ConvTParams {
     float* out;
     const float* bias;
     int accumulate;
+    int relu;
     int vec_ok;             // channel planes are 16-byte aligned: four adjacent pixels may leave as a float4
     int32_t* status;
 };
@@ -502,10 +504,15 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                 tmem_ld_wait();
                 __syncwarp();
 #pragma unroll
-                for (int g = 0; g < 8; ++g)
-                    *reinterpret_cast<float4*>(stg + lane * 36 + g * 4) =
-                        make_float4(__uint_as_float(r[g * 4]) + bv, __uint_as_float(r[g * 4 + 1]) + bv,
-                                    __uint_as_float(r[g * 4 + 2]) + bv, __uint_as_float(r[g * 4 + 3]) + bv);
+                for (int g = 0; g < 8; ++g) {
+                    float4 o = make_float4(__uint_as_float(r[g * 4]) + bv, __uint_as_float(r[g * 4 + 1]) + bv,
+                                           __uint_as_float(r[g * 4 + 2]) + bv, __uint_as_float(r[g * 4 + 3]) + bv);
+                    if (p.relu) {  // RELU.forward: x > 0 ? x : 0
+                        o.x = o.x > 0.0f ? o.x : 0.0f; o.y = o.y > 0.0f ? o.y : 0.0f;
+                        o.z = o.z > 0.0f ? o.z : 0.0f; o.w = o.w > 0.0f ? o.w : 0.0f;
+                    }
+                    *reinterpret_cast<float4*>(stg + lane * 36 + g * 4) = o;
+                }
                 __syncwarp();
                 const int j0 = c * 32 + sub * 4;
                 const int vec = col_vec[j0 >> 2];
@@ -634,7 +641,7 @@ int32_t run_igemm(mtl_ctx* ctx, const IgemmCall& c, int x3) {
         // segA selects the activation map, segB the weight map: lo*hi, hi*lo, hi*hi
         if (x3) { q.segA[0] = 1; q.segB[0] = 0; q.segA[1] = 0; q.segB[1] = 1; q.segA[2] = 0; q.segB[2] = 0; }
         else    { q.segA[0] = q.segA[1] = q.segA[2] = 0; q.segB[0] = q.segB[1] = q.segB[2] = 0; }
-        q.out = c.out; q.bias = c.bias; q.accumulate = c.accumulate; q.status = ctx->dev_status;
+        q.out = c.out; q.bias = c.bias; q.accumulate = c.accumulate; q.relu = c.relu; q.status = ctx->dev_status;
         q.vec_ok = ((c.OH * c.OW) % 4 == 0) && ((reinterpret_cast<uintptr_t>(c.out) & 15) == 0);
         CUtensorMap tm[4];
         for (int i = 0; i < 2; ++i) {
@@ -692,8 +699,11 @@ int32_t run_igemm(mtl_ctx* ctx, const IgemmCall& c, int x3) {
         rc = mtl_encode_tmap(ctx, &maps[2 + i], w, 3, wdims, wstr, wbox);
         if (rc) return rc;
     }
-    if (BN == 128) return launch_igemm<128>(ctx, maps, p);
-    return launch_igemm<64>(ctx, maps, p);
+    rc = (BN == 128) ? launch_igemm<128>(ctx, maps, p) : launch_igemm<64>(ctx, maps, p);
+    if (rc) return rc;
+    if (c.relu)  // this kernel has no fused activation: one in-place pass over the result
+        return mtl_unary_fwd(ctx, MTL_OP_RELU, c.out, c.out, (int64_t)c.N * c.Kout * c.OH * c.OW, 0.0f, 0.0f);
+    return MTL_OK;
 }
 
 bool igemm_geometry_ok(const ConvGeom& g) {
@@ -930,12 +940,12 @@ bool mtl_conv_dgrad_tc_supported(const ConvGeom& g, const float* ug, const float
 }
 
 int32_t mtl_conv_fwd_tc(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
-                        const ConvGeom& g, int x3) {
+                        const ConvGeom& g, int x3, int relu) {
     IgemmCall c;
     c.N = g.N; c.Cin = g.C; c.IH = g.H; c.IW = g.W; c.Kout = g.K; c.OH = g.OH; c.OW = g.OW;
     c.R = g.R; c.S = g.S; c.ph = g.ph; c.pw = g.pw;
     c.act = X; c.wt = Wt; c.wK = g.K; c.wC = g.C; c.flip = 0;
-    c.out = Y; c.bias = bias; c.accumulate = 0;
+    c.out = Y; c.bias = bias; c.accumulate = 0; c.relu = relu;
     return run_igemm(ctx, c, x3);
 }
 
@@ -945,7 +955,7 @@ int32_t mtl_conv_dgrad_tc(mtl_ctx* ctx, float* dX, const float* ug, const float*
     c.N = g.N; c.Cin = g.K; c.IH = g.OH; c.IW = g.OW; c.Kout = g.C; c.OH = g.H; c.OW = g.W;
     c.R = g.R; c.S = g.S; c.ph = g.R - 1 - g.ph; c.pw = g.S - 1 - g.pw;
     c.act = ug; c.wt = Wt; c.wK = g.K; c.wC = g.C; c.flip = 1;
-    c.out = dX; c.bias = nullptr; c.accumulate = accumulate;
+    c.out = dX; c.bias = nullptr; c.accumulate = accumulate; c.relu = 0;
     return run_igemm(ctx, c, x3);
 }
 

@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(kBlock) k_pool_fwd_2x2(float* __restrict__ Y, 
 template <bool FROM_IDX, bool ATOMIC>
 __global__ void __launch_bounds__(kBlock) k_pool_bwd(float* __restrict__ dX, const float* __restrict__ ug,
                                                      const float* __restrict__ X, const int32_t* __restrict__ idx,
-                                                     PoolGeom g, int64_t n_out) {
+                                                     const float* __restrict__ relu_of, PoolGeom g, int64_t n_out) {
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     int plane_out = g.OH * g.OW;
@@ -108,8 +108,10 @@ __global__ void __launch_bounds__(kBlock) k_pool_bwd(float* __restrict__ dX, con
         }
         if (bi < 0 || bi >= g.H * g.W) continue;  // no element exceeded -inf: nothing to route
         float* dst = dX + pl * (int64_t)g.H * g.W + bi;
-        if (ATOMIC) atomicAdd(dst, ug[o]);
-        else *dst += ug[o];
+        // fused RELU.backward of the layer below: the selected element is the pooled value itself
+        const float u = relu_of ? (relu_of[o] > 0.0f ? 1.0f : 0.0f) * ug[o] : ug[o];
+        if (ATOMIC) atomicAdd(dst, u);
+        else *dst += u;
     }
 }
 
@@ -118,7 +120,8 @@ __global__ void __launch_bounds__(kBlock) k_pool_bwd(float* __restrict__ dX, con
 template <bool FROM_IDX>
 __global__ void __launch_bounds__(kBlock) k_pool_bwd_2x2(float* __restrict__ dX, const float* __restrict__ ug,
                                                          const float* __restrict__ X, const int32_t* __restrict__ idx,
-                                                         int H, int W, int OH, int OW, int64_t n_pairs, int acc) {
+                                                         const float* __restrict__ relu_of, int H, int W, int OH,
+                                                         int OW, int64_t n_pairs, int acc) {
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     int pairs_per_row = OW >> 1;
@@ -150,6 +153,11 @@ __global__ void __launch_bounds__(kBlock) k_pool_bwd_2x2(float* __restrict__ dX,
             if (b.w > m1) { m1 = b.w; j1 = i00 + W + 3; }
         }
         float2 u = *reinterpret_cast<const float2*>(ug + o);
+        if (relu_of) {
+            const float2 y = *reinterpret_cast<const float2*>(relu_of + o);
+            u.x = (y.x > 0.0f ? 1.0f : 0.0f) * u.x;
+            u.y = (y.y > 0.0f ? 1.0f : 0.0f) * u.y;
+        }
         float4 ra, rb;
         ra.x = j0 == i00 ? u.x : 0.0f;
         ra.y = j0 == i00 + 1 ? u.x : 0.0f;
@@ -168,6 +176,77 @@ __global__ void __launch_bounds__(kBlock) k_pool_bwd_2x2(float* __restrict__ dX,
         }
         *reinterpret_cast<float4*>(d0) = ra;
         *reinterpret_cast<float4*>(d0 + W) = rb;
+    }
+}
+
+// The same 2x2 / stride 2 case for any even W (e.g. 14): one window per thread, float2 rows.
+__global__ void __launch_bounds__(kBlock) k_pool_fwd_2x2_one(float* __restrict__ Y, int32_t* __restrict__ idx,
+                                                             const float* __restrict__ X, int H, int W, int OH, int OW,
+                                                             int64_t n_out) {
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t o = tid; o < n_out; o += stride) {
+        int64_t row = o / OW;  // (plane, oh)
+        int ow = (int)(o - row * OW);
+        int64_t pl = row / OH;
+        int oh = (int)(row - pl * OH);
+        int i00 = (2 * oh) * W + 2 * ow;
+        const float* base = X + pl * (int64_t)H * W + i00;
+        float2 a = *reinterpret_cast<const float2*>(base);
+        float2 b = *reinterpret_cast<const float2*>(base + W);
+        float m = -INFINITY;
+        int j = -1;
+        if (a.x > m) { m = a.x; j = i00; }
+        if (a.y > m) { m = a.y; j = i00 + 1; }
+        if (b.x > m) { m = b.x; j = i00 + W; }
+        if (b.y > m) { m = b.y; j = i00 + W + 1; }
+        Y[o] = m;
+        if (idx) idx[o] = j;
+    }
+}
+
+template <bool FROM_IDX>
+__global__ void __launch_bounds__(kBlock) k_pool_bwd_2x2_one(float* __restrict__ dX, const float* __restrict__ ug,
+                                                             const float* __restrict__ X, const int32_t* __restrict__ idx,
+                                                             const float* __restrict__ relu_of, int H, int W, int OH,
+                                                             int OW, int64_t n_out, int acc) {
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t o = tid; o < n_out; o += stride) {
+        int64_t row = o / OW;
+        int ow = (int)(o - row * OW);
+        int64_t pl = row / OH;
+        int oh = (int)(row - pl * OH);
+        int i00 = (2 * oh) * W + 2 * ow;
+        int j;
+        if (FROM_IDX) {
+            j = idx[o];
+        } else {
+            const float* base = X + pl * (int64_t)H * W + i00;
+            float2 a = *reinterpret_cast<const float2*>(base);
+            float2 b = *reinterpret_cast<const float2*>(base + W);
+            float m = -INFINITY;
+            j = -1;
+            if (a.x > m) { m = a.x; j = i00; }
+            if (a.y > m) { m = a.y; j = i00 + 1; }
+            if (b.x > m) { m = b.x; j = i00 + W; }
+            if (b.y > m) { m = b.y; j = i00 + W + 1; }
+        }
+        float u = ug[o];
+        if (relu_of) u = (relu_of[o] > 0.0f ? 1.0f : 0.0f) * u;
+        float2 ra, rb;
+        ra.x = j == i00 ? u : 0.0f;
+        ra.y = j == i00 + 1 ? u : 0.0f;
+        rb.x = j == i00 + W ? u : 0.0f;
+        rb.y = j == i00 + W + 1 ? u : 0.0f;
+        float* d0 = dX + pl * (int64_t)H * W + i00;
+        if (acc) {
+            float2 oa = *reinterpret_cast<const float2*>(d0);
+            float2 ob = *reinterpret_cast<const float2*>(d0 + W);
+            ra.x += oa.x; ra.y += oa.y; rb.x += ob.x; rb.y += ob.y;
+        }
+        *reinterpret_cast<float2*>(d0) = ra;
+        *reinterpret_cast<float2*>(d0 + W) = rb;
     }
 }
 
@@ -190,7 +269,13 @@ bool is_fast_2x2(const PoolGeom& g, const void* X, const void* Y, const void* au
            (((uintptr_t)aux) & 7u) == 0;
 }
 
-int32_t pool_bwd(mtl_ctx* ctx, float* dX, const float* ug, const float* X, const int32_t* idx,
+bool is_fast_2x2_one(const PoolGeom& g, const void* X) {
+    // full coverage of the input needs even H and W; float2 rows need an 8-byte aligned base
+    return g.R == 2 && g.S == 2 && g.sh == 2 && g.sw == 2 && g.ph == 0 && g.pw == 0 && g.dh == 1 && g.dw == 1 &&
+           (g.W % 2) == 0 && (g.H % 2) == 0 && (((uintptr_t)X) & 7u) == 0;
+}
+
+int32_t pool_bwd(mtl_ctx* ctx, float* dX, const float* ug, const float* X, const int32_t* idx, const float* relu_of,
                  const mtl_conv2d_desc* d, int32_t accumulate) {
     PoolGeom g;
     int32_t rc = make_geom(ctx, d, &g);
@@ -203,9 +288,18 @@ int32_t pool_bwd(mtl_ctx* ctx, float* dX, const float* ug, const float* X, const
         int64_t n_pairs = n_out / 2;
         int grid = mtl_grid_for(n_pairs, kBlock, ctx->sm_count, 8);
         if (idx)
-            k_pool_bwd_2x2<true><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, g.H, g.W, g.OH, g.OW, n_pairs, accumulate ? 1 : 0);
+            k_pool_bwd_2x2<true><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, relu_of, g.H, g.W, g.OH, g.OW, n_pairs, accumulate ? 1 : 0);
         else
-            k_pool_bwd_2x2<false><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, g.H, g.W, g.OH, g.OW, n_pairs, accumulate ? 1 : 0);
+            k_pool_bwd_2x2<false><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, relu_of, g.H, g.W, g.OH, g.OW, n_pairs, accumulate ? 1 : 0);
+        MTL_LAUNCHED(ctx);
+        return MTL_OK;
+    }
+    if (is_fast_2x2_one(g, idx ? (const void*)dX : (const void*)X) && (((uintptr_t)dX) & 7u) == 0) {
+        int grid = mtl_grid_for(n_out, kBlock, ctx->sm_count, 8);
+        if (idx)
+            k_pool_bwd_2x2_one<true><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, relu_of, g.H, g.W, g.OH, g.OW, n_out, accumulate ? 1 : 0);
+        else
+            k_pool_bwd_2x2_one<false><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, relu_of, g.H, g.W, g.OH, g.OW, n_out, accumulate ? 1 : 0);
         MTL_LAUNCHED(ctx);
         return MTL_OK;
     }
@@ -213,11 +307,11 @@ int32_t pool_bwd(mtl_ctx* ctx, float* dX, const float* ug, const float* X, const
     bool overlap = g.sh < (g.R - 1) * g.dh + 1 || g.sw < (g.S - 1) * g.dw + 1;
     int grid = mtl_grid_for(n_out, kBlock, ctx->sm_count, 8);
     if (idx) {
-        if (overlap) k_pool_bwd<true, true><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, g, n_out);
-        else k_pool_bwd<true, false><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, g, n_out);
+        if (overlap) k_pool_bwd<true, true><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, relu_of, g, n_out);
+        else k_pool_bwd<true, false><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, relu_of, g, n_out);
     } else {
-        if (overlap) k_pool_bwd<false, true><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, g, n_out);
-        else k_pool_bwd<false, false><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, g, n_out);
+        if (overlap) k_pool_bwd<false, true><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, relu_of, g, n_out);
+        else k_pool_bwd<false, false><<<grid, kBlock, 0, ctx->stream>>>(dX, ug, X, idx, relu_of, g, n_out);
     }
     MTL_LAUNCHED(ctx);
     return MTL_OK;
@@ -253,6 +347,9 @@ int32_t mtl_maxpool2d_fwd(mtl_ctx* ctx, float* Y, int32_t* idx, const float* X, 
         int64_t n_pairs = n_out / 2;
         int grid = mtl_grid_for(n_pairs, kBlock, ctx->sm_count, 8);
         k_pool_fwd_2x2<<<grid, kBlock, 0, ctx->stream>>>(Y, idx, X, g.H, g.W, g.OH, g.OW, n_pairs);
+    } else if (is_fast_2x2_one(g, X)) {
+        int grid = mtl_grid_for(n_out, kBlock, ctx->sm_count, 8);
+        k_pool_fwd_2x2_one<<<grid, kBlock, 0, ctx->stream>>>(Y, idx, X, g.H, g.W, g.OH, g.OW, n_out);
     } else {
         int grid = mtl_grid_for(n_out, kBlock, ctx->sm_count, 8);
         k_pool_fwd_generic<<<grid, kBlock, 0, ctx->stream>>>(Y, idx, X, g, n_out);
@@ -265,14 +362,23 @@ int32_t mtl_maxpool2d_bwd(mtl_ctx* ctx, float* dX, const float* ug, const float*
                           int32_t accumulate) {
     MTL_CHECK_CTX(ctx);
     MTL_REQUIRE(ctx, X, "null input in mtl_maxpool2d_bwd");
-    return pool_bwd(ctx, dX, ug, X, nullptr, d, accumulate);
+    return pool_bwd(ctx, dX, ug, X, nullptr, nullptr, d, accumulate);
 }
 
 int32_t mtl_maxpool2d_bwd_idx(mtl_ctx* ctx, float* dX, const float* ug, const int32_t* idx,
                               const mtl_conv2d_desc* d, int32_t accumulate) {
     MTL_CHECK_CTX(ctx);
     MTL_REQUIRE(ctx, idx, "null indices in mtl_maxpool2d_bwd_idx");
-    return pool_bwd(ctx, dX, ug, nullptr, idx, d, accumulate);
+    return pool_bwd(ctx, dX, ug, nullptr, idx, nullptr, d, accumulate);
+}
+
+int32_t mtl_maxpool2d_bwd_idx_act(mtl_ctx* ctx, float* dX, const float* ug, const int32_t* idx, const float* pooled,
+                                  const mtl_conv2d_desc* d, int32_t act_op, int32_t accumulate) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, idx, "null indices in mtl_maxpool2d_bwd_idx_act");
+    MTL_REQUIRE(ctx, act_op == MTL_OP_RELU || act_op < 0, "mtl_maxpool2d_bwd_idx_act fuses RELU only (act_op %d)", act_op);
+    MTL_REQUIRE(ctx, act_op < 0 || pooled, "the fused RELU gradient needs the pooled output");
+    return pool_bwd(ctx, dX, ug, nullptr, idx, act_op == MTL_OP_RELU ? pooled : nullptr, d, accumulate);
 }
 
 }  // extern "C"

@@ -275,6 +275,9 @@ MTLH_API int32_t mtlh_model_get_grad(void* m, int32_t id, float* host_out) {
 MTLH_API int32_t mtlh_model_set_overwrite_first(void* m, int32_t on) {
     return guard([&] { static_cast<Model*>(m)->set_overwrite_first(on != 0); });
 }
+MTLH_API int32_t mtlh_model_set_fusion(void* m, int32_t on) {
+    return guard([&] { static_cast<Model*>(m)->set_fusion(on != 0); });
+}
 MTLH_API int64_t mtlh_model_n_trainable(void* m) { return static_cast<Model*>(m)->n_trainable(); }
 MTLH_API int32_t mtlh_model_n_inference_nodes(void* m) { return static_cast<Model*>(m)->n_inference_nodes(); }
 // Symbol ids and flat offsets of the trainable parameters, in optimizer order.

@@ -299,7 +299,54 @@ void Model::inference(const std::vector<const float*>& in, const std::vector<flo
 }
 
 void Model::execute(int num_nodes) {
-    for (int i = 0; i < num_nodes; ++i) forward_op(g_.nodes[i]);
+    for (int i = 0; i < num_nodes; ++i) {
+        if (fusion_ && fwd_skip_[i]) continue;  // computed by the CONV2D that feeds it
+        forward_op(g_.nodes[i]);
+    }
+}
+
+void Model::set_fusion(bool on) {
+    const int nn = (int)g_.nodes.size();
+    fusion_ = on;
+    fwd_relu_of_.assign(nn, -1);
+    bwd_relu_of_.assign(nn, -1);
+    fwd_skip_.assign(nn, 0);
+    bwd_skip_.assign(nn, 0);
+    relu_in_absent_.assign(nn, 0);
+    if (!on) return;
+    std::map<int, int> uses, producer;
+    for (int i = 0; i < nn; ++i) {
+        for (auto& s : g_.nodes[i].inputs) uses[s.id]++;
+        for (auto& s : g_.nodes[i].outputs) producer[s.id] = i;
+    }
+    auto visible = [&](const Symbol& s) {  // a tensor the user can ask for by name
+        for (auto& o : g_.outputs) if (o.id == s.id) return true;
+        return g_.loss_out && g_.loss_out->id == s.id;
+    };
+    for (int j = 0; j < nn; ++j) {
+        const Node& r = g_.nodes[j];
+        if (r.op != MTL_OP_RELU) continue;
+        const Symbol& rin = r.inputs[0];
+        const Symbol& rout = r.outputs[0];
+        const bool only_reader = uses[rin.id] == 1 && !visible(rin);
+        auto p = producer.find(rin.id);
+        if (only_reader && p != producer.end() && g_.nodes[p->second].op == MTL_OP_CONV2D && ((p->second < n_inference_nodes_) == (j < n_inference_nodes_) || n_inference_nodes_ == 0)) {
+            fwd_relu_of_[p->second] = j;
+            fwd_skip_[j] = 1;
+            relu_in_absent_[j] = 1;
+        }
+        // backward: the single consumer of the RELU output is a MAXPOOL2D, and the RELU is the single
+        // writer of its input's gradient (so the order of accumulation cannot change)
+        if (uses[rout.id] == 1 && !visible(rout) && only_reader && rin.trainable) {
+            for (int k = j + 1; k < nn; ++k) {
+                const Node& q = g_.nodes[k];
+                if (q.op == MTL_OP_MAXPOOL2D && q.inputs[0].id == rout.id) {
+                    bwd_relu_of_[k] = j;
+                    bwd_skip_[j] = 1;
+                }
+            }
+        }
+    }
 }
 
 static mtl_conv2d_desc conv_desc(const TensorShape& in, int K, int R, int S, const Attributes& a) {
@@ -354,7 +401,12 @@ void Model::forward_op(const Node& n) {
         case MTL_OP_CONV2D: {
             const Symbol& w = n.inputs[1];
             mtl_conv2d_desc d = conv_desc(t1.shape, (int)w.shape[0], (int)w.shape[2], (int)w.shape[3], n.attrs);
-            check(mtl_conv2d_fwd(ctx_, T(out), T(t1), T(w), T(n.inputs[2]), &d), "CONV2D forward");
+            const int self = (int)(&n - &g_.nodes[0]);
+            if (fusion_ && fwd_relu_of_[self] >= 0)
+                check(mtl_conv2d_fwd_act(ctx_, T(g_.nodes[fwd_relu_of_[self]].outputs[0]), T(t1), T(w), T(n.inputs[2]), &d,
+                                         MTL_OP_RELU), "CONV2D+RELU forward");
+            else
+                check(mtl_conv2d_fwd(ctx_, T(out), T(t1), T(w), T(n.inputs[2]), &d), "CONV2D forward");
             break;
         }
         case MTL_OP_MAXPOOL2D: {
@@ -399,7 +451,10 @@ void Model::backward_op(const Node& n, int tensor_id) {
         case MTL_OP_EXP: case MTL_OP_LOG: case MTL_OP_SIGMOID: case MTL_OP_RELU: case MTL_OP_LEAKYRELU:
         case MTL_OP_TANH: case MTL_OP_CLIP:
             unary_params(n, scalar_values_, &p0, &p1);
-            check(mtl_unary_bwd(ctx_, n.op, grad, ug, T(t1), t1.shape.num_elements(), p0, p1, acc), "unary backward");
+            // a RELU whose input was never written (fused into its CONV2D): out > 0 exactly where in > 0
+            check(mtl_unary_bwd(ctx_, n.op, grad, ug,
+                                (fusion_ && n.op == MTL_OP_RELU && relu_in_absent_[(int)(&n - &g_.nodes[0])]) ? T(out) : T(t1),
+                                t1.shape.num_elements(), p0, p1, acc), "unary backward");
             break;
         case MTL_OP_DOT:
             check(mtl_dot_bwd(ctx_, tensor_id, grad, ug, T(t1), T(n.inputs[1]), t1.shape[0], t1.shape[1],
@@ -423,7 +478,15 @@ void Model::backward_op(const Node& n, int tensor_id) {
             int node_index = (int)(&n - &g_.nodes[0]);
             // the indices stored by this step's forward pass select the same elements the
             // reference finds by re-scanning the input (pool.mojo:123-163)
-            check(mtl_maxpool2d_bwd_idx(ctx_, grad, ug, pool_idx_.at(node_index), &d, acc), "MAXPOOL2D backward");
+            if (fusion_ && bwd_relu_of_[node_index] >= 0) {
+                // acc was taken for the RELU output's gradient, which is not written: release it
+                grad_written_[tj.id] = false;
+                const Symbol& rin = g_.nodes[bwd_relu_of_[node_index]].inputs[0];
+                check(mtl_maxpool2d_bwd_idx_act(ctx_, G(rin), ug, pool_idx_.at(node_index), T(out), &d, MTL_OP_RELU,
+                                                acc_flag(rin)), "MAXPOOL2D+RELU backward");
+            } else {
+                check(mtl_maxpool2d_bwd_idx(ctx_, grad, ug, pool_idx_.at(node_index), &d, acc), "MAXPOOL2D backward");
+            }
             break;
         }
         case MTL_OP_FMA:
@@ -442,8 +505,9 @@ void Model::backward_enqueue() {
     grad_written_[g_.loss_out->id] = true;
     for (int i = (int)g_.nodes.size() - 1; i >= 0; --i) {
         const Node& n = g_.nodes[i];
-        for (int j = 0; j < (int)n.inputs.size(); ++j)
-            if (n.inputs[j].trainable) backward_op(n, j);
+        if (!(fusion_ && bwd_skip_[i]))  // else: done by the MAXPOOL2D that consumes this RELU
+            for (int j = 0; j < (int)n.inputs.size(); ++j)
+                if (n.inputs[j].trainable) backward_op(n, j);
         if (after_backward_node) after_backward_node(after_backward_user, i);
     }
 }

@@ -57,6 +57,15 @@ class Model {
     // Off: every contribution accumulates, exactly like backward_op (ops.mojo:405,463,498).
     void set_overwrite_first(bool on) { overwrite_first_ = on; }
 
+    // Chain fusion (off by default).  On: a CONV2D whose only consumer is a RELU writes the RELU's
+    // output directly (mtl_conv2d_fwd_act) and the RELU node is not run; a MAXPOOL2D fed by a RELU
+    // that nothing else reads performs that RELU's backward as well (mtl_maxpool2d_bwd_idx_act).
+    // Every tensor that IS written holds exactly the bits the unfused run writes; what is never
+    // written is the CONV2D output (pre-activation) and the gradient of the RELU output.  Symbols
+    // that are graph outputs or have other consumers are never fused away.
+    void set_fusion(bool on);
+    bool fusion() const { return fusion_; }
+
     // flat trainable spans (device pointers) for the optimizer and the gradient exchange
     float* params_flat() const { return tensors_; }
     float* grads_flat() const { return grads_; }
@@ -96,6 +105,12 @@ class Model {
     std::vector<int> never_written_;           // trainable symbols no backward node writes
     bool overwrite_first_ = true;
     int n_inference_nodes_ = 0;
+    bool fusion_ = false;
+    std::vector<int> fwd_relu_of_;     // per node: the RELU node a CONV2D also computes, or -1
+    std::vector<char> fwd_skip_;       // RELU nodes computed by their producer
+    std::vector<int> bwd_relu_of_;     // per node: the RELU node whose backward a MAXPOOL2D also performs, or -1
+    std::vector<char> bwd_skip_;       // RELU nodes whose backward their consumer performs
+    std::vector<char> relu_in_absent_; // RELU nodes whose input tensor is not written (use the output as mask)
 };
 
 class Adam {

@@ -279,6 +279,11 @@ class Model:
     def set_overwrite_first(self, on: bool):
         _ck(self.lib.mtlh_model_set_overwrite_first(self.handle, int(on)))
 
+    def set_fusion(self, on: bool):
+        """CONV2D+RELU forward and MAXPOOL2D+RELU backward as single launches; the CONV2D output and the
+        gradient of the RELU output are then never written (every other tensor is bit-identical)."""
+        _ck(self.lib.mtlh_model_set_fusion(self.handle, int(on)))
+
     def n_trainable(self) -> int:
         return int(self.lib.mtlh_model_n_trainable(self.handle))
 
@@ -313,9 +318,13 @@ class Adam:
 class Trainer:
     """forward / zero_grad / backward / step as one enqueued (optionally captured) step."""
 
-    def __init__(self, model: Model, adam: Adam, use_graph: bool = True, bucket_bytes: int = 256 * 1024):
+    def __init__(self, model: Model, adam: Adam, use_graph: bool = True, bucket_bytes: int = 256 * 1024,
+                 fuse: bool = True):
         self.lib = _lib.host_lib()
         self.model, self.adam = model, adam
+        # the training pipeline never reads per-node tensors, so CONV2D+RELU / MAXPOOL2D+RELU chains
+        # run fused by default (see Model.set_fusion for what is then left unwritten)
+        model.set_fusion(fuse)
         h = C.c_void_p()
         _ck(self.lib.mtlh_trainer_create(model.handle, adam.handle, int(use_graph), C.c_int64(bucket_bytes),
                                          C.byref(h)))

@@ -151,7 +151,10 @@ class Context:
             self._check(L.mtl_copy_f32(h, res.ptr, t1.ptr, t1.size, 0))
         elif op == OP.CONV2D:
             d = _conv_desc_from(t1.shape, t2.shape, attrs)
-            self._check(L.mtl_conv2d_fwd(h, res.ptr, t1.ptr, t2.ptr, t3.ptr, C.byref(d)))
+            if attrs.get("fused_act") is not None:  # CONV2D followed by RELU in one launch
+                self._check(L.mtl_conv2d_fwd_act(h, res.ptr, t1.ptr, t2.ptr, t3.ptr, C.byref(d), int(attrs["fused_act"])))
+            else:
+                self._check(L.mtl_conv2d_fwd(h, res.ptr, t1.ptr, t2.ptr, t3.ptr, C.byref(d)))
         elif op == OP.MAXPOOL2D:
             d = _pool_desc_from(t1.shape, attrs)
             idx = attrs.get("indices")
@@ -188,7 +191,11 @@ class Context:
         elif op == OP.MAXPOOL2D:
             d = _pool_desc_from(t1.shape, attrs)
             idx = attrs.get("indices")
-            if idx is not None:
+            if idx is not None and attrs.get("fused_act") is not None:
+                # MAXPOOL2D.backward followed by the backward of the RELU that fed the pooling
+                self._check(L.mtl_maxpool2d_bwd_idx_act(h, grad.ptr, ug.ptr, idx.ptr, attrs["pooled"].ptr, C.byref(d),
+                                                        int(attrs["fused_act"]), acc))
+            elif idx is not None:
                 self._check(L.mtl_maxpool2d_bwd_idx(h, grad.ptr, ug.ptr, idx.ptr, C.byref(d), acc))
             else:
                 self._check(L.mtl_maxpool2d_bwd(h, grad.ptr, ug.ptr, t1.ptr, C.byref(d), acc))

@@ -160,3 +160,32 @@ def test_trainer_graph_replay_equals_eager(ctx):
     for i in range(6):
         want.append(om.forward(xs[i], ys[i])); oad.zero_grad(); om.backward(); oad.step()
     assert_close(np.array(losses[False]), np.array(want, np.float32), 1e-3, 1e-6, "trainer vs oracle loop")
+
+
+@pytest.mark.parametrize("strict", (False, True))
+def test_chain_fusion_is_bit_identical(ctx, strict):
+    """CONV2D+RELU forward and MAXPOOL2D+RELU backward as single launches (Model.set_fusion): loss
+    trajectory, every parameter gradient and the final parameters equal the unfused run bit for bit;
+    only the CONV2D outputs and the gradients of the RELU outputs are left unwritten."""
+    B = 8
+    build = lambda ns, gg: build_cnn(ns, gg, B, 64, 128)
+    rng = np.random.default_rng(21)
+    x = rng.uniform(0, 1, (B, 1, 28, 28)).astype(np.float32)
+    y = np.eye(10, dtype=np.float32)[rng.integers(0, 10, B)]
+    runs = []
+    for fuse in (False, True):
+        (g, m), _ = make_pair(ctx, build, seed=20)
+        m.set_overwrite_first(not strict)
+        m.set_fusion(fuse)
+        adam = host_api.Adam(m, lr=1e-3)
+        losses = _train(m, adam, (x, y), 6)
+        m.forward(x, y); m.zero_grads(); m.backward()
+        grads = [m.grad(s) for s in g.params() if s.trainable]
+        params = [m.tensor(s) for s in g.params() if s.trainable]
+        logits = m.tensor(host_api.Symbol(g, g.node(8)["output"]))
+        runs.append((losses, grads, params, logits))
+    a, b = runs
+    assert np.array_equal(np.asarray(a[0]), np.asarray(b[0]))
+    for u, v in zip(a[1] + a[2] + [a[3]], b[1] + b[2] + [b[3]]):
+        assert np.array_equal(u, v)
+    assert ctx.device_status() == 0

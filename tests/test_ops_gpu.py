@@ -353,6 +353,70 @@ def test_conv_first_layer(ctx, case):
     assert rel_err(acc, (init + want[2]).astype(np.float64)) < 1e-5
 
 
+FUSED_CONV = [  # channel-major TC, pixel-major TC, first-layer rows kernel, generic CUDA-core kernel
+    (6, 64, 14, 14, 128, 5, 5, 2), (5, 16, 14, 14, 32, 5, 5, 2), (70, 1, 28, 28, 64, 5, 5, 2), (3, 2, 9, 11, 5, 3, 3, 1),
+]
+
+
+@pytest.mark.parametrize("case", FUSED_CONV)
+def test_conv_with_fused_relu_equals_two_calls(ctx, case):
+    """mtl_conv2d_fwd_act == RELU.forward(CONV2D.forward(...)), bit for bit, on every kernel path."""
+    N, C, H, W, K, R, S, p = case
+    rng = np.random.default_rng(sum(case) + 1)
+    x = ctx.array(rng.normal(0, 1, (N, C, H, W)).astype(np.float32))
+    w = ctx.array((rng.normal(0, 1, (K, C, R, S)) / np.sqrt(C * R * S)).astype(np.float32))
+    b = ctx.array(rng.normal(0, 1, K).astype(np.float32))
+    kw = dict(padding=(p, p), stride=(1, 1), dilation=(1, 1))
+    oh, ow = mb.conv2d_out_shape((N, C, H, W), (K, C, R, S), **kw)
+    for mode in (mb.MATH_TF32X3, mb.MATH_TF32, mb.MATH_FP32):
+        ctx.set_math_mode(mode)
+        try:
+            y = ctx.empty((N, K, oh, ow)); z = ctx.empty((N, K, oh, ow)); f = ctx.empty((N, K, oh, ow))
+            ctx.forward_op(OP.CONV2D, y, x, w, b, **kw)
+            ctx.forward_op(OP.RELU, z, y)
+            ctx.forward_op(OP.CONV2D, f, x, w, b, fused_act=OP.RELU, **kw)
+        finally:
+            ctx.set_math_mode(mb.MATH_TF32X3)
+        assert np.array_equal(f.numpy(), z.numpy()), "mode %d" % mode
+        assert (z.numpy() == 0).any() and (z.numpy() > 0).any()
+
+
+FUSED_POOL = [  # (N, C, H, W, kernel, stride, pad): two-window float4, one-window float2, generic, overlapping
+    (3, 4, 8, 8, 2, 2, 0), (3, 5, 14, 14, 2, 2, 0), (2, 3, 9, 9, 3, 2, 1), (2, 3, 8, 8, 3, 1, 1),
+]
+
+
+@pytest.mark.parametrize("case", FUSED_POOL)
+def test_pool_backward_with_fused_relu_equals_two_calls(ctx, case):
+    """mtl_maxpool2d_bwd_idx_act == RELU.backward(MAXPOOL2D.backward(...)) where the RELU feeds the pooling."""
+    N, Cc, H, W, k, s, p = case
+    rng = np.random.default_rng(sum(case) + 2)
+    pre = rng.normal(0, 1, (N, Cc, H, W)).astype(np.float32)
+    pre[0, 0, :4, :4] = -1.0                     # whole windows below zero: RELU output 0, mask 0
+    kw = dict(kernel_size=(k, k), stride=(s, s), padding=(p, p), dilation=(1, 1))
+    pre_d = ctx.array(pre)
+    act = ctx.empty(pre.shape)
+    ctx.forward_op(OP.RELU, act, pre_d)
+    oh, ow = mb.conv2d_out_shape(pre.shape, (1, Cc, k, k), padding=(p, p), stride=(s, s))
+    pooled, idx = ctx.empty((N, Cc, oh, ow)), ctx.empty((N, Cc, oh, ow), np.int32)
+    ctx.forward_op(OP.MAXPOOL2D, pooled, act, indices=idx, **kw)
+    ug = ctx.array(rng.normal(0, 1, (N, Cc, oh, ow)).astype(np.float32))
+    for accumulate in (False, True):
+        init = rng.normal(0, 1, pre.shape).astype(np.float32)
+        # two calls: gradient of the RELU output, then of its input
+        g_act = ctx.empty(pre.shape)
+        ctx.backward_op(0, OP.MAXPOOL2D, ug, act, grad=g_act, accumulate=False, indices=idx, **kw)
+        two = ctx.array(init)
+        ctx.backward_op(0, OP.RELU, g_act, pre_d, grad=two, accumulate=accumulate)
+        one = ctx.array(init)
+        ctx.backward_op(0, OP.MAXPOOL2D, ug, act, grad=one, accumulate=accumulate, indices=idx, pooled=pooled,
+                        fused_act=OP.RELU, **kw)
+        if s >= k:
+            assert np.array_equal(one.numpy(), two.numpy()), "accumulate=%s" % accumulate
+        else:  # overlapping windows add with atomics: the order of the sum is not fixed
+            assert_close(one.numpy(), two.numpy(), 1e-6, 1e-6, "accumulate=%s" % accumulate)
+
+
 # ------------------------------------------------------------------ MAXPOOL2D ------------------
 
 def test_maxpool_reference_cases(ctx):
