@@ -388,7 +388,9 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
+        // two producer lanes: issuing a TMA copy occupies its thread for a few hundred cycles, so the
+        // weight box (lane 0) and the pixel box (lane 1) of a stage are issued side by side
+        if (lane < 2) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -407,17 +409,19 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                     for (int r = 0; r < p.R && ok; ++r)
                         for (int s = 0; s < p.S && ok; ++s)
                             for (int cb = 0; cb < cblocks; ++cb) {
-                                if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
+                                if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) ok = false;
+                                if (__any_sync(0x3u, !ok)) { ok = false; break; }
                                 uint8_t* sa = tiles + stage * kTStageBytes;
                                 uint8_t* sb = sa + kTABytes;
-                                mbar_arrive_expect_tx(&full[stage], tx);
-                                tma_load_3d(sa, mw, &full[stage], cb * BK, kt * BM, r * p.S + s);
-                                tma_load_4d(sb, mx, &full[stage], cb * BK, ow0 + s - p.pw, oh0 + r - p.ph, n0);
+                                if (lane == 0) mbar_arrive_expect_tx(&full[stage], tx);
+                                __syncwarp(0x3u);
+                                if (lane == 0) tma_load_3d(sa, mw, &full[stage], cb * BK, kt * BM, r * p.S + s);
+                                else tma_load_4d(sb, mx, &full[stage], cb * BK, ow0 + s - p.pw, oh0 + r - p.ph, n0);
                                 if (++stage == kTStages) { stage = 0; phase ^= 1u; }
                             }
                 }
             }
-            if (!ok) atomicExch(p.status, MTL_ERR_TIMEOUT);
+            if (!ok && lane == 0) atomicExch(p.status, MTL_ERR_TIMEOUT);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -789,36 +793,41 @@ k_conv_wgrad_tc(const __grid_constant__ CUtensorMap mapU0, const __grid_constant
     const uint32_t tx_bytes = a_bytes + (uint32_t)(ntaps * cchunks) * 4096u;
 
     if (warp == 0) {
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int kb = 0; kb < kb_total && ok; ++kb) {
-                if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
-                const int seg = kb / n_chunks;
-                int pc = chunk_begin + (kb - seg * n_chunks);
-                const int tw = pc % p.tiles_w;
-                pc /= p.tiles_w;
-                const int th = pc % p.tiles_h;
-                const int tnb = pc / p.tiles_h;
-                const int ow0 = tw * p.bw, oh0 = th * p.bh, n0 = tnb * p.bn;
-                const CUtensorMap* mu = p.segA[seg] ? &mapU1 : &mapU0;
-                const CUtensorMap* mx = p.segB[seg] ? &mapX1 : &mapX0;
-                uint8_t* sa = tiles + stage * p.stage_bytes;
-                uint8_t* sb = sa + a_bytes;
-                mbar_arrive_expect_tx(&full[stage], tx_bytes);
-                // one 5-D box per operand tile: {32 channels, bw, bh, bn pixels, channel chunks}; TMA
-                // instructions are costly to issue, so fewer and larger ones keep the ring full
+        // The whole warp produces: issuing a TMA copy costs its thread a few hundred cycles, so the
+        // operand boxes of one stage are issued by different lanes at once (lane 0: the ug tile and
+        // the byte count, lane 1 + t: the input box of tap t).
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int kb = 0; kb < kb_total; ++kb) {
+            if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) ok = false;
+            if (__any_sync(0xffffffffu, !ok)) { ok = false; break; }
+            const int seg = kb / n_chunks;
+            int pc = chunk_begin + (kb - seg * n_chunks);
+            const int tw = pc % p.tiles_w;
+            pc /= p.tiles_w;
+            const int th = pc % p.tiles_h;
+            const int tnb = pc / p.tiles_h;
+            const int ow0 = tw * p.bw, oh0 = th * p.bh, n0 = tnb * p.bn;
+            const CUtensorMap* mu = p.segA[seg] ? &mapU1 : &mapU0;
+            const CUtensorMap* mx = p.segB[seg] ? &mapX1 : &mapX0;
+            uint8_t* sa = tiles + stage * p.stage_bytes;
+            uint8_t* sb = sa + a_bytes;
+            if (lane == 0) mbar_arrive_expect_tx(&full[stage], tx_bytes);
+            __syncwarp();
+            // one 5-D box per operand tile {32 channels, bw, bh, bn pixels, channel chunks}: the TMA
+            // unit spends about 35 ns per box besides about 1 ns per 128-byte row, so boxes stay large
+            if (lane == 0) {
                 tma_load_5d(sa, mu, &full[stage], 0, ow0, oh0, n0, kt * (BM / 32));
-                for (int t = 0; t < ntaps; ++t) {
-                    const int rs = tap0 + t;
-                    const int r = rs / p.S, s = rs - r * p.S;
-                    tma_load_5d(sb + t * cchunks * 4096, mx, &full[stage], 0, ow0 + s - p.pw, oh0 + r - p.ph, n0, 0);
-                }
-                if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+            } else if (lane <= ntaps) {
+                const int t = lane - 1;
+                const int rs = tap0 + t;
+                const int r = rs / p.S, s = rs - r * p.S;
+                tma_load_5d(sb + t * cchunks * 4096, mx, &full[stage], 0, ow0 + s - p.pw, oh0 + r - p.ph, n0, 0);
             }
-            if (!ok) atomicExch(p.status, MTL_ERR_TIMEOUT);
+            if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
+        if (!ok && lane == 0) atomicExch(p.status, MTL_ERR_TIMEOUT);
     } else if (warp == 1) {
         if (lane == 0) {
             // taps are multiplied in groups of up to 256 / C so that one instruction covers several
