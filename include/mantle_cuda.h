@@ -181,6 +181,14 @@ MTL_API int32_t mtl_maxpool2d_bwd_idx(mtl_ctx* ctx, float* dX, const float* ug,
  *                              the RELU's INPUT and `pooled` the pooling output of the forward pass: the
  *                              element a window selected is the pooled value itself, so (pooled > 0) is
  *                              the RELU mask of the only element that receives a gradient. */
+/*   mtl_conv2d_bwd_fused       CONV2D.backward for several operands in one call (conv.mojo:229-425): any of
+ *                              dX, dW, db may be null (not wanted); each has its own accumulate flag.  The
+ *                              gradients equal those of separate mtl_conv2d_bwd calls (db up to the order
+ *                              of its sum); ug is re-laid out once and the bias gradient is read off
+ *                              that pass. */
+MTL_API int32_t mtl_conv2d_bwd_fused(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug,
+                                     const float* X, const float* Wt, const mtl_conv2d_desc* d,
+                                     int32_t acc_dx, int32_t acc_dw, int32_t acc_db);
 MTL_API int32_t mtl_conv2d_fwd_act(mtl_ctx* ctx, float* Y, const float* X, const float* Wt,
                                    const float* bias, const mtl_conv2d_desc* d, int32_t act_op);
 MTL_API int32_t mtl_maxpool2d_bwd_idx_act(mtl_ctx* ctx, float* dX, const float* ug,

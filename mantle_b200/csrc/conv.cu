@@ -70,4 +70,29 @@ int32_t mtl_conv2d_bwd(mtl_ctx* ctx, int32_t tensor_id, float* grad, const float
     return mtl_conv_bgrad(ctx, grad, ug, g, accumulate);
 }
 
+int32_t mtl_conv2d_bwd_fused(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* X,
+                             const float* Wt, const mtl_conv2d_desc* d, int32_t acc_dx, int32_t acc_dw, int32_t acc_db) {
+    MTL_CHECK_CTX(ctx);
+    ConvGeom g;
+    int32_t rc = make_geom(ctx, d, &g);
+    if (rc) return rc;
+    MTL_REQUIRE(ctx, ug && (dX || dW || db), "null pointer in mtl_conv2d_bwd_fused");
+    MTL_REQUIRE(ctx, (!dX || Wt) && (!dW || X), "operand needed by a requested gradient is null");
+    const bool tc = ctx->math_mode != MTL_MATH_FP32;
+    const int x3 = ctx->math_mode == MTL_MATH_TF32X3;
+    if (tc && dX && dW && mtl_conv_dgrad_tc_supported(g, ug, Wt, dX) && mtl_conv_wgrad_tc_supported(g, ug, X, dW))
+        return mtl_conv_bwd_fused_tc(ctx, dX, dW, db, ug, X, Wt, g, acc_dx, acc_dw, acc_db, x3);
+    if (dW && db && !(tc && mtl_conv_wgrad_tc_supported(g, ug, X, dW)) && mtl_conv_wgrad_rows_supported(g, ug)) {
+        rc = mtl_conv_wgrad_bias_rows(ctx, dW, db, ug, X, g, acc_dw, acc_db);
+        if (rc) return rc;
+        dW = nullptr;
+        db = nullptr;
+    }
+    // whatever is left: one reference-shaped call per operand
+    if (dX && (rc = mtl_conv2d_bwd(ctx, 0, dX, ug, X, Wt, d, acc_dx))) return rc;
+    if (dW && (rc = mtl_conv2d_bwd(ctx, 1, dW, ug, X, Wt, d, acc_dw))) return rc;
+    if (db && (rc = mtl_conv2d_bwd(ctx, 2, db, ug, X, Wt, d, acc_db))) return rc;
+    return MTL_OK;
+}
+
 }  // extern "C"

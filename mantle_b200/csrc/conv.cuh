@@ -33,3 +33,10 @@ int32_t mtl_conv_dgrad_tc(mtl_ctx* ctx, float* dX, const float* ug, const float*
                           int accumulate, int x3);
 int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,
                           int accumulate, int x3);
+// dX, dW and optionally db (may be null) from one channels-last copy of ug.
+int32_t mtl_conv_bwd_fused_tc(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* X,
+                              const float* Wt, const ConvGeom& g, int acc_dx, int acc_dw, int acc_db, int x3);
+// Row-streaming first-layer kernel: dW and db in one pass over ug; false when the geometry does not qualify.
+bool mtl_conv_wgrad_rows_supported(const ConvGeom& g, const float* ug);
+int32_t mtl_conv_wgrad_bias_rows(mtl_ctx* ctx, float* dW, float* db, const float* ug, const float* X, const ConvGeom& g,
+                                 int acc_dw, int acc_db);

@@ -369,7 +369,8 @@ template <int R, int S, int OW, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 3) k_conv_wgrad_rows(float* __restrict__ partial,
                                                                 const float* __restrict__ ug,
                                                                 const float* __restrict__ X, ConvGeom g,
-                                                                int n_per_split, int ustride) {
+                                                                int n_per_split, int ustride,
+                                                                float* __restrict__ bias_partial) {
     constexpr int PW = 32, RS = R * S, NT = WARPS * 32;
     extern __shared__ __align__(16) float rows_smem[];
     const int PH = g.OH + R - 1;
@@ -418,6 +419,7 @@ __global__ void __launch_bounds__(WARPS * 32, 3) k_conv_wgrad_rows(float* __rest
     float acc[RS];
 #pragma unroll
     for (int t = 0; t < RS; ++t) acc[t] = 0.0f;
+    float bsum = 0.0f;  // sum of this lane's channel over the rows this warp sees (bias gradient)
 
     if (steps > 0) issue(0);
     for (int step = 0; step < steps; ++step) {
@@ -438,6 +440,7 @@ __global__ void __launch_bounds__(WARPS * 32, 3) k_conv_wgrad_rows(float* __rest
             for (int i = 0; i < OW / 4; ++i) {
                 const float4 q = *reinterpret_cast<const float4*>(ub + 4 * i);
                 u[4 * i] = q.x; u[4 * i + 1] = q.y; u[4 * i + 2] = q.z; u[4 * i + 3] = q.w;
+                bsum += (q.x + q.y) + (q.z + q.w);
             }
 #pragma unroll
             for (int r = 0; r < R; ++r) {
@@ -467,6 +470,17 @@ __global__ void __launch_bounds__(WARPS * 32, 3) k_conv_wgrad_rows(float* __rest
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) v += red[w * 32 * RS + i];
         partial[((int64_t)blockIdx.y * g.K * g.C + (int64_t)(k0 + kk) * g.C + c) * RS + t] = v;
+    }
+    if (bias_partial && c == 0) {  // every input channel sees the same ug: one of them reports
+        __syncthreads();
+        red[warp * 32 + lane] = bsum;
+        __syncthreads();
+        if (threadIdx.x < 32 && k0 + threadIdx.x < g.K) {
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) v += red[w * 32 + threadIdx.x];
+            bias_partial[(int64_t)blockIdx.y * g.K + k0 + threadIdx.x] = v;
+        }
     }
 }
 
@@ -626,6 +640,50 @@ static int pick_nsplit(const mtl_ctx* ctx, int blocks_x, int N) {
     return want;
 }
 
+// row-streaming variant: few input channels, 28-pixel rows, 'same'-style geometry
+bool mtl_conv_wgrad_rows_supported(const ConvGeom& g, const float* ug) {
+    return g.C <= 4 && g.K >= 16 && g.OW == 28 && g.OH % 7 == 0 && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1 &&
+           ((g.R == 5 && g.S == 5) || (g.R == 3 && g.S == 3)) && g.W + 2 * g.pw == g.OW + g.S - 1 &&
+           g.H + 2 * g.ph == g.OH + g.R - 1 && ((reinterpret_cast<uintptr_t>(ug) & 15) == 0) && g.N >= 64;
+}
+
+int32_t mtl_conv_wgrad_bias_rows(mtl_ctx* ctx, float* dW, float* db, const float* ug, const float* X, const ConvGeom& g,
+                                 int acc_dw, int acc_db) {
+    constexpr int WARPS = 7, OWc = 28;
+    const int kc = g.K * g.C;
+    const int taps = g.R * g.S;
+    const int kgroups = (g.K + 31) / 32;
+    int ustride = WARPS * OWc;
+    while ((ustride / 4) % 2 == 0) ustride += 4;     // odd multiple of 4 floats
+    const int PH = g.OH + g.R - 1;
+    size_t smem = (size_t)(2 * PH * 32 + 2 * 32 * ustride) * 4;
+    size_t red_bytes = (size_t)WARPS * 32 * taps * 4;
+    if (red_bytes > (size_t)2 * 32 * ustride * 4) smem += red_bytes - (size_t)2 * 32 * ustride * 4;
+    int ns = (ctx->sm_count * 3 + kgroups * g.C - 1) / (kgroups * g.C);
+    if (ns > g.N / 4) ns = g.N / 4;
+    if (ns < 1) ns = 1;
+    int nps = (g.N + ns - 1) / ns;
+    ns = (g.N + nps - 1) / nps;
+    MTL_REQUIRE(ctx, ns <= 65535, "too many batch splits");
+    void* ws2;
+    int32_t rc2 = mtl_workspace(ctx, ((size_t)ns * kc * taps + (size_t)ns * g.K) * 4, &ws2);
+    if (rc2) return rc2;
+    float* part = (float*)ws2;
+    float* bpart = db ? part + (size_t)ns * kc * taps : nullptr;
+    dim3 rgrid((unsigned)(kgroups * g.C), (unsigned)ns);
+    if (g.R == 5) {
+        MTL_CUDA(ctx, cudaFuncSetAttribute(k_conv_wgrad_rows<5, 5, OWc, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_conv_wgrad_rows<5, 5, OWc, WARPS><<<rgrid, WARPS * 32, smem, ctx->stream>>>(part, ug, X, g, nps, ustride, bpart);
+    } else {
+        MTL_CUDA(ctx, cudaFuncSetAttribute(k_conv_wgrad_rows<3, 3, OWc, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_conv_wgrad_rows<3, 3, OWc, WARPS><<<rgrid, WARPS * 32, smem, ctx->stream>>>(part, ug, X, g, nps, ustride, bpart);
+    }
+    MTL_LAUNCHED(ctx);
+    int32_t rc = mtl_sum_partials(ctx, dW, part, (int64_t)kc * taps, ns, acc_dw);
+    if (rc || !db) return rc;
+    return mtl_sum_partials(ctx, db, bpart, g.K, ns, acc_db);
+}
+
 int32_t mtl_conv_wgrad_simt(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,
                             int accumulate) {
     const int kc = g.K * g.C;
@@ -642,40 +700,7 @@ int32_t mtl_conv_wgrad_simt(mtl_ctx* ctx, float* dW, const float* ug, const floa
     const int PH = (g.OH - 1) * g.sh + (g.R - 1) * g.dh + 1 + 0, PW = (g.OW - 1) * g.sw + (g.S - 1) * g.dw + 1;
     const bool staged_ok = (size_t)PH * PW * 4 <= 40 * 1024 && ((g.R == 5 && g.S == 5) || (g.R == 3 && g.S == 3)) &&
                            g.OH * g.OW >= 64;
-    // row-streaming variant: few input channels, 28-pixel rows, 'same'-style geometry
-    const bool rows_ok = g.C <= 4 && g.K >= 16 && g.OW == 28 && g.OH % 7 == 0 && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1 &&
-                         ((g.R == 5 && g.S == 5) || (g.R == 3 && g.S == 3)) && g.W + 2 * g.pw == g.OW + g.S - 1 &&
-                         g.H + 2 * g.ph == g.OH + g.R - 1 && ((reinterpret_cast<uintptr_t>(ug) & 15) == 0) && g.N >= 64;
-    if (rows_ok) {
-        constexpr int WARPS = 7, OWc = 28;
-        const int kgroups = (g.K + 31) / 32;
-        int ustride = WARPS * OWc;
-        while ((ustride / 4) % 2 == 0) ustride += 4;     // odd multiple of 4 floats
-        const int PH = g.OH + g.R - 1;
-        size_t smem = (size_t)(2 * PH * 32 + 2 * 32 * ustride) * 4;
-        size_t red_bytes = (size_t)WARPS * 32 * taps * 4;
-        if (red_bytes > (size_t)2 * 32 * ustride * 4) smem += red_bytes - (size_t)2 * 32 * ustride * 4;
-        int ns = (ctx->sm_count * 3 + kgroups * g.C - 1) / (kgroups * g.C);
-        if (ns > g.N / 4) ns = g.N / 4;
-        if (ns < 1) ns = 1;
-        int nps = (g.N + ns - 1) / ns;
-        ns = (g.N + nps - 1) / nps;
-        MTL_REQUIRE(ctx, ns <= 65535, "too many batch splits");
-        void* ws2;
-        int32_t rc2 = mtl_workspace(ctx, (size_t)ns * kc * taps * 4, &ws2);
-        if (rc2) return rc2;
-        float* part = (float*)ws2;
-        dim3 rgrid((unsigned)(kgroups * g.C), (unsigned)ns);
-        if (g.R == 5) {
-            MTL_CUDA(ctx, cudaFuncSetAttribute(k_conv_wgrad_rows<5, 5, OWc, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            k_conv_wgrad_rows<5, 5, OWc, WARPS><<<rgrid, WARPS * 32, smem, ctx->stream>>>(part, ug, X, g, nps, ustride);
-        } else {
-            MTL_CUDA(ctx, cudaFuncSetAttribute(k_conv_wgrad_rows<3, 3, OWc, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            k_conv_wgrad_rows<3, 3, OWc, WARPS><<<rgrid, WARPS * 32, smem, ctx->stream>>>(part, ug, X, g, nps, ustride);
-        }
-        MTL_LAUNCHED(ctx);
-        return mtl_sum_partials(ctx, dW, part, (int64_t)kc * taps, ns, accumulate);
-    }
+    if (mtl_conv_wgrad_rows_supported(g, ug)) return mtl_conv_wgrad_bias_rows(ctx, dW, nullptr, ug, X, g, accumulate, 0);
     if (staged_ok) {
         constexpr int KB = 4;
         const int kgroups = (g.K + KB - 1) / KB;

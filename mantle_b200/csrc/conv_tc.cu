@@ -222,10 +222,14 @@ __device__ __forceinline__ void split_tf32(float v, float& h, float& l) {
 }
 
 // [N, C, HW] -> [N, HW, C] through a 32x32 shared-memory tile; optionally also writes the residual.
+// With `colsum` the block also leaves the sum of its 32 pixels for each of its 32 channels in
+// colsum[(n * pixel_tiles + pixel_tile) * C + c]: the bias gradient read off the same pass.
 template <bool SPLIT>
 __global__ void __launch_bounds__(256) k_nchw_to_nhwc(float* __restrict__ hi, float* __restrict__ lo,
-                                                      const float* __restrict__ X, int C, int HW) {
+                                                      const float* __restrict__ X, int C, int HW,
+                                                      float* __restrict__ colsum) {
     __shared__ float tile[32][33];
+    __shared__ float part[8][33];
     const int n = blockIdx.z;
     const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
@@ -236,11 +240,13 @@ __global__ void __launch_bounds__(256) k_nchw_to_nhwc(float* __restrict__ hi, fl
         tile[ty + 8 * i][tx] = (c < C && pp < HW) ? xin[(int64_t)c * HW + pp] : 0.0f;
     }
     __syncthreads();
+    float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         int pp = p0 + ty + 8 * i, c = c0 + tx;
         if (pp < HW && c < C) {
             float v = tile[tx][ty + 8 * i];
+            s += v;
             int64_t o = ((int64_t)n * HW + pp) * C + c;
             if (SPLIT) {
                 float h, l;
@@ -251,6 +257,39 @@ __global__ void __launch_bounds__(256) k_nchw_to_nhwc(float* __restrict__ hi, fl
                 hi[o] = v;
             }
         }
+    }
+    if (colsum) {
+        part[ty][tx] = s;
+        __syncthreads();
+        if (ty == 0 && c0 + tx < C) {
+            float t = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t += part[j][tx];
+            colsum[((int64_t)n * gridDim.x + blockIdx.x) * C + c0 + tx] = t;
+        }
+    }
+}
+
+// out[y][c] (+)= sum over the rows of slice y of m[row][c]: 32 columns x 8 row lanes per block,
+// coalesced row segments, fixed order of additions.  grid = (cols / 32, slices).
+__global__ void __launch_bounds__(256) k_colsum(float* __restrict__ out, const float* __restrict__ m, int64_t rows,
+                                                int cols, int64_t rows_per_slice, int accumulate) {
+    __shared__ float part[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + tx;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_slice;
+    const int64_t r1 = r0 + rows_per_slice < rows ? r0 + rows_per_slice : rows;
+    float s = 0.0f;
+    if (c < cols)
+        for (int64_t r = r0 + ty; r < r1; r += 8) s += m[r * cols + c];
+    part[ty][tx] = s;
+    __syncthreads();
+    if (ty == 0 && c < cols) {
+        float t = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t += part[j][tx];
+        float* o = out + (int64_t)blockIdx.y * cols + c;
+        *o = accumulate ? *o + t : t;
     }
 }
 
@@ -603,6 +642,18 @@ int32_t launch_igemm(mtl_ctx* ctx, const CUtensorMap* maps, const ConvTcParams& 
     return MTL_OK;
 }
 
+// Channels-last copy (hi [, lo]) of an NCHW tensor; see k_nchw_to_nhwc for `colsum`.
+int32_t stage_nhwc(mtl_ctx* ctx, float* hi, float* lo, const float* src, int N, int C, int HW, int x3, float* colsum) {
+    dim3 tg((unsigned)((HW + 31) / 32), (unsigned)((C + 31) / 32), (unsigned)N);
+    MTL_REQUIRE(ctx, N <= 65535 && tg.y <= 65535u, "batch too large for the layout pass");
+    if (x3) k_nchw_to_nhwc<true><<<tg, 256, 0, ctx->stream>>>(hi, lo, src, C, HW, colsum);
+    else k_nchw_to_nhwc<false><<<tg, 256, 0, ctx->stream>>>(hi, lo, src, C, HW, colsum);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
+int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, float* a_lo, float* w_hi, float* w_lo);
+
 int32_t run_igemm(mtl_ctx* ctx, const IgemmCall& c, int x3) {
     const int HW = c.IH * c.IW;
     const size_t n_act = (size_t)c.N * c.Cin * HW;
@@ -619,9 +670,16 @@ int32_t run_igemm(mtl_ctx* ctx, const IgemmCall& c, int x3) {
 
     dim3 tgrid((unsigned)((HW + 31) / 32), (unsigned)((c.Cin + 31) / 32), (unsigned)c.N);
     MTL_REQUIRE(ctx, c.N <= 65535 && tgrid.y <= 65535u, "batch too large for the layout pass");
-    if (x3) k_nchw_to_nhwc<true><<<tgrid, 256, 0, ctx->stream>>>(a_hi, a_lo, c.act, c.Cin, HW);
-    else k_nchw_to_nhwc<false><<<tgrid, 256, 0, ctx->stream>>>(a_hi, a_lo, c.act, c.Cin, HW);
+    if (x3) k_nchw_to_nhwc<true><<<tgrid, 256, 0, ctx->stream>>>(a_hi, a_lo, c.act, c.Cin, HW, nullptr);
+    else k_nchw_to_nhwc<false><<<tgrid, 256, 0, ctx->stream>>>(a_hi, a_lo, c.act, c.Cin, HW, nullptr);
     MTL_LAUNCHED(ctx);
+    return run_igemm_core(ctx, c, x3, a_hi, a_lo, w_hi, w_lo);
+}
+
+// Weight re-layout and the implicit-GEMM kernel; the channels-last activations are already in place.
+int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, float* a_lo, float* w_hi, float* w_lo) {
+    const size_t n_wt = (size_t)c.wK * c.wC * c.R * c.S;
+    int32_t rc = MTL_OK;
     int wgrid = mtl_grid_for((int64_t)n_wt, 256, ctx->sm_count, 8);
     if (x3) k_weights_relayout<true><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
     else k_weights_relayout<false><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
@@ -976,9 +1034,11 @@ bool mtl_conv_wgrad_tc_supported(const ConvGeom& g, const float* ug, const float
     return true;
 }
 
-int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,
-                          int accumulate, int x3) {
-    WgradParams p;
+namespace {
+
+// Geometry of the kernel-gradient launch; the number of floats of partial sums it needs.
+int32_t wgrad_plan(mtl_ctx* ctx, const ConvGeom& g, int x3, WgradParams* pp, size_t* n_part) {
+    WgradParams& p = *pp;
     p.N = g.N; p.OH = g.OH; p.OW = g.OW; p.Kout = g.K; p.C = g.C;
     p.R = g.R; p.S = g.S; p.ph = g.ph; p.pw = g.pw;
     choose_box32(g.OW, g.OH, g.N, &p.bw, &p.bh, &p.bn);
@@ -1014,31 +1074,17 @@ int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float*
     if (x3) { p.segA[0] = 1; p.segB[0] = 0; p.segA[1] = 0; p.segB[1] = 1; p.segA[2] = 0; p.segB[2] = 0; }
     else    { p.segA[0] = p.segA[1] = p.segA[2] = 0; p.segB[0] = p.segB[1] = p.segB[2] = 0; }
     p.status = ctx->dev_status;
+    *n_part = (size_t)p.nsplit * RS * g.K * g.C;
+    return MTL_OK;
+}
 
-    // scratch: channels-last copies of ug and X (hi [, lo]) and the per-split partial sums
-    const size_t n_u = (size_t)g.N * g.K * g.OH * g.OW, n_x = (size_t)g.N * g.C * g.H * g.W;
-    const size_t u_pad = (n_u + 63) & ~(size_t)63, x_pad = (n_x + 63) & ~(size_t)63;
-    const size_t n_part = (size_t)p.nsplit * RS * g.K * g.C;
-    const int parts = x3 ? 2 : 1;
-    void* ws;
-    int32_t rc = mtl_workspace(ctx, ((size_t)parts * (u_pad + x_pad) + n_part) * 4, &ws);
-    if (rc) return rc;
-    float* u_hi = (float*)ws;
-    float* u_lo = x3 ? u_hi + u_pad : nullptr;
-    float* x_hi = u_hi + (size_t)parts * u_pad;
-    float* x_lo = x3 ? x_hi + x_pad : nullptr;
-    p.partial = x_hi + (size_t)parts * x_pad;
-    MTL_REQUIRE(ctx, g.N <= 65535, "batch too large for the layout pass");
-    {
-        dim3 tg((unsigned)((g.OH * g.OW + 31) / 32), (unsigned)((g.K + 31) / 32), (unsigned)g.N);
-        if (x3) k_nchw_to_nhwc<true><<<tg, 256, 0, ctx->stream>>>(u_hi, u_lo, ug, g.K, g.OH * g.OW);
-        else k_nchw_to_nhwc<false><<<tg, 256, 0, ctx->stream>>>(u_hi, u_lo, ug, g.K, g.OH * g.OW);
-        MTL_LAUNCHED(ctx);
-        dim3 tx((unsigned)((g.H * g.W + 31) / 32), (unsigned)((g.C + 31) / 32), (unsigned)g.N);
-        if (x3) k_nchw_to_nhwc<true><<<tx, 256, 0, ctx->stream>>>(x_hi, x_lo, X, g.C, g.H * g.W);
-        else k_nchw_to_nhwc<false><<<tx, 256, 0, ctx->stream>>>(x_hi, x_lo, X, g.C, g.H * g.W);
-        MTL_LAUNCHED(ctx);
-    }
+
+// The launch itself: channels-last copies (hi [, lo]) of ug and X are in place.
+int32_t wgrad_core(mtl_ctx* ctx, float* dW, const float* u_hi, const float* u_lo, const float* x_hi, const float* x_lo,
+                   float* partial, WgradParams p, const ConvGeom& g, int accumulate, int x3) {
+    const int RS = g.R * g.S;
+    int32_t rc = MTL_OK;
+    p.partial = partial;
     CUtensorMap maps[4];
     for (int i = 0; i < 2; ++i) {
         const float* u = (i == 1 && x3) ? u_lo : u_hi;
@@ -1067,4 +1113,85 @@ int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float*
     k_wgrad_fold<<<fgrid, 256, 0, ctx->stream>>>(dW, p.partial, g.K, g.C, RS, p.nsplit, accumulate);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
+}
+
+}  // namespace
+
+int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,
+                          int accumulate, int x3) {
+    WgradParams p;
+    size_t n_part;
+    int32_t rc = wgrad_plan(ctx, g, x3, &p, &n_part);
+    if (rc) return rc;
+    // scratch: channels-last copies of ug and X (hi [, lo]) and the per-split partial sums
+    const size_t n_u = (size_t)g.N * g.K * g.OH * g.OW, n_x = (size_t)g.N * g.C * g.H * g.W;
+    const size_t u_pad = (n_u + 63) & ~(size_t)63, x_pad = (n_x + 63) & ~(size_t)63;
+    const int parts = x3 ? 2 : 1;
+    void* ws;
+    rc = mtl_workspace(ctx, ((size_t)parts * (u_pad + x_pad) + n_part) * 4, &ws);
+    if (rc) return rc;
+    float* u_hi = (float*)ws;
+    float* u_lo = x3 ? u_hi + u_pad : nullptr;
+    float* x_hi = u_hi + (size_t)parts * u_pad;
+    float* x_lo = x3 ? x_hi + x_pad : nullptr;
+    float* partial = x_hi + (size_t)parts * x_pad;
+    rc = stage_nhwc(ctx, u_hi, u_lo, ug, g.N, g.K, g.OH * g.OW, x3, nullptr);
+    if (rc) return rc;
+    rc = stage_nhwc(ctx, x_hi, x_lo, X, g.N, g.C, g.H * g.W, x3, nullptr);
+    if (rc) return rc;
+    return wgrad_core(ctx, dW, u_hi, u_lo, x_hi, x_lo, partial, p, g, accumulate, x3);
+}
+
+// dX, dW and (optionally) the bias gradient of one CONV2D from a single channels-last copy of ug:
+// the kernel gradient runs first, then the input gradient re-uses the copy; the bias gradient is
+// the per-channel sum the copy pass leaves behind.
+int32_t mtl_conv_bwd_fused_tc(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* X,
+                              const float* Wt, const ConvGeom& g, int acc_dx, int acc_dw, int acc_db, int x3) {
+    WgradParams p;
+    size_t n_part;
+    int32_t rc = wgrad_plan(ctx, g, x3, &p, &n_part);
+    if (rc) return rc;
+    const size_t n_u = (size_t)g.N * g.K * g.OH * g.OW, n_x = (size_t)g.N * g.C * g.H * g.W;
+    const size_t n_wt = (size_t)g.K * g.C * g.R * g.S;
+    const size_t u_pad = (n_u + 63) & ~(size_t)63, x_pad = (n_x + 63) & ~(size_t)63, wt_pad = (n_wt + 63) & ~(size_t)63;
+    const int parts = x3 ? 2 : 1;
+    const int ptiles = (g.OH * g.OW + 31) / 32;
+    const size_t n_bias = db ? ((size_t)g.N * ptiles + 256) * g.K : 0;
+    size_t second = (size_t)parts * x_pad + n_part;
+    if ((size_t)parts * wt_pad > second) second = (size_t)parts * wt_pad;
+    void* ws;
+    rc = mtl_workspace(ctx, ((size_t)parts * u_pad + second + n_bias) * 4, &ws);
+    if (rc) return rc;
+    float* u_hi = (float*)ws;
+    float* u_lo = x3 ? u_hi + u_pad : nullptr;
+    float* region = u_hi + (size_t)parts * u_pad;
+    float* x_hi = region;
+    float* x_lo = x3 ? x_hi + x_pad : nullptr;
+    float* partial = region + (size_t)parts * x_pad;
+    float* bias_part = region + second;
+    rc = stage_nhwc(ctx, u_hi, u_lo, ug, g.N, g.K, g.OH * g.OW, x3, db ? bias_part : nullptr);
+    if (rc) return rc;
+    if (db) {
+        // two levels: 256 slices of the per-block sums, then the slices
+        const int64_t rows = (int64_t)g.N * ptiles;
+        const int slices = rows < 256 ? (int)rows : 256;
+        const int64_t rps = (rows + slices - 1) / slices;
+        float* level1 = bias_part + rows * g.K;
+        dim3 g1((unsigned)((g.K + 31) / 32), (unsigned)slices);
+        k_colsum<<<g1, 256, 0, ctx->stream>>>(level1, bias_part, rows, g.K, rps, 0);
+        MTL_LAUNCHED(ctx);
+        k_colsum<<<(g.K + 31) / 32, 256, 0, ctx->stream>>>(db, level1, slices, g.K, slices, acc_db);
+        MTL_LAUNCHED(ctx);
+    }
+    rc = stage_nhwc(ctx, x_hi, x_lo, X, g.N, g.C, g.H * g.W, x3, nullptr);
+    if (rc) return rc;
+    rc = wgrad_core(ctx, dW, u_hi, u_lo, x_hi, x_lo, partial, p, g, acc_dw, x3);
+    if (rc) return rc;
+    // input gradient: the same copy of ug is the activation operand; its weights go where X was
+    IgemmCall c;
+    c.N = g.N; c.Cin = g.K; c.IH = g.OH; c.IW = g.OW; c.Kout = g.C; c.OH = g.H; c.OW = g.W;
+    c.R = g.R; c.S = g.S; c.ph = g.R - 1 - g.ph; c.pw = g.S - 1 - g.pw;
+    c.act = ug; c.wt = Wt; c.wK = g.K; c.wC = g.C; c.flip = 1;
+    c.out = dX; c.bias = nullptr; c.accumulate = acc_dx; c.relu = 0;
+    return run_igemm_core(ctx, c, x3, u_hi, u_lo, region, x3 ? region + wt_pad : nullptr);
 }

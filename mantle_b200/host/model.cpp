@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 namespace mantle {
@@ -505,9 +506,24 @@ void Model::backward_enqueue() {
     grad_written_[g_.loss_out->id] = true;
     for (int i = (int)g_.nodes.size() - 1; i >= 0; --i) {
         const Node& n = g_.nodes[i];
-        if (!(fusion_ && bwd_skip_[i]))  // else: done by the MAXPOOL2D that consumes this RELU
+        if (fusion_ && bwd_skip_[i]) {
+            // done by the MAXPOOL2D that consumes this RELU
+        } else if (fusion_ && n.op == MTL_OP_CONV2D) {
+            // all wanted operand gradients of the layer from one pass over ug (mtl_conv2d_bwd_fused)
+            const Symbol& x = n.inputs[0];
+            const Symbol& w = n.inputs[1];
+            const Symbol& b = n.inputs[2];
+            mtl_conv2d_desc d = conv_desc(x.shape, (int)w.shape[0], (int)w.shape[2], (int)w.shape[3], n.attrs);
+            float* dx = x.trainable ? G(x) : nullptr;
+            float* dw = w.trainable ? G(w) : nullptr;
+            float* db = b.trainable ? G(b) : nullptr;
+            const int ax = dx ? acc_flag(x) : 0, aw = dw ? acc_flag(w) : 0, ab = db ? acc_flag(b) : 0;
+            if (dx || dw || db)
+                check(mtl_conv2d_bwd_fused(ctx_, dx, dw, db, G(n.outputs[0]), T(x), T(w), &d, ax, aw, ab), "CONV2D backward");
+        } else {
             for (int j = 0; j < (int)n.inputs.size(); ++j)
                 if (n.inputs[j].trainable) backward_op(n, j);
+        }
         if (after_backward_node) after_backward_node(after_backward_user, i);
     }
 }

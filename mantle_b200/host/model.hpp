@@ -60,7 +60,9 @@ class Model {
     // Chain fusion (off by default).  On: a CONV2D whose only consumer is a RELU writes the RELU's
     // output directly (mtl_conv2d_fwd_act) and the RELU node is not run; a MAXPOOL2D fed by a RELU
     // that nothing else reads performs that RELU's backward as well (mtl_maxpool2d_bwd_idx_act).
-    // Every tensor that IS written holds exactly the bits the unfused run writes; what is never
+    // A CONV2D's operand gradients come from one mtl_conv2d_bwd_fused call (the bias gradient is then
+    // summed in a different order: equal within rounding, not bitwise).
+    // Every other tensor that IS written holds exactly the bits the unfused run writes; what is never
     // written is the CONV2D output (pre-activation) and the gradient of the RELU output.  Symbols
     // that are graph outputs or have other consumers are never fused away.
     void set_fusion(bool on);

@@ -417,6 +417,49 @@ def test_pool_backward_with_fused_relu_equals_two_calls(ctx, case):
             assert_close(one.numpy(), two.numpy(), 1e-6, 1e-6, "accumulate=%s" % accumulate)
 
 
+FUSED_BWD = [(6, 64, 14, 14, 128, 5, 5, 2), (2, 64, 56, 56, 64, 3, 3, 1), (70, 1, 28, 28, 64, 5, 5, 2),
+             (5, 16, 14, 14, 32, 5, 5, 2), (3, 2, 9, 11, 5, 3, 3, 1)]
+
+
+@pytest.mark.parametrize("case", FUSED_BWD)
+def test_conv_backward_fused_equals_separate_calls(ctx, case):
+    """mtl_conv2d_bwd_fused: dX and dW are the bits of the per-operand calls; db agrees within rounding."""
+    N, C, H, W, K, R, S, p = case
+    rng = np.random.default_rng(sum(case) + 3)
+    x = ctx.array(rng.normal(0, 1, (N, C, H, W)).astype(np.float32))
+    w = ctx.array((rng.normal(0, 1, (K, C, R, S)) / np.sqrt(C * R * S)).astype(np.float32))
+    b = ctx.array(np.zeros(K, np.float32))
+    kw = dict(padding=(p, p), stride=(1, 1), dilation=(1, 1))
+    oh, ow = mb.conv2d_out_shape((N, C, H, W), (K, C, R, S), **kw)
+    ug = ctx.array(rng.normal(0, 1, (N, K, oh, ow)).astype(np.float32))
+    d = mb.conv_desc(N, C, H, W, K, R, S, (p, p), (1, 1), (1, 1))
+    import ctypes as Cc
+    for mode in (mb.MATH_TF32X3, mb.MATH_TF32):
+        ctx.set_math_mode(mode)
+        try:
+            for acc in (0, 1):
+                init = [rng.normal(0, 1, s).astype(np.float32) for s in ((N, C, H, W), (K, C, R, S), (K,))]
+                sep = [ctx.array(a) for a in init]
+                for tid in range(3):
+                    ctx.backward_op(tid, OP.CONV2D, ug, x, w, b, grad=sep[tid], accumulate=bool(acc), **kw)
+                fus = [ctx.array(a) for a in init]
+                ctx._check(ctx.lib.mtl_conv2d_bwd_fused(ctx.handle, fus[0].ptr, fus[1].ptr, fus[2].ptr, ug.ptr, x.ptr, w.ptr,
+                                                        Cc.byref(d), acc, acc, acc))
+                assert np.array_equal(fus[0].numpy(), sep[0].numpy()), "dX mode %d acc %d" % (mode, acc)
+                assert np.array_equal(fus[1].numpy(), sep[1].numpy()), "dW mode %d acc %d" % (mode, acc)
+                assert rel_err(fus[2].numpy(), sep[2].numpy().astype(np.float64)) < 1e-5, "db"
+                # a subset: only the kernel and bias gradients
+                part = [ctx.array(a) for a in init]
+                ctx._check(ctx.lib.mtl_conv2d_bwd_fused(ctx.handle, None, part[1].ptr, part[2].ptr, ug.ptr, x.ptr, w.ptr,
+                                                        Cc.byref(d), 0, acc, acc))
+                assert rel_err(part[1].numpy(), sep[1].numpy().astype(np.float64)) < 1e-5
+                assert rel_err(part[2].numpy(), sep[2].numpy().astype(np.float64)) < 1e-5
+                assert np.array_equal(part[0].numpy(), init[0])
+        finally:
+            ctx.set_math_mode(mb.MATH_TF32X3)
+    assert ctx.device_status() == 0
+
+
 # ------------------------------------------------------------------ MAXPOOL2D ------------------
 
 def test_maxpool_reference_cases(ctx):
