@@ -191,6 +191,15 @@ MTL_API int32_t mtl_conv2d_bwd_fused(mtl_ctx* ctx, float* dX, float* dW, float* 
                                      int32_t acc_dx, int32_t acc_dw, int32_t acc_db);
 MTL_API int32_t mtl_conv2d_fwd_act(mtl_ctx* ctx, float* Y, const float* X, const float* Wt,
                                    const float* bias, const mtl_conv2d_desc* d, int32_t act_op);
+/*   mtl_conv2d_fwd_act_pool    pooled, idx = MAXPOOL2D.forward(act(CONV2D.forward(X, Wt, bias))) (conv.mojo:81-226,
+ *                              pool.mojo:44-100): `pool` describes the pooling of the convolution's output
+ *                              (N, C = K, H = OH, W = OW, R/S = kernel_size).  Where a kernel pools in its
+ *                              epilogue (2x2 windows, stride 2) the activation never reaches memory;
+ *                              otherwise it passes through scratch memory.  idx may be null. */
+MTL_API int32_t mtl_conv2d_fwd_act_pool(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X,
+                                        const float* Wt, const float* bias,
+                                        const mtl_conv2d_desc* d, int32_t act_op,
+                                        const mtl_conv2d_desc* pool);
 MTL_API int32_t mtl_maxpool2d_bwd_idx_act(mtl_ctx* ctx, float* dX, const float* ug,
                                           const int32_t* idx, const float* pooled,
                                           const mtl_conv2d_desc* d, int32_t act_op,

@@ -23,6 +23,8 @@ struct mtl_ctx {
     // scratch workspace, grown on demand outside capture
     void* ws = nullptr;
     size_t ws_bytes = 0;
+    void* ws2 = nullptr;  // second scratch block (mtl_workspace2)
+    size_t ws2_bytes = 0;
     bool capturing = false;
     int64_t launches = 0;
     int64_t launches_at_capture = 0;
@@ -67,6 +69,7 @@ struct mtl_graph {
 int32_t mtl_set_error(mtl_ctx* ctx, int32_t code, const char* fmt, ...);
 // Returns a device pointer to at least `bytes` of scratch, 256-byte aligned.
 int32_t mtl_workspace(mtl_ctx* ctx, size_t bytes, void** out);
+int32_t mtl_workspace2(mtl_ctx* ctx, size_t bytes, void** out);
 
 #define MTL_CHECK_CTX(ctx) \
     do {                   \

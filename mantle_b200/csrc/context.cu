@@ -40,6 +40,32 @@ int32_t mtl_workspace(mtl_ctx* ctx, size_t bytes, void** out) {
     return MTL_OK;
 }
 
+// A second scratch block for callers that run other library kernels (which use the first one)
+// on the data they keep here; same growth rules.
+int32_t mtl_workspace2(mtl_ctx* ctx, size_t bytes, void** out) {
+    if (bytes > ctx->ws2_bytes) {
+        if (ctx->capturing)
+            return mtl_set_error(ctx, MTL_ERR_NOMEM,
+                                 "scratch of %zu bytes needed during stream capture but only %zu reserved; run the "
+                                 "step once before capturing it",
+                                 bytes, ctx->ws2_bytes);
+        MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->ws2) MTL_CUDA(ctx, cudaFree(ctx->ws2));
+        ctx->ws2 = nullptr;
+        ctx->ws2_bytes = 0;
+        size_t want = (bytes + (size_t)(1 << 20) - 1) & ~((size_t)(1 << 20) - 1);
+        cudaError_t e = cudaMalloc(&ctx->ws2, want);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return mtl_set_error(ctx, MTL_ERR_NOMEM, "cudaMalloc of %zu scratch bytes failed: %s", want,
+                                 cudaGetErrorString(e));
+        }
+        ctx->ws2_bytes = want;
+    }
+    *out = ctx->ws2;
+    return MTL_OK;
+}
+
 extern "C" {
 
 const char* mtl_version(void) { return "mantle_cuda 0.1 (sm_100a)"; }
@@ -94,6 +120,7 @@ int32_t mtl_ctx_destroy(mtl_ctx* ctx) {
         if (ctx->t1[i]) cudaEventDestroy(ctx->t1[i]);
     }
     if (ctx->ws) cudaFree(ctx->ws);
+    if (ctx->ws2) cudaFree(ctx->ws2);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;

@@ -70,6 +70,33 @@ int32_t mtl_conv2d_bwd(mtl_ctx* ctx, int32_t tensor_id, float* grad, const float
     return mtl_conv_bgrad(ctx, grad, ug, g, accumulate);
 }
 
+int32_t mtl_conv2d_fwd_act_pool(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X, const float* Wt,
+                                const float* bias, const mtl_conv2d_desc* d, int32_t act_op,
+                                const mtl_conv2d_desc* pool) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, act_op == MTL_OP_RELU || act_op < 0, "mtl_conv2d_fwd_act_pool fuses RELU only (act_op %d)", act_op);
+    ConvGeom g;
+    int32_t rc = make_geom(ctx, d, &g);
+    if (rc) return rc;
+    MTL_REQUIRE(ctx, pooled && X && Wt && pool, "null pointer in mtl_conv2d_fwd_act_pool");
+    MTL_REQUIRE(ctx, pool->N == g.N && pool->C == g.K && pool->H == g.OH && pool->W == g.OW,
+                "the pooling descriptor does not describe the convolution's output");
+    const int relu = act_op == MTL_OP_RELU ? 1 : 0;
+    const bool pool_2x2 = pool->R == 2 && pool->S == 2 && pool->stride[0] == 2 && pool->stride[1] == 2 &&
+                          pool->pad[0] == 0 && pool->pad[1] == 0 && pool->dilation[0] == 1 && pool->dilation[1] == 1 &&
+                          g.OH % 2 == 0 && g.OW % 2 == 0;
+    const bool tc = ctx->math_mode != MTL_MATH_FP32 && mtl_conv_fwd_tc_supported(g, X, Wt, pooled);
+    if (pool_2x2 && !tc && mtl_conv_fwd_pool_simt_supported(g, pooled))
+        return mtl_conv_fwd_pool_simt(ctx, pooled, idx, X, Wt, bias, g, relu);
+    // no kernel pools this geometry in its epilogue: the activation goes through scratch memory
+    void* scratch;
+    rc = mtl_workspace2(ctx, (size_t)g.N * g.K * g.OH * g.OW * 4, &scratch);
+    if (rc) return rc;
+    rc = conv2d_fwd(ctx, (float*)scratch, X, Wt, bias, d, relu);
+    if (rc) return rc;
+    return mtl_maxpool2d_fwd(ctx, pooled, idx, (const float*)scratch, pool);
+}
+
 int32_t mtl_conv2d_bwd_fused(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* X,
                              const float* Wt, const mtl_conv2d_desc* d, int32_t acc_dx, int32_t acc_dw, int32_t acc_db) {
     MTL_CHECK_CTX(ctx);

@@ -23,6 +23,11 @@ int32_t mtl_conv_wgrad_simt(mtl_ctx* ctx, float* dW, const float* ug, const floa
                             int accumulate);
 int32_t mtl_conv_bgrad(mtl_ctx* ctx, float* db, const float* ug, const ConvGeom& g, int accumulate);
 
+// First-layer kernel that also pools (conv_simt.cu).
+bool mtl_conv_fwd_pool_simt_supported(const ConvGeom& g, const float* pooled);
+int32_t mtl_conv_fwd_pool_simt(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X, const float* Wt,
+                               const float* bias, const ConvGeom& g, int relu);
+
 // Tensor-core implicit-GEMM kernels (conv_tc.cu); *_supported says whether a geometry qualifies.
 bool mtl_conv_fwd_tc_supported(const ConvGeom& g, const float* X, const float* Wt, const float* Y);
 bool mtl_conv_dgrad_tc_supported(const ConvGeom& g, const float* ug, const float* Wt, const float* dX);

@@ -114,8 +114,12 @@ __global__ void __launch_bounds__(kBlock) k_conv_fwd_patch(float* __restrict__ Y
 // zero-padded plane in shared memory as broadcast float4 loads (8*R*C loads for OW*R*S*C FMAs);
 // the finished 32 channels x OW block is turned through shared memory so that OW/4 lanes store one
 // channel's row as consecutive float4s.  Bound by writing Y.
-template <int R, int S, int C, int OW, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, 2) k_conv_fwd_rows(float* __restrict__ Y, const float* __restrict__ X,
+// POOL: a warp produces two adjacent output rows, applies the activation and writes only their
+// 2x2 / stride-2 maxima and argmax indices (MAXPOOL2D.forward's strict '>' scan in row-major window
+// order, pool.mojo:44-100), so the full-size activation never reaches memory.
+template <int R, int S, int C, int OW, int WARPS, bool POOL>
+__global__ void __launch_bounds__(WARPS * 32, 2) k_conv_fwd_rows(float* __restrict__ Y, int32_t* __restrict__ pool_idx,
+                                                                  const float* __restrict__ X,
                                                                   const float* __restrict__ Wt,
                                                                   const float* __restrict__ bias, ConvGeom g, int relu) {
     constexpr int PW = 32, NT = WARPS * 32, SST = OW + ((OW / 4) % 2 == 0 ? 4 : 8);  // odd multiple of 4 floats
@@ -161,8 +165,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) k_conv_fwd_rows(float* __restri
         }
         __syncthreads();
         const float* xb = xs + buf * C * PH * PW;
-        for (int oh = warp; oh < g.OH; oh += WARPS) {
-            float out[OW];
+        auto row = [&](int oh, float (&out)[OW]) {
 #pragma unroll
             for (int i = 0; i < OW; ++i) out[i] = bv;
 #pragma unroll
@@ -184,18 +187,55 @@ __global__ void __launch_bounds__(WARPS * 32, 2) k_conv_fwd_rows(float* __restri
 #pragma unroll
                 for (int i = 0; i < OW; ++i) out[i] = out[i] > 0.0f ? out[i] : 0.0f;
             }
-            __syncwarp();
+        };
+        if constexpr (!POOL) {
+            for (int oh = warp; oh < g.OH; oh += WARPS) {
+                float out[OW];
+                row(oh, out);
+                __syncwarp();
 #pragma unroll
-            for (int i = 0; i < OW / 4; ++i)
-                *reinterpret_cast<float4*>(sw + lane * SST + 4 * i) = make_float4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
-            __syncwarp();
-            if (chl < CPI) {
+                for (int i = 0; i < OW / 4; ++i)
+                    *reinterpret_cast<float4*>(sw + lane * SST + 4 * i) = make_float4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+                __syncwarp();
+                if (chl < CPI) {
 #pragma unroll
-                for (int it = 0; it < (32 + CPI - 1) / CPI; ++it) {
-                    const int ch = it * CPI + chl;
-                    if (ch < 32 && k0 + ch < g.K) {
-                        const float4 q = *reinterpret_cast<const float4*>(sw + ch * SST + 4 * sub);
-                        *reinterpret_cast<float4*>(Y + (((int64_t)n * g.K + k0 + ch) * g.OH + oh) * OW + 4 * sub) = q;
+                    for (int it = 0; it < (32 + CPI - 1) / CPI; ++it) {
+                        const int ch = it * CPI + chl;
+                        if (ch < 32 && k0 + ch < g.K) {
+                            const float4 q = *reinterpret_cast<const float4*>(sw + ch * SST + 4 * sub);
+                            *reinterpret_cast<float4*>(Y + (((int64_t)n * g.K + k0 + ch) * g.OH + oh) * OW + 4 * sub) = q;
+                        }
+                    }
+                }
+            }
+        } else {
+            constexpr int POW = OW / 2, PST = POW + 1;   // odd row stride: conflict-free scalar access
+            const int POH = g.OH / 2;
+            int32_t* swi = reinterpret_cast<int32_t*>(sw + 32 * PST);
+            for (int pr = warp; pr < POH; pr += WARPS) {
+                float o0[OW], o1[OW];
+                row(2 * pr, o0);
+                row(2 * pr + 1, o1);
+                __syncwarp();
+#pragma unroll
+                for (int pw = 0; pw < POW; ++pw) {
+                    const int i00 = (2 * pr) * OW + 2 * pw;
+                    float m = -INFINITY;
+                    int j = -1;
+                    if (o0[2 * pw] > m) { m = o0[2 * pw]; j = i00; }
+                    if (o0[2 * pw + 1] > m) { m = o0[2 * pw + 1]; j = i00 + 1; }
+                    if (o1[2 * pw] > m) { m = o1[2 * pw]; j = i00 + OW; }
+                    if (o1[2 * pw + 1] > m) { m = o1[2 * pw + 1]; j = i00 + OW + 1; }
+                    sw[lane * PST + pw] = m;
+                    swi[lane * PST + pw] = j;
+                }
+                __syncwarp();
+                for (int e = lane; e < 32 * POW; e += 32) {
+                    const int ch = e / POW, pw = e - ch * POW;
+                    if (k0 + ch < g.K) {
+                        const int64_t o = (((int64_t)n * g.K + k0 + ch) * POH + pr) * POW + pw;
+                        Y[o] = sw[ch * PST + pw];
+                        if (pool_idx) pool_idx[o] = swi[ch * PST + pw];
                     }
                 }
             }
@@ -575,18 +615,18 @@ static int32_t launch_fwd_patch(mtl_ctx* ctx, float* Y, const float* X, const fl
     return MTL_OK;
 }
 
-template <int R, int S, int C>
-static int32_t launch_fwd_rows(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
-                               const ConvGeom& g, int relu) {
+template <int R, int S, int C, bool POOL>
+static int32_t launch_fwd_rows(mtl_ctx* ctx, float* Y, int32_t* pool_idx, const float* X, const float* Wt,
+                               const float* bias, const ConvGeom& g, int relu) {
     constexpr int WARPS = 7, OWc = 28, SST = 36;
     const int kgroups = (g.K + 31) / 32;
     const int PH = g.OH + R - 1;
     size_t smem = (size_t)(2 * C * PH * 32 + WARPS * 32 * SST) * 4;
     int per_group = (ctx->sm_count * 2 + kgroups - 1) / kgroups;
     if (per_group > g.N) per_group = g.N;
-    auto kern = k_conv_fwd_rows<R, S, C, OWc, WARPS>;
+    auto kern = k_conv_fwd_rows<R, S, C, OWc, WARPS, POOL>;
     MTL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<per_group * kgroups, WARPS * 32, smem, ctx->stream>>>(Y, X, Wt, bias, g, relu);
+    kern<<<per_group * kgroups, WARPS * 32, smem, ctx->stream>>>(Y, pool_idx, X, Wt, bias, g, relu);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -607,19 +647,35 @@ static int32_t conv_fwd_simt_plain(mtl_ctx* ctx, float* Y, const float* X, const
     return MTL_OK;
 }
 
+static bool fwd_rows_ok(const ConvGeom& g, const float* Y) {
+    return g.OW == 28 && g.K >= 16 && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1 &&
+           g.W + 2 * g.pw == g.OW + g.S - 1 && g.H + 2 * g.ph == g.OH + g.R - 1 && g.OH <= 64 &&
+           ((reinterpret_cast<uintptr_t>(Y) & 15) == 0) && g.N >= 64 &&
+           ((g.R == 5 && g.S == 5 && g.C == 1) || (g.R == 3 && g.S == 3 && (g.C == 1 || g.C == 3)));
+}
+
 int32_t mtl_conv_fwd_simt(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
                           const ConvGeom& g, int relu) {
-    const bool rows_ok = g.OW == 28 && g.K >= 16 && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1 &&
-                         g.W + 2 * g.pw == g.OW + g.S - 1 && g.H + 2 * g.ph == g.OH + g.R - 1 && g.OH <= 64 &&
-                         ((reinterpret_cast<uintptr_t>(Y) & 15) == 0) && g.N >= 64;
-    if (rows_ok) {
-        if (g.R == 5 && g.S == 5 && g.C == 1) return launch_fwd_rows<5, 5, 1>(ctx, Y, X, Wt, bias, g, relu);
-        if (g.R == 3 && g.S == 3 && g.C == 1) return launch_fwd_rows<3, 3, 1>(ctx, Y, X, Wt, bias, g, relu);
-        if (g.R == 3 && g.S == 3 && g.C == 3) return launch_fwd_rows<3, 3, 3>(ctx, Y, X, Wt, bias, g, relu);
+    if (fwd_rows_ok(g, Y)) {
+        if (g.R == 5) return launch_fwd_rows<5, 5, 1, false>(ctx, Y, nullptr, X, Wt, bias, g, relu);
+        if (g.C == 1) return launch_fwd_rows<3, 3, 1, false>(ctx, Y, nullptr, X, Wt, bias, g, relu);
+        return launch_fwd_rows<3, 3, 3, false>(ctx, Y, nullptr, X, Wt, bias, g, relu);
     }
     int32_t rc = conv_fwd_simt_plain(ctx, Y, X, Wt, bias, g);
     if (rc || !relu) return rc;
     return mtl_unary_fwd(ctx, MTL_OP_RELU, Y, Y, (int64_t)g.N * g.K * g.OH * g.OW, 0.0f, 0.0f);
+}
+
+// CONV2D (+ RELU) followed by a 2x2 / stride-2 MAXPOOL2D in one kernel; false when this geometry has none.
+bool mtl_conv_fwd_pool_simt_supported(const ConvGeom& g, const float* pooled) {
+    return fwd_rows_ok(g, pooled) && g.OH % 2 == 0;
+}
+
+int32_t mtl_conv_fwd_pool_simt(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X, const float* Wt,
+                               const float* bias, const ConvGeom& g, int relu) {
+    if (g.R == 5) return launch_fwd_rows<5, 5, 1, true>(ctx, pooled, idx, X, Wt, bias, g, relu);
+    if (g.C == 1) return launch_fwd_rows<3, 3, 1, true>(ctx, pooled, idx, X, Wt, bias, g, relu);
+    return launch_fwd_rows<3, 3, 3, true>(ctx, pooled, idx, X, Wt, bias, g, relu);
 }
 
 int32_t mtl_conv_dgrad_simt(mtl_ctx* ctx, float* dX, const float* ug, const float* Wt, const ConvGeom& g,

@@ -310,6 +310,7 @@ void Model::set_fusion(bool on) {
     const int nn = (int)g_.nodes.size();
     fusion_ = on;
     fwd_relu_of_.assign(nn, -1);
+    fwd_pool_of_.assign(nn, -1);
     bwd_relu_of_.assign(nn, -1);
     fwd_skip_.assign(nn, 0);
     bwd_skip_.assign(nn, 0);
@@ -344,6 +345,18 @@ void Model::set_fusion(bool on) {
                 if (q.op == MTL_OP_MAXPOOL2D && q.inputs[0].id == rout.id) {
                     bwd_relu_of_[k] = j;
                     bwd_skip_[j] = 1;
+                }
+            }
+        }
+        // forward: CONV2D -> RELU -> MAXPOOL2D as one call when neither intermediate tensor is needed
+        // (the pooling's backward then works from the indices and the pooled values alone)
+        if (fwd_skip_[j] && uses[rout.id] == 1 && !visible(rout) && (bwd_skip_[j] || !rout.trainable)) {
+            for (int k = j + 1; k < nn; ++k) {
+                const Node& q = g_.nodes[k];
+                if (q.op == MTL_OP_MAXPOOL2D && q.inputs[0].id == rout.id &&
+                    ((k < n_inference_nodes_) == (j < n_inference_nodes_) || n_inference_nodes_ == 0)) {
+                    fwd_pool_of_[p->second] = k;
+                    fwd_skip_[k] = 1;
                 }
             }
         }
@@ -403,7 +416,13 @@ void Model::forward_op(const Node& n) {
             const Symbol& w = n.inputs[1];
             mtl_conv2d_desc d = conv_desc(t1.shape, (int)w.shape[0], (int)w.shape[2], (int)w.shape[3], n.attrs);
             const int self = (int)(&n - &g_.nodes[0]);
-            if (fusion_ && fwd_relu_of_[self] >= 0)
+            if (fusion_ && fwd_pool_of_[self] >= 0) {
+                const int pk = fwd_pool_of_[self];
+                const Node& q = g_.nodes[pk];
+                mtl_conv2d_desc pd = conv_desc(q.inputs[0].shape, 1, q.attrs.kernel_size[0], q.attrs.kernel_size[1], q.attrs);
+                check(mtl_conv2d_fwd_act_pool(ctx_, T(q.outputs[0]), pool_idx_.at(pk), T(t1), T(w), T(n.inputs[2]), &d,
+                                              MTL_OP_RELU, &pd), "CONV2D+RELU+MAXPOOL2D forward");
+            } else if (fusion_ && fwd_relu_of_[self] >= 0)
                 check(mtl_conv2d_fwd_act(ctx_, T(g_.nodes[fwd_relu_of_[self]].outputs[0]), T(t1), T(w), T(n.inputs[2]), &d,
                                          MTL_OP_RELU), "CONV2D+RELU forward");
             else

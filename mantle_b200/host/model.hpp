@@ -58,7 +58,9 @@ class Model {
     void set_overwrite_first(bool on) { overwrite_first_ = on; }
 
     // Chain fusion (off by default).  On: a CONV2D whose only consumer is a RELU writes the RELU's
-    // output directly (mtl_conv2d_fwd_act) and the RELU node is not run; a MAXPOOL2D fed by a RELU
+    // output directly (mtl_conv2d_fwd_act) and the RELU node is not run -- and when a MAXPOOL2D is the
+    // RELU's only reader, the CONV2D writes the pooled values and indices (mtl_conv2d_fwd_act_pool) and
+    // the RELU output is not written either; a MAXPOOL2D fed by a RELU
     // that nothing else reads performs that RELU's backward as well (mtl_maxpool2d_bwd_idx_act).
     // A CONV2D's operand gradients come from one mtl_conv2d_bwd_fused call (the bias gradient is then
     // summed in a different order: equal within rounding, not bitwise).
@@ -109,6 +111,7 @@ class Model {
     int n_inference_nodes_ = 0;
     bool fusion_ = false;
     std::vector<int> fwd_relu_of_;     // per node: the RELU node a CONV2D also computes, or -1
+    std::vector<int> fwd_pool_of_;     // per node: the MAXPOOL2D node a CONV2D+RELU also computes, or -1
     std::vector<char> fwd_skip_;       // RELU nodes computed by their producer
     std::vector<int> bwd_relu_of_;     // per node: the RELU node whose backward a MAXPOOL2D also performs, or -1
     std::vector<char> bwd_skip_;       // RELU nodes whose backward their consumer performs

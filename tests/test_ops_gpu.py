@@ -381,6 +381,43 @@ def test_conv_with_fused_relu_equals_two_calls(ctx, case):
         assert (z.numpy() == 0).any() and (z.numpy() > 0).any()
 
 
+FUSED_CONV_POOL = [  # first-layer kernel that pools itself; tensor-core layer and odd shapes through scratch memory
+    (70, 1, 28, 28, 64, 5, 5, 2), (65, 3, 28, 28, 40, 3, 3, 1), (6, 64, 14, 14, 128, 5, 5, 2), (3, 2, 10, 12, 5, 3, 3, 1),
+]
+
+
+@pytest.mark.parametrize("case", FUSED_CONV_POOL)
+def test_conv_relu_pool_equals_three_calls(ctx, case):
+    """mtl_conv2d_fwd_act_pool == MAXPOOL2D.forward(RELU.forward(CONV2D.forward(...))): values and int32 indices."""
+    import ctypes as Cc
+    N, C, H, W, K, R, S, p = case
+    rng = np.random.default_rng(sum(case) + 5)
+    x = ctx.array(rng.normal(0, 1, (N, C, H, W)).astype(np.float32))
+    w = ctx.array((rng.normal(0, 1, (K, C, R, S)) / np.sqrt(C * R * S)).astype(np.float32))
+    b = ctx.array(rng.normal(0, 1, K).astype(np.float32))
+    kw = dict(padding=(p, p), stride=(1, 1), dilation=(1, 1))
+    oh, ow = mb.conv2d_out_shape((N, C, H, W), (K, C, R, S), **kw)
+    pkw = dict(kernel_size=(2, 2), stride=(2, 2), padding=(0, 0), dilation=(1, 1))
+    for mode in (mb.MATH_TF32X3, mb.MATH_FP32):
+        ctx.set_math_mode(mode)
+        try:
+            y, z = ctx.empty((N, K, oh, ow)), ctx.empty((N, K, oh, ow))
+            want_v, want_i = ctx.empty((N, K, oh // 2, ow // 2)), ctx.empty((N, K, oh // 2, ow // 2), np.int32)
+            ctx.forward_op(OP.CONV2D, y, x, w, b, **kw)
+            ctx.forward_op(OP.RELU, z, y)
+            ctx.forward_op(OP.MAXPOOL2D, want_v, z, indices=want_i, **pkw)
+            got_v, got_i = ctx.empty((N, K, oh // 2, ow // 2)), ctx.empty((N, K, oh // 2, ow // 2), np.int32)
+            d = mb.conv_desc(N, C, H, W, K, R, S, (p, p), (1, 1), (1, 1))
+            pd = mb.conv_desc(N, K, oh, ow, 1, 2, 2, (0, 0), (2, 2), (1, 1))
+            ctx._check(ctx.lib.mtl_conv2d_fwd_act_pool(ctx.handle, got_v.ptr, got_i.ptr, x.ptr, w.ptr, b.ptr, Cc.byref(d),
+                                                       int(OP.RELU), Cc.byref(pd)))
+        finally:
+            ctx.set_math_mode(mb.MATH_TF32X3)
+        assert np.array_equal(got_v.numpy(), want_v.numpy()), "values, mode %d" % mode
+        assert np.array_equal(got_i.numpy(), want_i.numpy()), "indices, mode %d" % mode
+        assert (got_v.numpy() == 0).any()
+
+
 FUSED_POOL = [  # (N, C, H, W, kernel, stride, pad): two-window float4, one-window float2, generic, overlapping
     (3, 4, 8, 8, 2, 2, 0), (3, 5, 14, 14, 2, 2, 0), (2, 3, 9, 9, 3, 2, 1), (2, 3, 8, 8, 3, 1, 1),
 ]
