@@ -109,6 +109,17 @@ MTL_API int32_t mtl_h2d(mtl_ctx* ctx, void* dst, const void* src_host, size_t by
 /* Model.forward's return / Model.inference's copies (model.mojo:99,108-110); dst is host;
  * waits for the stream. */
 MTL_API int32_t mtl_d2h(mtl_ctx* ctx, void* dst_host, const void* src, size_t bytes);
+/* Staged input copies on a second stream, so that the host-to-device copy of the next batch runs
+ * while the current step computes (no counterpart in the reference, whose Model.forward copies its
+ * inputs synchronously, model.mojo:117-119).  `slot` is 0..3; each slot stands for one staging buffer
+ * owned by the caller.
+ *   mtl_stage_h2d      copies on the copy stream once the compute stream has released the slot
+ *   mtl_stage_acquire  makes the compute stream wait for everything staged into the slot so far
+ *   mtl_stage_release  marks, on the compute stream, that the slot may be overwritten */
+MTL_API int32_t mtl_stage_h2d(mtl_ctx* ctx, int32_t slot, void* dst_dev, const void* src_host, size_t bytes);
+MTL_API int32_t mtl_stage_acquire(mtl_ctx* ctx, int32_t slot);
+MTL_API int32_t mtl_stage_release(mtl_ctx* ctx, int32_t slot);
+
 /* Asynchronous variants for pinned host memory (see mtl_host_alloc). */
 MTL_API int32_t mtl_h2d_async(mtl_ctx* ctx, void* dst, const void* src_host, size_t bytes);
 MTL_API int32_t mtl_d2h_async(mtl_ctx* ctx, void* dst_host, const void* src, size_t bytes);

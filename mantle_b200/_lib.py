@@ -86,6 +86,9 @@ SIGNATURES = {
     "mtl_maxpool2d_bwd": (_i32, [_vp, _vp, _vp, _vp, _pdesc, _i32]),
     "mtl_maxpool2d_bwd_idx": (_i32, [_vp, _vp, _vp, _vp, _pdesc, _i32]),
     "mtl_conv2d_bwd_fused": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _pdesc, _i32, _i32, _i32]),
+    "mtl_stage_h2d": (_i32, [_vp, _i32, _vp, _vp, C.c_size_t]),
+    "mtl_stage_acquire": (_i32, [_vp, _i32]),
+    "mtl_stage_release": (_i32, [_vp, _i32]),
     "mtl_conv2d_fwd_act_pool": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _pdesc, _i32, _pdesc]),
     "mtl_conv2d_fwd_act": (_i32, [_vp, _vp, _vp, _vp, _vp, _pdesc, _i32]),
     "mtl_maxpool2d_bwd_idx_act": (_i32, [_vp, _vp, _vp, _vp, _vp, _pdesc, _i32, _i32]),

@@ -36,6 +36,11 @@ struct mtl_ctx {
     void* dp = nullptr;
     // cached driver entry point for tensor-map encoding (tma.cuh)
     void* encode_tiled = nullptr;
+    // staged input copies (mtl_stage_*): a copy stream and two events per slot
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t stage_ready[4] = {0};
+    cudaEvent_t stage_free[4] = {0};
+    bool stage_released[4] = {false, false, false, false};
     // per-kernel event timing (mtl_prof_*)
     bool prof_on = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events[MTL_PROF_KERNELS];

@@ -119,6 +119,14 @@ int32_t mtl_ctx_destroy(mtl_ctx* ctx) {
         if (ctx->t0[i]) cudaEventDestroy(ctx->t0[i]);
         if (ctx->t1[i]) cudaEventDestroy(ctx->t1[i]);
     }
+    for (int i = 0; i < 4; ++i) {
+        if (ctx->stage_ready[i]) cudaEventDestroy(ctx->stage_ready[i]);
+        if (ctx->stage_free[i]) cudaEventDestroy(ctx->stage_free[i]);
+    }
+    if (ctx->copy_stream) {
+        cudaStreamSynchronize(ctx->copy_stream);
+        cudaStreamDestroy(ctx->copy_stream);
+    }
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->ws2) cudaFree(ctx->ws2);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
@@ -226,6 +234,50 @@ int32_t mtl_d2h_async(mtl_ctx* ctx, void* dst_host, const void* src, size_t byte
     MTL_CHECK_CTX(ctx);
     MTL_REQUIRE(ctx, (dst_host && src) || bytes == 0, "null pointer in mtl_d2h_async");
     if (bytes) MTL_CUDA(ctx, cudaMemcpyAsync(dst_host, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return MTL_OK;
+}
+
+static int32_t stage_setup(mtl_ctx* ctx, int32_t slot) {
+    MTL_REQUIRE(ctx, slot >= 0 && slot < 4, "staging slot %d out of range", slot);
+    if (!ctx->copy_stream) MTL_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+    if (!ctx->stage_ready[slot]) {
+        MTL_CUDA(ctx, cudaEventCreateWithFlags(&ctx->stage_ready[slot], cudaEventDisableTiming));
+        MTL_CUDA(ctx, cudaEventCreateWithFlags(&ctx->stage_free[slot], cudaEventDisableTiming));
+    }
+    return MTL_OK;
+}
+
+int32_t mtl_stage_h2d(mtl_ctx* ctx, int32_t slot, void* dst_dev, const void* src_host, size_t bytes) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, !ctx->capturing, "staged copies cannot be part of a captured step");
+    int32_t rc = stage_setup(ctx, slot);
+    if (rc) return rc;
+    MTL_REQUIRE(ctx, (dst_dev && src_host) || bytes == 0, "null pointer in mtl_stage_h2d");
+    if (ctx->stage_released[slot]) {
+        MTL_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->stage_free[slot], 0));
+        ctx->stage_released[slot] = false;
+    }
+    if (bytes) MTL_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->copy_stream));
+    return MTL_OK;
+}
+
+int32_t mtl_stage_acquire(mtl_ctx* ctx, int32_t slot) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, !ctx->capturing, "staged copies cannot be part of a captured step");
+    int32_t rc = stage_setup(ctx, slot);
+    if (rc) return rc;
+    MTL_CUDA(ctx, cudaEventRecord(ctx->stage_ready[slot], ctx->copy_stream));
+    MTL_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->stage_ready[slot], 0));
+    return MTL_OK;
+}
+
+int32_t mtl_stage_release(mtl_ctx* ctx, int32_t slot) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, !ctx->capturing, "staged copies cannot be part of a captured step");
+    int32_t rc = stage_setup(ctx, slot);
+    if (rc) return rc;
+    MTL_CUDA(ctx, cudaEventRecord(ctx->stage_free[slot], ctx->stream));
+    ctx->stage_released[slot] = true;
     return MTL_OK;
 }
 

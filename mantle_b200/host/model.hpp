@@ -41,6 +41,7 @@ class Model {
     void execute(int num_nodes);
     void backward_enqueue();
     float* loss_device() const;
+    float* input_device(int i) const { return T(g_.inputs.at((size_t)i)); }
 
     // Parameters.tensors / Parameters.grads access (host copies).
     void get_tensor(int symbol_id, float* host_out) const;

@@ -36,6 +36,8 @@ Trainer::~Trainer() {
     model_.after_backward_node = nullptr;
     model_.after_backward_user = nullptr;
     if (graph_) mtl_graph_destroy(model_.ctx(), graph_);
+    for (int b = 0; b < 2; ++b)
+        if (stage_[b]) mtl_free(model_.ctx(), stage_[b]);
     mtl_host_free(model_.ctx(), own_loss_);
 }
 
@@ -76,44 +78,70 @@ void Trainer::node_done(int node) {
     }
 }
 
-void Trainer::enqueue_body(float* pinned_loss) {
-    mtl_ctx* ctx = model_.ctx();
+void Trainer::enqueue_body() {
     model_.execute((int)model_.graph().nodes.size());
-    ck(ctx, mtl_d2h_async(ctx, pinned_loss, model_.loss_device(), 4), "loss read-back");
     adam_.zero_grad();
     model_.backward_enqueue();
     adam_.step_captured();
 }
 
+// Inputs travel host -> staging buffer on the copy stream (two buffers, used in turn) and staging
+// buffer -> input tensors on the compute stream, so a caller that enqueues step i + 1 while step i
+// is still running gets its copy overlapped with that step's kernels.
+void Trainer::stage_inputs(const std::vector<const float*>& host_inputs) {
+    mtl_ctx* ctx = model_.ctx();
+    const Graph& g = model_.graph();
+    if (host_inputs.size() != g.inputs.size()) throw Error(MTL_ERR_INVALID, "wrong number of inputs");
+    if (!stage_[0]) {
+        stage_floats_ = 0;
+        for (auto& s : g.inputs) stage_floats_ += (s.shape.num_elements() + 63) / 64 * 64;
+        for (int b = 0; b < 2; ++b)
+            ck(ctx, mtl_malloc(ctx, (size_t)std::max<int64_t>(stage_floats_, 64) * 4, (void**)&stage_[b]), "input staging buffer");
+    }
+    const int slot = (int)(staged_ & 1);
+    ++staged_;
+    int64_t off = 0;
+    for (size_t i = 0; i < host_inputs.size(); ++i) {
+        const int64_t n = g.inputs[i].shape.num_elements();
+        ck(ctx, mtl_stage_h2d(ctx, slot, stage_[slot] + off, host_inputs[i], (size_t)n * 4), "input copy");
+        off += (n + 63) / 64 * 64;
+    }
+    ck(ctx, mtl_stage_acquire(ctx, slot), "input copy wait");
+    off = 0;
+    for (size_t i = 0; i < host_inputs.size(); ++i) {
+        const int64_t n = g.inputs[i].shape.num_elements();
+        ck(ctx, mtl_copy_f32(ctx, model_.input_device((int)i), stage_[slot] + off, n, 0), "input placement");
+        off += (n + 63) / 64 * 64;
+    }
+    ck(ctx, mtl_stage_release(ctx, slot), "input staging release");
+}
+
 void Trainer::step_async(const std::vector<const float*>& host_inputs, float* pinned_loss) {
     mtl_ctx* ctx = model_.ctx();
-    model_.copy_inputs_async(host_inputs);
+    if (!host_inputs.empty()) stage_inputs(host_inputs);  // else: keep the inputs already resident
     ++steps_;
     if (!use_graph_ || steps_ == 1) {
         // the first step also sizes the scratch workspace, which must not grow during capture
-        enqueue_body(pinned_loss);
-        return;
-    }
-    if (!graph_ || graph_loss_slot_ != pinned_loss) {
-        if (graph_) {
-            ck(ctx, mtl_graph_destroy(ctx, graph_), "graph destroy");
-            graph_ = nullptr;
-        }
-        ck(ctx, mtl_graph_begin(ctx), "graph capture begin");
-        try {
-            enqueue_body(pinned_loss);
-        } catch (...) {
-            mtl_graph* dead = nullptr;
-            mtl_graph_end(ctx, &dead);
-            if (dead) mtl_graph_destroy(ctx, dead);
-            throw;
-        }
-        ck(ctx, mtl_graph_end(ctx, &graph_), "graph capture end");
-        graph_loss_slot_ = pinned_loss;
+        enqueue_body();
     } else {
-        adam_.note_replayed_step();
+        if (!graph_) {
+            ck(ctx, mtl_graph_begin(ctx), "graph capture begin");
+            try {
+                enqueue_body();
+            } catch (...) {
+                mtl_graph* dead = nullptr;
+                mtl_graph_end(ctx, &dead);
+                if (dead) mtl_graph_destroy(ctx, dead);
+                throw;
+            }
+            ck(ctx, mtl_graph_end(ctx, &graph_), "graph capture end");
+        } else {
+            adam_.note_replayed_step();
+        }
+        ck(ctx, mtl_graph_launch(ctx, graph_), "graph launch");
     }
-    ck(ctx, mtl_graph_launch(ctx, graph_), "graph launch");
+    // the loss tensor is not touched by the backward pass, so it is read after the whole step
+    ck(ctx, mtl_d2h_async(ctx, pinned_loss, model_.loss_device(), 4), "loss read-back");
 }
 
 float Trainer::step(const std::vector<const float*>& host_inputs) {

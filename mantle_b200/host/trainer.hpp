@@ -26,7 +26,8 @@ class Trainer {
     bool graph_active() const { return graph_ != nullptr; }
 
    private:
-    void enqueue_body(float* pinned_loss);
+    void enqueue_body();
+    void stage_inputs(const std::vector<const float*>& host_inputs);
     static void node_done_thunk(void* self, int node);
     void node_done(int node);
     void flush_bucket();
@@ -37,7 +38,9 @@ class Trainer {
     int64_t bucket_bytes_;
     int world_ = 1;
     mtl_graph* graph_ = nullptr;
-    float* graph_loss_slot_ = nullptr;  // the pinned slot the captured copy writes to
+    float* stage_[2] = {nullptr, nullptr};  // device staging buffers for the inputs, used in turn
+    int64_t stage_floats_ = 0;
+    int64_t staged_ = 0;
     float* own_loss_ = nullptr;         // pinned word used by step()
     int64_t steps_ = 0;
     // data-parallel bucketing: for every node, the trainable parameters whose gradient is final

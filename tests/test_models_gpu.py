@@ -193,3 +193,37 @@ def test_chain_fusion_matches_unfused(ctx, strict):
     for u, v in zip(a[1] + a[2] + [a[3]], b[1] + b[2] + [b[3]]):
         assert_close(u, v, 2e-4, 1e-6, "fused vs unfused")
     assert ctx.device_status() == 0
+
+
+def test_pipelined_steps_equal_synchronous_steps(ctx):
+    """Trainer.step_async with a new batch every call (host copy of batch i + 1 staged while step i
+    runs, one pinned loss word per step) gives the losses of one synchronous step() per batch."""
+    import ctypes as C
+    B, steps = 16, 7
+    build = lambda ns, gg: build_cnn(ns, gg, B)
+    rng = np.random.default_rng(31)
+    xs = rng.uniform(0, 1, (steps, B, 1, 28, 28)).astype(np.float32)
+    ys = np.eye(10, dtype=np.float32)[rng.integers(0, 10, (steps, B))]
+    results = []
+    for mode in ("sync", "async"):
+        (g, m), _ = make_pair(ctx, build, seed=30)
+        tr = host_api.Trainer(m, host_api.Adam(m, lr=1e-3), use_graph=True)
+        if mode == "sync":
+            losses = [tr.step(xs[i], ys[i]) for i in range(steps)]
+        else:
+            px, py, pl = C.c_void_p(), C.c_void_p(), C.c_void_p()
+            ctx._check(ctx.lib.mtl_host_alloc(ctx.handle, xs.nbytes, C.byref(px)))
+            ctx._check(ctx.lib.mtl_host_alloc(ctx.handle, ys.nbytes, C.byref(py)))
+            ctx._check(ctx.lib.mtl_host_alloc(ctx.handle, 4 * steps, C.byref(pl)))
+            C.memmove(px.value, xs.ctypes.data, xs.nbytes)
+            C.memmove(py.value, ys.ctypes.data, ys.nbytes)
+            for i in range(steps):
+                tr.step_async_ptrs([px.value + i * xs[0].nbytes, py.value + i * ys[0].nbytes], pl.value + 4 * i)
+            ctx.sync()
+            losses = list(np.ctypeslib.as_array(C.cast(pl, C.POINTER(C.c_float)), (steps,)).copy())
+            for p in (px, py, pl):
+                ctx.lib.mtl_host_free(ctx.handle, p)
+        tr.close()
+        results.append(np.asarray(losses, np.float32))
+    assert np.array_equal(results[0], results[1]), results
+    assert results[0][0] != results[0][-1]
