@@ -194,8 +194,7 @@ def run_ours(args):
     if world > 1:
         # the collective library's banner and debug lines must not reach stdout: rank 0 prints
         # exactly one JSON line there
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE"):
-            os.environ["NCCL_DEBUG_FILE"] = os.environ.get("NCCL_DEBUG_FILE", "/dev/stderr")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         import torch.distributed as dist
         dist.init_process_group("gloo", rank=rank, world_size=world)  # control plane only
 
@@ -211,7 +210,15 @@ def run_ours(args):
             idbuf = torch.tensor(list(raw), dtype=torch.uint8)
         dist.broadcast(idbuf, 0)
         raw = (C.c_uint8 * mb._lib.MTL_DP_ID_BYTES)(*idbuf.tolist())
-        ctx._check(lib.mtl_dp_init(ctx.handle, raw, rank, world))
+        # NCCL prints its version banner on file descriptor 1 while the communicator is created
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            ctx._check(lib.mtl_dp_init(ctx.handle, raw, rank, world))
+        finally:
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
 
     B = GLOBAL_BATCH // world
 
