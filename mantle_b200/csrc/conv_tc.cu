@@ -323,6 +323,44 @@ __global__ void __launch_bounds__(256) k_weights_relayout(float* __restrict__ hi
     }
 }
 
+// Paired layout for layers with at most 64 output channels: [r * SP + sp][128 rows][inner], row
+// 32 * q + 16 * h + j holding channel 16 * q + j of logical tap (r, 2 * sp + h); rows past the channel
+// count and the missing partner of an odd last tap are zero.  SP = ceil(S / 2).
+template <bool SPLIT>
+__global__ void __launch_bounds__(256) k_weights_relayout_paired(float* __restrict__ hi, float* __restrict__ lo,
+                                                                 const float* __restrict__ Wt, int K, int C, int R,
+                                                                 int S, int flip) {
+    const int SP = (S + 1) / 2;
+    const int inner = flip ? K : C, mid = flip ? C : K;
+    int64_t total = (int64_t)R * SP * 128 * inner;
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t o = tid; o < total; o += stride) {
+        int i0 = (int)(o % inner);
+        int64_t q = o / inner;
+        int row = (int)(q % 128);
+        int g = (int)(q / 128);
+        // rows are grouped per 32 (one TMEM lane quadrant = one epilogue warp): 16 channels of half 0,
+        // then the same 16 channels of half 1, so that the two halves of a channel meet in one warp
+        int h = (row >> 4) & 1, i1 = (row >> 5) * 16 + (row & 15);
+        int r = g / SP, s = 2 * (g - r * SP) + h;
+        float v = 0.0f;
+        if (i1 < mid && s < S) {
+            int k = flip ? i0 : i1, c = flip ? i1 : i0;
+            int rr = flip ? R - 1 - r : r, ss = flip ? S - 1 - s : s;
+            v = Wt[(((int64_t)k * C + c) * R + rr) * S + ss];
+        }
+        if (SPLIT) {
+            float hh, ll;
+            split_tf32(v, hh, ll);
+            hi[o] = hh;
+            lo[o] = ll;
+        } else {
+            hi[o] = v;
+        }
+    }
+}
+
 // Picks the pixel box {bw, bh, bn} (product <= 128) that wastes the fewest accumulator rows.
 void choose_box(int OW, int OH, int N, int* bw_, int* bh_, int* bn_) {
     double best = -1.0;
@@ -379,6 +417,15 @@ struct ConvTParams {
     const float* bias;
     int accumulate;
     int relu;
+    // Tap pairing (at most 64 output channels): of every 32 rows of the weight tile, 16 hold tap
+    // (r, 2*si) of 16 channels and 16 hold tap (r, 2*si + 1) of the same channels; both see the pixel
+    // box of the first tap, so the second half of the accumulator is the second tap's contribution to
+    // the pixel one column to the LEFT, and the epilogue adds half1[column + 1] to half0[column] with
+    // a warp shuffle.  The box is one column wider than the image.
+    int paired;
+    int s_count, s_step;    // iterations over the kernel width and their tap stride (1, or 2 when paired)
+    int acc_stride;         // TMEM columns between the two accumulators (248 when paired: the shifted
+                            // read of the second one must stay inside the 512 allocated columns)
     int vec_ok;             // channel planes are 16-byte aligned: four adjacent pixels may leave as a float4
     int32_t* status;
 };
@@ -405,7 +452,7 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
     const int tiles_m = p.tiles_w * p.tiles_h * p.tiles_nb;
     const int num_tiles = tiles_m * p.tiles_k;
     const int cblocks = (p.Cin + BK - 1) / BK;
-    const int kb_per_seg = p.R * p.S * cblocks;
+    const int kb_per_seg = p.R * p.s_count * cblocks;
     const int kb_total = kb_per_seg * p.nseg;
 
     if (threadIdx.x == 0) {
@@ -446,7 +493,7 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                     const CUtensorMap* mx = p.segA[seg] ? &mapX1 : &mapX0;
                     const CUtensorMap* mw = p.segB[seg] ? &mapW1 : &mapW0;
                     for (int r = 0; r < p.R && ok; ++r)
-                        for (int s = 0; s < p.S && ok; ++s)
+                        for (int si = 0; si < p.s_count && ok; ++si)
                             for (int cb = 0; cb < cblocks; ++cb) {
                                 if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) ok = false;
                                 if (__any_sync(0x3u, !ok)) { ok = false; break; }
@@ -454,8 +501,8 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                                 uint8_t* sb = sa + kTABytes;
                                 if (lane == 0) mbar_arrive_expect_tx(&full[stage], tx);
                                 __syncwarp(0x3u);
-                                if (lane == 0) tma_load_3d(sa, mw, &full[stage], cb * BK, kt * BM, r * p.S + s);
-                                else tma_load_4d(sb, mx, &full[stage], cb * BK, ow0 + s - p.pw, oh0 + r - p.ph, n0);
+                                if (lane == 0) tma_load_3d(sa, mw, &full[stage], cb * BK, kt * BM, r * p.s_count + si);
+                                else tma_load_4d(sb, mx, &full[stage], cb * BK, ow0 + si * p.s_step - p.pw, oh0 + r - p.ph, n0);
                                 if (++stage == kTStages) { stage = 0; phase ^= 1u; }
                             }
                 }
@@ -474,7 +521,7 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                 const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
                 if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
                 tc_fence_after_sync();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * 256);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * p.acc_stride);
                 for (int kb = 0; kb < kb_total; ++kb) {
                     if (!mbar_wait(&full[stage], phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
                     tc_fence_after_sync();
@@ -504,8 +551,9 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
             const int th = mt % p.tiles_h;
             const int tnb = mt / p.tiles_h;
             const int ow0 = tw * p.bw, oh0 = th * p.bh, n0 = tnb * p.bn;
-            const int k = kt * BM + krow;
-            const bool kvalid = k < p.Kout;
+            // paired: this warp's 32 rows are 16 channels twice (see k_weights_relayout_paired)
+            const int k = p.paired ? quad * 16 + (lane & 15) : kt * BM + krow;
+            const bool kvalid = k < p.Kout && (!p.paired || lane < 16);
             const float bv = (kvalid && p.bias) ? __ldg(p.bias + k) : 0.0f;
             const int acc = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
@@ -543,8 +591,21 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
 #pragma unroll 1
             for (int c = 0; c * 32 < p.npix; ++c) {
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * 256 + c * 32), r);
-                tmem_ld_wait();
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride + c * 32), r);
+                if (p.paired) {
+                    // lanes 16-31 hold the second tap of the channels of lanes 0-15: fetch it one
+                    // column to the right and add it across the warp
+                    uint32_t r2[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride + c * 32 + 1), r2);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float u = __shfl_down_sync(0xffffffffu, __uint_as_float(r2[i]), 16);
+                        r[i] = __float_as_uint(__uint_as_float(r[i]) + u);
+                    }
+                } else {
+                    tmem_ld_wait();
+                }
                 __syncwarp();
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
@@ -564,8 +625,8 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
 #pragma unroll
                     for (int it = 0; it < 8; ++it) {
                         const int ch = it * 4 + chl;
-                        const int kk = kt * BM + quad * 32 + ch;
-                        if (kk < p.Kout) {
+                        const int kk = p.paired ? quad * 16 + ch : kt * BM + quad * 32 + ch;
+                        if (kk < p.Kout && (!p.paired || ch < 16)) {
                             const float4 val = *reinterpret_cast<const float4*>(stg + ch * 36 + sub * 4);
                             float* base = p.out + (int64_t)kk * plane;
                             if (vec) {
@@ -642,6 +703,25 @@ int32_t launch_igemm(mtl_ctx* ctx, const CUtensorMap* maps, const ConvTcParams& 
     return MTL_OK;
 }
 
+bool igemm_channel_major(const IgemmCall& c) {
+    return c.Kout > 32 && (int64_t)c.N * c.OH * c.OW >= 1024 && (int64_t)c.N * c.Kout * c.OH * c.OW < (1ll << 31) &&
+           !(getenv("MANTLE_CONV_CHANNEL_MAJOR") && atoi(getenv("MANTLE_CONV_CHANNEL_MAJOR")) == 0);
+}
+// Two taps per instruction when the layer has at most 64 output channels (see ConvTParams::paired).
+bool igemm_paired(const IgemmCall& c) {
+    // Pairing shortens the main loop but lengthens the epilogue (second TMEM read, shuffles): it pays
+    // only when the reduction per tile is long enough for the main loop to be the longer of the two.
+    const int paired_kblocks = c.R * ((c.S + 1) / 2) * ((c.Cin + 31) / 32);
+    return igemm_channel_major(c) && c.Kout <= 64 && c.S >= 2 && c.OW + 1 <= 240 && paired_kblocks >= 32 &&
+           !(getenv("MANTLE_CONV_PAIRED") && atoi(getenv("MANTLE_CONV_PAIRED")) == 0);
+}
+// Floats of one re-laid-out copy of the weights.
+size_t igemm_weight_floats(const IgemmCall& c) {
+    const size_t plain = (size_t)c.wK * c.wC * c.R * c.S;
+    const size_t paired = (size_t)c.R * ((c.S + 1) / 2) * 128 * c.Cin;
+    return igemm_paired(c) && paired > plain ? paired : plain;
+}
+
 // Channels-last copy (hi [, lo]) of an NCHW tensor; see k_nchw_to_nhwc for `colsum`.
 int32_t stage_nhwc(mtl_ctx* ctx, float* hi, float* lo, const float* src, int N, int C, int HW, int x3, float* colsum) {
     dim3 tg((unsigned)((HW + 31) / 32), (unsigned)((C + 31) / 32), (unsigned)N);
@@ -657,7 +737,7 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
 int32_t run_igemm(mtl_ctx* ctx, const IgemmCall& c, int x3) {
     const int HW = c.IH * c.IW;
     const size_t n_act = (size_t)c.N * c.Cin * HW;
-    const size_t n_wt = (size_t)c.wK * c.wC * c.R * c.S;
+    const size_t n_wt = igemm_weight_floats(c);
     const size_t act_pad = (n_act + 63) & ~(size_t)63, wt_pad = (n_wt + 63) & ~(size_t)63;
     const int parts = x3 ? 2 : 1;
     void* ws;
@@ -678,21 +758,42 @@ int32_t run_igemm(mtl_ctx* ctx, const IgemmCall& c, int x3) {
 
 // Weight re-layout and the implicit-GEMM kernel; the channels-last activations are already in place.
 int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, float* a_lo, float* w_hi, float* w_lo) {
-    const size_t n_wt = (size_t)c.wK * c.wC * c.R * c.S;
+    const size_t n_wt = igemm_weight_floats(c);
     int32_t rc = MTL_OK;
+    const bool channel_major = igemm_channel_major(c);
+    const bool paired = igemm_paired(c);
     int wgrid = mtl_grid_for((int64_t)n_wt, 256, ctx->sm_count, 8);
-    if (x3) k_weights_relayout<true><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
-    else k_weights_relayout<false><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
+    if (paired) {
+        if (x3) k_weights_relayout_paired<true><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
+        else k_weights_relayout_paired<false><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
+    } else {
+        if (x3) k_weights_relayout<true><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
+        else k_weights_relayout<false><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
+    }
     MTL_LAUNCHED(ctx);
 
-    const bool channel_major = c.Kout >= 64 && (int64_t)c.N * c.OH * c.OW >= 1024 &&
-                               (int64_t)c.N * c.Kout * c.OH * c.OW < (1ll << 31) &&
-                               !(getenv("MANTLE_CONV_CHANNEL_MAJOR") && atoi(getenv("MANTLE_CONV_CHANNEL_MAJOR")) == 0);
     if (channel_major) {
         ConvTParams q;
         q.N = c.N; q.OH = c.OH; q.OW = c.OW; q.Kout = c.Kout; q.Cin = c.Cin;
         q.R = c.R; q.S = c.S; q.ph = c.ph; q.pw = c.pw;
-        choose_box_n(c.OW, c.OH, c.N, 256, &q.bw, &q.bh, &q.bn);
+        q.paired = paired ? 1 : 0;
+        q.s_count = paired ? (c.S + 1) / 2 : c.S;
+        q.s_step = paired ? 2 : 1;
+        q.acc_stride = paired ? 248 : 256;
+        if (paired) {
+            // whole rows plus the extra column; the box that fills most of 240 columns
+            q.bw = c.OW + 1;
+            double best = -1.0;
+            for (int bh = 1; bh <= c.OH && q.bw * bh <= 240; ++bh) {
+                int bn = 240 / (q.bw * bh);
+                if (bn > c.N) bn = c.N;
+                int64_t tiles = (int64_t)((c.OH + bh - 1) / bh) * ((c.N + bn - 1) / bn);
+                double eff = (double)c.OW * c.OH * c.N / ((double)tiles * 240.0) + 1e-4 * bh;
+                if (eff > best) { best = eff; q.bh = bh; q.bn = bn; }
+            }
+        } else {
+            choose_box_n(c.OW, c.OH, c.N, 256, &q.bw, &q.bh, &q.bn);
+        }
         q.npix = q.bw * q.bh * q.bn;
         q.n_mma = (q.npix + 15) / 16 * 16;
         q.tiles_w = (c.OW + q.bw - 1) / q.bw;
@@ -714,8 +815,9 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
             uint32_t abox[4] = {BK, (uint32_t)q.bw, (uint32_t)q.bh, (uint32_t)q.bn};
             rc = mtl_encode_tmap(ctx, &tm[i], a, 4, adims, astr, abox);
             if (rc) return rc;
-            uint64_t wdims[3] = {(uint64_t)c.Cin, (uint64_t)c.Kout, (uint64_t)(c.R * c.S)};
-            uint64_t wstr[2] = {(uint64_t)c.Cin * 4, (uint64_t)c.Kout * c.Cin * 4};
+            const uint64_t wrows = paired ? 128 : (uint64_t)c.Kout;
+            uint64_t wdims[3] = {(uint64_t)c.Cin, wrows, (uint64_t)(c.R * q.s_count)};
+            uint64_t wstr[2] = {(uint64_t)c.Cin * 4, wrows * c.Cin * 4};
             uint32_t wbox[3] = {BK, (uint32_t)BM, 1};
             rc = mtl_encode_tmap(ctx, &tm[2 + i], w, 3, wdims, wstr, wbox);
             if (rc) return rc;
@@ -1152,7 +1254,12 @@ int32_t mtl_conv_bwd_fused_tc(mtl_ctx* ctx, float* dX, float* dW, float* db, con
     int32_t rc = wgrad_plan(ctx, g, x3, &p, &n_part);
     if (rc) return rc;
     const size_t n_u = (size_t)g.N * g.K * g.OH * g.OW, n_x = (size_t)g.N * g.C * g.H * g.W;
-    const size_t n_wt = (size_t)g.K * g.C * g.R * g.S;
+    IgemmCall c;
+    c.N = g.N; c.Cin = g.K; c.IH = g.OH; c.IW = g.OW; c.Kout = g.C; c.OH = g.H; c.OW = g.W;
+    c.R = g.R; c.S = g.S; c.ph = g.R - 1 - g.ph; c.pw = g.S - 1 - g.pw;
+    c.act = ug; c.wt = Wt; c.wK = g.K; c.wC = g.C; c.flip = 1;
+    c.out = dX; c.bias = nullptr; c.accumulate = acc_dx; c.relu = 0;
+    const size_t n_wt = igemm_weight_floats(c);
     const size_t u_pad = (n_u + 63) & ~(size_t)63, x_pad = (n_x + 63) & ~(size_t)63, wt_pad = (n_wt + 63) & ~(size_t)63;
     const int parts = x3 ? 2 : 1;
     const int ptiles = (g.OH * g.OW + 31) / 32;
@@ -1188,10 +1295,5 @@ int32_t mtl_conv_bwd_fused_tc(mtl_ctx* ctx, float* dX, float* dW, float* db, con
     rc = wgrad_core(ctx, dW, u_hi, u_lo, x_hi, x_lo, partial, p, g, acc_dw, x3);
     if (rc) return rc;
     // input gradient: the same copy of ug is the activation operand; its weights go where X was
-    IgemmCall c;
-    c.N = g.N; c.Cin = g.K; c.IH = g.OH; c.IW = g.OW; c.Kout = g.C; c.OH = g.H; c.OW = g.W;
-    c.R = g.R; c.S = g.S; c.ph = g.R - 1 - g.ph; c.pw = g.S - 1 - g.pw;
-    c.act = ug; c.wt = Wt; c.wK = g.K; c.wC = g.C; c.flip = 1;
-    c.out = dX; c.bias = nullptr; c.accumulate = acc_dx; c.relu = 0;
     return run_igemm_core(ctx, c, x3, u_hi, u_lo, region, x3 ? region + wt_pad : nullptr);
 }

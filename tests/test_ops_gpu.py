@@ -291,6 +291,7 @@ TC_CONV = [  # (N, C, H, W, K, R, S, pad): stride 1, dilation 1 -> implicit GEMM
     (2, 64, 56, 56, 64, 3, 3, 1),      # >= 4096 output pixels: the kernel gradient also runs on tensor cores
     (24, 64, 14, 14, 128, 5, 5, 2),    # conv2 of the widened CNN
     (40, 32, 12, 12, 48, 3, 3, 1),     # out-channels not a multiple of the tile, odd pixel boxes
+    (9, 160, 10, 12, 40, 4, 5, 2),     # <= 64 output channels and a long reduction: two taps per instruction (forward)
 ]
 
 
