@@ -326,11 +326,13 @@ __global__ void __launch_bounds__(256) k_weights_relayout(float* __restrict__ hi
 // Paired layout for layers with at most 64 output channels: [r * SP + sp][128 rows][inner], row
 // 32 * q + 16 * h + j holding channel 16 * q + j of logical tap (r, 2 * sp + h); rows past the channel
 // count and the missing partner of an odd last tap are zero.  SP = ceil(S / 2).
+// pair == 0 ("spread"): one tap per slot, half 1 all zero -- only the row order is used, so that the
+// (at most 64) channels are shared by all four epilogue warps.
 template <bool SPLIT>
 __global__ void __launch_bounds__(256) k_weights_relayout_paired(float* __restrict__ hi, float* __restrict__ lo,
                                                                  const float* __restrict__ Wt, int K, int C, int R,
-                                                                 int S, int flip) {
-    const int SP = (S + 1) / 2;
+                                                                 int S, int flip, int pair) {
+    const int SP = pair ? (S + 1) / 2 : S;
     const int inner = flip ? K : C, mid = flip ? C : K;
     int64_t total = (int64_t)R * SP * 128 * inner;
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -343,9 +345,9 @@ __global__ void __launch_bounds__(256) k_weights_relayout_paired(float* __restri
         // rows are grouped per 32 (one TMEM lane quadrant = one epilogue warp): 16 channels of half 0,
         // then the same 16 channels of half 1, so that the two halves of a channel meet in one warp
         int h = (row >> 4) & 1, i1 = (row >> 5) * 16 + (row & 15);
-        int r = g / SP, s = 2 * (g - r * SP) + h;
+        int r = g / SP, s = pair ? 2 * (g - r * SP) + h : g - r * SP;
         float v = 0.0f;
-        if (i1 < mid && s < S) {
+        if (i1 < mid && s < S && (pair || h == 0)) {
             int k = flip ? i0 : i1, c = flip ? i1 : i0;
             int rr = flip ? R - 1 - r : r, ss = flip ? S - 1 - s : s;
             v = Wt[(((int64_t)k * C + c) * R + rr) * S + ss];
@@ -422,7 +424,7 @@ struct ConvTParams {
     // box of the first tap, so the second half of the accumulator is the second tap's contribution to
     // the pixel one column to the LEFT, and the epilogue adds half1[column + 1] to half0[column] with
     // a warp shuffle.  The box is one column wider than the image.
-    int paired;
+    int paired;             // 0 off, 1 two taps per instruction, 2 only the row order ("spread": no second tap)
     int s_count, s_step;    // iterations over the kernel width and their tap stride (1, or 2 when paired)
     int acc_stride;         // TMEM columns between the two accumulators (248 when paired: the shifted
                             // read of the second one must stay inside the 512 allocated columns)
@@ -592,7 +594,7 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
             for (int c = 0; c * 32 < p.npix; ++c) {
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride + c * 32), r);
-                if (p.paired) {
+                if (p.paired == 1) {
                     // lanes 16-31 hold the second tap of the channels of lanes 0-15: fetch it one
                     // column to the right and add it across the warp
                     uint32_t r2[32];
@@ -715,11 +717,18 @@ bool igemm_paired(const IgemmCall& c) {
     return igemm_channel_major(c) && c.Kout <= 64 && c.S >= 2 && c.OW + 1 <= 240 && paired_kblocks >= 32 &&
            !(getenv("MANTLE_CONV_PAIRED") && atoi(getenv("MANTLE_CONV_PAIRED")) == 0);
 }
+// At most 64 output channels without pairing: the channels are still spread over the four TMEM lane
+// quadrants (16 each) so that all four epilogue warps store, instead of two doing all of it.
+bool igemm_spread(const IgemmCall& c) {
+    return igemm_channel_major(c) && c.Kout <= 64 && !igemm_paired(c) &&
+           !(getenv("MANTLE_CONV_SPREAD") && atoi(getenv("MANTLE_CONV_SPREAD")) == 0);
+}
 // Floats of one re-laid-out copy of the weights.
 size_t igemm_weight_floats(const IgemmCall& c) {
     const size_t plain = (size_t)c.wK * c.wC * c.R * c.S;
-    const size_t paired = (size_t)c.R * ((c.S + 1) / 2) * 128 * c.Cin;
-    return igemm_paired(c) && paired > plain ? paired : plain;
+    if (igemm_paired(c)) return (size_t)c.R * ((c.S + 1) / 2) * 128 * c.Cin;
+    if (igemm_spread(c)) return (size_t)c.R * c.S * 128 * c.Cin;
+    return plain;
 }
 
 // Channels-last copy (hi [, lo]) of an NCHW tensor; see k_nchw_to_nhwc for `colsum`.
@@ -762,10 +771,11 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
     int32_t rc = MTL_OK;
     const bool channel_major = igemm_channel_major(c);
     const bool paired = igemm_paired(c);
+    const bool spread = igemm_spread(c);
     int wgrid = mtl_grid_for((int64_t)n_wt, 256, ctx->sm_count, 8);
-    if (paired) {
-        if (x3) k_weights_relayout_paired<true><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
-        else k_weights_relayout_paired<false><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
+    if (paired || spread) {
+        if (x3) k_weights_relayout_paired<true><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip, paired ? 1 : 0);
+        else k_weights_relayout_paired<false><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip, paired ? 1 : 0);
     } else {
         if (x3) k_weights_relayout<true><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
         else k_weights_relayout<false><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
@@ -776,7 +786,7 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
         ConvTParams q;
         q.N = c.N; q.OH = c.OH; q.OW = c.OW; q.Kout = c.Kout; q.Cin = c.Cin;
         q.R = c.R; q.S = c.S; q.ph = c.ph; q.pw = c.pw;
-        q.paired = paired ? 1 : 0;
+        q.paired = paired ? 1 : (spread ? 2 : 0);
         q.s_count = paired ? (c.S + 1) / 2 : c.S;
         q.s_step = paired ? 2 : 1;
         q.acc_stride = paired ? 248 : 256;
@@ -815,7 +825,7 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
             uint32_t abox[4] = {BK, (uint32_t)q.bw, (uint32_t)q.bh, (uint32_t)q.bn};
             rc = mtl_encode_tmap(ctx, &tm[i], a, 4, adims, astr, abox);
             if (rc) return rc;
-            const uint64_t wrows = paired ? 128 : (uint64_t)c.Kout;
+            const uint64_t wrows = (paired || spread) ? 128 : (uint64_t)c.Kout;
             uint64_t wdims[3] = {(uint64_t)c.Cin, wrows, (uint64_t)(c.R * q.s_count)};
             uint64_t wstr[2] = {(uint64_t)c.Cin * 4, wrows * c.Cin * 4};
             uint32_t wbox[3] = {BK, (uint32_t)BM, 1};
