@@ -6,6 +6,7 @@
 #include <string>
 
 #include "nn.hpp"
+#include "checkpoint.hpp"
 #include "trainer.hpp"
 
 #define MTLH_API extern "C" __attribute__((visibility("default")))
@@ -314,6 +315,18 @@ MTLH_API int32_t mtlh_adam_get_state(void* a, int32_t which, float* host_out) {
 
 // ------------------------------------------------------------------ Trainer ---------------
 
+// save_checkpoint / save_checkpoint_with_optim (adam may be null), checkpoint.mojo:197-300
+MTLH_API int32_t mtlh_checkpoint_save(void* m, void* a, const char* path, int32_t iter) {
+    return guard([&] { save_checkpoint(path, *static_cast<Model*>(m), static_cast<Adam*>(a), iter); });
+}
+// load_checkpoint / load_checkpoint_with_optim (adam may be null), checkpoint.mojo:303-440
+MTLH_API int32_t mtlh_checkpoint_load(void* m, void* a, const char* path, int32_t* iter, int32_t* has_optim) {
+    return guard([&] {
+        CheckpointInfo info = load_checkpoint(path, *static_cast<Model*>(m), static_cast<Adam*>(a));
+        if (iter) *iter = info.iter;
+        if (has_optim) *has_optim = info.has_optim_state ? 1 : 0;
+    });
+}
 MTLH_API int32_t mtlh_trainer_create(void* m, void* a, int32_t use_graph, int64_t bucket_bytes, void** out) {
     return guard([&] { *out = new Trainer(*static_cast<Model*>(m), *static_cast<Adam*>(a), use_graph != 0, bucket_bytes); });
 }

@@ -165,8 +165,13 @@ Model::Model(mtl_ctx* ctx, const Graph& g, uint64_t init_seed) : ctx_(ctx), g_(g
     }
     n_trainable_ = off;
     int64_t toff = off, goff = off;
+    std::map<int, bool> listed;
     auto add_tensor = [&](const Symbol& s) {
         shapes_[s.id] = s.shape;
+        if (!listed[s.id]) {
+            listed[s.id] = true;
+            alloc_order_.push_back(s);
+        }
         if (!tensor_off_.count(s.id)) {
             tensor_off_[s.id] = toff;
             toff += align_up(s.shape.num_elements());
@@ -585,6 +590,18 @@ void Adam::step_captured() {
     int rc = mtl_adam_step_dev(model_.ctx(), model_.params_flat(), model_.grads_flat(), m_, v_, model_.n_trainable(),
                                lr_, beta1_, beta2_, eps_, t_dev_, grad_scale_);
     if (rc != MTL_OK) throw Error(rc, std::string("Adam.step: ") + mtl_last_error(model_.ctx()));
+}
+
+void Adam::set_state(int which, const float* host_in) {
+    int rc = mtl_h2d(model_.ctx(), which == 0 ? m_ : v_, host_in, (size_t)model_.n_trainable() * 4);
+    if (rc != MTL_OK) throw Error(rc, std::string("Adam state upload: ") + mtl_last_error(model_.ctx()));
+}
+
+void Adam::set_iter(int iter) {
+    iter_ = iter;
+    int32_t t = iter;
+    int rc = mtl_h2d(model_.ctx(), t_dev_, &t, 4);
+    if (rc != MTL_OK) throw Error(rc, std::string("Adam counter upload: ") + mtl_last_error(model_.ctx()));
 }
 
 void Adam::get_state(int which, float* host_out) const {

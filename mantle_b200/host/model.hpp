@@ -48,6 +48,9 @@ class Model {
     void set_tensor(int symbol_id, const float* host_in);
     void get_grad(int symbol_id, float* host_out) const;
     bool has_grad(int symbol_id) const { return grad_off_.count(symbol_id) != 0; }
+    bool has_tensor(int symbol_id) const { return tensor_off_.count(symbol_id) != 0; }
+    // Every symbol with storage, in Parameters.tensors order (inputs, parameters, node outputs).
+    const std::vector<Symbol>& allocation_order() const { return alloc_order_; }
     TensorShape shape_of(int symbol_id) const;
     // Collection.set_zero on every gradient (optim.mojo:90-92).
     void zero_grads();
@@ -105,6 +108,7 @@ class Model {
     std::map<int, float> scalar_values_;      // host copies of [1]-shaped literals (POW exponent)
     std::map<int, int32_t*> pool_idx_;         // hidden argmax buffers, keyed by node index
     std::vector<Symbol> trainable_;
+    std::vector<Symbol> alloc_order_;
     std::vector<int64_t> trainable_off_;
     std::map<int, bool> grad_written_;
     std::vector<int> never_written_;           // trainable symbols no backward node writes
@@ -133,6 +137,9 @@ class Adam {
     int iter() const { return iter_; }
     void set_grad_scale(float s) { grad_scale_ = s; }
     void get_state(int which /*0 m, 1 v*/, float* host_out) const;
+    void set_state(int which /*0 m, 1 v*/, const float* host_in);
+    // Continue from a stored step count (host and device copies of the counter).
+    void set_iter(int iter);
 
    private:
     Model& model_;

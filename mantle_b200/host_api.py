@@ -315,6 +315,22 @@ class Adam:
         return self.lib.mtlh_adam_iter(self.handle)
 
 
+def save_checkpoint(path: str, model: "Model", adam: "Adam" = None, iter: int = 0):
+    """save_checkpoint / save_checkpoint_with_optim (mantle/serialize/checkpoint.mojo:197-300): every
+    tensor of the model, and with `adam` its momentum and rms state, read back from the device arenas."""
+    _ck(_lib.host_lib().mtlh_checkpoint_save(model.handle, adam.handle if adam is not None else None,
+                                             str(path).encode(), int(iter)))
+
+
+def load_checkpoint(path: str, model: "Model", adam: "Adam" = None):
+    """load_checkpoint / load_checkpoint_with_optim (checkpoint.mojo:303-440) into the device arenas.
+    Returns (iter, has_optim_state)."""
+    it, has = C.c_int32(), C.c_int32()
+    _ck(_lib.host_lib().mtlh_checkpoint_load(model.handle, adam.handle if adam is not None else None,
+                                             str(path).encode(), C.byref(it), C.byref(has)))
+    return it.value, bool(has.value)
+
+
 class Trainer:
     """forward / zero_grad / backward / step as one enqueued (optionally captured) step."""
 

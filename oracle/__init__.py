@@ -9,3 +9,4 @@ from .ops import (OP, lib, build, dot, dot_transpose_t1, dot_transpose_t2, conv_
                   maxpool2d_fwd, maxpool2d_bwd, binary_fwd, binary_bwd, unary_fwd, unary_bwd, reduce_fwd, reduce_bwd,
                   adam_step, broadcast_shapes, forward_op, backward_op)
 from .model import Graph, Model, Adam, nn, Symbol
+from . import checkpoint
