@@ -97,6 +97,33 @@ int32_t mtl_conv2d_fwd_act_pool(mtl_ctx* ctx, float* pooled, int32_t* idx, const
     return mtl_maxpool2d_fwd(ctx, pooled, idx, (const float*)scratch, pool);
 }
 
+int32_t mtl_conv2d_bwd_pooled(mtl_ctx* ctx, float* dW, float* db, const float* pooled_ug, const int32_t* idx,
+                              const float* pooled, const float* X, const mtl_conv2d_desc* d, int32_t act_op,
+                              const mtl_conv2d_desc* pool, int32_t acc_dw, int32_t acc_db) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, act_op == MTL_OP_RELU || act_op < 0, "mtl_conv2d_bwd_pooled fuses RELU only (act_op %d)", act_op);
+    ConvGeom g;
+    int32_t rc = make_geom(ctx, d, &g);
+    if (rc) return rc;
+    MTL_REQUIRE(ctx, pooled_ug && idx && X && pool && (dW || db), "null pointer in mtl_conv2d_bwd_pooled");
+    MTL_REQUIRE(ctx, act_op < 0 || pooled, "the fused RELU gradient needs the pooled output");
+    MTL_REQUIRE(ctx, pool->N == g.N && pool->C == g.K && pool->H == g.OH && pool->W == g.OW,
+                "the pooling descriptor does not describe the convolution's output");
+    const int relu = act_op == MTL_OP_RELU ? 1 : 0;
+    const bool pool_2x2 = pool->R == 2 && pool->S == 2 && pool->stride[0] == 2 && pool->stride[1] == 2 &&
+                          pool->pad[0] == 0 && pool->pad[1] == 0 && pool->dilation[0] == 1 && pool->dilation[1] == 1;
+    const bool tc = ctx->math_mode != MTL_MATH_FP32 && dW && mtl_conv_wgrad_tc_supported(g, pooled_ug, X, dW);
+    if (pool_2x2 && !tc && mtl_conv_wgrad_rows_pooled_supported(g))
+        return mtl_conv_wgrad_bias_rows_pooled(ctx, dW, db, pooled_ug, idx, pooled, X, g, relu, acc_dw, acc_db);
+    // no kernel consumes the pooled form for this geometry: the dense gradient passes through scratch
+    void* scratch;
+    rc = mtl_workspace2(ctx, (size_t)g.N * g.K * g.OH * g.OW * 4, &scratch);
+    if (rc) return rc;
+    rc = mtl_maxpool2d_bwd_idx_act(ctx, (float*)scratch, pooled_ug, idx, pooled, pool, relu ? MTL_OP_RELU : -1, 0);
+    if (rc) return rc;
+    return mtl_conv2d_bwd_fused(ctx, nullptr, dW, db, (const float*)scratch, X, nullptr, d, 0, acc_dw, acc_db);
+}
+
 int32_t mtl_conv2d_bwd_fused(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* X,
                              const float* Wt, const mtl_conv2d_desc* d, int32_t acc_dx, int32_t acc_dw, int32_t acc_db) {
     MTL_CHECK_CTX(ctx);

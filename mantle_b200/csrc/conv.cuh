@@ -28,6 +28,12 @@ bool mtl_conv_fwd_pool_simt_supported(const ConvGeom& g, const float* pooled);
 int32_t mtl_conv_fwd_pool_simt(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X, const float* Wt,
                                const float* bias, const ConvGeom& g, int relu);
 
+// Kernel and bias gradient of a first layer from the POOLED upper gradient (conv_simt.cu).
+bool mtl_conv_wgrad_rows_pooled_supported(const ConvGeom& g);
+int32_t mtl_conv_wgrad_bias_rows_pooled(mtl_ctx* ctx, float* dW, float* db, const float* pg, const int32_t* pidx,
+                                        const float* pv, const float* X, const ConvGeom& g, int relu, int acc_dw,
+                                        int acc_db);
+
 // Tensor-core implicit-GEMM kernels (conv_tc.cu); *_supported says whether a geometry qualifies.
 bool mtl_conv_fwd_tc_supported(const ConvGeom& g, const float* X, const float* Wt, const float* Y);
 bool mtl_conv_dgrad_tc_supported(const ConvGeom& g, const float* ug, const float* Wt, const float* dX);

@@ -524,6 +524,166 @@ __global__ void __launch_bounds__(WARPS * 32, 3) k_conv_wgrad_rows(float* __rest
     }
 }
 
+// The same kernel gradient for a layer followed by RELU and a 2x2 / stride-2 MAXPOOL2D, fed with the
+// POOLED upper gradient: pg (gradient of the pooling output), pidx (argmax indices of the forward
+// pass) and pv (pooled values, the RELU mask of the selected element).  The dense gradient of the
+// layer's output -- zero except one element per window -- is rebuilt 14 rows at a time in shared
+// memory (every thread writes the 2x2 windows of 14 pooled elements, so nothing has to be cleared)
+// and never exists in global memory.  The pooled data of the next chunk are fetched into registers
+// while the current chunk is multiplied.
+template <int R, int S, int OW, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 2) k_conv_wgrad_rows_pooled(float* __restrict__ partial,
+                                                                          const float* __restrict__ pg,
+                                                                          const int32_t* __restrict__ pidx,
+                                                                          const float* __restrict__ pv,
+                                                                          const float* __restrict__ X, ConvGeom g,
+                                                                          int n_per_split, int relu,
+                                                                          float* __restrict__ bias_partial) {
+    constexpr int PW = 32, RS = R * S, NT = WARPS * 32;
+    constexpr int CR = 2 * WARPS;            // dense rows per chunk
+    constexpr int POW = OW / 2, PRC = WARPS; // pooled row length, pooled rows per chunk
+    constexpr int EPT = POW;                 // pooled elements per thread and chunk: 32 * PRC * POW / NT
+    constexpr int UST = CR * OW + (((CR * OW) / 4) % 2 == 0 ? 4 : 0);  // odd multiple of 4 floats
+    extern __shared__ __align__(16) float rows_smem[];
+    const int PH = g.OH + R - 1;
+    float* xs = rows_smem;                   // [2][PH][PW] zero-padded input planes
+    float* tile = rows_smem + 2 * PH * PW;   // [32][UST] dense gradient rows of one chunk
+    const int kgroups = (g.K + 31) / 32;
+    const int kg = blockIdx.x % kgroups, c = blockIdx.x / kgroups;
+    const int k0 = kg * 32;
+    const int n_begin = blockIdx.y * n_per_split;
+    const int n_end = min(g.N, n_begin + n_per_split);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nchunks = g.OH / CR;
+    const int POH = g.OH / 2;
+    const int steps = (n_end - n_begin) * nchunks;
+
+    for (int i = threadIdx.x; i < 2 * PH * PW; i += NT) xs[i] = 0.0f;
+    __syncthreads();
+
+    // thread tid owns pooled row (channel tid / PRC, pooled row tid % PRC) of every chunk: POW
+    // consecutive elements in global memory, two dense rows of OW consecutive floats in the tile
+    float pgr[EPT];
+    int pir[EPT];
+    const int my_kk = threadIdx.x / PRC, my_phl = threadIdx.x - my_kk * PRC;
+    const bool my_valid = k0 + my_kk < g.K;
+    auto fetch = [&](int step) {  // pooled data of chunk `step` into registers, input plane of a new image
+        const int n = n_begin + step / nchunks, chunk = step % nchunks;
+        const int64_t o = (((int64_t)n * g.K + k0 + my_kk) * POH + chunk * PRC + my_phl) * POW;
+#pragma unroll
+        for (int j = 0; j < EPT; j += 2) {
+            float2 v = make_float2(0.0f, 0.0f);
+            int2 id = make_int2(-1, -1);
+            if (my_valid) {
+                v = __ldg(reinterpret_cast<const float2*>(pg + o + j));
+                id = __ldg(reinterpret_cast<const int2*>(pidx + o + j));
+                if (relu) {  // RELU.backward on the selected element
+                    const float2 y = __ldg(reinterpret_cast<const float2*>(pv + o + j));
+                    v.x = (y.x > 0.0f ? 1.0f : 0.0f) * v.x;
+                    v.y = (y.y > 0.0f ? 1.0f : 0.0f) * v.y;
+                }
+            }
+            pgr[j] = v.x; pgr[j + 1] = v.y;
+            pir[j] = id.x; pir[j + 1] = id.y;
+        }
+        if (chunk == 0) {
+            float* xb = xs + ((step / nchunks) & 1) * PH * PW;
+            const float* xc = X + ((int64_t)n * g.C + c) * g.H * g.W;
+            for (int i = threadIdx.x; i < g.H * g.W; i += NT) {
+                const int ih = i / g.W, iw = i - ih * g.W;
+                uint32_t dst = (uint32_t)__cvta_generic_to_shared(xb + (ih + g.ph) * PW + iw + g.pw);
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(xc + i) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+    };
+    auto scatter = [&](int step) {  // MAXPOOL2D.backward of the fetched elements into the tile
+        const int chunk = step % nchunks;
+        const int i00 = (chunk * CR + 2 * my_phl) * OW;  // plane-local index of this thread's first window
+        float* dst = tile + my_kk * UST + (2 * my_phl) * OW;
+#pragma unroll
+        for (int j = 0; j < EPT; j += 2) {
+            // d = 0, 1, OW, OW + 1 inside the window, anything else (no argmax) leaves zeros
+            const int d0 = pir[j] - (i00 + 2 * j), d1 = pir[j + 1] - (i00 + 2 * j + 2);
+            const float v0 = pgr[j], v1 = pgr[j + 1];
+            *reinterpret_cast<float4*>(dst + 2 * j) =
+                make_float4(d0 == 0 ? v0 : 0.0f, d0 == 1 ? v0 : 0.0f, d1 == 0 ? v1 : 0.0f, d1 == 1 ? v1 : 0.0f);
+            *reinterpret_cast<float4*>(dst + OW + 2 * j) =
+                make_float4(d0 == OW ? v0 : 0.0f, d0 == OW + 1 ? v0 : 0.0f, d1 == OW ? v1 : 0.0f, d1 == OW + 1 ? v1 : 0.0f);
+        }
+    };
+
+    float acc[RS];
+#pragma unroll
+    for (int t = 0; t < RS; ++t) acc[t] = 0.0f;
+    float bsum = 0.0f;
+
+    if (steps > 0) {
+        fetch(0);
+        scatter(0);
+    }
+    for (int step = 0; step < steps; ++step) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();  // tile of this chunk complete, input plane of this image landed
+        if (step + 1 < steps) fetch(step + 1);  // in flight while this chunk is multiplied
+        const int chunk = step % nchunks;
+        const float* xplane = xs + ((step / nchunks) & 1) * PH * PW;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+            const int lr = 2 * warp + half;
+            const int oh = chunk * CR + lr;
+            const float* ub = tile + lane * UST + lr * OW;
+            const float* xb = xplane + oh * PW;
+            float u[OW];
+#pragma unroll
+            for (int i = 0; i < OW / 4; ++i) {
+                const float4 q = *reinterpret_cast<const float4*>(ub + 4 * i);
+                u[4 * i] = q.x; u[4 * i + 1] = q.y; u[4 * i + 2] = q.z; u[4 * i + 3] = q.w;
+                bsum += (q.x + q.y) + (q.z + q.w);
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                float xr[PW];
+#pragma unroll
+                for (int i = 0; i < PW / 4; ++i) {
+                    const float4 q = *reinterpret_cast<const float4*>(xb + r * PW + 4 * i);
+                    xr[4 * i] = q.x; xr[4 * i + 1] = q.y; xr[4 * i + 2] = q.z; xr[4 * i + 3] = q.w;
+                }
+#pragma unroll
+                for (int ow = 0; ow < OW; ++ow)
+#pragma unroll
+                    for (int s2 = 0; s2 < S; ++s2) acc[r * S + s2] = fmaf(u[ow], xr[ow + s2], acc[r * S + s2]);
+            }
+        }
+        __syncthreads();
+        if (step + 1 < steps) scatter(step + 1);
+    }
+    __syncthreads();
+    float* red = tile;  // [WARPS][32][RS]
+#pragma unroll
+    for (int t = 0; t < RS; ++t) red[(warp * 32 + lane) * RS + t] = acc[t];
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * RS; i += NT) {
+        const int kk = i / RS, t = i - kk * RS;
+        if (k0 + kk >= g.K) continue;
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) v += red[w * 32 * RS + i];
+        partial[((int64_t)blockIdx.y * g.K * g.C + (int64_t)(k0 + kk) * g.C + c) * RS + t] = v;
+    }
+    if (bias_partial && c == 0) {
+        __syncthreads();
+        red[warp * 32 + lane] = bsum;
+        __syncthreads();
+        if (threadIdx.x < 32 && k0 + threadIdx.x < g.K) {
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) v += red[w * 32 + threadIdx.x];
+            bias_partial[(int64_t)blockIdx.y * g.K + k0 + threadIdx.x] = v;
+        }
+    }
+}
+
 // Any kernel size: one tap at a time.
 __global__ void __launch_bounds__(kBlock) k_conv_wgrad_generic(float* __restrict__ partial, const float* __restrict__ ug,
                                                                const float* __restrict__ X, ConvGeom g,
@@ -738,6 +898,51 @@ int32_t mtl_conv_wgrad_bias_rows(mtl_ctx* ctx, float* dW, float* db, const float
     int32_t rc = mtl_sum_partials(ctx, dW, part, (int64_t)kc * taps, ns, acc_dw);
     if (rc || !db) return rc;
     return mtl_sum_partials(ctx, db, bpart, g.K, ns, acc_db);
+}
+
+// The pooled form of the row-streaming kernel gradient (see k_conv_wgrad_rows_pooled).
+bool mtl_conv_wgrad_rows_pooled_supported(const ConvGeom& g) {
+    return g.C <= 4 && g.K >= 16 && g.OW == 28 && g.OH % 14 == 0 && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1 &&
+           ((g.R == 5 && g.S == 5) || (g.R == 3 && g.S == 3)) && g.W + 2 * g.pw == g.OW + g.S - 1 &&
+           g.H + 2 * g.ph == g.OH + g.R - 1 && g.N >= 64;
+}
+
+int32_t mtl_conv_wgrad_bias_rows_pooled(mtl_ctx* ctx, float* dW, float* db, const float* pg, const int32_t* pidx,
+                                        const float* pv, const float* X, const ConvGeom& g, int relu, int acc_dw,
+                                        int acc_db) {
+    constexpr int WARPS = 7, OWc = 28;
+    const int kc = g.K * g.C;
+    const int taps = g.R * g.S;
+    const int kgroups = (g.K + 31) / 32;
+    const int ust = 2 * WARPS * OWc + ((((2 * WARPS * OWc) / 4) % 2 == 0) ? 4 : 0);
+    const int PH = g.OH + g.R - 1;
+    size_t smem = (size_t)(2 * PH * 32 + 32 * ust) * 4;
+    int ns = (ctx->sm_count * 2 + kgroups * g.C - 1) / (kgroups * g.C);
+    if (ns > g.N / 4) ns = g.N / 4;
+    if (ns < 1) ns = 1;
+    int nps = (g.N + ns - 1) / ns;
+    ns = (g.N + nps - 1) / nps;
+    MTL_REQUIRE(ctx, ns <= 65535, "too many batch splits");
+    void* ws2;
+    int32_t rc2 = mtl_workspace(ctx, ((size_t)ns * kc * taps + (size_t)ns * g.K) * 4, &ws2);
+    if (rc2) return rc2;
+    float* part = (float*)ws2;
+    float* bpart = db ? part + (size_t)ns * kc * taps : nullptr;
+    dim3 rgrid((unsigned)(kgroups * g.C), (unsigned)ns);
+    if (g.R == 5) {
+        MTL_CUDA(ctx, cudaFuncSetAttribute(k_conv_wgrad_rows_pooled<5, 5, OWc, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_conv_wgrad_rows_pooled<5, 5, OWc, WARPS><<<rgrid, WARPS * 32, smem, ctx->stream>>>(part, pg, pidx, pv, X, g, nps, relu, bpart);
+    } else {
+        MTL_CUDA(ctx, cudaFuncSetAttribute(k_conv_wgrad_rows_pooled<3, 3, OWc, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_conv_wgrad_rows_pooled<3, 3, OWc, WARPS><<<rgrid, WARPS * 32, smem, ctx->stream>>>(part, pg, pidx, pv, X, g, nps, relu, bpart);
+    }
+    MTL_LAUNCHED(ctx);
+    if (dW) {
+        int32_t rc = mtl_sum_partials(ctx, dW, part, (int64_t)kc * taps, ns, acc_dw);
+        if (rc) return rc;
+    }
+    if (db) return mtl_sum_partials(ctx, db, bpart, g.K, ns, acc_db);
+    return MTL_OK;
 }
 
 int32_t mtl_conv_wgrad_simt(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,

@@ -317,6 +317,8 @@ void Model::set_fusion(bool on) {
     fwd_relu_of_.assign(nn, -1);
     fwd_pool_of_.assign(nn, -1);
     bwd_relu_of_.assign(nn, -1);
+    bwd_pooled_of_.assign(nn, -1);
+    bwd_pool_skip_.assign(nn, 0);
     fwd_skip_.assign(nn, 0);
     bwd_skip_.assign(nn, 0);
     relu_in_absent_.assign(nn, 0);
@@ -362,6 +364,14 @@ void Model::set_fusion(bool on) {
                     ((k < n_inference_nodes_) == (j < n_inference_nodes_) || n_inference_nodes_ == 0)) {
                     fwd_pool_of_[p->second] = k;
                     fwd_skip_[k] = 1;
+                    // backward: when the layer's input needs no gradient, its kernel and bias gradients
+                    // come straight from the pooled gradient and the dense one is never written
+                    const Node& cv = g_.nodes[p->second];
+                    if (bwd_skip_[j] && bwd_relu_of_[k] == j && !cv.inputs[0].trainable &&
+                        (cv.inputs[1].trainable || cv.inputs[2].trainable)) {
+                        bwd_pooled_of_[p->second] = k;
+                        bwd_pool_skip_[k] = 1;
+                    }
                 }
             }
         }
@@ -530,8 +540,22 @@ void Model::backward_enqueue() {
     grad_written_[g_.loss_out->id] = true;
     for (int i = (int)g_.nodes.size() - 1; i >= 0; --i) {
         const Node& n = g_.nodes[i];
-        if (fusion_ && bwd_skip_[i]) {
-            // done by the MAXPOOL2D that consumes this RELU
+        if (fusion_ && (bwd_skip_[i] || bwd_pool_skip_[i])) {
+            // a RELU whose backward its MAXPOOL2D performs, or a MAXPOOL2D whose backward the CONV2D at
+            // the head of the chain performs from the pooled gradient
+        } else if (fusion_ && n.op == MTL_OP_CONV2D && bwd_pooled_of_[i] >= 0) {
+            const Node& q = g_.nodes[bwd_pooled_of_[i]];  // the MAXPOOL2D at the end of the chain
+            const Symbol& x = n.inputs[0];
+            const Symbol& w = n.inputs[1];
+            const Symbol& b = n.inputs[2];
+            mtl_conv2d_desc d = conv_desc(x.shape, (int)w.shape[0], (int)w.shape[2], (int)w.shape[3], n.attrs);
+            mtl_conv2d_desc pd = conv_desc(q.inputs[0].shape, 1, q.attrs.kernel_size[0], q.attrs.kernel_size[1], q.attrs);
+            float* dw = w.trainable ? G(w) : nullptr;
+            float* db = b.trainable ? G(b) : nullptr;
+            const int aw = dw ? acc_flag(w) : 0, ab = db ? acc_flag(b) : 0;
+            if (dw || db)
+                check(mtl_conv2d_bwd_pooled(ctx_, dw, db, G(q.outputs[0]), pool_idx_.at(bwd_pooled_of_[i]), T(q.outputs[0]),
+                                            T(x), &d, MTL_OP_RELU, &pd, aw, ab), "CONV2D backward from the pooled gradient");
         } else if (fusion_ && n.op == MTL_OP_CONV2D) {
             // all wanted operand gradients of the layer from one pass over ug (mtl_conv2d_bwd_fused)
             const Symbol& x = n.inputs[0];

@@ -120,6 +120,8 @@ class Model {
     std::vector<char> fwd_skip_;       // RELU nodes computed by their producer
     std::vector<int> bwd_relu_of_;     // per node: the RELU node whose backward a MAXPOOL2D also performs, or -1
     std::vector<char> bwd_skip_;       // RELU nodes whose backward their consumer performs
+    std::vector<int> bwd_pooled_of_;   // per CONV2D node: the MAXPOOL2D whose pooled gradient it consumes directly, or -1
+    std::vector<char> bwd_pool_skip_;  // MAXPOOL2D nodes whose backward that CONV2D performs
     std::vector<char> relu_in_absent_; // RELU nodes whose input tensor is not written (use the output as mask)
 };
 

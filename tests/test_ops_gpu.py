@@ -419,6 +419,44 @@ def test_conv_relu_pool_equals_three_calls(ctx, case):
         assert (got_v.numpy() == 0).any()
 
 
+@pytest.mark.parametrize("case", [(70, 1, 28, 28, 64, 5, 5, 2), (65, 3, 28, 28, 40, 3, 3, 1), (6, 2, 12, 12, 5, 3, 3, 1)])
+def test_conv_backward_from_pooled_gradient(ctx, case):
+    """mtl_conv2d_bwd_pooled == CONV2D.backward[1, 2](RELU.backward(MAXPOOL2D.backward(ug))): the first-layer
+    kernel that rebuilds the dense gradient in shared memory, and the scratch-memory path."""
+    import ctypes as Cc
+    N, C, H, W, K, R, S, p = case
+    rng = np.random.default_rng(sum(case) + 7)
+    x = ctx.array(rng.normal(0, 1, (N, C, H, W)).astype(np.float32))
+    w = ctx.array((rng.normal(0, 1, (K, C, R, S)) / np.sqrt(C * R * S)).astype(np.float32))
+    b = ctx.array(rng.normal(0, 0.5, K).astype(np.float32))
+    kw = dict(padding=(p, p), stride=(1, 1), dilation=(1, 1))
+    pkw = dict(kernel_size=(2, 2), stride=(2, 2), padding=(0, 0), dilation=(1, 1))
+    oh, ow = mb.conv2d_out_shape((N, C, H, W), (K, C, R, S), **kw)
+    y, z = ctx.empty((N, K, oh, ow)), ctx.empty((N, K, oh, ow))
+    pooled, idx = ctx.empty((N, K, oh // 2, ow // 2)), ctx.empty((N, K, oh // 2, ow // 2), np.int32)
+    ctx.forward_op(OP.CONV2D, y, x, w, b, **kw)
+    ctx.forward_op(OP.RELU, z, y)
+    ctx.forward_op(OP.MAXPOOL2D, pooled, z, indices=idx, **pkw)
+    pug = ctx.array(rng.normal(0, 1, (N, K, oh // 2, ow // 2)).astype(np.float32))
+    # three reference-shaped calls
+    g_z, g_y = ctx.empty((N, K, oh, ow)), ctx.empty((N, K, oh, ow))
+    ctx.backward_op(0, OP.MAXPOOL2D, pug, z, grad=g_z, accumulate=False, indices=idx, **pkw)
+    ctx.backward_op(0, OP.RELU, g_z, y, grad=g_y, accumulate=False)
+    d = mb.conv_desc(N, C, H, W, K, R, S, (p, p), (1, 1), (1, 1))
+    pd = mb.conv_desc(N, K, oh, ow, 1, 2, 2, (0, 0), (2, 2), (1, 1))
+    for acc in (0, 1):
+        init = [rng.normal(0, 1, s).astype(np.float32) for s in ((K, C, R, S), (K,))]
+        want = [ctx.array(a) for a in init]
+        ctx.backward_op(1, OP.CONV2D, g_y, x, w, b, grad=want[0], accumulate=bool(acc), **kw)
+        ctx.backward_op(2, OP.CONV2D, g_y, x, w, b, grad=want[1], accumulate=bool(acc), **kw)
+        got = [ctx.array(a) for a in init]
+        ctx._check(ctx.lib.mtl_conv2d_bwd_pooled(ctx.handle, got[0].ptr, got[1].ptr, pug.ptr, idx.ptr, pooled.ptr, x.ptr,
+                                                 Cc.byref(d), int(OP.RELU), Cc.byref(pd), acc, acc))
+        assert rel_err(got[0].numpy(), want[0].numpy().astype(np.float64)) < 1e-5, "dW acc %d" % acc
+        assert rel_err(got[1].numpy(), want[1].numpy().astype(np.float64)) < 1e-5, "db acc %d" % acc
+    assert ctx.device_status() == 0
+
+
 FUSED_POOL = [  # (N, C, H, W, kernel, stride, pad): two-window float4, one-window float2, generic, overlapping
     (3, 4, 8, 8, 2, 2, 0), (3, 5, 14, 14, 2, 2, 0), (2, 3, 9, 9, 3, 2, 1), (2, 3, 8, 8, 3, 1, 1),
 ]
