@@ -221,6 +221,19 @@ MTL_API int32_t mtl_conv2d_fwd_act_pool(mtl_ctx* ctx, float* pooled, int32_t* id
                                         const float* Wt, const float* bias,
                                         const mtl_conv2d_desc* d, int32_t act_op,
                                         const mtl_conv2d_desc* pool);
+/* The same two calls with channels-last ([N, H, W, C]) twins, which the tensor-core convolution kernels
+ * read: `pooled_cl` (may be null) receives a channels-last copy of the pooled output, written by the
+ * kernel itself where it can and by one extra pass otherwise; `X_cl` (may be null) is such a copy of X
+ * that the caller already holds (used in plain TF32 mode, where it replaces the call's own copy pass).
+ * The caller owns both buffers and keeps X_cl equal to X. */
+MTL_API int32_t mtl_conv2d_fwd_act_pool_cl(mtl_ctx* ctx, float* pooled, int32_t* idx, float* pooled_cl,
+                                           const float* X, const float* X_cl, const float* Wt,
+                                           const float* bias, const mtl_conv2d_desc* d, int32_t act_op,
+                                           const mtl_conv2d_desc* pool);
+MTL_API int32_t mtl_conv2d_bwd_fused_cl(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug,
+                                        const float* X, const float* X_cl, const float* Wt,
+                                        const mtl_conv2d_desc* d, int32_t acc_dx, int32_t acc_dw,
+                                        int32_t acc_db);
 MTL_API int32_t mtl_maxpool2d_bwd_idx_act(mtl_ctx* ctx, float* dX, const float* ug,
                                           const int32_t* idx, const float* pooled,
                                           const mtl_conv2d_desc* d, int32_t act_op,

@@ -22,14 +22,14 @@ int32_t make_geom(mtl_ctx* ctx, const mtl_conv2d_desc* d, ConvGeom* g) {
 extern "C" {
 
 static int32_t conv2d_fwd(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
-                          const mtl_conv2d_desc* d, int relu) {
+                          const mtl_conv2d_desc* d, int relu, const float* X_cl = nullptr) {
     MTL_CHECK_CTX(ctx);
     ConvGeom g;
     int32_t rc = make_geom(ctx, d, &g);
     if (rc) return rc;
     MTL_REQUIRE(ctx, Y && X && Wt, "null pointer in CONV2D forward");
     if (ctx->math_mode != MTL_MATH_FP32 && mtl_conv_fwd_tc_supported(g, X, Wt, Y))
-        return mtl_conv_fwd_tc(ctx, Y, X, Wt, bias, g, ctx->math_mode == MTL_MATH_TF32X3, relu);
+        return mtl_conv_fwd_tc(ctx, Y, X, Wt, bias, g, ctx->math_mode == MTL_MATH_TF32X3, relu, X_cl);
     return mtl_conv_fwd_simt(ctx, Y, X, Wt, bias, g, relu);
 }
 
@@ -73,6 +73,12 @@ int32_t mtl_conv2d_bwd(mtl_ctx* ctx, int32_t tensor_id, float* grad, const float
 int32_t mtl_conv2d_fwd_act_pool(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X, const float* Wt,
                                 const float* bias, const mtl_conv2d_desc* d, int32_t act_op,
                                 const mtl_conv2d_desc* pool) {
+    return mtl_conv2d_fwd_act_pool_cl(ctx, pooled, idx, nullptr, X, nullptr, Wt, bias, d, act_op, pool);
+}
+
+int32_t mtl_conv2d_fwd_act_pool_cl(mtl_ctx* ctx, float* pooled, int32_t* idx, float* pooled_cl, const float* X,
+                                   const float* X_cl, const float* Wt, const float* bias, const mtl_conv2d_desc* d,
+                                   int32_t act_op, const mtl_conv2d_desc* pool) {
     MTL_CHECK_CTX(ctx);
     MTL_REQUIRE(ctx, act_op == MTL_OP_RELU || act_op < 0, "mtl_conv2d_fwd_act_pool fuses RELU only (act_op %d)", act_op);
     ConvGeom g;
@@ -87,14 +93,18 @@ int32_t mtl_conv2d_fwd_act_pool(mtl_ctx* ctx, float* pooled, int32_t* idx, const
                           g.OH % 2 == 0 && g.OW % 2 == 0;
     const bool tc = ctx->math_mode != MTL_MATH_FP32 && mtl_conv_fwd_tc_supported(g, X, Wt, pooled);
     if (pool_2x2 && !tc && mtl_conv_fwd_pool_simt_supported(g, pooled))
-        return mtl_conv_fwd_pool_simt(ctx, pooled, idx, X, Wt, bias, g, relu);
+        return mtl_conv_fwd_pool_simt(ctx, pooled, idx, pooled_cl, X, Wt, bias, g, relu);
     // no kernel pools this geometry in its epilogue: the activation goes through scratch memory
     void* scratch;
     rc = mtl_workspace2(ctx, (size_t)g.N * g.K * g.OH * g.OW * 4, &scratch);
     if (rc) return rc;
-    rc = conv2d_fwd(ctx, (float*)scratch, X, Wt, bias, d, relu);
+    rc = conv2d_fwd(ctx, (float*)scratch, X, Wt, bias, d, relu, X_cl);
     if (rc) return rc;
-    return mtl_maxpool2d_fwd(ctx, pooled, idx, (const float*)scratch, pool);
+    rc = mtl_maxpool2d_fwd(ctx, pooled, idx, (const float*)scratch, pool);
+    if (rc || !pooled_cl) return rc;
+    int32_t POH, POW;
+    if (mtl_conv2d_out_shape(pool, &POH, &POW) != MTL_OK) return mtl_set_error(ctx, MTL_ERR_INVALID, "bad pooling geometry");
+    return mtl_channels_last_copy(ctx, pooled_cl, pooled, g.N, g.K, POH * POW);
 }
 
 int32_t mtl_conv2d_bwd_pooled(mtl_ctx* ctx, float* dW, float* db, const float* pooled_ug, const int32_t* idx,
@@ -126,6 +136,12 @@ int32_t mtl_conv2d_bwd_pooled(mtl_ctx* ctx, float* dW, float* db, const float* p
 
 int32_t mtl_conv2d_bwd_fused(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* X,
                              const float* Wt, const mtl_conv2d_desc* d, int32_t acc_dx, int32_t acc_dw, int32_t acc_db) {
+    return mtl_conv2d_bwd_fused_cl(ctx, dX, dW, db, ug, X, nullptr, Wt, d, acc_dx, acc_dw, acc_db);
+}
+
+int32_t mtl_conv2d_bwd_fused_cl(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* X,
+                                const float* X_cl, const float* Wt, const mtl_conv2d_desc* d, int32_t acc_dx,
+                                int32_t acc_dw, int32_t acc_db) {
     MTL_CHECK_CTX(ctx);
     ConvGeom g;
     int32_t rc = make_geom(ctx, d, &g);
@@ -135,7 +151,7 @@ int32_t mtl_conv2d_bwd_fused(mtl_ctx* ctx, float* dX, float* dW, float* db, cons
     const bool tc = ctx->math_mode != MTL_MATH_FP32;
     const int x3 = ctx->math_mode == MTL_MATH_TF32X3;
     if (tc && dX && dW && mtl_conv_dgrad_tc_supported(g, ug, Wt, dX) && mtl_conv_wgrad_tc_supported(g, ug, X, dW))
-        return mtl_conv_bwd_fused_tc(ctx, dX, dW, db, ug, X, Wt, g, acc_dx, acc_dw, acc_db, x3);
+        return mtl_conv_bwd_fused_tc(ctx, dX, dW, db, ug, X, Wt, g, acc_dx, acc_dw, acc_db, x3, X_cl);
     if (dW && db && !(tc && mtl_conv_wgrad_tc_supported(g, ug, X, dW)) && mtl_conv_wgrad_rows_supported(g, ug)) {
         rc = mtl_conv_wgrad_bias_rows(ctx, dW, db, ug, X, g, acc_dw, acc_db);
         if (rc) return rc;

@@ -25,8 +25,8 @@ int32_t mtl_conv_bgrad(mtl_ctx* ctx, float* db, const float* ug, const ConvGeom&
 
 // First-layer kernel that also pools (conv_simt.cu).
 bool mtl_conv_fwd_pool_simt_supported(const ConvGeom& g, const float* pooled);
-int32_t mtl_conv_fwd_pool_simt(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X, const float* Wt,
-                               const float* bias, const ConvGeom& g, int relu);
+int32_t mtl_conv_fwd_pool_simt(mtl_ctx* ctx, float* pooled, int32_t* idx, float* pooled_cl, const float* X,
+                               const float* Wt, const float* bias, const ConvGeom& g, int relu);
 
 // Kernel and bias gradient of a first layer from the POOLED upper gradient (conv_simt.cu).
 bool mtl_conv_wgrad_rows_pooled_supported(const ConvGeom& g);
@@ -38,15 +38,18 @@ int32_t mtl_conv_wgrad_bias_rows_pooled(mtl_ctx* ctx, float* dW, float* db, cons
 bool mtl_conv_fwd_tc_supported(const ConvGeom& g, const float* X, const float* Wt, const float* Y);
 bool mtl_conv_dgrad_tc_supported(const ConvGeom& g, const float* ug, const float* Wt, const float* dX);
 bool mtl_conv_wgrad_tc_supported(const ConvGeom& g, const float* ug, const float* X, const float* dW);
+// X_cl (may be null): a channels-last copy of X the caller already holds; used in plain TF32 mode.
 int32_t mtl_conv_fwd_tc(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
-                        const ConvGeom& g, int x3, int relu);
+                        const ConvGeom& g, int x3, int relu, const float* X_cl);
+int32_t mtl_channels_last_copy(mtl_ctx* ctx, float* dst, const float* src, int N, int C, int HW);
 int32_t mtl_conv_dgrad_tc(mtl_ctx* ctx, float* dX, const float* ug, const float* Wt, const ConvGeom& g,
                           int accumulate, int x3);
 int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,
                           int accumulate, int x3);
 // dX, dW and optionally db (may be null) from one channels-last copy of ug.
 int32_t mtl_conv_bwd_fused_tc(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* X,
-                              const float* Wt, const ConvGeom& g, int acc_dx, int acc_dw, int acc_db, int x3);
+                              const float* Wt, const ConvGeom& g, int acc_dx, int acc_dw, int acc_db, int x3,
+                              const float* X_cl);
 // Row-streaming first-layer kernel: dW and db in one pass over ug; false when the geometry does not qualify.
 bool mtl_conv_wgrad_rows_supported(const ConvGeom& g, const float* ug);
 int32_t mtl_conv_wgrad_bias_rows(mtl_ctx* ctx, float* dW, float* db, const float* ug, const float* X, const ConvGeom& g,

@@ -119,6 +119,7 @@ __global__ void __launch_bounds__(kBlock) k_conv_fwd_patch(float* __restrict__ Y
 // order, pool.mojo:44-100), so the full-size activation never reaches memory.
 template <int R, int S, int C, int OW, int WARPS, bool POOL>
 __global__ void __launch_bounds__(WARPS * 32, 2) k_conv_fwd_rows(float* __restrict__ Y, int32_t* __restrict__ pool_idx,
+                                                                  float* __restrict__ pooled_cl,
                                                                   const float* __restrict__ X,
                                                                   const float* __restrict__ Wt,
                                                                   const float* __restrict__ bias, ConvGeom g, int relu) {
@@ -228,6 +229,9 @@ __global__ void __launch_bounds__(WARPS * 32, 2) k_conv_fwd_rows(float* __restri
                     if (o1[2 * pw + 1] > m) { m = o1[2 * pw + 1]; j = i00 + OW + 1; }
                     sw[lane * PST + pw] = m;
                     swi[lane * PST + pw] = j;
+                    // channels-last twin [N, POH, POW, K] for the layer that reads this output: the
+                    // lanes are adjacent channels, so this store is coalesced as it stands
+                    if (pooled_cl && k < g.K) pooled_cl[(((int64_t)n * POH + pr) * POW + pw) * g.K + k] = m;
                 }
                 __syncwarp();
                 for (int e = lane; e < 32 * POW; e += 32) {
@@ -776,8 +780,8 @@ static int32_t launch_fwd_patch(mtl_ctx* ctx, float* Y, const float* X, const fl
 }
 
 template <int R, int S, int C, bool POOL>
-static int32_t launch_fwd_rows(mtl_ctx* ctx, float* Y, int32_t* pool_idx, const float* X, const float* Wt,
-                               const float* bias, const ConvGeom& g, int relu) {
+static int32_t launch_fwd_rows(mtl_ctx* ctx, float* Y, int32_t* pool_idx, float* pooled_cl, const float* X,
+                               const float* Wt, const float* bias, const ConvGeom& g, int relu) {
     constexpr int WARPS = 7, OWc = 28, SST = 36;
     const int kgroups = (g.K + 31) / 32;
     const int PH = g.OH + R - 1;
@@ -786,7 +790,7 @@ static int32_t launch_fwd_rows(mtl_ctx* ctx, float* Y, int32_t* pool_idx, const 
     if (per_group > g.N) per_group = g.N;
     auto kern = k_conv_fwd_rows<R, S, C, OWc, WARPS, POOL>;
     MTL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<per_group * kgroups, WARPS * 32, smem, ctx->stream>>>(Y, pool_idx, X, Wt, bias, g, relu);
+    kern<<<per_group * kgroups, WARPS * 32, smem, ctx->stream>>>(Y, pool_idx, pooled_cl, X, Wt, bias, g, relu);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -817,9 +821,9 @@ static bool fwd_rows_ok(const ConvGeom& g, const float* Y) {
 int32_t mtl_conv_fwd_simt(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
                           const ConvGeom& g, int relu) {
     if (fwd_rows_ok(g, Y)) {
-        if (g.R == 5) return launch_fwd_rows<5, 5, 1, false>(ctx, Y, nullptr, X, Wt, bias, g, relu);
-        if (g.C == 1) return launch_fwd_rows<3, 3, 1, false>(ctx, Y, nullptr, X, Wt, bias, g, relu);
-        return launch_fwd_rows<3, 3, 3, false>(ctx, Y, nullptr, X, Wt, bias, g, relu);
+        if (g.R == 5) return launch_fwd_rows<5, 5, 1, false>(ctx, Y, nullptr, nullptr, X, Wt, bias, g, relu);
+        if (g.C == 1) return launch_fwd_rows<3, 3, 1, false>(ctx, Y, nullptr, nullptr, X, Wt, bias, g, relu);
+        return launch_fwd_rows<3, 3, 3, false>(ctx, Y, nullptr, nullptr, X, Wt, bias, g, relu);
     }
     int32_t rc = conv_fwd_simt_plain(ctx, Y, X, Wt, bias, g);
     if (rc || !relu) return rc;
@@ -831,11 +835,11 @@ bool mtl_conv_fwd_pool_simt_supported(const ConvGeom& g, const float* pooled) {
     return fwd_rows_ok(g, pooled) && g.OH % 2 == 0;
 }
 
-int32_t mtl_conv_fwd_pool_simt(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X, const float* Wt,
-                               const float* bias, const ConvGeom& g, int relu) {
-    if (g.R == 5) return launch_fwd_rows<5, 5, 1, true>(ctx, pooled, idx, X, Wt, bias, g, relu);
-    if (g.C == 1) return launch_fwd_rows<3, 3, 1, true>(ctx, pooled, idx, X, Wt, bias, g, relu);
-    return launch_fwd_rows<3, 3, 3, true>(ctx, pooled, idx, X, Wt, bias, g, relu);
+int32_t mtl_conv_fwd_pool_simt(mtl_ctx* ctx, float* pooled, int32_t* idx, float* pooled_cl, const float* X,
+                               const float* Wt, const float* bias, const ConvGeom& g, int relu) {
+    if (g.R == 5) return launch_fwd_rows<5, 5, 1, true>(ctx, pooled, idx, pooled_cl, X, Wt, bias, g, relu);
+    if (g.C == 1) return launch_fwd_rows<3, 3, 1, true>(ctx, pooled, idx, pooled_cl, X, Wt, bias, g, relu);
+    return launch_fwd_rows<3, 3, 3, true>(ctx, pooled, idx, pooled_cl, X, Wt, bias, g, relu);
 }
 
 int32_t mtl_conv_dgrad_simt(mtl_ctx* ctx, float* dX, const float* ug, const float* Wt, const ConvGeom& g,

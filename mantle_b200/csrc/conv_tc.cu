@@ -393,6 +393,7 @@ struct IgemmCall {
     const float* bias;
     int accumulate;
     int relu;           // clamp the result at zero after the bias (forward with a fused RELU)
+    const float* act_cl = nullptr;  // channels-last copy of `act` the caller already has (plain TF32 only)
 };
 
 // ------------------------------------------------------------------ channel-major variant -----
@@ -750,6 +751,12 @@ int32_t run_igemm(mtl_ctx* ctx, const IgemmCall& c, int x3) {
     const size_t act_pad = (n_act + 63) & ~(size_t)63, wt_pad = (n_wt + 63) & ~(size_t)63;
     const int parts = x3 ? 2 : 1;
     void* ws;
+    if (c.act_cl && !x3) {
+        // the caller keeps a channels-last copy of the activations: only the weights need scratch
+        int32_t rc0 = mtl_workspace(ctx, wt_pad * 4, &ws);
+        if (rc0) return rc0;
+        return run_igemm_core(ctx, c, x3, const_cast<float*>(c.act_cl), nullptr, (float*)ws, nullptr);
+    }
     int32_t rc = mtl_workspace(ctx, (size_t)parts * (act_pad + wt_pad) * 4, &ws);
     if (rc) return rc;
     float* a_hi = (float*)ws;
@@ -1118,13 +1125,18 @@ bool mtl_conv_dgrad_tc_supported(const ConvGeom& g, const float* ug, const float
     return true;
 }
 
+// Plain channels-last copy [N, C, HW] -> [N, HW, C] (no operand split), for callers that keep one.
+int32_t mtl_channels_last_copy(mtl_ctx* ctx, float* dst, const float* src, int N, int C, int HW) {
+    return stage_nhwc(ctx, dst, nullptr, src, N, C, HW, 0, nullptr);
+}
+
 int32_t mtl_conv_fwd_tc(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
-                        const ConvGeom& g, int x3, int relu) {
+                        const ConvGeom& g, int x3, int relu, const float* X_cl) {
     IgemmCall c;
     c.N = g.N; c.Cin = g.C; c.IH = g.H; c.IW = g.W; c.Kout = g.K; c.OH = g.OH; c.OW = g.OW;
     c.R = g.R; c.S = g.S; c.ph = g.ph; c.pw = g.pw;
     c.act = X; c.wt = Wt; c.wK = g.K; c.wC = g.C; c.flip = 0;
-    c.out = Y; c.bias = bias; c.accumulate = 0; c.relu = relu;
+    c.out = Y; c.bias = bias; c.accumulate = 0; c.relu = relu; c.act_cl = X_cl;
     return run_igemm(ctx, c, x3);
 }
 
@@ -1258,7 +1270,8 @@ int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float*
 // the kernel gradient runs first, then the input gradient re-uses the copy; the bias gradient is
 // the per-channel sum the copy pass leaves behind.
 int32_t mtl_conv_bwd_fused_tc(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* X,
-                              const float* Wt, const ConvGeom& g, int acc_dx, int acc_dw, int acc_db, int x3) {
+                              const float* Wt, const ConvGeom& g, int acc_dx, int acc_dw, int acc_db, int x3,
+                              const float* X_cl) {
     WgradParams p;
     size_t n_part;
     int32_t rc = wgrad_plan(ctx, g, x3, &p, &n_part);
@@ -1300,9 +1313,12 @@ int32_t mtl_conv_bwd_fused_tc(mtl_ctx* ctx, float* dX, float* dW, float* db, con
         k_colsum<<<(g.K + 31) / 32, 256, 0, ctx->stream>>>(db, level1, slices, g.K, slices, acc_db);
         MTL_LAUNCHED(ctx);
     }
-    rc = stage_nhwc(ctx, x_hi, x_lo, X, g.N, g.C, g.H * g.W, x3, nullptr);
-    if (rc) return rc;
-    rc = wgrad_core(ctx, dW, u_hi, u_lo, x_hi, x_lo, partial, p, g, acc_dw, x3);
+    const bool x_ready = X_cl && !x3;  // the caller's channels-last copy of X replaces the staging pass
+    if (!x_ready) {
+        rc = stage_nhwc(ctx, x_hi, x_lo, X, g.N, g.C, g.H * g.W, x3, nullptr);
+        if (rc) return rc;
+    }
+    rc = wgrad_core(ctx, dW, u_hi, u_lo, x_ready ? X_cl : x_hi, x_lo, partial, p, g, acc_dw, x3);
     if (rc) return rc;
     // input gradient: the same copy of ug is the activation operand; its weights go where X was
     return run_igemm_core(ctx, c, x3, u_hi, u_lo, region, x3 ? region + wt_pad : nullptr);

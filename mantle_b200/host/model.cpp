@@ -229,6 +229,7 @@ Model::Model(mtl_ctx* ctx, const Graph& g, uint64_t init_seed) : ctx_(ctx), g_(g
 
 Model::~Model() {
     for (auto& kv : pool_idx_) mtl_free(ctx_, kv.second);
+    for (auto& kv : twins_) mtl_free(ctx_, kv.second);
     mtl_free(ctx_, tensors_);
     mtl_free(ctx_, grads_);
 }
@@ -254,7 +255,14 @@ void Model::get_tensor(int id, float* out) const {
     Symbol s{id, shape_of(id), false};
     check(mtl_d2h(ctx_, out, T(s), (size_t)s.shape.num_elements() * 4), "get_tensor");
 }
+const float* Model::twin_of(const Symbol& s) const {
+    auto v = twin_valid_.find(s.id);
+    if (!fusion_ || v == twin_valid_.end() || !v->second) return nullptr;
+    return twins_.at(s.id);
+}
+
 void Model::set_tensor(int id, const float* in) {
+    twin_valid_[id] = false;  // a channels-last twin no longer matches
     Symbol s{id, shape_of(id), false};
     check(mtl_h2d(ctx_, T(s), in, (size_t)s.shape.num_elements() * 4), "set_tensor");
     if (s.shape.is_scalar() && scalar_values_.count(id)) scalar_values_[id] = in[0];
@@ -314,6 +322,7 @@ void Model::execute(int num_nodes) {
 void Model::set_fusion(bool on) {
     const int nn = (int)g_.nodes.size();
     fusion_ = on;
+    twin_valid_.clear();
     fwd_relu_of_.assign(nn, -1);
     fwd_pool_of_.assign(nn, -1);
     bwd_relu_of_.assign(nn, -1);
@@ -371,6 +380,17 @@ void Model::set_fusion(bool on) {
                         (cv.inputs[1].trainable || cv.inputs[2].trainable)) {
                         bwd_pooled_of_[p->second] = k;
                         bwd_pool_skip_[k] = 1;
+                    }
+                    // a CONV2D reads the pooled output: keep a channels-last twin of it, written by the
+                    // producing call and read by that layer's tensor-core kernels instead of their own copy
+                    const Symbol& po = q.outputs[0];
+                    bool feeds_conv = false;
+                    for (int c2 = k + 1; c2 < nn; ++c2)
+                        if (g_.nodes[c2].op == MTL_OP_CONV2D && g_.nodes[c2].inputs[0].id == po.id) feeds_conv = true;
+                    if (feeds_conv && !twins_.count(po.id)) {
+                        float* t = nullptr;
+                        check(mtl_malloc(ctx_, (size_t)po.shape.num_elements() * 4, (void**)&t), "channels-last twin");
+                        twins_[po.id] = t;
                     }
                 }
             }
@@ -435,8 +455,10 @@ void Model::forward_op(const Node& n) {
                 const int pk = fwd_pool_of_[self];
                 const Node& q = g_.nodes[pk];
                 mtl_conv2d_desc pd = conv_desc(q.inputs[0].shape, 1, q.attrs.kernel_size[0], q.attrs.kernel_size[1], q.attrs);
-                check(mtl_conv2d_fwd_act_pool(ctx_, T(q.outputs[0]), pool_idx_.at(pk), T(t1), T(w), T(n.inputs[2]), &d,
-                                              MTL_OP_RELU, &pd), "CONV2D+RELU+MAXPOOL2D forward");
+                float* out_cl = twins_.count(q.outputs[0].id) ? twins_.at(q.outputs[0].id) : nullptr;
+                check(mtl_conv2d_fwd_act_pool_cl(ctx_, T(q.outputs[0]), pool_idx_.at(pk), out_cl, T(t1), twin_of(t1), T(w),
+                                                 T(n.inputs[2]), &d, MTL_OP_RELU, &pd), "CONV2D+RELU+MAXPOOL2D forward");
+                if (out_cl) twin_valid_[q.outputs[0].id] = true;
             } else if (fusion_ && fwd_relu_of_[self] >= 0)
                 check(mtl_conv2d_fwd_act(ctx_, T(g_.nodes[fwd_relu_of_[self]].outputs[0]), T(t1), T(w), T(n.inputs[2]), &d,
                                          MTL_OP_RELU), "CONV2D+RELU forward");
@@ -567,7 +589,8 @@ void Model::backward_enqueue() {
             float* db = b.trainable ? G(b) : nullptr;
             const int ax = dx ? acc_flag(x) : 0, aw = dw ? acc_flag(w) : 0, ab = db ? acc_flag(b) : 0;
             if (dx || dw || db)
-                check(mtl_conv2d_bwd_fused(ctx_, dx, dw, db, G(n.outputs[0]), T(x), T(w), &d, ax, aw, ab), "CONV2D backward");
+                check(mtl_conv2d_bwd_fused_cl(ctx_, dx, dw, db, G(n.outputs[0]), T(x), twin_of(x), T(w), &d, ax, aw, ab),
+                      "CONV2D backward");
         } else {
             for (int j = 0; j < (int)n.inputs.size(); ++j)
                 if (n.inputs[j].trainable) backward_op(n, j);

@@ -96,6 +96,7 @@ class Model {
     float* T(const Symbol& s) const;
     float* G(const Symbol& s) const;
     int acc_flag(const Symbol& s);
+    const float* twin_of(const Symbol& s) const;  // valid channels-last twin of a tensor, or null
     void check(int rc, const char* what) const;
 
     mtl_ctx* ctx_;
@@ -122,6 +123,8 @@ class Model {
     std::vector<char> bwd_skip_;       // RELU nodes whose backward their consumer performs
     std::vector<int> bwd_pooled_of_;   // per CONV2D node: the MAXPOOL2D whose pooled gradient it consumes directly, or -1
     std::vector<char> bwd_pool_skip_;  // MAXPOOL2D nodes whose backward that CONV2D performs
+    std::map<int, float*> twins_;      // channels-last copies of pooled outputs that feed a CONV2D, by symbol id
+    std::map<int, bool> twin_valid_;   // written by the producing call of this step and not overwritten since
     std::vector<char> relu_in_absent_; // RELU nodes whose input tensor is not written (use the output as mask)
 };
 

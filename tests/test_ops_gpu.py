@@ -623,3 +623,47 @@ def test_invalid_arguments_return_status(ctx):
         ctx.forward_op(25, a, a)  # SLICE
     assert ctx.device_status() == 0
     assert ctx.launch_count() > 0
+
+
+def test_channels_last_twins(ctx):
+    """mtl_conv2d_fwd_act_pool_cl writes a channels-last copy of the pooled output (from the first-layer
+    kernel and from the extra-pass path); consumers given that copy as X_cl produce the bits they produce
+    from X alone (plain TF32 mode) and ignore it in 3xTF32 mode."""
+    import ctypes as Cc
+    rng = np.random.default_rng(91)
+    for (N, C, H, W, K, R, S, p) in ((70, 1, 28, 28, 64, 5, 5, 2), (6, 8, 12, 12, 16, 3, 3, 1)):
+        x = ctx.array(rng.normal(0, 1, (N, C, H, W)).astype(np.float32))
+        w = ctx.array((rng.normal(0, 1, (K, C, R, S)) / np.sqrt(C * R * S)).astype(np.float32))
+        b = ctx.array(rng.normal(0, 1, K).astype(np.float32))
+        d = mb.conv_desc(N, C, H, W, K, R, S, (p, p), (1, 1), (1, 1))
+        pd = mb.conv_desc(N, K, H, W, 1, 2, 2, (0, 0), (2, 2), (1, 1))
+        pooled, idx, twin = ctx.empty((N, K, H // 2, W // 2)), ctx.empty((N, K, H // 2, W // 2), np.int32), ctx.empty((N, H // 2, W // 2, K))
+        ctx._check(ctx.lib.mtl_conv2d_fwd_act_pool_cl(ctx.handle, pooled.ptr, idx.ptr, twin.ptr, x.ptr, None, w.ptr, b.ptr,
+                                                      Cc.byref(d), int(OP.RELU), Cc.byref(pd)))
+        assert np.array_equal(twin.numpy(), pooled.numpy().transpose(0, 2, 3, 1))
+    # consumer: the widened CNN's second layer
+    N, C, H, W, K = 12, 64, 14, 14, 128
+    x_h = rng.normal(0, 1, (N, C, H, W)).astype(np.float32)
+    x, x_cl = ctx.array(x_h), ctx.array(np.ascontiguousarray(x_h.transpose(0, 2, 3, 1)))
+    w = ctx.array((rng.normal(0, 1, (K, C, 5, 5)) / 40.0).astype(np.float32))
+    b = ctx.array(rng.normal(0, 1, K).astype(np.float32))
+    ug = ctx.array(rng.normal(0, 1, (N, K, H, W)).astype(np.float32))
+    d = mb.conv_desc(N, C, H, W, K, 5, 5, (2, 2), (1, 1), (1, 1))
+    pd = mb.conv_desc(N, K, H, W, 1, 2, 2, (0, 0), (2, 2), (1, 1))
+    for mode in (mb.MATH_TF32, mb.MATH_TF32X3):
+        ctx.set_math_mode(mode)
+        try:
+            outs = []
+            for cl in (None, x_cl.ptr):
+                pooled, idx = ctx.empty((N, K, 7, 7)), ctx.empty((N, K, 7, 7), np.int32)
+                ctx._check(ctx.lib.mtl_conv2d_fwd_act_pool_cl(ctx.handle, pooled.ptr, idx.ptr, None, x.ptr, cl, w.ptr, b.ptr,
+                                                              Cc.byref(d), int(OP.RELU), Cc.byref(pd)))
+                dx, dw, db = ctx.empty((N, C, H, W)), ctx.empty((K, C, 5, 5)), ctx.empty((K,))
+                ctx._check(ctx.lib.mtl_conv2d_bwd_fused_cl(ctx.handle, dx.ptr, dw.ptr, db.ptr, ug.ptr, x.ptr, cl, w.ptr,
+                                                           Cc.byref(d), 0, 0, 0))
+                outs.append([a.numpy() for a in (pooled, idx, dx, dw, db)])
+        finally:
+            ctx.set_math_mode(mb.MATH_TF32X3)
+        for a, b_ in zip(*outs):
+            assert np.array_equal(a, b_), "mode %d" % mode
+    assert ctx.device_status() == 0
