@@ -200,16 +200,19 @@ MTL_API int32_t mtl_maxpool2d_bwd_idx(mtl_ctx* ctx, float* dX, const float* ug,
 MTL_API int32_t mtl_conv2d_bwd_fused(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug,
                                      const float* X, const float* Wt, const mtl_conv2d_desc* d,
                                      int32_t acc_dx, int32_t acc_dw, int32_t acc_db);
-/*   mtl_conv2d_bwd_pooled      dW, db (+)= CONV2D.backward[1, 2] of RELU.backward(MAXPOOL2D.backward(pooled_ug)) for a
- *                              layer whose input needs no gradient (the first one): the kernel and bias
- *                              gradients are computed from the POOLED upper gradient, the argmax indices
- *                              and the pooled values, so the dense gradient of the layer's output (zero
- *                              except one element per window) is never written.  Other geometries rebuild
- *                              it in scratch memory.  dW or db may be null. */
-MTL_API int32_t mtl_conv2d_bwd_pooled(mtl_ctx* ctx, float* dW, float* db, const float* pooled_ug,
-                                      const int32_t* idx, const float* pooled, const float* X,
+/*   mtl_conv2d_bwd_pooled      dX, dW, db (+)= CONV2D.backward of RELU.backward(MAXPOOL2D.backward(pooled_ug)): the
+ *                              layer's gradients computed from the POOLED upper gradient, the argmax indices
+ *                              and the pooled values, so the dense gradient of the layer's output (zero except
+ *                              one element per window) is never written in NCHW: tensor-core layers scatter
+ *                              it straight into their channels-last operand copy, the first-layer kernel
+ *                              rebuilds it in shared memory; other geometries pass through scratch memory.
+ *                              Any of dX, dW, db may be null; X_cl as in mtl_conv2d_bwd_fused_cl. */
+MTL_API int32_t mtl_conv2d_bwd_pooled(mtl_ctx* ctx, float* dX, float* dW, float* db,
+                                      const float* pooled_ug, const int32_t* idx, const float* pooled,
+                                      const float* X, const float* X_cl, const float* Wt,
                                       const mtl_conv2d_desc* d, int32_t act_op,
-                                      const mtl_conv2d_desc* pool, int32_t acc_dw, int32_t acc_db);
+                                      const mtl_conv2d_desc* pool, int32_t acc_dx, int32_t acc_dw,
+                                      int32_t acc_db);
 MTL_API int32_t mtl_conv2d_fwd_act(mtl_ctx* ctx, float* Y, const float* X, const float* Wt,
                                    const float* bias, const mtl_conv2d_desc* d, int32_t act_op);
 /*   mtl_conv2d_fwd_act_pool    pooled, idx = MAXPOOL2D.forward(act(CONV2D.forward(X, Wt, bias))) (conv.mojo:81-226,

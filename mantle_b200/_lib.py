@@ -90,7 +90,7 @@ SIGNATURES = {
     "mtl_stage_acquire": (_i32, [_vp, _i32]),
     "mtl_stage_release": (_i32, [_vp, _i32]),
     "mtl_conv2d_fwd_act_pool": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _pdesc, _i32, _pdesc]),
-    "mtl_conv2d_bwd_pooled": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _pdesc, _i32, _pdesc, _i32, _i32]),
+    "mtl_conv2d_bwd_pooled": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _pdesc, _i32, _pdesc, _i32, _i32, _i32]),
     "mtl_conv2d_fwd_act_pool_cl": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _pdesc, _i32, _pdesc]),
     "mtl_conv2d_bwd_fused_cl": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _pdesc, _i32, _i32, _i32]),
     "mtl_conv2d_fwd_act": (_i32, [_vp, _vp, _vp, _vp, _vp, _pdesc, _i32]),

@@ -107,23 +107,34 @@ int32_t mtl_conv2d_fwd_act_pool_cl(mtl_ctx* ctx, float* pooled, int32_t* idx, fl
     return mtl_channels_last_copy(ctx, pooled_cl, pooled, g.N, g.K, POH * POW);
 }
 
-int32_t mtl_conv2d_bwd_pooled(mtl_ctx* ctx, float* dW, float* db, const float* pooled_ug, const int32_t* idx,
-                              const float* pooled, const float* X, const mtl_conv2d_desc* d, int32_t act_op,
-                              const mtl_conv2d_desc* pool, int32_t acc_dw, int32_t acc_db) {
+int32_t mtl_conv2d_bwd_pooled(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* pooled_ug,
+                              const int32_t* idx, const float* pooled, const float* X, const float* X_cl,
+                              const float* Wt, const mtl_conv2d_desc* d, int32_t act_op, const mtl_conv2d_desc* pool,
+                              int32_t acc_dx, int32_t acc_dw, int32_t acc_db) {
     MTL_CHECK_CTX(ctx);
     MTL_REQUIRE(ctx, act_op == MTL_OP_RELU || act_op < 0, "mtl_conv2d_bwd_pooled fuses RELU only (act_op %d)", act_op);
     ConvGeom g;
     int32_t rc = make_geom(ctx, d, &g);
     if (rc) return rc;
-    MTL_REQUIRE(ctx, pooled_ug && idx && X && pool && (dW || db), "null pointer in mtl_conv2d_bwd_pooled");
+    MTL_REQUIRE(ctx, pooled_ug && idx && pool && (dX || dW || db), "null pointer in mtl_conv2d_bwd_pooled");
+    MTL_REQUIRE(ctx, (!dX || Wt) && (!dW || X), "operand needed by a requested gradient is null");
     MTL_REQUIRE(ctx, act_op < 0 || pooled, "the fused RELU gradient needs the pooled output");
     MTL_REQUIRE(ctx, pool->N == g.N && pool->C == g.K && pool->H == g.OH && pool->W == g.OW,
                 "the pooling descriptor does not describe the convolution's output");
     const int relu = act_op == MTL_OP_RELU ? 1 : 0;
     const bool pool_2x2 = pool->R == 2 && pool->S == 2 && pool->stride[0] == 2 && pool->stride[1] == 2 &&
-                          pool->pad[0] == 0 && pool->pad[1] == 0 && pool->dilation[0] == 1 && pool->dilation[1] == 1;
-    const bool tc = ctx->math_mode != MTL_MATH_FP32 && dW && mtl_conv_wgrad_tc_supported(g, pooled_ug, X, dW);
-    if (pool_2x2 && !tc && mtl_conv_wgrad_rows_pooled_supported(g))
+                          pool->pad[0] == 0 && pool->pad[1] == 0 && pool->dilation[0] == 1 && pool->dilation[1] == 1 &&
+                          g.OH % 2 == 0 && g.OW % 2 == 0;
+    const bool tc_mode = ctx->math_mode != MTL_MATH_FP32;
+    const int x3 = ctx->math_mode == MTL_MATH_TF32X3;
+    // tensor-core layer: the pooled gradient is scattered straight into the channels-last operand copy
+    if (pool_2x2 && tc_mode && dX && dW && mtl_conv_dgrad_tc_supported(g, pooled_ug, Wt, dX) &&
+        mtl_conv_wgrad_tc_supported(g, pooled_ug, X, dW) && (size_t)(g.OH / 2) * (g.OW / 2) <= 784)
+        return mtl_conv_bwd_fused_tc_src(ctx, dX, dW, db, nullptr, pooled_ug, idx, pooled, relu, X, Wt, g, acc_dx, acc_dw,
+                                         acc_db, x3, X_cl);
+    // first layer on CUDA cores: the dense gradient is rebuilt in shared memory
+    const bool wgrad_tc = tc_mode && dW && mtl_conv_wgrad_tc_supported(g, pooled_ug, X, dW);
+    if (pool_2x2 && !dX && !wgrad_tc && mtl_conv_wgrad_rows_pooled_supported(g))
         return mtl_conv_wgrad_bias_rows_pooled(ctx, dW, db, pooled_ug, idx, pooled, X, g, relu, acc_dw, acc_db);
     // no kernel consumes the pooled form for this geometry: the dense gradient passes through scratch
     void* scratch;
@@ -131,7 +142,7 @@ int32_t mtl_conv2d_bwd_pooled(mtl_ctx* ctx, float* dW, float* db, const float* p
     if (rc) return rc;
     rc = mtl_maxpool2d_bwd_idx_act(ctx, (float*)scratch, pooled_ug, idx, pooled, pool, relu ? MTL_OP_RELU : -1, 0);
     if (rc) return rc;
-    return mtl_conv2d_bwd_fused(ctx, nullptr, dW, db, (const float*)scratch, X, nullptr, d, 0, acc_dw, acc_db);
+    return mtl_conv2d_bwd_fused_cl(ctx, dX, dW, db, (const float*)scratch, X, X_cl, Wt, d, acc_dx, acc_dw, acc_db);
 }
 
 int32_t mtl_conv2d_bwd_fused(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* X,

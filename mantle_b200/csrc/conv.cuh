@@ -50,6 +50,9 @@ int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float*
 int32_t mtl_conv_bwd_fused_tc(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* X,
                               const float* Wt, const ConvGeom& g, int acc_dx, int acc_dw, int acc_db, int x3,
                               const float* X_cl);
+int32_t mtl_conv_bwd_fused_tc_src(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* pg,
+                                  const int32_t* pidx, const float* pv, int relu, const float* X, const float* Wt,
+                                  const ConvGeom& g, int acc_dx, int acc_dw, int acc_db, int x3, const float* X_cl);
 // Row-streaming first-layer kernel: dW and db in one pass over ug; false when the geometry does not qualify.
 bool mtl_conv_wgrad_rows_supported(const ConvGeom& g, const float* ug);
 int32_t mtl_conv_wgrad_bias_rows(mtl_ctx* ctx, float* dW, float* db, const float* ug, const float* X, const ConvGeom& g,

@@ -293,6 +293,73 @@ __global__ void __launch_bounds__(256) k_colsum(float* __restrict__ out, const f
     }
 }
 
+// MAXPOOL2D.backward (2x2 windows, stride 2) followed by RELU.backward, written CHANNELS-LAST: from the
+// pooled upper gradient pg, the argmax indices and the pooled values pv (all [N, K, POH, POW]) to the
+// dense gradient [N, 2*POH, 2*POW, K] the implicit-GEMM kernels read, split into hi / lo on the way
+// when asked.  One block = one image x 32 channels: the pooled planes are read along their pixels
+// (coalesced), kept in shared memory, and written along the channels (coalesced).  colsum as in
+// k_nchw_to_nhwc: per-block channel sums, here colsum[n * K + k].
+template <bool SPLIT>
+__global__ void __launch_bounds__(256) k_pool_bwd_2x2_cl(float* __restrict__ hi, float* __restrict__ lo,
+                                                         float* __restrict__ colsum, const float* __restrict__ pg,
+                                                         const int32_t* __restrict__ pidx,
+                                                         const float* __restrict__ pv, int K, int POH, int POW,
+                                                         int relu) {
+    extern __shared__ float pool_smem[];
+    const int P = POH * POW, PS = P | 1;   // odd row stride: lanes (channels) hit different banks
+    float* val = pool_smem;                // [32][PS] gradient routed to the selected element
+    int* pos = reinterpret_cast<int*>(pool_smem + 32 * PS);  // [32][PS] which of the four (0..3), -1 none
+    __shared__ float part[8][33];
+    const int n = blockIdx.y, c0 = blockIdx.x * 32;
+    const int W = 2 * POW;
+    for (int e = threadIdx.x; e < 32 * P; e += 256) {
+        const int ch = e / P, q = e - ch * P;
+        float v = 0.0f;
+        int sub = -1;
+        if (c0 + ch < K) {
+            const int64_t o = ((int64_t)n * K + c0 + ch) * P + q;
+            v = pg[o];
+            if (relu) v = (pv[o] > 0.0f ? 1.0f : 0.0f) * v;   // RELU.backward on the selected element
+            const int qh = q / POW, qw = q - qh * POW;
+            const int d = pidx[o] - ((2 * qh) * W + 2 * qw);
+            sub = d == 0 ? 0 : d == 1 ? 1 : d == W ? 2 : d == W + 1 ? 3 : -1;
+        }
+        val[ch * PS + q] = v;
+        pos[ch * PS + q] = sub;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int k = c0 + lane;
+    float s = 0.0f;
+    for (int pix = warp; pix < 4 * P; pix += 8) {
+        const int oh = pix / W, ow = pix - oh * W;
+        const int q = (oh >> 1) * POW + (ow >> 1), sub = ((oh & 1) << 1) | (ow & 1);
+        const float v = pos[lane * PS + q] == sub ? val[lane * PS + q] : 0.0f;
+        s += v;
+        if (k < K) {
+            const int64_t o = ((int64_t)n * 4 * P + pix) * K + k;
+            if (SPLIT) {
+                float h, l;
+                split_tf32(v, h, l);
+                hi[o] = h;
+                lo[o] = l;
+            } else {
+                hi[o] = v;
+            }
+        }
+    }
+    if (colsum) {
+        part[warp][lane] = s;
+        __syncthreads();
+        if (warp == 0 && k < K) {
+            float t = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t += part[j][lane];
+            colsum[(int64_t)n * K + k] = t;
+        }
+    }
+}
+
 // Weights [K, C, R, S] -> forward layout [tap][K][C], or (flip) input-gradient layout
 // [flipped tap][C][K].
 template <bool SPLIT>
@@ -1272,6 +1339,15 @@ int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float*
 int32_t mtl_conv_bwd_fused_tc(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* X,
                               const float* Wt, const ConvGeom& g, int acc_dx, int acc_dw, int acc_db, int x3,
                               const float* X_cl) {
+    return mtl_conv_bwd_fused_tc_src(ctx, dX, dW, db, ug, nullptr, nullptr, nullptr, 0, X, Wt, g, acc_dx, acc_dw, acc_db,
+                                     x3, X_cl);
+}
+
+// The same with the upper gradient given either dense (ug) or pooled (pg, pidx, pv of a 2x2 / stride-2
+// MAXPOOL2D behind an optional RELU): the pooled form is scattered straight into the channels-last copy.
+int32_t mtl_conv_bwd_fused_tc_src(mtl_ctx* ctx, float* dX, float* dW, float* db, const float* ug, const float* pg,
+                                  const int32_t* pidx, const float* pv, int relu, const float* X, const float* Wt,
+                                  const ConvGeom& g, int acc_dx, int acc_dw, int acc_db, int x3, const float* X_cl) {
     WgradParams p;
     size_t n_part;
     int32_t rc = wgrad_plan(ctx, g, x3, &p, &n_part);
@@ -1285,7 +1361,7 @@ int32_t mtl_conv_bwd_fused_tc(mtl_ctx* ctx, float* dX, float* dW, float* db, con
     const size_t n_wt = igemm_weight_floats(c);
     const size_t u_pad = (n_u + 63) & ~(size_t)63, x_pad = (n_x + 63) & ~(size_t)63, wt_pad = (n_wt + 63) & ~(size_t)63;
     const int parts = x3 ? 2 : 1;
-    const int ptiles = (g.OH * g.OW + 31) / 32;
+    const int ptiles = pg ? 1 : (g.OH * g.OW + 31) / 32;  // rows of per-block channel sums per image
     const size_t n_bias = db ? ((size_t)g.N * ptiles + 256) * g.K : 0;
     size_t second = (size_t)parts * x_pad + n_part;
     if ((size_t)parts * wt_pad > second) second = (size_t)parts * wt_pad;
@@ -1299,8 +1375,24 @@ int32_t mtl_conv_bwd_fused_tc(mtl_ctx* ctx, float* dX, float* dW, float* db, con
     float* x_lo = x3 ? x_hi + x_pad : nullptr;
     float* partial = region + (size_t)parts * x_pad;
     float* bias_part = region + second;
-    rc = stage_nhwc(ctx, u_hi, u_lo, ug, g.N, g.K, g.OH * g.OW, x3, db ? bias_part : nullptr);
-    if (rc) return rc;
+    if (pg) {
+        const int POH = g.OH / 2, POW = g.OW / 2;
+        const int PS = (POH * POW) | 1;
+        const size_t smem = (size_t)2 * 32 * PS * 4;
+        dim3 grid((unsigned)((g.K + 31) / 32), (unsigned)g.N);
+        MTL_REQUIRE(ctx, g.N <= 65535 && smem <= 200 * 1024, "pooled plane too large for the scatter pass");
+        if (x3) {
+            MTL_CUDA(ctx, cudaFuncSetAttribute(k_pool_bwd_2x2_cl<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            k_pool_bwd_2x2_cl<true><<<grid, 256, smem, ctx->stream>>>(u_hi, u_lo, db ? bias_part : nullptr, pg, pidx, pv, g.K, POH, POW, relu);
+        } else {
+            MTL_CUDA(ctx, cudaFuncSetAttribute(k_pool_bwd_2x2_cl<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            k_pool_bwd_2x2_cl<false><<<grid, 256, smem, ctx->stream>>>(u_hi, u_lo, db ? bias_part : nullptr, pg, pidx, pv, g.K, POH, POW, relu);
+        }
+        MTL_LAUNCHED(ctx);
+    } else {
+        rc = stage_nhwc(ctx, u_hi, u_lo, ug, g.N, g.K, g.OH * g.OW, x3, db ? bias_part : nullptr);
+        if (rc) return rc;
+    }
     if (db) {
         // two levels: 256 slices of the per-block sums, then the slices
         const int64_t rows = (int64_t)g.N * ptiles;

@@ -373,11 +373,11 @@ void Model::set_fusion(bool on) {
                     ((k < n_inference_nodes_) == (j < n_inference_nodes_) || n_inference_nodes_ == 0)) {
                     fwd_pool_of_[p->second] = k;
                     fwd_skip_[k] = 1;
-                    // backward: when the layer's input needs no gradient, its kernel and bias gradients
-                    // come straight from the pooled gradient and the dense one is never written
+                    // backward: the layer's gradients come straight from the pooled gradient and the dense
+                    // gradient of its output is never written in NCHW
                     const Node& cv = g_.nodes[p->second];
-                    if (bwd_skip_[j] && bwd_relu_of_[k] == j && !cv.inputs[0].trainable &&
-                        (cv.inputs[1].trainable || cv.inputs[2].trainable)) {
+                    if (bwd_skip_[j] && bwd_relu_of_[k] == j &&
+                        (cv.inputs[0].trainable || cv.inputs[1].trainable || cv.inputs[2].trainable)) {
                         bwd_pooled_of_[p->second] = k;
                         bwd_pool_skip_[k] = 1;
                     }
@@ -572,12 +572,14 @@ void Model::backward_enqueue() {
             const Symbol& b = n.inputs[2];
             mtl_conv2d_desc d = conv_desc(x.shape, (int)w.shape[0], (int)w.shape[2], (int)w.shape[3], n.attrs);
             mtl_conv2d_desc pd = conv_desc(q.inputs[0].shape, 1, q.attrs.kernel_size[0], q.attrs.kernel_size[1], q.attrs);
+            float* dx = x.trainable ? G(x) : nullptr;
             float* dw = w.trainable ? G(w) : nullptr;
             float* db = b.trainable ? G(b) : nullptr;
-            const int aw = dw ? acc_flag(w) : 0, ab = db ? acc_flag(b) : 0;
-            if (dw || db)
-                check(mtl_conv2d_bwd_pooled(ctx_, dw, db, G(q.outputs[0]), pool_idx_.at(bwd_pooled_of_[i]), T(q.outputs[0]),
-                                            T(x), &d, MTL_OP_RELU, &pd, aw, ab), "CONV2D backward from the pooled gradient");
+            const int ax = dx ? acc_flag(x) : 0, aw = dw ? acc_flag(w) : 0, ab = db ? acc_flag(b) : 0;
+            if (dx || dw || db)
+                check(mtl_conv2d_bwd_pooled(ctx_, dx, dw, db, G(q.outputs[0]), pool_idx_.at(bwd_pooled_of_[i]), T(q.outputs[0]),
+                                            T(x), twin_of(x), T(w), &d, MTL_OP_RELU, &pd, ax, aw, ab),
+                      "CONV2D backward from the pooled gradient");
         } else if (fusion_ && n.op == MTL_OP_CONV2D) {
             // all wanted operand gradients of the layer from one pass over ug (mtl_conv2d_bwd_fused)
             const Symbol& x = n.inputs[0];

@@ -419,10 +419,12 @@ def test_conv_relu_pool_equals_three_calls(ctx, case):
         assert (got_v.numpy() == 0).any()
 
 
-@pytest.mark.parametrize("case", [(70, 1, 28, 28, 64, 5, 5, 2), (65, 3, 28, 28, 40, 3, 3, 1), (6, 2, 12, 12, 5, 3, 3, 1)])
+@pytest.mark.parametrize("case", [(70, 1, 28, 28, 64, 5, 5, 2), (65, 3, 28, 28, 40, 3, 3, 1), (6, 2, 12, 12, 5, 3, 3, 1),
+                                  (24, 64, 14, 14, 128, 5, 5, 2), (3, 64, 56, 56, 64, 3, 3, 1)])
 def test_conv_backward_from_pooled_gradient(ctx, case):
-    """mtl_conv2d_bwd_pooled == CONV2D.backward[1, 2](RELU.backward(MAXPOOL2D.backward(ug))): the first-layer
-    kernel that rebuilds the dense gradient in shared memory, and the scratch-memory path."""
+    """mtl_conv2d_bwd_pooled == CONV2D.backward(RELU.backward(MAXPOOL2D.backward(ug))): the first-layer kernel
+    that rebuilds the dense gradient in shared memory, the tensor-core path that scatters it into the
+    channels-last operand copy, and the scratch-memory path."""
     import ctypes as Cc
     N, C, H, W, K, R, S, p = case
     rng = np.random.default_rng(sum(case) + 7)
@@ -438,22 +440,42 @@ def test_conv_backward_from_pooled_gradient(ctx, case):
     ctx.forward_op(OP.RELU, z, y)
     ctx.forward_op(OP.MAXPOOL2D, pooled, z, indices=idx, **pkw)
     pug = ctx.array(rng.normal(0, 1, (N, K, oh // 2, ow // 2)).astype(np.float32))
-    # three reference-shaped calls
+    # reference-shaped calls
     g_z, g_y = ctx.empty((N, K, oh, ow)), ctx.empty((N, K, oh, ow))
     ctx.backward_op(0, OP.MAXPOOL2D, pug, z, grad=g_z, accumulate=False, indices=idx, **pkw)
     ctx.backward_op(0, OP.RELU, g_z, y, grad=g_y, accumulate=False)
     d = mb.conv_desc(N, C, H, W, K, R, S, (p, p), (1, 1), (1, 1))
     pd = mb.conv_desc(N, K, oh, ow, 1, 2, 2, (0, 0), (2, 2), (1, 1))
-    for acc in (0, 1):
-        init = [rng.normal(0, 1, s).astype(np.float32) for s in ((K, C, R, S), (K,))]
-        want = [ctx.array(a) for a in init]
-        ctx.backward_op(1, OP.CONV2D, g_y, x, w, b, grad=want[0], accumulate=bool(acc), **kw)
-        ctx.backward_op(2, OP.CONV2D, g_y, x, w, b, grad=want[1], accumulate=bool(acc), **kw)
-        got = [ctx.array(a) for a in init]
-        ctx._check(ctx.lib.mtl_conv2d_bwd_pooled(ctx.handle, got[0].ptr, got[1].ptr, pug.ptr, idx.ptr, pooled.ptr, x.ptr,
-                                                 Cc.byref(d), int(OP.RELU), Cc.byref(pd), acc, acc))
-        assert rel_err(got[0].numpy(), want[0].numpy().astype(np.float64)) < 1e-5, "dW acc %d" % acc
-        assert rel_err(got[1].numpy(), want[1].numpy().astype(np.float64)) < 1e-5, "db acc %d" % acc
+    tc = C >= 16
+    for mode in ((mb.MATH_TF32X3, mb.MATH_TF32) if tc else (mb.MATH_TF32X3,)):
+        ctx.set_math_mode(mode)
+        try:
+            for acc in (0, 1):
+                init = [rng.normal(0, 1, s).astype(np.float32) for s in ((N, C, H, W), (K, C, R, S), (K,))]
+                want = [ctx.array(a) for a in init]
+                for tid in range(3):
+                    ctx.backward_op(tid, OP.CONV2D, g_y, x, w, b, grad=want[tid], accumulate=bool(acc), **kw)
+                got = [ctx.array(a) for a in init]
+                ctx._check(ctx.lib.mtl_conv2d_bwd_pooled(ctx.handle, got[0].ptr, got[1].ptr, got[2].ptr, pug.ptr, idx.ptr,
+                                                         pooled.ptr, x.ptr, None, w.ptr, Cc.byref(d), int(OP.RELU),
+                                                         Cc.byref(pd), acc, acc, acc))
+                if tc:  # the same kernels on the same operand values: bitwise, bias sum within rounding
+                    assert np.array_equal(got[0].numpy(), want[0].numpy()), "dX mode %d acc %d" % (mode, acc)
+                    assert np.array_equal(got[1].numpy(), want[1].numpy()), "dW mode %d acc %d" % (mode, acc)
+                else:
+                    assert rel_err(got[0].numpy(), want[0].numpy().astype(np.float64)) < 1e-5
+                    assert rel_err(got[1].numpy(), want[1].numpy().astype(np.float64)) < 1e-5
+                assert rel_err(got[2].numpy(), want[2].numpy().astype(np.float64)) < 1e-5, "db acc %d" % acc
+                # only the kernel and bias gradients (a first layer)
+                part = [ctx.array(a) for a in init]
+                ctx._check(ctx.lib.mtl_conv2d_bwd_pooled(ctx.handle, None, part[1].ptr, part[2].ptr, pug.ptr, idx.ptr,
+                                                         pooled.ptr, x.ptr, None, w.ptr, Cc.byref(d), int(OP.RELU),
+                                                         Cc.byref(pd), 0, acc, acc))
+                assert rel_err(part[1].numpy(), want[1].numpy().astype(np.float64)) < (3e-5 if tc else 1e-5)
+                assert rel_err(part[2].numpy(), want[2].numpy().astype(np.float64)) < 1e-5
+                assert np.array_equal(part[0].numpy(), init[0])
+        finally:
+            ctx.set_math_mode(mb.MATH_TF32X3)
     assert ctx.device_status() == 0
 
 
