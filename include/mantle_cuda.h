@@ -242,6 +242,45 @@ MTL_API int32_t mtl_maxpool2d_bwd_idx_act(mtl_ctx* ctx, float* dX, const float* 
                                           const mtl_conv2d_desc* d, int32_t act_op,
                                           int32_t accumulate);
 
+/* ---------------------------------------------------------------- layout operators ------ */
+
+/* TRANSPOSE.forward / .backward (mantle/autograd/ops/basics.mojo:618-703): out = permute(in, axes);
+ * axes == NULL reverses the axes.  Backward adds the inverse permutation of ug to grad. */
+MTL_API int32_t mtl_transpose_fwd(mtl_ctx* ctx, float* out, const float* in, int32_t rank,
+                                  const int64_t* in_shape, const int32_t* axes);
+MTL_API int32_t mtl_transpose_bwd(mtl_ctx* ctx, float* grad, const float* ug, int32_t rank,
+                                  const int64_t* in_shape, const int32_t* axes, int32_t accumulate);
+
+/* SLICE (mantle/autograd/ops/mlops.mojo:376-656): the reference's "starts", "ends", "steps", "axes"
+ * attributes, n entries; axes[i] < 0 means axis i (its default).  Negative starts / ends count from
+ * the end and are clamped to [0, dim] (adjust_boundary); steps may be negative.  A slice that is
+ * empty or reaches outside the tensor is refused (the reference does not check). */
+typedef struct mtl_slice_desc {
+    int32_t n;
+    int32_t axes[8];
+    int64_t starts[8], ends[8], steps[8];
+} mtl_slice_desc;
+MTL_API int32_t mtl_slice_out_shape(int32_t rank, const int64_t* in_shape, const mtl_slice_desc* d,
+                                    int64_t* out_shape);
+MTL_API int32_t mtl_slice_fwd(mtl_ctx* ctx, float* out, const float* in, int32_t rank,
+                              const int64_t* in_shape, const mtl_slice_desc* d);
+MTL_API int32_t mtl_slice_bwd(mtl_ctx* ctx, float* grad, const float* ug, int32_t rank,
+                              const int64_t* in_shape, const mtl_slice_desc* d, int32_t accumulate);
+
+/* CONCAT / SPLIT (mantle/autograd/ops/dynamics.mojo:25-199) along axis `dim`.  in_shapes holds n_in
+ * shapes of `rank` entries each; sections holds the n_out extents of the split axis. */
+MTL_API int32_t mtl_concat_fwd(mtl_ctx* ctx, float* out, const float* const* ins, int32_t n_in,
+                               int32_t rank, const int64_t* in_shapes, int32_t dim);
+MTL_API int32_t mtl_concat_bwd(mtl_ctx* ctx, float* grad, const float* ug, int32_t input_id,
+                               int32_t n_in, int32_t rank, const int64_t* in_shapes, int32_t dim,
+                               int32_t accumulate);
+MTL_API int32_t mtl_split_fwd(mtl_ctx* ctx, float* const* outs, const float* in, int32_t n_out,
+                              int32_t rank, const int64_t* in_shape, const int64_t* sections,
+                              int32_t dim);
+MTL_API int32_t mtl_split_bwd(mtl_ctx* ctx, float* grad, const float* const* ugs, int32_t n_out,
+                              int32_t rank, const int64_t* in_shape, const int64_t* sections,
+                              int32_t dim, int32_t accumulate);
+
 /* ---------------------------------------------------------------- elementwise ----------- */
 
 /* ADD/SUB/MUL/DIV.forward -> elwise_op / broadcast_elwise_op (tensorutils.mojo:243-357):

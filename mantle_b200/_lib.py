@@ -42,6 +42,22 @@ def conv_desc(N, Cc, H, W, K, R, S, pad=(0, 0), stride=(1, 1), dilation=(1, 1)) 
     return d
 
 
+class SliceDesc(C.Structure):
+    _fields_ = [("n", C.c_int32), ("axes", C.c_int32 * 8), ("starts", C.c_int64 * 8), ("ends", C.c_int64 * 8),
+                ("steps", C.c_int64 * 8)]
+
+
+def slice_desc(starts, ends, steps=None, axes=None) -> SliceDesc:
+    """The SLICE attributes of the reference: one entry per sliced axis; `axes` defaults to 0, 1, ..."""
+    d = SliceDesc()
+    d.n = len(starts)
+    for i in range(d.n):
+        d.starts[i], d.ends[i] = starts[i], ends[i]
+        d.steps[i] = 1 if steps is None else steps[i]
+        d.axes[i] = -1 if axes is None else axes[i]
+    return d
+
+
 class MantleError(RuntimeError):
     def __init__(self, code: int, message: str):
         super().__init__("%s: %s" % (STATUS_NAMES.get(code, code), message))
@@ -51,6 +67,9 @@ class MantleError(RuntimeError):
 _vp, _i32, _i64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
 _pi64 = C.POINTER(C.c_int64)
 _pdesc = C.POINTER(ConvDesc)
+_pslice = C.POINTER(SliceDesc)
+_pi32 = C.POINTER(C.c_int32)
+_ppf = C.POINTER(C.c_void_p)
 
 # name -> (restype, argtypes); every symbol declared in include/mantle_cuda.h
 SIGNATURES = {
@@ -95,6 +114,15 @@ SIGNATURES = {
     "mtl_conv2d_bwd_fused_cl": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _pdesc, _i32, _i32, _i32]),
     "mtl_conv2d_fwd_act": (_i32, [_vp, _vp, _vp, _vp, _vp, _pdesc, _i32]),
     "mtl_maxpool2d_bwd_idx_act": (_i32, [_vp, _vp, _vp, _vp, _vp, _pdesc, _i32, _i32]),
+    "mtl_transpose_fwd": (_i32, [_vp, _vp, _vp, _i32, _pi64, _pi32]),
+    "mtl_transpose_bwd": (_i32, [_vp, _vp, _vp, _i32, _pi64, _pi32, _i32]),
+    "mtl_slice_out_shape": (_i32, [_i32, _pi64, _pslice, _pi64]),
+    "mtl_slice_fwd": (_i32, [_vp, _vp, _vp, _i32, _pi64, _pslice]),
+    "mtl_slice_bwd": (_i32, [_vp, _vp, _vp, _i32, _pi64, _pslice, _i32]),
+    "mtl_concat_fwd": (_i32, [_vp, _vp, _ppf, _i32, _i32, _pi64, _i32]),
+    "mtl_concat_bwd": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _pi64, _i32, _i32]),
+    "mtl_split_fwd": (_i32, [_vp, _ppf, _vp, _i32, _i32, _pi64, _pi64, _i32]),
+    "mtl_split_bwd": (_i32, [_vp, _vp, _ppf, _i32, _i32, _pi64, _pi64, _i32, _i32]),
     "mtl_binary_fwd": (_i32, [_vp, _i32, _vp, _vp, _vp, _i32, _pi64, _i32, _pi64]),
     "mtl_binary_bwd": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _pi64, _i32, _pi64, _i32]),
     "mtl_unary_fwd": (_i32, [_vp, _i32, _vp, _vp, _i64, _f32, _f32]),

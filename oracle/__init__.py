@@ -10,3 +10,4 @@ from .ops import (OP, lib, build, dot, dot_transpose_t1, dot_transpose_t2, conv_
                   adam_step, broadcast_shapes, forward_op, backward_op)
 from .model import Graph, Model, Adam, nn, Symbol
 from . import checkpoint
+from . import layout
