@@ -22,13 +22,18 @@ constexpr int BK = 32;  // 32 fp32 = one 128-byte swizzle row
 constexpr int kThreads = 192;
 constexpr uint64_t kWaitBudgetNs = 4000000000ull;  // 4 s: far beyond any legitimate wait
 
-template <int BN>
+// MT = 2: a CTA owns 256 rows, i.e. two M = 128 instructions per k step that share the B tile.  That
+// halves the operand rows fetched per flop (the TMA unit, not the tensor pipe, limits the 128-row
+// tile) at the price of the second accumulator buffer: the epilogue no longer overlaps the next
+// tile's main loop, which only matters for short K.
+template <int BN, int MT>
 struct Cfg {
-    static constexpr int kStages = BN == 256 ? 4 : 6;
-    static constexpr int kABytes = BM * BK * 4;
+    static constexpr int kStages = MT == 2 ? 3 : (BN == 256 ? 4 : 6);
+    static constexpr int kABytes = MT * BM * BK * 4;
     static constexpr int kBBytes = BN * BK * 4;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kTmemCols = 2 * BN;  // two accumulators
+    static constexpr int kAccs = MT == 2 ? 1 : 2;        // accumulator sets in tensor memory
+    static constexpr int kTmemCols = 2 * BN;             // 2 sets x BN, or 1 set x 2 halves x BN
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
@@ -56,11 +61,12 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = r / rows;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
             const __grid_constant__ CUtensorMap mapB0, const __grid_constant__ CUtensorMap mapB1, GemmParams p) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, MT>;
+    constexpr int BMT = BM * MT;  // rows of a CTA tile
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzle needs 1024-byte aligned tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -76,7 +82,7 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    const int tiles_m = (p.M + BM - 1) / BM;
+    const int tiles_m = (p.M + BMT - 1) / BMT;
     const int tiles_n = (p.N + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
     const int kb_per_seg = (p.K + BK - 1) / BK;
@@ -118,7 +124,7 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 int tm, tn;
                 tile_coords(t, tiles_m, tiles_n, tm, tn);
-                const int m0 = tm * BM, n0 = tn * BN;
+                const int m0 = tm * BMT, n0 = tn * BN;
                 for (int kb = 0; kb < kb_total; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
                     const int seg = kb / kb_per_seg;
@@ -134,7 +140,7 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                             tma_load_3d(sa, ma, &full[stage], 0, k0, m0 / 32);
                         } else {
 #pragma unroll
-                            for (int c = 0; c < BM / 32; ++c)
+                            for (int c = 0; c < BMT / 32; ++c)
                                 tma_load_2d(sa + c * 4096, ma, &full[stage], m0 + c * 32, k0);
                         }
                     } else {
@@ -165,8 +171,8 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
             bool ok = true;
             int local = 0;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
-                const int acc = local & 1;
-                const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+                const int acc = local % C::kAccs;
+                const uint32_t acc_phase = (uint32_t)(local / C::kAccs) & 1u;
                 if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
@@ -177,9 +183,13 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                     const uint32_t sb = sa + C::kABytes;
 #pragma unroll
                     for (int kk = 0; kk < BK / 8; ++kk) {
-                        const uint64_t da = A_MN ? desc_mn_major(sa, kk) : desc_k_major(sa, kk);
                         const uint64_t db = B_MN ? desc_mn_major(sb, kk) : desc_k_major(sb, kk);
-                        mma_tf32(tmem_d, da, db, idesc, (kb | kk) ? 1u : 0u);
+#pragma unroll
+                        for (int h = 0; h < MT; ++h) {  // the halves of a 256-row tile: 16 KB apart in both layouts
+                            const uint32_t sah = sa + (uint32_t)h * (BM * BK * 4);
+                            const uint64_t da = A_MN ? desc_mn_major(sah, kk) : desc_k_major(sah, kk);
+                            mma_tf32(tmem_d + (uint32_t)(h * BN), da, db, idesc, (kb | kk) ? 1u : 0u);
+                        }
                     }
                     mma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
                     if (++stage == p.stages) { stage = 0; phase ^= 1u; }
@@ -197,17 +207,18 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
             int tm, tn;
             tile_coords(t, tiles_m, tiles_n, tm, tn);
-            const int acc = local & 1;
-            const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+            const int acc = local % C::kAccs;
+            const uint32_t acc_phase = (uint32_t)(local / C::kAccs) & 1u;
             if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
             tc_fence_after_sync();
-            const int m = tm * BM + quad * 32 + lane;
             const int n_base = tn * BN;
-            float* crow = p.C + (int64_t)m * p.N;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int hc = 0; hc < MT * (BN / 32); ++hc) {
+                const int h = hc / (BN / 32), c = hc - h * (BN / 32);
+                const int m = tm * BMT + h * BM + quad * 32 + lane;
+                float* crow = p.C + (int64_t)m * p.N;
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32), r);
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((acc + h) * BN + c * 32), r);
                 tmem_ld_wait();
                 const int n0 = n_base + c * 32;
                 if (m < p.M && !p.skip_store) {
@@ -276,12 +287,12 @@ __global__ void __launch_bounds__(256) k_split_tf32(float* __restrict__ hi, floa
     for (int64_t i = (n4 << 2) + tid; i < n; i += stride) split(x[i], hi[i], lo[i]);
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int MT>
 int32_t launch_gemm(mtl_ctx* ctx, const CUtensorMap* maps, const GemmParams& p) {
-    using C = Cfg<BN>;
-    auto kern = k_gemm_tf32<BN, A_MN, B_MN>;
+    using C = Cfg<BN, MT>;
+    auto kern = k_gemm_tf32<BN, A_MN, B_MN, MT>;
     MTL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-    int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+    int tiles = ((p.M + BM * MT - 1) / (BM * MT)) * ((p.N + BN - 1) / BN);
     int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     {
         mtl_prof_scope prof(ctx, MTL_PROF_DOT_TC);
@@ -346,6 +357,15 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
         return mtl_set_error(ctx, MTL_ERR_UNSUPPORTED, "shape not supported by the tensor-core DOT kernel");
     int BN = N >= 256 ? 256 : 128;
     if (const char* e = getenv("MANTLE_GEMM_BN")) { int b = atoi(e); if (b == 128 || (b == 256 && N >= 256)) BN = b; }
+    // 256-row tiles when they do not cost waves: a 256 x 256 tile takes about 1.67x a 128 x 256 one
+    int MT = 1;
+    if (BN == 256 && M >= 256) {
+        const int64_t t1 = ((M + 127) / 128) * ((N + 255) / 256), t2 = ((M + 255) / 256) * ((N + 255) / 256);
+        const int64_t w1 = (t1 + ctx->sm_count - 1) / ctx->sm_count, w2 = (t2 + ctx->sm_count - 1) / ctx->sm_count;
+        if ((double)w2 * 1.67 < (double)w1 && K >= 512) MT = 2;
+    }
+    if (const char* e = getenv("MANTLE_GEMM_MT")) { int m = atoi(e); if (m == 1 || (m == 2 && BN == 256 && M >= 256)) MT = m; }
+    const int BMT = BM * MT;
     const float* a_src[2] = {A, nullptr};
     const float* b_src[2] = {B, nullptr};
     if (x3) {
@@ -378,9 +398,9 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
         uint32_t box[3];
         int rank = 2;
         if (a3d) { dims[0] = 32; dims[1] = (uint64_t)K; dims[2] = (uint64_t)(M / 32); strides[0] = (uint64_t)M * 4; strides[1] = 128;
-                   box[0] = 32; box[1] = BK; box[2] = BM / 32; rank = 3; }
+                   box[0] = 32; box[1] = BK; box[2] = (uint32_t)(BMT / 32); rank = 3; }
         else if (transA) { dims[0] = (uint64_t)M; dims[1] = (uint64_t)K; box[0] = 32; box[1] = BK; strides[0] = dims[0] * 4; }
-        else             { dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = BK; box[1] = BM; strides[0] = dims[0] * 4; }
+        else             { dims[0] = (uint64_t)K; dims[1] = (uint64_t)M; box[0] = BK; box[1] = (uint32_t)BMT; strides[0] = dims[0] * 4; }
         int32_t rc = mtl_encode_tmap(ctx, &maps[i], a, rank, dims, strides, box, transA != 0);
         if (rc) return rc;
         rank = 2;
@@ -400,20 +420,21 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
     p.C = C;
     p.accumulate = accumulate ? 1 : 0;
     p.status = ctx->dev_status;
-    p.stages = BN == 256 ? 4 : 6;
+    p.stages = MT == 2 ? 3 : (BN == 256 ? 4 : 6);
     p.a3d = a3d;
     p.b3d = b3d;
     p.skip_store = 0;
     if (const char* e = getenv("MANTLE_GEMM_STAGES")) { int s = atoi(e); if (s >= 1 && s <= p.stages) p.stages = s; }
     if (const char* e = getenv("MANTLE_GEMM_SKIP_STORE")) p.skip_store = atoi(e) != 0;
     const bool a_mn = transA != 0, b_mn = transB == 0;
-#define MTL_DISPATCH(BN_)                                                                     \
-    if (a_mn && b_mn) return launch_gemm<BN_, true, true>(ctx, maps, p);                     \
-    if (a_mn && !b_mn) return launch_gemm<BN_, true, false>(ctx, maps, p);                   \
-    if (!a_mn && b_mn) return launch_gemm<BN_, false, true>(ctx, maps, p);                   \
-    return launch_gemm<BN_, false, false>(ctx, maps, p);
-    if (BN == 256) { MTL_DISPATCH(256) }
-    MTL_DISPATCH(128)
+#define MTL_DISPATCH(BN_, MT_)                                                                \
+    if (a_mn && b_mn) return launch_gemm<BN_, true, true, MT_>(ctx, maps, p);                \
+    if (a_mn && !b_mn) return launch_gemm<BN_, true, false, MT_>(ctx, maps, p);              \
+    if (!a_mn && b_mn) return launch_gemm<BN_, false, true, MT_>(ctx, maps, p);              \
+    return launch_gemm<BN_, false, false, MT_>(ctx, maps, p);
+    if (BN == 256 && MT == 2) { MTL_DISPATCH(256, 2) }
+    if (BN == 256) { MTL_DISPATCH(256, 1) }
+    MTL_DISPATCH(128, 1)
 #undef MTL_DISPATCH
 }
 
