@@ -73,6 +73,7 @@ enum mtl_op {
     MTL_OP_SIGMOID = 13, MTL_OP_RELU = 14, MTL_OP_TANH = 15,
     MTL_OP_CONV2D = 16, MTL_OP_TRANSPOSE = 17, MTL_OP_MAXPOOL2D = 18, MTL_OP_FMA = 19,
     MTL_OP_CLIP = 20, MTL_OP_SQUEEZE = 21, MTL_OP_UNSQUEEZE = 22,
+    MTL_OP_CONCAT = 23, MTL_OP_SPLIT = 24, MTL_OP_SLICE = 25,
     MTL_OP_LEAKYRELU = 28
 };
 

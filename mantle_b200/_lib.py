@@ -24,6 +24,7 @@ class OP:
     ADD, SUB, MUL, DIV, EXP, LOG, POW, DOT, SUM, MEAN, MAX = range(11)
     FLATTEN, RESHAPE, SIGMOID, RELU, TANH, CONV2D, TRANSPOSE, MAXPOOL2D, FMA = range(11, 20)
     CLIP, SQUEEZE, UNSQUEEZE = 20, 21, 22
+    CONCAT, SPLIT, SLICE = 23, 24, 25
     LEAKYRELU = 28
 
 

@@ -61,6 +61,10 @@ struct mtlh_attrs {
     float clip_min, clip_max;
     int32_t n_dims;
     int32_t dims[MTL_MAX_RANK];
+    int32_t n_axes;
+    int32_t axes[MTL_MAX_RANK];
+    int32_t n_slice, has_steps;
+    int64_t starts[MTL_MAX_RANK], ends[MTL_MAX_RANK], steps[MTL_MAX_RANK];
 };
 
 static Attributes to_attrs(const mtlh_attrs* a) {
@@ -78,6 +82,12 @@ static Attributes to_attrs(const mtlh_attrs* a) {
     if (a->has_clip_min) r.clip_min = a->clip_min;
     if (a->has_clip_max) r.clip_max = a->clip_max;
     for (int i = 0; i < a->n_dims && i < MTL_MAX_RANK; ++i) r.dims.push_back(a->dims[i]);
+    for (int i = 0; i < a->n_axes && i < MTL_MAX_RANK; ++i) r.axes.push_back(a->axes[i]);
+    for (int i = 0; i < a->n_slice && i < MTL_MAX_RANK; ++i) {
+        r.starts.push_back(a->starts[i]);
+        r.ends.push_back(a->ends[i]);
+        if (a->has_steps) r.steps.push_back(a->steps[i]);
+    }
     return r;
 }
 

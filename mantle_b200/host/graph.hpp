@@ -58,6 +58,8 @@ struct Attributes {
     float negative_slope = 0.01f;            // LEAKYRELU
     std::optional<float> clip_min, clip_max; // CLIP
     std::vector<int> dims;                   // SQUEEZE / UNSQUEEZE
+    std::vector<int> axes;                   // TRANSPOSE (empty = reversed), SLICE (empty = 0, 1, ...)
+    std::vector<int64_t> starts, ends, steps;  // SLICE (steps empty = all 1)
 };
 
 struct Node {
@@ -137,6 +139,7 @@ struct Graph {
     static TensorShape reduce_shape(const TensorShape& t, const Attributes& a);
     static void conv_out(const TensorShape& in, int R, int S, const Attributes& a, int64_t* oh, int64_t* ow);
     static TensorShape static_result_shape(int op_id, const std::vector<Symbol>& operands, const Attributes& attrs);
+    static mtl_slice_desc slice_desc(const Attributes& a);
 };
 
 }  // namespace mantle

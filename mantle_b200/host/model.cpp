@@ -121,9 +121,49 @@ TensorShape Graph::static_result_shape(int op, const std::vector<Symbol>& o, con
         case MTL_OP_FMA:
             need(3);
             return o[0].shape;
+        case MTL_OP_TRANSPOSE: {  // basics.mojo:618-637
+            need(1);
+            const int rank = o[0].shape.rank;
+            if (!a.axes.empty() && (int)a.axes.size() != rank)
+                throw Error(MTL_ERR_INVALID, "TRANSPOSE axes must name every axis once");
+            TensorShape r;
+            r.rank = rank;
+            for (int i = 0; i < rank; ++i) {
+                const int ax = a.axes.empty() ? rank - 1 - i : a.axes[i];
+                if (ax < 0 || ax >= rank) throw Error(MTL_ERR_INVALID, "TRANSPOSE axis out of range");
+                r.dims[i] = o[0].shape[ax];
+            }
+            return r;
+        }
+        case MTL_OP_SLICE: {  // mlops.mojo:420-450
+            need(1);
+            mtl_slice_desc d = slice_desc(a);
+            TensorShape r;
+            r.rank = o[0].shape.rank;
+            if (mtl_slice_out_shape(o[0].shape.rank, o[0].shape.dims, &d, r.dims) != MTL_OK)
+                throw Error(MTL_ERR_INVALID, "SLICE attributes do not select a non-empty part of the tensor");
+            return r;
+        }
         default:
             throw Error(MTL_ERR_UNSUPPORTED, "operator id " + std::to_string(op) + " is not on the GPU path");
     }
+}
+
+// SLICE attributes in the C ABI's form
+mtl_slice_desc Graph::slice_desc(const Attributes& a) {
+    mtl_slice_desc d;
+    std::memset(&d, 0, sizeof(d));
+    if (a.starts.size() != a.ends.size() || a.starts.size() > (size_t)MTL_MAX_RANK ||
+        (!a.steps.empty() && a.steps.size() != a.starts.size()) || (!a.axes.empty() && a.axes.size() != a.starts.size()))
+        throw Error(MTL_ERR_INVALID, "SLICE needs starts, ends (and steps, axes) of one length");
+    d.n = (int32_t)a.starts.size();
+    for (int i = 0; i < d.n; ++i) {
+        d.starts[i] = a.starts[i];
+        d.ends[i] = a.ends[i];
+        d.steps[i] = a.steps.empty() ? 1 : a.steps[i];
+        d.axes[i] = a.axes.empty() ? -1 : a.axes[i];
+    }
+    return d;
 }
 
 // ------------------------------------------------------------------ Model ------------------
@@ -475,6 +515,15 @@ void Model::forward_op(const Node& n) {
         case MTL_OP_FMA:
             check(mtl_fma_fwd(ctx_, T(out), T(t1), T(n.inputs[1]), T(n.inputs[2]), t1.shape.num_elements()), "FMA forward");
             break;
+        case MTL_OP_TRANSPOSE:
+            check(mtl_transpose_fwd(ctx_, T(out), T(t1), t1.shape.rank, t1.shape.dims,
+                                    n.attrs.axes.empty() ? nullptr : n.attrs.axes.data()), "TRANSPOSE forward");
+            break;
+        case MTL_OP_SLICE: {
+            mtl_slice_desc d = Graph::slice_desc(n.attrs);
+            check(mtl_slice_fwd(ctx_, T(out), T(t1), t1.shape.rank, t1.shape.dims, &d), "SLICE forward");
+            break;
+        }
         default:
             throw Error(MTL_ERR_UNSUPPORTED, "operator id " + std::to_string(n.op) + " is not on the GPU path");
     }
@@ -549,6 +598,15 @@ void Model::backward_op(const Node& n, int tensor_id) {
         case MTL_OP_FMA:
             check(mtl_fma_bwd(ctx_, tensor_id, grad, ug, T(t1), T(n.inputs[1]), t1.shape.num_elements(), acc), "FMA backward");
             break;
+        case MTL_OP_TRANSPOSE:
+            check(mtl_transpose_bwd(ctx_, grad, ug, t1.shape.rank, t1.shape.dims,
+                                    n.attrs.axes.empty() ? nullptr : n.attrs.axes.data(), acc), "TRANSPOSE backward");
+            break;
+        case MTL_OP_SLICE: {
+            mtl_slice_desc d = Graph::slice_desc(n.attrs);
+            check(mtl_slice_bwd(ctx_, grad, ug, t1.shape.rank, t1.shape.dims, &d, acc), "SLICE backward");
+            break;
+        }
         default:
             throw Error(MTL_ERR_UNSUPPORTED, "operator id " + std::to_string(n.op) + " is not on the GPU path");
     }

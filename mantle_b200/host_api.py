@@ -22,7 +22,11 @@ class _Attrs(C.Structure):
                 ("kernel_size", C.c_int32 * 2), ("negative_slope", C.c_float),
                 ("has_clip_min", C.c_int32), ("has_clip_max", C.c_int32),
                 ("clip_min", C.c_float), ("clip_max", C.c_float),
-                ("n_dims", C.c_int32), ("dims", C.c_int32 * MTL_MAX_RANK)]
+                ("n_dims", C.c_int32), ("dims", C.c_int32 * MTL_MAX_RANK),
+                ("n_axes", C.c_int32), ("axes", C.c_int32 * MTL_MAX_RANK),
+                ("n_slice", C.c_int32), ("has_steps", C.c_int32),
+                ("starts", C.c_int64 * MTL_MAX_RANK), ("ends", C.c_int64 * MTL_MAX_RANK),
+                ("steps", C.c_int64 * MTL_MAX_RANK)]
 
 
 def _make_attrs(attrs: dict) -> _Attrs:
@@ -49,6 +53,15 @@ def _make_attrs(attrs: dict) -> _Attrs:
         elif k == "dims":
             a.n_dims = len(v)
             a.dims[:len(v)] = [int(x) for x in v]
+        elif k == "axes":
+            a.n_axes = len(v)
+            a.axes[:len(v)] = [int(x) for x in v]
+        elif k in ("starts", "ends"):
+            a.n_slice = len(v)
+            getattr(a, k)[:len(v)] = [int(x) for x in v]
+        elif k == "steps":
+            a.has_steps = 1
+            a.steps[:len(v)] = [int(x) for x in v]
         else:
             raise ValueError("unknown attribute %r" % k)
     return a

@@ -76,6 +76,12 @@ def static_result_shape(op, operands, attrs):
         oh, ow = _conv_out(s[0], k[0], k[1], attrs.get("padding", (0, 0)), attrs.get("stride", k),
                            attrs.get("dilation", (1, 1)))
         return (s[0][0], s[0][1], oh, ow)
+    if op == OP.TRANSPOSE:
+        axes = attrs.get("axes") or tuple(range(len(s[0]) - 1, -1, -1))
+        return tuple(s[0][a] for a in axes)
+    if op == OP.SLICE:
+        from . import layout
+        return tuple(layout.slice_plan(s[0], attrs["starts"], attrs["ends"], attrs.get("steps"), attrs.get("axes"))[2])
     raise NotImplementedError("operator %d" % op)
 
 

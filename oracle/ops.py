@@ -19,6 +19,7 @@ class OP:
     ADD, SUB, MUL, DIV, EXP, LOG, POW, DOT, SUM, MEAN, MAX = range(11)
     FLATTEN, RESHAPE, SIGMOID, RELU, TANH, CONV2D, TRANSPOSE, MAXPOOL2D, FMA = range(11, 20)
     CLIP, SQUEEZE, UNSQUEEZE = 20, 21, 22
+    CONCAT, SPLIT, SLICE = 23, 24, 25
     LEAKYRELU = 28
 
 
@@ -244,6 +245,12 @@ def forward_op(op, t1, t2=None, t3=None, **attrs):
                              attrs.get("dilation", (1, 1)))
     if op == OP.FMA:
         return (_f(t1) * _f(t2) + _f(t3)).astype(np.float32)  # fma in the reference; tolerance-compared
+    if op == OP.TRANSPOSE:
+        from . import layout
+        return layout.transpose_fwd(_f(t1), attrs.get("axes"))
+    if op == OP.SLICE:
+        from . import layout
+        return layout.slice_fwd(_f(t1), attrs["starts"], attrs["ends"], attrs.get("steps"), attrs.get("axes"))
     raise NotImplementedError(op)
 
 
@@ -268,6 +275,12 @@ def backward_op(tensor_id, op, ug, t1, t2=None, t3=None, grad=None, **attrs):
                             attrs.get("dilation", (1, 1)))
     elif op == OP.FMA:
         res = [_f(ug) * _f(t2), _f(ug) * _f(t1), _f(ug)][tensor_id]
+    elif op == OP.TRANSPOSE:
+        from . import layout
+        res = layout.transpose_bwd(ug, np.shape(t1), attrs.get("axes"))
+    elif op == OP.SLICE:
+        from . import layout
+        res = layout.slice_bwd(ug, np.shape(t1), attrs["starts"], attrs["ends"], attrs.get("steps"), attrs.get("axes"))
     else:
         raise NotImplementedError(op)
     if grad is None:

@@ -137,4 +137,10 @@ def test_host_graph_shape_rules(built):
     with pytest.raises(mb.MantleError):
         g.op(OP.DOT, g.input((2, 3)), g.input((4, 5)))
     with pytest.raises(mb.MantleError):
-        g.op(25, x)                               # SLICE is not on the GPU path
+        g.op(23, x)                               # CONCAT: a multi-output "dynamic" node, C ABI only
+    assert g.op(OP.TRANSPOSE, x).shape == (4, 3, 2)
+    assert g.op(OP.TRANSPOSE, x, axes=(1, 2, 0)).shape == (3, 4, 2)
+    assert g.op(OP.SLICE, x, starts=(1,), ends=(3,), steps=(1,), axes=(2,)).shape == (2, 3, 2)
+    assert g.op(OP.SLICE, x, starts=(0, 2, -1), ends=(2, 0, -5), steps=(1, -1, -2)).shape == (2, 2, 2)
+    with pytest.raises(mb.MantleError):
+        g.op(OP.SLICE, x, starts=(3,), ends=(1,), axes=(1,))   # empty

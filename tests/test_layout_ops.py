@@ -156,3 +156,36 @@ def test_concat_and_split_kernels(ctx):
         assert np.array_equal(g.numpy(), layout.split_bwd(ugs, t.shape, sections, 1) + (init if acc else 0))
     bad = (C.c_int64 * 3)(5, 5, 3)
     assert L.mtl_split_fwd(h, ptrs, ctx.array(t).ptr, 3, 3, _shape(t.shape), bad, 1) != 0
+
+
+@pytest.mark.gpu
+def test_transpose_and_slice_as_graph_nodes(ctx):
+    """A small graph through TRANSPOSE and SLICE nodes: loss and parameter gradients of the C++ mirror
+    against the oracle's executor (Graph.op with the reference's attribute names)."""
+    from mantle_b200 import OP, host_api
+    from test_models_gpu import make_pair
+
+    def build(ns, g):
+        x = g.input((6, 5))
+        y = g.input((3, 4))
+        h = ns.nn.Linear(g, x, 8)                                  # [6, 8]
+        h = g.op(OP.TRANSPOSE, h)                                  # [8, 6]
+        h = g.op(OP.SLICE, h, starts=(1, 5), ends=(8, 0), steps=(2, -2), axes=(0, 1))   # rows 1,3,5,7; cols 5,3,1 -> [4, 3]
+        h = g.op(OP.TRANSPOSE, h, axes=(1, 0))                     # [3, 4]
+        g.out(h)
+        g.loss(ns.nn.MSELoss(g, h, y))
+
+    (g, m), (og, om) = make_pair(ctx, build, seed=61)
+    rng = np.random.default_rng(62)
+    x = rng.normal(0, 1, (6, 5)).astype(np.float32)
+    y = rng.normal(0, 1, (3, 4)).astype(np.float32)
+    loss, oloss = m.forward(x, y), om.forward(x, y)
+    assert abs(loss - oloss) <= 1e-5 * abs(oloss) + 1e-6
+    m.zero_grads(); om.zero_grads()
+    m.backward(); om.backward()
+    for s, os_ in zip(g.params(), og.params()):
+        if s.trainable:
+            assert np.allclose(m.grad(s), om.grad(os_), rtol=1e-4, atol=1e-6)
+    out_sym = host_api.Symbol(g, g.node(4)["output"])   # Linear = DOT + ADD, then TRANSPOSE, SLICE, TRANSPOSE
+    got = m.inference(x, y, outputs=[out_sym])[0]
+    assert got.shape == (3, 4) and np.allclose(got, om.inference(x, y)[0], rtol=1e-5, atol=1e-6)
