@@ -1,0 +1,98 @@
+"""Data-parallel training on real GPUs (one process per GPU, NCCL through mtl_dp_*): the loss
+trajectory of G ranks on slices of the global batch equals the single-GPU trajectory on the whole
+batch within 1e-3 relative, and all ranks end with identical parameters.  Needs at least two
+visible GPUs; skipped otherwise."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+pytestmark = pytest.mark.gpu
+
+STEPS, GLOBAL_B = 12, 64
+
+
+def _data():
+    rng = np.random.default_rng(17)
+    x = rng.uniform(0, 1, (STEPS, GLOBAL_B, 1, 28, 28)).astype(np.float32)
+    y = np.eye(10, dtype=np.float32)[rng.integers(0, 10, (STEPS, GLOBAL_B))]
+    shapes = [(64, 1, 5, 5), (64,), (128, 64, 5, 5), (128,), (6272, 10), (10,)]
+    ws = [(rng.uniform(-1, 1, s) / np.sqrt(max(int(np.prod(s[1:])), 16))).astype(np.float32) for s in shapes]
+    return x, y, ws
+
+
+def _train(rank, world, uid, q):
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    import ctypes as C
+    import mantle_b200 as mb
+    from mantle_b200 import host_api, OP
+    from test_oracle_kat import build_cnn
+
+    class Ns:
+        OP, nn, Graph = OP, host_api.nn, host_api.Graph
+
+    x, y, ws = _data()
+    ctx = mb.Context(rank, mb.MATH_TF32X3)
+    if world > 1:
+        raw = (C.c_uint8 * mb._lib.MTL_DP_ID_BYTES)(*uid)
+        ctx._check(ctx.lib.mtl_dp_init(ctx.handle, raw, rank, world))
+    lb = GLOBAL_B // world
+    g = host_api.Graph()
+    build_cnn(Ns, g, lb, 64, 128)
+    m = host_api.Model(ctx, g)
+    tr = [s for s in g.params() if s.trainable]
+    for s, w in zip(tr, ws):
+        m.set_tensor(s, w)
+    trainer = host_api.Trainer(m, host_api.Adam(m, lr=1e-3), use_graph=True)
+    losses = [trainer.step(x[i, rank * lb:(rank + 1) * lb], y[i, rank * lb:(rank + 1) * lb]) for i in range(STEPS)]
+    params = [m.tensor(s) for s in tr]
+    status = ctx.device_status()
+    trainer.close()
+    q.put((rank, losses, params, status))
+    ctx.close()
+
+
+def _run(world):
+    import torch.multiprocessing as mp
+    import ctypes as C
+    import mantle_b200 as mb
+    uid = None
+    if world > 1:
+        raw = (C.c_uint8 * mb._lib.MTL_DP_ID_BYTES)()
+        assert mb.cuda_lib().mtl_dp_get_unique_id(raw) == 0, "NCCL is not loadable"
+        uid = list(raw)
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    procs = [mpc.Process(target=_train, args=(r, world, uid, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = sorted((q.get(timeout=300) for _ in range(world)), key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    return out
+
+
+@pytest.mark.parametrize("world", (2, 4, 8))
+def test_data_parallel_trajectory_equals_single_gpu(world):
+    import torch
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    single = _run(1)[0]
+    ranks = _run(world)
+    assert all(r[3] == 0 for r in ranks) and single[3] == 0
+    # the global loss is the mean of the per-rank mean losses (equal slice sizes)
+    got = np.mean([r[1] for r in ranks], axis=0)
+    want = np.asarray(single[1])
+    assert np.allclose(got, want, rtol=1e-3, atol=1e-6), (got, want)
+    assert got[-1] < got[0]
+    for r in ranks[1:]:                       # replicas stay identical
+        for a, b in zip(ranks[0][2], r[2]):
+            assert np.array_equal(a, b)
+    for a, b in zip(ranks[0][2], single[2]):  # and close to the single-GPU parameters
+        assert np.linalg.norm(a - b) <= 2e-2 * np.linalg.norm(b) + 1e-6
