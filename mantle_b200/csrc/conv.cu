@@ -94,6 +94,12 @@ int32_t mtl_conv2d_fwd_act_pool_cl(mtl_ctx* ctx, float* pooled, int32_t* idx, fl
     const bool tc = ctx->math_mode != MTL_MATH_FP32 && mtl_conv_fwd_tc_supported(g, X, Wt, pooled);
     if (pool_2x2 && !tc && mtl_conv_fwd_pool_simt_supported(g, pooled))
         return mtl_conv_fwd_pool_simt(ctx, pooled, idx, pooled_cl, X, Wt, bias, g, relu);
+    if (pool_2x2 && tc && mtl_conv_fwd_pool_tc_supported(g, X, Wt, pooled)) {
+        // the implicit-GEMM kernel pools in its epilogue: the activation never reaches memory
+        rc = mtl_conv_fwd_pool_tc(ctx, pooled, idx, X, Wt, bias, g, ctx->math_mode == MTL_MATH_TF32X3, relu, X_cl);
+        if (rc || !pooled_cl) return rc;
+        return mtl_channels_last_copy(ctx, pooled_cl, pooled, g.N, g.K, (g.OH / 2) * (g.OW / 2));
+    }
     // no kernel pools this geometry in its epilogue: the activation goes through scratch memory
     void* scratch;
     rc = mtl_workspace2(ctx, (size_t)g.N * g.K * g.OH * g.OW * 4, &scratch);

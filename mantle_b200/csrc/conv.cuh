@@ -42,6 +42,9 @@ bool mtl_conv_wgrad_tc_supported(const ConvGeom& g, const float* ug, const float
 int32_t mtl_conv_fwd_tc(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
                         const ConvGeom& g, int x3, int relu, const float* X_cl);
 int32_t mtl_channels_last_copy(mtl_ctx* ctx, float* dst, const float* src, int N, int C, int HW);
+bool mtl_conv_fwd_pool_tc_supported(const ConvGeom& g, const float* X, const float* Wt, const float* pooled);
+int32_t mtl_conv_fwd_pool_tc(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X, const float* Wt,
+                             const float* bias, const ConvGeom& g, int x3, int relu, const float* X_cl);
 int32_t mtl_conv_dgrad_tc(mtl_ctx* ctx, float* dX, const float* ug, const float* Wt, const ConvGeom& g,
                           int accumulate, int x3);
 int32_t mtl_conv_wgrad_tc(mtl_ctx* ctx, float* dW, const float* ug, const float* X, const ConvGeom& g,

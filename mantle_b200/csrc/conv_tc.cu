@@ -461,6 +461,8 @@ struct IgemmCall {
     int accumulate;
     int relu;           // clamp the result at zero after the bias (forward with a fused RELU)
     const float* act_cl = nullptr;  // channels-last copy of `act` the caller already has (plain TF32 only)
+    int pool = 0;                   // 2x2 / stride-2 max pooling in the epilogue: out = pooled values
+    int32_t* pool_idx = nullptr;    // argmax indices of that pooling (may be null)
 };
 
 // ------------------------------------------------------------------ channel-major variant -----
@@ -474,7 +476,8 @@ constexpr int kTStages = 4;
 constexpr int kTABytes = BM * BK * 4;        // weights tile
 constexpr int kTBBytes = 256 * BK * 4;       // pixel tile (maximum)
 constexpr int kTStageBytes = kTABytes + kTBBytes;
-constexpr int kTSmemBytes = kTStages * kTStageBytes + 1024 + 256 + 256 * 4 + 64 * 4 + 4 * 32 * 36 * 4;
+constexpr int kTStgFloats = 32 * 36 + 2 * 32 * 8;  // per epilogue warp: transposition block, pooled values + indices
+constexpr int kTSmemBytes = kTStages * kTStageBytes + 1024 + 256 + 256 * 4 + 64 * 4 + 4 * kTStgFloats * 4;
 
 struct ConvTParams {
     int N, OH, OW, Kout, Cin;
@@ -487,6 +490,11 @@ struct ConvTParams {
     const float* bias;
     int accumulate;
     int relu;
+    // 2x2 / stride-2 max pooling in the epilogue (box = whole rows, two of them, at most 32 pixels per
+    // image): `out` then receives the pooled values [N, Kout, OH/2, OW/2] and pool_idx the argmax indices
+    // (plane-local, MAXPOOL2D.forward's strict '>' scan in row-major window order, pool.mojo:44-100)
+    int pool;
+    int32_t* pool_idx;
     // Tap pairing (at most 64 output channels): of every 32 rows of the weight tile, 16 hold tap
     // (r, 2*si) of 16 channels and 16 hold tap (r, 2*si + 1) of the same channels; both see the pixel
     // box of the first tap, so the second half of the accumulator is the second tap's contribution to
@@ -515,7 +523,7 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* col_off = reinterpret_cast<int*>(smem + kTStages * kTStageBytes + 256);
     int* col_vec = col_off + 256;
-    float* stage_buf = reinterpret_cast<float*>(col_vec + 64);  // 4 warps x 32 x 36 floats
+    float* stage_buf = reinterpret_cast<float*>(col_vec + 64);  // 4 warps x kTStgFloats
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -656,8 +664,57 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
             // stores then take as long as the whole main loop).  Each warp therefore turns its
             // 32 channels x 32 pixels block through shared memory so that eight lanes write 32
             // adjacent pixels of one channel.
-            float* stg = stage_buf + (warp - 2) * (32 * 36);
+            float* stg = stage_buf + (warp - 2) * kTStgFloats;
             const int sub = lane & 7, chl = lane >> 3;
+            if (p.pool) {
+                // one image of the box at a time: its bw x 2 pixels are adjacent accumulator columns
+                const int P = p.bw * p.bh, PWD = p.bw >> 1, POH = p.OH >> 1;
+                float* prow = stg + lane * 33;                       // this thread's pixels, conflict-free
+                float* pvs = stg + 32 * 36;                          // [32][8] pooled values
+                int32_t* pis = reinterpret_cast<int32_t*>(pvs + 32 * 8);  // [32][8] argmax indices
+                const int poh = oh0 >> 1;
+#pragma unroll 1
+                for (int n_i = 0; n_i < p.bn; ++n_i) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride + n_i * P), r);
+                    tmem_ld_wait();
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float v = __uint_as_float(r[j]) + bv;
+                        if (p.relu) v = v > 0.0f ? v : 0.0f;
+                        prow[j] = v;
+                    }
+                    for (int pw = 0; pw < PWD; ++pw) {
+                        const int i00 = oh0 * p.OW + 2 * pw;
+                        const float a = prow[2 * pw], b = prow[2 * pw + 1], c = prow[p.bw + 2 * pw], d = prow[p.bw + 2 * pw + 1];
+                        float m = -INFINITY;
+                        int j = -1;
+                        if (a > m) { m = a; j = i00; }
+                        if (b > m) { m = b; j = i00 + 1; }
+                        if (c > m) { m = c; j = i00 + p.OW; }
+                        if (d > m) { m = d; j = i00 + p.OW + 1; }
+                        pvs[lane * 8 + pw] = m;
+                        pis[lane * 8 + pw] = j;
+                    }
+                    __syncwarp();
+                    const int n = n0 + n_i;
+                    if (n < p.N) {
+                        for (int e = lane; e < 32 * PWD; e += 32) {
+                            const int ch = e / PWD, pw = e - ch * PWD;
+                            const int kk = kt * BM + quad * 32 + ch;
+                            if (kk < p.Kout) {
+                                const int64_t o = (((int64_t)n * p.Kout + kk) * POH + poh) * PWD + pw;
+                                p.out[o] = pvs[ch * 8 + pw];
+                                if (p.pool_idx) p.pool_idx[o] = pis[ch * 8 + pw];
+                            }
+                        }
+                    }
+                }
+                tc_fence_before_sync();
+                mbar_arrive(&tmem_empty[acc]);
+                continue;
+            }
 #pragma unroll 1
             for (int c = 0; c * 32 < p.npix; ++c) {
                 uint32_t r[32];
@@ -864,7 +921,15 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
         q.s_count = paired ? (c.S + 1) / 2 : c.S;
         q.s_step = paired ? 2 : 1;
         q.acc_stride = paired ? 248 : 256;
-        if (paired) {
+        q.pool = c.pool;
+        q.pool_idx = c.pool_idx;
+        if (c.pool) {
+            // whole rows, two of them, as many images as fit while the last 32-column read stays inside
+            q.bw = c.OW;
+            q.bh = 2;
+            q.bn = (256 - 32) / (2 * c.OW) + 1;
+            if (q.bn > c.N) q.bn = c.N;
+        } else if (paired) {
             // whole rows plus the extra column; the box that fills most of 240 columns
             q.bw = c.OW + 1;
             double best = -1.0;
@@ -1190,6 +1255,27 @@ bool mtl_conv_dgrad_tc_supported(const ConvGeom& g, const float* ug, const float
     if (g.ph > g.R - 1 || g.pw > g.S - 1) return false;
     if ((((uintptr_t)ug) | ((uintptr_t)Wt) | ((uintptr_t)dX)) & 15u) return false;
     return true;
+}
+
+// CONV2D (+ RELU) + 2x2 / stride-2 MAXPOOL2D in the epilogue of the channel-major kernel.
+bool mtl_conv_fwd_pool_tc_supported(const ConvGeom& g, const float* X, const float* Wt, const float* pooled) {
+    if (!mtl_conv_fwd_tc_supported(g, X, Wt, pooled)) return false;
+    IgemmCall c;
+    c.N = g.N; c.Cin = g.C; c.IH = g.H; c.IW = g.W; c.Kout = g.K; c.OH = g.OH; c.OW = g.OW;
+    c.R = g.R; c.S = g.S; c.ph = g.ph; c.pw = g.pw; c.wK = g.K; c.wC = g.C; c.flip = 0;
+    return igemm_channel_major(c) && g.K > 64 && g.OW % 2 == 0 && g.OW <= 16 && g.OH % 2 == 0 &&
+           !(getenv("MANTLE_CONV_POOL_EPILOGUE") && atoi(getenv("MANTLE_CONV_POOL_EPILOGUE")) == 0);
+}
+
+int32_t mtl_conv_fwd_pool_tc(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X, const float* Wt,
+                             const float* bias, const ConvGeom& g, int x3, int relu, const float* X_cl) {
+    IgemmCall c;
+    c.N = g.N; c.Cin = g.C; c.IH = g.H; c.IW = g.W; c.Kout = g.K; c.OH = g.OH; c.OW = g.OW;
+    c.R = g.R; c.S = g.S; c.ph = g.ph; c.pw = g.pw;
+    c.act = X; c.wt = Wt; c.wK = g.K; c.wC = g.C; c.flip = 0;
+    c.out = pooled; c.bias = bias; c.accumulate = 0; c.relu = relu; c.act_cl = X_cl;
+    c.pool = 1; c.pool_idx = idx;
+    return run_igemm(ctx, c, x3);
 }
 
 // Plain channels-last copy [N, C, HW] -> [N, HW, C] (no operand split), for callers that keep one.
