@@ -476,7 +476,7 @@ constexpr int kTStages = 4;
 constexpr int kTABytes = BM * BK * 4;        // weights tile
 constexpr int kTBBytes = 256 * BK * 4;       // pixel tile (maximum)
 constexpr int kTStageBytes = kTABytes + kTBBytes;
-constexpr int kTStgFloats = 32 * 36 + 2 * 32 * 8;  // per epilogue warp: transposition block, pooled values + indices
+constexpr int kTStgFloats = 32 * 36;  // per epilogue warp: transposition block
 constexpr int kTSmemBytes = kTStages * kTStageBytes + 1024 + 256 + 256 * 4 + 64 * 4 + 4 * kTStgFloats * 4;
 
 struct ConvTParams {
@@ -507,6 +507,34 @@ struct ConvTParams {
     int vec_ok;             // channel planes are 16-byte aligned: four adjacent pixels may leave as a float4
     int32_t* status;
 };
+
+// 2x2 / stride-2 max pooling of one channel's BW x 2 pixels held in registers (r[0..BW) the upper row,
+// r[BW..2BW) the lower), after bias and RELU.  MAXPOOL2D.forward order: the window is scanned
+// row-major with a strict '>', so the first of equal values wins.  Values and argmax indices go to
+// shared memory at [channel * 9 + column] (stride 9 keeps both the writes and the reads spread
+// over the banks).
+template <int BW>
+__device__ __forceinline__ void pool_rows_in_registers(const uint32_t (&r)[32], float bv, int relu, int i00, int OW,
+                                                       float* pv, int32_t* pi) {
+#pragma unroll
+    for (int pw = 0; pw < BW / 2; ++pw) {
+        float a = __uint_as_float(r[2 * pw]) + bv, b = __uint_as_float(r[2 * pw + 1]) + bv;
+        float c = __uint_as_float(r[BW + 2 * pw]) + bv, d = __uint_as_float(r[BW + 2 * pw + 1]) + bv;
+        if (relu) {
+            a = a > 0.0f ? a : 0.0f; b = b > 0.0f ? b : 0.0f;
+            c = c > 0.0f ? c : 0.0f; d = d > 0.0f ? d : 0.0f;
+        }
+        float m = -INFINITY;
+        int j = -1;
+        const int i = i00 + 2 * pw;
+        if (a > m) { m = a; j = i; }
+        if (b > m) { m = b; j = i + 1; }
+        if (c > m) { m = c; j = i + OW; }
+        if (d > m) { m = d; j = i + OW + 1; }
+        pv[pw] = m;
+        pi[pw] = j;
+    }
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant__ CUtensorMap mapX1,
@@ -667,46 +695,80 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
             float* stg = stage_buf + (warp - 2) * kTStgFloats;
             const int sub = lane & 7, chl = lane >> 3;
             if (p.pool) {
-                // one image of the box at a time: its bw x 2 pixels are adjacent accumulator columns
+                // One image of the box at a time: its bw x 2 pixels are adjacent accumulator columns.
+                // Each thread parks its channel's pixels in shared memory; then eight lanes take the
+                // (up to) eight pooled columns of one channel, so a warp store covers four channels'
+                // pooled rows.  MAXPOOL2D.forward order: window scanned row-major, strict '>', first wins.
                 const int P = p.bw * p.bh, PWD = p.bw >> 1, POH = p.OH >> 1;
-                float* prow = stg + lane * 33;                       // this thread's pixels, conflict-free
-                float* pvs = stg + 32 * 36;                          // [32][8] pooled values
-                int32_t* pis = reinterpret_cast<int32_t*>(pvs + 32 * 8);  // [32][8] argmax indices
+                float* prow = stg + lane * 33;
                 const int poh = oh0 >> 1;
+                const int i00 = oh0 * p.OW + 2 * sub;
+                const bool pw_ok = sub < PWD;
+                const bool in_regs = p.bw == 14 || p.bw == 16 || p.bw == 12 || p.bw == 8;
 #pragma unroll 1
                 for (int n_i = 0; n_i < p.bn; ++n_i) {
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride + n_i * P), r);
                     tmem_ld_wait();
                     __syncwarp();
+                    const int n = n0 + n_i;
+                    const int kk0 = kt * BM + quad * 32 + chl;
+                    int64_t o = (((int64_t)n * p.Kout + kk0) * POH + poh) * PWD + sub;
+                    const int64_t ostep = (int64_t)4 * POH * PWD;
+                    if (in_regs) {
+                        float* pv = stg + lane * 9;
+                        int32_t* pi = reinterpret_cast<int32_t*>(stg + 32 * 9) + lane * 9;
+                        const int ib = oh0 * p.OW;
+                        if (p.bw == 14) pool_rows_in_registers<14>(r, bv, p.relu, ib, p.OW, pv, pi);
+                        else if (p.bw == 16) pool_rows_in_registers<16>(r, bv, p.relu, ib, p.OW, pv, pi);
+                        else if (p.bw == 12) pool_rows_in_registers<12>(r, bv, p.relu, ib, p.OW, pv, pi);
+                        else pool_rows_in_registers<8>(r, bv, p.relu, ib, p.OW, pv, pi);
+                        __syncwarp();
+                        if (n < p.N && pw_ok) {
+                            float m[8];
+                            int at[8];
+#pragma unroll
+                            for (int it = 0; it < 8; ++it) {
+                                m[it] = stg[(it * 4 + chl) * 9 + sub];
+                                at[it] = reinterpret_cast<const int32_t*>(stg + 32 * 9)[(it * 4 + chl) * 9 + sub];
+                            }
+#pragma unroll
+                            for (int it = 0; it < 8; ++it, o += ostep) {
+                                if (kk0 + it * 4 < p.Kout) {
+                                    p.out[o] = m[it];
+                                    if (p.pool_idx) p.pool_idx[o] = at[it];
+                                }
+                            }
+                        }
+                        continue;
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         float v = __uint_as_float(r[j]) + bv;
                         if (p.relu) v = v > 0.0f ? v : 0.0f;
                         prow[j] = v;
                     }
-                    for (int pw = 0; pw < PWD; ++pw) {
-                        const int i00 = oh0 * p.OW + 2 * pw;
-                        const float a = prow[2 * pw], b = prow[2 * pw + 1], c = prow[p.bw + 2 * pw], d = prow[p.bw + 2 * pw + 1];
-                        float m = -INFINITY;
-                        int j = -1;
-                        if (a > m) { m = a; j = i00; }
-                        if (b > m) { m = b; j = i00 + 1; }
-                        if (c > m) { m = c; j = i00 + p.OW; }
-                        if (d > m) { m = d; j = i00 + p.OW + 1; }
-                        pvs[lane * 8 + pw] = m;
-                        pis[lane * 8 + pw] = j;
-                    }
                     __syncwarp();
-                    const int n = n0 + n_i;
-                    if (n < p.N) {
-                        for (int e = lane; e < 32 * PWD; e += 32) {
-                            const int ch = e / PWD, pw = e - ch * PWD;
-                            const int kk = kt * BM + quad * 32 + ch;
-                            if (kk < p.Kout) {
-                                const int64_t o = (((int64_t)n * p.Kout + kk) * POH + poh) * PWD + pw;
-                                p.out[o] = pvs[ch * 8 + pw];
-                                if (p.pool_idx) p.pool_idx[o] = pis[ch * 8 + pw];
+                    if (n < p.N && pw_ok) {
+                        float m[8];
+                        int at[8];
+#pragma unroll
+                        for (int it = 0; it < 8; ++it) {
+                            const float* q = stg + (it * 4 + chl) * 33 + 2 * sub;
+                            const float a = q[0], b = q[1], c = q[p.bw], d = q[p.bw + 1];
+                            float mm = -INFINITY;
+                            int j = -1;
+                            if (a > mm) { mm = a; j = i00; }
+                            if (b > mm) { mm = b; j = i00 + 1; }
+                            if (c > mm) { mm = c; j = i00 + p.OW; }
+                            if (d > mm) { mm = d; j = i00 + p.OW + 1; }
+                            m[it] = mm; at[it] = j;
+                        }
+#pragma unroll
+                        for (int it = 0; it < 8; ++it, o += ostep) {
+                            if (kk0 + it * 4 < p.Kout) {
+                                p.out[o] = m[it];
+                                if (p.pool_idx) p.pool_idx[o] = at[it];
                             }
                         }
                     }

@@ -382,8 +382,11 @@ def test_conv_with_fused_relu_equals_two_calls(ctx, case):
         assert (z.numpy() == 0).any() and (z.numpy() > 0).any()
 
 
-FUSED_CONV_POOL = [  # first-layer kernel that pools itself; tensor-core layer and odd shapes through scratch memory
+FUSED_CONV_POOL = [  # first-layer kernel that pools itself; odd shapes through scratch memory; tensor-core layers that
+    # pool in the epilogue (row widths 14, 16, 12, 8 in registers, 10 through shared memory, partial channel tiles)
     (70, 1, 28, 28, 64, 5, 5, 2), (65, 3, 28, 28, 40, 3, 3, 1), (6, 64, 14, 14, 128, 5, 5, 2), (3, 2, 10, 12, 5, 3, 3, 1),
+    (23, 32, 14, 14, 160, 3, 3, 1), (5, 32, 16, 16, 80, 3, 3, 1), (10, 16, 12, 12, 72, 3, 3, 1), (20, 16, 8, 8, 128, 3, 3, 1),
+    (12, 16, 10, 10, 96, 3, 3, 1),
 ]
 
 
@@ -399,7 +402,7 @@ def test_conv_relu_pool_equals_three_calls(ctx, case):
     kw = dict(padding=(p, p), stride=(1, 1), dilation=(1, 1))
     oh, ow = mb.conv2d_out_shape((N, C, H, W), (K, C, R, S), **kw)
     pkw = dict(kernel_size=(2, 2), stride=(2, 2), padding=(0, 0), dilation=(1, 1))
-    for mode in (mb.MATH_TF32X3, mb.MATH_FP32):
+    for mode in (mb.MATH_TF32X3, mb.MATH_TF32, mb.MATH_FP32):
         ctx.set_math_mode(mode)
         try:
             y, z = ctx.empty((N, K, oh, ow)), ctx.empty((N, K, oh, ow))
