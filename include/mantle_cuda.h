@@ -385,7 +385,8 @@ enum mtl_prof_kernel {
     MTL_PROF_DOT_TC = 0,       /* tcgen05 GEMM behind OP.DOT                          */
     MTL_PROF_CONV_IGEMM = 1,   /* tcgen05 implicit GEMM: CONV2D forward / input grad  */
     MTL_PROF_CONV_WGRAD = 2,   /* tcgen05 implicit GEMM: CONV2D kernel gradient       */
-    MTL_PROF_KERNELS = 3
+    MTL_PROF_CONV_FIRST = 3,   /* tcgen05 first-layer CONV2D + RELU + MAXPOOL2D       */
+    MTL_PROF_KERNELS = 4
 };
 MTL_API int32_t mtl_prof_enable(mtl_ctx* ctx, int32_t on);
 MTL_API int32_t mtl_prof_reset(mtl_ctx* ctx);

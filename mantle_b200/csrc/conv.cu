@@ -92,6 +92,8 @@ int32_t mtl_conv2d_fwd_act_pool_cl(mtl_ctx* ctx, float* pooled, int32_t* idx, fl
                           pool->pad[0] == 0 && pool->pad[1] == 0 && pool->dilation[0] == 1 && pool->dilation[1] == 1 &&
                           g.OH % 2 == 0 && g.OW % 2 == 0;
     const bool tc = ctx->math_mode != MTL_MATH_FP32 && mtl_conv_fwd_tc_supported(g, X, Wt, pooled);
+    if (pool_2x2 && !tc && ctx->math_mode == MTL_MATH_TF32 && mtl_conv_first_pool_tc_supported(g, X, pooled, idx))
+        return mtl_conv_first_pool_tc(ctx, pooled, idx, pooled_cl, X, Wt, bias, g, relu);
     if (pool_2x2 && !tc && mtl_conv_fwd_pool_simt_supported(g, pooled))
         return mtl_conv_fwd_pool_simt(ctx, pooled, idx, pooled_cl, X, Wt, bias, g, relu);
     if (pool_2x2 && tc && mtl_conv_fwd_pool_tc_supported(g, X, Wt, pooled)) {

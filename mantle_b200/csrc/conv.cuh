@@ -42,6 +42,10 @@ bool mtl_conv_wgrad_tc_supported(const ConvGeom& g, const float* ug, const float
 int32_t mtl_conv_fwd_tc(mtl_ctx* ctx, float* Y, const float* X, const float* Wt, const float* bias,
                         const ConvGeom& g, int x3, int relu, const float* X_cl);
 int32_t mtl_channels_last_copy(mtl_ctx* ctx, float* dst, const float* src, int N, int C, int HW);
+// First layer (C*R*S <= 32) with RELU and 2x2 pooling on the tensor cores, plain TF32 mode.
+bool mtl_conv_first_pool_tc_supported(const ConvGeom& g, const float* X, const float* pooled, const int32_t* idx);
+int32_t mtl_conv_first_pool_tc(mtl_ctx* ctx, float* pooled, int32_t* idx, float* pooled_cl, const float* X,
+                               const float* Wt, const float* bias, const ConvGeom& g, int relu);
 bool mtl_conv_fwd_pool_tc_supported(const ConvGeom& g, const float* X, const float* Wt, const float* pooled);
 int32_t mtl_conv_fwd_pool_tc(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X, const float* Wt,
                              const float* bias, const ConvGeom& g, int x3, int relu, const float* X_cl);

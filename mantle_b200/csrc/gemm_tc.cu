@@ -305,7 +305,7 @@ int32_t launch_gemm(mtl_ctx* ctx, const CUtensorMap* maps, const GemmParams& p) 
 }  // namespace
 
 int32_t mtl_encode_tmap(mtl_ctx* ctx, CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                        const uint64_t* strides_bytes, const uint32_t* box, bool atom32) {
+                        const uint64_t* strides_bytes, const uint32_t* box, int mode) {
     typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -332,7 +332,8 @@ int32_t mtl_encode_tmap(mtl_ctx* ctx, CUtensorMap* out, const void* base, int ra
     CUresult r = ((encode_fn)ctx->encode_tiled)(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank,
                                                const_cast<void*>(base), gdim, gstr, gbox, estr,
                                                CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                               atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                                               mode == 2 ? CU_TENSOR_MAP_SWIZZLE_NONE
+                                               : mode == 1 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return mtl_set_error(ctx, MTL_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d)", (int)r, rank);

@@ -205,6 +205,16 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         : "r"(taddr)
         : "memory");
 }
+// 32 lanes x 16 consecutive fp32 columns.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 }  // namespace sm100
@@ -213,8 +223,9 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 struct mtl_ctx;
 
-// Encodes a tiled fp32 tensor map with 128-byte swizzle (16-byte chunks, or 32-byte chunks when
-// atom32 is set) and zero fill outside the tensor.
+// Encodes a tiled fp32 tensor map with zero fill outside the tensor.  mode 0: 128-byte swizzle with
+// 16-byte chunks; 1: 128-byte swizzle with 32-byte chunks; 2: no swizzle (box rows wider than 128
+// bytes are allowed).
 // dims/box: innermost first; strides_bytes: rank-1 entries for dims 1..rank-1.
 int32_t mtl_encode_tmap(mtl_ctx* ctx, CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                        const uint64_t* strides_bytes, const uint32_t* box, bool atom32 = false);
+                        const uint64_t* strides_bytes, const uint32_t* box, int mode = 0);
