@@ -142,6 +142,9 @@ int32_t mtl_conv2d_bwd_pooled(mtl_ctx* ctx, float* dX, float* dW, float* db, con
                                          acc_db, x3, X_cl);
     // first layer on CUDA cores: the dense gradient is rebuilt in shared memory
     const bool wgrad_tc = tc_mode && dW && mtl_conv_wgrad_tc_supported(g, pooled_ug, X, dW);
+    if (pool_2x2 && !dX && !wgrad_tc && ctx->math_mode == MTL_MATH_TF32 && (dW || db) &&
+        mtl_conv_first_wgrad_tc_supported(g, X, pooled_ug, idx, relu ? pooled : pooled_ug))
+        return mtl_conv_first_wgrad_tc(ctx, dW, db, pooled_ug, idx, pooled, X, g, relu, acc_dw, acc_db);
     if (pool_2x2 && !dX && !wgrad_tc && mtl_conv_wgrad_rows_pooled_supported(g))
         return mtl_conv_wgrad_bias_rows_pooled(ctx, dW, db, pooled_ug, idx, pooled, X, g, relu, acc_dw, acc_db);
     // no kernel consumes the pooled form for this geometry: the dense gradient passes through scratch

@@ -46,6 +46,10 @@ int32_t mtl_channels_last_copy(mtl_ctx* ctx, float* dst, const float* src, int N
 bool mtl_conv_first_pool_tc_supported(const ConvGeom& g, const float* X, const float* pooled, const int32_t* idx);
 int32_t mtl_conv_first_pool_tc(mtl_ctx* ctx, float* pooled, int32_t* idx, float* pooled_cl, const float* X,
                                const float* Wt, const float* bias, const ConvGeom& g, int relu);
+bool mtl_conv_first_wgrad_tc_supported(const ConvGeom& g, const float* X, const float* pg, const int32_t* pidx,
+                                       const float* pv);
+int32_t mtl_conv_first_wgrad_tc(mtl_ctx* ctx, float* dW, float* db, const float* pg, const int32_t* pidx,
+                                const float* pv, const float* X, const ConvGeom& g, int relu, int acc_dw, int acc_db);
 bool mtl_conv_fwd_pool_tc_supported(const ConvGeom& g, const float* X, const float* Wt, const float* pooled);
 int32_t mtl_conv_fwd_pool_tc(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X, const float* Wt,
                              const float* bias, const ConvGeom& g, int x3, int relu, const float* X_cl);

@@ -402,6 +402,344 @@ int32_t launch_first(mtl_ctx* ctx, float* pooled, int32_t* idx, float* pooled_cl
     return MTL_OK;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Kernel and bias gradient of the same layer from the POOLED upper gradient (CONV2D.backward of
+// RELU.backward of MAXPOOL2D.backward), plain TF32 mode.
+//
+// GEMM: D[(set, channel)][(set', tap)] += sum over pixels of dY[(set, channel)][pixel] * patch[(set', tap)][pixel]
+// with two pixel sets so that all 128 accumulator rows work (the blocks with set == set' are the
+// result, the other two are discarded).  A tile is four output rows of one image: set 0 the upper
+// row pair, set 1 the lower one, 2*OW pixels on K.  Builder warps rebuild the dense gradient of a
+// row pair in the K-major operand tile (every pooled element writes its whole 2x2 window: the
+// gradient where the argmax was, zeros elsewhere, nothing if RELU was inactive) and lay the input
+// rows out as shifted copies, one per tap; tap C*R*S is a row of ones, so its column is the bias
+// gradient.  The accumulator stays in tensor memory for the whole kernel; each CTA writes one partial
+// result, summed by a second launch.
+constexpr int kWBuildWarps = 16, kWBuildThreads = kWBuildWarps * 32;
+constexpr int kThreadsW = (kWBuildWarps + 2) * 32;
+constexpr int kWABytes = 2 * 128 * 128;   // (set, channel) rows, two k-blocks of 32 pixels
+constexpr int kWBBytes = 2 * 64 * 128;    // (set', tap) rows
+constexpr int kWStageBytes = kWABytes + kWBBytes;
+
+struct FirstWgradParams {
+    int N, K, OH, ph, pw;
+    int xw, xoff, xstart, box_floats;
+    int tiles;                 // N * (OH / 4)
+    int relu;
+    const float* pg;           // pooled upper gradient [N, K, OH/2, OW/2]
+    const int32_t* idx;        // argmax indices of the pooling
+    const float* pv;           // pooled output (RELU mask), may be null when relu == 0
+    float* part_w;             // [gridDim.x][K][C*R*S]
+    float* part_b;             // [gridDim.x][K]
+    int* status;
+};
+
+template <int R, int S, int C, int OW>
+struct FirstWgradCfg {
+    static constexpr int CRS = C * R * S;
+    static_assert(CRS <= 31, "one spare tap row carries the bias gradient");
+    static_assert(OW % 4 == 0, "four-pixel chunks must not straddle output rows");
+    static constexpr int IRB = 4 + R - 1;
+    static constexpr int XW_MAX = (OW + S - 1 + 3 + 3) / 4 * 4;
+    static constexpr int IN_STAGE_BYTES = (C * IRB * XW_MAX * 4 + 127) / 128 * 128;
+    static constexpr int PX = 2 * OW;            // pixels of a row pair = K extent of a set
+    static constexpr int KSTEPS = PX / 8;        // MMAs per tile
+    static constexpr int POW = OW / 2;
+    static constexpr int QPC = 2 * POW / 4;      // float4 loads per channel and tile (both row pairs)
+    static constexpr int ITEMS = 64 * QPC;
+    static constexpr int IPT = (ITEMS + kWBuildThreads - 1) / kWBuildThreads;
+    static constexpr int SMEM_BYTES = 1024 + 2 * kWStageBytes + 2 * IN_STAGE_BYTES + 64 * 33 * 4 + 256;
+    static_assert(SMEM_BYTES <= 232448, "shared memory");
+};
+
+template <int R, int S, int C, int OW>
+__global__ void __launch_bounds__(kThreadsW, 1)
+k_conv_first_wgrad_tc(const __grid_constant__ CUtensorMap mapX, FirstWgradParams p) {
+    using Cfg = FirstWgradCfg<R, S, C, OW>;
+    constexpr int CRS = Cfg::CRS, IRB = Cfg::IRB, PX = Cfg::PX, POW = Cfg::POW, QPC = Cfg::QPC, IPT = Cfg::IPT;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* ab = smem;                                                    // 2 stages of {A, B}
+    float* in_tiles = reinterpret_cast<float*>(smem + 2 * kWStageBytes);
+    float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(in_tiles) + 2 * Cfg::IN_STAGE_BYTES);  // [64][33]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(xch + 64 * 33);
+    uint64_t* in_full = bars;        // [2]
+    uint64_t* in_empty = bars + 2;   // [2]
+    uint64_t* ab_full = bars + 4;    // [2]
+    uint64_t* ab_empty = bars + 6;   // [2]
+    uint64_t* acc_done = bars + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kg = blockIdx.y;
+    const int POH = p.OH >> 1, TPI = POH >> 1;   // tiles per image
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&in_full[s], 1); mbar_init(&in_empty[s], kWBuildThreads);
+            mbar_init(&ab_full[s], kWBuildThreads); mbar_init(&ab_empty[s], 1);
+        }
+        mbar_init(acc_done, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&mapX);
+    }
+    if (warp == kWBuildWarps + 1) {
+        tmem_alloc(tmem_slot, 64);
+        tmem_relinquish();
+    }
+    // operand tiles start as zeros; the tap row C*R*S of each set is ones (bias gradient)
+    for (int i = threadIdx.x; i < 2 * kWStageBytes / 4; i += kThreadsW) reinterpret_cast<float*>(ab)[i] = 0.0f;
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * 2 * 2 * 32; i += kThreadsW) {
+        const int st = i >> 7, kb = (i >> 6) & 1, set = (i >> 5) & 1, k = i & 31;
+        *reinterpret_cast<float*>(ab + st * kWStageBytes + kWABytes + kb * (64 * 128) + swz_off(set * 32 + CRS, k)) = 1.0f;
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == kWBuildWarps) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            bool ok = true;
+            int local = 0;
+            for (int t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++local) {
+                const int st = local & 1;
+                const uint32_t ph = (uint32_t)(local >> 1) & 1u;
+                if (!mbar_wait(&in_empty[st], ph ^ 1u, abort_flag, kWaitNs)) { ok = false; break; }
+                mbar_arrive_expect_tx(&in_full[st], (uint32_t)(p.box_floats * 4));
+                const int n = t / TPI, j = t - n * TPI;
+                tma_load_4d(reinterpret_cast<uint8_t*>(in_tiles) + st * Cfg::IN_STAGE_BYTES, &mapX, &in_full[st], p.xstart,
+                            4 * j - p.ph, 0, n);
+            }
+            if (!ok) atomicExch(p.status, MTL_ERR_TIMEOUT);
+        }
+    } else if (warp == kWBuildWarps + 1) {
+        // ---------------------------------------------------------------- MMA issue
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_tf32(64, false, false);
+            bool ok = true;
+            int local = 0;
+            for (int t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++local) {
+                const int s = local & 1;
+                const uint32_t ph = (uint32_t)(local >> 1) & 1u;
+                if (!mbar_wait(&ab_full[s], ph, abort_flag, kWaitNs)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t sa = smem_u32(ab + s * kWStageBytes);
+                const uint32_t sb = sa + kWABytes;
+#pragma unroll
+                for (int ks = 0; ks < Cfg::KSTEPS; ++ks) {
+                    const int kb = ks >> 2, kk = ks & 3;
+                    mma_tf32(tmem_base, desc_k_major(sa + kb * 16384, kk), desc_k_major(sb + kb * (64 * 128), kk), idesc,
+                             (local | ks) ? 1u : 0u);
+                }
+                mma_commit(&ab_empty[s]);
+            }
+            if (ok) mma_commit(acc_done);
+            else atomicExch(p.status, MTL_ERR_TIMEOUT);
+        }
+    } else {
+        // ---------------------------------------------------------------- operand builders
+        const int tb = threadIdx.x;
+        // Everything that does not depend on the tile is worked out once: where this thread's pooled
+        // elements land in the gradient tile (upper and lower row of their windows), and which
+        // four-pixel pieces of which tap rows it copies.  Odd lanes take the elements of a quad in the
+        // order 1, 0, 3, 2: with every lane on the same element parity the 8-byte stores of a warp
+        // would use only half of the banks.
+        const int swap = lane & 1;
+        uint32_t a_up[IPT][4], a_lo[IPT][4];
+        int a_i0[IPT][4];
+        int a_src[IPT];     // element offset of the quad inside its tile's data, -1: nothing to do
+#pragma unroll
+        for (int i = 0; i < IPT; ++i) {
+            const int it = tb + i * kWBuildThreads;
+            const int cl = it / QPC, q = it - cl * QPC;
+            a_src[i] = (it < Cfg::ITEMS && kg * 64 + cl < p.K) ? ((kg * 64 + cl) * POH * POW + 4 * q) : -1;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int e = 4 * q + (u ^ swap);
+                const int set = e / POW, pw = e - set * POW;
+                const int row = set * 64 + (cl & 63);
+                const int j0 = 2 * pw, j1 = OW + 2 * pw;
+                a_up[i][u] = (uint32_t)((j0 >> 5) * 16384) + swz_off(row, j0 & 31);
+                a_lo[i][u] = (uint32_t)((j1 >> 5) * 16384) + swz_off(row, j1 & 31);
+                a_i0[i][u] = 2 * set * OW + 2 * pw;
+            }
+        }
+        constexpr int B_ITEMS = 2 * CRS * (PX / 4), BPT = (B_ITEMS + kWBuildThreads - 1) / kWBuildThreads;
+        int b_src[BPT];
+        uint32_t b_dst[BPT];
+#pragma unroll
+        for (int i = 0; i < BPT; ++i) {
+            const int it = tb + i * kWBuildThreads;
+            const int c4 = it % (PX / 4), rest = it / (PX / 4);
+            const int tap = rest % CRS, set = (rest / CRS) & 1;
+            const int cc = tap / (R * S), r = (tap / S) % R, s2 = tap % S;
+            const int px = 4 * c4, h = px / OW, ow = px - h * OW;
+            b_src[i] = it < B_ITEMS ? (cc * IRB + 2 * set + h + r) * p.xw + ow + s2 + p.xoff : -1;
+            b_dst[i] = (uint32_t)((px >> 5) * (64 * 128)) + swz_off(set * 32 + tap, px & 31);
+        }
+        // Pooled gradient, argmax index and pooled value of this thread's elements, for two tiles: the
+        // loads of a register set are issued as soon as the set's tile has been consumed, i.e. two
+        // tiles ahead of their use (one tile of MMAs is shorter than a DRAM round trip).
+        float4 gA[IPT], vA[IPT], gB[IPT], vB[IPT];
+        int4 iA[IPT], iB[IPT];
+        auto fetch = [&](int t, float4 (&g)[IPT], int4 (&ix)[IPT], float4 (&pvr)[IPT]) {
+            if (t >= p.tiles) return;
+            const int n = t / TPI, j = t - n * TPI;
+            const int tile_off = n * p.K * POH * POW + 2 * j * POW;   // below 2^31: checked by the host
+#pragma unroll
+            for (int i = 0; i < IPT; ++i) {
+                if (a_src[i] >= 0) {
+                    const int o = tile_off + a_src[i];
+                    g[i] = __ldg(reinterpret_cast<const float4*>(p.pg + o));
+                    ix[i] = __ldg(reinterpret_cast<const int4*>(p.idx + o));
+                    if (p.relu) pvr[i] = __ldg(reinterpret_cast<const float4*>(p.pv + o));
+                }
+            }
+        };
+        bool ok = true;
+        auto build = [&](int t, int local, float4 (&g)[IPT], int4 (&ix)[IPT], float4 (&pvr)[IPT]) {
+            const int st = local & 1;
+            const uint32_t ph = (uint32_t)(local >> 1) & 1u;
+            const int j = t % TPI;
+            if (!mbar_wait(&ab_empty[st], ph ^ 1u, abort_flag, kWaitNs)) { ok = false; return; }
+            uint8_t* a_st = ab + st * kWStageBytes;
+            uint8_t* b_st = a_st + kWABytes;
+            // dense gradient rows from the pooled elements in registers
+            const int tile_i0 = 4 * j * OW;
+#pragma unroll
+            for (int i = 0; i < IPT; ++i) {
+                if (a_src[i] >= 0) {
+                    const float gv[4] = {swap ? g[i].y : g[i].x, swap ? g[i].x : g[i].y, swap ? g[i].w : g[i].z, swap ? g[i].z : g[i].w};
+                    const float pvv[4] = {swap ? pvr[i].y : pvr[i].x, swap ? pvr[i].x : pvr[i].y, swap ? pvr[i].w : pvr[i].z,
+                                          swap ? pvr[i].z : pvr[i].w};
+                    const int iv[4] = {swap ? ix[i].y : ix[i].x, swap ? ix[i].x : ix[i].y, swap ? ix[i].w : ix[i].z, swap ? ix[i].z : ix[i].w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float val = (!p.relu || pvv[u] > 0.0f) ? gv[u] : 0.0f;   // RELU.backward: x > 0 ? ug : 0
+                        const int c = iv[u] - tile_i0 - a_i0[i][u];                    // 0, 1, OW, OW + 1
+                        const bool lower = c >= OW;
+                        const bool right = (c & 1) != 0;                               // OW is even
+                        const float2 hit = right ? make_float2(0.0f, val) : make_float2(val, 0.0f);
+                        const float2 zero = make_float2(0.0f, 0.0f);
+                        *reinterpret_cast<float2*>(a_st + a_up[i][u]) = lower ? zero : hit;
+                        *reinterpret_cast<float2*>(a_st + a_lo[i][u]) = lower ? hit : zero;
+                    }
+                }
+            }
+            fetch(t + 2 * (int)gridDim.x, g, ix, pvr);
+            // input rows as shifted copies: row (set', tap), four pixels per store
+            if (!mbar_wait(&in_full[st], ph, abort_flag, kWaitNs)) { ok = false; return; }
+            const float* xin = in_tiles + st * (Cfg::IN_STAGE_BYTES / 4);
+#pragma unroll
+            for (int i = 0; i < BPT; ++i) {
+                if (b_src[i] >= 0) {
+                    const float* src = xin + b_src[i];
+                    *reinterpret_cast<float4*>(b_st + b_dst[i]) = make_float4(src[0], src[1], src[2], src[3]);
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(&ab_full[st]);
+            mbar_arrive(&in_empty[st]);
+        };
+#pragma unroll
+        for (int i = 0; i < IPT; ++i) {
+            gA[i] = gB[i] = vA[i] = vB[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            iA[i] = iB[i] = make_int4(0, 0, 0, 0);
+        }
+        fetch(blockIdx.x, gA, iA, vA);
+        fetch(blockIdx.x + gridDim.x, gB, iB, vB);
+        for (int t = blockIdx.x, local = 0; t < p.tiles && ok; t += 2 * gridDim.x, local += 2) {
+            build(t, local, gA, iA, vA);
+            if (!ok || t + (int)gridDim.x >= p.tiles) break;
+            build(t + gridDim.x, local + 1, gB, iB, vB);
+        }
+        if (!ok && lane == 0) atomicExch(p.status, MTL_ERR_TIMEOUT);
+
+        // ------------------------------------------------------------ the CTA's partial result
+        if (warp < 4) {
+            const int quad = warp, set = quad >> 1, cl = (quad & 1) * 32 + lane;
+            uint32_t v[32];
+            bool done = ok && mbar_wait(acc_done, 0u, abort_flag, kWaitNs);
+            if (!done && lane == 0) atomicExch(p.status, MTL_ERR_TIMEOUT);
+            tc_fence_after_sync();
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(set * 32), v);
+            tmem_ld_wait();
+            if (set == 1) {
+#pragma unroll
+                for (int k = 0; k < 32; ++k) xch[cl * 33 + k] = __uint_as_float(v[k]);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int ch = kg * 64 + cl;
+            if (set == 0 && ch < p.K && done) {
+#pragma unroll
+                for (int k = 0; k < CRS; ++k)
+                    p.part_w[((int64_t)blockIdx.x * p.K + ch) * CRS + k] = __uint_as_float(v[k]) + xch[cl * 33 + k];
+                if (p.part_b) p.part_b[(int64_t)blockIdx.x * p.K + ch] = __uint_as_float(v[CRS]) + xch[cl * 33 + CRS];
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kWBuildWarps + 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 64);
+    }
+}
+
+template <int R, int S, int C, int OW>
+int32_t launch_first_wgrad(mtl_ctx* ctx, float* dW, float* db, const float* pg, const int32_t* pidx, const float* pv,
+                           const float* X, const ConvGeom& g, int relu, int acc_dw, int acc_db) {
+    using Cfg = FirstWgradCfg<R, S, C, OW>;
+    FirstWgradParams p;
+    p.N = g.N; p.K = g.K; p.OH = g.OH; p.ph = g.ph; p.pw = g.pw;
+    const int xs = (g.pw + 3) / 4 * 4;
+    p.xstart = -xs;
+    p.xoff = xs - g.pw;
+    p.xw = (OW + S - 1 + p.xoff + 3) / 4 * 4;
+    p.box_floats = C * Cfg::IRB * p.xw;
+    p.tiles = g.N * (g.OH / 4);
+    p.relu = relu;
+    p.pg = pg; p.idx = pidx; p.pv = pv; p.status = ctx->dev_status;
+    if (p.xw > Cfg::XW_MAX)
+        return mtl_set_error(ctx, MTL_ERR_UNSUPPORTED, "first-layer tensor-core gradient: input box too wide");
+    const int kgroups = (g.K + 63) / 64;
+    int gx = ctx->sm_count / kgroups;
+    if (gx < 1) gx = 1;
+    if (gx > p.tiles) gx = p.tiles;
+    void* ws;
+    int32_t rc = mtl_workspace(ctx, ((size_t)gx * g.K * Cfg::CRS + (size_t)gx * g.K) * 4, &ws);
+    if (rc) return rc;
+    p.part_w = (float*)ws;
+    p.part_b = db ? p.part_w + (size_t)gx * g.K * Cfg::CRS : nullptr;
+    CUtensorMap tm;
+    uint64_t dims[4] = {(uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.C, (uint64_t)g.N};
+    uint64_t strides[3] = {(uint64_t)g.W * 4, (uint64_t)g.H * g.W * 4, (uint64_t)g.C * g.H * g.W * 4};
+    uint32_t box[4] = {(uint32_t)p.xw, (uint32_t)Cfg::IRB, (uint32_t)C, 1u};
+    rc = mtl_encode_tmap(ctx, &tm, X, 4, dims, strides, box, 2);
+    if (rc) return rc;
+    auto kern = k_conv_first_wgrad_tc<R, S, C, OW>;
+    MTL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    {
+        mtl_prof_scope prof(ctx, MTL_PROF_CONV_FIRST);
+        kern<<<dim3(gx, kgroups), kThreadsW, Cfg::SMEM_BYTES, ctx->stream>>>(tm, p);
+    }
+    MTL_LAUNCHED(ctx);
+    if (dW) {
+        rc = mtl_sum_partials(ctx, dW, p.part_w, (int64_t)g.K * Cfg::CRS, gx, acc_dw);
+        if (rc) return rc;
+    }
+    if (db) return mtl_sum_partials(ctx, db, p.part_b, g.K, gx, acc_db);
+    return MTL_OK;
+}
+
 }  // namespace
 
 #define MTL_FIRST_TC_CASES(X_) X_(5, 5, 1, 28) X_(3, 3, 1, 28) X_(5, 5, 1, 32) X_(3, 3, 3, 32)
@@ -429,4 +767,23 @@ int32_t mtl_conv_first_pool_tc(mtl_ctx* ctx, float* pooled, int32_t* idx, float*
     MTL_FIRST_TC_CASES(X_)
 #undef X_
     return mtl_set_error(ctx, MTL_ERR_UNSUPPORTED, "first-layer tensor-core convolution: geometry not instantiated");
+}
+
+bool mtl_conv_first_wgrad_tc_supported(const ConvGeom& g, const float* X, const float* pg, const int32_t* pidx,
+                                       const float* pv) {
+    if (!mtl_conv_first_pool_tc_supported(g, X, pg, pidx)) return false;
+    if (g.OH % 4) return false;   // a tile is two whole row pairs of one image
+    if (((reinterpret_cast<uintptr_t>(pg) | reinterpret_cast<uintptr_t>(pidx) | reinterpret_cast<uintptr_t>(pv)) & 15u)) return false;
+    if (((g.OH / 2) * (g.OW / 2)) % 4) return false;   // 16-byte loads from every channel plane
+    return true;
+}
+
+int32_t mtl_conv_first_wgrad_tc(mtl_ctx* ctx, float* dW, float* db, const float* pg, const int32_t* pidx,
+                                const float* pv, const float* X, const ConvGeom& g, int relu, int acc_dw, int acc_db) {
+#define X_(R_, S_, C_, OW_)                                               \
+    if (g.R == R_ && g.S == S_ && g.C == C_ && g.OW == OW_)               \
+        return launch_first_wgrad<R_, S_, C_, OW_>(ctx, dW, db, pg, pidx, pv, X, g, relu, acc_dw, acc_db);
+    MTL_FIRST_TC_CASES(X_)
+#undef X_
+    return mtl_set_error(ctx, MTL_ERR_UNSUPPORTED, "first-layer tensor-core gradient: geometry not instantiated");
 }

@@ -439,6 +439,50 @@ def test_conv_relu_pool_equals_three_calls(ctx, case):
         assert (got_v.numpy() == 0).any()
 
 
+@pytest.mark.parametrize("case", [(70, 1, 28, 28, 64, 5, 5, 2), (10, 1, 28, 28, 70, 3, 3, 1), (9, 3, 32, 32, 40, 3, 3, 1),
+                                  (8, 1, 32, 32, 20, 5, 5, 0), (37, 1, 28, 28, 64, 5, 5, 2)])
+def test_first_layer_gradients_on_tensor_cores(ctx, case):
+    """Plain TF32 mode: mtl_conv2d_bwd_pooled without dX on a first layer (C*R*S <= 31) rebuilds the dense
+    gradient as a tensor-core operand and takes the bias gradient from a row of ones.  Compared with the
+    fp32 CUDA-core result of the three reference-shaped calls, to TF32 accuracy."""
+    import ctypes as Cc
+    N, C, H, W, K, R, S, p = case
+    rng = np.random.default_rng(sum(case) + 11)
+    x = ctx.array(rng.normal(0, 1, (N, C, H, W)).astype(np.float32))
+    w = ctx.array((rng.normal(0, 1, (K, C, R, S)) / np.sqrt(C * R * S)).astype(np.float32))
+    b = ctx.array(rng.normal(0, 0.5, K).astype(np.float32))
+    kw = dict(padding=(p, p), stride=(1, 1), dilation=(1, 1))
+    pkw = dict(kernel_size=(2, 2), stride=(2, 2), padding=(0, 0), dilation=(1, 1))
+    oh, ow = mb.conv2d_out_shape((N, C, H, W), (K, C, R, S), **kw)
+    y, z = ctx.empty((N, K, oh, ow)), ctx.empty((N, K, oh, ow))
+    pooled, idx = ctx.empty((N, K, oh // 2, ow // 2)), ctx.empty((N, K, oh // 2, ow // 2), np.int32)
+    ctx.forward_op(OP.CONV2D, y, x, w, b, **kw)
+    ctx.forward_op(OP.RELU, z, y)
+    ctx.forward_op(OP.MAXPOOL2D, pooled, z, indices=idx, **pkw)
+    pug = ctx.array(rng.normal(0, 1, (N, K, oh // 2, ow // 2)).astype(np.float32))
+    g_z, g_y = ctx.empty((N, K, oh, ow)), ctx.empty((N, K, oh, ow))
+    ctx.backward_op(0, OP.MAXPOOL2D, pug, z, grad=g_z, accumulate=False, indices=idx, **pkw)
+    ctx.backward_op(0, OP.RELU, g_z, y, grad=g_y, accumulate=False)
+    d = mb.conv_desc(N, C, H, W, K, R, S, (p, p), (1, 1), (1, 1))
+    pd = mb.conv_desc(N, K, oh, ow, 1, 2, 2, (0, 0), (2, 2), (1, 1))
+    for acc in (0, 1):
+        init = [rng.normal(0, 1, s).astype(np.float32) for s in ((K, C, R, S), (K,))]
+        want = [ctx.array(a) for a in init]
+        for tid in (1, 2):
+            ctx.backward_op(tid, OP.CONV2D, g_y, x, w, b, grad=want[tid - 1], accumulate=bool(acc), **kw)
+        got = [ctx.array(a) for a in init]
+        ctx.set_math_mode(mb.MATH_TF32)
+        try:
+            for act, pv in ((int(OP.RELU), pooled.ptr),):
+                ctx._check(ctx.lib.mtl_conv2d_bwd_pooled(ctx.handle, None, got[0].ptr, got[1].ptr, pug.ptr, idx.ptr, pv,
+                                                         x.ptr, None, w.ptr, Cc.byref(d), act, Cc.byref(pd), 0, acc, acc))
+        finally:
+            ctx.set_math_mode(mb.MATH_TF32X3)
+        assert rel_err(got[0].numpy(), want[0].numpy().astype(np.float64)) < 4e-3, "dW acc %d" % acc
+        assert rel_err(got[1].numpy(), want[1].numpy().astype(np.float64)) < 4e-3, "db acc %d" % acc
+    assert ctx.device_status() == 0
+
+
 @pytest.mark.parametrize("case", [(70, 1, 28, 28, 64, 5, 5, 2), (65, 3, 28, 28, 40, 3, 3, 1), (6, 2, 12, 12, 5, 3, 3, 1),
                                   (24, 64, 14, 14, 128, 5, 5, 2), (3, 64, 56, 56, 64, 3, 3, 1)])
 def test_conv_backward_from_pooled_gradient(ctx, case):
