@@ -340,6 +340,22 @@ MTL_API int32_t mtl_reduce_bwd(mtl_ctx* ctx, int32_t op, float* grad, const floa
 MTL_API int32_t mtl_reduce_all_static(mtl_ctx* ctx, int32_t op, float* out, const float* in,
                                       int64_t n);
 
+/* ---------------------------------------------------------------- fused loss ------------ */
+/* nn.CrossEntropyLoss (nn/loss.mojo:45-61) on logits [B, C] and targets [B, C] as one launch each way.
+ *   mtl_cross_entropy_fwd   loss[0] = scale * SUM(y_true * LogSoftmax(logits, axis 1)); equals the nine
+ *                           operator calls MAX, SUB, EXP, SUM, LOG, SUB, MUL, SUM, MUL(scale) of the
+ *                           reference's graph (same fp32 operations per row; only the final sum over
+ *                           rows runs in another order).  The reference's scale is -1 / B.
+ *   mtl_cross_entropy_bwd   dlogits (+)= gradient of that loss for an upper gradient of 1: the nine
+ *                           backward calls in reverse, MAX.backward's even split among ties included.
+ * The intermediate tensors of the nine nodes are not produced.  At most MTL_CROSS_ENTROPY_MAX_ELEMENTS
+ * logits per call (the forward is a single block); larger losses go through the operator calls. */
+#define MTL_CROSS_ENTROPY_MAX_ELEMENTS (1ll << 22)
+MTL_API int32_t mtl_cross_entropy_fwd(mtl_ctx* ctx, float* loss, const float* logits, const float* y_true,
+                                      int64_t B, int64_t C, float scale);
+MTL_API int32_t mtl_cross_entropy_bwd(mtl_ctx* ctx, float* dlogits, const float* logits, const float* y_true,
+                                      int64_t B, int64_t C, float scale, int32_t accumulate);
+
 /* ---------------------------------------------------------------- optimizer ------------- */
 
 /* Adam.step (mantle/nn/optim.mojo:94-140) over one flat fp32 span of n parameters:

@@ -429,8 +429,7 @@ struct FirstWgradParams {
     const float* pg;           // pooled upper gradient [N, K, OH/2, OW/2]
     const int32_t* idx;        // argmax indices of the pooling
     const float* pv;           // pooled output (RELU mask), may be null when relu == 0
-    float* part_w;             // [gridDim.x][K][C*R*S]
-    float* part_b;             // [gridDim.x][K]
+    float* part;               // [gridDim.x][K][32]: taps 0 .. C*R*S-1, then the bias column
     int* status;
 };
 
@@ -677,10 +676,13 @@ k_conv_first_wgrad_tc(const __grid_constant__ CUtensorMap mapX, FirstWgradParams
             asm volatile("bar.sync 1, 128;" ::: "memory");
             const int ch = kg * 64 + cl;
             if (set == 0 && ch < p.K && done) {
+                float4* dst = reinterpret_cast<float4*>(p.part + ((int64_t)blockIdx.x * p.K + ch) * 32);
 #pragma unroll
-                for (int k = 0; k < CRS; ++k)
-                    p.part_w[((int64_t)blockIdx.x * p.K + ch) * CRS + k] = __uint_as_float(v[k]) + xch[cl * 33 + k];
-                if (p.part_b) p.part_b[(int64_t)blockIdx.x * p.K + ch] = __uint_as_float(v[CRS]) + xch[cl * 33 + CRS];
+                for (int k = 0; k < 8; ++k)
+                    dst[k] = make_float4(__uint_as_float(v[4 * k]) + xch[cl * 33 + 4 * k],
+                                         __uint_as_float(v[4 * k + 1]) + xch[cl * 33 + 4 * k + 1],
+                                         __uint_as_float(v[4 * k + 2]) + xch[cl * 33 + 4 * k + 2],
+                                         __uint_as_float(v[4 * k + 3]) + xch[cl * 33 + 4 * k + 3]);
             }
         }
     }
@@ -691,6 +693,30 @@ k_conv_first_wgrad_tc(const __grid_constant__ CUtensorMap mapX, FirstWgradParams
         __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 64);
+    }
+}
+
+// Sums the CTAs' partial results in a fixed order: one block per output channel, 32 columns x 8
+// slices of the partials, the slices combined through shared memory.  Column C*R*S is the bias gradient.
+__global__ void __launch_bounds__(256) k_first_wgrad_reduce(float* __restrict__ dW, float* __restrict__ db,
+                                                            const float* __restrict__ part, int K, int CRS, int nparts,
+                                                            int acc_dw, int acc_db) {
+    __shared__ float sm[8][33];
+    const int ch = blockIdx.x, col = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    float s = 0.0f;
+    for (int q = slice; q < nparts; q += 8) s += part[((int64_t)q * K + ch) * 32 + col];
+    sm[slice][col] = s;
+    __syncthreads();
+    if (slice == 0) {
+        float t = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t += sm[j][col];
+        if (col < CRS && dW) {
+            float* o = dW + (int64_t)ch * CRS + col;
+            *o = acc_dw ? *o + t : t;
+        } else if (col == CRS && db) {
+            db[ch] = acc_db ? db[ch] + t : t;
+        }
     }
 }
 
@@ -715,10 +741,9 @@ int32_t launch_first_wgrad(mtl_ctx* ctx, float* dW, float* db, const float* pg, 
     if (gx < 1) gx = 1;
     if (gx > p.tiles) gx = p.tiles;
     void* ws;
-    int32_t rc = mtl_workspace(ctx, ((size_t)gx * g.K * Cfg::CRS + (size_t)gx * g.K) * 4, &ws);
+    int32_t rc = mtl_workspace(ctx, (size_t)gx * g.K * 32 * 4, &ws);
     if (rc) return rc;
-    p.part_w = (float*)ws;
-    p.part_b = db ? p.part_w + (size_t)gx * g.K * Cfg::CRS : nullptr;
+    p.part = (float*)ws;
     CUtensorMap tm;
     uint64_t dims[4] = {(uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.C, (uint64_t)g.N};
     uint64_t strides[3] = {(uint64_t)g.W * 4, (uint64_t)g.H * g.W * 4, (uint64_t)g.C * g.H * g.W * 4};
@@ -732,11 +757,8 @@ int32_t launch_first_wgrad(mtl_ctx* ctx, float* dW, float* db, const float* pg, 
         kern<<<dim3(gx, kgroups), kThreadsW, Cfg::SMEM_BYTES, ctx->stream>>>(tm, p);
     }
     MTL_LAUNCHED(ctx);
-    if (dW) {
-        rc = mtl_sum_partials(ctx, dW, p.part_w, (int64_t)g.K * Cfg::CRS, gx, acc_dw);
-        if (rc) return rc;
-    }
-    if (db) return mtl_sum_partials(ctx, db, p.part_b, g.K, gx, acc_db);
+    k_first_wgrad_reduce<<<g.K, 256, 0, ctx->stream>>>(dW, db, p.part, g.K, Cfg::CRS, gx, acc_dw, acc_db);
+    MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
 

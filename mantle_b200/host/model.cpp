@@ -354,7 +354,13 @@ void Model::inference(const std::vector<const float*>& in, const std::vector<flo
 
 void Model::execute(int num_nodes) {
     for (int i = 0; i < num_nodes; ++i) {
-        if (fusion_ && fwd_skip_[i]) continue;  // computed by the CONV2D that feeds it
+        if (fusion_ && fwd_skip_[i]) continue;  // computed by the call at the head of its chain
+        if (fusion_ && i == ce_head_) {
+            const Symbol& x = g_.nodes[i].inputs[0];
+            check(mtl_cross_entropy_fwd(ctx_, T(*g_.loss_out), T(x), T(g_.nodes[i + 6].inputs[0]), x.shape[0], x.shape[1],
+                                        scalar_values_.at(ce_scale_sym_)), "CrossEntropyLoss forward");
+            continue;
+        }
         forward_op(g_.nodes[i]);
     }
 }
@@ -371,6 +377,7 @@ void Model::set_fusion(bool on) {
     fwd_skip_.assign(nn, 0);
     bwd_skip_.assign(nn, 0);
     relu_in_absent_.assign(nn, 0);
+    ce_head_ = -1;
     if (!on) return;
     std::map<int, int> uses, producer;
     for (int i = 0; i < nn; ++i) {
@@ -435,6 +442,43 @@ void Model::set_fusion(bool on) {
                 }
             }
         }
+    }
+    // nn.CrossEntropyLoss at the end of the graph: MAX, SUB, EXP, SUM, LOG, SUB (LogSoftmax along axis 1),
+    // MUL by the targets, SUM, MUL by a literal -- nine nodes on [B, C] tensors, run as one call each way
+    // when nothing else reads their intermediate results.
+    for (int i = 0; i + 8 < nn; ++i) {
+        auto N = [&](int k) -> const Node& { return g_.nodes[i + k]; };
+        auto O = [&](int k) -> const Symbol& { return g_.nodes[i + k].outputs[0]; };
+        static const int ops[9] = {MTL_OP_MAX, MTL_OP_SUB, MTL_OP_EXP, MTL_OP_SUM, MTL_OP_LOG, MTL_OP_SUB,
+                                   MTL_OP_MUL, MTL_OP_SUM, MTL_OP_MUL};
+        bool m = true;
+        for (int k = 0; k < 9 && m; ++k) m = N(k).op == ops[k] && N(k).outputs.size() == 1;
+        if (!m) continue;
+        const Symbol& x = N(0).inputs[0];
+        if (x.shape.rank != 2 || !x.trainable) continue;
+        if (!N(0).attrs.axis || *N(0).attrs.axis != 1 || !N(3).attrs.axis || *N(3).attrs.axis != 1 || N(7).attrs.axis) continue;
+        if (N(1).inputs.size() != 2 || N(5).inputs.size() != 2 || N(6).inputs.size() != 2 || N(8).inputs.size() != 2) continue;
+        const Symbol& y = N(6).inputs[0];
+        const Symbol& lit = N(8).inputs[1];
+        m = N(1).inputs[0].id == x.id && N(1).inputs[1].id == O(0).id && N(2).inputs[0].id == O(1).id &&
+            N(3).inputs[0].id == O(2).id && N(4).inputs[0].id == O(3).id && N(5).inputs[0].id == O(1).id &&
+            N(5).inputs[1].id == O(4).id && N(6).inputs[1].id == O(5).id && N(7).inputs[0].id == O(6).id &&
+            N(8).inputs[0].id == O(7).id && g_.loss_out && g_.loss_out->id == O(8).id;
+        if (!m) continue;
+        if (y.trainable || lit.trainable || !lit.shape.is_scalar() || !scalar_values_.count(lit.id)) continue;
+        if (y.shape.rank != 2 || y.shape[0] != x.shape[0] || y.shape[1] != x.shape[1]) continue;
+        if (x.shape.num_elements() > MTL_CROSS_ENTROPY_MAX_ELEMENTS) continue;
+        if (n_inference_nodes_ > i) continue;   // part of the chain belongs to the inference graph
+        static const int want_uses[8] = {1, 2, 1, 1, 1, 1, 1, 1};
+        for (int k = 0; k < 8 && m; ++k) {
+            m = uses[O(k).id] == want_uses[k] && !visible(O(k));
+            for (auto& o : g_.outputs) if (o.id == O(k).id) m = false;
+        }
+        if (!m) continue;
+        ce_head_ = i;
+        ce_scale_sym_ = lit.id;
+        for (int k = 1; k < 9; ++k) { fwd_skip_[i + k] = 1; bwd_skip_[i + k] = 1; }
+        break;
     }
 }
 
@@ -623,6 +667,11 @@ void Model::backward_enqueue() {
         if (fusion_ && (bwd_skip_[i] || bwd_pool_skip_[i])) {
             // a RELU whose backward its MAXPOOL2D performs, or a MAXPOOL2D whose backward the CONV2D at
             // the head of the chain performs from the pooled gradient
+        } else if (fusion_ && i == ce_head_) {
+            // the nine backward calls of the loss chain, gradient seed 1 included
+            const Symbol& x = n.inputs[0];
+            check(mtl_cross_entropy_bwd(ctx_, G(x), T(x), T(g_.nodes[i + 6].inputs[0]), x.shape[0], x.shape[1],
+                                        scalar_values_.at(ce_scale_sym_), acc_flag(x)), "CrossEntropyLoss backward");
         } else if (fusion_ && n.op == MTL_OP_CONV2D && bwd_pooled_of_[i] >= 0) {
             const Node& q = g_.nodes[bwd_pooled_of_[i]];  // the MAXPOOL2D at the end of the chain
             const Symbol& x = n.inputs[0];

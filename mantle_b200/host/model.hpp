@@ -116,6 +116,8 @@ class Model {
     bool overwrite_first_ = true;
     int n_inference_nodes_ = 0;
     bool fusion_ = false;
+    int ce_head_ = -1;                 // first of the nine nodes of a CrossEntropyLoss run as one call each way, or -1
+    int ce_scale_sym_ = -1;            // id of the [1]-shaped literal the loss is scaled by
     std::vector<int> fwd_relu_of_;     // per node: the RELU node a CONV2D also computes, or -1
     std::vector<int> fwd_pool_of_;     // per node: the MAXPOOL2D node a CONV2D+RELU also computes, or -1
     std::vector<char> fwd_skip_;       // RELU nodes computed by their producer

@@ -753,3 +753,57 @@ def test_channels_last_twins(ctx):
         for a, b_ in zip(*outs):
             assert np.array_equal(a, b_), "mode %d" % mode
     assert ctx.device_status() == 0
+
+
+@pytest.mark.parametrize("B,C", [(37, 10), (2048, 10), (5, 3), (300, 130)])
+def test_cross_entropy_equals_nine_operator_calls(ctx, B, C):
+    """mtl_cross_entropy_fwd / _bwd == the reference's CrossEntropyLoss graph run node by node (loss.mojo:45-61,
+    activations.mojo:94-108), forward value and logits gradient, ties in the row maximum included."""
+    rng = np.random.default_rng(B * 131 + C)
+    xh = rng.normal(0, 2, (B, C)).astype(np.float32)
+    xh[0, :] = 0.5                       # a row of ties: MAX.backward splits evenly
+    xh[1, 0] = xh[1, 1] = xh[1].max() + 1
+    yh = np.eye(C, dtype=np.float32)[rng.integers(0, C, B)]
+    yh[2] = rng.uniform(0, 1, C)         # soft targets
+    x, y = ctx.array(xh), ctx.array(yh)
+    scale = np.float32(-1.0 / B)
+    mx, sm, lg = ctx.empty((B, 1)), ctx.empty((B, 1)), ctx.empty((B, 1))
+    xm, ex, ls, t = ctx.empty((B, C)), ctx.empty((B, C)), ctx.empty((B, C)), ctx.empty((B, C))
+    ret, loss, lit = ctx.empty((1,)), ctx.empty((1,)), ctx.array(np.array([scale], np.float32))
+    ctx.forward_op(OP.MAX, mx, x, axis=1)
+    ctx.forward_op(OP.SUB, xm, x, mx)
+    ctx.forward_op(OP.EXP, ex, xm)
+    ctx.forward_op(OP.SUM, sm, ex, axis=1)
+    ctx.forward_op(OP.LOG, lg, sm)
+    ctx.forward_op(OP.SUB, ls, xm, lg)
+    ctx.forward_op(OP.MUL, t, y, ls)
+    ctx.forward_op(OP.SUM, ret, t)
+    ctx.forward_op(OP.MUL, loss, ret, lit)
+    # backward, node by node in reverse, every gradient buffer starting at zero
+    g = {k: ctx.zeros(s) for k, s in (("loss", (1,)), ("ret", (1,)), ("t", (B, C)), ("ls", (B, C)), ("xm", (B, C)),
+                                      ("lg", (B, 1)), ("sm", (B, 1)), ("ex", (B, C)), ("mx", (B, 1)), ("x", (B, C)))}
+    ctx._check(ctx.lib.mtl_fill_f32(ctx.handle, g["loss"].ptr, 1, 1.0))
+    ctx.backward_op(0, OP.MUL, g["loss"], ret, lit, grad=g["ret"])
+    ctx.backward_op(0, OP.SUM, g["ret"], t, grad=g["t"])
+    ctx.backward_op(1, OP.MUL, g["t"], y, ls, grad=g["ls"])
+    ctx.backward_op(0, OP.SUB, g["ls"], xm, lg, grad=g["xm"])
+    ctx.backward_op(1, OP.SUB, g["ls"], xm, lg, grad=g["lg"])
+    ctx.backward_op(0, OP.LOG, g["lg"], sm, grad=g["sm"])
+    ctx.backward_op(0, OP.SUM, g["sm"], ex, grad=g["ex"], axis=1)
+    ctx.backward_op(0, OP.EXP, g["ex"], xm, grad=g["xm"])
+    ctx.backward_op(0, OP.SUB, g["xm"], x, mx, grad=g["x"])
+    ctx.backward_op(1, OP.SUB, g["xm"], x, mx, grad=g["mx"])
+    ctx.backward_op(0, OP.MAX, g["mx"], x, grad=g["x"], axis=1)
+    got_loss = ctx.empty((1,))
+    ctx._check(ctx.lib.mtl_cross_entropy_fwd(ctx.handle, got_loss.ptr, x.ptr, y.ptr, B, C, float(scale)))
+    assert_close(got_loss.numpy(), loss.numpy(), 2e-6, 1e-7, "loss")
+    want_loss = -np.sum(yh.astype(np.float64) * (xh - xh.max(1, keepdims=True) -
+                                                 np.log(np.exp(xh.astype(np.float64) - xh.max(1, keepdims=True)).sum(1, keepdims=True)))) / B
+    assert abs(float(got_loss.numpy()[0]) - want_loss) <= 1e-5 * abs(want_loss)
+    for acc in (0, 1):
+        init = rng.normal(0, 1, (B, C)).astype(np.float32)
+        got = ctx.array(init)
+        ctx._check(ctx.lib.mtl_cross_entropy_bwd(ctx.handle, got.ptr, x.ptr, y.ptr, B, C, float(scale), acc))
+        want = g["x"].numpy() + (init if acc else 0)
+        assert_close(got.numpy(), want, 1e-5, 1e-7 * float(np.abs(g["x"].numpy()).max()) + 1e-9, "dlogits acc %d" % acc)
+    assert ctx.device_status() == 0
