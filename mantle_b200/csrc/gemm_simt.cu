@@ -140,20 +140,31 @@ __global__ void __launch_bounds__(256) k_gemm_thin_tile(float* __restrict__ part
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[r][j] = 0.0f;
     const float* a0 = A + (int64_t)m0 * K + k_begin;
-    for (int kk = lane; kk < kn; kk += 32) {
-        float a[4];
+    // four k steps at a time: their sixteen loads of A are in flight together (the kernel is bound by
+    // the latency of streaming A, not by arithmetic)
+    for (int kk0 = lane; kk0 < kn; kk0 += 128) {
+        float a[4][4];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) a[r] = (m0 + r < M) ? __ldg(a0 + (int64_t)r * K + kk) : 0.0f;
-        float b[16];
+        for (int u = 0; u < 4; ++u)
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const float4 t = *reinterpret_cast<const float4*>(b_s + kk * 20 + q * 4);
-            b[q * 4] = t.x; b[q * 4 + 1] = t.y; b[q * 4 + 2] = t.z; b[q * 4 + 3] = t.w;
+            for (int r = 0; r < 4; ++r)
+                a[u][r] = (kk0 + 32 * u < kn && m0 + r < M) ? __ldg(a0 + (int64_t)r * K + kk0 + 32 * u) : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int kk = kk0 + 32 * u;
+            if (kk < kn) {
+                float b[16];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 t = *reinterpret_cast<const float4*>(b_s + kk * 20 + q * 4);
+                    b[q * 4] = t.x; b[q * 4 + 1] = t.y; b[q * 4 + 2] = t.z; b[q * 4 + 3] = t.w;
+                }
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[r][j] = fmaf(a[u][r], b[j], acc[r][j]);
+            }
         }
-#pragma unroll
-        for (int r = 0; r < 4; ++r)
-#pragma unroll
-            for (int j = 0; j < 16; ++j) acc[r][j] = fmaf(a[r], b[j], acc[r][j]);
     }
     float* out = partial + (int64_t)blockIdx.y * M * N;
 #pragma unroll
@@ -188,16 +199,25 @@ __global__ void __launch_bounds__(256) k_gemm_thin_n_ta(float* __restrict__ part
         __syncthreads();
         if (m < M) {
             const int kn = min(64, k_end - k0);
-            for (int kk = 0; kk < kn; ++kk) {
-                float a = __ldg(A + (int64_t)(k0 + kk) * M + m);
+            for (int kk0 = 0; kk0 < kn; kk0 += 8) {   // eight loads of A in flight
+                float a[8];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) acc[j] = fmaf(a, b_s[kk][j], acc[j]);
+                for (int u = 0; u < 8; ++u) a[u] = kk0 + u < kn ? __ldg(A + (int64_t)(k0 + kk0 + u) * M + m) : 0.0f;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (kk0 + u < kn) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) acc[j] = fmaf(a[u], b_s[kk0 + u][j], acc[j]);
+                    }
+                }
             }
         }
     }
     if (m < M) {
         float* out = partial + ((int64_t)blockIdx.y * M + m) * N;
-        for (int j = 0; j < N; ++j) out[j] = acc[j];
+#pragma unroll
+        for (int j = 0; j < 16; ++j)       // static indices: the accumulators stay in registers
+            if (j < N) out[j] = acc[j];
     }
 }
 

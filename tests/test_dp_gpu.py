@@ -25,6 +25,15 @@ def _data():
 
 
 def _train(rank, world, uid, q):
+    try:
+        _train_body(rank, world, uid, q)
+    except BaseException as e:  # the parent fails with the child's message instead of waiting for its time-out
+        import traceback
+        q.put((rank, "error", traceback.format_exc(), -1))
+        raise
+
+
+def _train_body(rank, world, uid, q):
     sys.path.insert(0, str(ROOT))
     sys.path.insert(0, str(ROOT / "tests"))
     import ctypes as C
@@ -70,11 +79,19 @@ def _run(world):
     procs = [mpc.Process(target=_train, args=(r, world, uid, q)) for r in range(world)]
     for p in procs:
         p.start()
-    out = sorted((q.get(timeout=300) for _ in range(world)), key=lambda t: t[0])
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
-    return out
+    out = []
+    try:
+        for _ in range(world):
+            item = q.get(timeout=180)
+            assert item[1] != "error", "rank %d failed:\n%s" % (item[0], item[2])
+            out.append(item)
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    assert all(p.exitcode == 0 for p in procs)
+    return sorted(out, key=lambda t: t[0])
 
 
 @pytest.mark.parametrize("world", (2, 4, 8))
