@@ -41,8 +41,8 @@ def _train_body(rank, world, uid, q):
     from mantle_b200 import host_api, OP
     from test_oracle_kat import build_cnn
 
-    class Ns:
-        OP, nn, Graph = OP, host_api.nn, host_api.Graph
+    import types
+    Ns = types.SimpleNamespace(OP=OP, nn=host_api.nn, Graph=host_api.Graph)
 
     x, y, ws = _data()
     ctx = mb.Context(rank, mb.MATH_TF32X3)
