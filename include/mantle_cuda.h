@@ -420,6 +420,13 @@ MTL_API int32_t mtl_dp_init(mtl_ctx* ctx, const uint8_t* id, int32_t rank, int32
 MTL_API int32_t mtl_dp_allreduce_async(mtl_ctx* ctx, float* buf, int64_t n);
 /* Makes the context's stream wait for all outstanding allreduces. */
 MTL_API int32_t mtl_dp_wait(mtl_ctx* ctx);
+/* Host callback of the fused CONV2D backward entry points (mtl_conv2d_bwd_fused*, mtl_conv2d_bwd_pooled):
+ * when they compute dX as well, `hook(user)` is called once every kernel that writes dW and db has been
+ * enqueued and before the kernels of dX, so that a data-parallel caller can start exchanging the
+ * layer's parameter gradients (mtl_dp_allreduce_async) while the input gradient is computed.  Paths
+ * that cannot separate the two do not call it; the caller learns from its own flag whether it ran.
+ * Pass a null hook to remove it. */
+MTL_API int32_t mtl_set_grads_ready_hook(mtl_ctx* ctx, void (*hook)(void* user), void* user);
 /* Broadcast `n` floats from `root` (initial parameters). */
 MTL_API int32_t mtl_dp_broadcast(mtl_ctx* ctx, float* buf, int64_t n, int32_t root);
 MTL_API int32_t mtl_dp_destroy(mtl_ctx* ctx);

@@ -150,6 +150,7 @@ SIGNATURES = {
     "mtl_dp_get_unique_id": (_i32, [C.POINTER(C.c_uint8)]),
     "mtl_dp_init": (_i32, [_vp, C.POINTER(C.c_uint8), _i32, _i32]),
     "mtl_dp_allreduce_async": (_i32, [_vp, _vp, _i64]),
+    "mtl_set_grads_ready_hook": (_i32, [_vp, _vp, _vp]),
     "mtl_dp_wait": (_i32, [_vp]),
     "mtl_dp_broadcast": (_i32, [_vp, _vp, _i64, _i32]),
     "mtl_dp_destroy": (_i32, [_vp]),

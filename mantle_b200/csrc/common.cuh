@@ -36,6 +36,8 @@ struct mtl_ctx {
     void* dp = nullptr;
     // cached driver entry point for tensor-map encoding (tma.cuh)
     void* encode_tiled = nullptr;
+    void (*grads_ready_hook)(void*) = nullptr;  // see mtl_set_grads_ready_hook
+    void* grads_ready_user = nullptr;
     // staged input copies (mtl_stage_*): a copy stream and two events per slot
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t stage_ready[4] = {0};

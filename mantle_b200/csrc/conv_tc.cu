@@ -1560,6 +1560,7 @@ int32_t mtl_conv_bwd_fused_tc_src(mtl_ctx* ctx, float* dX, float* dW, float* db,
     }
     rc = wgrad_core(ctx, dW, u_hi, u_lo, x_ready ? X_cl : x_hi, x_lo, partial, p, g, acc_dw, x3);
     if (rc) return rc;
+    if (ctx->grads_ready_hook) ctx->grads_ready_hook(ctx->grads_ready_user);   // dW and db are enqueued, dX is not
     // input gradient: the same copy of ug is the activation operand; its weights go where X was
     return run_igemm_core(ctx, c, x3, u_hi, u_lo, region, x3 ? region + wt_pad : nullptr);
 }

@@ -153,6 +153,13 @@ int32_t mtl_dp_broadcast(mtl_ctx* ctx, float* buf, int64_t n, int32_t root) {
     return MTL_OK;
 }
 
+int32_t mtl_set_grads_ready_hook(mtl_ctx* ctx, void (*hook)(void* user), void* user) {
+    MTL_CHECK_CTX(ctx);
+    ctx->grads_ready_hook = hook;
+    ctx->grads_ready_user = hook ? user : nullptr;
+    return MTL_OK;
+}
+
 int32_t mtl_dp_world_size(mtl_ctx* ctx) {
     if (!ctx || !ctx->dp) return 1;
     return ((DpState*)ctx->dp)->world;

@@ -1,4 +1,5 @@
 // Graph shape rules, the executor and Adam on top of the C ABI (see model.hpp).
+#include <exception>
 #include "model.hpp"
 
 #include <algorithm>
@@ -662,8 +663,28 @@ void Model::backward_enqueue() {
     // fill(grads[loss], 1.0), model.mojo:180
     check(mtl_fill_f32(ctx_, G(*g_.loss_out), g_.loss_out->shape.num_elements(), 1.0f), "seed loss gradient");
     grad_written_[g_.loss_out->id] = true;
+    // While a fused CONV2D backward runs, the library reports the moment its parameter gradients are
+    // enqueued (before the input gradient's kernels): the node's after_backward_node call is made
+    // then, so that a data-parallel trainer's exchange of those gradients overlaps the rest of the node.
+    struct EarlyHook {
+        Model* m; int node; bool fired = false; bool armed;
+        EarlyHook(Model* m_, int node_, bool arm) : m(m_), node(node_), armed(arm && m_->after_backward_node) {
+            if (armed) mtl_set_grads_ready_hook(m->ctx_, &EarlyHook::call, this);
+        }
+        ~EarlyHook() { if (armed) mtl_set_grads_ready_hook(m->ctx_, nullptr, nullptr); }
+        std::exception_ptr error;   // an exception must not travel through the C frames of the library
+        static void call(void* self) {
+            EarlyHook* h = static_cast<EarlyHook*>(self);
+            if (h->fired) return;
+            h->fired = true;
+            try { h->m->after_backward_node(h->m->after_backward_user, h->node); }
+            catch (...) { h->error = std::current_exception(); }
+        }
+        void rethrow() { if (error) std::rethrow_exception(error); }
+    };
     for (int i = (int)g_.nodes.size() - 1; i >= 0; --i) {
         const Node& n = g_.nodes[i];
+        bool node_reported = false;
         if (fusion_ && (bwd_skip_[i] || bwd_pool_skip_[i])) {
             // a RELU whose backward its MAXPOOL2D performs, or a MAXPOOL2D whose backward the CONV2D at
             // the head of the chain performs from the pooled gradient
@@ -683,10 +704,14 @@ void Model::backward_enqueue() {
             float* dw = w.trainable ? G(w) : nullptr;
             float* db = b.trainable ? G(b) : nullptr;
             const int ax = dx ? acc_flag(x) : 0, aw = dw ? acc_flag(w) : 0, ab = db ? acc_flag(b) : 0;
-            if (dx || dw || db)
+            if (dx || dw || db) {
+                EarlyHook early(this, i, dx != nullptr);
                 check(mtl_conv2d_bwd_pooled(ctx_, dx, dw, db, G(q.outputs[0]), pool_idx_.at(bwd_pooled_of_[i]), T(q.outputs[0]),
                                             T(x), twin_of(x), T(w), &d, MTL_OP_RELU, &pd, ax, aw, ab),
                       "CONV2D backward from the pooled gradient");
+                early.rethrow();
+                node_reported = early.fired;
+            }
         } else if (fusion_ && n.op == MTL_OP_CONV2D) {
             // all wanted operand gradients of the layer from one pass over ug (mtl_conv2d_bwd_fused)
             const Symbol& x = n.inputs[0];
@@ -697,14 +722,18 @@ void Model::backward_enqueue() {
             float* dw = w.trainable ? G(w) : nullptr;
             float* db = b.trainable ? G(b) : nullptr;
             const int ax = dx ? acc_flag(x) : 0, aw = dw ? acc_flag(w) : 0, ab = db ? acc_flag(b) : 0;
-            if (dx || dw || db)
+            if (dx || dw || db) {
+                EarlyHook early(this, i, dx != nullptr);
                 check(mtl_conv2d_bwd_fused_cl(ctx_, dx, dw, db, G(n.outputs[0]), T(x), twin_of(x), T(w), &d, ax, aw, ab),
                       "CONV2D backward");
+                early.rethrow();
+                node_reported = early.fired;
+            }
         } else {
             for (int j = 0; j < (int)n.inputs.size(); ++j)
                 if (n.inputs[j].trainable) backward_op(n, j);
         }
-        if (after_backward_node) after_backward_node(after_backward_user, i);
+        if (after_backward_node && !node_reported) after_backward_node(after_backward_user, i);
     }
 }
 
