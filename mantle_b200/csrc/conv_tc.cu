@@ -312,39 +312,53 @@ __global__ void __launch_bounds__(256) k_pool_bwd_2x2_cl(float* __restrict__ hi,
     __shared__ float part[8][33];
     const int n = blockIdx.y, c0 = blockIdx.x * 32;
     const int W = 2 * POW;
-    for (int e = threadIdx.x; e < 32 * P; e += 256) {
-        const int ch = e / P, q = e - ch * P;
-        float v = 0.0f;
-        int sub = -1;
-        if (c0 + ch < K) {
-            const int64_t o = ((int64_t)n * K + c0 + ch) * P + q;
-            v = pg[o];
-            if (relu) v = (pv[o] > 0.0f ? 1.0f : 0.0f) * v;   // RELU.backward on the selected element
-            const int qh = q / POW, qw = q - qh * POW;
-            const int d = pidx[o] - ((2 * qh) * W + 2 * qw);
-            sub = d == 0 ? 0 : d == 1 ? 1 : d == W ? 2 : d == W + 1 ? 3 : -1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // Phase 1, a warp per channel row, lanes along the pooled plane (coalesced): which of its window's
+    // four positions an element's gradient goes to, and the gradient after RELU.backward.
+    for (int q0 = 0; q0 < P; q0 += 32) {
+        const int q = q0 + lane;
+        const int qh = q / POW, qw = q - qh * POW;
+        const int first = (2 * qh) * W + 2 * qw;       // plane index of the window's upper left element
+        for (int ch = warp; ch < 32; ch += 8) {
+            if (q < P) {
+                float v = 0.0f;
+                int sub = -1;
+                if (c0 + ch < K) {
+                    const int64_t o = ((int64_t)n * K + c0 + ch) * P + q;
+                    v = pg[o];
+                    if (relu) v = (pv[o] > 0.0f ? 1.0f : 0.0f) * v;   // RELU.backward on the selected element
+                    const int d = pidx[o] - first;
+                    sub = d == 0 ? 0 : d == 1 ? 1 : d == W ? 2 : d == W + 1 ? 3 : -1;
+                }
+                val[ch * PS + q] = v;
+                pos[ch * PS + q] = sub;
+            }
         }
-        val[ch * PS + q] = v;
-        pos[ch * PS + q] = sub;
     }
     __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // Phase 2, lanes along the channels (coalesced channels-last stores): a warp takes a window at a
+    // time and writes its four pixels, the routed gradient in one of them and zeros in the others.
     const int k = c0 + lane;
     float s = 0.0f;
-    for (int pix = warp; pix < 4 * P; pix += 8) {
-        const int oh = pix / W, ow = pix - oh * W;
-        const int q = (oh >> 1) * POW + (ow >> 1), sub = ((oh & 1) << 1) | (ow & 1);
-        const float v = pos[lane * PS + q] == sub ? val[lane * PS + q] : 0.0f;
-        s += v;
+    for (int q = warp; q < P; q += 8) {
+        const int qh = q / POW, qw = q - qh * POW;
+        const float g = val[lane * PS + q];
+        const int sub = pos[lane * PS + q];
+        s += sub >= 0 ? g : 0.0f;
         if (k < K) {
-            const int64_t o = ((int64_t)n * 4 * P + pix) * K + k;
+            const int64_t o = ((int64_t)n * 4 * P + (2 * qh) * W + 2 * qw) * K + k;
+            const float v0 = sub == 0 ? g : 0.0f, v1 = sub == 1 ? g : 0.0f, v2 = sub == 2 ? g : 0.0f, v3 = sub == 3 ? g : 0.0f;
             if (SPLIT) {
                 float h, l;
-                split_tf32(v, h, l);
-                hi[o] = h;
-                lo[o] = l;
+                split_tf32(v0, h, l); hi[o] = h; lo[o] = l;
+                split_tf32(v1, h, l); hi[o + K] = h; lo[o + K] = l;
+                split_tf32(v2, h, l); hi[o + (int64_t)W * K] = h; lo[o + (int64_t)W * K] = l;
+                split_tf32(v3, h, l); hi[o + (int64_t)W * K + K] = h; lo[o + (int64_t)W * K + K] = l;
             } else {
-                hi[o] = v;
+                hi[o] = v0;
+                hi[o + K] = v1;
+                hi[o + (int64_t)W * K] = v2;
+                hi[o + (int64_t)W * K + K] = v3;
             }
         }
     }
