@@ -348,8 +348,9 @@ def run_ours(args):
                          "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
                          "frac": (achieved / tf32_peak) if achieved else None,
                          # dram read + write per launch from the ncu capture summarised under profiles/
-                         # (255.1 MB forward, 279.0 MB input gradient at batch 2048; both scale with the batch)
-                         "traffic": 267.05e6 * B / 2048, "traffic_unit": "bytes",
+                         # (157.7 MB forward with the pooling in the epilogue, 278.1 MB input gradient at batch
+                         # 2048: the average of the two launches of a step; both scale with the batch)
+                         "traffic": 217.9e6 * B / 2048, "traffic_unit": "bytes",
                          "peak_source": "%s bf16 sustained %.1f TF/s / 2 (TF32 runs at half the bf16 tensor rate)"
                                         % (pk["source"], pk["bf16_sustained"]),
                          "flops_per_launch": flops_per_launch, "avg_launch_ms": ig["avg_ms"], "launches_timed": ig["launches"]},
