@@ -1402,11 +1402,26 @@ int32_t wgrad_plan(mtl_ctx* ctx, const ConvGeom& g, int x3, WgradParams* pp, siz
     // taps per CTA: fit the accumulator columns, then balance the groups
     int tmax = 512 / g.C;
     if (tmax > RS) tmax = RS;
-    int best_t = 1, best_cost = 1 << 30;
+    // The kernel is bound by filling shared memory from L2 (every tap re-reads its shifted input box), not
+    // by the tensor pipe: measured on the 64->128 channel 5x5 layer, t = 4, 5, 6, 7, 8 taps per CTA take
+    // 0.384, 0.299, 0.317, 0.274, 0.353 ms.  Modelled time of a CTA: (bytes of one stage + a fixed 16 KB
+    // worth of per-stage overhead) x (pixel chunks per CTA); the CTAs left after dividing the SMs by the tap
+    // groups split the pixels, and at least three stages must fit shared memory.  Every tap group gets
+    // the same number of CTAs even when the last group has fewer taps: groups that walk the pixels in
+    // step share the gradient tiles in L2, groups at different speeds fetch them from DRAM once each
+    // (measured: 0.307 ms with the SMs shared out by work, 0.274 ms with equal shares).
+    int best_t = 1;
+    double best_cost = 1e30;
     for (int t = 1; t <= tmax; ++t) {
-        int cost = ((RS + t - 1) / t) * t;
-        if (cost < best_cost || (cost == best_cost && t > best_t)) { best_cost = cost; best_t = t; }
+        const int stage_bytes = 4 * 4096 + t * (g.C / 32) * 4096;
+        if (t > 1 && (232448 - 2048) / stage_bytes < 3) break;
+        const int groups = (RS + t - 1) / t;
+        int ns = ctx->sm_count / (groups * ((g.K + BM - 1) / BM));
+        if (ns < 1) ns = 1;
+        const double cost = (double)(stage_bytes + 16384) / ns;
+        if (cost < best_cost * 0.999) { best_cost = cost; best_t = t; }
     }
+    if (const char* e = getenv("MANTLE_WGRAD_TAPS")) { int t = atoi(e); if (t >= 1 && t <= tmax) best_t = t; }
     p.T = best_t;
     p.ngroups = (RS + p.T - 1) / p.T;
     p.ktiles = (g.K + BM - 1) / BM;
