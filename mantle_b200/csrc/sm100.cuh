@@ -53,6 +53,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// try_wait that lets the hardware park the thread for up to `hint_ns` while the phase is incomplete:
+// a waiting role then stops competing for issue slots with the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Waits for the phase with the given parity to complete.  Gives up after `budget_ns` of wall
 // time or as soon as *abort_flag is set by another role; returns false in both cases.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
@@ -61,8 +77,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 63u) == 0) {
+        if (mbar_try_wait_parked(bar, parity, 2000u)) return true;
+        if ((++spins & 15u) == 0) {
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > budget_ns) {
                 *abort_flag = 1;
