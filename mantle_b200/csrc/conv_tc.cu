@@ -1003,8 +1003,18 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
             // whole rows, two of them, as many images as fit while the last 32-column read stays inside
             q.bw = c.OW;
             q.bh = 2;
-            q.bn = (256 - 32) / (2 * c.OW) + 1;
-            if (q.bn > c.N) q.bn = c.N;
+            int bn_max = (256 - 32) / (2 * c.OW) + 1;
+            if (bn_max > c.N) bn_max = c.N;
+            // images per box: fewest (waves of tiles) x (TMA rows and boxes of a k-block), which for a small
+            // batch is not the fullest box (256 images: 203 tiles of 9 images and 259 tiles of 7 both take
+            // two waves on 148 SMs, and the tile of 7 is shorter)
+            double best = 1e30;
+            q.bn = bn_max;
+            for (int bn = bn_max; bn >= 1; --bn) {
+                const int64_t tiles = (int64_t)(c.OH / 2) * ((c.N + bn - 1) / bn) * ((c.Kout + BM - 1) / BM);
+                const double cost = (double)((tiles + ctx->sm_count - 1) / ctx->sm_count) * (128 + 2 * c.OW * bn + 70);
+                if (cost < best * 0.98) { best = cost; q.bn = bn; }
+            }
         } else if (paired) {
             // whole rows plus the extra column; the box that fills most of 240 columns
             q.bw = c.OW + 1;
@@ -1015,6 +1025,15 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
                 int64_t tiles = (int64_t)((c.OH + bh - 1) / bh) * ((c.N + bn - 1) / bn);
                 double eff = (double)c.OW * c.OH * c.N / ((double)tiles * 240.0) + 1e-4 * bh;
                 if (eff > best) { best = eff; q.bh = bh; q.bn = bn; }
+            }
+            // then fewer images per box if that shortens (waves of tiles) x (TMA rows and boxes of a
+            // k-block): for a small batch two waves of shorter tiles beat two waves of full ones
+            double cost0 = 1e30;
+            for (int bn = q.bn, bn0 = q.bn; bn >= 1; --bn) {
+                const int64_t tiles = (int64_t)((c.OH + q.bh - 1) / q.bh) * ((c.N + bn - 1) / bn);
+                const double cost = (double)((tiles + ctx->sm_count - 1) / ctx->sm_count) * (128 + q.bw * q.bh * bn + 70);
+                if (bn == bn0) cost0 = cost;
+                if (cost < cost0 * 0.98) { cost0 = cost; q.bn = bn; }
             }
         } else {
             choose_box_n(c.OW, c.OH, c.N, 256, &q.bw, &q.bh, &q.bn);
@@ -1295,8 +1314,17 @@ __global__ void __launch_bounds__(256) k_wgrad_fold(float* __restrict__ dW, cons
         int64_t q = i / C;
         int k = (int)(q % K);
         int rs = (int)(q / K);
+        // eight partials in flight at a time, added in ascending order (the loads do not depend on one another)
         float s = 0.0f;
-        for (int j = 0; j < nsplit; ++j) s += partial[(int64_t)j * total + i];
+        int j = 0;
+        for (; j + 8 <= nsplit; j += 8) {
+            float t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) t[u] = partial[(int64_t)(j + u) * total + i];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) s += t[u];
+        }
+        for (; j < nsplit; ++j) s += partial[(int64_t)j * total + i];
         int64_t o = ((int64_t)k * C + c) * RS + rs;
         dW[o] = accumulate ? dW[o] + s : s;
     }

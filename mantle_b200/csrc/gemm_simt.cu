@@ -227,7 +227,15 @@ __global__ void __launch_bounds__(256) k_fold_partials(float* __restrict__ out, 
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = tid; i < n; i += stride) {
         float s = 0.0f;
-        for (int j = 0; j < nsplit; ++j) s += partial[(int64_t)j * n + i];
+        int j = 0;
+        for (; j + 8 <= nsplit; j += 8) {   // eight partials in flight, added in ascending order
+            float t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) t[u] = partial[(int64_t)(j + u) * n + i];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) s += t[u];
+        }
+        for (; j < nsplit; ++j) s += partial[(int64_t)j * n + i];
         out[i] = accumulate ? out[i] + s : s;
     }
 }
