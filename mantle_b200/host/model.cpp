@@ -661,7 +661,9 @@ void Model::backward_enqueue() {
     if (!g_.loss_out) throw Error(MTL_ERR_INVALID, "no loss defined");
     grad_written_.clear();
     // fill(grads[loss], 1.0), model.mojo:180
-    check(mtl_fill_f32(ctx_, G(*g_.loss_out), g_.loss_out->shape.num_elements(), 1.0f), "seed loss gradient");
+    // (not needed when the loss chain runs as mtl_cross_entropy_bwd, which assumes the seed)
+    if (!(fusion_ && ce_head_ >= 0))
+        check(mtl_fill_f32(ctx_, G(*g_.loss_out), g_.loss_out->shape.num_elements(), 1.0f), "seed loss gradient");
     grad_written_[g_.loss_out->id] = true;
     // While a fused CONV2D backward runs, the library reports the moment its parameter gradients are
     // enqueued (before the input gradient's kernels): the node's after_backward_node call is made
