@@ -121,8 +121,11 @@ __global__ void __launch_bounds__(128) k_gemm_thin_n(float* __restrict__ C, cons
 // warp streams four rows of A with coalesced loads and keeps 4 x 16 partial sums per lane.
 // Splitting k gives enough blocks to fill the machine when M is only a few thousand rows.
 constexpr int kThinKC = 512;  // k extent of one block
-__global__ void __launch_bounds__(256) k_gemm_thin_tile(float* __restrict__ partial, const float* __restrict__ A,
+// NQ: float4 groups of a row of B that are multiplied (N rounded up to a multiple of four columns).
+template <int NQ>
+__global__ void __launch_bounds__(256, 3) k_gemm_thin_tile(float* __restrict__ partial, const float* __restrict__ A,
                                                         const float* __restrict__ B, int M, int N, int K) {
+    constexpr int NP = 4 * NQ;
     __shared__ __align__(16) float b_s[kThinKC * 20];
     const int k_begin = blockIdx.y * kThinKC;
     const int kn = min(kThinKC, K - k_begin);
@@ -132,13 +135,12 @@ __global__ void __launch_bounds__(256) k_gemm_thin_tile(float* __restrict__ part
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = (blockIdx.x * 8 + warp) * 4;
-    if (m0 >= M) return;
-    float acc[4][16];
+    const int m0 = (blockIdx.x * 8 + warp) * 4;   // rows past M load zeros and store nothing
+    float acc[4][NP];
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
-        for (int j = 0; j < 16; ++j) acc[r][j] = 0.0f;
+        for (int j = 0; j < NP; ++j) acc[r][j] = 0.0f;
     const float* a0 = A + (int64_t)m0 * K + k_begin;
     // four k steps at a time: their sixteen loads of A are in flight together (the kernel is bound by
     // the latency of streaming A, not by arithmetic)
@@ -153,29 +155,37 @@ __global__ void __launch_bounds__(256) k_gemm_thin_tile(float* __restrict__ part
         for (int u = 0; u < 4; ++u) {
             const int kk = kk0 + 32 * u;
             if (kk < kn) {
-                float b[16];
+                float b[NP];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
+                for (int q = 0; q < NQ; ++q) {
                     const float4 t = *reinterpret_cast<const float4*>(b_s + kk * 20 + q * 4);
                     b[q * 4] = t.x; b[q * 4 + 1] = t.y; b[q * 4 + 2] = t.z; b[q * 4 + 3] = t.w;
                 }
 #pragma unroll
                 for (int r = 0; r < 4; ++r)
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) acc[r][j] = fmaf(a[u][r], b[j], acc[r][j]);
+                    for (int j = 0; j < NP; ++j) acc[r][j] = fmaf(a[u][r], b[j], acc[r][j]);
             }
         }
     }
+    // the 32 lanes' partial sums of a row meet in shared memory: lane j then adds column j over the lanes
+    // in ascending order (cheaper than a five-step shuffle tree per value)
     float* out = partial + (int64_t)blockIdx.y * M * N;
+    __syncthreads();                              // every warp is done with the rows of B: their memory is reused
+    float* rs = b_s + warp * 32 * (NP + 1);       // per warp: the lanes' partial sums of one row, odd row stride
 #pragma unroll
-    for (int r = 0; r < 4; ++r)
+    for (int r = 0; r < 4; ++r) {
+        __syncwarp();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            float v = acc[r][j];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0 && j < N && m0 + r < M) out[(int64_t)(m0 + r) * N + j] = v;
+        for (int j = 0; j < NP; ++j) rs[lane * (NP + 1) + j] = acc[r][j];
+        __syncwarp();
+        if (lane < N && m0 + r < M) {
+            float s = 0.0f;
+#pragma unroll 8
+            for (int l = 0; l < 32; ++l) s += rs[l * (NP + 1) + lane];
+            out[(int64_t)(m0 + r) * N + lane] = s;
         }
+    }
 }
 
 // partial[split][M,N] = A^T . B over a slice of k, A stored [K, M] (m contiguous): one thread per
@@ -254,7 +264,10 @@ int32_t mtl_gemm_thin(mtl_ctx* ctx, float* C, const float* A, const float* B, in
         int32_t rc = mtl_workspace(ctx, (size_t)nsplit * M * N * 4, &ws);
         if (rc) return rc;
         dim3 grid((unsigned)((M + 31) / 32), (unsigned)nsplit);
-        k_gemm_thin_tile<<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K);
+        if (N <= 4) k_gemm_thin_tile<1><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K);
+        else if (N <= 8) k_gemm_thin_tile<2><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K);
+        else if (N <= 12) k_gemm_thin_tile<3><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K);
+        else k_gemm_thin_tile<4><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K);
         MTL_LAUNCHED(ctx);
         int fg = mtl_grid_for(M * N, 256, ctx->sm_count, 8);
         k_fold_partials<<<fg, 256, 0, ctx->stream>>>(C, (const float*)ws, M * N, nsplit, accumulate);
