@@ -190,16 +190,18 @@ __global__ void __launch_bounds__(256, 3) k_gemm_thin_tile(float* __restrict__ p
 
 // partial[split][M,N] = A^T . B over a slice of k, A stored [K, M] (m contiguous): one thread per
 // output row, rows of B staged in shared memory.
+template <int NQ>
 __global__ void __launch_bounds__(256) k_gemm_thin_n_ta(float* __restrict__ partial, const float* __restrict__ A,
                                                         const float* __restrict__ B, int M, int N, int K,
                                                         int k_per_split) {
-    __shared__ float b_s[64][16];
+    constexpr int NP = 4 * NQ;   // N rounded up to whole float4 groups
+    __shared__ __align__(16) float b_s[64][16];
     const int m = blockIdx.x * blockDim.x + threadIdx.x;
     const int k_begin = blockIdx.y * k_per_split;
     const int k_end = min(K, k_begin + k_per_split);
-    float acc[16];
+    float acc[NP];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+    for (int j = 0; j < NP; ++j) acc[j] = 0.0f;
     for (int k0 = k_begin; k0 < k_end; k0 += 64) {
         __syncthreads();
         for (int i = threadIdx.x; i < 64 * 16; i += blockDim.x) {
@@ -217,7 +219,13 @@ __global__ void __launch_bounds__(256) k_gemm_thin_n_ta(float* __restrict__ part
                 for (int u = 0; u < 8; ++u) {
                     if (kk0 + u < kn) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) acc[j] = fmaf(a[u], b_s[kk0 + u][j], acc[j]);
+                        for (int q = 0; q < NQ; ++q) {
+                            const float4 t = *reinterpret_cast<const float4*>(&b_s[kk0 + u][4 * q]);
+                            acc[4 * q] = fmaf(a[u], t.x, acc[4 * q]);
+                            acc[4 * q + 1] = fmaf(a[u], t.y, acc[4 * q + 1]);
+                            acc[4 * q + 2] = fmaf(a[u], t.z, acc[4 * q + 2]);
+                            acc[4 * q + 3] = fmaf(a[u], t.w, acc[4 * q + 3]);
+                        }
                     }
                 }
             }
@@ -226,7 +234,7 @@ __global__ void __launch_bounds__(256) k_gemm_thin_n_ta(float* __restrict__ part
     if (m < M) {
         float* out = partial + ((int64_t)blockIdx.y * M + m) * N;
 #pragma unroll
-        for (int j = 0; j < 16; ++j)       // static indices: the accumulators stay in registers
+        for (int j = 0; j < NP; ++j)       // static indices: the accumulators stay in registers
             if (j < N) out[j] = acc[j];
     }
 }
@@ -291,7 +299,10 @@ int32_t mtl_gemm_thin(mtl_ctx* ctx, float* C, const float* A, const float* B, in
     int32_t rc = mtl_workspace(ctx, (size_t)nsplit * M * N * 4, &ws);
     if (rc) return rc;
     dim3 grid((unsigned)gx, (unsigned)nsplit);
-    k_gemm_thin_n_ta<<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
+    if (N <= 4) k_gemm_thin_n_ta<1><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
+    else if (N <= 8) k_gemm_thin_n_ta<2><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
+    else if (N <= 12) k_gemm_thin_n_ta<3><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
+    else k_gemm_thin_n_ta<4><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
     MTL_LAUNCHED(ctx);
     int fg = mtl_grid_for(M * N, 256, ctx->sm_count, 8);
     k_fold_partials<<<fg, 256, 0, ctx->stream>>>(C, (const float*)ws, M * N, nsplit, accumulate);
