@@ -349,6 +349,29 @@ __global__ void __launch_bounds__(kBlock) k_binary_bwd_unb_block(float* __restri
     }
 }
 
+// The bias-gradient case of the kernel above without its general index arithmetic: ug is [R, C]
+// (row-major), grad is [C], ADD or SUB.  Same assignment of rows to threads and same reduction tree,
+// hence the same bits.
+__global__ void __launch_bounds__(kBlock) k_unb_rows(float* __restrict__ grad, const float* __restrict__ ug, int64_t R,
+                                                     int64_t C, float sign, int acc) {
+    __shared__ float warp_sums[kBlock / 32];
+    for (int64_t j = blockIdx.x; j < C; j += gridDim.x) {
+        float s = 0.0f;
+        for (int64_t r = threadIdx.x; r < R; r += blockDim.x) s += sign * ug[r * C + j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = s;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float t = threadIdx.x < kBlock / 32 ? warp_sums[threadIdx.x] : 0.0f;
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+            if (threadIdx.x == 0) grad[j] = acc ? grad[j] + t : t;
+        }
+        __syncthreads();
+    }
+}
+
 // One thread per grad element (short reductions).
 __global__ void __launch_bounds__(kBlock) k_binary_bwd_unb_thread(float* __restrict__ grad,
                                                                   const float* __restrict__ ug,
@@ -559,6 +582,15 @@ int32_t mtl_binary_bwd(mtl_ctx* ctx, int32_t op, int32_t tensor_id, float* grad,
             ub.red_ostride[ub.n_red++] = ostride[d];
             n_red *= bc.shape[d];
         }
+    }
+    if (n_red >= 128 && (op == MTL_OP_ADD || op == MTL_OP_SUB) && ub.n_keep == 1 && ub.n_red == 1 &&
+        ub.keep_ostride[0] == 1 && ub.red_ostride[0] == ub.keep_size[0]) {
+        // a bias gradient: column sums of a row-major [rows, n_grad] upper gradient
+        const float sign = (op == MTL_OP_SUB && tensor_id == 1) ? -1.0f : 1.0f;
+        int grid = (int)(n_grad < (int64_t)ctx->sm_count * kCtasPerSm ? n_grad : (int64_t)ctx->sm_count * kCtasPerSm);
+        k_unb_rows<<<grid, kBlock, 0, ctx->stream>>>(grad, ug, n_red, n_grad, sign, acc);
+        MTL_LAUNCHED(ctx);
+        return MTL_OK;
     }
     if (n_red >= 128) {
         int grid = (int)(n_grad < (int64_t)ctx->sm_count * kCtasPerSm ? n_grad : (int64_t)ctx->sm_count * kCtasPerSm);
