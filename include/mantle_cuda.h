@@ -129,6 +129,11 @@ MTL_API int32_t mtl_host_free(mtl_ctx* ctx, void* hptr);
 /* Collection.set_zero (collection.mojo:222) and fill (mantle/core/tensorutils.mojo:30-44). */
 MTL_API int32_t mtl_zero(mtl_ctx* ctx, void* dptr, size_t bytes);
 MTL_API int32_t mtl_fill_f32(mtl_ctx* ctx, float* dptr, int64_t n, float value);
+/* One-hot targets on the device: out[b][c] = 1 when c == Int(labels[b]) else 0, for fp32 class labels as the
+ * reference's DataLoader hands them over (examples/mnist.mojo:92-97 builds this tensor on the host every
+ * batch).  The step then copies B floats of labels instead of B*C floats of targets.  A label outside
+ * [0, C) gives an all-zero row (the reference would write outside the row). */
+MTL_API int32_t mtl_one_hot_f32(mtl_ctx* ctx, float* out, const float* labels, int64_t B, int64_t C);
 /* RESHAPE / FLATTEN / SQUEEZE / UNSQUEEZE forward and backward are copies
  * (mantle/autograd/ops/basics.mojo:706-756, mlops.mojo:302-373). accumulate != 0: dst += src. */
 MTL_API int32_t mtl_copy_f32(mtl_ctx* ctx, float* dst, const float* src, int64_t n,

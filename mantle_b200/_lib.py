@@ -96,6 +96,7 @@ SIGNATURES = {
     "mtl_host_free": (_i32, [_vp, _vp]),
     "mtl_zero": (_i32, [_vp, _vp, C.c_size_t]),
     "mtl_fill_f32": (_i32, [_vp, _vp, _i64, _f32]),
+    "mtl_one_hot_f32": (_i32, [_vp, _vp, _vp, _i64, _i64]),
     "mtl_copy_f32": (_i32, [_vp, _vp, _vp, _i64, _i32]),
     "mtl_dot_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64]),
     "mtl_dot_bwd": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),

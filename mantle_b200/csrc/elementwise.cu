@@ -452,7 +452,30 @@ bool unary_op_known(int op) {
 
 }  // namespace
 
+namespace {
+// out[b][c] = 1 when c == Int(labels[b]), else 0 (examples/mnist.mojo:92-97: labels arrive as fp32).
+// A label outside [0, C) leaves its row all zeros; the reference would write outside the row.
+__global__ void __launch_bounds__(kBlock) k_one_hot(float* __restrict__ out, const float* __restrict__ labels, int64_t B,
+                                                    int64_t C) {
+    const int64_t n = B * C;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = i / C, c = i - b * C;
+        out[i] = (int64_t)labels[b] == c ? 1.0f : 0.0f;
+    }
+}
+}  // namespace
+
 extern "C" {
+
+int32_t mtl_one_hot_f32(mtl_ctx* ctx, float* out, const float* labels, int64_t B, int64_t C) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, B >= 0 && C >= 1 && ((out && labels) || B == 0), "bad arguments to mtl_one_hot_f32");
+    if (B == 0) return MTL_OK;
+    int grid = mtl_grid_for(B * C, kBlock, ctx->sm_count, kCtasPerSm);
+    k_one_hot<<<grid, kBlock, 0, ctx->stream>>>(out, labels, B, C);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
 
 int32_t mtl_fill_f32(mtl_ctx* ctx, float* dptr, int64_t n, float value) {
     MTL_CHECK_CTX(ctx);

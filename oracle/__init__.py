@@ -7,7 +7,7 @@ Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may import
 mantle_b200 package never does."""
 from .ops import (OP, lib, build, dot, dot_transpose_t1, dot_transpose_t2, conv_out_shape, conv2d_fwd, conv2d_bwd,
                   maxpool2d_fwd, maxpool2d_bwd, binary_fwd, binary_bwd, unary_fwd, unary_bwd, reduce_fwd, reduce_bwd,
-                  adam_step, broadcast_shapes, forward_op, backward_op)
+                  adam_step, one_hot, broadcast_shapes, forward_op, backward_op)
 from .model import Graph, Model, Adam, nn, Symbol
 from . import checkpoint
 from . import layout

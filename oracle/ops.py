@@ -205,6 +205,18 @@ def reduce_bwd(op, ug, x, axis=None, grad=None):
     return grad
 
 
+def one_hot(labels, num_classes):
+    """examples/mnist.mojo:92-97: labels_one_hot[b * C + Int(labels[b])] = 1.0 on a zero tensor (fp32 labels,
+    truncated toward zero); rows whose label falls outside [0, C) stay zero here."""
+    lab = np.asarray(labels, np.float32).ravel()
+    out = np.zeros((lab.size, int(num_classes)), np.float32)
+    for b, v in enumerate(lab):
+        c = int(v)
+        if 0 <= c < num_classes:
+            out[b, c] = 1.0
+    return out
+
+
 def adam_step(params, grads, m, v, lr, beta1, beta2, eps, it, grad_scale=1.0):
     """In place on float32 contiguous arrays."""
     for a in (params, grads, m, v):

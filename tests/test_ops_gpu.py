@@ -807,3 +807,20 @@ def test_cross_entropy_equals_nine_operator_calls(ctx, B, C):
         want = g["x"].numpy() + (init if acc else 0)
         assert_close(got.numpy(), want, 1e-5, 1e-7 * float(np.abs(g["x"].numpy()).max()) + 1e-9, "dlogits acc %d" % acc)
     assert ctx.device_status() == 0
+
+
+def test_one_hot_on_device(ctx):
+    """mtl_one_hot_f32 == the host loop of examples/mnist.mojo:92-97 (fp32 labels, Int() truncation)."""
+    rng = np.random.default_rng(77)
+    for B, C in ((2048, 10), (37, 3), (5, 1)):
+        lab = rng.integers(0, C, B).astype(np.float32)
+        lab[0] = C - 1 + 0.75 if C > 1 else 0.25      # truncates to a valid class
+        want = oracle.one_hot(lab, C)
+        assert np.array_equal(want, np.eye(C, dtype=np.float32)[lab.astype(np.int64)])
+        d_lab, out = ctx.array(lab), ctx.empty((B, C))
+        ctx._check(ctx.lib.mtl_one_hot_f32(ctx.handle, out.ptr, d_lab.ptr, B, C))
+        assert np.array_equal(out.numpy(), want)
+    lab = np.array([0, 5, -3, 2], np.float32)            # 5 and -3 are outside [0, 3): zero rows
+    out = ctx.empty((4, 3))
+    ctx._check(ctx.lib.mtl_one_hot_f32(ctx.handle, out.ptr, ctx.array(lab).ptr, 4, 3))
+    assert np.array_equal(out.numpy(), oracle.one_hot(lab, 3)) and out.numpy()[1].sum() == 0 and out.numpy()[2].sum() == 0

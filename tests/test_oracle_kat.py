@@ -269,3 +269,10 @@ def test_model_trajectories_against_torch(name, builder, lr, rtol, steps):
         m.set_tensor(s, w)
     losses = _train(m, oracle.Adam(m, lr=lr), (z[name + "__x"], z[name + "__y"]), steps)
     assert_close(losses, z[name + "__losses"][:steps], rtol, 1e-6, name + " losses")
+
+
+def test_one_hot_restatement():
+    """examples/mnist.mojo:92-97 and the label pattern of test_models_mnist.mojo (label i for sample i)."""
+    assert np.array_equal(oracle.one_hot(np.arange(4, dtype=np.float32), 10), np.eye(10, dtype=np.float32)[:4])
+    got = oracle.one_hot(np.array([9.0, 0.0, 3.99], np.float32), 10)
+    assert got.shape == (3, 10) and got.sum() == 3 and got[0, 9] == 1 and got[1, 0] == 1 and got[2, 3] == 1
