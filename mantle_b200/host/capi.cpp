@@ -144,6 +144,29 @@ MTLH_API int32_t mtlh_graph_op(void* g, int32_t op, int32_t n_operands, const in
         *out_id = s.id;
     });
 }
+// g.concat(*operands, dim) and g.split(operand, sections, dim): graph.mojo:180-210
+MTLH_API int32_t mtlh_graph_concat(void* g, int32_t n_operands, const int32_t* operand_ids, int32_t dim, int32_t* out_id) {
+    return guard([&] {
+        auto* b = static_cast<GraphBox*>(g);
+        std::vector<Symbol> ops;
+        for (int i = 0; i < n_operands; ++i) ops.push_back(b->sym(operand_ids[i]));
+        Symbol s = b->g.concat(ops, dim);
+        b->remember(s);
+        *out_id = s.id;
+    });
+}
+MTLH_API int32_t mtlh_graph_split(void* g, int32_t operand_id, int32_t n_sections, const int64_t* sections, int32_t dim,
+                                  int32_t* out_ids) {
+    return guard([&] {
+        auto* b = static_cast<GraphBox*>(g);
+        std::vector<int64_t> sec(sections, sections + n_sections);
+        std::vector<Symbol> res = b->g.split(b->sym(operand_id), sec, dim);
+        for (size_t i = 0; i < res.size(); ++i) {
+            b->remember(res[i]);
+            out_ids[i] = res[i].id;
+        }
+    });
+}
 // g.op(op, symbol, literal) / g.op(op, literal, symbol): graph.mojo:131-157
 MTLH_API int32_t mtlh_graph_op_scalar(void* g, int32_t op, int32_t sym_id, double value, int32_t scalar_first,
                                       const mtlh_attrs* attrs, int32_t* out_id) {

@@ -60,6 +60,8 @@ struct Attributes {
     std::vector<int> dims;                   // SQUEEZE / UNSQUEEZE
     std::vector<int> axes;                   // TRANSPOSE (empty = reversed), SLICE (empty = 0, 1, ...)
     std::vector<int64_t> starts, ends, steps;  // SLICE (steps empty = all 1)
+    int cat_dim = 0;                         // CONCAT / SPLIT: the axis
+    std::vector<int64_t> sections;           // SPLIT: extents of the pieces along that axis
 };
 
 struct Node {
@@ -125,6 +127,50 @@ struct Graph {
         n.inputs = operands;
         n.outputs = {res};
         n.attrs = attrs;
+        nodes.push_back(std::move(n));
+        return res;
+    }
+    // graph.mojo:180-193 -- CONCAT: any number of operands, equal shapes except along `dim`
+    Symbol concat(const std::vector<Symbol>& operands, int dim = 0) {
+        if (operands.empty()) throw std::invalid_argument("CONCAT needs at least one operand");
+        TensorShape rs = operands[0].shape;
+        if (dim < 0 || dim >= rs.rank) throw std::invalid_argument("CONCAT dim out of range");
+        for (size_t i = 1; i < operands.size(); ++i) {
+            const TensorShape& s = operands[i].shape;
+            if (s.rank != rs.rank) throw std::invalid_argument("CONCAT operands differ in rank");
+            for (int d = 0; d < rs.rank; ++d)
+                if (d != dim && s[d] != operands[0].shape[d]) throw std::invalid_argument("CONCAT operands differ outside dim");
+            rs.dims[dim] += s[dim];
+        }
+        Symbol res{symbol_count++, rs, result_trainable(operands)};
+        Node n;
+        n.op = MTL_OP_CONCAT;
+        n.inputs = operands;
+        n.outputs = {res};
+        n.attrs.cat_dim = dim;
+        nodes.push_back(std::move(n));
+        return res;
+    }
+    // graph.mojo:200-210 -- SPLIT: one operand, one result per section
+    std::vector<Symbol> split(const Symbol& operand, const std::vector<int64_t>& sections, int dim = 0) {
+        if (dim < 0 || dim >= operand.shape.rank) throw std::invalid_argument("SPLIT dim out of range");
+        int64_t total = 0;
+        for (int64_t s : sections) {
+            if (s <= 0) throw std::invalid_argument("SPLIT sections must be positive");
+            total += s;
+        }
+        if (sections.empty() || total != operand.shape[dim]) throw std::invalid_argument("SPLIT sections do not add up to the axis");
+        Node n;
+        n.op = MTL_OP_SPLIT;
+        n.inputs = {operand};
+        n.attrs.cat_dim = dim;
+        n.attrs.sections = sections;
+        for (int64_t s : sections) {
+            TensorShape rs = operand.shape;
+            rs.dims[dim] = s;
+            n.outputs.push_back(Symbol{symbol_count++, rs, operand.trainable});
+        }
+        std::vector<Symbol> res = n.outputs;
         nodes.push_back(std::move(n));
         return res;
     }

@@ -512,6 +512,24 @@ void Model::forward_op(const Node& n) {
     const Symbol& t1 = n.inputs[0];
     float p0, p1;
     switch (n.op) {
+        case MTL_OP_CONCAT: {   // dynamics.mojo:25-108
+            std::vector<const float*> ins;
+            std::vector<int64_t> shapes;
+            for (auto& s : n.inputs) {
+                ins.push_back(T(s));
+                shapes.insert(shapes.end(), s.shape.dims, s.shape.dims + s.shape.rank);
+            }
+            check(mtl_concat_fwd(ctx_, T(out), ins.data(), (int32_t)ins.size(), t1.shape.rank, shapes.data(), n.attrs.cat_dim),
+                  "CONCAT forward");
+            break;
+        }
+        case MTL_OP_SPLIT: {    // dynamics.mojo:111-199
+            std::vector<float*> outs;
+            for (auto& s : n.outputs) outs.push_back(T(s));
+            check(mtl_split_fwd(ctx_, outs.data(), T(t1), (int32_t)outs.size(), t1.shape.rank, t1.shape.dims,
+                                n.attrs.sections.data(), n.attrs.cat_dim), "SPLIT forward");
+            break;
+        }
         case MTL_OP_ADD: case MTL_OP_SUB: case MTL_OP_MUL: case MTL_OP_DIV:
             check(mtl_binary_fwd(ctx_, n.op, T(out), T(t1), T(n.inputs[1]), t1.shape.rank, t1.shape.dims,
                                  n.inputs[1].shape.rank, n.inputs[1].shape.dims), "binary forward");
@@ -592,6 +610,20 @@ void Model::backward_op(const Node& n, int tensor_id) {
     int acc = acc_flag(tj);
     float p0, p1;
     switch (n.op) {
+        case MTL_OP_CONCAT: {
+            std::vector<int64_t> shapes;
+            for (auto& s : n.inputs) shapes.insert(shapes.end(), s.shape.dims, s.shape.dims + s.shape.rank);
+            check(mtl_concat_bwd(ctx_, grad, ug, tensor_id, (int32_t)n.inputs.size(), t1.shape.rank, shapes.data(),
+                                 n.attrs.cat_dim, acc), "CONCAT backward");
+            break;
+        }
+        case MTL_OP_SPLIT: {   // the operand's gradient gathers the gradients of all the pieces
+            std::vector<const float*> ugs;
+            for (auto& s : n.outputs) ugs.push_back(G(s));
+            check(mtl_split_bwd(ctx_, grad, ugs.data(), (int32_t)ugs.size(), t1.shape.rank, t1.shape.dims,
+                                n.attrs.sections.data(), n.attrs.cat_dim, acc), "SPLIT backward");
+            break;
+        }
         case MTL_OP_ADD: case MTL_OP_SUB: case MTL_OP_MUL: case MTL_OP_DIV:
             check(mtl_binary_bwd(ctx_, n.op, tensor_id, grad, ug, T(t1), T(n.inputs[1]), t1.shape.rank, t1.shape.dims,
                                  n.inputs[1].shape.rank, n.inputs[1].shape.dims, acc), "binary backward");

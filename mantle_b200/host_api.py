@@ -4,7 +4,7 @@ mantle/nn/model.mojo, mantle/nn/optim.mojo, mantle/nn/*).  These classes only fo
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 
@@ -143,6 +143,20 @@ class Graph:
             ids = (C.c_int32 * len(operands))(*[o.id for o in operands])
             _ck(self.lib.mtlh_graph_op(self.handle, op, len(operands), ids, C.byref(a), C.byref(out)))
         return Symbol(self, out.value)
+
+    def concat(self, *operands: Symbol, dim: int = 0) -> Symbol:
+        """graph.mojo:180-193."""
+        ids = (C.c_int32 * len(operands))(*[o.id for o in operands])
+        out = C.c_int32()
+        _ck(self.lib.mtlh_graph_concat(self.handle, len(operands), ids, int(dim), C.byref(out)))
+        return Symbol(self, out.value)
+
+    def split(self, operand: Symbol, sections: Sequence[int], dim: int = 0) -> List[Symbol]:
+        """graph.mojo:200-210: one result symbol per section."""
+        sec = (C.c_int64 * len(sections))(*[int(s) for s in sections])
+        outs = (C.c_int32 * len(sections))()
+        _ck(self.lib.mtlh_graph_split(self.handle, operand.id, len(sections), sec, int(dim), outs))
+        return [Symbol(self, outs[i]) for i in range(len(sections))]
 
     def out(self, s: Symbol):
         _ck(self.lib.mtlh_graph_out(self.handle, s.id))

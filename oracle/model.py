@@ -14,7 +14,7 @@ from typing import Optional, Sequence
 
 import numpy as np
 
-from . import ops
+from . import layout, ops
 from .ops import OP
 
 
@@ -127,6 +127,26 @@ class Graph:
         self.symbol_count += 1
         self.nodes.append(Node(op, operands, [res], attrs))
         return res
+
+    def concat(self, *operands, dim=0):
+        """graph.mojo:180-193."""
+        shape = list(operands[0].shape)
+        shape[dim] = sum(o.shape[dim] for o in operands)
+        res = Symbol(self.symbol_count, tuple(shape), any(o.trainable for o in operands))
+        self.symbol_count += 1
+        self.nodes.append(Node(OP.CONCAT, operands, [res], {"dim": dim}))
+        return res
+
+    def split(self, operand, sections, dim=0):
+        """graph.mojo:200-210: one result symbol per section."""
+        assert sum(sections) == operand.shape[dim]
+        outs = []
+        for s in sections:
+            shape = tuple(s if a == dim else d for a, d in enumerate(operand.shape))
+            outs.append(Symbol(self.symbol_count, shape, operand.trainable))
+            self.symbol_count += 1
+        self.nodes.append(Node(OP.SPLIT, (operand,), outs, {"sections": list(sections), "dim": dim}))
+        return outs
 
     def counts(self):
         return {"nodes": len(self.nodes), "params": len(self.param_syms), "inputs": len(self.inputs),
@@ -253,6 +273,13 @@ class Model:
             self.tensors[s.id] = np.ascontiguousarray(v, np.float32).reshape(s.shape).copy()
         for n in self.g.nodes[:num_nodes]:
             t = [self.tensors[i.id] for i in n.inputs]
+            if n.op == OP.CONCAT:       # dynamics.mojo:25-108
+                self.tensors[n.outputs[0].id] = layout.concat_fwd(t, n.attrs["dim"])
+                continue
+            if n.op == OP.SPLIT:        # dynamics.mojo:111-199
+                for o, piece in zip(n.outputs, layout.split_fwd(t[0], n.attrs["sections"], n.attrs["dim"])):
+                    self.tensors[o.id] = piece
+                continue
             if n.op == OP.POW:
                 t = t[:1]
             self.tensors[n.outputs[0].id] = ops.forward_op(n.op, *t, **self._attrs(n))
@@ -270,6 +297,17 @@ class Model:
         self.grads[self.g.loss_out.id].fill(1.0)
         for n in reversed(self.g.nodes):
             t = [self.tensors[i.id] for i in n.inputs]
+            if n.op == OP.CONCAT:
+                shapes = [i.shape for i in n.inputs]
+                for j, operand in enumerate(n.inputs):
+                    if operand.trainable:
+                        self.grads[operand.id] += layout.concat_bwd(self.grads[n.outputs[0].id], shapes, j, n.attrs["dim"])
+                continue
+            if n.op == OP.SPLIT:
+                if n.inputs[0].trainable:
+                    self.grads[n.inputs[0].id] += layout.split_bwd([self.grads[o.id] for o in n.outputs], n.inputs[0].shape,
+                                                                   n.attrs["sections"], n.attrs["dim"])
+                continue
             args = t[:1] if n.op == OP.POW else t
             while len(args) < 3:
                 args = args + [None]

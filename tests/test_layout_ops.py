@@ -189,3 +189,68 @@ def test_transpose_and_slice_as_graph_nodes(ctx):
     out_sym = host_api.Symbol(g, g.node(4)["output"])   # Linear = DOT + ADD, then TRANSPOSE, SLICE, TRANSPOSE
     got = m.inference(x, y, outputs=[out_sym])[0]
     assert got.shape == (3, 4) and np.allclose(got, om.inference(x, y)[0], rtol=1e-5, atol=1e-6)
+
+
+def _build_concat_split(ns, g):
+    from mantle_b200 import OP
+    x = g.input((4, 6))
+    y = g.input((4, 3))
+    h = ns.nn.Linear(g, x, 6)                                      # trainable path in front of the SPLIT
+    a, b = g.split(h, [2, 4], dim=1)                               # [4, 2], [4, 4]
+    h = g.concat(g.op(OP.TANH, b), g.op(OP.RELU, a), a, dim=1)     # [4, 8]: `a` is read twice
+    top, rest = g.split(h, [1, 3], dim=0)                          # [1, 8], [3, 8]
+    h = g.concat(rest, top, dim=0)                                 # rows rotated
+    out = ns.nn.Linear(g, h, 3)
+    g.out(out)
+    g.loss(ns.nn.MSELoss(g, out, y))
+    g.test_out = out
+
+
+def test_concat_split_nodes_in_the_oracle_executor():
+    """Graph.concat / Graph.split (graph.mojo:180-210) in the CPU executor against plain numpy."""
+    og = oracle.Graph()
+    _build_concat_split(oracle, og)
+    om = oracle.Model(og)
+    rng = np.random.default_rng(71)
+    x = rng.normal(0, 1, (4, 6)).astype(np.float32)
+    y = rng.normal(0, 1, (4, 3)).astype(np.float32)
+    w1, b1, w2, b2 = [om.tensor(s).astype(np.float64) for s in og.params() if s.trainable]
+    h = x @ w1 + b1
+    a, b = h[:, :2], h[:, 2:]
+    h = np.concatenate([np.tanh(b), np.maximum(a, 0), a], 1)
+    h = np.concatenate([h[1:], h[:1]], 0)
+    want = np.mean((y - (h @ w2 + b2)) ** 2)
+    assert abs(om.forward(x, y) - want) <= 1e-5 * abs(want)
+    # gradient of the first weight by central differences through the whole chain
+    om.zero_grads(); om.backward()
+    s_w1 = [s for s in og.params() if s.trainable][0]
+    g_w1 = om.grad(s_w1)
+    base = om.tensor(s_w1)
+    for (i, j) in ((0, 0), (3, 4), (5, 1)):
+        d = np.zeros_like(base); d[i, j] = 1e-2
+        om.set_tensor(s_w1, base + d); lp = om.forward(x, y)
+        om.set_tensor(s_w1, base - d); lm = om.forward(x, y)
+        om.set_tensor(s_w1, base)
+        assert abs((lp - lm) / 2e-2 - g_w1[i, j]) <= 2e-2 * abs(g_w1[i, j]) + 2e-3
+
+
+@pytest.mark.gpu
+def test_concat_and_split_as_graph_nodes(ctx):
+    """CONCAT (several operands, one read twice) and SPLIT (several results) as nodes of the C++ mirror: loss,
+    every parameter gradient and the graph output against the oracle's executor, in both accumulation modes."""
+    from test_models_gpu import make_pair
+    for strict in (False, True):
+        (g, m), (og, om) = make_pair(ctx, _build_concat_split, seed=72)
+        m.set_overwrite_first(not strict)
+        rng = np.random.default_rng(73)
+        x = rng.normal(0, 1, (4, 6)).astype(np.float32)
+        y = rng.normal(0, 1, (4, 3)).astype(np.float32)
+        loss, oloss = m.forward(x, y), om.forward(x, y)
+        assert abs(loss - oloss) <= 1e-5 * abs(oloss) + 1e-6
+        m.zero_grads(); om.zero_grads()
+        m.backward(); om.backward()
+        for s, os_ in zip(g.params(), og.params()):
+            if s.trainable:
+                assert np.allclose(m.grad(s), om.grad(os_), rtol=1e-4, atol=1e-6), strict
+        assert np.allclose(m.inference(x, y, outputs=[g.test_out])[0], om.inference(x, y)[0], rtol=1e-5, atol=1e-6)
+    assert ctx.device_status() == 0
