@@ -320,20 +320,25 @@ __global__ void __launch_bounds__(256) k_pool_bwd_2x2_cl(float* __restrict__ hi,
     const int W = 2 * POW;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // Phase 1, a warp per channel row, lanes along the pooled plane (coalesced): which of its window's
-    // four positions an element's gradient goes to, and the gradient after RELU.backward.
+    // four positions an element's gradient goes to, and the gradient after RELU.backward.  All offsets
+    // inside one image fit 32 bits; the image's base pointers carry the 64-bit part.
+    const float* pg_n = pg + (int64_t)n * K * P;
+    const int32_t* pidx_n = pidx + (int64_t)n * K * P;
+    const float* pv_n = relu ? pv + (int64_t)n * K * P : nullptr;
     for (int q0 = 0; q0 < P; q0 += 32) {
         const int q = q0 + lane;
         const int qh = q / POW, qw = q - qh * POW;
         const int first = (2 * qh) * W + 2 * qw;       // plane index of the window's upper left element
-        for (int ch = warp; ch < 32; ch += 8) {
-            if (q < P) {
+        if (q < P) {
+#pragma unroll 4
+            for (int ch = warp; ch < 32; ch += 8) {
                 float v = 0.0f;
                 int sub = -1;
                 if (c0 + ch < K) {
-                    const int64_t o = ((int64_t)n * K + c0 + ch) * P + q;
-                    v = pg[o];
-                    if (relu) v = (pv[o] > 0.0f ? 1.0f : 0.0f) * v;   // RELU.backward on the selected element
-                    const int d = pidx[o] - first;
+                    const int o = (c0 + ch) * P + q;
+                    v = pg_n[o];
+                    if (relu) v = (pv_n[o] > 0.0f ? 1.0f : 0.0f) * v;   // RELU.backward on the selected element
+                    const int d = pidx_n[o] - first;
                     sub = d == 0 ? 0 : d == 1 ? 1 : d == W ? 2 : d == W + 1 ? 3 : -1;
                 }
                 val[ch * PS + q] = v;
@@ -346,27 +351,32 @@ __global__ void __launch_bounds__(256) k_pool_bwd_2x2_cl(float* __restrict__ hi,
     // time and writes its four pixels, the routed gradient in one of them and zeros in the others.
     const int k = c0 + lane;
     float s = 0.0f;
+    float* hi_n = hi + (int64_t)n * 4 * P * K;
+    float* lo_n = SPLIT ? lo + (int64_t)n * 4 * P * K : nullptr;
+    const int row = W * K;                          // one output row of the image, channels-last
+    int qh = warp / POW, qw = warp - qh * POW;      // window (qh, qw) = window number `warp`, then + 8 each turn
     for (int q = warp; q < P; q += 8) {
-        const int qh = q / POW, qw = q - qh * POW;
         const float g = val[lane * PS + q];
         const int sub = pos[lane * PS + q];
         s += sub >= 0 ? g : 0.0f;
         if (k < K) {
-            const int64_t o = ((int64_t)n * 4 * P + (2 * qh) * W + 2 * qw) * K + k;
+            const int o = (2 * qh) * row + 2 * qw * K + k;
             const float v0 = sub == 0 ? g : 0.0f, v1 = sub == 1 ? g : 0.0f, v2 = sub == 2 ? g : 0.0f, v3 = sub == 3 ? g : 0.0f;
             if (SPLIT) {
                 float h, l;
-                split_tf32(v0, h, l); hi[o] = h; lo[o] = l;
-                split_tf32(v1, h, l); hi[o + K] = h; lo[o + K] = l;
-                split_tf32(v2, h, l); hi[o + (int64_t)W * K] = h; lo[o + (int64_t)W * K] = l;
-                split_tf32(v3, h, l); hi[o + (int64_t)W * K + K] = h; lo[o + (int64_t)W * K + K] = l;
+                split_tf32(v0, h, l); hi_n[o] = h; lo_n[o] = l;
+                split_tf32(v1, h, l); hi_n[o + K] = h; lo_n[o + K] = l;
+                split_tf32(v2, h, l); hi_n[o + row] = h; lo_n[o + row] = l;
+                split_tf32(v3, h, l); hi_n[o + row + K] = h; lo_n[o + row + K] = l;
             } else {
-                hi[o] = v0;
-                hi[o + K] = v1;
-                hi[o + (int64_t)W * K] = v2;
-                hi[o + (int64_t)W * K + K] = v3;
+                hi_n[o] = v0;
+                hi_n[o + K] = v1;
+                hi_n[o + row] = v2;
+                hi_n[o + row + K] = v3;
             }
         }
+        qw += 8;
+        while (qw >= POW) { qw -= POW; ++qh; }
     }
     if (colsum) {
         part[warp][lane] = s;
