@@ -91,6 +91,13 @@ MTL_API int32_t mtl_ctx_math_mode(mtl_ctx* ctx);
 /* Pre-sizes the internal scratch workspace (operand splits, channels-last staging, split-K
  * partials).  It grows on demand outside stream capture; growth during capture is an error. */
 MTL_API int32_t mtl_ctx_reserve_workspace(mtl_ctx* ctx, size_t bytes);
+/* State of that workspace (any out pointer may be null): its size and address, the number of
+ * instantiated graphs (mtl_graph_end) still alive on the context, and the number of older
+ * workspace blocks kept because such a graph was captured with them.  A block that has to grow
+ * while graphs are alive is not freed -- a replayed step goes on using the block it was captured
+ * with -- and is released when the last graph is destroyed.  No counterpart in the reference. */
+MTL_API int32_t mtl_ctx_workspace_info(mtl_ctx* ctx, size_t* bytes, void** block, int32_t* live_graphs,
+                                       int32_t* retired_blocks);
 MTL_API int32_t mtl_sync(mtl_ctx* ctx);
 MTL_API const char* mtl_last_error(mtl_ctx* ctx);
 /* Number of kernels this library launched on the context since creation (memsets and copies
@@ -310,6 +317,11 @@ MTL_API int32_t mtl_unary_fwd(mtl_ctx* ctx, int32_t op, float* out, const float*
 MTL_API int32_t mtl_unary_bwd(mtl_ctx* ctx, int32_t op, float* grad, const float* ug,
                               const float* in, int64_t n, float p0, float p1,
                               int32_t accumulate);
+/* POW.backward for the exponent (tensor_id 1, basics.mojo:359-376): grad[0] (+)= sum over the n
+ * elements of in^exponent * log(in) * ug, where log(in) counts as 0 when it is infinite (in == 0).
+ * grad is the [1]-shaped gradient of the exponent; the sum runs as a two-pass tree. */
+MTL_API int32_t mtl_pow_bwd_exponent(mtl_ctx* ctx, float* grad, const float* ug, const float* in,
+                                     int64_t n, float exponent, int32_t accumulate);
 /* FMA.forward/backward (basics.mojo:759-817): out = a*b + c, all the same shape. */
 MTL_API int32_t mtl_fma_fwd(mtl_ctx* ctx, float* out, const float* a, const float* b,
                             const float* c, int64_t n);
@@ -338,7 +350,9 @@ MTL_API int32_t mtl_reduce_bwd(mtl_ctx* ctx, int32_t op, float* grad, const floa
  * therefore accepts at most MTL_REDUCE_STATIC_MAX_ELEMENTS elements; larger sizes are rejected
  * with MTL_ERR_INVALID.  Results equal mtl_reduce_fwd(op, out, in, 1, {n}, -1).
  * The first call on a device looks up the array's device address (no allocation); make that call
- * before starting a stream capture.  All calls on a device share the one array: two calls whose
+ * before starting a stream capture (inside mtl_graph_begin/_end a first call is refused with
+ * MTL_ERR_INVALID).  Like every entry point it runs with the context's device current and leaves the
+ * caller's current device as it found it.  All calls on a device share the one array: two calls whose
  * kernels overlap on the GPU (different streams or contexts) race and give wrong results; calls
  * on one stream are ordered and safe. */
 #define MTL_REDUCE_STATIC_MAX_ELEMENTS (1ll << 28)

@@ -81,6 +81,7 @@ SIGNATURES = {
     "mtl_ctx_set_math_mode": (_i32, [_vp, _i32]),
     "mtl_ctx_math_mode": (_i32, [_vp]),
     "mtl_ctx_reserve_workspace": (_i32, [_vp, C.c_size_t]),
+    "mtl_ctx_workspace_info": (_i32, [_vp, C.POINTER(C.c_size_t), C.POINTER(_vp), C.POINTER(_i32), C.POINTER(_i32)]),
     "mtl_sync": (_i32, [_vp]),
     "mtl_last_error": (C.c_char_p, [_vp]),
     "mtl_launch_count": (_i64, [_vp]),
@@ -129,6 +130,7 @@ SIGNATURES = {
     "mtl_binary_bwd": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _pi64, _i32, _pi64, _i32]),
     "mtl_unary_fwd": (_i32, [_vp, _i32, _vp, _vp, _i64, _f32, _f32]),
     "mtl_unary_bwd": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _f32, _f32, _i32]),
+    "mtl_pow_bwd_exponent": (_i32, [_vp, _vp, _vp, _vp, _i64, _f32, _i32]),
     "mtl_fma_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64]),
     "mtl_fma_bwd": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i32]),
     "mtl_reduce_fwd": (_i32, [_vp, _i32, _vp, _vp, _i32, _pi64, _i32]),
@@ -187,4 +189,5 @@ def host_lib() -> C.CDLL:
         _host = C.CDLL(str(HOST_LIB_PATH))
         _host.mtlh_last_error.restype = C.c_char_p
         _host.mtlh_model_n_trainable.restype = C.c_int64
+        _host.mtlh_trainer_input_bytes.restype = C.c_int64
     return _host

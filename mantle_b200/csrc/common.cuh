@@ -14,8 +14,26 @@
 
 #define MTL_NUM_TIMERS 64
 
+// Tuning switches, read from the environment ONCE when a context is created (the launch paths never
+// call getenv).  A negative value means "not set: use the built-in choice".
+struct mtl_tuning {
+    bool log_errors = false;          // MANTLE_CUDA_LOG=1: print every recorded error to stderr
+    bool conv_channel_major = true;   // MANTLE_CONV_CHANNEL_MAJOR=0 switches the channel-major implicit GEMM off
+    bool conv_paired = true;          // MANTLE_CONV_PAIRED=0: one filter tap per instruction
+    bool conv_spread = true;          // MANTLE_CONV_SPREAD=0: plain row order of the pixel boxes
+    bool conv_pool_epilogue = true;   // MANTLE_CONV_POOL_EPILOGUE=0: conv -> ReLU -> pool through scratch memory
+    bool conv_first_tc = true;        // MANTLE_CONV_FIRST_TC=0: first layer on the CUDA-core kernels in every mode
+    bool gemm_3d_boxes = true;        // MANTLE_GEMM_NO3D set: one 2-D box per 32-wide chunk of an MN-major operand
+    int wgrad_taps = -1;              // MANTLE_WGRAD_TAPS: filter taps per CTA of the kernel gradient
+    int gemm_bn = -1;                 // MANTLE_GEMM_BN: DOT tile width (128 / 256)
+    int gemm_mt = -1;                 // MANTLE_GEMM_MT: 1 = 128-row tiles, 2 = 256-row tiles
+    int gemm_stages = -1;             // MANTLE_GEMM_STAGES: operand ring depth
+    int gemm_split_k = -1;            // MANTLE_GEMM_SPLITK: 0 = never split the reduction, n >= 2 = n slices
+};
+
 struct mtl_ctx {
     int device = 0;
+    mtl_tuning tune;
     cudaStream_t stream = nullptr;
     bool owns_stream = false;
     int math_mode = MTL_MATH_TF32X3;
@@ -26,6 +44,11 @@ struct mtl_ctx {
     void* ws2 = nullptr;  // second scratch block (mtl_workspace2)
     size_t ws2_bytes = 0;
     bool capturing = false;
+    // Instantiated graphs of this context that are alive.  They hold the scratch pointers that were
+    // current when they were captured, so while any is alive a scratch block that has to grow is not
+    // freed but parked on `retired` (freed when the last graph goes, or with the context).
+    int live_graphs = 0;
+    std::vector<void*> retired;
     int64_t launches = 0;
     int64_t launches_at_capture = 0;
     int32_t* dev_status = nullptr;  // one word written by bounded device waits
@@ -74,14 +97,33 @@ struct mtl_graph {
 };
 
 int32_t mtl_set_error(mtl_ctx* ctx, int32_t code, const char* fmt, ...);
+// The environment switches, read once per process on first use (contexts copy them at creation).
+const mtl_tuning& mtl_global_tuning();
 // Returns a device pointer to at least `bytes` of scratch, 256-byte aligned.
 int32_t mtl_workspace(mtl_ctx* ctx, size_t bytes, void** out);
 int32_t mtl_workspace2(mtl_ctx* ctx, size_t bytes, void** out);
 
-#define MTL_CHECK_CTX(ctx) \
-    do {                   \
-        if (!(ctx)) return MTL_ERR_INVALID; \
-    } while (0)
+// Makes the context's device current for the duration of an entry point and puts the caller's
+// device back afterwards, so that one host thread can drive contexts on different GPUs in turn.
+struct mtl_device_guard {
+    int prev = -1;
+    bool switched = false;
+    explicit mtl_device_guard(int device) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { cudaGetLastError(); prev = -1; }
+        if (prev != device) switched = cudaSetDevice(device) == cudaSuccess;
+    }
+    ~mtl_device_guard() {
+        if (switched && prev >= 0) cudaSetDevice(prev);
+    }
+    mtl_device_guard(const mtl_device_guard&) = delete;
+    mtl_device_guard& operator=(const mtl_device_guard&) = delete;
+};
+
+// First statement of every entry point that takes a context: rejects a null context and makes the
+// context's device current until the entry point returns.
+#define MTL_CHECK_CTX(ctx)                  \
+    if (!(ctx)) return MTL_ERR_INVALID;     \
+    mtl_device_guard mtl_guard__((ctx)->device)
 
 #define MTL_REQUIRE(ctx, cond, ...)                                  \
     do {                                                             \

@@ -9,32 +9,76 @@ int32_t mtl_set_error(mtl_ctx* ctx, int32_t code, const char* fmt, ...) {
         va_start(ap, fmt);
         vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
         va_end(ap);
-        const char* log = getenv("MANTLE_CUDA_LOG");
-        if (log && log[0] == '1') fprintf(stderr, "[mantle_cuda] error %d: %s\n", code, ctx->err);
+        if (ctx->tune.log_errors) fprintf(stderr, "[mantle_cuda] error %d: %s\n", code, ctx->err);
     }
     return code;
 }
 
+// Replaces a scratch block by a larger one.  The stream is drained first; the old block is freed
+// unless an instantiated graph of this context may still name it, in which case it is parked until
+// the last such graph is destroyed (a replayed step keeps using the block it was captured with).
+static int32_t grow_block(mtl_ctx* ctx, void** block, size_t* have, size_t bytes, const char* what) {
+    if (ctx->capturing)
+        return mtl_set_error(ctx, MTL_ERR_NOMEM,
+                             "%s of %zu bytes needed during stream capture but only %zu reserved; run the step "
+                             "once (or call mtl_ctx_reserve_workspace) before capturing it",
+                             what, bytes, *have);
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    size_t want = (bytes + (size_t)(1 << 20) - 1) & ~((size_t)(1 << 20) - 1);
+    void* fresh = nullptr;
+    if (*block && ctx->live_graphs == 0) {
+        MTL_CUDA(ctx, cudaFree(*block));
+        *block = nullptr;
+        *have = 0;
+    }
+    cudaError_t e = cudaMalloc(&fresh, want);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return mtl_set_error(ctx, MTL_ERR_NOMEM, "cudaMalloc of %zu %s bytes failed: %s", want, what,
+                             cudaGetErrorString(e));
+    }
+    if (*block) ctx->retired.push_back(*block);  // still named by a live graph
+    *block = fresh;
+    *have = want;
+    return MTL_OK;
+}
+
+void mtl_release_retired(mtl_ctx* ctx) {
+    if (ctx->live_graphs > 0) return;
+    for (void* p : ctx->retired) cudaFree(p);
+    ctx->retired.clear();
+}
+
+static int env_int(const char* name, int unset) {
+    const char* e = getenv(name);
+    return (e && *e) ? atoi(e) : unset;
+}
+
+static void read_tuning(mtl_tuning* t) {  // the only place the library reads its environment switches
+    const char* log = getenv("MANTLE_CUDA_LOG");
+    t->log_errors = log && log[0] == '1';
+    t->conv_channel_major = env_int("MANTLE_CONV_CHANNEL_MAJOR", 1) != 0;
+    t->conv_paired = env_int("MANTLE_CONV_PAIRED", 1) != 0;
+    t->conv_spread = env_int("MANTLE_CONV_SPREAD", 1) != 0;
+    t->conv_pool_epilogue = env_int("MANTLE_CONV_POOL_EPILOGUE", 1) != 0;
+    t->conv_first_tc = env_int("MANTLE_CONV_FIRST_TC", 1) != 0;
+    t->gemm_3d_boxes = getenv("MANTLE_GEMM_NO3D") == nullptr;
+    t->wgrad_taps = env_int("MANTLE_WGRAD_TAPS", -1);
+    t->gemm_bn = env_int("MANTLE_GEMM_BN", -1);
+    t->gemm_mt = env_int("MANTLE_GEMM_MT", -1);
+    t->gemm_stages = env_int("MANTLE_GEMM_STAGES", -1);
+    t->gemm_split_k = env_int("MANTLE_GEMM_SPLITK", -1);
+}
+
+const mtl_tuning& mtl_global_tuning() {
+    static const mtl_tuning t = [] { mtl_tuning v; read_tuning(&v); return v; }();
+    return t;
+}
+
 int32_t mtl_workspace(mtl_ctx* ctx, size_t bytes, void** out) {
     if (bytes > ctx->ws_bytes) {
-        if (ctx->capturing)
-            return mtl_set_error(ctx, MTL_ERR_NOMEM,
-                                 "workspace of %zu bytes needed during stream capture but only %zu "
-                                 "reserved; call mtl_ctx_reserve_workspace first",
-                                 bytes, ctx->ws_bytes);
-        // Growth is rare (first call of each shape): drain the stream, then replace the block.
-        MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        if (ctx->ws) MTL_CUDA(ctx, cudaFree(ctx->ws));
-        ctx->ws = nullptr;
-        ctx->ws_bytes = 0;
-        size_t want = (bytes + (size_t)(1 << 20) - 1) & ~((size_t)(1 << 20) - 1);
-        cudaError_t e = cudaMalloc(&ctx->ws, want);
-        if (e != cudaSuccess) {
-            cudaGetLastError();
-            return mtl_set_error(ctx, MTL_ERR_NOMEM, "cudaMalloc of %zu workspace bytes failed: %s",
-                                 want, cudaGetErrorString(e));
-        }
-        ctx->ws_bytes = want;
+        int32_t rc = grow_block(ctx, &ctx->ws, &ctx->ws_bytes, bytes, "workspace");
+        if (rc) return rc;
     }
     *out = ctx->ws;
     return MTL_OK;
@@ -44,23 +88,8 @@ int32_t mtl_workspace(mtl_ctx* ctx, size_t bytes, void** out) {
 // on the data they keep here; same growth rules.
 int32_t mtl_workspace2(mtl_ctx* ctx, size_t bytes, void** out) {
     if (bytes > ctx->ws2_bytes) {
-        if (ctx->capturing)
-            return mtl_set_error(ctx, MTL_ERR_NOMEM,
-                                 "scratch of %zu bytes needed during stream capture but only %zu reserved; run the "
-                                 "step once before capturing it",
-                                 bytes, ctx->ws2_bytes);
-        MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        if (ctx->ws2) MTL_CUDA(ctx, cudaFree(ctx->ws2));
-        ctx->ws2 = nullptr;
-        ctx->ws2_bytes = 0;
-        size_t want = (bytes + (size_t)(1 << 20) - 1) & ~((size_t)(1 << 20) - 1);
-        cudaError_t e = cudaMalloc(&ctx->ws2, want);
-        if (e != cudaSuccess) {
-            cudaGetLastError();
-            return mtl_set_error(ctx, MTL_ERR_NOMEM, "cudaMalloc of %zu scratch bytes failed: %s", want,
-                                 cudaGetErrorString(e));
-        }
-        ctx->ws2_bytes = want;
+        int32_t rc = grow_block(ctx, &ctx->ws2, &ctx->ws2_bytes, bytes, "scratch");
+        if (rc) return rc;
     }
     *out = ctx->ws2;
     return MTL_OK;
@@ -82,6 +111,7 @@ int32_t mtl_ctx_create(int32_t device, mtl_ctx** out) {
     if (cudaSetDevice(device) != cudaSuccess) return MTL_ERR_CUDA;
     mtl_ctx* ctx = new mtl_ctx();
     ctx->device = device;
+    ctx->tune = mtl_global_tuning();
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
         delete ctx;
         return MTL_ERR_CUDA;
@@ -129,6 +159,7 @@ int32_t mtl_ctx_destroy(mtl_ctx* ctx) {
     }
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->ws2) cudaFree(ctx->ws2);
+    for (void* p : ctx->retired) cudaFree(p);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -159,6 +190,15 @@ int32_t mtl_ctx_reserve_workspace(mtl_ctx* ctx, size_t bytes) {
     MTL_CHECK_CTX(ctx);
     void* p;
     return mtl_workspace(ctx, bytes, &p);
+}
+
+int32_t mtl_ctx_workspace_info(mtl_ctx* ctx, size_t* bytes, void** block, int32_t* live_graphs, int32_t* retired_blocks) {
+    MTL_CHECK_CTX(ctx);
+    if (bytes) *bytes = ctx->ws_bytes;
+    if (block) *block = ctx->ws;
+    if (live_graphs) *live_graphs = ctx->live_graphs;
+    if (retired_blocks) *retired_blocks = (int32_t)ctx->retired.size();
+    return MTL_OK;
 }
 
 int32_t mtl_sync(mtl_ctx* ctx) {
@@ -334,6 +374,7 @@ int32_t mtl_graph_end(mtl_ctx* ctx, mtl_graph** out) {
     mg->graph = g;
     mg->exec = exec;
     mg->launches = ctx->launches - ctx->launches_at_capture;
+    ctx->live_graphs += 1;
     // captured launches did not run: they are counted each time the graph is launched
     ctx->launches = ctx->launches_at_capture;
     *out = mg;
@@ -355,6 +396,8 @@ int32_t mtl_graph_destroy(mtl_ctx* ctx, mtl_graph* g) {
     if (g->exec) cudaGraphExecDestroy(g->exec);
     if (g->graph) cudaGraphDestroy(g->graph);
     delete g;
+    if (ctx->live_graphs > 0) ctx->live_graphs -= 1;
+    mtl_release_retired(ctx);
     return MTL_OK;
 }
 

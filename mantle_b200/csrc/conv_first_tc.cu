@@ -767,7 +767,7 @@ int32_t launch_first_wgrad(mtl_ctx* ctx, float* dW, float* db, const float* pg, 
 #define MTL_FIRST_TC_CASES(X_) X_(5, 5, 1, 28) X_(3, 3, 1, 28) X_(5, 5, 1, 32) X_(3, 3, 3, 32)
 
 bool mtl_conv_first_pool_tc_supported(const ConvGeom& g, const float* X, const float* pooled, const int32_t* idx) {
-    if (getenv("MANTLE_CONV_FIRST_TC") && atoi(getenv("MANTLE_CONV_FIRST_TC")) == 0) return false;
+    if (!mtl_global_tuning().conv_first_tc) return false;
     if (g.sh != 1 || g.sw != 1 || g.dh != 1 || g.dw != 1) return false;
     if (g.OH % 2 || g.OW % 2 || g.W % 4) return false;
     if ((reinterpret_cast<uintptr_t>(X) & 15u) || !pooled) return false;

@@ -924,7 +924,7 @@ int32_t launch_igemm(mtl_ctx* ctx, const CUtensorMap* maps, const ConvTcParams& 
 
 bool igemm_channel_major(const IgemmCall& c) {
     return c.Kout > 32 && (int64_t)c.N * c.OH * c.OW >= 1024 && (int64_t)c.N * c.Kout * c.OH * c.OW < (1ll << 31) &&
-           !(getenv("MANTLE_CONV_CHANNEL_MAJOR") && atoi(getenv("MANTLE_CONV_CHANNEL_MAJOR")) == 0);
+           mtl_global_tuning().conv_channel_major;
 }
 // Two taps per instruction when the layer has at most 64 output channels (see ConvTParams::paired).
 bool igemm_paired(const IgemmCall& c) {
@@ -932,13 +932,13 @@ bool igemm_paired(const IgemmCall& c) {
     // only when the reduction per tile is long enough for the main loop to be the longer of the two.
     const int paired_kblocks = c.R * ((c.S + 1) / 2) * ((c.Cin + 31) / 32);
     return igemm_channel_major(c) && c.Kout <= 64 && c.S >= 2 && c.OW + 1 <= 240 && paired_kblocks >= 32 &&
-           !(getenv("MANTLE_CONV_PAIRED") && atoi(getenv("MANTLE_CONV_PAIRED")) == 0);
+           mtl_global_tuning().conv_paired;
 }
 // At most 64 output channels without pairing: the channels are still spread over the four TMEM lane
 // quadrants (16 each) so that all four epilogue warps store, instead of two doing all of it.
 bool igemm_spread(const IgemmCall& c) {
     return igemm_channel_major(c) && c.Kout <= 64 && !igemm_paired(c) &&
-           !(getenv("MANTLE_CONV_SPREAD") && atoi(getenv("MANTLE_CONV_SPREAD")) == 0);
+           mtl_global_tuning().conv_spread;
 }
 // Floats of one re-laid-out copy of the weights.
 size_t igemm_weight_floats(const IgemmCall& c) {
@@ -1384,7 +1384,7 @@ bool mtl_conv_fwd_pool_tc_supported(const ConvGeom& g, const float* X, const flo
     c.N = g.N; c.Cin = g.C; c.IH = g.H; c.IW = g.W; c.Kout = g.K; c.OH = g.OH; c.OW = g.OW;
     c.R = g.R; c.S = g.S; c.ph = g.ph; c.pw = g.pw; c.wK = g.K; c.wC = g.C; c.flip = 0;
     return igemm_channel_major(c) && g.K > 64 && g.OW % 2 == 0 && g.OW <= 16 && g.OH % 2 == 0 &&
-           !(getenv("MANTLE_CONV_POOL_EPILOGUE") && atoi(getenv("MANTLE_CONV_POOL_EPILOGUE")) == 0);
+           mtl_global_tuning().conv_pool_epilogue;
 }
 
 int32_t mtl_conv_fwd_pool_tc(mtl_ctx* ctx, float* pooled, int32_t* idx, const float* X, const float* Wt,
@@ -1465,7 +1465,7 @@ int32_t wgrad_plan(mtl_ctx* ctx, const ConvGeom& g, int x3, WgradParams* pp, siz
         const double cost = (double)(stage_bytes + 16384) / ns;
         if (cost < best_cost * 0.999) { best_cost = cost; best_t = t; }
     }
-    if (const char* e = getenv("MANTLE_WGRAD_TAPS")) { int t = atoi(e); if (t >= 1 && t <= tmax) best_t = t; }
+    if (ctx->tune.wgrad_taps >= 1 && ctx->tune.wgrad_taps <= tmax) best_t = ctx->tune.wgrad_taps;
     p.T = best_t;
     p.ngroups = (RS + p.T - 1) / p.T;
     p.ktiles = (g.K + BM - 1) / BM;

@@ -46,7 +46,6 @@ struct GemmParams {
     int32_t* status;
     int a3d, b3d;     // MN-major operand fetched as one 3-D box {32, BK, chunks} instead of one box per chunk
     int stages;       // ring depth actually used (<= the configuration's maximum)
-    int skip_store;   // tuning aid: run the epilogue without writing C
 };
 
 // Tile order: groups of 16 tile-rows; inside a group the tile-column changes slowest so that
@@ -221,7 +220,7 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((acc + h) * BN + c * 32), r);
                 tmem_ld_wait();
                 const int n0 = n_base + c * 32;
-                if (m < p.M && !p.skip_store) {
+                if (m < p.M) {
                     if (vec_ok) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
@@ -357,7 +356,7 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
     if (!mtl_gemm_tc_supported(M, N, K, transA, transB, A, B, C))
         return mtl_set_error(ctx, MTL_ERR_UNSUPPORTED, "shape not supported by the tensor-core DOT kernel");
     int BN = N >= 256 ? 256 : 128;
-    if (const char* e = getenv("MANTLE_GEMM_BN")) { int b = atoi(e); if (b == 128 || (b == 256 && N >= 256)) BN = b; }
+    if (ctx->tune.gemm_bn == 128 || (ctx->tune.gemm_bn == 256 && N >= 256)) BN = ctx->tune.gemm_bn;
     // 256-row tiles when they do not cost waves: a 256 x 256 tile takes about 1.67x a 128 x 256 one
     int MT = 1;
     if (BN == 256 && M >= 256) {
@@ -365,7 +364,7 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
         const int64_t w1 = (t1 + ctx->sm_count - 1) / ctx->sm_count, w2 = (t2 + ctx->sm_count - 1) / ctx->sm_count;
         if ((double)w2 * 1.67 < (double)w1 && K >= 512) MT = 2;
     }
-    if (const char* e = getenv("MANTLE_GEMM_MT")) { int m = atoi(e); if (m == 1 || (m == 2 && BN == 256 && M >= 256)) MT = m; }
+    if (ctx->tune.gemm_mt == 1 || (ctx->tune.gemm_mt == 2 && BN == 256 && M >= 256)) MT = ctx->tune.gemm_mt;
     const int BMT = BM * MT;
     const float* a_src[2] = {A, nullptr};
     const float* b_src[2] = {B, nullptr};
@@ -389,7 +388,7 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
     // An MN-major operand stored [K, MN] can be fetched with ONE 3-D box per stage when MN is a
     // multiple of 32: dims {32, K, MN/32} with strides {row, 128 B}, box {32, BK, chunks}; its
     // shared-memory image [chunk][k][32] is exactly the chunked layout the descriptors expect.
-    const bool no3d = getenv("MANTLE_GEMM_NO3D") != nullptr;
+    const bool no3d = !ctx->tune.gemm_3d_boxes;
     const int a3d = transA && (M % 32 == 0) && !no3d, b3d = !transB && (N % 32 == 0) && !no3d;
     CUtensorMap maps[4];
     for (int i = 0; i < 2; ++i) {
@@ -424,9 +423,7 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
     p.stages = MT == 2 ? 3 : (BN == 256 ? 4 : 6);
     p.a3d = a3d;
     p.b3d = b3d;
-    p.skip_store = 0;
-    if (const char* e = getenv("MANTLE_GEMM_STAGES")) { int s = atoi(e); if (s >= 1 && s <= p.stages) p.stages = s; }
-    if (const char* e = getenv("MANTLE_GEMM_SKIP_STORE")) p.skip_store = atoi(e) != 0;
+    if (ctx->tune.gemm_stages >= 1 && ctx->tune.gemm_stages <= p.stages) p.stages = ctx->tune.gemm_stages;
     const bool a_mn = transA != 0, b_mn = transB == 0;
 #define MTL_DISPATCH(BN_, MT_)                                                                \
     if (a_mn && b_mn) return launch_gemm<BN_, true, true, MT_>(ctx, maps, p);                \

@@ -284,7 +284,9 @@ int32_t pool_bwd(mtl_ctx* ctx, float* dX, const float* ug, const float* X, const
     int64_t planes = (int64_t)g.N * g.C;
     int64_t n_out = planes * g.OH * g.OW;
     int64_t n_in = planes * g.H * g.W;
-    if (is_fast_2x2(g, idx ? (const void*)dX : (const void*)X, ug, idx) && (((uintptr_t)dX) & 15u) == 0) {
+    // the two-window kernel reads ug and the pooled values (relu_of) as float2: both need 8-byte alignment
+    if (is_fast_2x2(g, idx ? (const void*)dX : (const void*)X, ug, idx) && (((uintptr_t)dX) & 15u) == 0 &&
+        (((uintptr_t)relu_of) & 7u) == 0) {
         int64_t n_pairs = n_out / 2;
         int grid = mtl_grid_for(n_pairs, kBlock, ctx->sm_count, 8);
         if (idx)

@@ -77,6 +77,34 @@ __global__ void __launch_bounds__(kBlock) k_reduce_final(float* __restrict__ out
     if (threadIdx.x == 0) out[0] = divide ? t / scale : t;
 }
 
+// POW.backward for the exponent, pass 1: partial[block] = sum over a grid-strided slice of
+// x^a * log(x) * ug, with log(x) taken as 0 where it is infinite (x == 0), basics.mojo:359-376.
+__global__ void __launch_bounds__(kBlock) k_pow_exponent_partial(float* __restrict__ partial, const float* __restrict__ x,
+                                                                 const float* __restrict__ ug, int64_t n, float a) {
+    __shared__ float smem[32];
+    float acc = 0.0f;
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = tid; i < n; i += stride) {
+        const float v = x[i];
+        float lg = logf(v);
+        if (isinf(lg)) lg = 0.0f;
+        acc += powf(v, a) * lg * ug[i];
+    }
+    float t = block_reduce<R_SUM>(acc, smem);
+    if (threadIdx.x == 0) partial[blockIdx.x] = t;
+}
+
+// pass 2: one block folds the partials into the [1]-shaped gradient
+__global__ void __launch_bounds__(kBlock) k_pow_exponent_final(float* __restrict__ grad, const float* __restrict__ partial,
+                                                               int n_partial, int acc) {
+    __shared__ float smem[32];
+    float v = 0.0f;
+    for (int i = threadIdx.x; i < n_partial; i += blockDim.x) v += partial[i];
+    float t = block_reduce<R_SUM>(v, smem);
+    if (threadIdx.x == 0) grad[0] = acc ? grad[0] + t : t;
+}
+
 // Axis reduction, one thread per output element (short axes).
 template <int MODE>
 __global__ void __launch_bounds__(kBlock) k_reduce_axis_thread(float* __restrict__ out, const float* __restrict__ in,
@@ -271,6 +299,22 @@ int32_t mtl_reduce_bwd(mtl_ctx* ctx, int32_t op, float* grad, const float* ug, c
     return MTL_OK;
 }
 
+int32_t mtl_pow_bwd_exponent(mtl_ctx* ctx, float* grad, const float* ug, const float* in, int64_t n, float exponent,
+                             int32_t accumulate) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, grad && ug && in && n >= 1, "bad arguments to mtl_pow_bwd_exponent");
+    int blocks = mtl_grid_for(n, kBlock, ctx->sm_count, 4);
+    if (blocks > 1024) blocks = 1024;
+    void* ws;
+    int32_t rc = mtl_workspace(ctx, 1024 * sizeof(float), &ws);
+    if (rc) return rc;
+    k_pow_exponent_partial<<<blocks, kBlock, 0, ctx->stream>>>((float*)ws, in, ug, n, exponent);
+    MTL_LAUNCHED(ctx);
+    k_pow_exponent_final<<<1, kBlock, 0, ctx->stream>>>(grad, (const float*)ws, blocks, accumulate ? 1 : 0);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
 // ------------------------------------------------------------------ no-allocation variant ----
 // Scratch for mtl_reduce_all_static: one partial per block of the first pass.  It lives in the
 // library image, so every GPU that loads the library carries these 4 KB until the process exits.
@@ -279,7 +323,8 @@ static __device__ __align__(256) float g_static_reduce_partials[MTL_STATIC_REDUC
 
 // Device address of the array above for each device ordinal, resolved on first use.  In host code
 // the array's name only stands for the symbol; a kernel must be handed the address that
-// cudaGetSymbolAddress reports for the device that is current.
+// cudaGetSymbolAddress reports for the device that is current.  The cache is written without a
+// lock: two host threads that race on a device's first call both store the same address.
 static float* g_static_reduce_addr[64] = {nullptr};
 
 int32_t mtl_reduce_all_static(mtl_ctx* ctx, int32_t op, float* out, const float* in, int64_t n) {
@@ -293,8 +338,11 @@ int32_t mtl_reduce_all_static(mtl_ctx* ctx, int32_t op, float* out, const float*
     MTL_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "device ordinal %d out of range", ctx->device);
     float* partial = g_static_reduce_addr[ctx->device];
     if (!partial) {
-        // one-time set-up for this device: make it current, then ask where the array lives on it
-        MTL_CUDA(ctx, cudaSetDevice(ctx->device));
+        // one-time set-up for this device (it is current here: every entry point makes its context's
+        // device current and restores the caller's on return): ask where the array lives on it.
+        // The lookup may load the module, which must not happen inside a stream capture.
+        MTL_REQUIRE(ctx, !ctx->capturing,
+                    "the first mtl_reduce_all_static call on a device must come before stream capture starts");
         void* p = nullptr;
         MTL_CUDA(ctx, cudaGetSymbolAddress(&p, g_static_reduce_partials));
         partial = g_static_reduce_addr[ctx->device] = (float*)p;

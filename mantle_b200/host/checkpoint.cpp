@@ -1,3 +1,4 @@
+#include <algorithm>
 #include "checkpoint.hpp"
 
 #include <cstdio>
@@ -105,22 +106,31 @@ CheckpointInfo load_checkpoint(const std::string& path, Model& model, Adam* adam
         const uint8_t kind = d[off++];
         const uint32_t rank = get_u32(d, off);
         if (rank > (uint32_t)MTL_MAX_RANK) throw Error(MTL_ERR_INVALID, "checkpoint entry has rank above 8");
-        int64_t n = 1;
-        for (uint32_t i = 0; i < rank; ++i) n *= (int64_t)get_u32(d, off);
+        // Dimensions are untrusted: bound every partial product by the floats the rest of the file can
+        // still hold, so that neither the element count nor the byte count can wrap around.
+        uint64_t n = 1;
+        for (uint32_t i = 0; i < rank; ++i) {
+            const uint64_t dim = get_u32(d, off);
+            const uint64_t room = (uint64_t)(d.size() - std::min(off, d.size())) / 4;
+            if (dim != 0 && n > room / dim)
+                throw Error(MTL_ERR_INVALID, "checkpoint entry for symbol " + std::to_string(id) +
+                                                 " declares more elements than the file holds");
+            n *= dim;
+        }
         const size_t bytes = (size_t)n * 4;
-        if (off + bytes > d.size()) throw Error(MTL_ERR_INVALID, "checkpoint file is truncated");
+        if (off > d.size() || bytes > d.size() - off) throw Error(MTL_ERR_INVALID, "checkpoint file is truncated");
         host.resize((size_t)n);
         std::memcpy(host.data(), d.data() + off, bytes);
         off += bytes;
         if (e < n_tensors) {
             if (!model.has_tensor((int)id)) continue;  // unknown symbol: skipped, as the reference does
-            if (model.shape_of((int)id).num_elements() != n)
+            if ((uint64_t)model.shape_of((int)id).num_elements() != n)
                 throw Error(MTL_ERR_INVALID, "checkpoint entry for symbol " + std::to_string(id) + " has another size");
             model.set_tensor((int)id, host.data());
         } else if (adam) {
             for (size_t p = 0; p < tr.size(); ++p) {
                 if ((uint32_t)tr[p].id != id) continue;
-                if (tr[p].shape.num_elements() != n)
+                if ((uint64_t)tr[p].shape.num_elements() != n)
                     throw Error(MTL_ERR_INVALID, "optimizer entry for symbol " + std::to_string(id) + " has another size");
                 float* dst = (kind == kMomentum ? m.data() : v.data()) + toff[p];
                 std::memcpy(dst, host.data(), bytes);

@@ -506,11 +506,22 @@ static void unary_params(const Node& n, const std::map<int, float>& scalars, flo
     }
 }
 
+// A POW exponent that is trainable changes on the device with every optimizer step: read it back
+// (4 bytes, waits for the stream) before it is used as a kernel argument.  Literal exponents -- every
+// POW the reference's layers build -- keep the host copy taken at construction.
+void Model::refresh_pow_exponent(const Node& n) {
+    if (n.op != MTL_OP_POW || n.inputs.size() < 2 || !n.inputs[1].trainable) return;
+    float v = 0.0f;
+    check(mtl_d2h(ctx_, &v, T(n.inputs[1]), 4), "POW exponent read-back");
+    scalar_values_[n.inputs[1].id] = v;
+}
+
 // forward_op, ops.mojo:243-352
 void Model::forward_op(const Node& n) {
     const Symbol& out = n.outputs[0];
     const Symbol& t1 = n.inputs[0];
     float p0, p1;
+    refresh_pow_exponent(n);
     switch (n.op) {
         case MTL_OP_CONCAT: {   // dynamics.mojo:25-108
             std::vector<const float*> ins;
@@ -609,6 +620,7 @@ void Model::backward_op(const Node& n, int tensor_id) {
     float* grad = G(tj);
     int acc = acc_flag(tj);
     float p0, p1;
+    refresh_pow_exponent(n);
     switch (n.op) {
         case MTL_OP_CONCAT: {
             std::vector<int64_t> shapes;
@@ -629,7 +641,11 @@ void Model::backward_op(const Node& n, int tensor_id) {
                                  n.inputs[1].shape.rank, n.inputs[1].shape.dims, acc), "binary backward");
             break;
         case MTL_OP_POW:
-            if (tensor_id != 0) throw Error(MTL_ERR_UNSUPPORTED, "gradient of the POW exponent is not on the GPU path");
+            if (tensor_id == 1) {   // basics.mojo:359-376: the exponent's gradient is a sum over all elements
+                unary_params(n, scalar_values_, &p0, &p1);
+                check(mtl_pow_bwd_exponent(ctx_, grad, ug, T(t1), t1.shape.num_elements(), p0, acc), "POW exponent backward");
+                break;
+            }
             // fallthrough
         case MTL_OP_EXP: case MTL_OP_LOG: case MTL_OP_SIGMOID: case MTL_OP_RELU: case MTL_OP_LEAKYRELU:
         case MTL_OP_TANH: case MTL_OP_CLIP:
@@ -797,15 +813,13 @@ Adam::~Adam() {
     mtl_free(model_.ctx(), t_dev_);
 }
 
-void Adam::step() {
-    iter_ += 1;  // optim.mojo:96
-    int rc = mtl_adam_step(model_.ctx(), model_.params_flat(), model_.grads_flat(), m_, v_, model_.n_trainable(), lr_,
-                           beta1_, beta2_, eps_, iter_, grad_scale_);
-    if (rc != MTL_OK) throw Error(rc, std::string("Adam.step: ") + mtl_last_error(model_.ctx()));
-}
+// Both forms advance the SAME counter: the one in device memory is what the update reads (so that a
+// captured step can be replayed), iter_ is its host copy.  Eager steps and Trainer steps may
+// therefore be mixed on one optimizer without the bias corrections 1 - beta^t going stale.
+void Adam::step() { step_captured(); }  // optim.mojo:94-140
 
 void Adam::step_captured() {
-    iter_ += 1;
+    iter_ += 1;  // optim.mojo:96
     int rc = mtl_adam_step_dev(model_.ctx(), model_.params_flat(), model_.grads_flat(), m_, v_, model_.n_trainable(),
                                lr_, beta1_, beta2_, eps_, t_dev_, grad_scale_);
     if (rc != MTL_OK) throw Error(rc, std::string("Adam.step: ") + mtl_last_error(model_.ctx()));

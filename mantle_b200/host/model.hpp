@@ -93,6 +93,7 @@ class Model {
    private:
     void forward_op(const Node& n);
     void backward_op(const Node& n, int tensor_id);
+    void refresh_pow_exponent(const Node& n);
     float* T(const Symbol& s) const;
     float* G(const Symbol& s) const;
     int acc_flag(const Symbol& s);

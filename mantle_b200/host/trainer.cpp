@@ -41,6 +41,28 @@ Trainer::~Trainer() {
     mtl_host_free(model_.ctx(), own_loss_);
 }
 
+void Trainer::set_label_input(int input_index, int num_classes) {
+    const Graph& g = model_.graph();
+    if (input_index < 0 || (size_t)input_index >= g.inputs.size()) throw Error(MTL_ERR_INVALID, "no such graph input");
+    const TensorShape& s = g.inputs[(size_t)input_index].shape;
+    if (s.rank != 2 || s[1] != num_classes || num_classes < 1)
+        throw Error(MTL_ERR_INVALID, "a label input must be shaped [B, num_classes]");
+    if (stage_[0]) throw Error(MTL_ERR_INVALID, "declare label inputs before the first step");
+    label_classes_.resize(g.inputs.size(), 0);
+    label_classes_[(size_t)input_index] = num_classes;
+}
+
+int64_t Trainer::host_floats(size_t i) const {
+    const TensorShape& s = model_.graph().inputs[i].shape;
+    return (i < label_classes_.size() && label_classes_[i]) ? s[0] : s.num_elements();
+}
+
+int64_t Trainer::input_bytes_per_step() const {
+    int64_t n = 0;
+    for (size_t i = 0; i < model_.graph().inputs.size(); ++i) n += host_floats(i) * 4;
+    return n;
+}
+
 void Trainer::node_done_thunk(void* self, int node) { static_cast<Trainer*>(self)->node_done(node); }
 
 void Trainer::flush_bucket() {
@@ -94,7 +116,7 @@ void Trainer::stage_inputs(const std::vector<const float*>& host_inputs) {
     if (host_inputs.size() != g.inputs.size()) throw Error(MTL_ERR_INVALID, "wrong number of inputs");
     if (!stage_[0]) {
         stage_floats_ = 0;
-        for (auto& s : g.inputs) stage_floats_ += (s.shape.num_elements() + 63) / 64 * 64;
+        for (size_t i = 0; i < g.inputs.size(); ++i) stage_floats_ += (host_floats(i) + 63) / 64 * 64;
         for (int b = 0; b < 2; ++b)
             ck(ctx, mtl_malloc(ctx, (size_t)std::max<int64_t>(stage_floats_, 64) * 4, (void**)&stage_[b]), "input staging buffer");
     }
@@ -102,15 +124,19 @@ void Trainer::stage_inputs(const std::vector<const float*>& host_inputs) {
     ++staged_;
     int64_t off = 0;
     for (size_t i = 0; i < host_inputs.size(); ++i) {
-        const int64_t n = g.inputs[i].shape.num_elements();
+        const int64_t n = host_floats(i);
         ck(ctx, mtl_stage_h2d(ctx, slot, stage_[slot] + off, host_inputs[i], (size_t)n * 4), "input copy");
         off += (n + 63) / 64 * 64;
     }
     ck(ctx, mtl_stage_acquire(ctx, slot), "input copy wait");
     off = 0;
     for (size_t i = 0; i < host_inputs.size(); ++i) {
-        const int64_t n = g.inputs[i].shape.num_elements();
-        ck(ctx, mtl_copy_f32(ctx, model_.input_device((int)i), stage_[slot] + off, n, 0), "input placement");
+        const int64_t n = host_floats(i);
+        if (i < label_classes_.size() && label_classes_[i])
+            ck(ctx, mtl_one_hot_f32(ctx, model_.input_device((int)i), stage_[slot] + off, n, label_classes_[i]),
+               "one-hot targets");
+        else
+            ck(ctx, mtl_copy_f32(ctx, model_.input_device((int)i), stage_[slot] + off, n, 0), "input placement");
         off += (n + 63) / 64 * 64;
     }
     ck(ctx, mtl_stage_release(ctx, slot), "input staging release");

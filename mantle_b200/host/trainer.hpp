@@ -22,6 +22,14 @@ class Trainer {
     // Same, but only enqueues; the loss lands in *pinned_loss once the stream reaches it.
     void step_async(const std::vector<const float*>& host_inputs, float* pinned_loss);
 
+    // Declares graph input `input_index`, shaped [B, num_classes], as one-hot targets that the CALLER
+    // hands over as B fp32 class labels (what the reference's DataLoader yields, data/dataloader.mojo:135-189;
+    // examples/mnist.mojo:92-97 expands them on the host every batch).  step() / step_async() then copy
+    // B floats for this input and the one-hot rows are written on the device (mtl_one_hot_f32).
+    void set_label_input(int input_index, int num_classes);
+    // Bytes a step copies host -> device for its inputs (labels counted as labels).
+    int64_t input_bytes_per_step() const;
+
     int64_t steps() const { return steps_; }
     bool graph_active() const { return graph_ != nullptr; }
 
@@ -40,6 +48,8 @@ class Trainer {
     mtl_graph* graph_ = nullptr;
     float* stage_[2] = {nullptr, nullptr};  // device staging buffers for the inputs, used in turn
     int64_t stage_floats_ = 0;
+    std::vector<int> label_classes_;        // per graph input: 0 = dense tensor, C = labels expanded to C classes
+    int64_t host_floats(size_t input) const;  // floats the caller provides for an input
     int64_t staged_ = 0;
     float* own_loss_ = nullptr;         // pinned word used by step()
     int64_t steps_ = 0;

@@ -396,5 +396,13 @@ class Trainer:
         _ck(self.lib.mtlh_trainer_step_async(self.handle, len(ptrs), arr,
                                              C.cast(C.c_void_p(pinned_loss_ptr), C.POINTER(C.c_float))))
 
+    def set_label_input(self, input_index: int, num_classes: int):
+        """Input `input_index` ([B, num_classes] one-hot targets in the graph) is fed as B fp32 class labels;
+        the one-hot rows are built on the device (examples/mnist.mojo:92-97 builds them on the host)."""
+        _ck(self.lib.mtlh_trainer_set_label_input(self.handle, int(input_index), int(num_classes)))
+
+    def input_bytes_per_step(self) -> int:
+        return int(self.lib.mtlh_trainer_input_bytes(self.handle))
+
     def graph_active(self) -> bool:
         return bool(self.lib.mtlh_trainer_graph_active(self.handle))

@@ -173,6 +173,8 @@ class Context:
         if op in _BINARY:
             self._check(L.mtl_binary_bwd(h, op, tensor_id, grad.ptr, ug.ptr, t1.ptr, t2.ptr, len(t1.shape),
                                          _shape_arr(t1.shape), len(t2.shape), _shape_arr(t2.shape), acc))
+        elif op == OP.POW and tensor_id == 1:   # gradient of the [1]-shaped exponent
+            self._check(L.mtl_pow_bwd_exponent(h, grad.ptr, ug.ptr, t1.ptr, t1.size, float(attrs["exponent"]), acc))
         elif op in _UNARY:
             p0, p1 = _unary_params(op, attrs)
             self._check(L.mtl_unary_bwd(h, op, grad.ptr, ug.ptr, t1.ptr, t1.size, p0, p1, acc))

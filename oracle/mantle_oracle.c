@@ -23,6 +23,9 @@
  *
  * Build: see oracle/Makefile (gcc -O3 -march=x86-64-v3 -ffp-contract=off -fopenmp -shared).
  */
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <float.h>
 #include <math.h>
 #include <stdint.h>
@@ -39,6 +42,24 @@ static int64_t mo_numel(int rank, const int64_t* shape) {
     int64_t n = 1;
     for (int i = 0; i < rank; ++i) n *= shape[i];
     return n;
+}
+
+/* Host threads the parallel loops below use.  The reference forks one task per row block / image /
+ * channel on all host cores (std.algorithm.parallelize); launchers such as torch.distributed.run
+ * export OMP_NUM_THREADS=1 for multi-process jobs, so a timing harness sets the count explicitly. */
+MO_API void mo_set_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+MO_API int mo_max_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
 }
 
 /* broadcast_shapes, mantle/core/tensorutils.mojo:89-127. Returns rank, or -1 if incompatible. */
@@ -470,6 +491,19 @@ MO_API void mo_unary_bwd(int op, float* grad, const float* ug, const float* t, i
         }
         grad[i] += v;
     }
+}
+
+/* POW.backward for the exponent (basics.mojo:359-376): grad[0] += sum_i x_i^a * log(x_i) * ug_i with
+ * log(x) replaced by 0 where it is infinite (x == 0); the reference sums nelts-lane partial sums
+ * (host dependent), here the running fp32 sum in index order -- tolerance-compared. */
+MO_API void mo_pow_bwd_exponent(float* grad, const float* ug, const float* t, int64_t n, float a) {
+    float acc = grad[0];
+    for (int64_t i = 0; i < n; ++i) {
+        float lg = logf(t[i]);
+        if (isinf(lg)) lg = 0.0f;
+        acc += powf(t[i], a) * lg * ug[i];
+    }
+    grad[0] = acc;
 }
 
 /* ------------------------------------------------------------------ reductions ---------- */

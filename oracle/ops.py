@@ -50,6 +50,12 @@ def lib() -> C.CDLL:
     return _lib
 
 
+def set_threads(n: int) -> int:
+    """Sets the number of host threads the oracle's parallel loops use; returns the count in effect."""
+    lib().mo_set_threads(int(n))
+    return int(lib().mo_max_threads())
+
+
 def _f(a) -> np.ndarray:
     return np.ascontiguousarray(a, dtype=np.float32)
 
@@ -185,6 +191,14 @@ def unary_bwd(op, ug, x, p0=0.0, p1=0.0, grad=None):
     return grad
 
 
+def pow_bwd_exponent(ug, x, exponent, grad=None):
+    """POW.backward[tensor_id = 1], basics.mojo:359-376: the gradient of the [1]-shaped exponent."""
+    ug, x = _f(ug), _f(x)
+    grad = np.zeros((1,), np.float32) if grad is None else grad
+    lib().mo_pow_bwd_exponent(_p(grad), _p(ug), _p(x), C.c_int64(x.size), C.c_float(exponent))
+    return grad
+
+
 def _reduced_shape(shape, axis):
     if axis is None or axis < 0:
         return (1,)
@@ -270,6 +284,8 @@ def backward_op(tensor_id, op, ug, t1, t2=None, t3=None, grad=None, **attrs):
     """backward_op, ops.mojo:355-528: grad += local gradient; returns grad."""
     if op in _BINARY:
         return binary_bwd(op, tensor_id, ug, t1, t2, grad)
+    if op == OP.POW and tensor_id == 1:
+        return pow_bwd_exponent(ug, t1, float(attrs["exponent"]), grad)
     if op in _UNARY:
         p0, p1 = _unary_params(op, attrs)
         return unary_bwd(op, ug, t1, p0, p1, grad)

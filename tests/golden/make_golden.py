@@ -146,7 +146,7 @@ def make_models(rng):
     """100-step loss trajectories on one fixed batch, as test_models_{regression,sin_estimate,mnist}
     do (Adam, identical literal weights on both sides)."""
     out = {}
-    # regression: Linear(13 -> 1), MSE, batch 32 (BASELINE config 0 shape), lr 0.05
+    # regression: Linear(13 -> 1), MSE, batch 32 (the shape of examples/housing.mojo), lr 0.05
     x = rng.normal(0, 1, (32, 13)).astype(np.float32)
     w_true = rng.normal(0, 1, 13).astype(np.float32)
     y = (x @ w_true + 20.0 + rng.normal(0, 0.5, 32)).astype(np.float32).reshape(32, 1)
@@ -183,7 +183,7 @@ def make_models(rng):
         losses.append(loss.item())
     out["sin__losses"] = np.array(losses, np.float32)
 
-    # CNN (BASELINE config 2), cross entropy written as -sum(t * log_softmax) / N, lr 1e-3.
+    # CNN of examples/mnist.mojo, cross entropy written as -sum(t * log_softmax) / N, lr 1e-3.
     # test_models_mnist.mojo:229-295 sets every weight to 0.02: the gradient reaching the layers
     # below the classifier is then pure rounding noise (the class gradients of a sample sum to
     # zero), which Adam's normalisation amplifies, so seeded U(+-1/sqrt(fan_in)) weights are used.

@@ -140,3 +140,12 @@ def test_device_checkpoint_matches_restatement_and_resumes(ctx, tmp_path):
     bad.write_bytes(b"nope" * 8)
     with pytest.raises(Exception, match="bad magic"):
         host_api.load_checkpoint(bad, m3)
+    # a header whose dimensions multiply to more floats than the file holds (or wrap around 2^64)
+    # is refused as a corrupt file, not answered with an allocation failure
+    import struct
+    for dims in ((0x80000000, 0x80000000, 4), (0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF), (1 << 30,)):
+        blob = struct.pack("<IIIII", 0x42534C54, 1, 0, 1, 0) + struct.pack("<IBI", tr[0].id, 0, len(dims))
+        blob += b"".join(struct.pack("<I", d) for d in dims) + b"\0" * 64
+        bad.write_bytes(blob)
+        with pytest.raises(Exception, match="more elements than the file holds|truncated"):
+            host_api.load_checkpoint(bad, m3)

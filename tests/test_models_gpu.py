@@ -1,6 +1,6 @@
 """Model-level parity: the host mirror of Mantle's executor (Model.forward / backward, Adam.step)
 driving the CUDA kernels, against the CPU oracle's executor and the PyTorch fixtures, on the
-BASELINE configurations' graphs with identical injected weights.  Loss trajectories are held to
+graphs of the reference's three example networks with identical injected weights.  Loss trajectories are held to
 1e-3 relative (1e-4 for the two regression networks, as tests/python/test_models_*.mojo do)."""
 import numpy as np
 import pytest
@@ -114,7 +114,7 @@ def test_inference_outputs(ctx):
 
 
 def test_widened_cnn_uses_tensor_cores_and_matches(ctx):
-    """BASELINE config 4's network (Conv 1->64, 64->128, Linear 6272->10) at a small batch: conv2's
+    """The widened CNN (Conv 1->64, 64->128, Linear 6272->10) at a small batch: conv2's
     forward and input gradient run on the tcgen05 implicit-GEMM kernels."""
     B = 8
     build = lambda ns, gg: build_cnn(ns, gg, B, 64, 128)
@@ -227,3 +227,98 @@ def test_pipelined_steps_equal_synchronous_steps(ctx):
         results.append(np.asarray(losses, np.float32))
     assert np.array_equal(results[0], results[1]), results
     assert results[0][0] != results[0][-1]
+
+
+def test_workspace_growth_keeps_a_captured_step_valid(ctx):
+    """A captured step holds the scratch pointers it was recorded with.  Asking the context for a larger
+    workspace afterwards (another model, a large standalone operator) must not free that block while
+    the graph is alive: the replayed step has to produce the same losses as an undisturbed run."""
+    import ctypes as C
+    B = 8
+    build = lambda ns, gg: build_cnn(ns, gg, B, 64, 128)
+    rng = np.random.default_rng(21)
+    xs = rng.uniform(0, 1, (6, B, 1, 28, 28)).astype(np.float32)
+    ys = np.eye(10, dtype=np.float32)[rng.integers(0, 10, (6, B))]
+
+    def info():
+        nbytes, block, live, retired = C.c_size_t(), C.c_void_p(), C.c_int32(), C.c_int32()
+        ctx._check(ctx.lib.mtl_ctx_workspace_info(ctx.handle, C.byref(nbytes), C.byref(block), C.byref(live), C.byref(retired)))
+        return nbytes.value, block.value, live.value, retired.value
+
+    (g, m), _ = make_pair(ctx, build, seed=22)
+    tr = host_api.Trainer(m, host_api.Adam(m, lr=1e-3), use_graph=True)
+    want = [tr.step(xs[i], ys[i]) for i in range(6)]
+    tr.close()
+
+    (g, m), _ = make_pair(ctx, build, seed=22)
+    tr = host_api.Trainer(m, host_api.Adam(m, lr=1e-3), use_graph=True)
+    got = [tr.step(xs[i], ys[i]) for i in range(3)]
+    assert tr.graph_active()
+    size0, block0, live0, retired0 = info()
+    assert live0 >= 1
+    ctx.reserve_workspace(size0 + (64 << 20))           # forces a new, larger block
+    size1, block1, live1, retired1 = info()
+    assert size1 > size0 and live1 == live0 and retired1 == retired0 + 1, "the old block must be parked, not freed"
+    # scribble over the NEW block through a standalone operator, then go on replaying
+    a = ctx.array(rng.normal(0, 1, (512, 512)).astype(np.float32))
+    c = ctx.empty((512, 512))
+    ctx.forward_op(OP.DOT, c, a, a)
+    got += [tr.step(xs[i], ys[i]) for i in range(3, 6)]
+    assert got == want, "replay after workspace growth differs from the undisturbed run"
+    tr.close()
+    assert info()[3] == 0 or info()[2] > 0, "parked blocks are released with the last graph"
+    assert ctx.device_status() == 0
+
+
+def test_eager_and_trainer_steps_share_one_adam_counter(ctx):
+    """Two eager Adam.step() calls followed by two Trainer steps (the second one replayed from the
+    captured graph) must equal four steps of the reference's loop: the bias corrections 1 - beta^t
+    continue at t = 3, 4 instead of starting over."""
+    B = 8
+    build = lambda ns, gg: build_cnn(ns, gg, B)
+    rng = np.random.default_rng(31)
+    x = rng.uniform(0, 1, (B, 1, 28, 28)).astype(np.float32)
+    y = np.eye(10, dtype=np.float32)[rng.integers(0, 10, B)]
+    (g, m), (og, om) = make_pair(ctx, build, seed=32)
+    adam, oadam = host_api.Adam(m, lr=1e-2), oracle.Adam(om, lr=1e-2)
+    want = []
+    for _ in range(5):
+        want.append(om.forward(x, y)); oadam.zero_grad(); om.backward(); oadam.step()
+    got = []
+    for _ in range(2):
+        got.append(m.forward(x, y)); adam.zero_grad(); m.backward(); adam.step()
+    assert adam.iter == 2
+    tr = host_api.Trainer(m, adam, use_graph=True, fuse=False)
+    got += [tr.step(x, y) for _ in range(3)]
+    assert adam.iter == 5
+    tr.close()
+    assert_close(np.array(got, np.float32), np.array(want, np.float32), 1e-4, 1e-6, "mixed eager / Trainer steps")
+
+
+def test_trainer_builds_one_hot_targets_on_the_device(ctx):
+    """A Trainer fed fp32 class labels (what the reference's DataLoader yields) writes the one-hot rows
+    on the device; losses are bit-identical to feeding the one-hot rows examples/mnist.mojo:92-97
+    builds on the host, and the step copies B floats instead of B * 10 for that input."""
+    B = 16
+    build = lambda ns, gg: build_cnn(ns, gg, B)
+    rng = np.random.default_rng(41)
+    xs = rng.uniform(0, 1, (5, B, 1, 28, 28)).astype(np.float32)
+    labels = rng.integers(0, 10, (5, B)).astype(np.float32)
+    losses = {}
+    for on_device in (False, True):
+        (g, m), _ = make_pair(ctx, build, seed=42)
+        tr = host_api.Trainer(m, host_api.Adam(m, lr=1e-3), use_graph=True)
+        if on_device:
+            tr.set_label_input(1, 10)
+            assert tr.input_bytes_per_step() == (B * 784 + B) * 4
+            losses[on_device] = [tr.step(xs[i], labels[i]) for i in range(5)]
+        else:
+            assert tr.input_bytes_per_step() == (B * 784 + B * 10) * 4
+            losses[on_device] = [tr.step(xs[i], oracle.one_hot(labels[i], 10)) for i in range(5)]
+        tr.close()
+    assert losses[True] == losses[False]
+    (g, m), _ = make_pair(ctx, build, seed=42)
+    tr = host_api.Trainer(m, host_api.Adam(m, lr=1e-3), use_graph=False)
+    with pytest.raises(mb.MantleError):
+        tr.set_label_input(0, 10)      # the image input is not [B, 10]
+    tr.close()

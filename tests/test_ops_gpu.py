@@ -89,6 +89,48 @@ def test_unary_forward_backward(ctx):
                      oracle.backward_op(0, op, ug, x, **kw), what=name + " bwd overwrite")
 
 
+def test_fma_forward_and_three_backward_arms(ctx):
+    """FMA (basics.mojo:759-817) at the shape of tests/python/test_ops_torch.mojo:881 (an odd element
+    count, so the vector tail runs too) and on a tiny tensor."""
+    rng = np.random.default_rng(12)
+    for shape in ((87, 73, 84), (2, 3)):
+        t1, t2, t3, ug = (rng.normal(0, 1, shape).astype(np.float32) for _ in range(4))
+        got = run_fwd(ctx, OP.FMA, shape, t1, t2, t3)
+        assert_close(got, oracle.forward_op(OP.FMA, t1, t2, t3), 1e-5, 1e-6, "FMA forward")
+        # one fused multiply-add rounds once: never further than one ulp of the two-rounding product + sum
+        assert_close(got, (t1.astype(np.float64) * t2 + t3).astype(np.float32), 2e-7, 1e-7, "FMA forward vs float64")
+        init = rng.normal(0, 1, shape).astype(np.float32)
+        for tid in range(3):
+            want = oracle.backward_op(tid, OP.FMA, ug, t1, t2, t3, grad=init.copy())
+            assert_close(run_bwd(ctx, tid, OP.FMA, ug, t1, t2, t3, grad_shape=shape, init=init), want, what="FMA d%d" % tid)
+            assert_close(run_bwd(ctx, tid, OP.FMA, ug, t1, t2, t3, grad_shape=shape, init=init, accumulate=False),
+                         oracle.backward_op(tid, OP.FMA, ug, t1, t2, t3), what="FMA d%d overwrite" % tid)
+
+
+def test_pow_exponent_gradient(ctx):
+    """POW.backward for the exponent (basics.mojo:359-376): the reference's known answers
+    (test_backward.mojo:142-168) and seeded data with zeros in it (log(0) counts as 0)."""
+    ones = np.ones((2, 3), np.float32)
+    got = run_bwd(ctx, 1, OP.POW, ones, np.full((2, 3), 2, np.float32), grad_shape=(1,), exponent=2)
+    assert_close(got, np.array([24 * np.log(2.0)], np.float32))
+    got = run_bwd(ctx, 1, OP.POW, ones, np.zeros((2, 3), np.float32), grad_shape=(1,), exponent=0)
+    assert_close(got, np.zeros(1, np.float32))
+    rng = np.random.default_rng(13)
+    for n, a in ((1000, 2.0), (70001, 3.0), (7, 1.0)):
+        x = rng.uniform(0.1, 2.0, (n,)).astype(np.float32)
+        x[::17] = 0.0
+        ug = rng.normal(0, 1, (n,)).astype(np.float32)
+        want = (np.where(x > 0, x.astype(np.float64) ** a * np.log(np.maximum(x, 1e-30).astype(np.float64)), 0.0) * ug).sum()
+        init = np.array([0.25], np.float32)
+        got = run_bwd(ctx, 1, OP.POW, ug, x, grad_shape=(1,), init=init, exponent=a)
+        tol = 2e-5 * np.abs(np.where(x > 0, x.astype(np.float64) ** a * np.log(np.maximum(x, 1e-30)), 0.0) * ug).sum() + 1e-6
+        assert abs(float(got[0]) - (want + 0.25)) <= tol, (n, a, got, want)
+        ora = oracle.backward_op(1, OP.POW, ug, x, exponent=a, grad=init.copy())
+        assert abs(float(got[0]) - float(ora[0])) <= 2 * tol      # the oracle sums serially in fp32
+        got = run_bwd(ctx, 1, OP.POW, ug, x, grad_shape=(1,), init=init, accumulate=False, exponent=a)
+        assert abs(float(got[0]) - want) <= tol
+
+
 def test_relu_large_vectorised(ctx):
     rng = np.random.default_rng(3)
     x = rng.normal(0, 1, (8, 16, 28, 28)).astype(np.float32)

@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 
 import oracle
+from mantle_b200.models import build_cnn, build_regression, build_sin
 from oracle import OP, nn
 from helpers import assert_close, cases, golden
 
@@ -68,6 +69,29 @@ def test_unary_backward_kat():
     assert_close(oracle.forward_op(OP.RELU, t), np.array([[3, 3, 3], [0, 0, 0]], np.float32))
     assert_close(oracle.backward_op(0, OP.RELU, full((2, 3), 5), t), np.array([[5, 5, 5], [0, 0, 0]], np.float32))
     assert_close(oracle.backward_op(0, OP.SIGMOID, full((2, 3), 5), full((2, 3), 0)), full((2, 3), 1.25))
+
+
+def test_pow_exponent_backward_kat():
+    # test_backward.mojo:142-168: d(x^a)/da summed over the tensor; log(0) counts as 0
+    want = np.array([6 * 4 * math.log(2.0)], np.float32)
+    assert_close(oracle.backward_op(1, OP.POW, full((2, 3), 1), full((2, 3), 2), exponent=2), want)
+    assert_close(oracle.backward_op(1, OP.POW, full((2, 3), 1), full((2, 3), 0), exponent=0), np.zeros(1, np.float32))
+    assert_close(oracle.backward_op(0, OP.POW, full((2, 3), 1), full((2, 3), 0), exponent=0), full((2, 3), 0))
+    # accumulation into an existing gradient (ops.mojo:463)
+    g = np.array([1.5], np.float32)
+    oracle.backward_op(1, OP.POW, full((2, 3), 1), full((2, 3), 2), exponent=2, grad=g)
+    assert_close(g, want + 1.5)
+
+
+def test_fma_kat():
+    # tests/mojo/test_ops.mojo:256-270
+    assert_close(oracle.forward_op(OP.FMA, full((2, 3), 1), full((2, 3), 2), full((2, 3), 3)), full((2, 3), 5))
+    # tests/python/test_ops_torch.mojo:881-905 (torch: t1 * t2 + t3, upper gradient t1) at its shape
+    rng = np.random.default_rng(11)
+    t1, t2, t3 = (rng.uniform(0, 1, (87, 73, 84)).astype(np.float32) for _ in range(3))
+    assert_close(oracle.forward_op(OP.FMA, t1, t2, t3), t1 * t2 + t3, 1e-5, 1e-6)
+    for tid, want in enumerate((t1 * t2, t1 * t1, t1)):
+        assert_close(oracle.backward_op(tid, OP.FMA, t1, t1, t2, t3), want, 1e-6, 1e-7, "FMA grad %d" % tid)
 
 
 def test_reduce_backward_kat():
@@ -216,35 +240,6 @@ def _train(model, opt, inputs, steps):
         model.backward()
         opt.step()
     return np.array(losses, np.float32)
-
-
-def build_regression(ns, g):
-    x = g.input((32, 13))
-    y = g.input((32, 1))
-    out = ns.nn.Linear(g, x, 1)
-    g.out(out)
-    g.loss(ns.nn.MSELoss(g, out, y))
-
-
-def build_sin(ns, g):
-    x = g.input((32, 1))
-    y = g.input((32, 1))
-    h = ns.nn.ReLU(g, ns.nn.Linear(g, x, 32))
-    h = ns.nn.ReLU(g, ns.nn.Linear(g, h, 32))
-    out = ns.nn.Linear(g, h, 1)
-    g.out(out)
-    g.loss(ns.nn.MSELoss(g, out, y))
-
-
-def build_cnn(ns, g, B=4, c1=16, c2=32):
-    x = g.input((B, 1, 28, 28))
-    y = g.input((B, 10))
-    h = ns.nn.MaxPool2d(g, ns.nn.ReLU(g, ns.nn.Conv2d(g, x, c1, (5, 5), padding=(2, 2))), (2, 2))
-    h = ns.nn.MaxPool2d(g, ns.nn.ReLU(g, ns.nn.Conv2d(g, h, c2, (5, 5), padding=(2, 2))), (2, 2))
-    h = g.op(ns.OP.RESHAPE, h, shape=(B, c2 * 7 * 7))
-    out = ns.nn.Linear(g, h, 10)
-    g.out(out)
-    g.loss(ns.nn.CrossEntropyLoss(g, out, y))
 
 
 TRAJ = [("reg", build_regression, 0.05, 1e-4, 100), ("sin", build_sin, 0.01, 1e-4, 100),

@@ -1,0 +1,271 @@
+"""Parity at the sizes and in the arithmetic the throughput numbers are quoted on.
+
+* the widened CNN (Conv 1->64, Conv 64->128, Linear 6272->10) in plain TF32, 100 Adam steps at a
+  batch that reaches every kernel the full-size step uses (first-layer tensor-core kernels, pooled
+  epilogue, pooled-gradient scatter, thin classifier products), loss trajectory against the CPU
+  oracle at 1e-3 relative;
+* one step at the per-GPU batches of the data-parallel runs (2048, 1024, 512, 256 = global batch
+  2048 on 1, 2, 4, 8 GPUs): loss and all six parameter gradients, TF32 and 3xTF32, against the
+  oracle at 256 and against this backend's own fp32 CUDA-core path (which the other tests pin to the
+  oracle) at the larger ones;
+* the standalone operator shapes: DOT with M = N = K in {1024, 2048, 4096, 8192}, CONV2D on
+  [256, 64, 56, 56] with a 3x3 kernel, MAXPOOL2D 2x2 on [256, 64, 112, 112].  The operators are
+  separable over rows / images, so the oracle checks a slice of the full-size result.
+
+Tolerances (all written at the comparison): op outputs rtol 1e-4 / atol 1e-5 in 3xTF32 mode and
+rtol 5e-3 in plain TF32 mode, both relative to the scale of the output for data that is not unit
+scale; loss trajectories 1e-3 relative; max-pool values and indices exact."""
+import numpy as np
+import pytest
+
+import mantle_b200 as mb
+import oracle
+from mantle_b200 import OP, host_api
+from mantle_b200.models import GpuNs, build_cnn, cnn_batch_pool, cnn_weights
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _cnn(ctx_or_none, B, seed=43):
+    """The widened CNN at batch B on the GPU mirror (ctx given) or on the oracle (None)."""
+    if ctx_or_none is None:
+        g = oracle.Graph()
+        build_cnn(oracle, g, B, 64, 128)
+        m = oracle.Model(g)
+    else:
+        g = host_api.Graph()
+        build_cnn(GpuNs, g, B, 64, 128)
+        m = host_api.Model(ctx_or_none, g)
+    tr = [s for s in g.params() if s.trainable]
+    for s, w in zip(tr, cnn_weights([s.shape for s in tr], seed)):
+        m.set_tensor(s, w)
+    return g, m, tr
+
+
+def _norm_err(got, want):
+    want = np.asarray(want, np.float64)
+    return float(np.max(np.abs(np.asarray(got, np.float64) - want)) / max(np.max(np.abs(want)), 1e-30))
+
+
+# ------------------------------------------------------------------ trajectories ---------------
+
+@pytest.mark.parametrize("mode,name", [(mb.MATH_TF32, "tf32"), (mb.MATH_TF32X3, "tf32x3")])
+def test_widened_cnn_trajectory_100_steps(ctx, mode, name):
+    """Fresh batch every step from a seeded pool (as the benchmark draws them), through the Trainer
+    (chain fusion, captured step), against the oracle running the reference's loop
+    forward / zero_grad / backward / step on the same batches: 1e-3 relative on every loss."""
+    B, steps = 96, 100
+    x, _, y = cnn_batch_pool(4 * B, seed=7)
+    og, om, _ = _cnn(None, B)
+    oopt = oracle.Adam(om, lr=1e-3)
+    want = []
+    for i in range(steps):
+        lo = (i % 4) * B
+        want.append(om.forward(x[lo:lo + B], y[lo:lo + B]))
+        oopt.zero_grad(); om.backward(); oopt.step()
+    want = np.array(want, np.float32)
+
+    ctx.set_math_mode(mode)
+    try:
+        g, m, _ = _cnn(ctx, B)
+        opt = host_api.Adam(m, lr=1e-3)
+        tr = host_api.Trainer(m, opt, use_graph=True)
+        got = np.array([tr.step(x[(i % 4) * B:(i % 4) * B + B], y[(i % 4) * B:(i % 4) * B + B]) for i in range(steps)],
+                       np.float32)
+        tr.close(); opt.close(); m.close()
+    finally:
+        ctx.set_math_mode(mb.MATH_TF32X3)
+    assert ctx.device_status() == 0
+    dev = np.abs(got - want) / np.abs(want)
+    print("\n%s: max relative loss deviation over %d steps %.3e (at step %d); loss %.5f -> %.5f"
+          % (name, steps, dev.max(), int(dev.argmax()), want[0], want[-1]))
+    assert want[-1] < 0.9 * want[0], "the network must actually train for the comparison to mean anything"
+    assert_close(got, want, 1e-3, 0.0, "loss trajectory, %s" % name)
+
+
+# ------------------------------------------------------------------ one step at full batch -----
+
+def _one_step(ctx, mode, B, x, y, fusion):
+    ctx.set_math_mode(mode)
+    try:
+        g, m, tr = _cnn(ctx, B)
+        m.set_fusion(fusion)
+        loss = m.forward(x, y)
+        m.zero_grads()
+        m.backward()
+        grads = [m.grad(s) for s in tr]
+        m.close()
+    finally:
+        ctx.set_math_mode(mb.MATH_TF32X3)
+    return loss, grads
+
+
+@pytest.mark.parametrize("B", [256, 512, 1024, 2048])
+def test_one_step_at_the_per_gpu_batches(ctx, B):
+    """Loss and the six parameter gradients of one step, with the chain fusion the Trainer uses.
+    Reference values: the oracle at B = 256; at every B the fp32 CUDA-core path of this backend,
+    unfused (pinned to the oracle at 1e-4 by the model tests and compared with it here at 256)."""
+    x, _, y = cnn_batch_pool(B, seed=100 + B)
+    ref_loss, ref_grads = _one_step(ctx, mb.MATH_FP32, B, x, y, fusion=False)
+    if B == 256:
+        og, om, otr = _cnn(None, B)
+        oloss = om.forward(x, y)
+        om.zero_grads(); om.backward()
+        assert abs(ref_loss - oloss) <= 1e-5 * abs(oloss)
+        for i, s in enumerate(otr):
+            e = _norm_err(ref_grads[i], om.grad(s))
+            assert e < 2e-5, "fp32 path vs oracle, gradient %d: normalised max error %.3e" % (i, e)
+        ref_loss, ref_grads = oloss, [om.grad(s) for s in otr]
+    # rtol: 1e-4 (3xTF32) and 5e-3 (TF32), relative to the largest gradient element of the tensor
+    for mode, tol, ltol, name in ((mb.MATH_TF32X3, 1e-4, 1e-5, "tf32x3"), (mb.MATH_TF32, 5e-3, 1e-3, "tf32")):
+        loss, grads = _one_step(ctx, mode, B, x, y, fusion=True)
+        assert ctx.device_status() == 0
+        assert abs(loss - ref_loss) <= ltol * abs(ref_loss), "%s loss %r vs %r" % (name, loss, ref_loss)
+        errs = [_norm_err(g, r) for g, r in zip(grads, ref_grads)]
+        print("\nB=%d %s: loss %.6f (ref %.6f), normalised gradient errors %s" % (B, name, loss, ref_loss,
+                                                                                ["%.2e" % e for e in errs]))
+        for i, e in enumerate(errs):
+            assert e < tol, "%s, batch %d, gradient %d: normalised max error %.3e" % (name, B, i, e)
+
+
+# ------------------------------------------------------------------ standalone operator shapes -
+
+@pytest.mark.parametrize("S", [1024, 2048, 4096, 8192])
+def test_dot_square_full_size(ctx, S):
+    """All three products of DOT at M = N = K = S on N(0,1) data.  Rows of a product depend on one
+    row of its left operand only, so the oracle computes 48 rows (three bands) of each."""
+    rng = np.random.default_rng(S)
+    a = rng.normal(0, 1, (S, S)).astype(np.float32)
+    b = rng.normal(0, 1, (S, S)).astype(np.float32)
+    ug = rng.normal(0, 1, (S, S)).astype(np.float32)
+    rows = np.concatenate([np.arange(0, 16), np.arange(S // 2 - 8, S // 2 + 8), np.arange(S - 16, S)])
+    want_c = oracle.dot(a[rows], b)                                # C[rows]  = A[rows] . B
+    want_da = oracle.dot_transpose_t2(ug[rows], b)                 # dA[rows] = ug[rows] . B^T
+    want_db = oracle.dot_transpose_t1(np.ascontiguousarray(a[:, rows]), ug)   # dB[rows] = A[:, rows]^T . ug
+    scale = float(np.sqrt(S))
+    da_, db_, dug = ctx.array(a), ctx.array(b), ctx.array(ug)
+    out = ctx.empty((S, S))
+    for mode, rtol, name in ((mb.MATH_TF32X3, 1e-4, "tf32x3"), (mb.MATH_TF32, 5e-3, "tf32")):
+        ctx.set_math_mode(mode)
+        try:
+            ctx.forward_op(OP.DOT, out, da_, db_)
+            c = out.numpy()[rows]
+            ctx.backward_op(0, OP.DOT, dug, da_, db_, grad=out, accumulate=False)
+            dA = out.numpy()[rows]
+            ctx.backward_op(1, OP.DOT, dug, da_, db_, grad=out, accumulate=False)
+            dB = out.numpy()[rows]
+        finally:
+            ctx.set_math_mode(mb.MATH_TF32X3)
+        assert ctx.device_status() == 0
+        for got, want, what in ((c, want_c, "C"), (dA, want_da, "dA"), (dB, want_db, "dB")):
+            # element-wise: |got - want| <= rtol * |want| + rtol * sqrt(K) (the typical magnitude of an output)
+            assert_close(got, want, rtol, rtol * scale, "DOT %d %s %s" % (S, what, name))
+    for t in (da_, db_, dug, out):
+        t.free()
+
+
+def test_conv_full_size_sweep_shape(ctx):
+    """CONV2D on X [256, 64, 56, 56], W [64, 64, 3, 3], stride 1, pad 1, N(0,1) data.  Forward and
+    input gradient: images are independent, the oracle computes images 0..3 and 252..255.  Kernel and
+    bias gradients sum over all images: compared with this backend's fp32 CUDA-core path."""
+    rng = np.random.default_rng(56)
+    N, C, H, K = 256, 64, 56, 64
+    x = rng.normal(0, 1, (N, C, H, H)).astype(np.float32)
+    w = rng.normal(0, 1, (K, C, 3, 3)).astype(np.float32)
+    b = rng.normal(0, 1, (K,)).astype(np.float32)
+    ug = rng.normal(0, 1, (N, K, H, H)).astype(np.float32)
+    kw = dict(padding=(1, 1))
+    sl = np.r_[0:4, N - 4:N]
+    want_y = oracle.conv2d_fwd(x[sl], w, b, **kw)
+    want_dx = oracle.conv2d_bwd(0, ug[sl], x[sl], w, **kw)
+    dx_, dw_, db_, dug = ctx.array(x), ctx.array(w), ctx.array(b), ctx.array(ug)
+    y_, gx_, gw_, gb_ = ctx.empty(ug.shape), ctx.empty(x.shape), ctx.empty(w.shape), ctx.empty(b.shape)
+
+    def run(mode):
+        ctx.set_math_mode(mode)
+        try:
+            ctx.forward_op(OP.CONV2D, y_, dx_, dw_, db_, **kw)
+            ctx.backward_op(0, OP.CONV2D, dug, dx_, dw_, db_, grad=gx_, accumulate=False, **kw)
+            ctx.backward_op(1, OP.CONV2D, dug, dx_, dw_, db_, grad=gw_, accumulate=False, **kw)
+            ctx.backward_op(2, OP.CONV2D, dug, dx_, dw_, db_, grad=gb_, accumulate=False, **kw)
+            return y_.numpy()[sl], gx_.numpy()[sl], gw_.numpy(), gb_.numpy()
+        finally:
+            ctx.set_math_mode(mb.MATH_TF32X3)
+
+    _, _, ref_dw, ref_db = run(mb.MATH_FP32)
+    scale = float(np.sqrt(C * 9))   # typical magnitude of an output / input-gradient element
+    for mode, rtol, name in ((mb.MATH_TF32X3, 1e-4, "tf32x3"), (mb.MATH_TF32, 5e-3, "tf32")):
+        y, gx, gw, gb = run(mode)
+        assert ctx.device_status() == 0
+        assert_close(y, want_y, rtol, rtol * scale, "CONV2D forward " + name)
+        assert_close(gx, want_dx, rtol, rtol * scale, "CONV2D input gradient " + name)
+        e = _norm_err(gw, ref_dw)
+        assert e < rtol, "CONV2D kernel gradient %s: normalised max error %.3e" % (name, e)
+        assert_close(gb, ref_db, 1e-4, 1e-4 * float(np.abs(ref_db).max()), "CONV2D bias gradient " + name)
+    for t in (dx_, dw_, db_, dug, y_, gx_, gw_, gb_):
+        t.free()
+
+
+def test_maxpool_full_size_sweep_shape(ctx):
+    """MAXPOOL2D 2x2 / stride 2 on [256, 64, 112, 112]: values and int32 argmax of every window exact
+    (numpy's first-maximum argmax over the window in the reference's (kx, ky) scan order), the
+    backward scatter exact, and the oracle itself on the first and last image."""
+    rng = np.random.default_rng(112)
+    N, C, H = 256, 64, 112
+    x = rng.normal(0, 1, (N, C, H, H)).astype(np.float32)
+    win = x.reshape(N, C, H // 2, 2, H // 2, 2).transpose(0, 1, 2, 4, 3, 5).reshape(N, C, H // 2, H // 2, 4)
+    want_y = win.max(axis=-1)
+    k = win.argmax(axis=-1)                                   # 0..3 = (dy, dx) row-major: the scan order
+    oh, ow = np.meshgrid(np.arange(H // 2), np.arange(H // 2), indexing="ij")
+    want_idx = ((2 * oh + k // 2) * H + 2 * ow + k % 2).astype(np.int32)
+    dx_ = ctx.array(x)
+    y_, idx_ = ctx.empty(want_y.shape), ctx.empty(want_y.shape, np.int32)
+    ctx.forward_op(OP.MAXPOOL2D, y_, dx_, kernel_size=(2, 2), indices=idx_)
+    assert np.array_equal(y_.numpy(), want_y)
+    assert np.array_equal(idx_.numpy(), want_idx)
+    ug = rng.normal(0, 1, want_y.shape).astype(np.float32)
+    dug, g_ = ctx.array(ug), ctx.empty(x.shape)
+    want_g = np.zeros((N * C, H * H), np.float32)
+    np.put_along_axis(want_g, want_idx.reshape(N * C, -1), ug.reshape(N * C, -1), axis=1)
+    for use_idx in (True, False):
+        ctx.backward_op(0, OP.MAXPOOL2D, dug, dx_, grad=g_, accumulate=False, kernel_size=(2, 2),
+                        **({"indices": idx_} if use_idx else {}))
+        assert np.array_equal(g_.numpy().reshape(N * C, -1), want_g), "backward, indices=%s" % use_idx
+    for n in (0, N - 1):
+        oy, oi = oracle.maxpool2d_fwd(x[n:n + 1], (2, 2), return_indices=True)
+        assert np.array_equal(oy, want_y[n:n + 1]) and np.array_equal(oi, want_idx[n:n + 1])
+        assert np.array_equal(oracle.maxpool2d_bwd(ug[n:n + 1], x[n:n + 1], (2, 2)).reshape(C, -1),
+                              want_g[n * C:(n + 1) * C])
+    assert ctx.device_status() == 0
+    for t in (dx_, y_, idx_, dug, g_):
+        t.free()
+
+
+def test_conv_unit_scale_at_the_stated_tolerance(ctx):
+    """3xTF32 on unit-scale data at plain rtol 1e-4 / atol 1e-5, element-wise, for the three conv
+    products: conv2 of the widened CNN (reduction length 1600) and the 3x3 / 64-channel sweep layer
+    (576).  Inputs U(0,1) as the images are, weights U(+-1/sqrt(fan_in)) as the layers initialise
+    them, so that outputs are O(1)."""
+    rng = np.random.default_rng(5)
+    for (N, C, H, K, R, pad) in ((24, 64, 14, 128, 5, 2), (4, 64, 56, 64, 3, 1)):
+        fan = C * R * R
+        x = rng.uniform(0, 1, (N, C, H, H)).astype(np.float32)
+        w = (rng.uniform(-1, 1, (K, C, R, R)) / np.sqrt(fan)).astype(np.float32)
+        b = (rng.uniform(-1, 1, (K,)) / np.sqrt(fan)).astype(np.float32)
+        ug = (rng.uniform(-1, 1, (N, K, H, H)) / np.sqrt(K * R * R)).astype(np.float32)
+        kw = dict(padding=(pad, pad))
+        d = [ctx.array(t) for t in (x, w, b)]
+        dug = ctx.array(ug)
+        y_, gx_, gw_ = ctx.empty(ug.shape), ctx.empty(x.shape), ctx.empty(w.shape)
+        ctx.forward_op(OP.CONV2D, y_, *d, **kw)
+        ctx.backward_op(0, OP.CONV2D, dug, *d, grad=gx_, accumulate=False, **kw)
+        ctx.backward_op(1, OP.CONV2D, dug, *d, grad=gw_, accumulate=False, **kw)
+        assert_close(y_.numpy(), oracle.conv2d_fwd(x, w, b, **kw), 1e-4, 1e-5, "forward %s" % ((N, C, H, K, R),))
+        assert_close(gx_.numpy(), oracle.conv2d_bwd(0, ug, x, w, **kw), 1e-4, 1e-5, "input gradient")
+        # the kernel gradient sums N*OH*OW products of O(1/sqrt(K R S)) terms: O(1) as well
+        assert_close(gw_.numpy(), oracle.conv2d_bwd(1, ug, x, w, **kw), 1e-4, 1e-5 * max(1.0, np.sqrt(N * H * H / (K * R * R))),
+                     "kernel gradient")
+        for t in d + [dug, y_, gx_, gw_]:
+            t.free()
+    assert ctx.device_status() == 0
