@@ -427,6 +427,20 @@ MTL_API int32_t mtl_prof_enable(mtl_ctx* ctx, int32_t on);
 MTL_API int32_t mtl_prof_reset(mtl_ctx* ctx);
 MTL_API int32_t mtl_prof_get(mtl_ctx* ctx, int32_t which, float* total_ms, int32_t* launches);
 
+/* Caller-tagged ranges: per-node timing in the manner of PerfMetrics.start_forward_pass /
+ * end_forward_pass(pos) (mantle/autograd/perf_utils.mojo:60-112), measured on the device.  While
+ * profiling is enabled (mtl_prof_enable) and no capture is in progress, everything enqueued on the
+ * context between begin(tag) and end is bracketed by CUDA events; ranges do not nest.  A caller
+ * that runs a graph tags each node with its index.  mtl_prof_range_get waits for range i and
+ * returns its tag, duration and the number of kernels launched inside it; mtl_prof_dump writes one
+ * CSV line per tag (ranges, kernel launches, total / mean milliseconds, share) followed by the
+ * per-kernel totals of mtl_prof_get.  mtl_prof_reset clears ranges too. */
+MTL_API int32_t mtl_prof_range_begin(mtl_ctx* ctx, int32_t tag);
+MTL_API int32_t mtl_prof_range_end(mtl_ctx* ctx);
+MTL_API int32_t mtl_prof_range_count(mtl_ctx* ctx, int32_t* out_n);
+MTL_API int32_t mtl_prof_range_get(mtl_ctx* ctx, int32_t i, int32_t* tag, float* ms, int32_t* launches);
+MTL_API int32_t mtl_prof_dump(mtl_ctx* ctx, const char* path);
+
 /* ---------------------------------------------------------------- data parallel --------- */
 
 /* Data-parallel training is new in this backend (the reference is single-process).  One process
@@ -434,6 +448,18 @@ MTL_API int32_t mtl_prof_get(mtl_ctx* ctx, int32_t which, float* total_ms, int32
 #define MTL_DP_ID_BYTES 128
 MTL_API int32_t mtl_dp_get_unique_id(uint8_t* out_id /* host, MTL_DP_ID_BYTES */);
 MTL_API int32_t mtl_dp_init(mtl_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world);
+/* Joining waits for every rank, but not for ever: after MANTLE_DP_INIT_TIMEOUT_S seconds (default
+ * 120) mtl_dp_init returns MTL_ERR_COMM naming the rank that gave up, so that a rank that is late or
+ * never starts cannot hang the others' hosts.
+ *   mtl_dp_probe   the same rendezvous without a context, as a launcher's preflight: joins the group
+ *                  within timeout_ms and leaves it again; MTL_OK when every rank arrived in time.
+ *                  Use a fresh id for it (an id serves one group).
+ *   mtl_dp_status  polls the collective library for an asynchronous error (a peer that died, a
+ *                  network fault).  On error the communicator is aborted, MTL_ERR_COMM is returned and
+ *                  every later mtl_dp_allreduce_async / mtl_dp_broadcast fails fast with the same
+ *                  code.  Host-only and cheap: call it between steps, never inside a capture. */
+MTL_API int32_t mtl_dp_probe(const uint8_t* id, int32_t rank, int32_t world, int32_t timeout_ms);
+MTL_API int32_t mtl_dp_status(mtl_ctx* ctx);
 /* Sum-allreduce of `n` floats in place on a communication stream, ordered after everything
  * enqueued on the context's stream so far; overlaps with later launches until mtl_dp_wait. */
 MTL_API int32_t mtl_dp_allreduce_async(mtl_ctx* ctx, float* buf, int64_t n);

@@ -150,8 +150,15 @@ SIGNATURES = {
     "mtl_prof_enable": (_i32, [_vp, _i32]),
     "mtl_prof_reset": (_i32, [_vp]),
     "mtl_prof_get": (_i32, [_vp, _i32, C.POINTER(_f32), C.POINTER(_i32)]),
+    "mtl_prof_range_begin": (_i32, [_vp, _i32]),
+    "mtl_prof_range_end": (_i32, [_vp]),
+    "mtl_prof_range_count": (_i32, [_vp, C.POINTER(_i32)]),
+    "mtl_prof_range_get": (_i32, [_vp, _i32, C.POINTER(_i32), C.POINTER(_f32), C.POINTER(_i32)]),
+    "mtl_prof_dump": (_i32, [_vp, C.c_char_p]),
     "mtl_dp_get_unique_id": (_i32, [C.POINTER(C.c_uint8)]),
     "mtl_dp_init": (_i32, [_vp, C.POINTER(C.c_uint8), _i32, _i32]),
+    "mtl_dp_probe": (_i32, [C.POINTER(C.c_uint8), _i32, _i32, _i32]),
+    "mtl_dp_status": (_i32, [_vp]),
     "mtl_dp_allreduce_async": (_i32, [_vp, _vp, _i64]),
     "mtl_set_grads_ready_hook": (_i32, [_vp, _vp, _vp]),
     "mtl_dp_wait": (_i32, [_vp]),

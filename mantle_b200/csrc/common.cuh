@@ -69,6 +69,11 @@ struct mtl_ctx {
     // per-kernel event timing (mtl_prof_*)
     bool prof_on = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events[MTL_PROF_KERNELS];
+    // caller-tagged ranges (mtl_prof_range_*): everything enqueued between begin and end
+    struct prof_range { int32_t tag; cudaEvent_t e0, e1; int64_t launches; };
+    std::vector<prof_range> ranges;
+    bool range_open = false;
+    prof_range open_range = {0, nullptr, nullptr, 0};
 };
 
 // Brackets one launch of a profiled kernel with events when profiling is on.

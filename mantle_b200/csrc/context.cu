@@ -404,6 +404,16 @@ int32_t mtl_graph_destroy(mtl_ctx* ctx, mtl_graph* g) {
 // ------------------------------------------------------------------ kernel profile -------
 
 static void prof_clear(mtl_ctx* ctx) {
+    for (auto& r : ctx->ranges) {
+        cudaEventDestroy(r.e0);
+        cudaEventDestroy(r.e1);
+    }
+    ctx->ranges.clear();
+    if (ctx->range_open) {
+        cudaEventDestroy(ctx->open_range.e0);
+        cudaEventDestroy(ctx->open_range.e1);
+        ctx->range_open = false;
+    }
     for (int k = 0; k < MTL_PROF_KERNELS; ++k) {
         for (auto& ev : ctx->prof_events[k]) {
             cudaEventDestroy(ev.first);
@@ -438,6 +448,86 @@ int32_t mtl_prof_get(mtl_ctx* ctx, int32_t which, float* total_ms, int32_t* laun
     }
     *total_ms = sum;
     *launches = (int32_t)ctx->prof_events[which].size();
+    return MTL_OK;
+}
+
+int32_t mtl_prof_range_begin(mtl_ctx* ctx, int32_t tag) {
+    MTL_CHECK_CTX(ctx);
+    if (!ctx->prof_on || ctx->capturing) return MTL_OK;   // events cannot be read back from a captured step
+    MTL_REQUIRE(ctx, !ctx->range_open, "mtl_prof_range_begin: range %d is still open", ctx->open_range.tag);
+    mtl_ctx::prof_range r = {tag, nullptr, nullptr, ctx->launches};
+    MTL_CUDA(ctx, cudaEventCreate(&r.e0));
+    MTL_CUDA(ctx, cudaEventCreate(&r.e1));
+    MTL_CUDA(ctx, cudaEventRecord(r.e0, ctx->stream));
+    ctx->open_range = r;
+    ctx->range_open = true;
+    return MTL_OK;
+}
+
+int32_t mtl_prof_range_end(mtl_ctx* ctx) {
+    MTL_CHECK_CTX(ctx);
+    if (!ctx->range_open) return MTL_OK;
+    MTL_CUDA(ctx, cudaEventRecord(ctx->open_range.e1, ctx->stream));
+    ctx->open_range.launches = ctx->launches - ctx->open_range.launches;
+    ctx->ranges.push_back(ctx->open_range);
+    ctx->range_open = false;
+    return MTL_OK;
+}
+
+int32_t mtl_prof_range_count(mtl_ctx* ctx, int32_t* out_n) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, out_n, "null out pointer");
+    *out_n = (int32_t)ctx->ranges.size();
+    return MTL_OK;
+}
+
+int32_t mtl_prof_range_get(mtl_ctx* ctx, int32_t i, int32_t* tag, float* ms, int32_t* launches) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, i >= 0 && (size_t)i < ctx->ranges.size() && tag && ms && launches, "bad range query");
+    const auto& r = ctx->ranges[(size_t)i];
+    MTL_CUDA(ctx, cudaEventSynchronize(r.e1));
+    MTL_CUDA(ctx, cudaEventElapsedTime(ms, r.e0, r.e1));
+    *tag = r.tag;
+    *launches = (int32_t)r.launches;
+    return MTL_OK;
+}
+
+int32_t mtl_prof_dump(mtl_ctx* ctx, const char* path) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, path, "null path");
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    FILE* f = fopen(path, "w");
+    if (!f) return mtl_set_error(ctx, MTL_ERR_INVALID, "cannot open %s for writing", path);
+    // one line per tag in order of first appearance: ranges, kernel launches, total and mean device time
+    std::vector<int32_t> tags;
+    std::vector<double> total;
+    std::vector<int64_t> count, launches;
+    for (auto& r : ctx->ranges) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) { cudaGetLastError(); ms = 0.0f; }
+        size_t k = 0;
+        while (k < tags.size() && tags[k] != r.tag) ++k;
+        if (k == tags.size()) { tags.push_back(r.tag); total.push_back(0); count.push_back(0); launches.push_back(0); }
+        total[k] += ms; count[k] += 1; launches[k] += r.launches;
+    }
+    double sum = 0;
+    for (double t : total) sum += t;
+    fprintf(f, "tag,ranges,kernel_launches,total_ms,mean_ms,percent\n");
+    for (size_t k = 0; k < tags.size(); ++k)
+        fprintf(f, "%d,%lld,%lld,%.6f,%.6f,%.3f\n", tags[k], (long long)count[k], (long long)launches[k], total[k],
+                total[k] / (double)count[k], sum > 0 ? 100.0 * total[k] / sum : 0.0);
+    static const char* names[MTL_PROF_KERNELS] = {"dot_tc", "conv_igemm", "conv_wgrad", "conv_first"};
+    for (int k = 0; k < MTL_PROF_KERNELS; ++k) {
+        double t = 0;
+        for (auto& ev : ctx->prof_events[k]) {
+            float ms = 0.0f;
+            if (cudaEventElapsedTime(&ms, ev.first, ev.second) == cudaSuccess) t += ms; else cudaGetLastError();
+        }
+        if (!ctx->prof_events[k].empty())
+            fprintf(f, "kernel:%s,%zu,%zu,%.6f,%.6f,\n", names[k], ctx->prof_events[k].size(), ctx->prof_events[k].size(), t,
+                    t / (double)ctx->prof_events[k].size());
+    }
+    fclose(f);
     return MTL_OK;
 }
 

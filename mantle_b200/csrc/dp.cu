@@ -6,6 +6,12 @@
 #include <stdio.h>
 #include <dlfcn.h>
 
+#include <chrono>
+#include <condition_variable>
+#include <memory>
+#include <mutex>
+#include <thread>
+
 #include "common.cuh"
 
 namespace {
@@ -22,6 +28,8 @@ struct NcclApi {
     int (*GetUniqueId)(ncclUniqueId*) = nullptr;
     int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     int (*CommDestroy)(ncclComm_t) = nullptr;
+    int (*CommAbort)(ncclComm_t) = nullptr;
+    int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;
     int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     int (*Broadcast)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
@@ -51,6 +59,8 @@ bool load_nccl(char* why, size_t why_len) {
     MTL_SYM(GetUniqueId, "ncclGetUniqueId")
     MTL_SYM(CommInitRank, "ncclCommInitRank")
     MTL_SYM(CommDestroy, "ncclCommDestroy")
+    MTL_SYM(CommAbort, "ncclCommAbort")
+    MTL_SYM(CommGetAsyncError, "ncclCommGetAsyncError")
     MTL_SYM(AllReduce, "ncclAllReduce")
     MTL_SYM(Broadcast, "ncclBroadcast")
     MTL_SYM(GetErrorString, "ncclGetErrorString")
@@ -59,8 +69,65 @@ bool load_nccl(char* why, size_t why_len) {
     return true;
 }
 
+// Joining a group blocks inside the collective library until every rank has arrived; a rank that
+// never arrives would block the others for ever.  The join therefore runs on a helper thread and the
+// caller waits for it with a deadline.  When the deadline passes the caller gets MTL_ERR_COMM back;
+// the helper stays blocked in the library (it cannot be interrupted before a communicator exists) and
+// is left behind -- it holds no GPU work and ends with the process.  The shared record outlives
+// whichever side finishes last.
+struct JoinRecord {
+    std::mutex mu;
+    std::condition_variable cv;
+    bool finished = false, abandoned = false;
+    int result = 0;
+    ncclComm_t comm = nullptr;
+};
+
+int join_timeout_ms() {
+    const char* e = getenv("MANTLE_DP_INIT_TIMEOUT_S");
+    double s = (e && *e) ? atof(e) : 120.0;
+    if (s <= 0) s = 120.0;
+    return (int)(s * 1000.0);
+}
+
+// Returns MTL_OK with *comm set, or MTL_ERR_COMM with the reason in `why`.  `device` >= 0 is made
+// current on the helper thread (the library binds the communicator to the current device).
+int32_t join_with_deadline(const ncclUniqueId& uid, int rank, int world, int device, int timeout_ms, ncclComm_t* comm,
+                           char* why, size_t why_len) {
+    auto rec = std::make_shared<JoinRecord>();
+    std::thread([rec, uid, rank, world, device] {
+        if (device >= 0) cudaSetDevice(device);
+        ncclComm_t c = nullptr;
+        int r = g_nccl.CommInitRank(&c, world, uid, rank);
+        std::unique_lock<std::mutex> lk(rec->mu);
+        if (rec->abandoned) {            // the caller gave up: nobody will use this communicator
+            lk.unlock();
+            if (r == ncclSuccess && c) g_nccl.CommAbort(c);
+            return;
+        }
+        rec->result = r;
+        rec->comm = c;
+        rec->finished = true;
+        rec->cv.notify_all();
+    }).detach();
+    std::unique_lock<std::mutex> lk(rec->mu);
+    if (!rec->cv.wait_for(lk, std::chrono::milliseconds(timeout_ms), [&] { return rec->finished; })) {
+        rec->abandoned = true;
+        snprintf(why, why_len, "rank %d of %d: the group was not complete after %.1f s (a rank is late or missing); "
+                 "set MANTLE_DP_INIT_TIMEOUT_S to wait longer", rank, world, timeout_ms / 1000.0);
+        return MTL_ERR_COMM;
+    }
+    if (rec->result != ncclSuccess) {
+        snprintf(why, why_len, "ncclCommInitRank failed: %s", g_nccl.GetErrorString(rec->result));
+        return MTL_ERR_COMM;
+    }
+    *comm = rec->comm;
+    return MTL_OK;
+}
+
 struct DpState {
     ncclComm_t comm = nullptr;
+    bool failed = false;          // an asynchronous error was seen: the communicator is aborted, not destroyed
     int rank = 0, world = 1;
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t ready = nullptr;  // compute -> comm
@@ -123,10 +190,9 @@ int32_t mtl_dp_init(mtl_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world
         snprintf(buf, sizeof(buf), "%d", ctas);
         setenv("NCCL_MAX_CTAS", buf, 0);   // a value set by the user wins
     }
-    int r = g_nccl.CommInitRank(&st->comm, world, uid, rank);
-    if (r != ncclSuccess) {
+    if (join_with_deadline(uid, rank, world, ctx->device, join_timeout_ms(), &st->comm, why, sizeof(why)) != MTL_OK) {
         delete st;
-        return mtl_set_error(ctx, MTL_ERR_COMM, "ncclCommInitRank failed: %s", g_nccl.GetErrorString(r));
+        return mtl_set_error(ctx, MTL_ERR_COMM, "%s", why);
     }
     int prio_lo = 0, prio_hi = 0;
     cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
@@ -150,6 +216,7 @@ int32_t mtl_dp_allreduce_async(mtl_ctx* ctx, float* buf, int64_t n) {
     DpState* st = (DpState*)ctx->dp;
     MTL_REQUIRE(ctx, st, "mtl_dp_init has not been called");
     MTL_REQUIRE(ctx, buf && n >= 0, "bad arguments to mtl_dp_allreduce_async");
+    if (st->failed) return mtl_set_error(ctx, MTL_ERR_COMM, "the communicator failed earlier and was aborted");
     if (n == 0 || st->world == 1) return MTL_OK;
     MTL_CUDA(ctx, cudaEventRecord(st->ready, ctx->stream));
     MTL_CUDA(ctx, cudaStreamWaitEvent(st->comm_stream, st->ready, 0));
@@ -169,11 +236,46 @@ int32_t mtl_dp_wait(mtl_ctx* ctx) {
     return MTL_OK;
 }
 
+int32_t mtl_dp_status(mtl_ctx* ctx) {
+    MTL_CHECK_CTX(ctx);
+    DpState* st = (DpState*)ctx->dp;
+    MTL_REQUIRE(ctx, st, "mtl_dp_init has not been called");
+    if (st->failed) return mtl_set_error(ctx, MTL_ERR_COMM, "the communicator failed earlier and was aborted");
+    int async = ncclSuccess;
+    int r = g_nccl.CommGetAsyncError(st->comm, &async);
+    if (r == ncclSuccess && async == ncclSuccess) return MTL_OK;
+    const int bad = r != ncclSuccess ? r : async;
+    st->failed = true;
+    g_nccl.CommAbort(st->comm);   // frees the library's resources without waiting for the peers
+    st->comm = nullptr;
+    return mtl_set_error(ctx, MTL_ERR_COMM, "asynchronous collective error: %s; the communicator was aborted",
+                         g_nccl.GetErrorString(bad));
+}
+
+int32_t mtl_dp_probe(const uint8_t* id, int32_t rank, int32_t world, int32_t timeout_ms) {
+    if (!id || world < 1 || rank < 0 || rank >= world || timeout_ms <= 0) return MTL_ERR_INVALID;
+    char why[256];
+    if (!load_nccl(why, sizeof(why))) {
+        fprintf(stderr, "[mantle_cuda] %s\n", why);
+        return MTL_ERR_COMM;
+    }
+    ncclUniqueId uid;
+    memcpy(&uid, id, MTL_DP_ID_BYTES);
+    ncclComm_t comm = nullptr;
+    if (join_with_deadline(uid, rank, world, -1, timeout_ms, &comm, why, sizeof(why)) != MTL_OK) {
+        fprintf(stderr, "[mantle_cuda] %s\n", why);
+        return MTL_ERR_COMM;
+    }
+    g_nccl.CommDestroy(comm);
+    return MTL_OK;
+}
+
 int32_t mtl_dp_broadcast(mtl_ctx* ctx, float* buf, int64_t n, int32_t root) {
     MTL_CHECK_CTX(ctx);
     DpState* st = (DpState*)ctx->dp;
     MTL_REQUIRE(ctx, st, "mtl_dp_init has not been called");
     MTL_REQUIRE(ctx, buf && n >= 0 && root >= 0 && root < st->world, "bad arguments to mtl_dp_broadcast");
+    if (st->failed) return mtl_set_error(ctx, MTL_ERR_COMM, "the communicator failed earlier and was aborted");
     if (n == 0 || st->world == 1) return MTL_OK;
     MTL_NCCL(ctx, g_nccl.Broadcast(buf, buf, (size_t)n, ncclFloat32, root, st->comm, ctx->stream));
     return MTL_OK;

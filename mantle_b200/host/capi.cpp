@@ -346,6 +346,51 @@ MTLH_API int32_t mtlh_adam_get_state(void* a, int32_t which, float* host_out) {
     return guard([&] { static_cast<Adam*>(a)->get_state(which, host_out); });
 }
 
+MTLH_API int32_t mtlh_adam_set_state(void* a, int32_t which, const float* host_in) {
+    return guard([&] { static_cast<Adam*>(a)->set_state(which, host_in); });
+}
+MTLH_API int32_t mtlh_adam_set_iter(void* a, int32_t iter) {
+    return guard([&] { static_cast<Adam*>(a)->set_iter(iter); });
+}
+// Offsets (in floats) of the trainable parameters inside the flat spans, in get_trainable_parameters order.
+MTLH_API int32_t mtlh_model_trainable_offsets(void* m, int64_t* out, int32_t cap, int32_t* n) {
+    return guard([&] {
+        const auto& off = static_cast<Model*>(m)->trainable_offsets();
+        for (size_t i = 0; i < off.size() && (int32_t)i < cap; ++i) out[i] = off[i];
+        if (n) *n = (int32_t)off.size();
+    });
+}
+
+// PerfMetrics (perf_utils.mojo:60-236): per-node device time
+MTLH_API int32_t mtlh_model_set_profiling(void* m, int32_t on) {
+    return guard([&] { static_cast<Model*>(m)->set_profiling(on != 0); });
+}
+// per node i: out[4 * i + 0..3] = forward ms, backward ms, forward launches, backward launches (sums over the passes)
+MTLH_API int32_t mtlh_model_perf_metrics(void* m, double* out, int32_t n_nodes, int32_t* fwd_passes, int32_t* bwd_passes) {
+    return guard([&] {
+        int fp = 0, bp = 0;
+        auto v = static_cast<Model*>(m)->perf_metrics(&fp, &bp);
+        for (size_t i = 0; i < v.size() && (int32_t)i < n_nodes; ++i) {
+            out[4 * i] = v[i].fwd_ms; out[4 * i + 1] = v[i].bwd_ms;
+            out[4 * i + 2] = (double)v[i].fwd_launches; out[4 * i + 3] = (double)v[i].bwd_launches;
+        }
+        if (fwd_passes) *fwd_passes = fp;
+        if (bwd_passes) *bwd_passes = bp;
+    });
+}
+// print_forward_perf_metrics / print_backward_perf_metrics: the table as text (truncated to cap - 1 bytes)
+MTLH_API int32_t mtlh_model_perf_report(void* m, int32_t forward, const char* time_format, int32_t print_shape, char* buf,
+                                        int64_t cap) {
+    return guard([&] {
+        std::string r = static_cast<Model*>(m)->perf_report(forward != 0, time_format ? time_format : "ms", print_shape != 0);
+        if (cap > 0) {
+            size_t n = std::min<size_t>((size_t)cap - 1, r.size());
+            std::memcpy(buf, r.data(), n);
+            buf[n] = 0;
+        }
+    });
+}
+
 // ------------------------------------------------------------------ Trainer ---------------
 
 // save_checkpoint / save_checkpoint_with_optim (adam may be null), checkpoint.mojo:197-300

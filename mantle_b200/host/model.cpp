@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
+#include <cstdio>
 #include <cstring>
 
 namespace mantle {
@@ -353,9 +354,26 @@ void Model::inference(const std::vector<const float*>& in, const std::vector<flo
         check(mtl_d2h(ctx_, out[i], T(g_.outputs[i]), (size_t)g_.outputs[i].shape.num_elements() * 4), "output copy");
 }
 
+namespace {
+constexpr int32_t kBackwardTag = 1 << 20;  // profile tags: node index, plus this for the backward pass
+// Brackets one node's calls as a profiling range when the model profiles.
+struct NodeRange {
+    mtl_ctx* ctx;
+    bool on;
+    NodeRange(mtl_ctx* c, bool enabled, int32_t tag) : ctx(c), on(enabled) {
+        if (on) mtl_prof_range_begin(ctx, tag);
+    }
+    ~NodeRange() {
+        if (on) mtl_prof_range_end(ctx);
+    }
+};
+}  // namespace
+
 void Model::execute(int num_nodes) {
+    if (profiling_) ++fwd_passes_;
     for (int i = 0; i < num_nodes; ++i) {
         if (fusion_ && fwd_skip_[i]) continue;  // computed by the call at the head of its chain
+        NodeRange range(ctx_, profiling_, i);
         if (fusion_ && i == ce_head_) {
             const Symbol& x = g_.nodes[i].inputs[0];
             check(mtl_cross_entropy_fwd(ctx_, T(*g_.loss_out), T(x), T(g_.nodes[i + 6].inputs[0]), x.shape[0], x.shape[1],
@@ -364,6 +382,87 @@ void Model::execute(int num_nodes) {
         }
         forward_op(g_.nodes[i]);
     }
+}
+
+void Model::set_profiling(bool on) {
+    profiling_ = on;
+    fwd_passes_ = bwd_passes_ = 0;
+    check(mtl_prof_reset(ctx_), "profile reset");
+    check(mtl_prof_enable(ctx_, on ? 1 : 0), "profile switch");
+}
+
+std::vector<Model::NodePerf> Model::perf_metrics(int* fwd_passes, int* bwd_passes) {
+    std::vector<NodePerf> out(g_.nodes.size());
+    int32_t n = 0;
+    check(mtl_prof_range_count(ctx_, &n), "profile read-out");
+    for (int32_t r = 0; r < n; ++r) {
+        int32_t tag = 0, launches = 0;
+        float ms = 0.0f;
+        check(mtl_prof_range_get(ctx_, r, &tag, &ms, &launches), "profile read-out");
+        const bool bwd = tag >= kBackwardTag;
+        const int node = bwd ? tag - kBackwardTag : tag;
+        if (node < 0 || (size_t)node >= out.size()) continue;
+        if (bwd) { out[node].bwd_ms += ms; out[node].bwd_launches += launches; }
+        else     { out[node].fwd_ms += ms; out[node].fwd_launches += launches; }
+    }
+    if (fwd_passes) *fwd_passes = fwd_passes_;
+    if (bwd_passes) *bwd_passes = bwd_passes_;
+    return out;
+}
+
+static const char* op_name(int op) {
+    switch (op) {
+        case MTL_OP_ADD: return "ADD"; case MTL_OP_SUB: return "SUB"; case MTL_OP_MUL: return "MUL";
+        case MTL_OP_DIV: return "DIV"; case MTL_OP_EXP: return "EXP"; case MTL_OP_LOG: return "LOG";
+        case MTL_OP_POW: return "POW"; case MTL_OP_DOT: return "DOT"; case MTL_OP_SUM: return "SUM";
+        case MTL_OP_MEAN: return "MEAN"; case MTL_OP_MAX: return "MAX"; case MTL_OP_FLATTEN: return "FLATTEN";
+        case MTL_OP_RESHAPE: return "RESHAPE"; case MTL_OP_SIGMOID: return "SIGMOID"; case MTL_OP_RELU: return "RELU";
+        case MTL_OP_TANH: return "TANH"; case MTL_OP_CONV2D: return "CONV2D"; case MTL_OP_TRANSPOSE: return "TRANSPOSE";
+        case MTL_OP_MAXPOOL2D: return "MAXPOOL2D"; case MTL_OP_FMA: return "FMA"; case MTL_OP_CLIP: return "CLIP";
+        case MTL_OP_SQUEEZE: return "SQUEEZE"; case MTL_OP_UNSQUEEZE: return "UNSQUEEZE"; case MTL_OP_CONCAT: return "CONCAT";
+        case MTL_OP_SPLIT: return "SPLIT"; case MTL_OP_SLICE: return "SLICE"; case MTL_OP_LEAKYRELU: return "LEAKYRELU";
+        default: return "?";
+    }
+}
+
+std::string Model::perf_report(bool forward, const std::string& time_format, bool print_shape) {
+    int fp = 0, bp = 0;
+    std::vector<NodePerf> m = perf_metrics(&fp, &bp);
+    const int passes = std::max(1, forward ? fp : bp);
+    const double unit = time_format == "ns" ? 1e6 : time_format == "s" ? 1e-3 : 1.0;  // from milliseconds
+    double total = 0;
+    for (auto& v : m) total += forward ? v.fwd_ms : v.bwd_ms;
+    auto fit = [](std::string s, size_t n) { s.resize(std::max(n, s.size()), ' '); return s.substr(0, n); };
+    auto shape_str = [](const TensorShape& t) {
+        std::string r = "<";
+        for (int i = 0; i < t.rank; ++i) r += (i ? "x" : "") + std::to_string(t.dims[i]);
+        return r + ">";
+    };
+    char buf[64];
+    std::string out = forward ? "\n\nForward pass performance metrics:\n" : "\n\nBackward pass performance metrics:\n";
+    out += fit("Node", 5) + "| " + fit("Operator", 15) + "| " + fit("Time [" + time_format + "]", 20) + "| " +
+           fit("Percentage [%]", 20) + "| " + fit("Kernels", 8);
+    if (print_shape) out += "| Shape\t <out> = OP( <in1>, <in2>, <in3> )";
+    out += "\n";
+    for (size_t i = 0; i < m.size(); ++i) {
+        const double ms = forward ? m[i].fwd_ms : m[i].bwd_ms;
+        const int64_t launches = forward ? m[i].fwd_launches : m[i].bwd_launches;
+        snprintf(buf, sizeof(buf), "%.4f", ms / passes * unit);
+        out += fit(std::to_string(i), 5) + "| " + fit(op_name(g_.nodes[i].op), 15) + "| " + fit(buf, 20) + "| ";
+        snprintf(buf, sizeof(buf), "%.3f %%", total > 0 ? 100.0 * ms / total : 0.0);
+        out += fit(buf, 20) + "| " + fit(std::to_string(launches / passes), 8);
+        if (print_shape) {
+            out += "| ";
+            for (size_t j = 0; j < g_.nodes[i].outputs.size(); ++j) out += (j ? ", " : "") + fit(shape_str(g_.nodes[i].outputs[j].shape), 15);
+            out += " = OP(";
+            for (size_t j = 0; j < g_.nodes[i].inputs.size(); ++j) out += (j ? ", " : "") + fit(shape_str(g_.nodes[i].inputs[j].shape), 15);
+            out += ")";
+        }
+        out += "\n";
+    }
+    snprintf(buf, sizeof(buf), "%.6f", total / passes * unit);
+    out += std::string("\nTotal average ") + (forward ? "Forward" : "Backward") + " time: " + buf + " " + time_format + "\n";
+    return out;
 }
 
 void Model::set_fusion(bool on) {
@@ -707,6 +806,7 @@ void Model::backward_op(const Node& n, int tensor_id) {
 
 void Model::backward_enqueue() {
     if (!g_.loss_out) throw Error(MTL_ERR_INVALID, "no loss defined");
+    if (profiling_) ++bwd_passes_;
     grad_written_.clear();
     // fill(grads[loss], 1.0), model.mojo:180
     // (not needed when the loss chain runs as mtl_cross_entropy_bwd, which assumes the seed)
@@ -735,6 +835,7 @@ void Model::backward_enqueue() {
     for (int i = (int)g_.nodes.size() - 1; i >= 0; --i) {
         const Node& n = g_.nodes[i];
         bool node_reported = false;
+        NodeRange range(ctx_, profiling_ && !(fusion_ && (bwd_skip_[i] || bwd_pool_skip_[i])), kBackwardTag + i);
         if (fusion_ && (bwd_skip_[i] || bwd_pool_skip_[i])) {
             // a RELU whose backward its MAXPOOL2D performs, or a MAXPOOL2D whose backward the CONV2D at
             // the head of the chain performs from the pooled gradient

@@ -74,6 +74,21 @@ class Model {
     void set_fusion(bool on);
     bool fusion() const { return fusion_; }
 
+    // Per-node timing, the counterpart of PerfMetrics (mantle/autograd/perf_utils.mojo:60-236; the
+    // reference's hook, model.mojo:397-400, is an empty stub).  While on, every node's forward and
+    // backward call is bracketed on the device (mtl_prof_range_*), so a node's time is the device time
+    // of all kernels it launched -- not host time as in the reference.  Nodes a fused call computes
+    // (a RELU run by its CONV2D, the loss chain) show zero; their time is in the node at the head of
+    // the chain.  Steps replayed from a captured graph are not seen: profile with an eager Trainer
+    // (use_graph = false) or with Model.forward / backward.
+    void set_profiling(bool on);
+    struct NodePerf { double fwd_ms = 0, bwd_ms = 0; int64_t fwd_launches = 0, bwd_launches = 0; };
+    // Sums over the passes recorded since profiling was switched on; *passes = forward / backward passes seen.
+    std::vector<NodePerf> perf_metrics(int* fwd_passes, int* bwd_passes);
+    // The table PerfMetrics.print_perf_metrics prints: Node | Operator | Time [unit] | Percentage [%]
+    // (| shapes), time = mean per pass.  time_format: "ns", "ms" or "s".
+    std::string perf_report(bool forward, const std::string& time_format, bool print_shape);
+
     // flat trainable spans (device pointers) for the optimizer and the gradient exchange
     float* params_flat() const { return tensors_; }
     float* grads_flat() const { return grads_; }
@@ -117,6 +132,8 @@ class Model {
     bool overwrite_first_ = true;
     int n_inference_nodes_ = 0;
     bool fusion_ = false;
+    bool profiling_ = false;
+    int fwd_passes_ = 0, bwd_passes_ = 0;
     int ce_head_ = -1;                 // first of the nine nodes of a CrossEntropyLoss run as one call each way, or -1
     int ce_scale_sym_ = -1;            // id of the [1]-shaped literal the loss is scaled by
     std::vector<int> fwd_relu_of_;     // per node: the RELU node a CONV2D also computes, or -1

@@ -311,6 +311,25 @@ class Model:
         gradient of the RELU output are then never written (every other tensor is bit-identical)."""
         _ck(self.lib.mtlh_model_set_fusion(self.handle, int(on)))
 
+    def set_profiling(self, on: bool):
+        """Per-node device timing, the counterpart of PerfMetrics (mantle/autograd/perf_utils.mojo:60-236)."""
+        _ck(self.lib.mtlh_model_set_profiling(self.handle, int(on)))
+
+    def perf_metrics(self):
+        """(per-node array [n_nodes, 4]: forward ms, backward ms, forward launches, backward launches -- sums over
+        the recorded passes, forward passes, backward passes)."""
+        n = self.graph.counts()["nodes"]
+        out = np.zeros((n, 4), np.float64)
+        fp, bp = C.c_int32(), C.c_int32()
+        _ck(self.lib.mtlh_model_perf_metrics(self.handle, out.ctypes.data_as(C.POINTER(C.c_double)), n, C.byref(fp), C.byref(bp)))
+        return out, fp.value, bp.value
+
+    def perf_report(self, forward: bool = True, time_format: str = "ms", print_shape: bool = False) -> str:
+        """print_forward_perf_metrics / print_backward_perf_metrics as text."""
+        buf = C.create_string_buffer(1 << 16)
+        _ck(self.lib.mtlh_model_perf_report(self.handle, int(forward), time_format.encode(), int(print_shape), buf, len(buf)))
+        return buf.value.decode()
+
     def n_trainable(self) -> int:
         return int(self.lib.mtlh_model_n_trainable(self.handle))
 
@@ -340,6 +359,28 @@ class Adam:
     @property
     def iter(self) -> int:
         return self.lib.mtlh_adam_iter(self.handle)
+
+    def _offsets(self):
+        off, n = (C.c_int64 * 256)(), C.c_int32()
+        _ck(self.lib.mtlh_model_trainable_offsets(self.model.handle, off, 256, C.byref(n)))
+        return [off[i] for i in range(n.value)]
+
+    def state(self, which: int) -> np.ndarray:
+        """The flat momentum (which = 0) or rms (1) span, optim.mojo:142-149, as the device holds it."""
+        out = np.zeros(max(self.model.n_trainable(), 1), np.float32)
+        _ck(self.lib.mtlh_adam_get_state(self.handle, which, out.ctypes.data_as(C.POINTER(C.c_float))))
+        return out
+
+    def set_state(self, momentum: Sequence[np.ndarray], rms: Sequence[np.ndarray], iter: int):
+        """Loads momentum / rms tensors (one per trainable parameter, in get_trainable_parameters order) and
+        the step count, e.g. to continue from another implementation's state."""
+        offs = self._offsets()
+        for which, tensors in ((0, momentum), (1, rms)):
+            flat = np.zeros(max(self.model.n_trainable(), 1), np.float32)
+            for o, t in zip(offs, tensors):
+                flat[o:o + t.size] = np.asarray(t, np.float32).ravel()
+            _ck(self.lib.mtlh_adam_set_state(self.handle, which, flat.ctypes.data_as(C.POINTER(C.c_float))))
+        _ck(self.lib.mtlh_adam_set_iter(self.handle, int(iter)))
 
 
 def save_checkpoint(path: str, model: "Model", adam: "Adam" = None, iter: int = 0):

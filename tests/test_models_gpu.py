@@ -322,3 +322,43 @@ def test_trainer_builds_one_hot_targets_on_the_device(ctx):
     with pytest.raises(mb.MantleError):
         tr.set_label_input(0, 10)      # the image input is not [B, 10]
     tr.close()
+
+
+def test_per_node_profile_table(ctx, tmp_path):
+    """PerfMetrics (perf_utils.mojo:60-236) on device time: every node that launches kernels gets a forward
+    and a backward time, the shares add up to 100 %, fused-away nodes show zero, and the report has the
+    reference's columns."""
+    B = 8
+    (g, m), _ = make_pair(ctx, lambda ns, gg: build_cnn(ns, gg, B, 64, 128), seed=61)
+    rng = np.random.default_rng(62)
+    x = rng.uniform(0, 1, (B, 1, 28, 28)).astype(np.float32)
+    y = np.eye(10, dtype=np.float32)[rng.integers(0, 10, B)]
+    n_nodes = g.counts()["nodes"]
+    m.forward(x, y); m.zero_grads(); m.backward()          # unprofiled warm-up (workspace growth)
+    m.set_profiling(True)
+    for _ in range(3):
+        m.forward(x, y); m.zero_grads(); m.backward()
+    per_node, fp, bp = m.perf_metrics()
+    assert fp == 3 and bp == 3 and per_node.shape == (n_nodes, 4)
+    assert np.all(per_node[:, 0] > 0), "every node of the unfused graph launches at least one forward kernel"
+    assert np.all(per_node[:, 2] >= 3)
+    with_bwd = [i for i in range(n_nodes) if per_node[i, 3] > 0]
+    assert len(with_bwd) >= n_nodes // 2 and np.all(per_node[with_bwd, 1] > 0)
+    rep = m.perf_report(True, "ms", True)
+    assert "Forward pass performance metrics" in rep and "CONV2D" in rep and "Percentage [%]" in rep
+    assert rep.count("\n") >= n_nodes + 4 and "Total average Forward time" in rep
+    shares = [float(line.split("|")[3].replace("%", "")) for line in rep.splitlines() if line[:1].isdigit()]
+    assert len(shares) == n_nodes and abs(sum(shares) - 100.0) < 0.1
+    assert "Backward pass performance metrics" in m.perf_report(False, "ns", False)
+    dump = tmp_path / "prof.csv"
+    ctx._check(ctx.lib.mtl_prof_dump(ctx.handle, str(dump).encode()))
+    lines = dump.read_text().splitlines()
+    assert lines[0].startswith("tag,ranges,kernel_launches") and len(lines) >= 2 * n_nodes - 1
+    # with chain fusion the nodes a fused call computes show zero and the head of the chain carries the time
+    m.set_fusion(True)
+    m.set_profiling(True)
+    m.forward(x, y); m.zero_grads(); m.backward()
+    fused, _, _ = m.perf_metrics()
+    assert (fused[:, 2] == 0).sum() >= 4 and fused[0, 0] > 0
+    m.set_profiling(False)
+    m.close()

@@ -1,20 +1,20 @@
 """Parity at the sizes and in the arithmetic the throughput numbers are quoted on.
 
-* the widened CNN (Conv 1->64, Conv 64->128, Linear 6272->10) in plain TF32, 100 Adam steps at a
-  batch that reaches every kernel the full-size step uses (first-layer tensor-core kernels, pooled
-  epilogue, pooled-gradient scatter, thin classifier products), loss trajectory against the CPU
-  oracle at 1e-3 relative;
+* the widened CNN (Conv 1->64, Conv 64->128, Linear 6272->10) in plain TF32 and 3xTF32, 100 Adam
+  steps at a batch that reaches every kernel the full-size step uses (first-layer tensor-core
+  kernels, pooled epilogue, pooled-gradient scatter, thin classifier products) against the CPU
+  oracle: free-running (1e-3 for the first 10 steps, then within the measured drift of two fp32
+  implementations) and restarted from the oracle's state every 5th step (1e-3 on the loss);
 * one step at the per-GPU batches of the data-parallel runs (2048, 1024, 512, 256 = global batch
-  2048 on 1, 2, 4, 8 GPUs): loss and all six parameter gradients, TF32 and 3xTF32, against the
-  oracle at 256 and against this backend's own fp32 CUDA-core path (which the other tests pin to the
-  oracle) at the larger ones;
+  2048 on 1, 2, 4, 8 GPUs): loss and all six parameter gradients in fp32, 3xTF32 and TF32 against
+  float64, and against the oracle at 256;
 * the standalone operator shapes: DOT with M = N = K in {1024, 2048, 4096, 8192}, CONV2D on
   [256, 64, 56, 56] with a 3x3 kernel, MAXPOOL2D 2x2 on [256, 64, 112, 112].  The operators are
   separable over rows / images, so the oracle checks a slice of the full-size result.
 
 Tolerances (all written at the comparison): op outputs rtol 1e-4 / atol 1e-5 in 3xTF32 mode and
 rtol 5e-3 in plain TF32 mode, both relative to the scale of the output for data that is not unit
-scale; loss trajectories 1e-3 relative; max-pool values and indices exact."""
+scale; losses 1e-3 relative; max-pool values and indices exact."""
 import numpy as np
 import pytest
 
@@ -49,23 +49,54 @@ def _norm_err(got, want):
 
 
 # ------------------------------------------------------------------ trajectories ---------------
+#
+# Two correct fp32 implementations of this training run do NOT stay within 1e-3 of each other for 100
+# steps: PyTorch-CPU in float32 with four threads and with one thread (only the order of the sums
+# differs) are 1.9e-2 apart at step 99, float32 and float64 9.4e-2 (tests/golden/cnn_wide_b96_drift.json,
+# written by tests/golden/make_drift_fixture.py).  Adam divides every gradient element by its own running
+# magnitude, so rounding noise in elements whose true gradient is near zero becomes an update of the
+# full step size, and the difference feeds back.  The trajectory is therefore compared three ways:
+#   * free-running, first 10 steps: 1e-3 relative (the drift between float32 and float64 there is 6e-5);
+#   * free-running, all 100 steps: within 5x the float32-vs-float64 drift envelope of the fixture
+#     (never tighter than 2e-3) -- a wrong kernel shows up as a deviation of order one within a few steps;
+#   * restarted from the oracle's own state (parameters, Adam moments, step count) every 5th step, so
+#     that nothing accumulates: loss of that step at 1e-3 (plain TF32) / 2e-5 (3xTF32) relative, and the
+#     parameter update of the step against the oracle's.
+
+TRAJ_B, TRAJ_STEPS, TRAJ_EVERY = 96, 100, 5
+
+
+@pytest.fixture(scope="module")
+def oracle_run():
+    """The reference's loop on the CPU oracle: losses of 100 steps and its full state every 5th step."""
+    import json
+    from helpers import GOLDEN
+    B, steps = TRAJ_B, TRAJ_STEPS
+    x, _, y = cnn_batch_pool(4 * B, seed=7)
+    oracle.set_threads(len(__import__("os").sched_getaffinity(0)))
+    og, om, otr = _cnn(None, B)
+    oopt = oracle.Adam(om, lr=1e-3)
+    losses, snaps = [], {}
+    for i in range(steps):
+        if i % TRAJ_EVERY == 0:
+            snaps[i] = {"p": [om.tensor(s).copy() for s in otr], "m": [oopt.m[s.id].copy() for s in otr],
+                        "v": [oopt.v[s.id].copy() for s in otr]}
+        lo = (i % 4) * B
+        losses.append(om.forward(x[lo:lo + B], y[lo:lo + B]))
+        oopt.zero_grad(); om.backward(); oopt.step()
+        if i % TRAJ_EVERY == 0:
+            snaps[i]["p_next"] = [om.tensor(s).copy() for s in otr]
+    drift = json.loads((GOLDEN / "cnn_wide_b96_drift.json").read_text())
+    return {"x": x, "y": y, "losses": np.array(losses, np.float32), "snaps": snaps, "drift": drift}
+
 
 @pytest.mark.parametrize("mode,name", [(mb.MATH_TF32, "tf32"), (mb.MATH_TF32X3, "tf32x3")])
-def test_widened_cnn_trajectory_100_steps(ctx, mode, name):
+def test_widened_cnn_trajectory_100_steps(ctx, oracle_run, mode, name):
     """Fresh batch every step from a seeded pool (as the benchmark draws them), through the Trainer
     (chain fusion, captured step), against the oracle running the reference's loop
-    forward / zero_grad / backward / step on the same batches: 1e-3 relative on every loss."""
-    B, steps = 96, 100
-    x, _, y = cnn_batch_pool(4 * B, seed=7)
-    og, om, _ = _cnn(None, B)
-    oopt = oracle.Adam(om, lr=1e-3)
-    want = []
-    for i in range(steps):
-        lo = (i % 4) * B
-        want.append(om.forward(x[lo:lo + B], y[lo:lo + B]))
-        oopt.zero_grad(); om.backward(); oopt.step()
-    want = np.array(want, np.float32)
-
+    forward / zero_grad / backward / step on the same batches."""
+    B, steps = TRAJ_B, TRAJ_STEPS
+    x, y, want = oracle_run["x"], oracle_run["y"], oracle_run["losses"]
     ctx.set_math_mode(mode)
     try:
         g, m, _ = _cnn(ctx, B)
@@ -78,10 +109,54 @@ def test_widened_cnn_trajectory_100_steps(ctx, mode, name):
         ctx.set_math_mode(mb.MATH_TF32X3)
     assert ctx.device_status() == 0
     dev = np.abs(got - want) / np.abs(want)
-    print("\n%s: max relative loss deviation over %d steps %.3e (at step %d); loss %.5f -> %.5f"
-          % (name, steps, dev.max(), int(dev.argmax()), want[0], want[-1]))
+    f64 = np.array(oracle_run["drift"]["losses_f64"])
+    print("\n%s free-running: max relative deviation from the oracle %.2e in steps 0-9, %.2e in 0-29, %.2e in 0-99; "
+          "oracle vs float64 torch %.2e in 0-99; loss %.4f -> %.4f"
+          % (name, dev[:10].max(), dev[:30].max(), dev.max(), (np.abs(want - f64) / f64).max(), want[0], want[-1]))
     assert want[-1] < 0.9 * want[0], "the network must actually train for the comparison to mean anything"
-    assert_close(got, want, 1e-3, 0.0, "loss trajectory, %s" % name)
+    assert_close(got[:10], want[:10], 1e-3, 0.0, "loss, first 10 steps, %s" % name)
+    envelope = np.maximum.accumulate(np.array(oracle_run["drift"]["drift_f32_vs_f64"]))
+    bound = np.maximum(5.0 * envelope, 2e-3)
+    worst = int(np.argmax(dev / bound))
+    assert np.all(dev <= bound), "%s: deviation %.3e at step %d exceeds 5x the float32-vs-float64 drift (%.3e)" % (
+        name, dev[worst], worst, bound[worst])
+
+
+@pytest.mark.parametrize("mode,name,loss_tol", [(mb.MATH_TF32, "tf32", 1e-3), (mb.MATH_TF32X3, "tf32x3", 2e-5)])
+def test_widened_cnn_steps_from_the_oracle_state(ctx, oracle_run, mode, name, loss_tol):
+    """Twenty steps spread over the 100-step run (steps 0, 5, ..., 95), each started from the oracle's
+    parameters, Adam moments and step count: the loss of the step, and the update it applies."""
+    B = TRAJ_B
+    x, y, want = oracle_run["x"], oracle_run["y"], oracle_run["losses"]
+    ctx.set_math_mode(mode)
+    worst_loss, worst_upd = 0.0, [0.0] * 6
+    try:
+        g, m, trn = _cnn(ctx, B)
+        opt = host_api.Adam(m, lr=1e-3)
+        tr = host_api.Trainer(m, opt, use_graph=False)
+        for k, snap in sorted(oracle_run["snaps"].items()):
+            for s, p in zip(trn, snap["p"]):
+                m.set_tensor(s, p)
+            opt.set_state(snap["m"], snap["v"], k)
+            lo = (k % 4) * B
+            loss = tr.step(x[lo:lo + B], y[lo:lo + B])
+            worst_loss = max(worst_loss, abs(loss - want[k]) / abs(want[k]))
+            for i, s in enumerate(trn):
+                d_gpu = m.tensor(s).astype(np.float64) - snap["p"][i]
+                d_ora = snap["p_next"][i].astype(np.float64) - snap["p"][i]
+                worst_upd[i] = max(worst_upd[i], float(np.linalg.norm(d_gpu - d_ora) / max(np.linalg.norm(d_ora), 1e-30)))
+        assert opt.iter == 96
+        tr.close(); opt.close(); m.close()
+    finally:
+        ctx.set_math_mode(mb.MATH_TF32X3)
+    assert ctx.device_status() == 0
+    print("\n%s from the oracle's state: worst relative loss deviation %.2e; worst relative L2 difference of the "
+          "applied update per tensor %s" % (name, worst_loss, ["%.2e" % u for u in worst_upd]))
+    assert worst_loss <= loss_tol, "%s: loss deviates by %.3e" % (name, worst_loss)
+    # Adam turns each gradient element into a step of about lr * sign: elements whose gradient is within
+    # rounding noise of zero may step the other way, which bounds the agreement of the update (in L2)
+    for i, u in enumerate(worst_upd):
+        assert u <= (0.25 if mode == mb.MATH_TF32 else 0.1), "%s: update of tensor %d differs by %.3e (relative L2)" % (name, i, u)
 
 
 # ------------------------------------------------------------------ one step at full batch -----
@@ -101,32 +176,57 @@ def _one_step(ctx, mode, B, x, y, fusion):
     return loss, grads
 
 
+def _float64_step(B, x, y):
+    """Loss and parameter gradients of the same step in float64 (PyTorch on the CPU): the yardstick
+    both fp32 implementations are measured against."""
+    import torch
+    import torch.nn.functional as F
+    shapes = [(64, 1, 5, 5), (64,), (128, 64, 5, 5), (128,), (6272, 10), (10,)]
+    ws = [torch.tensor(w, dtype=torch.float64, requires_grad=True) for w in cnn_weights(shapes, 43)]
+    tx, ty = torch.tensor(x, dtype=torch.float64), torch.tensor(y, dtype=torch.float64)
+    h = F.max_pool2d(F.relu(F.conv2d(tx, ws[0], ws[1], padding=2)), 2)
+    h = F.max_pool2d(F.relu(F.conv2d(h, ws[2], ws[3], padding=2)), 2)
+    loss = -(ty * F.log_softmax(h.reshape(B, -1) @ ws[4] + ws[5], dim=1)).sum() / B
+    loss.backward()
+    return float(loss.detach()), [w.grad.numpy() for w in ws]
+
+
 @pytest.mark.parametrize("B", [256, 512, 1024, 2048])
 def test_one_step_at_the_per_gpu_batches(ctx, B):
-    """Loss and the six parameter gradients of one step, with the chain fusion the Trainer uses.
-    Reference values: the oracle at B = 256; at every B the fp32 CUDA-core path of this backend,
-    unfused (pinned to the oracle at 1e-4 by the model tests and compared with it here at 256)."""
+    """Loss and the six parameter gradients of one step at the batch one GPU sees when the global batch
+    of 2048 is split over 8, 4, 2 and 1 GPUs, with the chain fusion the Trainer uses.
+
+    The kernel gradients are sums of B * OH * OW terms of both signs (up to 1.6 million per element for
+    the first layer).  The reference adds them serially in fp32 (conv.mojo:340-393), and so does the
+    oracle: against float64 its own normalised error is 2e-4 / 5e-4 for the two kernel gradients at
+    B = 256.  Every implementation is therefore measured against float64, and the CUDA path must be at
+    least as close to it as the stated tolerance (1e-4 in 3xTF32, 5e-3 in plain TF32, relative to the
+    largest element of the gradient) -- and, at B = 256, agree with the oracle within the oracle's own
+    error plus that tolerance."""
     x, _, y = cnn_batch_pool(B, seed=100 + B)
-    ref_loss, ref_grads = _one_step(ctx, mb.MATH_FP32, B, x, y, fusion=False)
+    true_loss, true_grads = _float64_step(B, x, y)
+    ora_err = None
     if B == 256:
         og, om, otr = _cnn(None, B)
         oloss = om.forward(x, y)
         om.zero_grads(); om.backward()
-        assert abs(ref_loss - oloss) <= 1e-5 * abs(oloss)
-        for i, s in enumerate(otr):
-            e = _norm_err(ref_grads[i], om.grad(s))
-            assert e < 2e-5, "fp32 path vs oracle, gradient %d: normalised max error %.3e" % (i, e)
-        ref_loss, ref_grads = oloss, [om.grad(s) for s in otr]
-    # rtol: 1e-4 (3xTF32) and 5e-3 (TF32), relative to the largest gradient element of the tensor
-    for mode, tol, ltol, name in ((mb.MATH_TF32X3, 1e-4, 1e-5, "tf32x3"), (mb.MATH_TF32, 5e-3, 1e-3, "tf32")):
-        loss, grads = _one_step(ctx, mode, B, x, y, fusion=True)
+        ora_grads = [om.grad(s) for s in otr]
+        ora_err = [_norm_err(g, t) for g, t in zip(ora_grads, true_grads)]
+        print("\nB=256 oracle vs float64: loss %.3e, gradients %s" % (abs(oloss - true_loss) / true_loss, ["%.2e" % e for e in ora_err]))
+        assert abs(oloss - true_loss) <= 1e-5 * true_loss and max(ora_err) < 2e-3
+    for mode, tol, ltol, fusion, name in ((mb.MATH_FP32, 1e-4, 1e-5, False, "fp32"), (mb.MATH_TF32X3, 1e-4, 1e-5, True, "tf32x3"),
+                                          (mb.MATH_TF32, 5e-3, 1e-3, True, "tf32")):
+        loss, grads = _one_step(ctx, mode, B, x, y, fusion)
         assert ctx.device_status() == 0
-        assert abs(loss - ref_loss) <= ltol * abs(ref_loss), "%s loss %r vs %r" % (name, loss, ref_loss)
-        errs = [_norm_err(g, r) for g, r in zip(grads, ref_grads)]
-        print("\nB=%d %s: loss %.6f (ref %.6f), normalised gradient errors %s" % (B, name, loss, ref_loss,
-                                                                                ["%.2e" % e for e in errs]))
+        errs = [_norm_err(g, t) for g, t in zip(grads, true_grads)]
+        print("B=%d %s vs float64: loss %.3e, gradients %s" % (B, name, abs(loss - true_loss) / true_loss, ["%.2e" % e for e in errs]))
+        assert abs(loss - true_loss) <= ltol * true_loss, "%s loss %r vs %r" % (name, loss, true_loss)
         for i, e in enumerate(errs):
-            assert e < tol, "%s, batch %d, gradient %d: normalised max error %.3e" % (name, B, i, e)
+            assert e < tol, "%s, batch %d, gradient %d: normalised max error %.3e against float64" % (name, B, i, e)
+        if ora_err is not None:
+            for i, (g, o) in enumerate(zip(grads, ora_grads)):
+                e = _norm_err(g, o)
+                assert e < ora_err[i] + tol, "%s vs oracle, gradient %d: %.3e (oracle's own error %.3e)" % (name, i, e, ora_err[i])
 
 
 # ------------------------------------------------------------------ standalone operator shapes -
