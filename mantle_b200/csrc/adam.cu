@@ -25,7 +25,8 @@ __host__ __device__ __forceinline__ float pow_int(float b, int e) {
     return r;
 }
 
-__global__ void k_bump(int32_t* t) { *t += 1; }
+__global__ void k_bump(int32_t* t) {
+    mtl_pdl_sync(); *t += 1; }
 
 __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, const AdamK& k) {
     g *= k.gscale;
@@ -39,6 +40,7 @@ __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, 
 __global__ void __launch_bounds__(kBlock) k_adam(float* __restrict__ p, const float* __restrict__ g,
                                                  float* __restrict__ m, float* __restrict__ v, int64_t n,
                                                  AdamK k, int vec, const int32_t* __restrict__ t_dev) {
+    mtl_pdl_sync();
     if (t_dev) {
         int t = *t_dev;
         k.c1 = 1.0f - pow_int(k.b1, t);
@@ -74,7 +76,7 @@ static int32_t adam_launch(mtl_ctx* ctx, float* params, const float* grads, floa
     MTL_REQUIRE(ctx, n >= 0 && ((params && grads && m && v) || n == 0), "null pointer in mtl_adam_step");
     MTL_REQUIRE(ctx, t_dev || t >= 1, "Adam iteration count must be >= 1, got %d", t);
     if (t_dev) {
-        k_bump<<<1, 1, 0, ctx->stream>>>(t_dev);
+        mtl_launch_pdl(ctx, k_bump, dim3(1), dim3(1), (size_t)(0), t_dev);
         MTL_LAUNCHED(ctx);
     }
     if (n == 0) return MTL_OK;
@@ -88,7 +90,7 @@ static int32_t adam_launch(mtl_ctx* ctx, float* params, const float* grads, floa
     k.gscale = grad_scale;
     int vec = ((((uintptr_t)params) | ((uintptr_t)grads) | ((uintptr_t)m) | ((uintptr_t)v)) & 15u) == 0;
     int grid = mtl_grid_for((n + 3) / 4, kBlock, ctx->sm_count, 8);
-    k_adam<<<grid, kBlock, 0, ctx->stream>>>(params, grads, m, v, n, k, vec, t_dev);
+    mtl_launch_pdl(ctx, k_adam, dim3(grid), dim3(kBlock), (size_t)(0), params, grads, m, v, n, k, vec, t_dev);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }

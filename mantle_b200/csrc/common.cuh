@@ -29,6 +29,7 @@ struct mtl_tuning {
     int gemm_mt = -1;                 // MANTLE_GEMM_MT: 1 = 128-row tiles, 2 = 256-row tiles
     int gemm_stages = -1;             // MANTLE_GEMM_STAGES: operand ring depth
     int gemm_split_k = -1;            // MANTLE_GEMM_SPLITK: 0 = never split the reduction, n >= 2 = n slices
+    bool pdl = true;                  // MANTLE_PDL=0: plain stream order between the kernels of a step
 };
 
 struct mtl_ctx {
@@ -154,6 +155,38 @@ struct mtl_device_guard {
                                  cudaGetErrorString(e__), __FILE__, __LINE__);           \
         }                                                                                \
     } while (0)
+
+// ---- programmatic dependent launch ---------------------------------------------------------
+// A training step at small batches is a chain of short kernels, and the gap between two of them
+// (the first one draining, the second one being scheduled and setting itself up) is paid two dozen
+// times per step.  Kernels launched through mtl_launch_pdl may be scheduled while their predecessor
+// in the stream is still running; each of them calls mtl_pdl_sync() before it touches global
+// memory, which (1) waits until the predecessor has completed and its writes are visible and
+// (2) lets the successor be scheduled in turn.  What overlaps is therefore only a kernel's set-up
+// (barrier initialisation, tensor-memory allocation, index arithmetic) and the scheduling itself;
+// the order of all memory effects is the stream order, also inside a captured graph.
+// EVERY kernel launched this way must call mtl_pdl_sync() before its first global access.
+#ifdef __CUDACC__
+__device__ __forceinline__ void mtl_pdl_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... Params, typename... Args>
+inline void mtl_launch_pdl(mtl_ctx* ctx, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->tune.pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);  // errors surface through MTL_LAUNCHED
+}
+#endif
 
 static inline int64_t mtl_numel(int32_t rank, const int64_t* shape) {
     int64_t n = 1;

@@ -68,6 +68,7 @@ static void read_tuning(mtl_tuning* t) {  // the only place the library reads it
     t->gemm_mt = env_int("MANTLE_GEMM_MT", -1);
     t->gemm_stages = env_int("MANTLE_GEMM_STAGES", -1);
     t->gemm_split_k = env_int("MANTLE_GEMM_SPLITK", -1);
+    t->pdl = env_int("MANTLE_PDL", 1) != 0;
 }
 
 const mtl_tuning& mtl_global_tuning() {

@@ -154,6 +154,7 @@ k_conv_first_pool_tc(const __grid_constant__ CUtensorMap mapX, FirstParams p) {
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
+    mtl_pdl_sync();   // the weights read below come from the previous step's optimizer kernel
     // weight tile: k-block b holds W in the rows of pixel set b and zeros in the other 64 rows
     for (int i = threadIdx.x; i < 2 * 128 * 32; i += kThreadsF) {
         const int kb = i >> 12, row = (i >> 5) & 127, k = i & 31;
@@ -396,7 +397,7 @@ int32_t launch_first(mtl_ctx* ctx, float* pooled, int32_t* idx, float* pooled_cl
     if (gx > p.tiles) gx = p.tiles;
     {
         mtl_prof_scope prof(ctx, MTL_PROF_CONV_FIRST);
-        kern<<<dim3(gx, kgroups), kThreadsF, Cfg::SMEM_BYTES, ctx->stream>>>(tm, p);
+        mtl_launch_pdl(ctx, kern, dim3(dim3(gx, kgroups)), dim3(kThreadsF), (size_t)(Cfg::SMEM_BYTES), tm, p);
     }
     MTL_LAUNCHED(ctx);
     return MTL_OK;
@@ -500,6 +501,7 @@ k_conv_first_wgrad_tc(const __grid_constant__ CUtensorMap mapX, FirstWgradParams
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    mtl_pdl_sync();   // everything above touched only shared / tensor memory
 
     if (warp == kWBuildWarps) {
         // ---------------------------------------------------------------- TMA producer
@@ -701,6 +703,7 @@ k_conv_first_wgrad_tc(const __grid_constant__ CUtensorMap mapX, FirstWgradParams
 __global__ void __launch_bounds__(256) k_first_wgrad_reduce(float* __restrict__ dW, float* __restrict__ db,
                                                             const float* __restrict__ part, int K, int CRS, int nparts,
                                                             int acc_dw, int acc_db) {
+    mtl_pdl_sync();
     __shared__ float sm[8][33];
     const int ch = blockIdx.x, col = threadIdx.x & 31, slice = threadIdx.x >> 5;
     float s = 0.0f;
@@ -754,10 +757,10 @@ int32_t launch_first_wgrad(mtl_ctx* ctx, float* dW, float* db, const float* pg, 
     MTL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     {
         mtl_prof_scope prof(ctx, MTL_PROF_CONV_FIRST);
-        kern<<<dim3(gx, kgroups), kThreadsW, Cfg::SMEM_BYTES, ctx->stream>>>(tm, p);
+        mtl_launch_pdl(ctx, kern, dim3(dim3(gx, kgroups)), dim3(kThreadsW), (size_t)(Cfg::SMEM_BYTES), tm, p);
     }
     MTL_LAUNCHED(ctx);
-    k_first_wgrad_reduce<<<g.K, 256, 0, ctx->stream>>>(dW, db, p.part, g.K, Cfg::CRS, gx, acc_dw, acc_db);
+    mtl_launch_pdl(ctx, k_first_wgrad_reduce, dim3(g.K), dim3(256), (size_t)(0), dW, db, p.part, g.K, Cfg::CRS, gx, acc_dw, acc_db);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }

@@ -93,6 +93,7 @@ k_conv_igemm(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ 
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    mtl_pdl_sync();   // everything above touched only shared / tensor memory
 
     if (warp == 0) {
         if (lane == 0) {
@@ -228,6 +229,7 @@ template <bool SPLIT>
 __global__ void __launch_bounds__(256) k_nchw_to_nhwc(float* __restrict__ hi, float* __restrict__ lo,
                                                       const float* __restrict__ X, int C, int HW,
                                                       float* __restrict__ colsum) {
+    mtl_pdl_sync();
     __shared__ float tile[32][33];
     __shared__ float part[8][33];
     const int n = blockIdx.z;
@@ -274,6 +276,7 @@ __global__ void __launch_bounds__(256) k_nchw_to_nhwc(float* __restrict__ hi, fl
 // coalesced row segments, fixed order of additions.  grid = (cols / 32, slices).
 __global__ void __launch_bounds__(256) k_colsum(float* __restrict__ out, const float* __restrict__ m, int64_t rows,
                                                 int cols, int64_t rows_per_slice, int accumulate) {
+    mtl_pdl_sync();
     __shared__ float part[8][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + tx;
@@ -311,6 +314,7 @@ __global__ void __launch_bounds__(256) k_pool_bwd_2x2_cl(float* __restrict__ hi,
                                                          const int32_t* __restrict__ pidx,
                                                          const float* __restrict__ pv, int K, int POH, int POW,
                                                          int relu) {
+    mtl_pdl_sync();
     extern __shared__ float pool_smem[];
     const int P = POH * POW, PS = P | 1;   // odd row stride: lanes (channels) hit different banks
     float* val = pool_smem;                // [32][PS] gradient routed to the selected element
@@ -396,6 +400,7 @@ template <bool SPLIT>
 __global__ void __launch_bounds__(256) k_weights_relayout(float* __restrict__ hi, float* __restrict__ lo,
                                                           const float* __restrict__ Wt, int K, int C, int R, int S,
                                                           int flip) {
+    mtl_pdl_sync();
     int64_t total = (int64_t)K * C * R * S;
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -429,6 +434,7 @@ template <bool SPLIT>
 __global__ void __launch_bounds__(256) k_weights_relayout_paired(float* __restrict__ hi, float* __restrict__ lo,
                                                                  const float* __restrict__ Wt, int K, int C, int R,
                                                                  int S, int flip, int pair) {
+    mtl_pdl_sync();
     const int SP = pair ? (S + 1) / 2 : S;
     const int inner = flip ? K : C, mid = flip ? C : K;
     int64_t total = (int64_t)R * SP * 128 * inner;
@@ -608,6 +614,7 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    mtl_pdl_sync();   // everything above touched only shared / tensor memory
 
     if (warp == 0) {
         // two producer lanes: issuing a TMA copy occupies its thread for a few hundred cycles, so the
@@ -916,7 +923,7 @@ int32_t launch_igemm(mtl_ctx* ctx, const CUtensorMap* maps, const ConvTcParams& 
     int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     {
         mtl_prof_scope prof(ctx, MTL_PROF_CONV_IGEMM);
-        kern<<<grid, kThreads, C::kSmemBytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+        mtl_launch_pdl(ctx, kern, dim3(grid), dim3(kThreads), (size_t)(C::kSmemBytes), maps[0], maps[1], maps[2], maps[3], p);
     }
     MTL_LAUNCHED(ctx);
     return MTL_OK;
@@ -952,8 +959,8 @@ size_t igemm_weight_floats(const IgemmCall& c) {
 int32_t stage_nhwc(mtl_ctx* ctx, float* hi, float* lo, const float* src, int N, int C, int HW, int x3, float* colsum) {
     dim3 tg((unsigned)((HW + 31) / 32), (unsigned)((C + 31) / 32), (unsigned)N);
     MTL_REQUIRE(ctx, N <= 65535 && tg.y <= 65535u, "batch too large for the layout pass");
-    if (x3) k_nchw_to_nhwc<true><<<tg, 256, 0, ctx->stream>>>(hi, lo, src, C, HW, colsum);
-    else k_nchw_to_nhwc<false><<<tg, 256, 0, ctx->stream>>>(hi, lo, src, C, HW, colsum);
+    if (x3) mtl_launch_pdl(ctx, k_nchw_to_nhwc<true>, dim3(tg), dim3(256), (size_t)(0), hi, lo, src, C, HW, colsum);
+    else mtl_launch_pdl(ctx, k_nchw_to_nhwc<false>, dim3(tg), dim3(256), (size_t)(0), hi, lo, src, C, HW, colsum);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -982,8 +989,8 @@ int32_t run_igemm(mtl_ctx* ctx, const IgemmCall& c, int x3) {
 
     dim3 tgrid((unsigned)((HW + 31) / 32), (unsigned)((c.Cin + 31) / 32), (unsigned)c.N);
     MTL_REQUIRE(ctx, c.N <= 65535 && tgrid.y <= 65535u, "batch too large for the layout pass");
-    if (x3) k_nchw_to_nhwc<true><<<tgrid, 256, 0, ctx->stream>>>(a_hi, a_lo, c.act, c.Cin, HW, nullptr);
-    else k_nchw_to_nhwc<false><<<tgrid, 256, 0, ctx->stream>>>(a_hi, a_lo, c.act, c.Cin, HW, nullptr);
+    if (x3) mtl_launch_pdl(ctx, k_nchw_to_nhwc<true>, dim3(tgrid), dim3(256), (size_t)(0), a_hi, a_lo, c.act, c.Cin, HW, nullptr);
+    else mtl_launch_pdl(ctx, k_nchw_to_nhwc<false>, dim3(tgrid), dim3(256), (size_t)(0), a_hi, a_lo, c.act, c.Cin, HW, nullptr);
     MTL_LAUNCHED(ctx);
     return run_igemm_core(ctx, c, x3, a_hi, a_lo, w_hi, w_lo);
 }
@@ -997,11 +1004,11 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
     const bool spread = igemm_spread(c);
     int wgrid = mtl_grid_for((int64_t)n_wt, 256, ctx->sm_count, 8);
     if (paired || spread) {
-        if (x3) k_weights_relayout_paired<true><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip, paired ? 1 : 0);
-        else k_weights_relayout_paired<false><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip, paired ? 1 : 0);
+        if (x3) mtl_launch_pdl(ctx, k_weights_relayout_paired<true>, dim3(wgrid), dim3(256), (size_t)(0), w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip, paired ? 1 : 0);
+        else mtl_launch_pdl(ctx, k_weights_relayout_paired<false>, dim3(wgrid), dim3(256), (size_t)(0), w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip, paired ? 1 : 0);
     } else {
-        if (x3) k_weights_relayout<true><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
-        else k_weights_relayout<false><<<wgrid, 256, 0, ctx->stream>>>(w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
+        if (x3) mtl_launch_pdl(ctx, k_weights_relayout<true>, dim3(wgrid), dim3(256), (size_t)(0), w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
+        else mtl_launch_pdl(ctx, k_weights_relayout<false>, dim3(wgrid), dim3(256), (size_t)(0), w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip);
     }
     MTL_LAUNCHED(ctx);
 
@@ -1087,7 +1094,7 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
         int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
         {
             mtl_prof_scope prof(ctx, MTL_PROF_CONV_IGEMM);
-            k_conv_igemm_t<<<grid, kThreads, kTSmemBytes, ctx->stream>>>(tm[0], tm[1], tm[2], tm[3], q);
+            mtl_launch_pdl(ctx, k_conv_igemm_t, dim3(grid), dim3(kThreads), (size_t)(kTSmemBytes), tm[0], tm[1], tm[2], tm[3], q);
         }
         MTL_LAUNCHED(ctx);
         return MTL_OK;
@@ -1209,6 +1216,7 @@ k_conv_wgrad_tc(const __grid_constant__ CUtensorMap mapU0, const __grid_constant
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    mtl_pdl_sync();   // everything above touched only shared / tensor memory
     const uint32_t a_bytes = 4u * 4096u;
     const uint32_t tx_bytes = a_bytes + (uint32_t)(ntaps * cchunks) * 4096u;
 
@@ -1321,6 +1329,7 @@ k_conv_wgrad_tc(const __grid_constant__ CUtensorMap mapU0, const __grid_constant
 // dW[k][c][r][s] (+)= sum over splits of partial[split][rs][k][c]
 __global__ void __launch_bounds__(256) k_wgrad_fold(float* __restrict__ dW, const float* __restrict__ partial, int K,
                                                     int C, int RS, int nsplit, int accumulate) {
+    mtl_pdl_sync();
     int64_t total = (int64_t)K * C * RS;
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -1518,11 +1527,11 @@ int32_t wgrad_core(mtl_ctx* ctx, float* dW, const float* u_hi, const float* u_lo
     const int grid = p.ngroups * p.ktiles * p.nsplit;
     {
         mtl_prof_scope prof(ctx, MTL_PROF_CONV_WGRAD);
-        k_conv_wgrad_tc<<<grid, kThreads, smem_bytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+        mtl_launch_pdl(ctx, k_conv_wgrad_tc, dim3(grid), dim3(kThreads), (size_t)(smem_bytes), maps[0], maps[1], maps[2], maps[3], p);
     }
     MTL_LAUNCHED(ctx);
     int fgrid = mtl_grid_for((int64_t)g.K * g.C * RS, 256, ctx->sm_count, 8);
-    k_wgrad_fold<<<fgrid, 256, 0, ctx->stream>>>(dW, p.partial, g.K, g.C, RS, p.nsplit, accumulate);
+    mtl_launch_pdl(ctx, k_wgrad_fold, dim3(fgrid), dim3(256), (size_t)(0), dW, p.partial, g.K, g.C, RS, p.nsplit, accumulate);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -1604,10 +1613,10 @@ int32_t mtl_conv_bwd_fused_tc_src(mtl_ctx* ctx, float* dX, float* dW, float* db,
         MTL_REQUIRE(ctx, g.N <= 65535 && smem <= 200 * 1024, "pooled plane too large for the scatter pass");
         if (x3) {
             MTL_CUDA(ctx, cudaFuncSetAttribute(k_pool_bwd_2x2_cl<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            k_pool_bwd_2x2_cl<true><<<grid, 256, smem, ctx->stream>>>(u_hi, u_lo, db ? bias_part : nullptr, pg, pidx, pv, g.K, POH, POW, relu);
+            mtl_launch_pdl(ctx, k_pool_bwd_2x2_cl<true>, dim3(grid), dim3(256), (size_t)(smem), u_hi, u_lo, db ? bias_part : nullptr, pg, pidx, pv, g.K, POH, POW, relu);
         } else {
             MTL_CUDA(ctx, cudaFuncSetAttribute(k_pool_bwd_2x2_cl<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            k_pool_bwd_2x2_cl<false><<<grid, 256, smem, ctx->stream>>>(u_hi, u_lo, db ? bias_part : nullptr, pg, pidx, pv, g.K, POH, POW, relu);
+            mtl_launch_pdl(ctx, k_pool_bwd_2x2_cl<false>, dim3(grid), dim3(256), (size_t)(smem), u_hi, u_lo, db ? bias_part : nullptr, pg, pidx, pv, g.K, POH, POW, relu);
         }
         MTL_LAUNCHED(ctx);
     } else {
@@ -1621,9 +1630,9 @@ int32_t mtl_conv_bwd_fused_tc_src(mtl_ctx* ctx, float* dX, float* dW, float* db,
         const int64_t rps = (rows + slices - 1) / slices;
         float* level1 = bias_part + rows * g.K;
         dim3 g1((unsigned)((g.K + 31) / 32), (unsigned)slices);
-        k_colsum<<<g1, 256, 0, ctx->stream>>>(level1, bias_part, rows, g.K, rps, 0);
+        mtl_launch_pdl(ctx, k_colsum, dim3(g1), dim3(256), (size_t)(0), level1, bias_part, rows, g.K, rps, 0);
         MTL_LAUNCHED(ctx);
-        k_colsum<<<(g.K + 31) / 32, 256, 0, ctx->stream>>>(db, level1, slices, g.K, slices, acc_db);
+        mtl_launch_pdl(ctx, k_colsum, dim3((g.K + 31) / 32), dim3(256), (size_t)(0), db, level1, slices, g.K, slices, acc_db);
         MTL_LAUNCHED(ctx);
     }
     const bool x_ready = X_cl && !x3;  // the caller's channels-last copy of X replaces the staging pass

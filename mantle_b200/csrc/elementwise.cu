@@ -80,6 +80,7 @@ __device__ __forceinline__ float bin_apply(int op, float a, float b) {
 template <class F>
 __global__ void __launch_bounds__(kBlock) k_map1(float* __restrict__ out, const float* __restrict__ in,
                                                  int64_t n, F f, int vec) {
+    mtl_pdl_sync();
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     if (vec) {
@@ -102,6 +103,7 @@ template <class F>
 __global__ void __launch_bounds__(kBlock) k_map2(float* __restrict__ out, const float* __restrict__ x,
                                                  const float* __restrict__ y, int64_t n, F f, int vec,
                                                  int acc) {
+    mtl_pdl_sync();
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     if (vec) {
@@ -131,6 +133,7 @@ __global__ void __launch_bounds__(kBlock) k_map2(float* __restrict__ out, const 
 }
 
 __global__ void __launch_bounds__(kBlock) k_fill(float* __restrict__ p, int64_t n, float v, int vec) {
+    mtl_pdl_sync();
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     if (vec) {
@@ -200,6 +203,7 @@ __device__ __forceinline__ void bcast_index(const Bcast& bc, int64_t i, int64_t&
 __global__ void __launch_bounds__(kBlock) k_binary_bcast(float* __restrict__ out, const float* __restrict__ a,
                                                          const float* __restrict__ b, int64_t n, int op,
                                                          Bcast bc) {
+    mtl_pdl_sync();
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = tid; i < n; i += stride) {
@@ -213,6 +217,7 @@ __global__ void __launch_bounds__(kBlock) k_binary_bcast(float* __restrict__ out
 __global__ void __launch_bounds__(kBlock) k_binary_scalar(float* __restrict__ out, const float* __restrict__ t,
                                                           const float* __restrict__ s, int64_t n, int op,
                                                           int scalar_first, int vec) {
+    mtl_pdl_sync();
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     float sv = __ldg(s);
@@ -258,6 +263,7 @@ __global__ void __launch_bounds__(kBlock) k_binary_bwd_full(float* __restrict__ 
                                                             const float* __restrict__ a,
                                                             const float* __restrict__ b, int64_t n, int op,
                                                             int tensor_id, int b_is_scalar, int acc, Bcast bc) {
+    mtl_pdl_sync();
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = tid; i < n; i += stride) {
@@ -324,6 +330,7 @@ __global__ void __launch_bounds__(kBlock) k_binary_bwd_unb_block(float* __restri
                                                                  const float* __restrict__ b, int64_t n_grad,
                                                                  int64_t n_red, int op, int tensor_id,
                                                                  int b_is_scalar, int acc, Bcast bc, Unbcast ub) {
+    mtl_pdl_sync();
     __shared__ float warp_sums[kBlock / 32];
     for (int64_t j = blockIdx.x; j < n_grad; j += gridDim.x) {
         int64_t base = unb_base(ub, j);
@@ -354,6 +361,7 @@ __global__ void __launch_bounds__(kBlock) k_binary_bwd_unb_block(float* __restri
 // hence the same bits.
 __global__ void __launch_bounds__(kBlock) k_unb_rows(float* __restrict__ grad, const float* __restrict__ ug, int64_t R,
                                                      int64_t C, float sign, int acc) {
+    mtl_pdl_sync();
     __shared__ float warp_sums[kBlock / 32];
     for (int64_t j = blockIdx.x; j < C; j += gridDim.x) {
         float s = 0.0f;
@@ -379,6 +387,7 @@ __global__ void __launch_bounds__(kBlock) k_binary_bwd_unb_thread(float* __restr
                                                                   const float* __restrict__ b, int64_t n_grad,
                                                                   int64_t n_red, int op, int tensor_id,
                                                                   int b_is_scalar, int acc, Bcast bc, Unbcast ub) {
+    mtl_pdl_sync();
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t j = tid; j < n_grad; j += stride) {
@@ -398,6 +407,7 @@ __global__ void __launch_bounds__(kBlock) k_binary_bwd_unb_thread(float* __restr
 __global__ void __launch_bounds__(kBlock) k_fma(float* __restrict__ out, const float* __restrict__ a,
                                                 const float* __restrict__ b, const float* __restrict__ c,
                                                 int64_t n) {
+    mtl_pdl_sync();
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = tid; i < n; i += stride) out[i] = fmaf(a[i], b[i], c[i]);
@@ -457,6 +467,7 @@ namespace {
 // A label outside [0, C) leaves its row all zeros; the reference would write outside the row.
 __global__ void __launch_bounds__(kBlock) k_one_hot(float* __restrict__ out, const float* __restrict__ labels, int64_t B,
                                                     int64_t C) {
+    mtl_pdl_sync();
     const int64_t n = B * C;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t b = i / C, c = i - b * C;
@@ -472,7 +483,7 @@ int32_t mtl_one_hot_f32(mtl_ctx* ctx, float* out, const float* labels, int64_t B
     MTL_REQUIRE(ctx, B >= 0 && C >= 1 && ((out && labels) || B == 0), "bad arguments to mtl_one_hot_f32");
     if (B == 0) return MTL_OK;
     int grid = mtl_grid_for(B * C, kBlock, ctx->sm_count, kCtasPerSm);
-    k_one_hot<<<grid, kBlock, 0, ctx->stream>>>(out, labels, B, C);
+    mtl_launch_pdl(ctx, k_one_hot, dim3(grid), dim3(kBlock), (size_t)(0), out, labels, B, C);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -482,7 +493,7 @@ int32_t mtl_fill_f32(mtl_ctx* ctx, float* dptr, int64_t n, float value) {
     MTL_REQUIRE(ctx, n >= 0 && (dptr || n == 0), "bad arguments to mtl_fill_f32");
     if (n == 0) return MTL_OK;
     int grid = mtl_grid_for((n + 3) / 4, kBlock, ctx->sm_count, kCtasPerSm);
-    k_fill<<<grid, kBlock, 0, ctx->stream>>>(dptr, n, value, aligned16(dptr));
+    mtl_launch_pdl(ctx, k_fill, dim3(grid), dim3(kBlock), (size_t)(0), dptr, n, value, aligned16(dptr));
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -497,7 +508,7 @@ int32_t mtl_copy_f32(mtl_ctx* ctx, float* dst, const float* src, int64_t n, int3
     }
     int vec = aligned16(dst) && aligned16(src);
     int grid = mtl_grid_for((n + 3) / 4, kBlock, ctx->sm_count, kCtasPerSm);
-    k_map2<<<grid, kBlock, 0, ctx->stream>>>(dst, dst, src, n, AddTo{}, vec, 0);
+    mtl_launch_pdl(ctx, k_map2<AddTo>, dim3(grid), dim3(kBlock), (size_t)(0), dst, dst, src, n, AddTo{}, vec, 0);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -510,7 +521,7 @@ int32_t mtl_unary_fwd(mtl_ctx* ctx, int32_t op, float* out, const float* in, int
     if (n == 0) return MTL_OK;
     int vec = aligned16(out) && aligned16(in);
     int grid = mtl_grid_for((n + 3) / 4, kBlock, ctx->sm_count, kCtasPerSm);
-    k_map1<<<grid, kBlock, 0, ctx->stream>>>(out, in, n, UnaryFwd{op, p0, p1}, vec);
+    mtl_launch_pdl(ctx, k_map1<UnaryFwd>, dim3(grid), dim3(kBlock), (size_t)(0), out, in, n, UnaryFwd{op, p0, p1}, vec);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -523,7 +534,7 @@ int32_t mtl_unary_bwd(mtl_ctx* ctx, int32_t op, float* grad, const float* ug, co
     if (n == 0) return MTL_OK;
     int vec = aligned16(grad) && aligned16(ug) && aligned16(in);
     int grid = mtl_grid_for((n + 3) / 4, kBlock, ctx->sm_count, kCtasPerSm);
-    k_map2<<<grid, kBlock, 0, ctx->stream>>>(grad, in, ug, n, UnaryBwd{op, p0, p1}, vec, accumulate ? 1 : 0);
+    mtl_launch_pdl(ctx, k_map2<UnaryBwd>, dim3(grid), dim3(kBlock), (size_t)(0), grad, in, ug, n, UnaryBwd{op, p0, p1}, vec, accumulate ? 1 : 0);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -545,14 +556,14 @@ int32_t mtl_binary_fwd(mtl_ctx* ctx, int32_t op, float* out, const float* a, con
         const float* s = scalar_first ? a : b;
         int vec = aligned16(out) && aligned16(t);
         int grid = mtl_grid_for((n + 3) / 4, kBlock, ctx->sm_count, kCtasPerSm);
-        k_binary_scalar<<<grid, kBlock, 0, ctx->stream>>>(out, t, s, n, op, scalar_first, vec);
+        mtl_launch_pdl(ctx, k_binary_scalar, dim3(grid), dim3(kBlock), (size_t)(0), out, t, s, n, op, scalar_first, vec);
     } else if (same_shape(a_rank, a_shape, b_rank, b_shape)) {
         int vec = aligned16(out) && aligned16(a) && aligned16(b);
         int grid = mtl_grid_for((n + 3) / 4, kBlock, ctx->sm_count, kCtasPerSm);
-        k_map2<<<grid, kBlock, 0, ctx->stream>>>(out, a, b, n, BinF{op}, vec, 0);
+        mtl_launch_pdl(ctx, k_map2<BinF>, dim3(grid), dim3(kBlock), (size_t)(0), out, a, b, n, BinF{op}, vec, 0);
     } else {
         int grid = mtl_grid_for(n, kBlock, ctx->sm_count, kCtasPerSm);
-        k_binary_bcast<<<grid, kBlock, 0, ctx->stream>>>(out, a, b, n, op, bc);
+        mtl_launch_pdl(ctx, k_binary_bcast, dim3(grid), dim3(kBlock), (size_t)(0), out, a, b, n, op, bc);
     }
     MTL_LAUNCHED(ctx);
     return MTL_OK;
@@ -581,7 +592,7 @@ int32_t mtl_binary_bwd(mtl_ctx* ctx, int32_t op, int32_t tensor_id, float* grad,
     if (n_grad == n) {
         // grad already has the broadcast extent: accumulate_op[add] (tensorutils.mojo:469-470)
         int grid = mtl_grid_for(n, kBlock, ctx->sm_count, kCtasPerSm);
-        k_binary_bwd_full<<<grid, kBlock, 0, ctx->stream>>>(grad, ug, a, b, n, op, tensor_id, b_is_scalar, acc, bc);
+        mtl_launch_pdl(ctx, k_binary_bwd_full, dim3(grid), dim3(kBlock), (size_t)(0), grad, ug, a, b, n, op, tensor_id, b_is_scalar, acc, bc);
         MTL_LAUNCHED(ctx);
         return MTL_OK;
     }
@@ -611,17 +622,17 @@ int32_t mtl_binary_bwd(mtl_ctx* ctx, int32_t op, int32_t tensor_id, float* grad,
         // a bias gradient: column sums of a row-major [rows, n_grad] upper gradient
         const float sign = (op == MTL_OP_SUB && tensor_id == 1) ? -1.0f : 1.0f;
         int grid = (int)(n_grad < (int64_t)ctx->sm_count * kCtasPerSm ? n_grad : (int64_t)ctx->sm_count * kCtasPerSm);
-        k_unb_rows<<<grid, kBlock, 0, ctx->stream>>>(grad, ug, n_red, n_grad, sign, acc);
+        mtl_launch_pdl(ctx, k_unb_rows, dim3(grid), dim3(kBlock), (size_t)(0), grad, ug, n_red, n_grad, sign, acc);
         MTL_LAUNCHED(ctx);
         return MTL_OK;
     }
     if (n_red >= 128) {
         int grid = (int)(n_grad < (int64_t)ctx->sm_count * kCtasPerSm ? n_grad : (int64_t)ctx->sm_count * kCtasPerSm);
-        k_binary_bwd_unb_block<<<grid, kBlock, 0, ctx->stream>>>(grad, ug, a, b, n_grad, n_red, op, tensor_id,
+        mtl_launch_pdl(ctx, k_binary_bwd_unb_block, dim3(grid), dim3(kBlock), (size_t)(0), grad, ug, a, b, n_grad, n_red, op, tensor_id,
                                                                   b_is_scalar, acc, bc, ub);
     } else {
         int grid = mtl_grid_for(n_grad, kBlock, ctx->sm_count, kCtasPerSm);
-        k_binary_bwd_unb_thread<<<grid, kBlock, 0, ctx->stream>>>(grad, ug, a, b, n_grad, n_red, op, tensor_id,
+        mtl_launch_pdl(ctx, k_binary_bwd_unb_thread, dim3(grid), dim3(kBlock), (size_t)(0), grad, ug, a, b, n_grad, n_red, op, tensor_id,
                                                                    b_is_scalar, acc, bc, ub);
     }
     MTL_LAUNCHED(ctx);
@@ -633,7 +644,7 @@ int32_t mtl_fma_fwd(mtl_ctx* ctx, float* out, const float* a, const float* b, co
     MTL_REQUIRE(ctx, n >= 0 && ((out && a && b && c) || n == 0), "bad arguments to mtl_fma_fwd");
     if (n == 0) return MTL_OK;
     int grid = mtl_grid_for(n, kBlock, ctx->sm_count, kCtasPerSm);
-    k_fma<<<grid, kBlock, 0, ctx->stream>>>(out, a, b, c, n);
+    mtl_launch_pdl(ctx, k_fma, dim3(grid), dim3(kBlock), (size_t)(0), out, a, b, c, n);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -649,7 +660,7 @@ int32_t mtl_fma_bwd(mtl_ctx* ctx, int32_t tensor_id, float* grad, const float* u
     MTL_REQUIRE(ctx, other, "operand needed by this gradient is null");
     int vec = aligned16(grad) && aligned16(ug) && aligned16(other);
     int grid = mtl_grid_for((n + 3) / 4, kBlock, ctx->sm_count, kCtasPerSm);
-    k_map2<<<grid, kBlock, 0, ctx->stream>>>(grad, ug, other, n, BinF{MTL_OP_MUL}, vec, accumulate ? 1 : 0);
+    mtl_launch_pdl(ctx, k_map2<BinF>, dim3(grid), dim3(kBlock), (size_t)(0), grad, ug, other, n, BinF{MTL_OP_MUL}, vec, accumulate ? 1 : 0);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }

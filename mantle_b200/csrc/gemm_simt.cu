@@ -11,6 +11,7 @@ template <int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 k_gemm_simt(float* __restrict__ C, const float* __restrict__ A, const float* __restrict__ B, int M, int N, int K,
             int transA, int transB, int accumulate) {
+    mtl_pdl_sync();
     constexpr int NT = (BM / TM) * (BN / TN);
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[BK][BN + 4];
@@ -83,6 +84,7 @@ template <int ROWS>
 __global__ void __launch_bounds__(128) k_gemm_thin_n(float* __restrict__ C, const float* __restrict__ A,
                                                      const float* __restrict__ B, int M, int N, int K,
                                                      int accumulate) {
+    mtl_pdl_sync();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const int m0 = warp * ROWS;
     if (m0 >= M) return;
@@ -125,6 +127,7 @@ constexpr int kThinKC = 512;  // k extent of one block
 template <int NQ>
 __global__ void __launch_bounds__(256, 3) k_gemm_thin_tile(float* __restrict__ partial, const float* __restrict__ A,
                                                         const float* __restrict__ B, int M, int N, int K) {
+    mtl_pdl_sync();
     constexpr int NP = 4 * NQ;
     __shared__ __align__(16) float b_s[kThinKC * 20];
     const int k_begin = blockIdx.y * kThinKC;
@@ -194,6 +197,7 @@ template <int NQ>
 __global__ void __launch_bounds__(256) k_gemm_thin_n_ta(float* __restrict__ partial, const float* __restrict__ A,
                                                         const float* __restrict__ B, int M, int N, int K,
                                                         int k_per_split) {
+    mtl_pdl_sync();
     constexpr int NP = 4 * NQ;   // N rounded up to whole float4 groups
     __shared__ __align__(16) float b_s[64][16];
     const int m = blockIdx.x * blockDim.x + threadIdx.x;
@@ -241,6 +245,7 @@ __global__ void __launch_bounds__(256) k_gemm_thin_n_ta(float* __restrict__ part
 
 __global__ void __launch_bounds__(256) k_fold_partials(float* __restrict__ out, const float* __restrict__ partial,
                                                        int64_t n, int nsplit, int accumulate) {
+    mtl_pdl_sync();
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = tid; i < n; i += stride) {
@@ -272,13 +277,13 @@ int32_t mtl_gemm_thin(mtl_ctx* ctx, float* C, const float* A, const float* B, in
         int32_t rc = mtl_workspace(ctx, (size_t)nsplit * M * N * 4, &ws);
         if (rc) return rc;
         dim3 grid((unsigned)((M + 31) / 32), (unsigned)nsplit);
-        if (N <= 4) k_gemm_thin_tile<1><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K);
-        else if (N <= 8) k_gemm_thin_tile<2><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K);
-        else if (N <= 12) k_gemm_thin_tile<3><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K);
-        else k_gemm_thin_tile<4><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K);
+        if (N <= 4) mtl_launch_pdl(ctx, k_gemm_thin_tile<1>, dim3(grid), dim3(256), (size_t)(0), (float*)ws, A, B, (int)M, (int)N, (int)K);
+        else if (N <= 8) mtl_launch_pdl(ctx, k_gemm_thin_tile<2>, dim3(grid), dim3(256), (size_t)(0), (float*)ws, A, B, (int)M, (int)N, (int)K);
+        else if (N <= 12) mtl_launch_pdl(ctx, k_gemm_thin_tile<3>, dim3(grid), dim3(256), (size_t)(0), (float*)ws, A, B, (int)M, (int)N, (int)K);
+        else mtl_launch_pdl(ctx, k_gemm_thin_tile<4>, dim3(grid), dim3(256), (size_t)(0), (float*)ws, A, B, (int)M, (int)N, (int)K);
         MTL_LAUNCHED(ctx);
         int fg = mtl_grid_for(M * N, 256, ctx->sm_count, 8);
-        k_fold_partials<<<fg, 256, 0, ctx->stream>>>(C, (const float*)ws, M * N, nsplit, accumulate);
+        mtl_launch_pdl(ctx, k_fold_partials, dim3(fg), dim3(256), (size_t)(0), C, (const float*)ws, M * N, nsplit, accumulate);
         MTL_LAUNCHED(ctx);
         return MTL_OK;
     }
@@ -286,7 +291,7 @@ int32_t mtl_gemm_thin(mtl_ctx* ctx, float* C, const float* A, const float* B, in
         constexpr int ROWS = 4;
         int64_t warps = (M + ROWS - 1) / ROWS;
         int grid = (int)((warps * 32 + 127) / 128);
-        k_gemm_thin_n<ROWS><<<grid, 128, 0, ctx->stream>>>(C, A, B, (int)M, (int)N, (int)K, accumulate);
+        mtl_launch_pdl(ctx, k_gemm_thin_n<ROWS>, dim3(grid), dim3(128), (size_t)(0), C, A, B, (int)M, (int)N, (int)K, accumulate);
         MTL_LAUNCHED(ctx);
         return MTL_OK;
     }
@@ -299,13 +304,13 @@ int32_t mtl_gemm_thin(mtl_ctx* ctx, float* C, const float* A, const float* B, in
     int32_t rc = mtl_workspace(ctx, (size_t)nsplit * M * N * 4, &ws);
     if (rc) return rc;
     dim3 grid((unsigned)gx, (unsigned)nsplit);
-    if (N <= 4) k_gemm_thin_n_ta<1><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
-    else if (N <= 8) k_gemm_thin_n_ta<2><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
-    else if (N <= 12) k_gemm_thin_n_ta<3><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
-    else k_gemm_thin_n_ta<4><<<grid, 256, 0, ctx->stream>>>((float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
+    if (N <= 4) mtl_launch_pdl(ctx, k_gemm_thin_n_ta<1>, dim3(grid), dim3(256), (size_t)(0), (float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
+    else if (N <= 8) mtl_launch_pdl(ctx, k_gemm_thin_n_ta<2>, dim3(grid), dim3(256), (size_t)(0), (float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
+    else if (N <= 12) mtl_launch_pdl(ctx, k_gemm_thin_n_ta<3>, dim3(grid), dim3(256), (size_t)(0), (float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
+    else mtl_launch_pdl(ctx, k_gemm_thin_n_ta<4>, dim3(grid), dim3(256), (size_t)(0), (float*)ws, A, B, (int)M, (int)N, (int)K, (int)kps);
     MTL_LAUNCHED(ctx);
     int fg = mtl_grid_for(M * N, 256, ctx->sm_count, 8);
-    k_fold_partials<<<fg, 256, 0, ctx->stream>>>(C, (const float*)ws, M * N, nsplit, accumulate);
+    mtl_launch_pdl(ctx, k_fold_partials, dim3(fg), dim3(256), (size_t)(0), C, (const float*)ws, M * N, nsplit, accumulate);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -317,11 +322,11 @@ int32_t mtl_gemm_simt(mtl_ctx* ctx, float* C, const float* A, const float* B, in
     if (N <= 16) {
         dim3 grid((unsigned)((N + 15) / 16), (unsigned)((M + 255) / 256));
         MTL_REQUIRE(ctx, grid.y <= 65535u, "DOT: M too large for the skinny kernel");
-        k_gemm_simt<256, 16, 16, 4, 4><<<grid, 256, 0, ctx->stream>>>(C, A, B, (int)M, (int)N, (int)K, transA, transB, accumulate);
+        mtl_launch_pdl(ctx, k_gemm_simt<256, 16, 16, 4, 4>, dim3(grid), dim3(256), (size_t)(0), C, A, B, (int)M, (int)N, (int)K, transA, transB, accumulate);
     } else {
         dim3 grid((unsigned)((N + 63) / 64), (unsigned)((M + 63) / 64));
         MTL_REQUIRE(ctx, grid.y <= 65535u, "DOT: M too large for the CUDA-core kernel");
-        k_gemm_simt<64, 64, 16, 4, 4><<<grid, 256, 0, ctx->stream>>>(C, A, B, (int)M, (int)N, (int)K, transA, transB, accumulate);
+        mtl_launch_pdl(ctx, k_gemm_simt<64, 64, 16, 4, 4>, dim3(grid), dim3(256), (size_t)(0), C, A, B, (int)M, (int)N, (int)K, transA, transB, accumulate);
     }
     MTL_LAUNCHED(ctx);
     return MTL_OK;

@@ -16,6 +16,7 @@ constexpr int kLossBlock = 1024;
 // One block.  Thread t owns rows t, t + 1024, ...; the per-thread sums are combined by a tree.
 __global__ void __launch_bounds__(kLossBlock) k_cross_entropy_fwd(float* __restrict__ loss, const float* __restrict__ x,
                                                                   const float* __restrict__ y, int B, int C, float scale) {
+    mtl_pdl_sync();
     __shared__ float part[kLossBlock];
     float acc = 0.0f;
     for (int b = threadIdx.x; b < B; b += kLossBlock) {
@@ -47,6 +48,7 @@ __global__ void __launch_bounds__(kLossBlock) k_cross_entropy_fwd(float* __restr
 __global__ void __launch_bounds__(256) k_cross_entropy_bwd(float* __restrict__ dx, const float* __restrict__ x,
                                                            const float* __restrict__ y, int B, int C, float scale,
                                                            int accumulate) {
+    mtl_pdl_sync();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
     const float* xr = x + (int64_t)b * C;
@@ -84,7 +86,7 @@ int32_t mtl_cross_entropy_fwd(mtl_ctx* ctx, float* loss, const float* logits, co
     MTL_REQUIRE(ctx, B >= 1 && C >= 1 && B * C <= MTL_CROSS_ENTROPY_MAX_ELEMENTS,
                 "mtl_cross_entropy_fwd handles up to %lld logits, got %lld x %lld",
                 (long long)MTL_CROSS_ENTROPY_MAX_ELEMENTS, (long long)B, (long long)C);
-    k_cross_entropy_fwd<<<1, kLossBlock, 0, ctx->stream>>>(loss, logits, y_true, (int)B, (int)C, scale);
+    mtl_launch_pdl(ctx, k_cross_entropy_fwd, dim3(1), dim3(kLossBlock), (size_t)(0), loss, logits, y_true, (int)B, (int)C, scale);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -97,7 +99,7 @@ int32_t mtl_cross_entropy_bwd(mtl_ctx* ctx, float* dlogits, const float* logits,
                 "mtl_cross_entropy_bwd handles up to %lld logits, got %lld x %lld",
                 (long long)MTL_CROSS_ENTROPY_MAX_ELEMENTS, (long long)B, (long long)C);
     const int blocks = (int)((B + 255) / 256);
-    k_cross_entropy_bwd<<<blocks, 256, 0, ctx->stream>>>(dlogits, logits, y_true, (int)B, (int)C, scale, accumulate);
+    mtl_launch_pdl(ctx, k_cross_entropy_bwd, dim3(blocks), dim3(256), (size_t)(0), dlogits, logits, y_true, (int)B, (int)C, scale, accumulate);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }

@@ -206,6 +206,29 @@ Model::Model(mtl_ctx* ctx, const Graph& g, uint64_t init_seed) : ctx_(ctx), g_(g
         off += align_up(p.shape.num_elements());
     }
     n_trainable_ = off;
+    // RESHAPE / FLATTEN / SQUEEZE / UNSQUEEZE move no data (basics.mojo:706-756 and mlops.mojo:302-373 copy
+    // element i to element i): when such a node is the ONLY reader of a node output, its result shares
+    // that tensor's storage, and so do the two gradients, instead of being copied each way every step.
+    // Both symbols keep their own shape and can be read by name; every value is what the copies gave.
+    {
+        std::map<int, int> uses, producer;
+        for (size_t i = 0; i < g_.nodes.size(); ++i) {
+            for (auto& s : g_.nodes[i].inputs) uses[s.id]++;
+            for (auto& s : g_.nodes[i].outputs) producer[s.id] = (int)i;
+        }
+        alias_node_.assign(g_.nodes.size(), 0);
+        for (size_t i = 0; i < g_.nodes.size(); ++i) {
+            const Node& n = g_.nodes[i];
+            const bool is_copy = n.op == MTL_OP_RESHAPE || n.op == MTL_OP_FLATTEN || n.op == MTL_OP_SQUEEZE || n.op == MTL_OP_UNSQUEEZE;
+            if (!is_copy || n.inputs.size() != 1 || n.outputs.size() != 1) continue;
+            const Symbol& in = n.inputs[0];
+            const Symbol& out = n.outputs[0];
+            if (!producer.count(in.id) || uses[in.id] != 1 || in.trainable != out.trainable) continue;
+            if (in.shape.num_elements() != out.shape.num_elements()) continue;
+            alias_of_[out.id] = in.id;
+            alias_node_[i] = 1;
+        }
+    }
     int64_t toff = off, goff = off;
     std::map<int, bool> listed;
     auto add_tensor = [&](const Symbol& s) {
@@ -213,6 +236,12 @@ Model::Model(mtl_ctx* ctx, const Graph& g, uint64_t init_seed) : ctx_(ctx), g_(g
         if (!listed[s.id]) {
             listed[s.id] = true;
             alloc_order_.push_back(s);
+        }
+        auto al = alias_of_.find(s.id);
+        if (al != alias_of_.end() && tensor_off_.count(al->second)) {   // the producer's output was placed earlier
+            tensor_off_[s.id] = tensor_off_.at(al->second);
+            if (s.trainable) grad_off_[s.id] = grad_off_.at(al->second);
+            return;
         }
         if (!tensor_off_.count(s.id)) {
             tensor_off_[s.id] = toff;
@@ -658,6 +687,7 @@ void Model::forward_op(const Node& n) {
                                  n.attrs.axis ? *n.attrs.axis : -1), "reduce forward");
             break;
         case MTL_OP_FLATTEN: case MTL_OP_RESHAPE: case MTL_OP_SQUEEZE: case MTL_OP_UNSQUEEZE:
+            if (alias_node_[(size_t)(&n - &g_.nodes[0])]) break;   // the result shares its operand's storage
             check(mtl_copy_f32(ctx_, T(out), T(t1), t1.shape.num_elements(), 0), "copy forward");
             break;
         case MTL_OP_CONV2D: {
@@ -763,6 +793,8 @@ void Model::backward_op(const Node& n, int tensor_id) {
                                  n.attrs.axis ? *n.attrs.axis : -1, acc), "reduce backward");
             break;
         case MTL_OP_FLATTEN: case MTL_OP_RESHAPE: case MTL_OP_SQUEEZE: case MTL_OP_UNSQUEEZE:
+            // shared storage: the operand's gradient IS the result's gradient (this node is its only writer)
+            if (alias_node_[(size_t)(&n - &g_.nodes[0])]) break;
             check(mtl_copy_f32(ctx_, grad, ug, t1.shape.num_elements(), acc), "copy backward");
             break;
         case MTL_OP_CONV2D: {

@@ -127,6 +127,8 @@ class Model {
     std::vector<Symbol> trainable_;
     std::vector<Symbol> alloc_order_;
     std::vector<int64_t> trainable_off_;
+    std::map<int, int> alias_of_;              // result symbol of a copy node -> the operand whose storage it shares
+    std::vector<char> alias_node_;             // copy nodes that move no data
     std::map<int, bool> grad_written_;
     std::vector<int> never_written_;           // trainable symbols no backward node writes
     bool overwrite_first_ = true;
