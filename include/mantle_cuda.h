@@ -106,12 +106,24 @@ MTL_API int64_t mtl_launch_count(mtl_ctx* ctx);
 /* Reads and clears the device-side status word that bounded waits write on time-out. */
 MTL_API int32_t mtl_device_status(mtl_ctx* ctx, int32_t* out_status);
 MTL_API const char* mtl_version(void);
+/* Self-test of the bounded device-side wait: launches one small kernel that waits, for at most
+ * budget_us microseconds, on a barrier nothing will ever complete.  The wait gives up, the kernel
+ * writes MTL_ERR_TIMEOUT to the status word that mtl_device_status reads (and clears) and returns;
+ * the context stays usable.  *waited_us (may be null) receives how long the kernel waited.  It shows
+ * that a lost completion inside a tensor-core kernel ends as a status code, not as a hung GPU. */
+MTL_API int32_t mtl_selftest_bounded_wait(mtl_ctx* ctx, int32_t budget_us, int32_t* waited_us);
 
 /* ---------------------------------------------------------------- memory ---------------- */
 
 /* Device storage behind Collection / Parameters (mantle/autograd/collection.mojo:175-222). */
 MTL_API int32_t mtl_malloc(mtl_ctx* ctx, size_t bytes, void** out_dptr);
 MTL_API int32_t mtl_free(mtl_ctx* ctx, void* dptr);
+/* Debug aid, no counterpart in the reference.  With MANTLE_CUDA_DEBUG=1 in the environment when a
+ * context is created, every mtl_malloc block sits between two 256-byte guard zones filled with a
+ * byte pattern; mtl_debug_check (also run by mtl_sync and mtl_free in that mode) waits for the
+ * stream and verifies them, returning MTL_ERR_INVALID with a message that names the damaged block,
+ * the side and the distance of the stray write.  Without the variable it returns MTL_OK at once. */
+MTL_API int32_t mtl_debug_check(mtl_ctx* ctx);
 /* Model.execute step 1, inputs into the arena (mantle/nn/model.mojo:117-119); src is host. */
 MTL_API int32_t mtl_h2d(mtl_ctx* ctx, void* dst, const void* src_host, size_t bytes);
 /* Model.forward's return / Model.inference's copies (model.mojo:99,108-110); dst is host;

@@ -87,8 +87,10 @@ SIGNATURES = {
     "mtl_launch_count": (_i64, [_vp]),
     "mtl_device_status": (_i32, [_vp, C.POINTER(_i32)]),
     "mtl_version": (C.c_char_p, []),
+    "mtl_selftest_bounded_wait": (_i32, [_vp, _i32, C.POINTER(_i32)]),
     "mtl_malloc": (_i32, [_vp, C.c_size_t, C.POINTER(_vp)]),
     "mtl_free": (_i32, [_vp, _vp]),
+    "mtl_debug_check": (_i32, [_vp]),
     "mtl_h2d": (_i32, [_vp, _vp, _vp, C.c_size_t]),
     "mtl_d2h": (_i32, [_vp, _vp, _vp, C.c_size_t]),
     "mtl_h2d_async": (_i32, [_vp, _vp, _vp, C.c_size_t]),
@@ -191,9 +193,11 @@ def host_lib() -> C.CDLL:
     global _host
     if _host is None:
         cuda_lib()
-        if not HOST_LIB_PATH.exists():
-            raise ImportError("%s is missing: build it with `python -m mantle_b200.build`" % HOST_LIB_PATH)
-        _host = C.CDLL(str(HOST_LIB_PATH))
+        import os
+        path = Path(os.environ.get("MANTLE_HOST_LIB") or HOST_LIB_PATH)   # another build of mantle_b200/host (sanitizer runs)
+        if not path.exists():
+            raise ImportError("%s is missing: build it with `python -m mantle_b200.build`" % path)
+        _host = C.CDLL(str(path))
         _host.mtlh_last_error.restype = C.c_char_p
         _host.mtlh_model_n_trainable.restype = C.c_int64
         _host.mtlh_trainer_input_bytes.restype = C.c_int64

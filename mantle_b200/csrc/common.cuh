@@ -30,6 +30,7 @@ struct mtl_tuning {
     int gemm_stages = -1;             // MANTLE_GEMM_STAGES: operand ring depth
     int gemm_split_k = -1;            // MANTLE_GEMM_SPLITK: 0 = never split the reduction, n >= 2 = n slices
     bool pdl = true;                  // MANTLE_PDL=0: plain stream order between the kernels of a step
+    bool debug_guards = false;        // MANTLE_CUDA_DEBUG=1: guard words around every mtl_malloc block, checked at mtl_sync
 };
 
 struct mtl_ctx {
@@ -50,6 +51,8 @@ struct mtl_ctx {
     // freed but parked on `retired` (freed when the last graph goes, or with the context).
     int live_graphs = 0;
     std::vector<void*> retired;
+    // debug guards (tune.debug_guards): user pointer -> payload bytes of every live mtl_malloc block
+    std::vector<std::pair<void*, size_t>> guarded;
     int64_t launches = 0;
     int64_t launches_at_capture = 0;
     int32_t* dev_status = nullptr;  // one word written by bounded device waits

@@ -3,6 +3,10 @@
 
 #include "common.cuh"
 
+// guard zones of the debug allocator (see mtl_debug_check)
+static constexpr size_t kGuardBytes = 256;
+static constexpr int kGuardByte = 0xA5;
+
 int32_t mtl_set_error(mtl_ctx* ctx, int32_t code, const char* fmt, ...) {
     if (ctx) {
         va_list ap;
@@ -69,6 +73,7 @@ static void read_tuning(mtl_tuning* t) {  // the only place the library reads it
     t->gemm_stages = env_int("MANTLE_GEMM_STAGES", -1);
     t->gemm_split_k = env_int("MANTLE_GEMM_SPLITK", -1);
     t->pdl = env_int("MANTLE_PDL", 1) != 0;
+    t->debug_guards = env_int("MANTLE_CUDA_DEBUG", 0) != 0;
 }
 
 const mtl_tuning& mtl_global_tuning() {
@@ -161,6 +166,7 @@ int32_t mtl_ctx_destroy(mtl_ctx* ctx) {
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->ws2) cudaFree(ctx->ws2);
     for (void* p : ctx->retired) cudaFree(p);
+    for (auto& g : ctx->guarded) cudaFree((uint8_t*)g.first - kGuardBytes);   // blocks the caller never freed
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -205,6 +211,7 @@ int32_t mtl_ctx_workspace_info(mtl_ctx* ctx, size_t* bytes, void** block, int32_
 int32_t mtl_sync(mtl_ctx* ctx) {
     MTL_CHECK_CTX(ctx);
     MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->tune.debug_guards && !ctx->capturing) return mtl_debug_check(ctx);
     return MTL_OK;
 }
 
@@ -223,16 +230,52 @@ int32_t mtl_device_status(mtl_ctx* ctx, int32_t* out_status) {
 
 // ------------------------------------------------------------------ memory ---------------
 
+// Debug guards (MANTLE_CUDA_DEBUG=1): every mtl_malloc block is placed between two 256-byte guard
+// zones filled with a byte pattern.  A kernel that writes a little past either end of a tensor then
+// damages a guard instead of a neighbouring allocation, and mtl_debug_check (called by mtl_sync and
+// mtl_free in this mode) names the block: which allocation, which side, at which byte.
+
+static int32_t check_guards(mtl_ctx* ctx, void* only) {
+    uint8_t host[2 * kGuardBytes];
+    for (size_t i = 0; i < ctx->guarded.size(); ++i) {
+        uint8_t* user = (uint8_t*)ctx->guarded[i].first;
+        if (only && user != only) continue;
+        const size_t bytes = ctx->guarded[i].second;
+        const size_t back_off = (bytes + 15) & ~(size_t)15;   // the rear guard starts at the next 16-byte boundary
+        MTL_CUDA(ctx, cudaMemcpy(host, user - kGuardBytes, kGuardBytes, cudaMemcpyDeviceToHost));
+        MTL_CUDA(ctx, cudaMemcpy(host + kGuardBytes, user + back_off, kGuardBytes, cudaMemcpyDeviceToHost));
+        for (size_t b = 0; b < 2 * kGuardBytes; ++b) {
+            if (host[b] == (uint8_t)kGuardByte) continue;
+            const bool front = b < kGuardBytes;
+            return mtl_set_error(ctx, MTL_ERR_INVALID,
+                                 "guard damaged: allocation #%zu (%zu bytes at %p) was written %s it, %zu bytes %s",
+                                 i, bytes, (void*)user, front ? "before" : "after",
+                                 front ? kGuardBytes - b : b - kGuardBytes + (back_off - bytes), front ? "before its start" : "past its end");
+        }
+    }
+    return MTL_OK;
+}
+
 int32_t mtl_malloc(mtl_ctx* ctx, size_t bytes, void** out_dptr) {
     MTL_CHECK_CTX(ctx);
     MTL_REQUIRE(ctx, out_dptr, "null out pointer");
     *out_dptr = nullptr;
     if (bytes == 0) bytes = 4;
-    cudaError_t e = cudaMalloc(out_dptr, bytes);
+    const bool guard = ctx->tune.debug_guards;
+    const size_t back_off = (bytes + 15) & ~(size_t)15;
+    void* raw = nullptr;
+    cudaError_t e = cudaMalloc(&raw, guard ? back_off + 2 * kGuardBytes : bytes);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return mtl_set_error(ctx, MTL_ERR_NOMEM, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
     }
+    if (guard) {
+        MTL_CUDA(ctx, cudaMemset(raw, kGuardByte, kGuardBytes));
+        MTL_CUDA(ctx, cudaMemset((uint8_t*)raw + kGuardBytes + back_off, kGuardByte, kGuardBytes));
+        raw = (uint8_t*)raw + kGuardBytes;
+        ctx->guarded.push_back({raw, bytes});
+    }
+    *out_dptr = raw;
     return MTL_OK;
 }
 
@@ -240,8 +283,25 @@ int32_t mtl_free(mtl_ctx* ctx, void* dptr) {
     MTL_CHECK_CTX(ctx);
     if (!dptr) return MTL_OK;
     MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->tune.debug_guards) {
+        for (size_t i = 0; i < ctx->guarded.size(); ++i) {
+            if (ctx->guarded[i].first != dptr) continue;
+            int32_t rc = check_guards(ctx, dptr);
+            ctx->guarded.erase(ctx->guarded.begin() + (long)i);
+            cudaFree((uint8_t*)dptr - kGuardBytes);
+            return rc;
+        }
+    }
     MTL_CUDA(ctx, cudaFree(dptr));
     return MTL_OK;
+}
+
+int32_t mtl_debug_check(mtl_ctx* ctx) {
+    MTL_CHECK_CTX(ctx);
+    if (!ctx->tune.debug_guards) return MTL_OK;
+    MTL_REQUIRE(ctx, !ctx->capturing, "guards cannot be checked during stream capture");
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return check_guards(ctx, nullptr);
 }
 
 int32_t mtl_h2d(mtl_ctx* ctx, void* dst, const void* src_host, size_t bytes) {

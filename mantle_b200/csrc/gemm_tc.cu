@@ -262,6 +262,27 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
     }
 }
 
+// Self-test of the bounded wait every tensor-core kernel is built on: one CTA initialises an mbarrier
+// that nothing will ever arrive on and waits for it with the given budget.  The wait must give up, the
+// kernel must record MTL_ERR_TIMEOUT in the context's status word and return normally.
+__global__ void k_bounded_wait_selftest(int32_t* status, uint64_t budget_ns, int32_t* waited_us) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint64_t t0 = globaltimer_ns();
+        const bool ok = mbar_wait(&bar, 0, &abort_flag, budget_ns);
+        if (waited_us) *waited_us = (int32_t)((globaltimer_ns() - t0) / 1000);
+        if (!ok) atomicExch(status, MTL_ERR_TIMEOUT);
+    }
+    __syncthreads();
+}
+
 // hi = x rounded to tf32 (low 13 mantissa bits zero), lo = x - hi (exact in fp32)
 __global__ void __launch_bounds__(256) k_split_tf32(float* __restrict__ hi, float* __restrict__ lo,
                                                     const float* __restrict__ x, int64_t n) {
@@ -437,6 +458,24 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
 }
 
 extern "C" {
+
+int32_t mtl_selftest_bounded_wait(mtl_ctx* ctx, int32_t budget_us, int32_t* waited_us) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, budget_us >= 1 && budget_us <= 1000000, "budget must be 1 .. 1000000 microseconds");
+    MTL_REQUIRE(ctx, !ctx->capturing, "the self-test reads its result back and cannot be captured");
+    int32_t* d_waited = nullptr;
+    void* ws;
+    int32_t rc = mtl_workspace(ctx, 256, &ws);
+    if (rc) return rc;
+    d_waited = (int32_t*)ws;
+    k_bounded_wait_selftest<<<1, 32, 0, ctx->stream>>>(ctx->dev_status, (uint64_t)budget_us * 1000ull, d_waited);
+    MTL_LAUNCHED(ctx);
+    if (waited_us) {
+        MTL_CUDA(ctx, cudaMemcpyAsync(waited_us, d_waited, 4, cudaMemcpyDeviceToHost, ctx->stream));
+        MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    return MTL_OK;
+}
 
 int32_t mtl_dot_fwd(mtl_ctx* ctx, float* C, const float* A, const float* B, int64_t M, int64_t K, int64_t N) {
     MTL_CHECK_CTX(ctx);

@@ -42,8 +42,15 @@ def build(force: bool = False) -> Path:
 
 
 def lib() -> C.CDLL:
+    """The C restatement.  MANTLE_ORACLE_LIB names another build of mantle_oracle.c to load instead (the
+    sanitizer run of the CPU tests points it at an ASan + UBSan build)."""
     global _lib
     if _lib is None:
+        import os
+        override = os.environ.get("MANTLE_ORACLE_LIB")
+        if override:
+            _lib = C.CDLL(override)
+            return _lib
         if not _LIB_PATH.exists():
             build()
         _lib = C.CDLL(str(_LIB_PATH))

@@ -866,3 +866,24 @@ def test_one_hot_on_device(ctx):
     out = ctx.empty((4, 3))
     ctx._check(ctx.lib.mtl_one_hot_f32(ctx.handle, out.ptr, ctx.array(lab).ptr, 4, 3))
     assert np.array_equal(out.numpy(), oracle.one_hot(lab, 3)) and out.numpy()[1].sum() == 0 and out.numpy()[2].sum() == 0
+
+
+def test_bounded_wait_runs_out_and_the_context_stays_usable(ctx):
+    """A device-side wait that can never complete gives up after its budget (1 ms here), the kernel
+    reports MTL_ERR_TIMEOUT through the context's status word and returns; the next operator works
+    and the status reads clean again.  Nothing faults or hangs: the wait is the same bounded wait all
+    tensor-core kernels use (with a 4 s budget that a correct run never reaches)."""
+    import ctypes as C
+    assert ctx.device_status() == 0
+    waited = C.c_int32()
+    ctx._check(ctx.lib.mtl_selftest_bounded_wait(ctx.handle, 1000, C.byref(waited)))
+    assert 900 <= waited.value < 100000, "waited %d us for a 1000 us budget" % waited.value
+    assert ctx.device_status() == 5          # MTL_ERR_TIMEOUT, read and cleared
+    assert ctx.device_status() == 0
+    rng = np.random.default_rng(77)
+    a = rng.normal(0, 1, (256, 128)).astype(np.float32)
+    b = rng.normal(0, 1, (128, 256)).astype(np.float32)
+    got = run_fwd(ctx, OP.DOT, (256, 256), a, b)
+    assert rel_err(got, a.astype(np.float64) @ b) < 3e-5
+    assert ctx.device_status() == 0
+    assert ctx.lib.mtl_selftest_bounded_wait(ctx.handle, 0, None) == 1     # MTL_ERR_INVALID
