@@ -170,6 +170,26 @@ MTL_API int32_t mtl_dot_bwd(mtl_ctx* ctx, int32_t tensor_id, float* grad, const 
                             const float* A, const float* B, int64_t M, int64_t K, int64_t N,
                             int32_t accumulate);
 
+/* nn.Linear, i.e. the DOT node and the ADD of the bias that follows it (mantle/nn/layers/linear.mojo:25-46),
+ * as one call each way.  No single counterpart in the reference: each call gives the result of the
+ * reference's operator calls named below.
+ *   mtl_linear_fwd   C[M,N] = A[M,K] . B[K,N] + bias[N]: DOT.forward (basics.mojo:230-237) followed by
+ *                    ADD.forward with the bias broadcast over the rows (basics.mojo:21-43); bias may be null.
+ *   mtl_linear_bwd   from the upper gradient ug[M,N] of the ADD's result: dA (+)= ug . B^T and
+ *                    dB (+)= A^T . ug (DOT.backward, basics.mojo:240-257), dbias (+)= column sums of ug
+ *                    (ADD.backward with un-broadcasting, basics.mojo:46-66, tensorutils.mojo:455-487).  Any of
+ *                    dA, dB, dbias may be null; each has its own accumulate flag.
+ * For N <= 16 outside MTL_MATH_FP32 each call is ONE launch: the sums over k (forward) and over the
+ * batch (dB) are cut into slices, and the block that finishes last for a group of rows folds the slices
+ * in ascending order, so the result does not depend on scheduling (fp32 FMA on CUDA cores; the sums
+ * are re-associated with respect to the reference's chain, within rtol = atol = 1e-5).  Other shapes
+ * and MTL_MATH_FP32 run the separate operator entry points. */
+MTL_API int32_t mtl_linear_fwd(mtl_ctx* ctx, float* C, const float* A, const float* B, const float* bias,
+                               int64_t M, int64_t K, int64_t N);
+MTL_API int32_t mtl_linear_bwd(mtl_ctx* ctx, float* dA, float* dB, float* dbias, const float* ug,
+                               const float* A, const float* B, int64_t M, int64_t K, int64_t N,
+                               int32_t acc_da, int32_t acc_db, int32_t acc_dbias);
+
 /* ---------------------------------------------------------------- CONV2D ---------------- */
 
 /* Geometry shared by the convolution and pooling entry points; the index lists are the
@@ -399,8 +419,9 @@ MTL_API int32_t mtl_adam_step(mtl_ctx* ctx, float* params, const float* grads, f
                               float eps, int32_t t, float grad_scale);
 
 /* Same step with the iteration count kept in device memory: `t_dev` (one int32, start it at 0)
- * is incremented on the stream before the update reads it, so the call can sit inside a captured
- * step that is replayed many times (Adam.iter, optim.mojo:59,96). */
+ * holds the number of steps taken; the update runs as step *t_dev + 1 and stores that number back
+ * when it is done, so the call can sit inside a captured step that is replayed many times
+ * (Adam.iter, optim.mojo:59,96). */
 MTL_API int32_t mtl_adam_step_dev(mtl_ctx* ctx, float* params, const float* grads, float* m,
                                   float* v, int64_t n, float lr, float beta1, float beta2,
                                   float eps, int32_t* t_dev, float grad_scale);

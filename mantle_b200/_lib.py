@@ -103,6 +103,8 @@ SIGNATURES = {
     "mtl_copy_f32": (_i32, [_vp, _vp, _vp, _i64, _i32]),
     "mtl_dot_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64]),
     "mtl_dot_bwd": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),
+    "mtl_linear_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64]),
+    "mtl_linear_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32]),
     "mtl_conv2d_out_shape": (_i32, [_pdesc, C.POINTER(_i32), C.POINTER(_i32)]),
     "mtl_conv2d_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _pdesc]),
     "mtl_conv2d_bwd": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _pdesc, _i32]),

@@ -25,9 +25,6 @@ __host__ __device__ __forceinline__ float pow_int(float b, int e) {
     return r;
 }
 
-__global__ void k_bump(int32_t* t) {
-    mtl_pdl_sync(); *t += 1; }
-
 __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, const AdamK& k) {
     g *= k.gscale;
     m = k.b1 * m + k.omb1 * g;       // beta1 * momentum + (1 - beta1) * grad
@@ -39,10 +36,13 @@ __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, 
 
 __global__ void __launch_bounds__(kBlock) k_adam(float* __restrict__ p, const float* __restrict__ g,
                                                  float* __restrict__ m, float* __restrict__ v, int64_t n,
-                                                 AdamK k, int vec, const int32_t* __restrict__ t_dev) {
+                                                 AdamK k, int vec, int32_t* __restrict__ t_dev,
+                                                 int32_t* __restrict__ ticket) {
     mtl_pdl_sync();
+    int t = 0;
     if (t_dev) {
-        int t = *t_dev;
+        // the step count lives on the device (captured steps are replayed): this step is number *t_dev + 1
+        t = *reinterpret_cast<volatile int32_t*>(t_dev) + 1;
         k.c1 = 1.0f - pow_int(k.b1, t);
         k.c2 = 1.0f - pow_int(k.b2, t);
     }
@@ -66,6 +66,15 @@ __global__ void __launch_bounds__(kBlock) k_adam(float* __restrict__ p, const fl
     } else {
         for (int64_t i = tid; i < n; i += stride) adam_one(p[i], g[i], m[i], v[i], k);
     }
+    if (t_dev) {
+        // every block has read the old count before it takes a ticket; the block that takes the last one
+        // stores the new count and puts the ticket counter back
+        __syncthreads();
+        if (threadIdx.x == 0 && atomicAdd(ticket, 1) == (int)gridDim.x - 1) {
+            *t_dev = t;
+            *ticket = 0;
+        }
+    }
 }
 
 }  // namespace
@@ -75,11 +84,6 @@ static int32_t adam_launch(mtl_ctx* ctx, float* params, const float* grads, floa
                            int32_t* t_dev) {
     MTL_REQUIRE(ctx, n >= 0 && ((params && grads && m && v) || n == 0), "null pointer in mtl_adam_step");
     MTL_REQUIRE(ctx, t_dev || t >= 1, "Adam iteration count must be >= 1, got %d", t);
-    if (t_dev) {
-        mtl_launch_pdl(ctx, k_bump, dim3(1), dim3(1), (size_t)(0), t_dev);
-        MTL_LAUNCHED(ctx);
-    }
-    if (n == 0) return MTL_OK;
     AdamK k;
     k.lr = lr; k.b1 = beta1; k.b2 = beta2; k.eps = eps;
     k.omb1 = 1.0f - beta1;
@@ -89,8 +93,9 @@ static int32_t adam_launch(mtl_ctx* ctx, float* params, const float* grads, floa
     k.c2 = 1.0f - pow_int(beta2, t_dev ? 1 : t);
     k.gscale = grad_scale;
     int vec = ((((uintptr_t)params) | ((uintptr_t)grads) | ((uintptr_t)m) | ((uintptr_t)v)) & 15u) == 0;
+    if (n == 0 && !t_dev) return MTL_OK;
     int grid = mtl_grid_for((n + 3) / 4, kBlock, ctx->sm_count, 8);
-    mtl_launch_pdl(ctx, k_adam, dim3(grid), dim3(kBlock), (size_t)(0), params, grads, m, v, n, k, vec, t_dev);
+    mtl_launch_pdl(ctx, k_adam, dim3(grid), dim3(kBlock), (size_t)(0), params, grads, m, v, n, k, vec, t_dev, ctx->tickets + 8191);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }

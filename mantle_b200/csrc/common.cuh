@@ -20,6 +20,7 @@ struct mtl_tuning {
     bool log_errors = false;          // MANTLE_CUDA_LOG=1: print every recorded error to stderr
     bool conv_channel_major = true;   // MANTLE_CONV_CHANNEL_MAJOR=0 switches the channel-major implicit GEMM off
     bool conv_paired = true;          // MANTLE_CONV_PAIRED=0: one filter tap per instruction
+    int conv_paired_min_kblocks = 8;  // MANTLE_CONV_PAIRED_MIN_KB: shortest reduction (k-blocks per tile) that pairs taps
     bool conv_spread = true;          // MANTLE_CONV_SPREAD=0: plain row order of the pixel boxes
     bool conv_pool_epilogue = true;   // MANTLE_CONV_POOL_EPILOGUE=0: conv -> ReLU -> pool through scratch memory
     bool conv_first_tc = true;        // MANTLE_CONV_FIRST_TC=0: first layer on the CUDA-core kernels in every mode
@@ -56,6 +57,9 @@ struct mtl_ctx {
     int64_t launches = 0;
     int64_t launches_at_capture = 0;
     int32_t* dev_status = nullptr;  // one word written by bounded device waits
+    // 8192 zeroed counters behind the status word: kernels that fold their own partial results count
+    // the blocks that have finished a group here; the block that folds puts the counter back to zero
+    int32_t* tickets = nullptr;
     char err[512] = {0};
     cudaEvent_t t0[MTL_NUM_TIMERS] = {0};
     cudaEvent_t t1[MTL_NUM_TIMERS] = {0};

@@ -64,6 +64,7 @@ static void read_tuning(mtl_tuning* t) {  // the only place the library reads it
     t->conv_channel_major = env_int("MANTLE_CONV_CHANNEL_MAJOR", 1) != 0;
     t->conv_paired = env_int("MANTLE_CONV_PAIRED", 1) != 0;
     t->conv_spread = env_int("MANTLE_CONV_SPREAD", 1) != 0;
+    t->conv_paired_min_kblocks = env_int("MANTLE_CONV_PAIRED_MIN_KB", 8);
     t->conv_pool_epilogue = env_int("MANTLE_CONV_POOL_EPILOGUE", 1) != 0;
     t->conv_first_tc = env_int("MANTLE_CONV_FIRST_TC", 1) != 0;
     t->gemm_3d_boxes = getenv("MANTLE_GEMM_NO3D") == nullptr;
@@ -125,12 +126,14 @@ int32_t mtl_ctx_create(int32_t device, mtl_ctx** out) {
     ctx->owns_stream = true;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
-    if (cudaMalloc((void**)&ctx->dev_status, 256) != cudaSuccess ||
-        cudaMemset(ctx->dev_status, 0, 256) != cudaSuccess) {
+    const size_t status_bytes = 256 + 8192 * sizeof(int32_t);
+    if (cudaMalloc((void**)&ctx->dev_status, status_bytes) != cudaSuccess ||
+        cudaMemset(ctx->dev_status, 0, status_bytes) != cudaSuccess) {
         cudaStreamDestroy(ctx->stream);
         delete ctx;
         return MTL_ERR_CUDA;
     }
+    ctx->tickets = ctx->dev_status + 64;
     const char* mode = getenv("MANTLE_CUDA_MATH");
     if (mode) {
         if (!strcmp(mode, "fp32")) ctx->math_mode = MTL_MATH_FP32;

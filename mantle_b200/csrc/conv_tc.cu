@@ -819,15 +819,17 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride + c * 32), r);
                 if (p.paired == 1) {
-                    // lanes 16-31 hold the second tap of the channels of lanes 0-15: fetch it one
-                    // column to the right and add it across the warp
+                    // lanes 16-31 hold the second tap of the channels of lanes 0-15, which belongs to the pixel
+                    // one column to the left: those lanes take their values one column to the right.  The two
+                    // halves meet in the transposition block below (row ch and row ch + 16), where the reading
+                    // side adds them -- no warp shuffles, which would compete with the main loop for the
+                    // shared-memory pipe.
                     uint32_t r2[32];
                     tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride + c * 32 + 1), r2);
                     tmem_ld_wait();
+                    if (lane >= 16) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float u = __shfl_down_sync(0xffffffffu, __uint_as_float(r2[i]), 16);
-                        r[i] = __float_as_uint(__uint_as_float(r[i]) + u);
+                        for (int i = 0; i < 32; ++i) r[i] = r2[i];
                     }
                 } else {
                     tmem_ld_wait();
@@ -837,7 +839,7 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                 for (int g = 0; g < 8; ++g) {
                     float4 o = make_float4(__uint_as_float(r[g * 4]) + bv, __uint_as_float(r[g * 4 + 1]) + bv,
                                            __uint_as_float(r[g * 4 + 2]) + bv, __uint_as_float(r[g * 4 + 3]) + bv);
-                    if (p.relu) {  // RELU.forward: x > 0 ? x : 0
+                    if (p.relu && p.paired != 1) {  // RELU.forward: x > 0 ? x : 0 (paired: after the halves are added)
                         o.x = o.x > 0.0f ? o.x : 0.0f; o.y = o.y > 0.0f ? o.y : 0.0f;
                         o.z = o.z > 0.0f ? o.z : 0.0f; o.w = o.w > 0.0f ? o.w : 0.0f;
                     }
@@ -853,7 +855,15 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                         const int ch = it * 4 + chl;
                         const int kk = p.paired ? quad * 16 + ch : kt * BM + quad * 32 + ch;
                         if (kk < p.Kout && (!p.paired || ch < 16)) {
-                            const float4 val = *reinterpret_cast<const float4*>(stg + ch * 36 + sub * 4);
+                            float4 val = *reinterpret_cast<const float4*>(stg + ch * 36 + sub * 4);
+                            if (p.paired == 1) {
+                                const float4 v2 = *reinterpret_cast<const float4*>(stg + (ch + 16) * 36 + sub * 4);
+                                val.x += v2.x; val.y += v2.y; val.z += v2.z; val.w += v2.w;
+                                if (p.relu) {
+                                    val.x = val.x > 0.0f ? val.x : 0.0f; val.y = val.y > 0.0f ? val.y : 0.0f;
+                                    val.z = val.z > 0.0f ? val.z : 0.0f; val.w = val.w > 0.0f ? val.w : 0.0f;
+                                }
+                            }
                             float* base = p.out + (int64_t)kk * plane;
                             if (vec) {
                                 float4* dst = reinterpret_cast<float4*>(base + o0);
@@ -938,8 +948,8 @@ bool igemm_paired(const IgemmCall& c) {
     // Pairing shortens the main loop but lengthens the epilogue (second TMEM read, shuffles): it pays
     // only when the reduction per tile is long enough for the main loop to be the longer of the two.
     const int paired_kblocks = c.R * ((c.S + 1) / 2) * ((c.Cin + 31) / 32);
-    return igemm_channel_major(c) && c.Kout <= 64 && c.S >= 2 && c.OW + 1 <= 240 && paired_kblocks >= 32 &&
-           mtl_global_tuning().conv_paired;
+    return igemm_channel_major(c) && c.Kout <= 64 && c.S >= 2 && c.OW + 1 <= 240 &&
+           paired_kblocks >= mtl_global_tuning().conv_paired_min_kblocks && mtl_global_tuning().conv_paired;
 }
 // At most 64 output channels without pairing: the channels are still spread over the four TMEM lane
 // quadrants (16 each) so that all four epilogue warps store, instead of two doing all of it.

@@ -46,7 +46,52 @@ struct GemmParams {
     int32_t* status;
     int a3d, b3d;     // MN-major operand fetched as one 3-D box {32, BK, chunks} instead of one box per chunk
     int stages;       // ring depth actually used (<= the configuration's maximum)
+    // Stream-K schedule (sk != 0): the tiles' k-blocks, laid end to end, are dealt out evenly over the
+    // CTAs, so that a problem with fewer tiles than SMs -- or a tile count that leaves most of the last
+    // wave idle -- still keeps every SM busy.  A CTA then works on up to two partial tiles (the first and
+    // the last of its range).  Every part of a split tile is written to scratch memory; the CTA that
+    // finishes the last part of a tile (a ticket counter per tile) adds the parts in ascending k order
+    // and stores the tile, so the result does not depend on which CTA runs when.
+    int sk;
+    int sk_grid;            // CTAs of the launch: at most four per tile, so that a tile has few parts
+    long long sk_q, sk_r;   // CTA c covers units [c*q + min(c, r), (c+1)*q + min(c+1, r))
+    float* sk_scratch;      // [gridDim.x][2][tile rows][BN]
+    int32_t* sk_tickets;    // one counter per tile, zero between launches
 };
+
+// Walks the (tile, k-block range) segments of one CTA; identical in the three roles of the kernel.
+struct SegIter {
+    int sk, G, num_tiles, kb_total, t, first;
+    long long u, u_end;
+    __device__ __forceinline__ static long long start_of(long long c, long long q, long long r) { return c * q + (c < r ? c : r); }
+    __device__ __forceinline__ void init(const GemmParams& p, int num_tiles_, int kb_total_) {
+        sk = p.sk; G = gridDim.x; num_tiles = num_tiles_; kb_total = kb_total_; t = blockIdx.x; first = 1;
+        u = start_of(blockIdx.x, p.sk_q, p.sk_r);
+        u_end = start_of(blockIdx.x + 1, p.sk_q, p.sk_r);
+    }
+    // slot: -1 for a whole tile, else which of this CTA's two scratch tiles the part goes to
+    __device__ __forceinline__ bool next(int& tile, int& kb0, int& kb1, int& slot) {
+        if (!sk) {
+            if (t >= num_tiles) return false;
+            tile = t; kb0 = 0; kb1 = kb_total; slot = -1; t += G;
+            return true;
+        }
+        if (u >= u_end) return false;
+        tile = (int)(u / kb_total);
+        kb0 = (int)(u - (long long)tile * kb_total);
+        const long long left = u_end - u;
+        kb1 = (long long)kb0 + left < (long long)kb_total ? kb0 + (int)left : kb_total;
+        slot = (kb0 == 0 && kb1 == kb_total) ? -1 : (first ? 0 : 1);
+        first = 0;
+        u += kb1 - kb0;
+        return true;
+    }
+};
+
+// The CTA whose range contains unit u (inverse of SegIter::start_of).
+__device__ __forceinline__ int cta_of_unit(long long u, long long q, long long r) {
+    return u < (q + 1) * r ? (int)(u / (q + 1)) : (int)(r + (u - (q + 1) * r) / q);
+}
 
 // Tile order: groups of 16 tile-rows; inside a group the tile-column changes slowest so that
 // CTAs running at the same time share B tiles and a bounded set of A tiles in L2.
@@ -77,6 +122,7 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
     uint64_t* tmem_empty = tmem_full + 2;         // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* fold_flag = abort_flag + 1;   // epilogue warps: does this CTA fold the tile it just finished a part of
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -120,11 +166,14 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            SegIter it;
+            it.init(p, num_tiles, kb_total);
+            int t, kb0, kb1, slot;
+            while (ok && it.next(t, kb0, kb1, slot)) {
                 int tm, tn;
                 tile_coords(t, tiles_m, tiles_n, tm, tn);
                 const int m0 = tm * BMT, n0 = tn * BN;
-                for (int kb = 0; kb < kb_total; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
                     const int seg = kb / kb_per_seg;
                     const int k0 = (kb - seg * kb_per_seg) * BK;
@@ -169,13 +218,16 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
             uint32_t phase = 0;
             bool ok = true;
             int local = 0;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+            SegIter it;
+            it.init(p, num_tiles, kb_total);
+            int t, kb0, kb1, slot;
+            for (; ok && it.next(t, kb0, kb1, slot); ++local) {
                 const int acc = local % C::kAccs;
                 const uint32_t acc_phase = (uint32_t)(local / C::kAccs) & 1u;
                 if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < kb_total; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&full[stage], phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t sa = smem_u32(tiles + stage * C::kStageBytes);
@@ -187,7 +239,7 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
                         for (int h = 0; h < MT; ++h) {  // the halves of a 256-row tile: 16 KB apart in both layouts
                             const uint32_t sah = sa + (uint32_t)h * (BM * BK * 4);
                             const uint64_t da = A_MN ? desc_mn_major(sah, kk) : desc_k_major(sah, kk);
-                            mma_tf32(tmem_d + (uint32_t)(h * BN), da, db, idesc, (kb | kk) ? 1u : 0u);
+                            mma_tf32(tmem_d + (uint32_t)(h * BN), da, db, idesc, (kb > kb0 || kk) ? 1u : 0u);
                         }
                     }
                     mma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
@@ -203,7 +255,10 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
         const bool vec_ok = (p.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
         bool ok = true;
         int local = 0;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+        SegIter it;
+        it.init(p, num_tiles, kb_total);
+        int t, kb0, kb1, slot;
+        for (; ok && it.next(t, kb0, kb1, slot); ++local) {
             int tm, tn;
             tile_coords(t, tiles_m, tiles_n, tm, tn);
             const int acc = local % C::kAccs;
@@ -211,6 +266,98 @@ k_gemm_tf32(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ C
             if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
             tc_fence_after_sync();
             const int n_base = tn * BN;
+            if (slot >= 0) {
+                // ---- a part of a split tile: park it in scratch memory, then see who finishes the tile
+                float* part = p.sk_scratch + ((size_t)blockIdx.x * 2 + slot) * ((size_t)BMT * BN);
+#pragma unroll 1
+                for (int hc = 0; hc < MT * (BN / 32); ++hc) {
+                    const int h = hc / (BN / 32), c = hc - h * (BN / 32);
+                    const int row = h * BM + quad * 32 + lane;
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)((acc + h) * BN + c * 32), r);
+                    tmem_ld_wait();
+                    // layout of a part: [chunk of 32 columns][group of 4 columns][row of the 128-row half]: the
+                    // 32 lanes of a warp write 512 contiguous bytes per store
+                    float4* dst = reinterpret_cast<float4*>(part) + (size_t)hc * 8 * 128 + quad * 32 + lane;
+                    (void)row;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        dst[j * 128] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                }
+                tc_fence_before_sync();
+                mbar_arrive(&tmem_empty[acc]);          // the accumulator is free for the next segment
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const long long u_lo = (long long)t * kb_total, u_hi = u_lo + kb_total - 1;
+                const int c_lo = cta_of_unit(u_lo, p.sk_q, p.sk_r), c_hi = cta_of_unit(u_hi, p.sk_q, p.sk_r);
+                if (threadIdx.x == 64) *fold_flag = atomicAdd(&p.sk_tickets[t], 1) == c_hi - c_lo;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (!*fold_flag) continue;
+                __threadfence();
+                // ---- the last part is in: add the parts in ascending k order and store the tile
+#pragma unroll 1
+                for (int hc = 0; hc < MT * (BN / 32); ++hc) {
+                    const int h = hc / (BN / 32), c = hc - h * (BN / 32);
+                    const int row = h * BM + quad * 32 + lane;
+                    const int m = tm * BMT + row;
+                    const int n0 = n_base + c * 32;
+                    if (m >= p.M || n0 >= p.N) continue;
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+                    // two parts at a time: sixteen 16-byte loads in flight per thread, added in ascending k order
+                    for (int cc = c_lo; cc <= c_hi; cc += 2) {
+                        // a CTA that starts inside this tile holds the part in its first scratch tile, one that
+                        // ends inside it (having started earlier) in its second
+                        const int sl0 = SegIter::start_of(cc, p.sk_q, p.sk_r) >= u_lo ? 0 : 1;
+                        const bool two = cc + 1 <= c_hi;
+                        const float4* s0 = reinterpret_cast<const float4*>(p.sk_scratch + ((size_t)cc * 2 + sl0) * ((size_t)BMT * BN)) +
+                                           (size_t)hc * 8 * 128 + quad * 32 + lane;
+                        const float4* s1 = reinterpret_cast<const float4*>(p.sk_scratch + ((size_t)(cc + 1) * 2) * ((size_t)BMT * BN)) +
+                                           (size_t)hc * 8 * 128 + quad * 32 + lane;   // a later part always starts inside the tile
+                        float4 a4[8], b4[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) a4[j] = __ldcg(s0 + j * 128);
+                        if (two) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) b4[j] = __ldcg(s1 + j * 128);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            v[4 * j] += a4[j].x; v[4 * j + 1] += a4[j].y; v[4 * j + 2] += a4[j].z; v[4 * j + 3] += a4[j].w;
+                        }
+                        if (two) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                v[4 * j] += b4[j].x; v[4 * j + 1] += b4[j].y; v[4 * j + 2] += b4[j].z; v[4 * j + 3] += b4[j].w;
+                            }
+                        }
+                    }
+                    float* crow = p.C + (int64_t)m * p.N;
+                    if (vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            if (n0 + j < p.N) {
+                                float4 o4 = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                float4* dst = reinterpret_cast<float4*>(crow + n0 + j);
+                                if (p.accumulate) {
+                                    const float4 o = *dst;
+                                    o4.x += o.x; o4.y += o.y; o4.z += o.z; o4.w += o.w;
+                                }
+                                *dst = o4;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + j < p.N) crow[n0 + j] = p.accumulate ? crow[n0 + j] + v[j] : v[j];
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) p.sk_tickets[t] = 0;   // ready for the next launch
+                continue;
+            }
 #pragma unroll 1
             for (int hc = 0; hc < MT * (BN / 32); ++hc) {
                 const int h = hc / (BN / 32), c = hc - h * (BN / 32);
@@ -313,7 +460,7 @@ int32_t launch_gemm(mtl_ctx* ctx, const CUtensorMap* maps, const GemmParams& p) 
     auto kern = k_gemm_tf32<BN, A_MN, B_MN, MT>;
     MTL_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     int tiles = ((p.M + BM * MT - 1) / (BM * MT)) * ((p.N + BN - 1) / BN);
-    int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    int grid = p.sk ? p.sk_grid : (tiles < ctx->sm_count ? tiles : ctx->sm_count);   // stream-K: equal shares of k-blocks
     {
         mtl_prof_scope prof(ctx, MTL_PROF_DOT_TC);
         kern<<<grid, kThreads, C::kSmemBytes, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
@@ -377,6 +524,8 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
     if (!mtl_gemm_tc_supported(M, N, K, transA, transB, A, B, C))
         return mtl_set_error(ctx, MTL_ERR_UNSUPPORTED, "shape not supported by the tensor-core DOT kernel");
     int BN = N >= 256 ? 256 : 128;
+    // few tiles: 128-column tiles put twice as many SMs to work (1024^3: 64 instead of 32)
+    if (BN == 256 && ((M + 127) / 128) * ((N + 255) / 256) * 2 <= ctx->sm_count) BN = 128;
     if (ctx->tune.gemm_bn == 128 || (ctx->tune.gemm_bn == 256 && N >= 256)) BN = ctx->tune.gemm_bn;
     // 256-row tiles when they do not cost waves: a 256 x 256 tile takes about 1.67x a 128 x 256 one
     int MT = 1;
@@ -385,17 +534,49 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
         const int64_t w1 = (t1 + ctx->sm_count - 1) / ctx->sm_count, w2 = (t2 + ctx->sm_count - 1) / ctx->sm_count;
         if ((double)w2 * 1.67 < (double)w1 && K >= 512) MT = 2;
     }
+    // Stream-K (see GemmParams::sk) when whole tiles would leave a large part of the last wave idle.  The
+    // schedule makes the wave count irrelevant, so the tile is then the largest one that still gives at
+    // least a third as many tiles as SMs (a tile is split over at most about three CTAs: the CTA that
+    // finishes a tile reads all of its parts back).
+    const int kb_units = (int)((K + BK - 1) / BK) * (x3 ? 3 : 1);
+    int sk = 0;
+    {
+        const int64_t tiles = ((M + BM * MT - 1) / (BM * MT)) * ((N + BN - 1) / BN);
+        const int64_t waves = (tiles + ctx->sm_count - 1) / ctx->sm_count;
+        const double fill = (double)tiles / (double)(waves * ctx->sm_count);
+        // (only for problems of at least one full wave: below that the parts' trip through memory costs more
+        // than the idle SMs; measured 1024^3 and 2048^3 slower, 4096^3 faster)
+        if (fill < 0.92 && kb_units >= 8 && tiles >= ctx->sm_count && ctx->tune.gemm_split_k != 0) sk = 1;
+        if (ctx->tune.gemm_split_k >= 1) sk = 1;
+        if (sk && ctx->tune.gemm_bn < 0 && ctx->tune.gemm_mt < 0) {
+            const int64_t want = (ctx->sm_count + 2) / 3;
+            const int64_t t22 = ((M + 255) / 256) * ((N + 255) / 256), t12 = ((M + 127) / 128) * ((N + 255) / 256);
+            if (N >= 256 && M >= 256 && K >= 512 && t22 >= want) { BN = 256; MT = 2; }
+            else if (N >= 256 && t12 >= want) { BN = 256; MT = 1; }
+            else { BN = 128; MT = 1; }
+        }
+    }
     if (ctx->tune.gemm_mt == 1 || (ctx->tune.gemm_mt == 2 && BN == 256 && M >= 256)) MT = ctx->tune.gemm_mt;
     const int BMT = BM * MT;
     const float* a_src[2] = {A, nullptr};
     const float* b_src[2] = {B, nullptr};
+    // scratch of the stream-K schedule: two tiles per CTA, behind the hi / lo operand copies
+    const size_t sk_floats = sk ? (size_t)ctx->sm_count * 2 * BMT * BN : 0;
+    float* sk_scratch = nullptr;
+    if (sk && !x3) {
+        void* ws;
+        int32_t rc = mtl_workspace(ctx, sk_floats * sizeof(float), &ws);
+        if (rc) return rc;
+        sk_scratch = (float*)ws;
+    }
     if (x3) {
         size_t na = (size_t)M * K, nb = (size_t)K * N;
         size_t na_pad = (na + 63) & ~(size_t)63, nb_pad = (nb + 63) & ~(size_t)63;
         void* ws;
-        int32_t rc = mtl_workspace(ctx, (2 * na_pad + 2 * nb_pad) * sizeof(float), &ws);
+        int32_t rc = mtl_workspace(ctx, (2 * na_pad + 2 * nb_pad + sk_floats) * sizeof(float), &ws);
         if (rc) return rc;
         float* w = (float*)ws;
+        sk_scratch = w + 2 * na_pad + 2 * nb_pad;
         float *ahi = w, *alo = w + na_pad, *bhi = w + 2 * na_pad, *blo = w + 2 * na_pad + nb_pad;
         int g1 = mtl_grid_for((int64_t)(na + 3) / 4, 256, ctx->sm_count, 8);
         k_split_tf32<<<g1, 256, 0, ctx->stream>>>(ahi, alo, A, (int64_t)na);
@@ -444,6 +625,20 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
     p.stages = MT == 2 ? 3 : (BN == 256 ? 4 : 6);
     p.a3d = a3d;
     p.b3d = b3d;
+    p.sk = 0; p.sk_grid = 0; p.sk_q = 0; p.sk_r = 0; p.sk_scratch = nullptr; p.sk_tickets = ctx->tickets;
+    {
+        const int64_t tiles = ((M + BMT - 1) / BMT) * ((N + BN - 1) / BN);
+        const int64_t units = tiles * kb_units;
+        int64_t grid = ctx->sm_count;
+        if (grid > tiles * 4) grid = tiles * 4;
+        if (sk && tiles <= 8190 && grid > tiles / 2 && units >= grid * 2) {
+            p.sk = 1;
+            p.sk_grid = (int)grid;
+            p.sk_q = units / grid;
+            p.sk_r = units % grid;
+            p.sk_scratch = sk_scratch;
+        }
+    }
     if (ctx->tune.gemm_stages >= 1 && ctx->tune.gemm_stages <= p.stages) p.stages = ctx->tune.gemm_stages;
     const bool a_mn = transA != 0, b_mn = transB == 0;
 #define MTL_DISPATCH(BN_, MT_)                                                                \

@@ -1,0 +1,343 @@
+// nn.Linear as the reference builds it -- a DOT node followed by an ADD of the bias
+// (mantle/nn/layers/linear.mojo:25-46) -- for layers with at most 16 outputs (classifier heads), as
+// ONE launch forward and ONE launch backward.  Such products are tiny in arithmetic and bound by
+// streaming the [M, K] activations once; run as separate operator calls they cost eight launches a
+// step (product, fold of the k-slices, bias add; bias gradient in two, the two operand gradients,
+// another fold), which at small batches is most of their time.
+//
+//   forward   C[M,N] (+)= A[M,K] . B[K,N] + bias[N]
+//             DOT.forward (basics.mojo:230-237) then ADD.forward with a broadcast bias (basics.mojo:21-43)
+//   backward  dA[M,K] (+)= ug . B^T, dB[K,N] (+)= A^T . ug      DOT.backward (basics.mojo:240-257)
+//             dbias[N] (+)= column sums of ug                   ADD.backward + un-broadcast (basics.mojo:46-66,
+//                                                               tensorutils.mojo:455-487)
+//
+// Sums over k (forward) and over the batch (dB) are split over many blocks so that the GPU is full at
+// any batch size; the slices are folded IN THE SAME LAUNCH, in ascending slice order, by whichever
+// block of a row group finishes last (a ticket counter per row group), so results do not depend on
+// the order in which blocks run.  Arithmetic is fp32 FMA on CUDA cores; the k sum is re-associated
+// with respect to the reference's ascending chain (compared at rtol = atol = 1e-5), so MTL_MATH_FP32,
+// which promises that chain bit for bit, takes the separate operator kernels instead.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kKC = 512;          // largest k extent of one forward block (rows of B staged in shared memory)
+constexpr int kTicketsFwd = 4096; // ticket slots [0, 4096) forward row groups, [4096, 8192) dB column groups
+
+// ------------------------------------------------------------------ forward --------------------
+template <int NQ>
+__global__ void __launch_bounds__(256, 3) k_linear_fwd(float* __restrict__ C, float* __restrict__ partial,
+                                                       int32_t* __restrict__ tickets, const float* __restrict__ A,
+                                                       const float* __restrict__ B, const float* __restrict__ bias,
+                                                       int M, int N, int K, int kc, int accumulate) {
+    constexpr int NP = 4 * NQ;
+    __shared__ __align__(16) float b_s[kKC * 20];
+    __shared__ int s_last;
+    mtl_pdl_sync();
+    const int k_begin = blockIdx.y * kc;
+    const int kn = min(kc, K - k_begin);
+    for (int i = threadIdx.x; i < kn * 16; i += 256) {
+        const int kk = i >> 4, j = i & 15;
+        b_s[kk * 20 + j] = j < N ? __ldg(B + (int64_t)(k_begin + kk) * N + j) : 0.0f;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = (blockIdx.x * 8 + warp) * 4;   // rows past M load zeros and store nothing
+    float acc[4][NP];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int j = 0; j < NP; ++j) acc[r][j] = 0.0f;
+    const float* a0 = A + (int64_t)m0 * K + k_begin;
+    // four k steps at a time: their sixteen loads of A are in flight together
+    for (int kk0 = lane; kk0 < kn; kk0 += 128) {
+        float a[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                a[u][r] = (kk0 + 32 * u < kn && m0 + r < M) ? __ldg(a0 + (int64_t)r * K + kk0 + 32 * u) : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int kk = kk0 + 32 * u;
+            if (kk < kn) {
+                float b[NP];
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) {
+                    const float4 t = *reinterpret_cast<const float4*>(b_s + kk * 20 + q * 4);
+                    b[q * 4] = t.x; b[q * 4 + 1] = t.y; b[q * 4 + 2] = t.z; b[q * 4 + 3] = t.w;
+                }
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) acc[r][j] = fmaf(a[u][r], b[j], acc[r][j]);
+            }
+        }
+    }
+    // the 32 lanes' partial sums of a row meet in shared memory; lane j adds column j over the lanes
+    float* out = partial + (int64_t)blockIdx.y * M * N;
+    __syncthreads();                              // every warp is done with the rows of B: their memory is reused
+    float* rs = b_s + warp * 32 * (NP + 1);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < NP; ++j) rs[lane * (NP + 1) + j] = acc[r][j];
+        __syncwarp();
+        if (lane < N && m0 + r < M) {
+            float s = 0.0f;
+#pragma unroll 8
+            for (int l = 0; l < 32; ++l) s += rs[l * (NP + 1) + lane];
+            out[(int64_t)(m0 + r) * N + lane] = s;
+        }
+    }
+    // ---- the block that finishes last for this group of 32 rows folds the k slices, in ascending order
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(&tickets[blockIdx.x], 1) == (int)gridDim.y - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int nsplit = gridDim.y;
+    for (int idx = threadIdx.x; idx < 32 * N; idx += 256) {
+        const int row = idx / N, col = idx - row * N;
+        const int m = blockIdx.x * 32 + row;
+        if (m >= M) continue;
+        float s = 0.0f;
+        for (int sp = 0; sp < nsplit; ++sp) s += __ldcg(partial + ((int64_t)sp * M + m) * N + col);
+        if (bias) s += __ldg(bias + col);         // ADD.forward after DOT.forward
+        float* c = C + (int64_t)m * N + col;
+        *c = accumulate ? *c + s : s;
+    }
+    if (threadIdx.x == 0) tickets[blockIdx.x] = 0;   // ready for the next launch
+}
+
+// ------------------------------------------------------------------ backward -------------------
+struct LinBwd {
+    float* dA; float* dB; float* dbias;
+    const float* ug; const float* A; const float* B;
+    float* partial;          // [msplit][K][N] slices of dB
+    int32_t* tickets;        // one per group of 256 columns of A (= rows of dB)
+    int M, N, K;
+    int acc_da, acc_db, acc_dbias;
+    int n_da_blocks, da_kt;  // role dA: blocks, and tiles of 1024 along K
+    int n_db_blocks, kgroups, msplit, rows_per_split;   // role dB
+    int vec_da;              // dA rows are 16-byte aligned: float4 stores
+};
+
+// dA[m, k] (+)= sum_j ug[m, j] * B[k, j]: eight rows of ug per block, four adjacent k per thread.
+__device__ __forceinline__ void role_da(const LinBwd& p, int b, float* smem) {
+    const int kt = b % p.da_kt, mt = b / p.da_kt;
+    const int m0 = mt * 8;
+    float* ug_s = smem;                                   // [8][16]
+    if (threadIdx.x < 128) {
+        const int r = threadIdx.x >> 4, j = threadIdx.x & 15;
+        ug_s[threadIdx.x] = (m0 + r < p.M && j < p.N) ? __ldg(p.ug + (int64_t)(m0 + r) * p.N + j) : 0.0f;
+    }
+    __syncthreads();
+    const int k0 = (kt * 256 + threadIdx.x) * 4;
+    if (k0 >= p.K) return;
+    float w[4][16];
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) w[kk][j] = (k0 + kk < p.K && j < p.N) ? __ldg(p.B + (int64_t)(k0 + kk) * p.N + j) : 0.0f;
+#pragma unroll 2
+    for (int r = 0; r < 8; ++r) {
+        if (m0 + r >= p.M) break;
+        float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float u = ug_s[r * 16 + j];             // ascending j, like dot_transpose_t2's chain
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) o[kk] = fmaf(u, w[kk][j], o[kk]);
+        }
+        float* dst = p.dA + (int64_t)(m0 + r) * p.K + k0;
+        if (p.vec_da && k0 + 3 < p.K) {
+            float4 v = make_float4(o[0], o[1], o[2], o[3]);
+            if (p.acc_da) {
+                const float4 old = *reinterpret_cast<const float4*>(dst);
+                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+            }
+            *reinterpret_cast<float4*>(dst) = v;
+        } else {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+                if (k0 + kk < p.K) dst[kk] = p.acc_da ? dst[kk] + o[kk] : o[kk];
+        }
+    }
+}
+
+// dB[k, j] (+)= sum_m A[m, k] * ug[m, j]: one thread per k, a slice of the batch per block; the block
+// that finishes last for its 256 values of k folds the slices in ascending order.
+__device__ __forceinline__ void role_db(const LinBwd& p, int b, float* smem, int* s_last) {
+    const int kg = b % p.kgroups, sp = b / p.kgroups;
+    const int k = kg * 256 + threadIdx.x;
+    const int m_begin = sp * p.rows_per_split;
+    const int m_end = min(p.M, m_begin + p.rows_per_split);
+    float acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+    float* ug_s = smem;                                   // [64][16]
+    for (int mb = m_begin; mb < m_end; mb += 64) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+            const int r = i >> 4, j = i & 15;
+            ug_s[i] = (mb + r < m_end && j < p.N) ? __ldg(p.ug + (int64_t)(mb + r) * p.N + j) : 0.0f;
+        }
+        __syncthreads();
+        if (k < p.K) {
+            const int mn = min(64, m_end - mb);
+            for (int r0 = 0; r0 < mn; r0 += 8) {          // eight loads of A in flight
+                float a[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) a[u] = r0 + u < mn ? __ldg(p.A + (int64_t)(mb + r0 + u) * p.K + k) : 0.0f;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 t = *reinterpret_cast<const float4*>(ug_s + (r0 + u) * 16 + 4 * q);
+                        acc[4 * q] = fmaf(a[u], t.x, acc[4 * q]);
+                        acc[4 * q + 1] = fmaf(a[u], t.y, acc[4 * q + 1]);
+                        acc[4 * q + 2] = fmaf(a[u], t.z, acc[4 * q + 2]);
+                        acc[4 * q + 3] = fmaf(a[u], t.w, acc[4 * q + 3]);
+                    }
+                }
+            }
+        }
+    }
+    if (k < p.K) {
+        float* out = p.partial + ((int64_t)sp * p.K + k) * p.N;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (j < p.N) out[j] = acc[j];
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) *s_last = atomicAdd(&p.tickets[kg], 1) == p.msplit - 1;
+    __syncthreads();
+    if (!*s_last) return;
+    __threadfence();
+    const int kn = min(256, p.K - kg * 256);
+    for (int idx = threadIdx.x; idx < kn * p.N; idx += 256) {   // consecutive threads, consecutive floats
+        const int64_t off = (int64_t)kg * 256 * p.N + idx;
+        float s = 0.0f;
+        for (int q = 0; q < p.msplit; ++q) s += __ldcg(p.partial + (int64_t)q * p.K * p.N + off);
+        p.dB[off] = p.acc_db ? p.dB[off] + s : s;
+    }
+    if (threadIdx.x == 0) p.tickets[kg] = 0;
+}
+
+// dbias[j] (+)= sum_m ug[m, j]: one block, sixteen row phases per column, folded in a fixed order.
+__device__ __forceinline__ void role_dbias(const LinBwd& p, float* smem) {
+    const int j = threadIdx.x & 15, ph = threadIdx.x >> 4;   // 16 phases
+    float s = 0.0f;
+    if (j < p.N)
+        for (int m = ph; m < p.M; m += 16) s += __ldg(p.ug + (int64_t)m * p.N + j);
+    smem[ph * 16 + j] = s;
+    __syncthreads();
+    if (threadIdx.x < p.N) {
+        float t = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 16; ++q) t += smem[q * 16 + threadIdx.x];
+        p.dbias[threadIdx.x] = p.acc_dbias ? p.dbias[threadIdx.x] + t : t;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_linear_bwd(LinBwd p) {
+    __shared__ __align__(16) float smem[64 * 16];
+    __shared__ int s_last;
+    mtl_pdl_sync();
+    int b = blockIdx.x;
+    if (b < p.n_db_blocks) { role_db(p, b, smem, &s_last); return; }      // the longest role first
+    b -= p.n_db_blocks;
+    if (b < p.n_da_blocks) { role_da(p, b, smem); return; }
+    role_dbias(p, smem);
+}
+
+bool linear_supported(mtl_ctx* ctx, int64_t M, int64_t K, int64_t N) {
+    return ctx->math_mode != MTL_MATH_FP32 && N >= 1 && N <= 16 && M >= 1 && K >= 1 && M <= (int64_t)kTicketsFwd * 32 &&
+           K <= (int64_t)kTicketsFwd * 256 && M * K < (1ll << 40);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t mtl_linear_fwd(mtl_ctx* ctx, float* C, const float* A, const float* B, const float* bias, int64_t M, int64_t K,
+                       int64_t N) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, C && A && B, "null pointer in mtl_linear_fwd");
+    MTL_REQUIRE(ctx, M >= 1 && K >= 1 && N >= 1, "Linear extents must be positive");
+    if (!linear_supported(ctx, M, K, N)) {
+        // the reference's two operator calls, one after the other
+        int32_t rc = mtl_dot_fwd(ctx, C, A, B, M, K, N);
+        if (rc || !bias) return rc;
+        const int64_t cs[2] = {M, N}, bs[1] = {N};
+        return mtl_binary_fwd(ctx, MTL_OP_ADD, C, C, bias, 2, cs, 1, bs);
+    }
+    // k extent per block: enough blocks to fill the machine about four times over
+    const int rb = (int)((M + 31) / 32);
+    int kc = kKC;
+    while (kc > 128 && (int64_t)rb * ((K + kc - 1) / kc) < 4ll * ctx->sm_count) kc >>= 1;
+    const int nsplit = (int)((K + kc - 1) / kc);
+    void* ws;
+    int32_t rc = mtl_workspace(ctx, (size_t)nsplit * M * N * 4, &ws);
+    if (rc) return rc;
+    dim3 grid((unsigned)rb, (unsigned)nsplit);
+    MTL_REQUIRE(ctx, nsplit <= 65535, "Linear: reduction too long");
+#define MTL_LIN_FWD(NQ_) mtl_launch_pdl(ctx, k_linear_fwd<NQ_>, grid, dim3(256), (size_t)0, C, (float*)ws, ctx->tickets, A, B, bias, \
+                                        (int)M, (int)N, (int)K, kc, 0)
+    if (N <= 4) MTL_LIN_FWD(1);
+    else if (N <= 8) MTL_LIN_FWD(2);
+    else if (N <= 12) MTL_LIN_FWD(3);
+    else MTL_LIN_FWD(4);
+#undef MTL_LIN_FWD
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
+int32_t mtl_linear_bwd(mtl_ctx* ctx, float* dA, float* dB, float* dbias, const float* ug, const float* A, const float* B,
+                       int64_t M, int64_t K, int64_t N, int32_t acc_da, int32_t acc_db, int32_t acc_dbias) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, ug, "null upper gradient in mtl_linear_bwd");
+    MTL_REQUIRE(ctx, M >= 1 && K >= 1 && N >= 1, "Linear extents must be positive");
+    MTL_REQUIRE(ctx, (!dA || B) && (!dB || A), "mtl_linear_bwd: dA needs B and dB needs A");
+    if (!dA && !dB && !dbias) return MTL_OK;
+    if (!linear_supported(ctx, M, K, N)) {
+        int32_t rc = MTL_OK;
+        const int64_t cs[2] = {M, N}, bs[1] = {N};
+        if (dbias) rc = mtl_binary_bwd(ctx, MTL_OP_ADD, 1, dbias, ug, ug, dbias, 2, cs, 1, bs, acc_dbias);
+        if (!rc && dB) rc = mtl_dot_bwd(ctx, 1, dB, ug, A, B, M, K, N, acc_db);
+        if (!rc && dA) rc = mtl_dot_bwd(ctx, 0, dA, ug, A, B, M, K, N, acc_da);
+        return rc;
+    }
+    LinBwd p;
+    p.dA = dA; p.dB = dB; p.dbias = dbias; p.ug = ug; p.A = A; p.B = B;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.acc_da = acc_da ? 1 : 0; p.acc_db = acc_db ? 1 : 0; p.acc_dbias = acc_dbias ? 1 : 0;
+    p.da_kt = (int)((K + 1023) / 1024);
+    p.n_da_blocks = dA ? (int)((M + 7) / 8) * p.da_kt : 0;
+    p.vec_da = dA && (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(dA) & 15u) == 0);
+    p.kgroups = (int)((K + 255) / 256);
+    p.msplit = 0; p.rows_per_split = 0; p.n_db_blocks = 0; p.partial = nullptr;
+    p.tickets = ctx->tickets + kTicketsFwd;
+    if (dB) {
+        int want = (4 * ctx->sm_count + p.kgroups - 1) / p.kgroups;      // slices of the batch
+        int64_t rows = (M + want - 1) / want;
+        rows = (rows + 31) / 32 * 32;
+        p.rows_per_split = (int)rows;
+        p.msplit = (int)((M + rows - 1) / rows);
+        p.n_db_blocks = p.kgroups * p.msplit;
+        void* ws;
+        int32_t rc = mtl_workspace(ctx, (size_t)p.msplit * K * N * 4, &ws);
+        if (rc) return rc;
+        p.partial = (float*)ws;
+    }
+    const int blocks = p.n_db_blocks + p.n_da_blocks + (dbias ? 1 : 0);
+    mtl_launch_pdl(ctx, k_linear_bwd, dim3((unsigned)blocks), dim3(256), (size_t)0, p);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
+}  // extern "C"

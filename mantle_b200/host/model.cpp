@@ -506,6 +506,8 @@ void Model::set_fusion(bool on) {
     fwd_skip_.assign(nn, 0);
     bwd_skip_.assign(nn, 0);
     relu_in_absent_.assign(nn, 0);
+    lin_add_of_.assign(nn, -1);
+    lin_dot_of_.assign(nn, -1);
     ce_head_ = -1;
     if (!on) return;
     std::map<int, int> uses, producer;
@@ -570,6 +572,29 @@ void Model::set_fusion(bool on) {
                     }
                 }
             }
+        }
+    }
+    // nn.Linear with a narrow output (linear.mojo:25-46): DOT whose only reader is an ADD of a [N] bias, N <= 16.
+    // One mtl_linear_fwd / mtl_linear_bwd call covers both nodes; the DOT's own output and its gradient are
+    // not materialised.
+    for (int i = 0; i < nn; ++i) {
+        const Node& d = g_.nodes[i];
+        if (d.op != MTL_OP_DOT || d.outputs.size() != 1) continue;
+        const Symbol& dout = d.outputs[0];
+        if (uses[dout.id] != 1 || visible(dout) || d.inputs[1].shape[1] > 16) continue;
+        for (int j = i + 1; j < nn; ++j) {
+            const Node& a = g_.nodes[j];
+            if (a.op != MTL_OP_ADD || a.inputs.size() != 2 || a.inputs[0].id != dout.id) continue;
+            const Symbol& bias = a.inputs[1];
+            const bool row_bias = (bias.shape.rank == 1 && bias.shape[0] == dout.shape[1]) ||
+                                  (bias.shape.rank == 2 && bias.shape[0] == 1 && bias.shape[1] == dout.shape[1]);
+            if (!row_bias || producer.count(bias.id)) break;     // the bias must be a plain parameter or input
+            if ((i < n_inference_nodes_) != (j < n_inference_nodes_) && n_inference_nodes_ != 0) break;
+            lin_add_of_[i] = j;
+            lin_dot_of_[j] = i;
+            fwd_skip_[j] = 1;
+            bwd_skip_[j] = 1;
+            break;
         }
     }
     // nn.CrossEntropyLoss at the end of the graph: MAX, SUB, EXP, SUM, LOG, SUB (LogSoftmax along axis 1),
@@ -678,10 +703,18 @@ void Model::forward_op(const Node& n) {
             unary_params(n, scalar_values_, &p0, &p1);
             check(mtl_unary_fwd(ctx_, n.op, T(out), T(t1), t1.shape.num_elements(), p0, p1), "unary forward");
             break;
-        case MTL_OP_DOT:
+        case MTL_OP_DOT: {
+            const int self = (int)(&n - &g_.nodes[0]);
+            if (fusion_ && lin_add_of_[self] >= 0) {
+                const Node& add = g_.nodes[lin_add_of_[self]];
+                check(mtl_linear_fwd(ctx_, T(add.outputs[0]), T(t1), T(n.inputs[1]), T(add.inputs[1]), t1.shape[0], t1.shape[1],
+                                     n.inputs[1].shape[1]), "Linear forward");
+                break;
+            }
             check(mtl_dot_fwd(ctx_, T(out), T(t1), T(n.inputs[1]), t1.shape[0], t1.shape[1], n.inputs[1].shape[1]),
                   "DOT forward");
             break;
+        }
         case MTL_OP_SUM: case MTL_OP_MEAN: case MTL_OP_MAX:
             check(mtl_reduce_fwd(ctx_, n.op, T(out), T(t1), t1.shape.rank, t1.shape.dims,
                                  n.attrs.axis ? *n.attrs.axis : -1), "reduce forward");
@@ -876,6 +909,18 @@ void Model::backward_enqueue() {
             const Symbol& x = n.inputs[0];
             check(mtl_cross_entropy_bwd(ctx_, G(x), T(x), T(g_.nodes[i + 6].inputs[0]), x.shape[0], x.shape[1],
                                         scalar_values_.at(ce_scale_sym_), acc_flag(x)), "CrossEntropyLoss backward");
+        } else if (fusion_ && n.op == MTL_OP_DOT && lin_add_of_[i] >= 0) {
+            // DOT.backward for both operands and the bias ADD's backward, from the gradient of the ADD's result
+            const Node& add = g_.nodes[lin_add_of_[i]];
+            const Symbol& a = n.inputs[0];
+            const Symbol& w = n.inputs[1];
+            const Symbol& b = add.inputs[1];
+            float* da = a.trainable ? G(a) : nullptr;
+            float* dw = w.trainable ? G(w) : nullptr;
+            float* db = b.trainable ? G(b) : nullptr;
+            const int xa = da ? acc_flag(a) : 0, xw = dw ? acc_flag(w) : 0, xb = db ? acc_flag(b) : 0;
+            check(mtl_linear_bwd(ctx_, da, dw, db, G(add.outputs[0]), T(a), T(w), a.shape[0], a.shape[1], w.shape[1], xa, xw, xb),
+                  "Linear backward");
         } else if (fusion_ && n.op == MTL_OP_CONV2D && bwd_pooled_of_[i] >= 0) {
             const Node& q = g_.nodes[bwd_pooled_of_[i]];  // the MAXPOOL2D at the end of the chain
             const Symbol& x = n.inputs[0];

@@ -101,6 +101,12 @@ class Model {
     const Graph& graph() const { return g_; }
     int n_inference_nodes() const { return n_inference_nodes_; }
 
+    // The node during whose backward call the operand gradients of `node` are written: the node itself,
+    // or -- for the bias ADD of a fused Linear layer -- the DOT node in front of it.
+    int backward_performed_at(int node) const {
+        return (fusion_ && (size_t)node < lin_dot_of_.size() && lin_dot_of_[(size_t)node] >= 0) ? lin_dot_of_[(size_t)node] : node;
+    }
+
     // Called between backward nodes by the data-parallel trainer: node index (reverse order) done.
     void (*after_backward_node)(void* user, int node_index) = nullptr;
     void* after_backward_user = nullptr;
@@ -148,6 +154,8 @@ class Model {
     std::map<int, float*> twins_;      // channels-last copies of pooled outputs that feed a CONV2D, by symbol id
     std::map<int, bool> twin_valid_;   // written by the producing call of this step and not overwritten since
     std::vector<char> relu_in_absent_; // RELU nodes whose input tensor is not written (use the output as mask)
+    std::vector<int> lin_add_of_;      // per DOT node: the ADD(bias) node that one mtl_linear_* call also covers, or -1
+    std::vector<int> lin_dot_of_;      // per ADD node: the DOT node whose call covers it, or -1
 };
 
 class Adam {

@@ -16,8 +16,14 @@ Trainer::Trainer(Model& model, Adam& adam, bool use_graph, int64_t bucket_bytes)
     world_ = mtl_dp_world_size(ctx);
     ck(ctx, mtl_host_alloc(ctx, 64, (void**)&own_loss_), "pinned loss word");
     if (world_ > 1) adam_.set_grad_scale(1.0f / (float)world_);
-    // A parameter's gradient is final after the lowest-numbered node that reads it (nodes run in
-    // reverse order during backward).
+    map_final_nodes();
+    model_.after_backward_node = &Trainer::node_done_thunk;
+    model_.after_backward_user = this;
+}
+
+// A parameter's gradient is final after the lowest-numbered node that reads it has run its backward
+// (nodes run in reverse order) -- or, with chain fusion, after the node whose call writes it.
+void Trainer::map_final_nodes() {
     const Graph& g = model_.graph();
     final_at_node_.assign(g.nodes.size(), {});
     const auto& tr = model_.trainable_parameters();
@@ -26,10 +32,9 @@ Trainer::Trainer(Model& model, Adam& adam, bool use_graph, int64_t bucket_bytes)
         for (size_t i = 0; i < g.nodes.size() && first < 0; ++i)
             for (auto& in : g.nodes[i].inputs)
                 if (in.id == tr[p].id) first = (int)i;
-        if (first >= 0) final_at_node_[first].push_back((int)p);
+        if (first >= 0) final_at_node_[(size_t)model_.backward_performed_at(first)].push_back((int)p);
     }
-    model_.after_backward_node = &Trainer::node_done_thunk;
-    model_.after_backward_user = this;
+    fusion_mapped_ = model_.fusion();
 }
 
 Trainer::~Trainer() {
@@ -101,6 +106,7 @@ void Trainer::node_done(int node) {
 }
 
 void Trainer::enqueue_body() {
+    if (fusion_mapped_ != model_.fusion()) map_final_nodes();   // fusion was switched after construction
     model_.execute((int)model_.graph().nodes.size());
     adam_.zero_grad();
     model_.backward_enqueue();

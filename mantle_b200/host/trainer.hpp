@@ -39,6 +39,8 @@ class Trainer {
     static void node_done_thunk(void* self, int node);
     void node_done(int node);
     void flush_bucket();
+    void map_final_nodes();
+    bool fusion_mapped_ = false;
 
     Model& model_;
     Adam& adam_;

@@ -164,10 +164,10 @@ def test_trainer_graph_replay_equals_eager(ctx):
 
 @pytest.mark.parametrize("strict", (False, True))
 def test_chain_fusion_matches_unfused(ctx, strict):
-    """CONV2D+RELU forward and MAXPOOL2D+RELU backward as single launches (Model.set_fusion): loss
-    trajectory, every parameter gradient and the final parameters equal the unfused run (bit for bit up
-    to the conv bias gradients, which are summed in another order); only the CONV2D outputs and the
-    gradients of the RELU outputs are left unwritten."""
+    """CONV2D+RELU forward, MAXPOOL2D+RELU backward and the Linear layer as single launches
+    (Model.set_fusion): loss trajectory, every parameter gradient and the final parameters equal the
+    unfused run up to the order of a few sums (conv bias gradients, the Linear layer's slices, the rows
+    of the loss); only the CONV2D / DOT outputs and the gradients of the RELU outputs are left unwritten."""
     B = 8
     build = lambda ns, gg: build_cnn(ns, gg, B, 64, 128)
     rng = np.random.default_rng(21)
@@ -190,8 +190,12 @@ def test_chain_fusion_matches_unfused(ctx, strict):
     # conv bias gradients inside mtl_conv2d_bwd_fused, the rows of the loss inside mtl_cross_entropy_fwd)
     assert abs(a[0][0] - b[0][0]) <= 2e-6 * abs(a[0][0])   # the fused loss sums the rows in another order
     assert_close(np.asarray(a[0]), np.asarray(b[0]), 1e-5, 1e-7, "losses")
+    # The fused Linear layer folds its k / batch slices in another order than the separate kernels: last-bit
+    # differences in its gradients, which six Adam steps (a step is lr * sign for an element whose gradient
+    # is tiny) turn into parameter differences of a fraction of lr = 1e-3.  The absolute part of the
+    # tolerance therefore scales with the tensor's largest element.
     for u, v in zip(a[1] + a[2] + [a[3]], b[1] + b[2] + [b[3]]):
-        assert_close(u, v, 2e-4, 1e-6, "fused vs unfused")
+        assert_close(u, v, 2e-3, 1e-6 + 3e-3 * float(np.abs(v).max()), "fused vs unfused")
     assert ctx.device_status() == 0
 
 

@@ -887,3 +887,52 @@ def test_bounded_wait_runs_out_and_the_context_stays_usable(ctx):
     assert rel_err(got, a.astype(np.float64) @ b) < 3e-5
     assert ctx.device_status() == 0
     assert ctx.lib.mtl_selftest_bounded_wait(ctx.handle, 0, None) == 1     # MTL_ERR_INVALID
+
+
+@pytest.mark.parametrize("M,K,N", [(256, 6272, 10), (2048, 6272, 10), (64, 1568, 10), (37, 515, 3), (300, 130, 16), (8, 40, 1)])
+def test_linear_layer_as_one_call_each_way(ctx, M, K, N):
+    """mtl_linear_fwd / mtl_linear_bwd against the reference's operator sequence on the oracle (DOT then ADD
+    of the bias; DOT.backward for both operands, ADD.backward with un-broadcasting for the bias) and
+    against the separate entry points of this library, in both accumulate settings."""
+    import ctypes as C
+    rng = np.random.default_rng(M * 7 + K + N)
+    a = rng.normal(0, 1, (M, K)).astype(np.float32)
+    w = (rng.normal(0, 1, (K, N)) / np.sqrt(K)).astype(np.float32)
+    b = rng.normal(0, 1, (N,)).astype(np.float32)
+    ug = rng.normal(0, 1, (M, N)).astype(np.float32)
+    L, h = ctx.lib, ctx.handle
+    da_, dw_, db_, dug = ctx.array(a), ctx.array(w), ctx.array(b), ctx.array(ug)
+    c = ctx.empty((M, N))
+    ctx._check(L.mtl_linear_fwd(h, c.ptr, da_.ptr, dw_.ptr, db_.ptr, M, K, N))
+    want = oracle.binary_fwd(OP.ADD, oracle.dot(a, w), b)
+    assert_close(c.numpy(), want, 1e-5, 1e-5, "Linear forward")
+    ctx._check(L.mtl_linear_fwd(h, c.ptr, da_.ptr, dw_.ptr, None, M, K, N))       # no bias: plain DOT
+    assert_close(c.numpy(), oracle.dot(a, w), 1e-5, 1e-5, "Linear forward without bias")
+    want_da, want_dw = oracle.dot_transpose_t2(ug, w), oracle.dot_transpose_t1(a, ug)
+    want_db = oracle.binary_bwd(OP.ADD, 1, ug, want, b)
+    for acc in (0, 1):
+        ia, iw, ib = (rng.normal(0, 1, s).astype(np.float32) for s in ((M, K), (K, N), (N,)))
+        ga, gw, gb = ctx.array(ia), ctx.array(iw), ctx.array(ib)
+        ctx._check(L.mtl_linear_bwd(h, ga.ptr, gw.ptr, gb.ptr, dug.ptr, da_.ptr, dw_.ptr, M, K, N, acc, acc, acc))
+        assert_close(ga.numpy(), want_da + acc * ia, 1e-5, 1e-5, "dA acc=%d" % acc)
+        assert_close(gw.numpy(), want_dw + acc * iw, 1e-4, 1e-4, "dB acc=%d" % acc)     # sums over the batch, re-associated
+        assert_close(gb.numpy(), want_db + acc * ib, 1e-4, 1e-4, "dbias acc=%d" % acc)
+    # any subset of the three gradients
+    gw2 = ctx.zeros((K, N))
+    ctx._check(L.mtl_linear_bwd(h, None, gw2.ptr, None, dug.ptr, da_.ptr, None, M, K, N, 0, 0, 0))
+    assert np.array_equal(gw2.numpy(), gw.numpy() - iw) or np.allclose(gw2.numpy(), want_dw, 1e-4, 1e-4)
+    # two calls in a row give identical bits (the ticket counters are back at zero, the fold order is fixed)
+    gw3 = ctx.zeros((K, N))
+    ctx._check(L.mtl_linear_bwd(h, None, gw3.ptr, None, dug.ptr, da_.ptr, None, M, K, N, 0, 0, 0))
+    assert np.array_equal(gw2.numpy(), gw3.numpy())
+    c2 = ctx.empty((M, N))
+    ctx._check(L.mtl_linear_fwd(h, c2.ptr, da_.ptr, dw_.ptr, None, M, K, N))
+    assert np.array_equal(c.numpy(), c2.numpy())
+    # MTL_MATH_FP32 keeps the reference's ascending chain bit for bit (separate operator kernels)
+    ctx.set_math_mode(mb.MATH_FP32)
+    try:
+        ctx._check(L.mtl_linear_fwd(h, c.ptr, da_.ptr, dw_.ptr, None, M, K, N))
+        assert np.array_equal(c.numpy(), oracle.dot(a, w))
+    finally:
+        ctx.set_math_mode(mb.MATH_TF32X3)
+    assert ctx.device_status() == 0

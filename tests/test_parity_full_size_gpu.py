@@ -202,16 +202,19 @@ def test_one_step_at_the_per_gpu_batches(ctx, B):
     arithmetic modes, against the same step in float64 (PyTorch on the CPU) -- and against the oracle at
     B = 256, whose own distance from float64 is printed beside them.
 
-    What can be held how tightly.  The loss and the classifier's gradients depend smoothly on the
-    arithmetic: 1e-5 in fp32 and 3xTF32, 1e-3 / 5e-3 in plain TF32.  The gradients below the two
-    RELU / MAXPOOL2D pairs do not: a pre-activation within rounding of zero, or two window elements within
-    rounding of each other, sends a whole gradient term another way, in ANY two implementations that
-    round differently.  The oracle itself is 2e-4 .. 5e-4 (normalised to the largest element) from float64
-    there at B = 256, this backend's fp32 path 4e-4 .. 2e-3 over the four batch sizes.  Those four
-    gradients are therefore held to 5e-3 of their largest element in every mode, which still catches
-    any wrong term (a missing tap, image or sign moves them by 1e-1 or more); their element-wise
-    parity at rtol 1e-4 / atol 1e-5 is established per operator, on identical inputs, in test_ops_gpu.py
-    and in the CONV2D tests below."""
+    What can be held how tightly (measured values in brackets).  The loss and the classifier's gradients
+    depend smoothly on the arithmetic: 1e-5 in fp32 and 3xTF32 [<= 7e-6], 1e-3 on the loss and 5e-3 on
+    those gradients in plain TF32 [1e-5; 2e-3].  The gradients below the two RELU / MAXPOOL2D pairs are
+    sums of up to 1.6 million terms of both signs that cancel to a small remainder, and a pre-activation
+    within rounding of zero -- or two window elements within rounding of each other -- sends a whole
+    term another way; both effects hit ANY implementation that rounds differently from float64.  The
+    oracle, which adds serially in fp32 as the reference does (conv.mojo:340-393), is 1e-4 .. 5e-4 from
+    float64 there at B = 256 (normalised to the largest element of the gradient); this backend's fp32 and
+    3xTF32 paths are 2e-4 .. 2.2e-3 over the four batch sizes, and plain TF32 (10-bit operands under the
+    same cancellation) 7e-3 .. 2.6e-2.  Those four gradients are therefore held to 5e-3 (fp32, 3xTF32) and
+    5e-2 (TF32) of their largest element, which still catches any wrong term (a missing tap, image or
+    sign moves them by 1e-1 or more); element-wise parity at rtol 1e-4 / atol 1e-5 is established per
+    operator, on identical inputs, in test_ops_gpu.py and in the CONV2D tests below."""
     x, _, y = cnn_batch_pool(B, seed=100 + B)
     true_loss, true_grads = _float64_step(B, x, y)
     report, failures = [], []
@@ -224,8 +227,9 @@ def test_one_step_at_the_per_gpu_batches(ctx, B):
         ora_err = [_norm_err(g, t) for g, t in zip(ora_grads, true_grads)]
         report.append("B=256 oracle vs float64: loss %.2e, gradients %s" % (abs(oloss - true_loss) / true_loss, ["%.1e" % e for e in ora_err]))
         assert abs(oloss - true_loss) <= 1e-5 * true_loss and max(ora_err) < 5e-3
-    for mode, smooth_tol, ltol, fusion, name in ((mb.MATH_FP32, 1e-5, 1e-5, False, "fp32"), (mb.MATH_TF32X3, 1e-5, 1e-5, True, "tf32x3"),
-                                                 (mb.MATH_TF32, 5e-3, 1e-3, True, "tf32")):
+    for mode, smooth_tol, rough_tol, ltol, fusion, name in ((mb.MATH_FP32, 1e-5, 5e-3, 1e-5, False, "fp32"),
+                                                            (mb.MATH_TF32X3, 1e-5, 5e-3, 1e-5, True, "tf32x3"),
+                                                            (mb.MATH_TF32, 5e-3, 5e-2, 1e-3, True, "tf32")):
         loss, grads = _one_step(ctx, mode, B, x, y, fusion)
         assert ctx.device_status() == 0
         errs = [_norm_err(g, t) for g, t in zip(grads, true_grads)]
@@ -233,14 +237,14 @@ def test_one_step_at_the_per_gpu_batches(ctx, B):
         if abs(loss - true_loss) > ltol * true_loss:
             failures.append("%s loss %r vs %r" % (name, loss, true_loss))
         for i, e in enumerate(errs):
-            tol = 5e-3 if i < 4 else smooth_tol
+            tol = rough_tol if i < 4 else smooth_tol
             if not e < tol:
                 failures.append("%s, gradient %d: normalised max error %.3e against float64 (limit %.0e)" % (name, i, e, tol))
         if ora_grads is not None:
             oe = [_norm_err(g, o) for g, o in zip(grads, ora_grads)]
             report.append("B=256 %s vs oracle: gradients %s" % (name, ["%.1e" % e for e in oe]))
             for i, e in enumerate(oe):
-                if not e < (5e-3 if i < 4 else smooth_tol + 2e-6):
+                if not e < (rough_tol if i < 4 else smooth_tol + 2e-6):
                     failures.append("%s vs oracle, gradient %d: %.3e" % (name, i, e))
     print("\n" + "\n".join(report))
     assert not failures, "; ".join(failures)
