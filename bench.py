@@ -336,7 +336,7 @@ def run_ours(args):
     for s, w in zip(tr, cnn_weights([s.shape for s in tr])):
         model.set_tensor(s, w)
     adam = host_api.Adam(model, lr=1e-3)
-    trainer = host_api.Trainer(model, adam, use_graph=not args.no_graph)
+    trainer = host_api.Trainer(model, adam, use_graph=not args.no_graph, bucket_bytes=args.bucket_kb * 1024)
     trainer.set_label_input(1, 10)      # targets travel as B fp32 labels; one-hot rows are built on the device
 
     # synthetic pool in pinned host memory: images and fp32 class labels
@@ -441,9 +441,24 @@ def run_ours(args):
     final_loss = reduce_ranks([float(loss_view[0])], "sum")[0] / world
     e2e_ms, dev_ms = statistics.median(e2e_rounds), statistics.median(dev_rounds)
 
+    # ---- data parallel: the same step without the gradient exchange (a timing diagnostic, not training):
+    # the difference to the full step is the part of the communication that the backward pass does not hide
+    compute_only_ms = None
+    trainer.close()
+    if world > 1:
+        trainer_c = host_api.Trainer(model, adam, use_graph=not args.no_graph, bucket_bytes=args.bucket_kb * 1024)
+        trainer_c.set_label_input(1, 10)
+        trainer_c.set_exchange(False)
+        for i in range(3):
+            trainer_c.step_async_ptrs(batch_ptrs(i), ploss.value)
+        saved = args.min_seconds
+        args.min_seconds = min(saved, 0.5)
+        compute_only_ms = statistics.median(timed_rounds(lambda i: trainer_c.step_async_ptrs([], ploss.value), 4)) / K
+        args.min_seconds = saved
+        trainer_c.close()
+
     # ---- per-kernel durations of the dominant kernels, live, while the GPU is still hot: eager
     # steps with CUDA-event brackets on the launching stream around each tensor-core launch
-    trainer.close()
     prof_trainer = host_api.Trainer(model, adam, use_graph=False)
     prof_trainer.set_label_input(1, 10)
     ctx._check(lib.mtl_prof_reset(ctx.handle))
@@ -533,6 +548,9 @@ def run_ours(args):
                          "flops_per_launch": flops_per_launch, "avg_launch_ms": ig["avg_ms"], "launches_timed": ig["launches"]},
             "kernels": kern,
             "step_tflops": K * GLOBAL_BATCH * FLOP_PER_SAMPLE / (dev_ms * 1e-3) / 1e12,
+            "data_parallel": None if world == 1 else {
+                "compute_only_ms_per_step": compute_only_ms, "exposed_exchange_ms_per_step": dev_ms / K - compute_only_ms,
+                "note": "compute_only = the same captured step with the gradient all-reduce left out (timing diagnostic)"},
             "loss_check": loss_check, "loss_last": final_loss,
             "loss": "mean over ranks; loss_last is the loss after the device-resident rounds, which repeat one batch",
             "device_status": status,
@@ -568,6 +586,8 @@ def main():
     ap.add_argument("--min-seconds", type=float, default=2.0,
                     help="device time each of the two timed arms accumulates before it stops (rounds of --steps)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--bucket-kb", type=int, default=256,
+                    help="data parallel: gradient spans are exchanged once this many KB of them are final")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
                     help="diagnostic only: the headline number is quoted at the default")
     ap.add_argument("--no-cpu-baseline", action="store_true")

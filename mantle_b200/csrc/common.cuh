@@ -20,7 +20,7 @@ struct mtl_tuning {
     bool log_errors = false;          // MANTLE_CUDA_LOG=1: print every recorded error to stderr
     bool conv_channel_major = true;   // MANTLE_CONV_CHANNEL_MAJOR=0 switches the channel-major implicit GEMM off
     bool conv_paired = true;          // MANTLE_CONV_PAIRED=0: one filter tap per instruction
-    int conv_paired_min_kblocks = 8;  // MANTLE_CONV_PAIRED_MIN_KB: shortest reduction (k-blocks per tile) that pairs taps
+    int conv_paired_min_kblocks = 32;  // MANTLE_CONV_PAIRED_MIN_KB: shortest reduction (k-blocks per tile) that pairs taps
     bool conv_spread = true;          // MANTLE_CONV_SPREAD=0: plain row order of the pixel boxes
     bool conv_pool_epilogue = true;   // MANTLE_CONV_POOL_EPILOGUE=0: conv -> ReLU -> pool through scratch memory
     bool conv_first_tc = true;        // MANTLE_CONV_FIRST_TC=0: first layer on the CUDA-core kernels in every mode
@@ -29,7 +29,7 @@ struct mtl_tuning {
     int gemm_bn = -1;                 // MANTLE_GEMM_BN: DOT tile width (128 / 256)
     int gemm_mt = -1;                 // MANTLE_GEMM_MT: 1 = 128-row tiles, 2 = 256-row tiles
     int gemm_stages = -1;             // MANTLE_GEMM_STAGES: operand ring depth
-    int gemm_split_k = -1;            // MANTLE_GEMM_SPLITK: 0 = never split the reduction, n >= 2 = n slices
+    int gemm_split_k = -1;            // MANTLE_GEMM_SPLITK=1: stream-K schedule for DOT when whole tiles leave SMs idle
     bool pdl = true;                  // MANTLE_PDL=0: plain stream order between the kernels of a step
     bool debug_guards = false;        // MANTLE_CUDA_DEBUG=1: guard words around every mtl_malloc block, checked at mtl_sync
 };

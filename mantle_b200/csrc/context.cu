@@ -64,7 +64,7 @@ static void read_tuning(mtl_tuning* t) {  // the only place the library reads it
     t->conv_channel_major = env_int("MANTLE_CONV_CHANNEL_MAJOR", 1) != 0;
     t->conv_paired = env_int("MANTLE_CONV_PAIRED", 1) != 0;
     t->conv_spread = env_int("MANTLE_CONV_SPREAD", 1) != 0;
-    t->conv_paired_min_kblocks = env_int("MANTLE_CONV_PAIRED_MIN_KB", 8);
+    t->conv_paired_min_kblocks = env_int("MANTLE_CONV_PAIRED_MIN_KB", 32);
     t->conv_pool_epilogue = env_int("MANTLE_CONV_POOL_EPILOGUE", 1) != 0;
     t->conv_first_tc = env_int("MANTLE_CONV_FIRST_TC", 1) != 0;
     t->gemm_3d_boxes = getenv("MANTLE_GEMM_NO3D") == nullptr;

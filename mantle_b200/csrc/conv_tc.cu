@@ -814,25 +814,27 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                 mbar_arrive(&tmem_empty[acc]);
                 continue;
             }
+            // The accumulator leaves tensor memory 32 columns at a time.  The read of the NEXT 32 columns is
+            // issued as soon as the current ones are parked in shared memory, so that its latency runs under
+            // the transposed read-back and the global stores of the current block (with short reductions this
+            // epilogue, not the main loop, sets the pace of the kernel).
+            uint32_t r[32], r2[32];
+            const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride);
+            tmem_ld_32x32(acc_addr, r);
+            if (p.paired == 1) tmem_ld_32x32(acc_addr + 1u, r2);
 #pragma unroll 1
             for (int c = 0; c * 32 < p.npix; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride + c * 32), r);
+                tmem_ld_wait();
                 if (p.paired == 1) {
                     // lanes 16-31 hold the second tap of the channels of lanes 0-15, which belongs to the pixel
-                    // one column to the left: those lanes take their values one column to the right.  The two
-                    // halves meet in the transposition block below (row ch and row ch + 16), where the reading
-                    // side adds them -- no warp shuffles, which would compete with the main loop for the
-                    // shared-memory pipe.
-                    uint32_t r2[32];
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride + c * 32 + 1), r2);
-                    tmem_ld_wait();
+                    // one column to the left: those lanes take their values one column to the right (r2).  The
+                    // two halves meet in the transposition block below (row ch and row ch + 16), where the
+                    // reading side adds them -- no warp shuffles, which would compete with the main loop for
+                    // the shared-memory pipe.
                     if (lane >= 16) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = r2[i];
                     }
-                } else {
-                    tmem_ld_wait();
                 }
                 __syncwarp();
 #pragma unroll
@@ -844,6 +846,10 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                         o.z = o.z > 0.0f ? o.z : 0.0f; o.w = o.w > 0.0f ? o.w : 0.0f;
                     }
                     *reinterpret_cast<float4*>(stg + lane * 36 + g * 4) = o;
+                }
+                if ((c + 1) * 32 < p.npix) {
+                    tmem_ld_32x32(acc_addr + (uint32_t)((c + 1) * 32), r);
+                    if (p.paired == 1) tmem_ld_32x32(acc_addr + (uint32_t)((c + 1) * 32 + 1), r2);
                 }
                 __syncwarp();
                 const int j0 = c * 32 + sub * 4;
@@ -1049,8 +1055,11 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
                 if (cost < best * 0.98) { best = cost; q.bn = bn; }
             }
         } else if (paired) {
-            // whole rows plus the extra column; the box that fills most of 240 columns
-            q.bw = c.OW + 1;
+            // whole rows plus the extra column; the box that fills most of 240 columns.  When the rows are a
+            // multiple of four pixels wide the box is widened to the next multiple of four, so that every
+            // group of four accumulator columns is either four aligned pixels of one row (one 16-byte store)
+            // or entirely outside the image
+            q.bw = (c.OW % 4 == 0 && c.OW + 4 <= 240) ? c.OW + 4 : c.OW + 1;
             double best = -1.0;
             for (int bh = 1; bh <= c.OH && q.bw * bh <= 240; ++bh) {
                 int bn = 240 / (q.bw * bh);

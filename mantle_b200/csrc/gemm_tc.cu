@@ -534,20 +534,18 @@ int32_t mtl_gemm_tc(mtl_ctx* ctx, float* C, const float* A, const float* B, int6
         const int64_t w1 = (t1 + ctx->sm_count - 1) / ctx->sm_count, w2 = (t2 + ctx->sm_count - 1) / ctx->sm_count;
         if ((double)w2 * 1.67 < (double)w1 && K >= 512) MT = 2;
     }
-    // Stream-K (see GemmParams::sk) when whole tiles would leave a large part of the last wave idle.  The
-    // schedule makes the wave count irrelevant, so the tile is then the largest one that still gives at
-    // least a third as many tiles as SMs (a tile is split over at most about three CTAs: the CTA that
-    // finishes a tile reads all of its parts back).
+    // Stream-K (see GemmParams::sk) is an opt-in (MANTLE_GEMM_SPLITK=1).  It keeps every SM busy whatever the
+    // tile count, but each part of a split tile makes a trip through memory and only the four epilogue warps
+    // of a CTA move it: measured on B200, 4096^3 took 0.273 ms with it against 0.205 ms with whole tiles
+    // (1.73 waves), 2048^3 0.120 against 0.041 ms.  With it the tile is the largest one that still gives at
+    // least a third as many tiles as SMs, so that a tile has about three parts at most.
     const int kb_units = (int)((K + BK - 1) / BK) * (x3 ? 3 : 1);
     int sk = 0;
     {
         const int64_t tiles = ((M + BM * MT - 1) / (BM * MT)) * ((N + BN - 1) / BN);
         const int64_t waves = (tiles + ctx->sm_count - 1) / ctx->sm_count;
         const double fill = (double)tiles / (double)(waves * ctx->sm_count);
-        // (only for problems of at least one full wave: below that the parts' trip through memory costs more
-        // than the idle SMs; measured 1024^3 and 2048^3 slower, 4096^3 faster)
-        if (fill < 0.92 && kb_units >= 8 && tiles >= ctx->sm_count && ctx->tune.gemm_split_k != 0) sk = 1;
-        if (ctx->tune.gemm_split_k >= 1) sk = 1;
+        if (fill < 0.92 && kb_units >= 8 && ctx->tune.gemm_split_k >= 1) sk = 1;
         if (sk && ctx->tune.gemm_bn < 0 && ctx->tune.gemm_mt < 0) {
             const int64_t want = (ctx->sm_count + 2) / 3;
             const int64_t t22 = ((M + 255) / 256) * ((N + 255) / 256), t12 = ((M + 127) / 128) * ((N + 255) / 256);

@@ -120,64 +120,70 @@ struct LinBwd {
     int32_t* tickets;        // one per group of 256 columns of A (= rows of dB)
     int M, N, K;
     int acc_da, acc_db, acc_dbias;
-    int n_da_blocks, da_kt;  // role dA: blocks, and tiles of 1024 along K
+    int n_da_blocks, da_kt, da_rows;  // role dA: blocks, tiles of 1024 along K, rows of ug per block
     int n_db_blocks, kgroups, msplit, rows_per_split;   // role dB
-    int vec_da;              // dA rows are 16-byte aligned: float4 stores
 };
 
-// dA[m, k] (+)= sum_j ug[m, j] * B[k, j]: eight rows of ug per block, four adjacent k per thread.
+// dA[m, k] (+)= sum_j ug[m, j] * B[k, j].  A block owns da_rows rows of ug and 1024 values of k.  Its
+// slice of B (1024 x N floats, contiguous) is read once with coalesced loads into shared memory, row
+// stride N | 1 floats (odd: lanes that read consecutive rows hit different banks); thread t then keeps
+// rows k0 + t, + 256, + 512, + 768 in registers and walks the rows of ug, so that a warp's stores are
+// 32 consecutive floats of one row of dA.
+constexpr int kDaKT = 1024;
+template <int NP>
 __device__ __forceinline__ void role_da(const LinBwd& p, int b, float* smem) {
     const int kt = b % p.da_kt, mt = b / p.da_kt;
-    const int m0 = mt * 8;
-    float* ug_s = smem;                                   // [8][16]
-    if (threadIdx.x < 128) {
-        const int r = threadIdx.x >> 4, j = threadIdx.x & 15;
-        ug_s[threadIdx.x] = (m0 + r < p.M && j < p.N) ? __ldg(p.ug + (int64_t)(m0 + r) * p.N + j) : 0.0f;
+    const int m0 = mt * p.da_rows;
+    const int k_base = kt * kDaKT;
+    const int kn = min(kDaKT, p.K - k_base);
+    const int ws = p.N | 1;
+    float* w_s = smem;                                    // [1024][N | 1]
+    float* ug_s = smem + kDaKT * ws;                      // [da_rows][16]
+    const float* wsrc = p.B + (int64_t)k_base * p.N;
+    for (int i = threadIdx.x; i < kn * p.N; i += 256) {
+        const int kk = i / p.N, j = i - kk * p.N;
+        w_s[kk * ws + j] = __ldg(wsrc + i);
+    }
+    for (int i = threadIdx.x; i < p.da_rows * 16; i += 256) {
+        const int r = i >> 4, j = i & 15;
+        ug_s[i] = (m0 + r < p.M && j < p.N) ? __ldg(p.ug + (int64_t)(m0 + r) * p.N + j) : 0.0f;
     }
     __syncthreads();
-    const int k0 = (kt * 256 + threadIdx.x) * 4;
-    if (k0 >= p.K) return;
-    float w[4][16];
+    float w[4][NP];
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk)
+    for (int kk = 0; kk < 4; ++kk) {
+        const int kl = threadIdx.x + 256 * kk;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) w[kk][j] = (k0 + kk < p.K && j < p.N) ? __ldg(p.B + (int64_t)(k0 + kk) * p.N + j) : 0.0f;
+        for (int j = 0; j < NP; ++j) w[kk][j] = (kl < kn && j < p.N) ? w_s[kl * ws + j] : 0.0f;
+    }
+    const int rows = min(p.da_rows, p.M - m0);
 #pragma unroll 2
-    for (int r = 0; r < 8; ++r) {
-        if (m0 + r >= p.M) break;
+    for (int r = 0; r < rows; ++r) {
         float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < NP; ++j) {
             const float u = ug_s[r * 16 + j];             // ascending j, like dot_transpose_t2's chain
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) o[kk] = fmaf(u, w[kk][j], o[kk]);
         }
-        float* dst = p.dA + (int64_t)(m0 + r) * p.K + k0;
-        if (p.vec_da && k0 + 3 < p.K) {
-            float4 v = make_float4(o[0], o[1], o[2], o[3]);
-            if (p.acc_da) {
-                const float4 old = *reinterpret_cast<const float4*>(dst);
-                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
-            }
-            *reinterpret_cast<float4*>(dst) = v;
-        } else {
+        float* dst = p.dA + (int64_t)(m0 + r) * p.K + k_base + threadIdx.x;
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-                if (k0 + kk < p.K) dst[kk] = p.acc_da ? dst[kk] + o[kk] : o[kk];
-        }
+        for (int kk = 0; kk < 4; ++kk)
+            if (threadIdx.x + 256 * kk < kn) dst[256 * kk] = p.acc_da ? dst[256 * kk] + o[kk] : o[kk];
     }
 }
 
 // dB[k, j] (+)= sum_m A[m, k] * ug[m, j]: one thread per k, a slice of the batch per block; the block
 // that finishes last for its 256 values of k folds the slices in ascending order.
+template <int NP>
 __device__ __forceinline__ void role_db(const LinBwd& p, int b, float* smem, int* s_last) {
     const int kg = b % p.kgroups, sp = b / p.kgroups;
     const int k = kg * 256 + threadIdx.x;
     const int m_begin = sp * p.rows_per_split;
     const int m_end = min(p.M, m_begin + p.rows_per_split);
-    float acc[16];
+    float acc[NP];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+    for (int j = 0; j < NP; ++j) acc[j] = 0.0f;
     float* ug_s = smem;                                   // [64][16]
     for (int mb = m_begin; mb < m_end; mb += 64) {
         __syncthreads();
@@ -195,7 +201,7 @@ __device__ __forceinline__ void role_db(const LinBwd& p, int b, float* smem, int
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
+                    for (int q = 0; q < NP / 4; ++q) {
                         const float4 t = *reinterpret_cast<const float4*>(ug_s + (r0 + u) * 16 + 4 * q);
                         acc[4 * q] = fmaf(a[u], t.x, acc[4 * q]);
                         acc[4 * q + 1] = fmaf(a[u], t.y, acc[4 * q + 1]);
@@ -209,7 +215,7 @@ __device__ __forceinline__ void role_db(const LinBwd& p, int b, float* smem, int
     if (k < p.K) {
         float* out = p.partial + ((int64_t)sp * p.K + k) * p.N;
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
+        for (int j = 0; j < NP; ++j)
             if (j < p.N) out[j] = acc[j];
     }
     __threadfence();
@@ -244,14 +250,15 @@ __device__ __forceinline__ void role_dbias(const LinBwd& p, float* smem) {
     }
 }
 
+template <int NP>
 __global__ void __launch_bounds__(256) k_linear_bwd(LinBwd p) {
-    __shared__ __align__(16) float smem[64 * 16];
+    extern __shared__ __align__(16) float smem[];   // role dA: B slice + rows of ug; role dB: 64 rows of ug
     __shared__ int s_last;
     mtl_pdl_sync();
     int b = blockIdx.x;
-    if (b < p.n_db_blocks) { role_db(p, b, smem, &s_last); return; }      // the longest role first
+    if (b < p.n_db_blocks) { role_db<NP>(p, b, smem, &s_last); return; }      // the longest role first
     b -= p.n_db_blocks;
-    if (b < p.n_da_blocks) { role_da(p, b, smem); return; }
+    if (b < p.n_da_blocks) { role_da<NP>(p, b, smem); return; }
     role_dbias(p, smem);
 }
 
@@ -316,14 +323,16 @@ int32_t mtl_linear_bwd(mtl_ctx* ctx, float* dA, float* dB, float* dbias, const f
     p.dA = dA; p.dB = dB; p.dbias = dbias; p.ug = ug; p.A = A; p.B = B;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.acc_da = acc_da ? 1 : 0; p.acc_db = acc_db ? 1 : 0; p.acc_dbias = acc_dbias ? 1 : 0;
-    p.da_kt = (int)((K + 1023) / 1024);
-    p.n_da_blocks = dA ? (int)((M + 7) / 8) * p.da_kt : 0;
-    p.vec_da = dA && (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(dA) & 15u) == 0);
+    p.da_kt = (int)((K + kDaKT - 1) / kDaKT);
+    // rows of ug per block: 32 amortise the block's slice of B; fewer when that would leave SMs without a block
+    p.da_rows = 32;
+    while (p.da_rows > 4 && ((M + p.da_rows - 1) / p.da_rows) * p.da_kt < 2ll * ctx->sm_count) p.da_rows >>= 1;
+    p.n_da_blocks = dA ? (int)((M + p.da_rows - 1) / p.da_rows) * p.da_kt : 0;
     p.kgroups = (int)((K + 255) / 256);
     p.msplit = 0; p.rows_per_split = 0; p.n_db_blocks = 0; p.partial = nullptr;
     p.tickets = ctx->tickets + kTicketsFwd;
     if (dB) {
-        int want = (4 * ctx->sm_count + p.kgroups - 1) / p.kgroups;      // slices of the batch
+        int want = (8 * ctx->sm_count + p.kgroups - 1) / p.kgroups;      // slices of the batch
         int64_t rows = (M + want - 1) / want;
         rows = (rows + 31) / 32 * 32;
         p.rows_per_split = (int)rows;
@@ -335,7 +344,18 @@ int32_t mtl_linear_bwd(mtl_ctx* ctx, float* dA, float* dB, float* dbias, const f
         p.partial = (float*)ws;
     }
     const int blocks = p.n_db_blocks + p.n_da_blocks + (dbias ? 1 : 0);
-    mtl_launch_pdl(ctx, k_linear_bwd, dim3((unsigned)blocks), dim3(256), (size_t)0, p);
+    const size_t smem_bytes = dA ? (size_t)(kDaKT * ((int)N | 1) + 32 * 16) * 4 : (size_t)64 * 16 * 4;
+#define MTL_LIN_BWD(NP_)                                                                                              \
+    do {                                                                                                              \
+        MTL_CUDA(ctx, cudaFuncSetAttribute(k_linear_bwd<NP_>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                           (int)((kDaKT * 17 + 32 * 16) * 4)));                                       \
+        mtl_launch_pdl(ctx, k_linear_bwd<NP_>, dim3((unsigned)blocks), dim3(256), smem_bytes, p);                     \
+    } while (0)
+    if (N <= 4) MTL_LIN_BWD(4);
+    else if (N <= 8) MTL_LIN_BWD(8);
+    else if (N <= 12) MTL_LIN_BWD(12);
+    else MTL_LIN_BWD(16);
+#undef MTL_LIN_BWD
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }

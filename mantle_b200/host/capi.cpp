@@ -427,5 +427,8 @@ MTLH_API int32_t mtlh_trainer_step_async(void* t, int32_t n_in, const float* con
 MTLH_API int32_t mtlh_trainer_set_label_input(void* t, int32_t input_index, int32_t num_classes) {
     return guard([&] { static_cast<Trainer*>(t)->set_label_input(input_index, num_classes); });
 }
+MTLH_API int32_t mtlh_trainer_set_exchange(void* t, int32_t on) {
+    return guard([&] { static_cast<Trainer*>(t)->set_exchange(on != 0); });
+}
 MTLH_API int64_t mtlh_trainer_input_bytes(void* t) { return static_cast<Trainer*>(t)->input_bytes_per_step(); }
 MTLH_API int32_t mtlh_trainer_graph_active(void* t) { return static_cast<Trainer*>(t)->graph_active() ? 1 : 0; }

@@ -78,7 +78,7 @@ void Trainer::flush_bucket() {
 }
 
 void Trainer::node_done(int node) {
-    if (world_ <= 1) return;
+    if (world_ <= 1 || !exchange_) return;
     const auto& tr = model_.trainable_parameters();
     const auto& off = model_.trainable_offsets();
     for (int p : final_at_node_[node]) {

@@ -30,6 +30,11 @@ class Trainer {
     // Bytes a step copies host -> device for its inputs (labels counted as labels).
     int64_t input_bytes_per_step() const;
 
+    // Diagnostic: with the exchange off a data-parallel Trainer skips the all-reduce of the gradients
+    // (every rank then trains on its own shard only -- NOT a valid training run).  Timing a step with and
+    // without it separates the compute time of a rank from the exposed part of the communication.
+    void set_exchange(bool on) { exchange_ = on; }
+
     int64_t steps() const { return steps_; }
     bool graph_active() const { return graph_ != nullptr; }
 
@@ -41,6 +46,7 @@ class Trainer {
     void flush_bucket();
     void map_final_nodes();
     bool fusion_mapped_ = false;
+    bool exchange_ = true;
 
     Model& model_;
     Adam& adam_;

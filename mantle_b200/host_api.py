@@ -442,6 +442,10 @@ class Trainer:
         the one-hot rows are built on the device (examples/mnist.mojo:92-97 builds them on the host)."""
         _ck(self.lib.mtlh_trainer_set_label_input(self.handle, int(input_index), int(num_classes)))
 
+    def set_exchange(self, on: bool):
+        """Diagnostic: skip the gradient all-reduce of a data-parallel step (timing only, not a valid training run)."""
+        _ck(self.lib.mtlh_trainer_set_exchange(self.handle, int(on)))
+
     def input_bytes_per_step(self) -> int:
         return int(self.lib.mtlh_trainer_input_bytes(self.handle))
 

@@ -113,3 +113,44 @@ def test_data_parallel_trajectory_equals_single_gpu(world):
             assert np.array_equal(a, b)
     for a, b in zip(ranks[0][2], single[2]):  # and close to the single-GPU parameters
         assert np.linalg.norm(a - b) <= 2e-2 * np.linalg.norm(b) + 1e-6
+
+
+def _visible_gpus():
+    import ctypes as C
+    try:
+        rt = C.CDLL("libcudart.so")
+    except OSError:
+        try:
+            rt = C.CDLL("libcudart.so.12")
+        except OSError:
+            return 0
+    n = C.c_int(0)
+    return n.value if rt.cudaGetDeviceCount(C.byref(n)) == 0 else 0
+
+
+def test_two_contexts_on_two_devices_from_one_thread():
+    """Every entry point makes its context's device current for the call and restores the caller's: one
+    host thread can drive contexts on different GPUs in turn (allocation, operators, a captured step)
+    and each result lands on, and is computed by, its own device."""
+    if _visible_gpus() < 2:
+        pytest.skip("needs two visible GPUs")
+    import mantle_b200 as mb
+    from mantle_b200 import OP
+    import oracle
+    c0, c1 = mb.Context(0), mb.Context(1)
+    rng = np.random.default_rng(5)
+    a = rng.normal(0, 1, (256, 128)).astype(np.float32)
+    b = rng.normal(0, 1, (128, 256)).astype(np.float32)
+    outs = []
+    for step in range(3):                       # interleaved calls on the two contexts
+        for ctx, scale in ((c0, 1.0), (c1, 2.0)):
+            da, db = ctx.array(a * np.float32(scale)), ctx.array(b)
+            out = ctx.empty((256, 256))
+            ctx.forward_op(OP.DOT, out, da, db)
+            outs.append((scale, out))
+    want = oracle.dot(a, b)
+    for scale, out in outs:
+        got = out.numpy()
+        assert float(np.max(np.abs(got - scale * want)) / np.max(np.abs(want))) < 3e-5
+    assert c0.device_status() == 0 and c1.device_status() == 0
+    c1.close(); c0.close()
