@@ -103,6 +103,11 @@ MTL_API const char* mtl_last_error(mtl_ctx* ctx);
 /* Number of kernels this library launched on the context since creation (memsets and copies
  * are not counted). */
 MTL_API int64_t mtl_launch_count(mtl_ctx* ctx);
+/* Tiles of the implicit-GEMM convolution kernels that were split along the reduction over two
+ * CTAs (the tiles of a partial last wave), summed over every launch of the context so far; -1
+ * without a context.  A diagnostic: tests use it to know that the split path ran.  No counterpart
+ * in the reference. */
+MTL_API int64_t mtl_conv_split_tiles(mtl_ctx* ctx);
 /* Reads and clears the device-side status word that bounded waits write on time-out. */
 MTL_API int32_t mtl_device_status(mtl_ctx* ctx, int32_t* out_status);
 MTL_API const char* mtl_version(void);

@@ -85,6 +85,7 @@ SIGNATURES = {
     "mtl_sync": (_i32, [_vp]),
     "mtl_last_error": (C.c_char_p, [_vp]),
     "mtl_launch_count": (_i64, [_vp]),
+    "mtl_conv_split_tiles": (_i64, [_vp]),
     "mtl_device_status": (_i32, [_vp, C.POINTER(_i32)]),
     "mtl_version": (C.c_char_p, []),
     "mtl_selftest_bounded_wait": (_i32, [_vp, _i32, C.POINTER(_i32)]),

@@ -20,6 +20,7 @@ struct mtl_tuning {
     bool log_errors = false;          // MANTLE_CUDA_LOG=1: print every recorded error to stderr
     bool conv_channel_major = true;   // MANTLE_CONV_CHANNEL_MAJOR=0 switches the channel-major implicit GEMM off
     bool conv_paired = true;          // MANTLE_CONV_PAIRED=0: one filter tap per instruction
+    int conv_tail_split = 0;           // MANTLE_CONV_TAIL_SPLIT=0: tiles of a partial last wave are never split along k
     int conv_paired_min_kblocks = 32;  // MANTLE_CONV_PAIRED_MIN_KB: shortest reduction (k-blocks per tile) that pairs taps
     bool conv_spread = true;          // MANTLE_CONV_SPREAD=0: plain row order of the pixel boxes
     bool conv_pool_epilogue = true;   // MANTLE_CONV_POOL_EPILOGUE=0: conv -> ReLU -> pool through scratch memory
@@ -40,12 +41,15 @@ struct mtl_ctx {
     cudaStream_t stream = nullptr;
     bool owns_stream = false;
     int math_mode = MTL_MATH_TF32X3;
-    int sm_count = 148;
+    int sm_count = 148;        // SMs the persistent grids may use (a data-parallel group takes some off)
+    int sm_count_total = 148;  // SMs of the device
     // scratch workspace, grown on demand outside capture
     void* ws = nullptr;
     size_t ws_bytes = 0;
     void* ws2 = nullptr;  // second scratch block (mtl_workspace2)
     size_t ws2_bytes = 0;
+    int64_t conv_split_tiles = 0;   // mtl_conv_split_tiles
+    void* split_scratch = nullptr;  // partial accumulators of k-split tail tiles (mtl_split_scratch), fixed size
     bool capturing = false;
     // Instantiated graphs of this context that are alive.  They hold the scratch pointers that were
     // current when they were captured, so while any is alive a scratch block that has to grow is not
@@ -115,6 +119,7 @@ const mtl_tuning& mtl_global_tuning();
 // Returns a device pointer to at least `bytes` of scratch, 256-byte aligned.
 int32_t mtl_workspace(mtl_ctx* ctx, size_t bytes, void** out);
 int32_t mtl_workspace2(mtl_ctx* ctx, size_t bytes, void** out);
+int32_t mtl_split_scratch(mtl_ctx* ctx, void** out);
 
 // Makes the context's device current for the duration of an entry point and puts the caller's
 // device back afterwards, so that one host thread can drive contexts on different GPUs in turn.

@@ -65,6 +65,7 @@ static void read_tuning(mtl_tuning* t) {  // the only place the library reads it
     t->conv_paired = env_int("MANTLE_CONV_PAIRED", 1) != 0;
     t->conv_spread = env_int("MANTLE_CONV_SPREAD", 1) != 0;
     t->conv_paired_min_kblocks = env_int("MANTLE_CONV_PAIRED_MIN_KB", 32);
+    t->conv_tail_split = env_int("MANTLE_CONV_TAIL_SPLIT", 0) != 0;
     t->conv_pool_epilogue = env_int("MANTLE_CONV_POOL_EPILOGUE", 1) != 0;
     t->conv_first_tc = env_int("MANTLE_CONV_FIRST_TC", 1) != 0;
     t->gemm_3d_boxes = getenv("MANTLE_GEMM_NO3D") == nullptr;
@@ -88,6 +89,23 @@ int32_t mtl_workspace(mtl_ctx* ctx, size_t bytes, void** out) {
         if (rc) return rc;
     }
     *out = ctx->ws;
+    return MTL_OK;
+}
+
+// Room for one partial accumulator tile (128 rows x 256 fp32 columns) per SM: what the implicit-GEMM
+// kernels need when the tiles of a partial last wave are split along k over two CTAs each.  Allocated
+// once, never moved, so that captured graphs may keep naming it.
+int32_t mtl_split_scratch(mtl_ctx* ctx, void** out) {
+    if (!ctx->split_scratch) {
+        const size_t want = (size_t)ctx->sm_count_total * 128 * 256 * 4;
+        cudaError_t e = cudaMalloc(&ctx->split_scratch, want);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            ctx->split_scratch = nullptr;
+            return mtl_set_error(ctx, MTL_ERR_NOMEM, "cudaMalloc of %zu split-scratch bytes failed: %s", want, cudaGetErrorString(e));
+        }
+    }
+    *out = ctx->split_scratch;
     return MTL_OK;
 }
 
@@ -125,7 +143,7 @@ int32_t mtl_ctx_create(int32_t device, mtl_ctx** out) {
     }
     ctx->owns_stream = true;
     cudaDeviceProp prop;
-    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
+    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) ctx->sm_count = ctx->sm_count_total = prop.multiProcessorCount;
     const size_t status_bytes = 256 + 8192 * sizeof(int32_t);
     if (cudaMalloc((void**)&ctx->dev_status, status_bytes) != cudaSuccess ||
         cudaMemset(ctx->dev_status, 0, status_bytes) != cudaSuccess) {
@@ -168,6 +186,7 @@ int32_t mtl_ctx_destroy(mtl_ctx* ctx) {
     }
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->ws2) cudaFree(ctx->ws2);
+    if (ctx->split_scratch) cudaFree(ctx->split_scratch);
     for (void* p : ctx->retired) cudaFree(p);
     for (auto& g : ctx->guarded) cudaFree((uint8_t*)g.first - kGuardBytes);   // blocks the caller never freed
     if (ctx->dev_status) cudaFree(ctx->dev_status);
@@ -221,6 +240,7 @@ int32_t mtl_sync(mtl_ctx* ctx) {
 const char* mtl_last_error(mtl_ctx* ctx) { return ctx ? ctx->err : "null context"; }
 
 int64_t mtl_launch_count(mtl_ctx* ctx) { return ctx ? ctx->launches : -1; }
+int64_t mtl_conv_split_tiles(mtl_ctx* ctx) { return ctx ? ctx->conv_split_tiles : -1; }
 
 int32_t mtl_device_status(mtl_ctx* ctx, int32_t* out_status) {
     MTL_CHECK_CTX(ctx);

@@ -541,8 +541,32 @@ struct ConvTParams {
     int acc_stride;         // TMEM columns between the two accumulators (248 when paired: the shifted
                             // read of the second one must stay inside the 512 allocated columns)
     int vec_ok;             // channel planes are 16-byte aligned: four adjacent pixels may leave as a float4
+    // Work items: the first `whole_items` are whole tiles; every later pair is ONE tile whose k-blocks are
+    // split at kb_half over two CTAs (the tiles of a partial last wave, when twice as many CTAs are free).
+    // Each half parks its accumulator in split_scratch unless the other half is already there; whichever
+    // finishes second adds the parked half to its own (a + b == b + a, so the result does not depend on
+    // which one that was) and runs the ordinary epilogue.
+    int whole_items, n_items, kb_half;
+    float4* split_scratch;      // per split tile and half: [16 column chunks][4 warps][4][32 lanes] float4
+    int32_t* split_tickets;     // per split tile, zero between launches
     int32_t* status;
 };
+
+struct ConvTItem {
+    int tile, kb0, kb1, slot, part;   // slot < 0: a whole tile
+};
+__device__ __forceinline__ ConvTItem conv_t_item(const ConvTParams& p, int w, int kb_total) {
+    ConvTItem it;
+    if (w < p.whole_items) {
+        it.tile = w; it.kb0 = 0; it.kb1 = kb_total; it.slot = -1; it.part = 0;
+    } else {
+        const int i = w - p.whole_items;
+        it.slot = i >> 1; it.part = i & 1; it.tile = p.whole_items + it.slot;
+        it.kb0 = it.part ? p.kb_half : 0;
+        it.kb1 = it.part ? kb_total : p.kb_half;
+    }
+    return it;
+}
 
 // 2x2 / stride-2 max pooling of one channel's BW x 2 pixels held in registers (r[0..BW) the upper row,
 // r[BW..2BW) the lower), after bias and RELU.  MAXPOOL2D.forward order: the window is scanned
@@ -585,14 +609,13 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
     uint64_t* tmem_empty = tmem_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* split_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
     int* col_off = reinterpret_cast<int*>(smem + kTStages * kTStageBytes + 256);
     int* col_vec = col_off + 256;
     float* stage_buf = reinterpret_cast<float*>(col_vec + 64);  // 4 warps x kTStgFloats
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int tiles_m = p.tiles_w * p.tiles_h * p.tiles_nb;
-    const int num_tiles = tiles_m * p.tiles_k;
     const int cblocks = (p.Cin + BK - 1) / BK;
     const int kb_per_seg = p.R * p.s_count * cblocks;
     const int kb_total = kb_per_seg * p.nseg;
@@ -624,7 +647,9 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
             uint32_t phase = 0;
             bool ok = true;
             const uint32_t tx = (uint32_t)kTABytes + (uint32_t)p.npix * 128u;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int w = blockIdx.x; w < p.n_items && ok; w += gridDim.x) {
+                const ConvTItem it = conv_t_item(p, w, kb_total);
+                const int t = it.tile;
                 const int kt = t % p.tiles_k;
                 int mt = t / p.tiles_k;
                 const int tw = mt % p.tiles_w;
@@ -632,22 +657,32 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                 const int th = mt % p.tiles_h;
                 const int tnb = mt / p.tiles_h;
                 const int ow0 = tw * p.bw, oh0 = th * p.bh, n0 = tnb * p.bn;
-                for (int seg = 0; seg < p.nseg && ok; ++seg) {
+                // k-block kb = ((seg * R + r) * s_count + si) * cblocks + cb
+                int seg = it.kb0 / kb_per_seg;
+                int rest = it.kb0 - seg * kb_per_seg;
+                int r = rest / (p.s_count * cblocks);
+                rest -= r * p.s_count * cblocks;
+                int si = rest / cblocks;
+                int cb = rest - si * cblocks;
+                for (int kb = it.kb0; kb < it.kb1; ++kb) {
                     const CUtensorMap* mx = p.segA[seg] ? &mapX1 : &mapX0;
                     const CUtensorMap* mw = p.segB[seg] ? &mapW1 : &mapW0;
-                    for (int r = 0; r < p.R && ok; ++r)
-                        for (int si = 0; si < p.s_count && ok; ++si)
-                            for (int cb = 0; cb < cblocks; ++cb) {
-                                if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) ok = false;
-                                if (__any_sync(0x3u, !ok)) { ok = false; break; }
-                                uint8_t* sa = tiles + stage * kTStageBytes;
-                                uint8_t* sb = sa + kTABytes;
-                                if (lane == 0) mbar_arrive_expect_tx(&full[stage], tx);
-                                __syncwarp(0x3u);
-                                if (lane == 0) tma_load_3d(sa, mw, &full[stage], cb * BK, kt * BM, r * p.s_count + si);
-                                else tma_load_4d(sb, mx, &full[stage], cb * BK, ow0 + si * p.s_step - p.pw, oh0 + r - p.ph, n0);
-                                if (++stage == kTStages) { stage = 0; phase ^= 1u; }
-                            }
+                    if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) ok = false;
+                    if (__any_sync(0x3u, !ok)) { ok = false; break; }
+                    uint8_t* sa = tiles + stage * kTStageBytes;
+                    uint8_t* sb = sa + kTABytes;
+                    if (lane == 0) mbar_arrive_expect_tx(&full[stage], tx);
+                    __syncwarp(0x3u);
+                    if (lane == 0) tma_load_3d(sa, mw, &full[stage], cb * BK, kt * BM, r * p.s_count + si);
+                    else tma_load_4d(sb, mx, &full[stage], cb * BK, ow0 + si * p.s_step - p.pw, oh0 + r - p.ph, n0);
+                    if (++stage == kTStages) { stage = 0; phase ^= 1u; }
+                    if (++cb == cblocks) {
+                        cb = 0;
+                        if (++si == p.s_count) {
+                            si = 0;
+                            if (++r == p.R) { r = 0; ++seg; }
+                        }
+                    }
                 }
             }
             if (!ok && lane == 0) atomicExch(p.status, MTL_ERR_TIMEOUT);
@@ -659,20 +694,21 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
             uint32_t phase = 0;
             bool ok = true;
             int local = 0;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+            for (int w = blockIdx.x; w < p.n_items && ok; w += gridDim.x, ++local) {
+                const ConvTItem it = conv_t_item(p, w, kb_total);
                 const int acc = local & 1;
                 const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
                 if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, kWaitBudgetNs)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * p.acc_stride);
-                for (int kb = 0; kb < kb_total; ++kb) {
+                for (int kb = it.kb0; kb < it.kb1; ++kb) {
                     if (!mbar_wait(&full[stage], phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t sa = smem_u32(tiles + stage * kTStageBytes);
                     const uint32_t sb = sa + kTABytes;
 #pragma unroll
                     for (int kk = 0; kk < BK / 8; ++kk)
-                        mma_tf32(tmem_d, desc_k_major(sa, kk), desc_k_major(sb, kk), idesc, (kb | kk) ? 1u : 0u);
+                        mma_tf32(tmem_d, desc_k_major(sa, kk), desc_k_major(sb, kk), idesc, (kb > it.kb0 || kk) ? 1u : 0u);
                     mma_commit(&empty[stage]);
                     if (++stage == kTStages) { stage = 0; phase ^= 1u; }
                 }
@@ -686,7 +722,9 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
         const int plane = p.OH * p.OW;
         bool ok = true;
         int local = 0;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+        for (int w = blockIdx.x; w < p.n_items && ok; w += gridDim.x, ++local) {
+            const ConvTItem it = conv_t_item(p, w, kb_total);
+            const int t = it.tile;
             const int kt = t % p.tiles_k;
             int mt = t / p.tiles_k;
             const int tw = mt % p.tiles_w;
@@ -702,6 +740,64 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, kWaitBudgetNs)) { ok = false; break; }
             tc_fence_after_sync();
+            if (it.slot >= 0) {
+                // One half of a k-split tile.  Nobody waits here: a half that finds the other already parked
+                // skips its own dump, otherwise it parks its accumulator and draws a ticket; the second to
+                // draw adds the parked half into its own tensor memory and carries on as if it had run the
+                // whole reduction.
+                const uint32_t half_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.acc_stride);
+                const int nchunk = p.n_mma >> 4;
+                float4* mine = p.split_scratch + (size_t)(it.slot * 2 + it.part) * (16 * 4 * 4 * 32);
+                const float4* other = p.split_scratch + (size_t)(it.slot * 2 + (it.part ^ 1)) * (16 * 4 * 4 * 32);
+                int32_t* ticket = p.split_tickets + it.slot;
+                if (threadIdx.x == 64) *split_flag = *reinterpret_cast<volatile int32_t*>(ticket);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                int folder = *split_flag;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (!folder) {
+                    for (int c = 0; c < nchunk; ++c) {
+                        uint32_t v[16];
+                        tmem_ld_32x16(half_addr + (uint32_t)(c * 16), v);
+                        tmem_ld_wait();
+                        float4* dst = mine + ((size_t)(c * 4 + quad) * 4) * 32 + lane;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g)
+                            __stcg(dst + g * 32, make_float4(__uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
+                                                             __uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3])));
+                    }
+                    __threadfence();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (threadIdx.x == 64) *split_flag = atomicAdd(ticket, 1);
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    folder = *split_flag;
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
+                if (!folder) {
+                    tc_fence_before_sync();
+                    mbar_arrive(&tmem_empty[acc]);
+                    continue;
+                }
+                __threadfence();
+                for (int c = 0; c < nchunk; ++c) {
+                    uint32_t v[16];
+                    tmem_ld_32x16(half_addr + (uint32_t)(c * 16), v);
+                    const float4* src = other + ((size_t)(c * 4 + quad) * 4) * 32 + lane;
+                    float4 o[4];
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) o[g] = __ldcg(src + g * 32);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        v[g * 4] = __float_as_uint(__uint_as_float(v[g * 4]) + o[g].x);
+                        v[g * 4 + 1] = __float_as_uint(__uint_as_float(v[g * 4 + 1]) + o[g].y);
+                        v[g * 4 + 2] = __float_as_uint(__uint_as_float(v[g * 4 + 2]) + o[g].z);
+                        v[g * 4 + 3] = __float_as_uint(__uint_as_float(v[g * 4 + 3]) + o[g].w);
+                    }
+                    tmem_st_32x16(half_addr + (uint32_t)(c * 16), v);
+                }
+                tmem_st_wait();
+                if (threadIdx.x == 64) *ticket = 0;   // ready for the next launch
+            }
             // Column j of the accumulator is pixel (j % bw, (j / bw) % bh, j / (bw*bh)) of the box.
             // The 128 epilogue threads first tabulate, per column, the offset of that pixel inside
             // one channel plane set (-1 = outside the tensor) and, per group of four columns,
@@ -930,6 +1026,19 @@ void choose_box_n(int OW, int OH, int N, int limit, int* bw_, int* bh_, int* bn_
     }
 }
 
+// k_conv_igemm_t's work items: the tiles of a partial last wave are split along k over two CTAs each when
+// twice as many CTAs are free and the reduction is long enough to be worth a trip of one accumulator
+// through L2 (put at an eighth of a tile in the cost of a plan).
+static bool igemm_tail_splits(const mtl_ctx* ctx, int64_t tiles, int kblocks) {
+    const int64_t rem = tiles % ctx->sm_count;
+    return ctx->tune.conv_tail_split && rem > 0 && 2 * rem <= ctx->sm_count && kblocks >= 16;
+}
+static double igemm_waves(const mtl_ctx* ctx, int64_t tiles, int kblocks) {
+    const int64_t full = tiles / ctx->sm_count, rem = tiles % ctx->sm_count;
+    if (rem == 0) return (double)full;
+    return (double)full + (igemm_tail_splits(ctx, tiles, kblocks) ? 0.625 : 1.0);
+}
+
 template <int BN>
 int32_t launch_igemm(mtl_ctx* ctx, const CUtensorMap* maps, const ConvTcParams& p) {
     using C = Cfg<BN>;
@@ -950,24 +1059,25 @@ bool igemm_channel_major(const IgemmCall& c) {
            mtl_global_tuning().conv_channel_major;
 }
 // Two taps per instruction when the layer has at most 64 output channels (see ConvTParams::paired).
-bool igemm_paired(const IgemmCall& c) {
-    // Pairing shortens the main loop but lengthens the epilogue (second TMEM read, shuffles): it pays
-    // only when the reduction per tile is long enough for the main loop to be the longer of the two.
-    const int paired_kblocks = c.R * ((c.S + 1) / 2) * ((c.Cin + 31) / 32);
+bool igemm_paired(const IgemmCall& c, int x3) {
+    // Pairing shortens the main loop but lengthens the epilogue (a second TMEM read per column chunk): it
+    // pays only when the reduction per tile is long enough for the main loop to be the longer of the two.
+    // A 3xTF32 k-block issues three products, so its main loop is three times as long.
+    const int paired_kblocks = c.R * ((c.S + 1) / 2) * ((c.Cin + 31) / 32) * (x3 ? 3 : 1);
     return igemm_channel_major(c) && c.Kout <= 64 && c.S >= 2 && c.OW + 1 <= 240 &&
            paired_kblocks >= mtl_global_tuning().conv_paired_min_kblocks && mtl_global_tuning().conv_paired;
 }
 // At most 64 output channels without pairing: the channels are still spread over the four TMEM lane
 // quadrants (16 each) so that all four epilogue warps store, instead of two doing all of it.
-bool igemm_spread(const IgemmCall& c) {
-    return igemm_channel_major(c) && c.Kout <= 64 && !igemm_paired(c) &&
+bool igemm_spread(const IgemmCall& c, int x3) {
+    return igemm_channel_major(c) && c.Kout <= 64 && !igemm_paired(c, x3) &&
            mtl_global_tuning().conv_spread;
 }
 // Floats of one re-laid-out copy of the weights.
-size_t igemm_weight_floats(const IgemmCall& c) {
+size_t igemm_weight_floats(const IgemmCall& c, int x3) {
     const size_t plain = (size_t)c.wK * c.wC * c.R * c.S;
-    if (igemm_paired(c)) return (size_t)c.R * ((c.S + 1) / 2) * 128 * c.Cin;
-    if (igemm_spread(c)) return (size_t)c.R * c.S * 128 * c.Cin;
+    if (igemm_paired(c, x3)) return (size_t)c.R * ((c.S + 1) / 2) * 128 * c.Cin;
+    if (igemm_spread(c, x3)) return (size_t)c.R * c.S * 128 * c.Cin;
     return plain;
 }
 
@@ -986,7 +1096,7 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
 int32_t run_igemm(mtl_ctx* ctx, const IgemmCall& c, int x3) {
     const int HW = c.IH * c.IW;
     const size_t n_act = (size_t)c.N * c.Cin * HW;
-    const size_t n_wt = igemm_weight_floats(c);
+    const size_t n_wt = igemm_weight_floats(c, x3);
     const size_t act_pad = (n_act + 63) & ~(size_t)63, wt_pad = (n_wt + 63) & ~(size_t)63;
     const int parts = x3 ? 2 : 1;
     void* ws;
@@ -1013,11 +1123,11 @@ int32_t run_igemm(mtl_ctx* ctx, const IgemmCall& c, int x3) {
 
 // Weight re-layout and the implicit-GEMM kernel; the channels-last activations are already in place.
 int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, float* a_lo, float* w_hi, float* w_lo) {
-    const size_t n_wt = igemm_weight_floats(c);
+    const size_t n_wt = igemm_weight_floats(c, x3);
     int32_t rc = MTL_OK;
     const bool channel_major = igemm_channel_major(c);
-    const bool paired = igemm_paired(c);
-    const bool spread = igemm_spread(c);
+    const bool paired = igemm_paired(c, x3);
+    const bool spread = igemm_spread(c, x3);
     int wgrid = mtl_grid_for((int64_t)n_wt, 256, ctx->sm_count, 8);
     if (paired || spread) {
         if (x3) mtl_launch_pdl(ctx, k_weights_relayout_paired<true>, dim3(wgrid), dim3(256), (size_t)(0), w_hi, w_lo, c.wt, c.wK, c.wC, c.R, c.S, c.flip, paired ? 1 : 0);
@@ -1038,6 +1148,7 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
         q.acc_stride = paired ? 248 : 256;
         q.pool = c.pool;
         q.pool_idx = c.pool_idx;
+        const int kblocks = c.R * q.s_count * ((c.Cin + BK - 1) / BK) * (x3 ? 3 : 1);
         if (c.pool) {
             // whole rows, two of them, as many images as fit while the last 32-column read stays inside
             q.bw = c.OW;
@@ -1045,13 +1156,12 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
             int bn_max = (256 - 32) / (2 * c.OW) + 1;
             if (bn_max > c.N) bn_max = c.N;
             // images per box: fewest (waves of tiles) x (TMA rows and boxes of a k-block), which for a small
-            // batch is not the fullest box (256 images: 203 tiles of 9 images and 259 tiles of 7 both take
-            // two waves on 148 SMs, and the tile of 7 is shorter)
+            // batch is not always the fullest box (two waves of shorter tiles beat two waves of full ones)
             double best = 1e30;
             q.bn = bn_max;
             for (int bn = bn_max; bn >= 1; --bn) {
                 const int64_t tiles = (int64_t)(c.OH / 2) * ((c.N + bn - 1) / bn) * ((c.Kout + BM - 1) / BM);
-                const double cost = (double)((tiles + ctx->sm_count - 1) / ctx->sm_count) * (128 + 2 * c.OW * bn + 70);
+                const double cost = igemm_waves(ctx, tiles, kblocks) * (128 + 2 * c.OW * bn + 70);
                 if (cost < best * 0.98) { best = cost; q.bn = bn; }
             }
         } else if (paired) {
@@ -1073,7 +1183,7 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
             double cost0 = 1e30;
             for (int bn = q.bn, bn0 = q.bn; bn >= 1; --bn) {
                 const int64_t tiles = (int64_t)((c.OH + q.bh - 1) / q.bh) * ((c.N + bn - 1) / bn);
-                const double cost = (double)((tiles + ctx->sm_count - 1) / ctx->sm_count) * (128 + q.bw * q.bh * bn + 70);
+                const double cost = igemm_waves(ctx, tiles, kblocks) * (128 + q.bw * q.bh * bn + 70);
                 if (bn == bn0) cost0 = cost;
                 if (cost < cost0 * 0.98) { cost0 = cost; q.bn = bn; }
             }
@@ -1109,8 +1219,23 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
             if (rc) return rc;
         }
         MTL_CUDA(ctx, cudaFuncSetAttribute(k_conv_igemm_t, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmemBytes));
-        int tiles = q.tiles_w * q.tiles_h * q.tiles_nb * q.tiles_k;
-        int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+        const int tiles = q.tiles_w * q.tiles_h * q.tiles_nb * q.tiles_k;
+        q.whole_items = q.n_items = tiles;
+        q.kb_half = 0;
+        q.split_scratch = nullptr;
+        q.split_tickets = ctx->tickets + 4096;
+        if (igemm_tail_splits(ctx, tiles, kblocks)) {
+            const int rem = tiles % ctx->sm_count;   // 2 * rem <= sm_count <= sm_count_total slots of scratch
+            void* sp;
+            rc = mtl_split_scratch(ctx, &sp);
+            if (rc) return rc;
+            q.split_scratch = (float4*)sp;
+            q.whole_items = tiles - rem;
+            q.n_items = q.whole_items + 2 * rem;
+            q.kb_half = (kblocks + 1) / 2;
+            ctx->conv_split_tiles += rem;
+        }
+        int grid = q.n_items < ctx->sm_count ? q.n_items : ctx->sm_count;
         {
             mtl_prof_scope prof(ctx, MTL_PROF_CONV_IGEMM);
             mtl_launch_pdl(ctx, k_conv_igemm_t, dim3(grid), dim3(kThreads), (size_t)(kTSmemBytes), tm[0], tm[1], tm[2], tm[3], q);
@@ -1607,7 +1732,7 @@ int32_t mtl_conv_bwd_fused_tc_src(mtl_ctx* ctx, float* dX, float* dW, float* db,
     c.R = g.R; c.S = g.S; c.ph = g.R - 1 - g.ph; c.pw = g.S - 1 - g.pw;
     c.act = ug; c.wt = Wt; c.wK = g.K; c.wC = g.C; c.flip = 1;
     c.out = dX; c.bias = nullptr; c.accumulate = acc_dx; c.relu = 0;
-    const size_t n_wt = igemm_weight_floats(c);
+    const size_t n_wt = igemm_weight_floats(c, x3);
     const size_t u_pad = (n_u + 63) & ~(size_t)63, x_pad = (n_x + 63) & ~(size_t)63, wt_pad = (n_wt + 63) & ~(size_t)63;
     const int parts = x3 ? 2 : 1;
     const int ptiles = pg ? 1 : (g.OH * g.OW + 31) / 32;  // rows of per-block channel sums per image

@@ -100,6 +100,9 @@ class Context:
     def launch_count(self) -> int:
         return int(self.lib.mtl_launch_count(self.handle))
 
+    def conv_split_tiles(self) -> int:
+        return int(self.lib.mtl_conv_split_tiles(self.handle))
+
     def device_status(self) -> int:
         s = C.c_int32()
         self._check(self.lib.mtl_device_status(self.handle, C.byref(s)))
