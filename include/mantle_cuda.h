@@ -501,6 +501,23 @@ MTL_API int32_t mtl_dp_status(mtl_ctx* ctx);
 /* Sum-allreduce of `n` floats in place on a communication stream, ordered after everything
  * enqueued on the context's stream so far; overlaps with later launches until mtl_dp_wait. */
 MTL_API int32_t mtl_dp_allreduce_async(mtl_ctx* ctx, float* buf, int64_t n);
+/* The same sum for the LAST bucket of a step, which has nothing left to overlap with.  When every rank of the
+ * group runs on this machine and could map every other rank's exchange buffer (CUDA IPC, decided once in
+ * mtl_dp_init; MANTLE_DP_TAIL_EXCHANGE=0 on any rank switches it off for the group) and n is at most 16384,
+ * ONE kernel on the context's stream pushes the values into the peers' buffers over NVLink and collects
+ * theirs, summing in rank order, so every rank holds the same bits when the kernel ends: no communication
+ * stream, no mtl_dp_wait needed for it.  Every rank must call it the same number of times with the same n.  A
+ * peer that does not answer within 20 s ends the wait: the kernel writes MTL_ERR_TIMEOUT to the status word
+ * (mtl_device_status), leaves `buf` unsummed and returns.  Otherwise the call is mtl_dp_allreduce_async. */
+MTL_API int32_t mtl_dp_allreduce_tail(mtl_ctx* ctx, float* buf, int64_t n);
+/* 1 when mtl_dp_allreduce_tail exchanges directly, 0 when it falls back to the collective library. */
+MTL_API int32_t mtl_dp_tail_exchange_enabled(mtl_ctx* ctx);
+/* Self-test of that exchange on ONE GPU: `world` emulated ranks (2..8) in one cooperative launch, rank r
+ * owning grads[r*n .. r*n+n) (device memory), `steps` exchanges in a row; afterwards every rank's slice
+ * holds the rank-ordered sum.  With silent_rank >= 0 that rank never pushes and the others give up after
+ * budget_us microseconds: the status word reads MTL_ERR_TIMEOUT and their slices are unchanged. */
+MTL_API int32_t mtl_selftest_tail_exchange(mtl_ctx* ctx, float* grads, int32_t world, int32_t n, int32_t steps,
+                                           int32_t silent_rank, int32_t budget_us);
 /* Makes the context's stream wait for all outstanding allreduces. */
 MTL_API int32_t mtl_dp_wait(mtl_ctx* ctx);
 /* Host callback of the fused CONV2D backward entry points (mtl_conv2d_bwd_fused*, mtl_conv2d_bwd_pooled):

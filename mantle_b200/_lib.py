@@ -165,6 +165,9 @@ SIGNATURES = {
     "mtl_dp_probe": (_i32, [C.POINTER(C.c_uint8), _i32, _i32, _i32]),
     "mtl_dp_status": (_i32, [_vp]),
     "mtl_dp_allreduce_async": (_i32, [_vp, _vp, _i64]),
+    "mtl_dp_allreduce_tail": (_i32, [_vp, _vp, _i64]),
+    "mtl_dp_tail_exchange_enabled": (_i32, [_vp]),
+    "mtl_selftest_tail_exchange": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _i32]),
     "mtl_set_grads_ready_hook": (_i32, [_vp, _vp, _vp]),
     "mtl_dp_wait": (_i32, [_vp]),
     "mtl_dp_broadcast": (_i32, [_vp, _vp, _i64, _i32]),

@@ -2,6 +2,19 @@
 // over NVLink through NCCL on a separate communication stream, event-ordered against the compute
 // stream so that the exchange of a finished gradient bucket overlaps the backward pass of earlier
 // layers.  NCCL is bound at run time (dlopen) so that single-GPU use needs no NCCL at all.
+//
+// The LAST bucket of a step cannot overlap anything: the gradients of the first layer are final only
+// when the backward pass is over, and a library collective then costs its launch, its protocol and
+// two stream hand-overs (measured: 35 - 43 us of a step exposed at 2 GPUs) for a few kilobytes.  For
+// that bucket (mtl_dp_allreduce_tail) the ranks of one machine exchange directly over NVLink: every
+// rank maps every other rank's exchange buffer (CUDA IPC) at start-up, and one kernel on the compute
+// stream pushes its values into the peers' buffers as 8-byte {value, step number} words and then
+// collects the peers' values from its own buffer, summing in rank order (every rank gets the same bits).
+// An 8-byte store is indivisible, so a word whose step number matches carries its value: no flags, no
+// fences.  Two buffer halves used in turn keep a fast rank's next step off the words a slow rank still
+// reads (a rank cannot run two steps ahead: its next exchange needs the slow rank's push).  Every wait
+// on a peer is bounded; when it runs out the kernel writes MTL_ERR_TIMEOUT to the status word, leaves
+// the gradient as it was and returns.
 #include <stdlib.h>
 #include <stdio.h>
 #include <dlfcn.h>
@@ -11,6 +24,7 @@
 #include <memory>
 #include <mutex>
 #include <thread>
+#include <vector>
 
 #include "common.cuh"
 
@@ -20,8 +34,8 @@ namespace {
 typedef struct ncclComm* ncclComm_t;
 typedef struct { char internal[128]; } ncclUniqueId;
 enum { ncclSuccess = 0 };
-enum { ncclFloat32 = 7 };
-enum { ncclSum = 0 };
+enum { ncclInt8 = 0, ncclInt32 = 2, ncclFloat32 = 7 };
+enum { ncclSum = 0, ncclMin = 3 };
 
 struct NcclApi {
     void* lib = nullptr;
@@ -32,6 +46,7 @@ struct NcclApi {
     int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;
     int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
     int (*Broadcast)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;   // optional
     const char* (*GetErrorString)(int) = nullptr;
 };
 
@@ -65,6 +80,7 @@ bool load_nccl(char* why, size_t why_len) {
     MTL_SYM(Broadcast, "ncclBroadcast")
     MTL_SYM(GetErrorString, "ncclGetErrorString")
 #undef MTL_SYM
+    *(void**)(&g_nccl.AllGather) = dlsym(lib, "ncclAllGather");   // without it the tail exchange stays off
     g_nccl.lib = lib;
     return true;
 }
@@ -134,7 +150,96 @@ struct DpState {
     cudaEvent_t done = nullptr;   // comm -> compute
     bool pending = false;
     int reserved_sms = 0;         // SMs the compute kernels leave to the collective (taken off ctx->sm_count)
+    // direct exchange of the last bucket (see the top of this file)
+    bool tail_on = false;
+    uint2* xbuf = nullptr;        // this rank's buffer: [2 halves][world][kTailCap] {value, step}
+    uint2* peer_xbuf[8] = {};     // every rank's buffer as mapped here ([rank] = xbuf)
+    uint32_t* tail_seq = nullptr; // device: number of exchanges done
 };
+
+constexpr int kTailCap = 16384;           // floats per exchange (64 KB of gradient)
+constexpr int kTailMaxWorld = 8;
+constexpr uint64_t kTailBudgetNs = 20ull * 1000 * 1000 * 1000;
+
+struct TailX {
+    float* grad;
+    int n, rank, world;
+    uint2* slots[kTailMaxWorld];   // slots[r]: rank r's buffer
+    uint32_t* seq;                 // exchanges done so far (this rank's counter)
+    int32_t* ticket;               // zero between launches
+    int32_t* status;
+    uint64_t budget_ns;
+};
+
+__device__ __forceinline__ uint64_t tail_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void st_word(uint2* p, uint32_t value, uint32_t step) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(value), "r"(step) : "memory");
+}
+__device__ __forceinline__ uint2 ld_word(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+
+// One rank's part of the exchange, run by `nblocks` blocks of 256 threads (block index `b` among them).
+// Thread i pushes element i to every peer, then collects element i of every peer: no thread waits for
+// another thread of its own rank.
+__device__ void tail_exchange_rank(const TailX& p, int b, int nblocks, bool silent) {
+    __shared__ int s_last;
+    const uint32_t step = *reinterpret_cast<volatile uint32_t*>(p.seq) + 1u;
+    const int half = (int)(step & 1u);
+    bool timed_out = false;
+    for (int i = b * 256 + (int)threadIdx.x; i < p.n && !silent; i += nblocks * 256) {
+        const float g = p.grad[i];
+        for (int r = 0; r < p.world; ++r)
+            if (r != p.rank) st_word(p.slots[r] + ((size_t)(half * p.world + p.rank) * kTailCap + i), __float_as_uint(g), step);
+        float sum = 0.0f;
+        const uint64_t t0 = tail_timer_ns();
+        for (int r = 0; r < p.world && !timed_out; ++r) {
+            float v = g;
+            if (r != p.rank) {
+                const uint2* src = p.slots[p.rank] + ((size_t)(half * p.world + r) * kTailCap + i);
+                uint2 w = ld_word(src);
+                for (uint32_t spins = 0; w.y != step; ++spins) {
+                    if ((spins & 63u) == 63u && tail_timer_ns() - t0 > p.budget_ns) { timed_out = true; break; }
+                    w = ld_word(src);
+                }
+                v = __uint_as_float(w.x);
+            }
+            sum += v;
+        }
+        if (timed_out) break;
+        p.grad[i] = sum;
+    }
+    if (timed_out) atomicExch(p.status, MTL_ERR_TIMEOUT);
+    // the block that finishes last counts the exchange (every block has read the counter by then)
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(p.ticket, 1) == nblocks - 1;
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+        *reinterpret_cast<volatile uint32_t*>(p.seq) = step;
+        *p.ticket = 0;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_tail_exchange(TailX p) {
+    mtl_pdl_sync();
+    tail_exchange_rank(p, (int)blockIdx.x, (int)gridDim.x, false);
+}
+
+// All ranks of a group in ONE launch on one GPU (self-test): blockIdx.y is the rank.  The blocks wait on
+// one another, so the launch is cooperative (all blocks resident) and small.
+struct TailXAll {
+    TailX r[kTailMaxWorld];
+    int silent_rank;   // a rank that never pushes (-1: none)
+};
+__global__ void __launch_bounds__(256) k_tail_exchange_all(TailXAll a) {
+    tail_exchange_rank(a.r[blockIdx.y], (int)blockIdx.x, (int)gridDim.x, (int)blockIdx.y == a.silent_rank);
+}
 
 #define MTL_NCCL(ctx, call)                                                                      \
     do {                                                                                         \
@@ -143,7 +248,67 @@ struct DpState {
             return mtl_set_error(ctx, MTL_ERR_COMM, "%s failed: %s", #call, g_nccl.GetErrorString(r__)); \
     } while (0)
 
+void tail_release(DpState* st) {
+    for (int r = 0; r < kTailMaxWorld; ++r) {
+        if (st->peer_xbuf[r] && r != st->rank) cudaIpcCloseMemHandle(st->peer_xbuf[r]);
+        st->peer_xbuf[r] = nullptr;
+    }
+    if (st->xbuf) cudaFree(st->xbuf);
+    st->xbuf = nullptr;
+    st->tail_seq = nullptr;
+    st->tail_on = false;
+}
+
 }  // namespace
+
+// Maps every rank's exchange buffer into this process.  Every rank runs the same collectives here, whether
+// or not it wants (or manages) the direct exchange, and the group uses it only if EVERY rank mapped every
+// buffer: a rank on its own would wait for pushes that never come.
+static int32_t tail_setup(mtl_ctx* ctx, DpState* st, bool want) {
+    const int W = st->world;
+    const size_t words = (size_t)2 * W * kTailCap;
+    int ok = want ? 1 : 0;
+    cudaIpcMemHandle_t mine;
+    memset(&mine, 0, sizeof(mine));
+    if (ok && (cudaMalloc(&st->xbuf, words * sizeof(uint2) + 256) != cudaSuccess ||
+               cudaMemset(st->xbuf, 0, words * sizeof(uint2) + 256) != cudaSuccess ||
+               cudaDeviceSynchronize() != cudaSuccess || cudaIpcGetMemHandle(&mine, st->xbuf) != cudaSuccess)) {
+        cudaGetLastError();
+        ok = 0;
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    uint8_t* dev = nullptr;   // [W handles][one int32 flag]
+    MTL_CUDA(ctx, cudaMalloc(&dev, (size_t)(W + 1) * 64));
+    std::unique_ptr<uint8_t, void (*)(uint8_t*)> dev_owner(dev, [](uint8_t* q) { cudaFree(q); });
+    MTL_CUDA(ctx, cudaMemcpyAsync(dev + (size_t)st->rank * 64, &mine, 64, cudaMemcpyHostToDevice, ctx->stream));
+    MTL_NCCL(ctx, g_nccl.AllGather(dev + (size_t)st->rank * 64, dev, 64, ncclInt8, st->comm, ctx->stream));
+    std::vector<cudaIpcMemHandle_t> all((size_t)W);
+    MTL_CUDA(ctx, cudaMemcpyAsync(all.data(), dev, (size_t)W * 64, cudaMemcpyDeviceToHost, ctx->stream));
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int r = 0; r < W && ok; ++r) {
+        if (r == st->rank) { st->peer_xbuf[r] = st->xbuf; continue; }
+        void* q = nullptr;
+        if (cudaIpcOpenMemHandle(&q, all[(size_t)r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            cudaGetLastError();
+            ok = 0;
+        } else {
+            st->peer_xbuf[r] = (uint2*)q;
+        }
+    }
+    int32_t flag = ok;
+    int32_t* dflag = reinterpret_cast<int32_t*>(dev + (size_t)W * 64);
+    MTL_CUDA(ctx, cudaMemcpyAsync(dflag, &flag, 4, cudaMemcpyHostToDevice, ctx->stream));
+    MTL_NCCL(ctx, g_nccl.AllReduce(dflag, dflag, 1, ncclInt32, ncclMin, st->comm, ctx->stream));
+    MTL_CUDA(ctx, cudaMemcpyAsync(&flag, dflag, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (flag == 1) {
+        st->tail_on = true;
+        st->tail_seq = reinterpret_cast<uint32_t*>(st->xbuf + words);
+    } else {
+        tail_release(st);
+    }
+    return MTL_OK;
+}
 
 extern "C" {
 
@@ -208,6 +373,12 @@ int32_t mtl_dp_init(mtl_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world
         st->reserved_sms = reserve;
         ctx->sm_count -= reserve;          // persistent grids are sized from this
     }
+    int want_tail = 1;
+    if (const char* e = getenv("MANTLE_DP_TAIL_EXCHANGE")) want_tail = atoi(e);
+    if (world > 1 && world <= kTailMaxWorld && g_nccl.AllGather) {
+        int32_t rc = tail_setup(ctx, st, want_tail != 0);
+        if (rc) return rc;
+    }
     return MTL_OK;
 }
 
@@ -222,6 +393,68 @@ int32_t mtl_dp_allreduce_async(mtl_ctx* ctx, float* buf, int64_t n) {
     MTL_CUDA(ctx, cudaStreamWaitEvent(st->comm_stream, st->ready, 0));
     MTL_NCCL(ctx, g_nccl.AllReduce(buf, buf, (size_t)n, ncclFloat32, ncclSum, st->comm, st->comm_stream));
     st->pending = true;
+    return MTL_OK;
+}
+
+int32_t mtl_dp_allreduce_tail(mtl_ctx* ctx, float* buf, int64_t n) {
+    MTL_CHECK_CTX(ctx);
+    DpState* st = (DpState*)ctx->dp;
+    MTL_REQUIRE(ctx, st, "mtl_dp_init has not been called");
+    MTL_REQUIRE(ctx, buf && n >= 0, "bad arguments to mtl_dp_allreduce_tail");
+    if (!st->tail_on || n > kTailCap) return mtl_dp_allreduce_async(ctx, buf, n);
+    if (st->failed) return mtl_set_error(ctx, MTL_ERR_COMM, "the communicator failed earlier and was aborted");
+    if (n == 0) return MTL_OK;
+    TailX p;
+    p.grad = buf; p.n = (int)n; p.rank = st->rank; p.world = st->world;
+    for (int r = 0; r < kTailMaxWorld; ++r) p.slots[r] = st->peer_xbuf[r];
+    p.seq = st->tail_seq;
+    p.ticket = ctx->tickets + 8190;
+    p.status = ctx->dev_status;
+    p.budget_ns = kTailBudgetNs;
+    const int blocks = (int)((n + 255) / 256) < 32 ? (int)((n + 255) / 256) : 32;
+    mtl_launch_pdl(ctx, k_tail_exchange, dim3(blocks), dim3(256), (size_t)0, p);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
+
+int32_t mtl_dp_tail_exchange_enabled(mtl_ctx* ctx) {
+    if (!ctx || !ctx->dp) return 0;
+    return ((DpState*)ctx->dp)->tail_on ? 1 : 0;
+}
+
+int32_t mtl_selftest_tail_exchange(mtl_ctx* ctx, float* grads, int32_t world, int32_t n, int32_t steps,
+                                   int32_t silent_rank, int32_t budget_us) {
+    MTL_CHECK_CTX(ctx);
+    MTL_REQUIRE(ctx, grads && world >= 2 && world <= kTailMaxWorld && n >= 1 && n <= kTailCap && steps >= 1 &&
+                         silent_rank < world && budget_us >= 1,
+                "bad arguments to mtl_selftest_tail_exchange");
+    int coop = 0;
+    MTL_CUDA(ctx, cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, ctx->device));
+    MTL_REQUIRE(ctx, coop, "the device cannot launch cooperatively");
+    const size_t words = (size_t)2 * world * kTailCap;
+    const size_t per_rank = words * sizeof(uint2) + 256;
+    uint8_t* mem = nullptr;
+    MTL_CUDA(ctx, cudaMalloc(&mem, per_rank * world));
+    std::unique_ptr<uint8_t, void (*)(uint8_t*)> owner(mem, [](uint8_t* q) { cudaFree(q); });
+    MTL_CUDA(ctx, cudaMemsetAsync(mem, 0, per_rank * world, ctx->stream));
+    TailXAll a;
+    a.silent_rank = silent_rank;
+    for (int r = 0; r < world; ++r) {
+        TailX& p = a.r[r];
+        p.grad = grads + (size_t)r * n; p.n = n; p.rank = r; p.world = world;
+        for (int q = 0; q < kTailMaxWorld; ++q) p.slots[q] = q < world ? reinterpret_cast<uint2*>(mem + per_rank * q) : nullptr;
+        p.seq = reinterpret_cast<uint32_t*>(mem + per_rank * r + words * sizeof(uint2));
+        p.ticket = reinterpret_cast<int32_t*>(p.seq) + 1;
+        p.status = ctx->dev_status;
+        p.budget_ns = (uint64_t)budget_us * 1000ull;
+    }
+    const int blocks = (n + 255) / 256 < 8 ? (n + 255) / 256 : 8;   // at most 64 blocks in all: resident together
+    void* args[] = {&a};
+    for (int s = 0; s < steps; ++s) {
+        MTL_CUDA(ctx, cudaLaunchCooperativeKernel((void*)k_tail_exchange_all, dim3(blocks, world), dim3(256), args, 0, ctx->stream));
+        MTL_LAUNCHED(ctx);
+    }
+    MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return MTL_OK;
 }
 
@@ -300,6 +533,7 @@ int32_t mtl_dp_destroy(mtl_ctx* ctx) {
     cudaStreamSynchronize(st->comm_stream);
     cudaStreamSynchronize(ctx->stream);
     if (st->comm) g_nccl.CommDestroy(st->comm);
+    tail_release(st);
     cudaEventDestroy(st->ready);
     cudaEventDestroy(st->done);
     cudaStreamDestroy(st->comm_stream);

@@ -70,9 +70,13 @@ int64_t Trainer::input_bytes_per_step() const {
 
 void Trainer::node_done_thunk(void* self, int node) { static_cast<Trainer*>(self)->node_done(node); }
 
-void Trainer::flush_bucket() {
+// `last`: the bucket that ends the backward pass, which nothing can overlap: exchanged directly between the
+// GPUs on the compute stream when the group can (mtl_dp_allreduce_tail), else like the others.
+void Trainer::flush_bucket(bool last) {
     if (pending_lo_ < 0) return;
-    ck(model_.ctx(), mtl_dp_allreduce_async(model_.ctx(), model_.grads_flat() + pending_lo_, pending_hi_ - pending_lo_),
+    float* span = model_.grads_flat() + pending_lo_;
+    const int64_t n = pending_hi_ - pending_lo_;
+    ck(model_.ctx(), last ? mtl_dp_allreduce_tail(model_.ctx(), span, n) : mtl_dp_allreduce_async(model_.ctx(), span, n),
        "gradient allreduce");
     pending_lo_ = pending_hi_ = -1;
 }
@@ -100,7 +104,7 @@ void Trainer::node_done(int node) {
     }
     if (pending_lo_ >= 0 && (pending_hi_ - pending_lo_) * 4 >= bucket_bytes_) flush_bucket();
     if (node == 0) {
-        flush_bucket();
+        flush_bucket(true);
         ck(model_.ctx(), mtl_dp_wait(model_.ctx()), "gradient allreduce wait");
     }
 }

@@ -43,7 +43,7 @@ class Trainer {
     void stage_inputs(const std::vector<const float*>& host_inputs);
     static void node_done_thunk(void* self, int node);
     void node_done(int node);
-    void flush_bucket();
+    void flush_bucket(bool last = false);
     void map_final_nodes();
     bool fusion_mapped_ = false;
     bool exchange_ = true;

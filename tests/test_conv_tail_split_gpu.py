@@ -2,7 +2,7 @@
 CTAs (MANTLE_CONV_TAIL_SPLIT, read when the library is first used, hence child processes): forward, input
 gradient and the fused CONV2D + RELU + MAXPOOL2D forward at shapes whose plans split, in both tensor-core
 modes, against the same calls with the split switched off (the two differ by one fp32 re-association per
-output, so 2e-6 of the largest value; pooling indices identical except where two window elements are that
+output, so 5e-6 of the largest value; pooling indices identical except where two window elements are that
 close); two runs of the split path give identical bits.  The unsplit kernels are held to float64 elsewhere."""
 import os
 import subprocess
@@ -81,6 +81,6 @@ def test_split_tiles_match_whole_tiles(tmp_path):
                 assert np.allclose(pv_on[differ], pv_off[differ], rtol=0, atol=4e-6 * np.abs(pv_off).max()), key
             continue
         scale = np.abs(b).max()
-        assert np.max(np.abs(a - b)) <= 2e-6 * scale, (key, float(np.max(np.abs(a - b)) / scale))
+        assert np.max(np.abs(a - b)) <= 5e-6 * scale, (key, float(np.max(np.abs(a - b)) / scale))
         # the split path does not depend on which half arrives second
         assert np.array_equal(a, on[key[:-1] + "1"]), key

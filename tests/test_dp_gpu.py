@@ -24,6 +24,10 @@ def _data():
     return x, y, ws
 
 
+def _tail_values(rank):
+    return np.random.default_rng(100 + rank).normal(0, 1, 3001).astype(np.float32)
+
+
 def _train(rank, world, uid, q):
     try:
         _train_body(rank, world, uid, q)
@@ -59,9 +63,18 @@ def _train_body(rank, world, uid, q):
     trainer = host_api.Trainer(m, host_api.Adam(m, lr=1e-3), use_graph=True)
     losses = [trainer.step(x[i, rank * lb:(rank + 1) * lb], y[i, rank * lb:(rank + 1) * lb]) for i in range(STEPS)]
     params = [m.tensor(s) for s in tr]
+    # the direct exchange of a step's last bucket, called by hand: two exchanges in a row of rank-specific values
+    tail_on = int(ctx.lib.mtl_dp_tail_exchange_enabled(ctx.handle))
+    tail = None
+    if world > 1:
+        v = ctx.array(_tail_values(rank))
+        for _ in range(2):
+            ctx._check(ctx.lib.mtl_dp_allreduce_tail(ctx.handle, v.ptr, v.size))
+        ctx.sync()
+        tail = v.numpy()
     status = ctx.device_status()
     trainer.close()
-    q.put((rank, losses, params, status))
+    q.put((rank, losses, params, status, tail_on, tail))
     ctx.close()
 
 
@@ -113,6 +126,17 @@ def test_data_parallel_trajectory_equals_single_gpu(world):
             assert np.array_equal(a, b)
     for a, b in zip(ranks[0][2], single[2]):  # and close to the single-GPU parameters
         assert np.linalg.norm(a - b) <= 2e-2 * np.linalg.norm(b) + 1e-6
+    # ranks of one machine exchange the last bucket directly; the sum runs in rank order on every rank
+    assert all(r[4] == 1 for r in ranks), [r[4] for r in ranks]
+    want = np.zeros(3001, np.float32)
+    for r in range(world):
+        want = want + _tail_values(r)
+    first = want.copy()
+    want = np.zeros(3001, np.float32)
+    for r in range(world):
+        want = want + first
+    for r in ranks:
+        assert np.array_equal(r[5], want)
 
 
 def _visible_gpus():
