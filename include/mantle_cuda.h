@@ -404,6 +404,10 @@ MTL_API int32_t mtl_reduce_all_static(mtl_ctx* ctx, int32_t op, float* out, cons
  *                           rows runs in another order).  The reference's scale is -1 / B.
  *   mtl_cross_entropy_bwd   dlogits (+)= gradient of that loss for an upper gradient of 1: the nine
  *                           backward calls in reverse, MAX.backward's even split among ties included.
+ *   mtl_cross_entropy_fwd_grad  both in one launch: the same loss and, overwritten, the same dlogits --
+ *                           for a training step, where the backward pass follows the forward with the
+ *                           logits and targets unchanged (Model.forward then Model.backward,
+ *                           nn/model.mojo:113-330).
  * The intermediate tensors of the nine nodes are not produced.  At most MTL_CROSS_ENTROPY_MAX_ELEMENTS
  * logits per call (the forward is a single block); larger losses go through the operator calls. */
 #define MTL_CROSS_ENTROPY_MAX_ELEMENTS (1ll << 22)
@@ -411,6 +415,8 @@ MTL_API int32_t mtl_cross_entropy_fwd(mtl_ctx* ctx, float* loss, const float* lo
                                       int64_t B, int64_t C, float scale);
 MTL_API int32_t mtl_cross_entropy_bwd(mtl_ctx* ctx, float* dlogits, const float* logits, const float* y_true,
                                       int64_t B, int64_t C, float scale, int32_t accumulate);
+MTL_API int32_t mtl_cross_entropy_fwd_grad(mtl_ctx* ctx, float* loss, float* dlogits, const float* logits,
+                                           const float* y_true, int64_t B, int64_t C, float scale);
 
 /* ---------------------------------------------------------------- optimizer ------------- */
 

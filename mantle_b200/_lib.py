@@ -143,6 +143,7 @@ SIGNATURES = {
     "mtl_reduce_all_static": (_i32, [_vp, _i32, _vp, _vp, _i64]),
     "mtl_cross_entropy_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32]),
     "mtl_cross_entropy_bwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _i32]),
+    "mtl_cross_entropy_fwd_grad": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32]),
     "mtl_adam_step": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _i32, _f32]),
     "mtl_adam_step_dev": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _vp, _f32]),
     "mtl_graph_begin": (_i32, [_vp]),

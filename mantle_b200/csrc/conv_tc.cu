@@ -657,6 +657,29 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                 const int th = mt % p.tiles_h;
                 const int tnb = mt / p.tiles_h;
                 const int ow0 = tw * p.bw, oh0 = th * p.bh, n0 = tnb * p.bn;
+                if (it.slot < 0) {
+                    // a whole tile: plain nested loops (measured: walking them through one flat k-block counter,
+                    // as the split items below do, made this kernel 6 - 12 % slower -- the producer's issue rate
+                    // is on the critical path)
+                    for (int seg = 0; seg < p.nseg && ok; ++seg) {
+                        const CUtensorMap* mx = p.segA[seg] ? &mapX1 : &mapX0;
+                        const CUtensorMap* mw = p.segB[seg] ? &mapW1 : &mapW0;
+                        for (int r = 0; r < p.R && ok; ++r)
+                            for (int si = 0; si < p.s_count && ok; ++si)
+                                for (int cb = 0; cb < cblocks; ++cb) {
+                                    if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, kWaitBudgetNs)) ok = false;
+                                    if (__any_sync(0x3u, !ok)) { ok = false; break; }
+                                    uint8_t* sa = tiles + stage * kTStageBytes;
+                                    uint8_t* sb = sa + kTABytes;
+                                    if (lane == 0) mbar_arrive_expect_tx(&full[stage], tx);
+                                    __syncwarp(0x3u);
+                                    if (lane == 0) tma_load_3d(sa, mw, &full[stage], cb * BK, kt * BM, r * p.s_count + si);
+                                    else tma_load_4d(sb, mx, &full[stage], cb * BK, ow0 + si * p.s_step - p.pw, oh0 + r - p.ph, n0);
+                                    if (++stage == kTStages) { stage = 0; phase ^= 1u; }
+                                }
+                    }
+                    continue;
+                }
                 // k-block kb = ((seg * R + r) * s_count + si) * cblocks + cb
                 int seg = it.kb0 / kb_per_seg;
                 int rest = it.kb0 - seg * kb_per_seg;
@@ -1471,12 +1494,80 @@ k_conv_wgrad_tc(const __grid_constant__ CUtensorMap mapU0, const __grid_constant
 }
 
 // dW[k][c][r][s] (+)= sum over splits of partial[split][rs][k][c]
+// Column sums of a [rows, cols] matrix of per-block channel sums (the bias gradient), run by the extra blocks
+// of the fold launch below: a block owns eight columns, its 32 row lanes walk the rows 32 apart with four
+// loads in flight and meet in shared memory, lane 0 first -- a fixed order whatever the grid.
+struct BiasFold {
+    float* db = nullptr;          // null: no bias gradient in this launch
+    const float* part = nullptr;
+    int64_t rows = 0;
+    int cols = 0;
+    int accumulate = 0;
+};
+__device__ void bias_fold_block(const BiasFold& b, int blk) {
+    __shared__ float part[32][9];
+    const int cl = threadIdx.x & 7, rl = threadIdx.x >> 3;
+    const int c = blk * 8 + cl;
+    float s = 0.0f;
+    if (c < b.cols) {
+        int64_t r = rl;
+        for (; r + 96 < b.rows; r += 128) {
+            const float a0 = b.part[r * b.cols + c], a1 = b.part[(r + 32) * b.cols + c];
+            const float a2 = b.part[(r + 64) * b.cols + c], a3 = b.part[(r + 96) * b.cols + c];
+            s += a0; s += a1; s += a2; s += a3;
+        }
+        for (; r < b.rows; r += 32) s += b.part[r * b.cols + c];
+    }
+    part[rl][cl] = s;
+    __syncthreads();
+    if (rl == 0 && c < b.cols) {
+        float t = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) t += part[j][cl];
+        b.db[c] = b.accumulate ? b.db[c] + t : t;
+    }
+}
+
 __global__ void __launch_bounds__(256) k_wgrad_fold(float* __restrict__ dW, const float* __restrict__ partial, int K,
-                                                    int C, int RS, int nsplit, int accumulate) {
+                                                    int C, int RS, int nsplit, int accumulate, int fold_blocks, BiasFold bias) {
     mtl_pdl_sync();
-    int64_t total = (int64_t)K * C * RS;
+    if ((int)blockIdx.x >= fold_blocks) {
+        bias_fold_block(bias, (int)blockIdx.x - fold_blocks);
+        return;
+    }
+    const int64_t total = (int64_t)K * C * RS;
+    if ((C & 3) == 0) {
+        // four channels per thread: 16-byte loads of the partials, eight slices in flight, slices added in
+        // ascending order
+        const int64_t total4 = total >> 2;
+        const float4* p4 = reinterpret_cast<const float4*>(partial);
+        for (int64_t i4 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i4 < total4; i4 += (int64_t)fold_blocks * blockDim.x) {
+            const int64_t i = i4 << 2;             // scratch layout [rs][k][c]
+            const int c = (int)(i % C);
+            const int64_t q = i / C;
+            const int k = (int)(q % K);
+            const int rs = (int)(q / K);
+            float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            int j = 0;
+            for (; j + 8 <= nsplit; j += 8) {
+                float4 t[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) t[u] = p4[(int64_t)(j + u) * total4 + i4];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { s.x += t[u].x; s.y += t[u].y; s.z += t[u].z; s.w += t[u].w; }
+            }
+            for (; j < nsplit; ++j) {
+                const float4 t = p4[(int64_t)j * total4 + i4];
+                s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+            }
+            float* o = dW + ((int64_t)k * C + c) * RS + rs;
+            if (accumulate) { o[0] += s.x; o[RS] += s.y; o[2 * RS] += s.z; o[3 * RS] += s.w; }
+            else { o[0] = s.x; o[RS] = s.y; o[2 * RS] = s.z; o[3 * RS] = s.w; }
+        }
+        return;
+    }
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    int64_t stride = (int64_t)fold_blocks * blockDim.x;
     for (int64_t i = tid; i < total; i += stride) {
         // i enumerates the scratch layout [rs][k][c] so that reads are coalesced
         int c = (int)(i % C);
@@ -1646,7 +1737,7 @@ int32_t wgrad_plan(mtl_ctx* ctx, const ConvGeom& g, int x3, WgradParams* pp, siz
 
 // The launch itself: channels-last copies (hi [, lo]) of ug and X are in place.
 int32_t wgrad_core(mtl_ctx* ctx, float* dW, const float* u_hi, const float* u_lo, const float* x_hi, const float* x_lo,
-                   float* partial, WgradParams p, const ConvGeom& g, int accumulate, int x3) {
+                   float* partial, WgradParams p, const ConvGeom& g, int accumulate, int x3, BiasFold bias = BiasFold()) {
     const int RS = g.R * g.S;
     int32_t rc = MTL_OK;
     p.partial = partial;
@@ -1674,8 +1765,10 @@ int32_t wgrad_core(mtl_ctx* ctx, float* dW, const float* u_hi, const float* u_lo
         mtl_launch_pdl(ctx, k_conv_wgrad_tc, dim3(grid), dim3(kThreads), (size_t)(smem_bytes), maps[0], maps[1], maps[2], maps[3], p);
     }
     MTL_LAUNCHED(ctx);
-    int fgrid = mtl_grid_for((int64_t)g.K * g.C * RS, 256, ctx->sm_count, 8);
-    mtl_launch_pdl(ctx, k_wgrad_fold, dim3(fgrid), dim3(256), (size_t)(0), dW, p.partial, g.K, g.C, RS, p.nsplit, accumulate);
+    int fgrid = mtl_grid_for((int64_t)g.K * g.C * RS / ((g.C & 3) == 0 ? 4 : 1), 256, ctx->sm_count, 8);
+    const int bias_blocks = bias.db ? (bias.cols + 7) / 8 : 0;
+    mtl_launch_pdl(ctx, k_wgrad_fold, dim3(fgrid + bias_blocks), dim3(256), (size_t)(0), dW, p.partial, g.K, g.C, RS, p.nsplit, accumulate,
+                   fgrid, bias);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
@@ -1767,7 +1860,13 @@ int32_t mtl_conv_bwd_fused_tc_src(mtl_ctx* ctx, float* dX, float* dW, float* db,
         rc = stage_nhwc(ctx, u_hi, u_lo, ug, g.N, g.K, g.OH * g.OW, x3, db ? bias_part : nullptr);
         if (rc) return rc;
     }
-    if (db) {
+    BiasFold bias_fold;
+    if (db && (int64_t)g.N * ptiles <= 4096) {
+        // few rows of per-block sums (the pooled path has one per image): summed by extra blocks of the
+        // kernel-gradient fold launch instead of by launches of their own
+        bias_fold.db = db; bias_fold.part = bias_part; bias_fold.rows = (int64_t)g.N * ptiles; bias_fold.cols = g.K;
+        bias_fold.accumulate = acc_db;
+    } else if (db) {
         // two levels: 256 slices of the per-block sums, then the slices
         const int64_t rows = (int64_t)g.N * ptiles;
         const int slices = rows < 256 ? (int)rows : 256;
@@ -1784,7 +1883,7 @@ int32_t mtl_conv_bwd_fused_tc_src(mtl_ctx* ctx, float* dX, float* dW, float* db,
         rc = stage_nhwc(ctx, x_hi, x_lo, X, g.N, g.C, g.H * g.W, x3, nullptr);
         if (rc) return rc;
     }
-    rc = wgrad_core(ctx, dW, u_hi, u_lo, x_ready ? X_cl : x_hi, x_lo, partial, p, g, acc_dw, x3);
+    rc = wgrad_core(ctx, dW, u_hi, u_lo, x_ready ? X_cl : x_hi, x_lo, partial, p, g, acc_dw, x3, bias_fold);
     if (rc) return rc;
     if (ctx->grads_ready_hook) ctx->grads_ready_hook(ctx->grads_ready_user);   // dW and db are enqueued, dX is not
     // input gradient: the same copy of ug is the activation operand; its weights go where X was

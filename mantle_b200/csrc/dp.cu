@@ -339,13 +339,13 @@ int32_t mtl_dp_init(mtl_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world
     ncclUniqueId uid;
     memcpy(&uid, id, MTL_DP_ID_BYTES);
     // The tensor-core kernels are persistent: one CTA per SM that needs the SM's whole shared memory, tiles
-    // dealt out in advance.  A collective kernel that holds a few SMs when such a kernel starts makes the
-    // CTAs meant for those SMs start late, and the whole kernel ends late by as much (measured: +0.08 to
-    // +0.10 ms per step at 2, 4 and 8 GPUs, far more than the exchange itself).  So the collective is
-    // limited to a few CTAs and the compute kernels leave that many SMs free (below).
-    // Measured at 2 GPUs, global batch 2048 / 512: 0.774 / 0.302 ms per step with nothing reserved, 0.739 /
-    // 0.294 ms with 8 SMs reserved and at most 8 (or 4) collective CTAs, 0.755 ms with 16 reserved.
-    int reserve = 8;
+    // dealt out in advance, so a collective kernel can only run beside them on SMs they leave free.
+    // MANTLE_DP_RESERVE_SMS = n makes every persistent grid n CTAs smaller and limits the collective to n
+    // CTAs.  Measured with the kernels as they are now, global batch 2048 (ms per step, 0 / 8 reserved):
+    // 2 GPUs 0.721 / 0.756, 4 GPUs 0.431 / 0.454, 4 GPUs at 256 images each 0.284 / 0.304 (and 0.325 with 4).
+    // Leaving nothing free wins: the exchange of a bucket then runs in the gaps between the persistent
+    // kernels and beside the lighter ones, and the compute kernels keep all SMs.
+    int reserve = 0;
     if (const char* e = getenv("MANTLE_DP_RESERVE_SMS")) reserve = atoi(e);
     if (reserve < 0) reserve = 0;
     if (reserve > 0 && world > 1) {

@@ -21,63 +21,99 @@
 
 namespace {
 
-constexpr int kKC = 512;          // largest k extent of one forward block (rows of B staged in shared memory)
+constexpr int kKC = 256;          // largest k extent of one forward block (rows of B staged in shared memory)
 constexpr int kTicketsFwd = 4096; // ticket slots [0, 4096) forward row groups, [4096, 8192) dB column groups
 
 // ------------------------------------------------------------------ forward --------------------
+// A block of eight warps owns 32 rows of A (four per warp) and one k slice of at most 256.  Every thread
+// first asks for ALL its operands -- eight 16-byte loads of A and its share of the block's rows of B (kn * N
+// contiguous floats, fetched as 16-byte pieces) -- so a block pays the memory latency once; two blocks share
+// an SM.  Lane l of a warp holds k = 4 * (32 u + l) + e (u < 2, e < 4) of its four rows; the rows of B sit in
+// shared memory in the order (e, 32 u + l), padded to an odd number of 16-byte units, so that the lanes of a
+// warp read different banks.
 template <int NQ>
-__global__ void __launch_bounds__(256, 3) k_linear_fwd(float* __restrict__ C, float* __restrict__ partial,
+__global__ void __launch_bounds__(256, 2) k_linear_fwd(float* __restrict__ C, float* __restrict__ partial,
                                                        int32_t* __restrict__ tickets, const float* __restrict__ A,
                                                        const float* __restrict__ B, const float* __restrict__ bias,
                                                        int M, int N, int K, int kc, int accumulate) {
     constexpr int NP = 4 * NQ;
-    __shared__ __align__(16) float b_s[kKC * 20];
+    constexpr int RU = NQ | 1;
+    constexpr int kPieces = (kKC * NP / 4 + 255) / 256;
+    constexpr int kRed = (8 * 32 * (NP + 1) + 3) / 4;              // float4 units the row reduction below needs
+    __shared__ float4 b_s[kKC * RU > kRed ? kKC * RU : kRed];
     __shared__ int s_last;
     mtl_pdl_sync();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_begin = blockIdx.y * kc;
-    const int kn = min(kc, K - k_begin);
-    for (int i = threadIdx.x; i < kn * 16; i += 256) {
-        const int kk = i >> 4, j = i & 15;
-        b_s[kk * 20 + j] = j < N ? __ldg(B + (int64_t)(k_begin + kk) * N + j) : 0.0f;
+    const int kn = min(kc, K - k_begin);          // a multiple of four (K and kc are)
+    const int m0 = (blockIdx.x * 8 + warp) * 4;   // rows past M load zeros and store nothing
+    float4 a[2][4];
+    const float* a0 = A + (int64_t)m0 * K + k_begin;
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int kk = (u * 32 + lane) * 4;
+            a[u][r] = (kk < kn && m0 + r < M) ? __ldg(reinterpret_cast<const float4*>(a0 + (int64_t)r * K + kk))
+                                              : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+    const int total = kn * N;                     // a multiple of four
+    const float4* bsrc = reinterpret_cast<const float4*>(B + (int64_t)k_begin * N);
+    float4 piece[kPieces];
+#pragma unroll
+    for (int t = 0; t < kPieces; ++t) {
+        const int f = t * 256 + (int)threadIdx.x;
+        piece[t] = f * 4 < total ? __ldg(bsrc + f) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    float* b_f = reinterpret_cast<float*>(b_s);
+    if (N < NP) {                                  // the columns past N must read as zeros
+        for (int i = threadIdx.x; i < kKC * RU; i += 256) b_s[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int t = 0; t < kPieces; ++t) {
+        const int f = t * 256 + (int)threadIdx.x;
+        if (f * 4 < total) {
+            const float pv[4] = {piece[t].x, piece[t].y, piece[t].z, piece[t].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int idx = f * 4 + e;
+                const int kk = idx / N, j = idx - kk * N;
+                b_f[((kk & 3) * (kKC / 4) + (kk >> 2)) * (RU * 4) + j] = pv[e];
+            }
+        }
     }
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = (blockIdx.x * 8 + warp) * 4;   // rows past M load zeros and store nothing
     float acc[4][NP];
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
         for (int j = 0; j < NP; ++j) acc[r][j] = 0.0f;
-    const float* a0 = A + (int64_t)m0 * K + k_begin;
-    // four k steps at a time: their sixteen loads of A are in flight together
-    for (int kk0 = lane; kk0 < kn; kk0 += 128) {
-        float a[4][4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+    for (int u = 0; u < 2; ++u) {
+        const int g4 = u * 32 + lane;
+        if (g4 * 4 < kn) {
 #pragma unroll
-            for (int r = 0; r < 4; ++r)
-                a[u][r] = (kk0 + 32 * u < kn && m0 + r < M) ? __ldg(a0 + (int64_t)r * K + kk0 + 32 * u) : 0.0f;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int kk = kk0 + 32 * u;
-            if (kk < kn) {
+            for (int e = 0; e < 4; ++e) {
                 float b[NP];
 #pragma unroll
                 for (int q = 0; q < NQ; ++q) {
-                    const float4 t = *reinterpret_cast<const float4*>(b_s + kk * 20 + q * 4);
+                    const float4 t = b_s[(e * (kKC / 4) + g4) * RU + q];
                     b[q * 4] = t.x; b[q * 4 + 1] = t.y; b[q * 4 + 2] = t.z; b[q * 4 + 3] = t.w;
                 }
 #pragma unroll
-                for (int r = 0; r < 4; ++r)
+                for (int r = 0; r < 4; ++r) {
+                    const float av = e == 0 ? a[u][r].x : e == 1 ? a[u][r].y : e == 2 ? a[u][r].z : a[u][r].w;
 #pragma unroll
-                    for (int j = 0; j < NP; ++j) acc[r][j] = fmaf(a[u][r], b[j], acc[r][j]);
+                    for (int j = 0; j < NP; ++j) acc[r][j] = fmaf(av, b[j], acc[r][j]);
+                }
             }
         }
     }
     // the 32 lanes' partial sums of a row meet in shared memory; lane j adds column j over the lanes
     float* out = partial + (int64_t)blockIdx.y * M * N;
     __syncthreads();                              // every warp is done with the rows of B: their memory is reused
-    float* rs = b_s + warp * 32 * (NP + 1);
+    float* rs = b_f + warp * 32 * (NP + 1);
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
         __syncwarp();
@@ -126,9 +162,8 @@ struct LinBwd {
 
 // dA[m, k] (+)= sum_j ug[m, j] * B[k, j].  A block owns da_rows rows of ug and 1024 values of k.  Its
 // slice of B (1024 x N floats, contiguous) is read once with coalesced loads into shared memory, row
-// stride N | 1 floats (odd: lanes that read consecutive rows hit different banks); thread t then keeps
-// rows k0 + t, + 256, + 512, + 768 in registers and walks the rows of ug, so that a warp's stores are
-// 32 consecutive floats of one row of dA.
+// stride N | 1 floats; thread t then keeps rows k0 + 4 t .. 4 t + 3 in registers and walks the rows of ug,
+// storing four consecutive values of a row of dA at a time (a warp's store covers 512 contiguous bytes).
 constexpr int kDaKT = 1024;
 template <int NP>
 __device__ __forceinline__ void role_da(const LinBwd& p, int b, float* smem) {
@@ -139,10 +174,31 @@ __device__ __forceinline__ void role_da(const LinBwd& p, int b, float* smem) {
     const int ws = p.N | 1;
     float* w_s = smem;                                    // [1024][N | 1]
     float* ug_s = smem + kDaKT * ws;                      // [da_rows][16]
-    const float* wsrc = p.B + (int64_t)k_base * p.N;
-    for (int i = threadIdx.x; i < kn * p.N; i += 256) {
-        const int kk = i / p.N, j = i - kk * p.N;
-        w_s[kk * ws + j] = __ldg(wsrc + i);
+    // the slice is kn * N contiguous floats (a multiple of four, 16-byte aligned): every thread's 16-byte
+    // pieces are in flight together
+    {
+        const float4* wsrc = reinterpret_cast<const float4*>(p.B + (int64_t)k_base * p.N);
+        const int total = kn * p.N;
+        constexpr int kPieces = (kDaKT * NP / 4 + 255) / 256;
+        float4 piece[kPieces];
+#pragma unroll
+        for (int t = 0; t < kPieces; ++t) {
+            const int f = t * 256 + (int)threadIdx.x;
+            piece[t] = f * 4 < total ? __ldg(wsrc + f) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int t = 0; t < kPieces; ++t) {
+            const int f = t * 256 + (int)threadIdx.x;
+            if (f * 4 < total) {
+                const float pv[4] = {piece[t].x, piece[t].y, piece[t].z, piece[t].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int idx = f * 4 + e;
+                    const int kk = idx / p.N, j = idx - kk * p.N;
+                    w_s[kk * ws + j] = pv[e];
+                }
+            }
+        }
     }
     for (int i = threadIdx.x; i < p.da_rows * 16; i += 256) {
         const int r = i >> 4, j = i & 15;
@@ -152,7 +208,7 @@ __device__ __forceinline__ void role_da(const LinBwd& p, int b, float* smem) {
     float w[4][NP];
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-        const int kl = threadIdx.x + 256 * kk;
+        const int kl = threadIdx.x * 4 + kk;
 #pragma unroll
         for (int j = 0; j < NP; ++j) w[kk][j] = (kl < kn && j < p.N) ? w_s[kl * ws + j] : 0.0f;
     }
@@ -166,10 +222,15 @@ __device__ __forceinline__ void role_da(const LinBwd& p, int b, float* smem) {
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) o[kk] = fmaf(u, w[kk][j], o[kk]);
         }
-        float* dst = p.dA + (int64_t)(m0 + r) * p.K + k_base + threadIdx.x;
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-            if (threadIdx.x + 256 * kk < kn) dst[256 * kk] = p.acc_da ? dst[256 * kk] + o[kk] : o[kk];
+        if ((int)threadIdx.x * 4 < kn) {                  // kn is a multiple of four
+            float4* dst = reinterpret_cast<float4*>(p.dA + (int64_t)(m0 + r) * p.K + k_base + threadIdx.x * 4);
+            float4 v = make_float4(o[0], o[1], o[2], o[3]);
+            if (p.acc_da) {
+                const float4 old = *dst;
+                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+            }
+            *dst = v;
+        }
     }
 }
 
@@ -194,12 +255,12 @@ __device__ __forceinline__ void role_db(const LinBwd& p, int b, float* smem, int
         __syncthreads();
         if (k < p.K) {
             const int mn = min(64, m_end - mb);
-            for (int r0 = 0; r0 < mn; r0 += 8) {          // eight loads of A in flight
-                float a[8];
+            for (int r0 = 0; r0 < mn; r0 += 32) {         // 32 loads of A in flight: two memory round trips per 64 rows
+                float a[32];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) a[u] = r0 + u < mn ? __ldg(p.A + (int64_t)(mb + r0 + u) * p.K + k) : 0.0f;
+                for (int u = 0; u < 32; ++u) a[u] = r0 + u < mn ? __ldg(p.A + (int64_t)(mb + r0 + u) * p.K + k) : 0.0f;
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < 32; ++u) {
 #pragma unroll
                     for (int q = 0; q < NP / 4; ++q) {
                         const float4 t = *reinterpret_cast<const float4*>(ug_s + (r0 + u) * 16 + 4 * q);
@@ -276,17 +337,17 @@ int32_t mtl_linear_fwd(mtl_ctx* ctx, float* C, const float* A, const float* B, c
     MTL_CHECK_CTX(ctx);
     MTL_REQUIRE(ctx, C && A && B, "null pointer in mtl_linear_fwd");
     MTL_REQUIRE(ctx, M >= 1 && K >= 1 && N >= 1, "Linear extents must be positive");
-    if (!linear_supported(ctx, M, K, N)) {
+    if (!linear_supported(ctx, M, K, N) || K % 4 != 0 || ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15u)) {   // 16-byte loads
         // the reference's two operator calls, one after the other
         int32_t rc = mtl_dot_fwd(ctx, C, A, B, M, K, N);
         if (rc || !bias) return rc;
         const int64_t cs[2] = {M, N}, bs[1] = {N};
         return mtl_binary_fwd(ctx, MTL_OP_ADD, C, C, bias, 2, cs, 1, bs);
     }
-    // k extent per block: enough blocks to fill the machine about four times over
+    // k extent per block: enough blocks (two fit an SM) to fill the machine
     const int rb = (int)((M + 31) / 32);
     int kc = kKC;
-    while (kc > 128 && (int64_t)rb * ((K + kc - 1) / kc) < 4ll * ctx->sm_count) kc >>= 1;
+    while (kc > 128 && (int64_t)rb * ((K + kc - 1) / kc) < 2ll * ctx->sm_count) kc >>= 1;
     const int nsplit = (int)((K + kc - 1) / kc);
     void* ws;
     int32_t rc = mtl_workspace(ctx, (size_t)nsplit * M * N * 4, &ws);
@@ -311,7 +372,9 @@ int32_t mtl_linear_bwd(mtl_ctx* ctx, float* dA, float* dB, float* dbias, const f
     MTL_REQUIRE(ctx, M >= 1 && K >= 1 && N >= 1, "Linear extents must be positive");
     MTL_REQUIRE(ctx, (!dA || B) && (!dB || A), "mtl_linear_bwd: dA needs B and dB needs A");
     if (!dA && !dB && !dbias) return MTL_OK;
-    if (!linear_supported(ctx, M, K, N)) {
+    const bool vec_ok = K % 4 == 0 && ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(dA) |
+                                        reinterpret_cast<uintptr_t>(B)) & 15u) == 0;   // 16-byte accesses
+    if (!linear_supported(ctx, M, K, N) || !vec_ok) {
         int32_t rc = MTL_OK;
         const int64_t cs[2] = {M, N}, bs[1] = {N};
         if (dbias) rc = mtl_binary_bwd(ctx, MTL_OP_ADD, 1, dbias, ug, ug, dbias, 2, cs, 1, bs, acc_dbias);
@@ -344,7 +407,8 @@ int32_t mtl_linear_bwd(mtl_ctx* ctx, float* dA, float* dB, float* dbias, const f
         p.partial = (float*)ws;
     }
     const int blocks = p.n_db_blocks + p.n_da_blocks + (dbias ? 1 : 0);
-    const size_t smem_bytes = dA ? (size_t)(kDaKT * ((int)N | 1) + 32 * 16) * 4 : (size_t)64 * 16 * 4;
+    size_t smem_bytes = (size_t)64 * 16 * 4;
+    if (dA && (size_t)(kDaKT * ((int)N | 1) + 32 * 16) * 4 > smem_bytes) smem_bytes = (size_t)(kDaKT * ((int)N | 1) + 32 * 16) * 4;
 #define MTL_LIN_BWD(NP_)                                                                                              \
     do {                                                                                                              \
         MTL_CUDA(ctx, cudaFuncSetAttribute(k_linear_bwd<NP_>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \

@@ -405,8 +405,16 @@ void Model::execute(int num_nodes) {
         NodeRange range(ctx_, profiling_, i);
         if (fusion_ && i == ce_head_) {
             const Symbol& x = g_.nodes[i].inputs[0];
-            check(mtl_cross_entropy_fwd(ctx_, T(*g_.loss_out), T(x), T(g_.nodes[i + 6].inputs[0]), x.shape[0], x.shape[1],
-                                        scalar_values_.at(ce_scale_sym_)), "CrossEntropyLoss forward");
+            // When the logits' gradient has no other contributor, the forward launch writes it as well and
+            // the backward pass finds it there (the seed is 1 and neither logits nor targets change in between).
+            if (overwrite_first_ && ce_sole_reader_) {
+                check(mtl_cross_entropy_fwd_grad(ctx_, T(*g_.loss_out), G(x), T(x), T(g_.nodes[i + 6].inputs[0]), x.shape[0],
+                                                 x.shape[1], scalar_values_.at(ce_scale_sym_)), "CrossEntropyLoss forward");
+                ce_grad_fresh_ = true;
+            } else {
+                check(mtl_cross_entropy_fwd(ctx_, T(*g_.loss_out), T(x), T(g_.nodes[i + 6].inputs[0]), x.shape[0], x.shape[1],
+                                            scalar_values_.at(ce_scale_sym_)), "CrossEntropyLoss forward");
+            }
             continue;
         }
         forward_op(g_.nodes[i]);
@@ -509,6 +517,8 @@ void Model::set_fusion(bool on) {
     lin_add_of_.assign(nn, -1);
     lin_dot_of_.assign(nn, -1);
     ce_head_ = -1;
+    ce_sole_reader_ = false;
+    ce_grad_fresh_ = false;
     if (!on) return;
     std::map<int, int> uses, producer;
     for (int i = 0; i < nn; ++i) {
@@ -631,6 +641,7 @@ void Model::set_fusion(bool on) {
         if (!m) continue;
         ce_head_ = i;
         ce_scale_sym_ = lit.id;
+        ce_sole_reader_ = uses[x.id] == 2;   // MAX and the first SUB of this chain
         for (int k = 1; k < 9; ++k) { fwd_skip_[i + k] = 1; bwd_skip_[i + k] = 1; }
         break;
     }
@@ -907,8 +918,13 @@ void Model::backward_enqueue() {
         } else if (fusion_ && i == ce_head_) {
             // the nine backward calls of the loss chain, gradient seed 1 included
             const Symbol& x = n.inputs[0];
-            check(mtl_cross_entropy_bwd(ctx_, G(x), T(x), T(g_.nodes[i + 6].inputs[0]), x.shape[0], x.shape[1],
-                                        scalar_values_.at(ce_scale_sym_), acc_flag(x)), "CrossEntropyLoss backward");
+            const int acc = acc_flag(x);
+            if (ce_grad_fresh_ && !acc) {
+                ce_grad_fresh_ = false;   // written by the forward launch; a second backward pass recomputes it
+            } else {
+                check(mtl_cross_entropy_bwd(ctx_, G(x), T(x), T(g_.nodes[i + 6].inputs[0]), x.shape[0], x.shape[1],
+                                            scalar_values_.at(ce_scale_sym_), acc), "CrossEntropyLoss backward");
+            }
         } else if (fusion_ && n.op == MTL_OP_DOT && lin_add_of_[i] >= 0) {
             // DOT.backward for both operands and the bias ADD's backward, from the gradient of the ADD's result
             const Node& add = g_.nodes[lin_add_of_[i]];

@@ -143,6 +143,8 @@ class Model {
     bool profiling_ = false;
     int fwd_passes_ = 0, bwd_passes_ = 0;
     int ce_head_ = -1;                 // first of the nine nodes of a CrossEntropyLoss run as one call each way, or -1
+    bool ce_sole_reader_ = false;      // the loss chain is the only reader of its logits
+    bool ce_grad_fresh_ = false;       // the last forward pass left the logits' gradient in place
     int ce_scale_sym_ = -1;            // id of the [1]-shaped literal the loss is scaled by
     std::vector<int> fwd_relu_of_;     // per node: the RELU node a CONV2D also computes, or -1
     std::vector<int> fwd_pool_of_;     // per node: the MAXPOOL2D node a CONV2D+RELU also computes, or -1

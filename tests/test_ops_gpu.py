@@ -848,6 +848,12 @@ def test_cross_entropy_equals_nine_operator_calls(ctx, B, C):
         ctx._check(ctx.lib.mtl_cross_entropy_bwd(ctx.handle, got.ptr, x.ptr, y.ptr, B, C, float(scale), acc))
         want = g["x"].numpy() + (init if acc else 0)
         assert_close(got.numpy(), want, 1e-5, 1e-7 * float(np.abs(g["x"].numpy()).max()) + 1e-9, "dlogits acc %d" % acc)
+    # both in one launch: the same bits as the two calls
+    sep_loss, sep_grad = got_loss.numpy(), ctx.empty((B, C))
+    ctx._check(ctx.lib.mtl_cross_entropy_bwd(ctx.handle, sep_grad.ptr, x.ptr, y.ptr, B, C, float(scale), 0))
+    one_loss, one_grad = ctx.empty((1,)), ctx.array(rng.normal(0, 1, (B, C)).astype(np.float32))
+    ctx._check(ctx.lib.mtl_cross_entropy_fwd_grad(ctx.handle, one_loss.ptr, one_grad.ptr, x.ptr, y.ptr, B, C, float(scale)))
+    assert np.array_equal(one_loss.numpy(), sep_loss) and np.array_equal(one_grad.numpy(), sep_grad.numpy())
     assert ctx.device_status() == 0
 
 
@@ -889,7 +895,8 @@ def test_bounded_wait_runs_out_and_the_context_stays_usable(ctx):
     assert ctx.lib.mtl_selftest_bounded_wait(ctx.handle, 0, None) == 1     # MTL_ERR_INVALID
 
 
-@pytest.mark.parametrize("M,K,N", [(256, 6272, 10), (2048, 6272, 10), (64, 1568, 10), (37, 515, 3), (300, 130, 16), (8, 40, 1)])
+@pytest.mark.parametrize("M,K,N", [(256, 6272, 10), (2048, 6272, 10), (64, 1568, 10), (37, 515, 3), (300, 130, 16), (8, 40, 1),
+                                   (37, 516, 3), (300, 132, 16), (5, 2052, 7), (1000, 1024, 12), (19, 4, 5)])
 def test_linear_layer_as_one_call_each_way(ctx, M, K, N):
     """mtl_linear_fwd / mtl_linear_bwd against the reference's operator sequence on the oracle (DOT then ADD
     of the bias; DOT.backward for both operands, ADD.backward with un-broadcasting for the bias) and
