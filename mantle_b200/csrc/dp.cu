@@ -10,6 +10,11 @@
 // rank maps every other rank's exchange buffer (CUDA IPC) at start-up, and one kernel on the compute
 // stream pushes its values into the peers' buffers as 8-byte {value, step number} words and then
 // collects the peers' values from its own buffer, summing in rank order (every rank gets the same bits).
+// The same kernel can carry the other buckets (up to 2 MB, channel 1 of the buffers, on the communication
+// stream; MANTLE_DP_BUCKET_EXCHANGE=1).  It is light enough to run beside a persistent tensor-core CTA,
+// which the library collective's CTAs are not -- but measured it loses to the library at that size: 2 GPUs
+// 0.692 against 0.683 ms per step, 4 GPUs 0.431 against 0.407 ms (twice the bytes on the wire, and its
+// polling shares SMs with the compute kernels).  So it is an opt-in and only the last bucket goes direct.
 // An 8-byte store is indivisible, so a word whose step number matches carries its value: no flags, no
 // fences.  Two buffer halves used in turn keep a fast rank's next step off the words a slow rank still
 // reads (a rank cannot run two steps ahead: its next exchange needs the slow rank's push).  Every wait
@@ -152,19 +157,23 @@ struct DpState {
     int reserved_sms = 0;         // SMs the compute kernels leave to the collective (taken off ctx->sm_count)
     // direct exchange of the last bucket (see the top of this file)
     bool tail_on = false;
-    uint2* xbuf = nullptr;        // this rank's buffer: [2 halves][world][kTailCap] {value, step}
+    uint2* xbuf = nullptr;        // this rank's buffer: per channel [2 halves][world][capacity] {value, step}
     uint2* peer_xbuf[8] = {};     // every rank's buffer as mapped here ([rank] = xbuf)
-    uint32_t* tail_seq = nullptr; // device: number of exchanges done
+    uint32_t* ctl = nullptr;      // device, behind the words: per channel {exchanges done, ticket}
+    bool bucket_direct = false;   // MANTLE_DP_BUCKET_EXCHANGE=1: the other buckets (up to 2 MB) go direct as well, on the communication stream
 };
 
-constexpr int kTailCap = 16384;           // floats per exchange (64 KB of gradient)
+constexpr int kTailCap = 16384;           // channel 0 (compute stream): floats per exchange (64 KB of gradient)
+constexpr int kBucketCap = 1 << 19;       // channel 1 (communication stream): 2 MB of gradient
 constexpr int kTailMaxWorld = 8;
+inline size_t chan_words(int world, int chan) { return (size_t)2 * world * (chan ? kBucketCap : kTailCap); }
+inline size_t chan_offset(int world, int chan) { return chan ? chan_words(world, 0) : 0; }
 constexpr uint64_t kTailBudgetNs = 20ull * 1000 * 1000 * 1000;
 
 struct TailX {
     float* grad;
-    int n, rank, world;
-    uint2* slots[kTailMaxWorld];   // slots[r]: rank r's buffer
+    int n, rank, world, cap;       // cap: floats per (half, rank) slot of this channel
+    uint2* slots[kTailMaxWorld];   // slots[r]: rank r's buffer (this channel's part)
     uint32_t* seq;                 // exchanges done so far (this rank's counter)
     int32_t* ticket;               // zero between launches
     int32_t* status;
@@ -186,34 +195,41 @@ __device__ __forceinline__ uint2 ld_word(const uint2* p) {
 }
 
 // One rank's part of the exchange, run by `nblocks` blocks of 256 threads (block index `b` among them).
-// Thread i pushes element i to every peer, then collects element i of every peer: no thread waits for
-// another thread of its own rank.
+// A thread first pushes all its elements to every peer, then collects them from every peer: no thread waits
+// for another thread of its own rank.  The polling loop naps between looks, so that a block that shares
+// its SM with a tensor-core CTA takes few of its issue slots.
 __device__ void tail_exchange_rank(const TailX& p, int b, int nblocks, bool silent) {
     __shared__ int s_last;
     const uint32_t step = *reinterpret_cast<volatile uint32_t*>(p.seq) + 1u;
     const int half = (int)(step & 1u);
     bool timed_out = false;
-    for (int i = b * 256 + (int)threadIdx.x; i < p.n && !silent; i += nblocks * 256) {
-        const float g = p.grad[i];
-        for (int r = 0; r < p.world; ++r)
-            if (r != p.rank) st_word(p.slots[r] + ((size_t)(half * p.world + p.rank) * kTailCap + i), __float_as_uint(g), step);
-        float sum = 0.0f;
-        const uint64_t t0 = tail_timer_ns();
-        for (int r = 0; r < p.world && !timed_out; ++r) {
-            float v = g;
-            if (r != p.rank) {
-                const uint2* src = p.slots[p.rank] + ((size_t)(half * p.world + r) * kTailCap + i);
-                uint2 w = ld_word(src);
-                for (uint32_t spins = 0; w.y != step; ++spins) {
-                    if ((spins & 63u) == 63u && tail_timer_ns() - t0 > p.budget_ns) { timed_out = true; break; }
-                    w = ld_word(src);
-                }
-                v = __uint_as_float(w.x);
-            }
-            sum += v;
+    const int first = b * 256 + (int)threadIdx.x, stride = nblocks * 256;
+    if (!silent) {
+        for (int i = first; i < p.n; i += stride) {
+            const uint32_t g = __float_as_uint(p.grad[i]);
+            for (int r = 0; r < p.world; ++r)
+                if (r != p.rank) st_word(p.slots[r] + ((size_t)(half * p.world + p.rank) * p.cap + i), g, step);
         }
-        if (timed_out) break;
-        p.grad[i] = sum;
+        const uint64_t t0 = tail_timer_ns();
+        for (int i = first; i < p.n && !timed_out; i += stride) {
+            const float g = p.grad[i];
+            float sum = 0.0f;
+            for (int r = 0; r < p.world && !timed_out; ++r) {
+                float v = g;
+                if (r != p.rank) {
+                    const uint2* src = p.slots[p.rank] + ((size_t)(half * p.world + r) * p.cap + i);
+                    uint2 w = ld_word(src);
+                    for (uint32_t spins = 0; w.y != step; ++spins) {
+                        if ((spins & 15u) == 15u && tail_timer_ns() - t0 > p.budget_ns) { timed_out = true; break; }
+                        __nanosleep(64);
+                        w = ld_word(src);
+                    }
+                    v = __uint_as_float(w.x);
+                }
+                sum += v;
+            }
+            if (!timed_out) p.grad[i] = sum;
+        }
     }
     if (timed_out) atomicExch(p.status, MTL_ERR_TIMEOUT);
     // the block that finishes last counts the exchange (every block has read the counter by then)
@@ -255,18 +271,36 @@ void tail_release(DpState* st) {
     }
     if (st->xbuf) cudaFree(st->xbuf);
     st->xbuf = nullptr;
-    st->tail_seq = nullptr;
+    st->ctl = nullptr;
     st->tail_on = false;
 }
 
 }  // namespace
+
+// Launches the direct exchange of `n` floats on `stream` through channel `chan` of the buffers.
+static int32_t launch_direct(mtl_ctx* ctx, DpState* st, int chan, float* buf, int64_t n, cudaStream_t stream) {
+    TailX p;
+    p.grad = buf; p.n = (int)n; p.rank = st->rank; p.world = st->world;
+    p.cap = chan ? kBucketCap : kTailCap;
+    for (int r = 0; r < kTailMaxWorld; ++r) p.slots[r] = st->peer_xbuf[r] ? st->peer_xbuf[r] + chan_offset(st->world, chan) : nullptr;
+    p.seq = st->ctl + 2 * chan;
+    p.ticket = reinterpret_cast<int32_t*>(st->ctl + 2 * chan + 1);
+    p.status = ctx->dev_status;
+    p.budget_ns = kTailBudgetNs;
+    const int64_t want = (n + 255) / 256;
+    const int blocks = (int)(want < 64 ? want : 64);
+    if (stream == ctx->stream) mtl_launch_pdl(ctx, k_tail_exchange, dim3(blocks), dim3(256), (size_t)0, p);
+    else k_tail_exchange<<<blocks, 256, 0, stream>>>(p);
+    MTL_LAUNCHED(ctx);
+    return MTL_OK;
+}
 
 // Maps every rank's exchange buffer into this process.  Every rank runs the same collectives here, whether
 // or not it wants (or manages) the direct exchange, and the group uses it only if EVERY rank mapped every
 // buffer: a rank on its own would wait for pushes that never come.
 static int32_t tail_setup(mtl_ctx* ctx, DpState* st, bool want) {
     const int W = st->world;
-    const size_t words = (size_t)2 * W * kTailCap;
+    const size_t words = chan_words(W, 0) + chan_words(W, 1);
     int ok = want ? 1 : 0;
     cudaIpcMemHandle_t mine;
     memset(&mine, 0, sizeof(mine));
@@ -303,7 +337,7 @@ static int32_t tail_setup(mtl_ctx* ctx, DpState* st, bool want) {
     MTL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (flag == 1) {
         st->tail_on = true;
-        st->tail_seq = reinterpret_cast<uint32_t*>(st->xbuf + words);
+        st->ctl = reinterpret_cast<uint32_t*>(st->xbuf + words);
     } else {
         tail_release(st);
     }
@@ -375,6 +409,7 @@ int32_t mtl_dp_init(mtl_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world
     }
     int want_tail = 1;
     if (const char* e = getenv("MANTLE_DP_TAIL_EXCHANGE")) want_tail = atoi(e);
+    if (const char* e = getenv("MANTLE_DP_BUCKET_EXCHANGE")) st->bucket_direct = atoi(e) != 0;
     if (world > 1 && world <= kTailMaxWorld && g_nccl.AllGather) {
         int32_t rc = tail_setup(ctx, st, want_tail != 0);
         if (rc) return rc;
@@ -391,7 +426,12 @@ int32_t mtl_dp_allreduce_async(mtl_ctx* ctx, float* buf, int64_t n) {
     if (n == 0 || st->world == 1) return MTL_OK;
     MTL_CUDA(ctx, cudaEventRecord(st->ready, ctx->stream));
     MTL_CUDA(ctx, cudaStreamWaitEvent(st->comm_stream, st->ready, 0));
-    MTL_NCCL(ctx, g_nccl.AllReduce(buf, buf, (size_t)n, ncclFloat32, ncclSum, st->comm, st->comm_stream));
+    if (st->tail_on && st->bucket_direct && n <= kBucketCap)
+    {   // fits beside the tensor-core kernels; see the top of this file
+        int32_t rc = launch_direct(ctx, st, 1, buf, n, st->comm_stream);
+        if (rc) return rc;
+    } else
+        MTL_NCCL(ctx, g_nccl.AllReduce(buf, buf, (size_t)n, ncclFloat32, ncclSum, st->comm, st->comm_stream));
     st->pending = true;
     return MTL_OK;
 }
@@ -404,17 +444,7 @@ int32_t mtl_dp_allreduce_tail(mtl_ctx* ctx, float* buf, int64_t n) {
     if (!st->tail_on || n > kTailCap) return mtl_dp_allreduce_async(ctx, buf, n);
     if (st->failed) return mtl_set_error(ctx, MTL_ERR_COMM, "the communicator failed earlier and was aborted");
     if (n == 0) return MTL_OK;
-    TailX p;
-    p.grad = buf; p.n = (int)n; p.rank = st->rank; p.world = st->world;
-    for (int r = 0; r < kTailMaxWorld; ++r) p.slots[r] = st->peer_xbuf[r];
-    p.seq = st->tail_seq;
-    p.ticket = ctx->tickets + 8190;
-    p.status = ctx->dev_status;
-    p.budget_ns = kTailBudgetNs;
-    const int blocks = (int)((n + 255) / 256) < 32 ? (int)((n + 255) / 256) : 32;
-    mtl_launch_pdl(ctx, k_tail_exchange, dim3(blocks), dim3(256), (size_t)0, p);
-    MTL_LAUNCHED(ctx);
-    return MTL_OK;
+    return launch_direct(ctx, st, 0, buf, n, ctx->stream);
 }
 
 int32_t mtl_dp_tail_exchange_enabled(mtl_ctx* ctx) {
@@ -431,7 +461,7 @@ int32_t mtl_selftest_tail_exchange(mtl_ctx* ctx, float* grads, int32_t world, in
     int coop = 0;
     MTL_CUDA(ctx, cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, ctx->device));
     MTL_REQUIRE(ctx, coop, "the device cannot launch cooperatively");
-    const size_t words = (size_t)2 * world * kTailCap;
+    const size_t words = chan_words(world, 0);
     const size_t per_rank = words * sizeof(uint2) + 256;
     uint8_t* mem = nullptr;
     MTL_CUDA(ctx, cudaMalloc(&mem, per_rank * world));
@@ -441,7 +471,7 @@ int32_t mtl_selftest_tail_exchange(mtl_ctx* ctx, float* grads, int32_t world, in
     a.silent_rank = silent_rank;
     for (int r = 0; r < world; ++r) {
         TailX& p = a.r[r];
-        p.grad = grads + (size_t)r * n; p.n = n; p.rank = r; p.world = world;
+        p.grad = grads + (size_t)r * n; p.n = n; p.rank = r; p.world = world; p.cap = kTailCap;
         for (int q = 0; q < kTailMaxWorld; ++q) p.slots[q] = q < world ? reinterpret_cast<uint2*>(mem + per_rank * q) : nullptr;
         p.seq = reinterpret_cast<uint32_t*>(mem + per_rank * r + words * sizeof(uint2));
         p.ticket = reinterpret_cast<int32_t*>(p.seq) + 1;

@@ -139,6 +139,22 @@ def test_data_parallel_trajectory_equals_single_gpu(world):
         assert np.array_equal(r[5], want)
 
 
+def test_direct_exchange_of_every_bucket_opt_in(monkeypatch):
+    """MANTLE_DP_BUCKET_EXCHANGE=1: the buckets that overlap the backward pass travel through the library's own
+    exchange kernel as well (on the communication stream) instead of NCCL; same trajectory, identical replicas."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    single = _run(1)[0]
+    monkeypatch.setenv("MANTLE_DP_BUCKET_EXCHANGE", "1")
+    ranks = _run(2)
+    assert all(r[3] == 0 and r[4] == 1 for r in ranks)
+    got = np.mean([r[1] for r in ranks], axis=0)
+    assert np.allclose(got, np.asarray(single[1]), rtol=1e-3, atol=1e-6)
+    for a, b in zip(ranks[0][2], ranks[1][2]):
+        assert np.array_equal(a, b)
+
+
 def _visible_gpus():
     import ctypes as C
     try:
