@@ -1495,7 +1495,7 @@ k_conv_wgrad_tc(const __grid_constant__ CUtensorMap mapU0, const __grid_constant
 
 // dW[k][c][r][s] (+)= sum over splits of partial[split][rs][k][c]
 // Column sums of a [rows, cols] matrix of per-block channel sums (the bias gradient), run by the extra blocks
-// of the fold launch below: a block owns eight columns, its 32 row lanes walk the rows 32 apart with four
+// of the fold launch below: a block owns eight columns, its 32 row lanes walk the rows 32 apart with sixteen
 // loads in flight and meet in shared memory, lane 0 first -- a fixed order whatever the grid.
 struct BiasFold {
     float* db = nullptr;          // null: no bias gradient in this launch
@@ -1511,10 +1511,12 @@ __device__ void bias_fold_block(const BiasFold& b, int blk) {
     float s = 0.0f;
     if (c < b.cols) {
         int64_t r = rl;
-        for (; r + 96 < b.rows; r += 128) {
-            const float a0 = b.part[r * b.cols + c], a1 = b.part[(r + 32) * b.cols + c];
-            const float a2 = b.part[(r + 64) * b.cols + c], a3 = b.part[(r + 96) * b.cols + c];
-            s += a0; s += a1; s += a2; s += a3;
+        for (; r + 15 * 32 < b.rows; r += 16 * 32) {
+            float a[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) a[u] = b.part[(r + 32 * u) * b.cols + c];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) s += a[u];
         }
         for (; r < b.rows; r += 32) s += b.part[r * b.cols + c];
     }

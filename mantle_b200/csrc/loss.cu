@@ -42,13 +42,23 @@ __device__ __forceinline__ void cross_entropy_row_grad(float* __restrict__ gr, c
     }
 }
 
-// One block.  Thread t owns rows t, t + 1024, ...; the per-thread sums are combined by a tree.  With `dx` the
-// thread also writes the gradient of its rows (what k_cross_entropy_bwd computes), so that a training step
-// spends one launch on the loss instead of two.
+// Block 0: the loss.  Thread t owns rows t, t + 1024, ...; the per-thread sums are combined by a tree.  With
+// `dx` the launch has more blocks, and block b > 0 writes the gradient of rows (b - 1) * 1024 + t (what
+// k_cross_entropy_bwd computes), so that a training step spends one launch on the loss instead of two.
 __global__ void __launch_bounds__(kLossBlock) k_cross_entropy_fwd(float* __restrict__ loss, float* __restrict__ dx,
                                                                   const float* __restrict__ x,
                                                                   const float* __restrict__ y, int B, int C, float scale) {
     mtl_pdl_sync();
+    if (blockIdx.x > 0) {
+        const int b = ((int)blockIdx.x - 1) * kLossBlock + (int)threadIdx.x;
+        if (b < B) {
+            const float* xr = x + (int64_t)b * C;
+            float mx = -FLT_MAX;
+            for (int c = 0; c < C; ++c) mx = fmaxf(mx, xr[c]);
+            cross_entropy_row_grad(dx + (int64_t)b * C, xr, y + (int64_t)b * C, C, scale, mx, 0);
+        }
+        return;
+    }
     __shared__ float part[kLossBlock];
     float acc = 0.0f;
     for (int b = threadIdx.x; b < B; b += kLossBlock) {
@@ -60,7 +70,6 @@ __global__ void __launch_bounds__(kLossBlock) k_cross_entropy_fwd(float* __restr
         for (int c = 0; c < C; ++c) sm += expf(xr[c] - mx);
         const float lg = logf(sm);
         for (int c = 0; c < C; ++c) acc += yr[c] * ((xr[c] - mx) - lg);
-        if (dx) cross_entropy_row_grad(dx + (int64_t)b * C, xr, yr, C, scale, mx, 0);
     }
     part[threadIdx.x] = acc;
     __syncthreads();
@@ -109,7 +118,8 @@ int32_t mtl_cross_entropy_fwd_grad(mtl_ctx* ctx, float* loss, float* dlogits, co
     MTL_REQUIRE(ctx, B >= 1 && C >= 1 && B * C <= MTL_CROSS_ENTROPY_MAX_ELEMENTS,
                 "mtl_cross_entropy_fwd_grad handles up to %lld logits, got %lld x %lld",
                 (long long)MTL_CROSS_ENTROPY_MAX_ELEMENTS, (long long)B, (long long)C);
-    mtl_launch_pdl(ctx, k_cross_entropy_fwd, dim3(1), dim3(kLossBlock), (size_t)(0), loss, dlogits, logits, y_true, (int)B, (int)C, scale);
+    const int grad_blocks = (int)((B + kLossBlock - 1) / kLossBlock);
+    mtl_launch_pdl(ctx, k_cross_entropy_fwd, dim3(1 + grad_blocks), dim3(kLossBlock), (size_t)(0), loss, dlogits, logits, y_true, (int)B, (int)C, scale);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
