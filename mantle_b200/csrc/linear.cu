@@ -14,120 +14,158 @@
 // Sums over k (forward) and over the batch (dB) are split over many blocks so that the GPU is full at
 // any batch size; the slices are folded IN THE SAME LAUNCH, in ascending slice order, by whichever
 // block of a row group finishes last (a ticket counter per row group), so results do not depend on
-// the order in which blocks run.  Arithmetic is fp32 FMA on CUDA cores; the k sum is re-associated
-// with respect to the reference's ascending chain (compared at rtol = atol = 1e-5), so MTL_MATH_FP32,
-// which promises that chain bit for bit, takes the separate operator kernels instead.
+// the order in which blocks run.  The forward product runs on the tensor cores' warp-level instruction with
+// every operand split into two TF32 parts (three products, fp32 accumulation: within a few ulp of fp32), the
+// gradients as fp32 FMA on CUDA cores; sums are re-associated with respect to the reference's ascending chain
+// (compared at rtol = atol = 1e-5), so MTL_MATH_FP32, which promises that chain bit for bit, takes the
+// separate operator kernels instead.
 #include "common.cuh"
 
 namespace {
 
-constexpr int kKC = 256;          // largest k extent of one forward block (rows of B staged in shared memory)
 constexpr int kTicketsFwd = 4096; // ticket slots [0, 4096) forward row groups, [4096, 8192) dB column groups
 
 // ------------------------------------------------------------------ forward --------------------
-// A block of eight warps owns 32 rows of A (four per warp) and one k slice of at most 256.  Every thread
-// first asks for ALL its operands -- eight 16-byte loads of A and its share of the block's rows of B (kn * N
-// contiguous floats, fetched as 16-byte pieces) -- so a block pays the memory latency once; two blocks share
-// an SM.  Lane l of a warp holds k = 4 * (32 u + l) + e (u < 2, e < 4) of its four rows; the rows of B sit in
-// shared memory in the order (e, 32 u + l), padded to an odd number of 16-byte units, so that the lanes of a
-// warp read different banks.
-template <int NQ>
-__global__ void __launch_bounds__(256, 2) k_linear_fwd(float* __restrict__ C, float* __restrict__ partial,
-                                                       int32_t* __restrict__ tickets, const float* __restrict__ A,
-                                                       const float* __restrict__ B, const float* __restrict__ bias,
-                                                       int M, int N, int K, int kc, int accumulate) {
-    constexpr int NP = 4 * NQ;
-    constexpr int RU = NQ | 1;
-    constexpr int kPieces = (kKC * NP / 4 + 255) / 256;
-    constexpr int kRed = (8 * 32 * (NP + 1) + 3) / 4;              // float4 units the row reduction below needs
-    __shared__ float4 b_s[kKC * RU > kRed ? kKC * RU : kRed];
+// The sums over k are done by the tensor cores' warp-level instruction
+// (mma.sync m16n8k8, TF32 operands, fp32 accumulation), which needs no exchange between lanes: a warp owns 16
+// rows of A, a block of eight warps 128 rows and one k slice.  Each operand is split into a TF32 head and a
+// TF32 tail and three products are accumulated (head x head, head x tail, tail x head), which keeps the
+// result within a few ulp of the fp32 product; the kernel is bound by streaming A, not by arithmetic.
+// The reduction order inside a step is free, so the k positions of a fragment are chosen to make the loads
+// wide: lane (g, t) -- g = lane / 4, t = lane % 4 -- reads rows g and g + 8 at k0 + 4 t .. + 3 and at
+// k0 + 16 + 4 t .. + 3 (16-byte loads; eight lanes cover 128 contiguous bytes of a row), and the j-th of four
+// instructions takes element j of each piece; the matching rows of B are k0 + 4 t + j and k0 + 16 + 4 t + j.
+// B's rows sit in shared memory with a stride of 18 floats: the 32 lanes of a fragment read hit 32 banks.
+__device__ __forceinline__ uint32_t tf32_head(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32_16x8x8(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+constexpr int kMmaKC = 256;      // largest k slice of a block
+constexpr int kMmaBS = 18;       // floats between rows of B in shared memory
+
+template <int NT>   // n8 tiles: 1 for N <= 8, 2 for N <= 16
+__global__ void __launch_bounds__(256, 2) k_linear_fwd_mma(float* __restrict__ C, float* __restrict__ partial,
+                                                           int32_t* __restrict__ tickets, const float* __restrict__ A,
+                                                           const float* __restrict__ B, const float* __restrict__ bias,
+                                                           int M, int N, int K, int kc, int accumulate) {
+    __shared__ float b_s[kMmaKC * kMmaBS];
     __shared__ int s_last;
     mtl_pdl_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
     const int k_begin = blockIdx.y * kc;
     const int kn = min(kc, K - k_begin);          // a multiple of four (K and kc are)
-    const int m0 = (blockIdx.x * 8 + warp) * 4;   // rows past M load zeros and store nothing
-    float4 a[2][4];
-    const float* a0 = A + (int64_t)m0 * K + k_begin;
+    const int m0 = blockIdx.x * 128 + warp * 16;  // rows past M load zeros and store nothing
+    const float* row_lo = A + (int64_t)(m0 + g) * K + k_begin;
+    const float* row_hi = A + (int64_t)(m0 + g + 8) * K + k_begin;
+    const bool lo_ok = m0 + g < M, hi_ok = m0 + g + 8 < M;
+    // The operands of A travel in batches of two steps (64 values of k): two batches are in flight before
+    // anything else, and the batch after next is asked for before a batch is multiplied.
+    float4 pa[2][2][4];                           // [buffer][step][row g | row g+8 | row g (+16) | row g+8 (+16)]
+    auto fetch = [&](float4 (&dst)[2][4], int s0) {
 #pragma unroll
-    for (int u = 0; u < 2; ++u)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int kk = (u * 32 + lane) * 4;
-            a[u][r] = (kk < kn && m0 + r < M) ? __ldg(reinterpret_cast<const float4*>(a0 + (int64_t)r * K + kk))
-                                              : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int s = 0; s < 2; ++s) {
+            const int k0 = (s0 + s) * 32 + 4 * t;
+            const float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            dst[s][0] = (lo_ok && k0 < kn) ? __ldg(reinterpret_cast<const float4*>(row_lo + k0)) : z;
+            dst[s][1] = (hi_ok && k0 < kn) ? __ldg(reinterpret_cast<const float4*>(row_hi + k0)) : z;
+            dst[s][2] = (lo_ok && k0 + 16 < kn) ? __ldg(reinterpret_cast<const float4*>(row_lo + k0 + 16)) : z;
+            dst[s][3] = (hi_ok && k0 + 16 < kn) ? __ldg(reinterpret_cast<const float4*>(row_hi + k0 + 16)) : z;
         }
-    const int total = kn * N;                     // a multiple of four
-    const float4* bsrc = reinterpret_cast<const float4*>(B + (int64_t)k_begin * N);
-    float4 piece[kPieces];
-#pragma unroll
-    for (int t = 0; t < kPieces; ++t) {
-        const int f = t * 256 + (int)threadIdx.x;
-        piece[t] = f * 4 < total ? __ldg(bsrc + f) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    }
-    float* b_f = reinterpret_cast<float*>(b_s);
-    if (N < NP) {                                  // the columns past N must read as zeros
-        for (int i = threadIdx.x; i < kKC * RU; i += 256) b_s[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        __syncthreads();
-    }
-#pragma unroll
-    for (int t = 0; t < kPieces; ++t) {
-        const int f = t * 256 + (int)threadIdx.x;
-        if (f * 4 < total) {
-            const float pv[4] = {piece[t].x, piece[t].y, piece[t].z, piece[t].w};
+    };
+    fetch(pa[0], 0);
+    fetch(pa[1], 2);
+    // the slice's rows of B, zero beyond column N
+    for (int i = threadIdx.x; i < kMmaKC * kMmaBS; i += 256) b_s[i] = 0.0f;
+    __syncthreads();
+    {
+        const int total = kn * N;                 // a multiple of four
+        const float4* bsrc = reinterpret_cast<const float4*>(B + (int64_t)k_begin * N);
+        for (int f = threadIdx.x; f * 4 < total; f += 256) {
+            const float4 v = __ldg(bsrc + f);
+            const float pv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int idx = f * 4 + e;
                 const int kk = idx / N, j = idx - kk * N;
-                b_f[((kk & 3) * (kKC / 4) + (kk >> 2)) * (RU * 4) + j] = pv[e];
+                b_s[kk * kMmaBS + j] = pv[e];
             }
         }
     }
     __syncthreads();
-    float acc[4][NP];
+    float acc[NT][4];
 #pragma unroll
-    for (int r = 0; r < 4; ++r)
+    for (int n = 0; n < NT; ++n)
 #pragma unroll
-        for (int j = 0; j < NP; ++j) acc[r][j] = 0.0f;
+        for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+    const int steps = (kn + 31) / 32;
+    auto multiply = [&](const float4 (&src)[2][4], int s0) {
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-        const int g4 = u * 32 + lane;
-        if (g4 * 4 < kn) {
+        for (int s = 0; s < 2; ++s) {
+            if (s0 + s < steps) {
+                const int kb = (s0 + s) * 32 + 4 * t;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float b[NP];
+                for (int j = 0; j < 4; ++j) {
+                    const float av[4] = {j == 0 ? src[s][0].x : j == 1 ? src[s][0].y : j == 2 ? src[s][0].z : src[s][0].w,
+                                         j == 0 ? src[s][1].x : j == 1 ? src[s][1].y : j == 2 ? src[s][1].z : src[s][1].w,
+                                         j == 0 ? src[s][2].x : j == 1 ? src[s][2].y : j == 2 ? src[s][2].z : src[s][2].w,
+                                         j == 0 ? src[s][3].x : j == 1 ? src[s][3].y : j == 2 ? src[s][3].z : src[s][3].w};
+                    uint32_t ah[4], al[4];
 #pragma unroll
-                for (int q = 0; q < NQ; ++q) {
-                    const float4 t = b_s[(e * (kKC / 4) + g4) * RU + q];
-                    b[q * 4] = t.x; b[q * 4 + 1] = t.y; b[q * 4 + 2] = t.z; b[q * 4 + 3] = t.w;
-                }
+                    for (int i = 0; i < 4; ++i) {
+                        ah[i] = tf32_head(av[i]);
+                        al[i] = tf32_head(av[i] - __uint_as_float(ah[i]));
+                    }
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const float av = e == 0 ? a[u][r].x : e == 1 ? a[u][r].y : e == 2 ? a[u][r].z : a[u][r].w;
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) acc[r][j] = fmaf(av, b[j], acc[r][j]);
+                    for (int n = 0; n < NT; ++n) {
+                        const float b0 = b_s[(kb + j) * kMmaBS + n * 8 + g];
+                        const float b1 = b_s[(kb + 16 + j) * kMmaBS + n * 8 + g];
+                        const uint32_t b0h = tf32_head(b0), b1h = tf32_head(b1);
+                        const uint32_t b0l = tf32_head(b0 - __uint_as_float(b0h)), b1l = tf32_head(b1 - __uint_as_float(b1h));
+                        mma_tf32_16x8x8(acc[n], al, b0h, b1h);      // small terms first
+                        mma_tf32_16x8x8(acc[n], ah, b0l, b1l);
+                        mma_tf32_16x8x8(acc[n], ah, b0h, b1h);
+                    }
                 }
             }
         }
+    };
+    for (int s0 = 0; s0 < steps; s0 += 4) {
+        float4 cur[2][4];
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) cur[s][i] = pa[0][s][i];
+        if (s0 + 4 < steps) fetch(pa[0], s0 + 4);
+        multiply(cur, s0);
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) cur[s][i] = pa[1][s][i];
+        if (s0 + 6 < steps) fetch(pa[1], s0 + 6);
+        multiply(cur, s0 + 2);
     }
-    // the 32 lanes' partial sums of a row meet in shared memory; lane j adds column j over the lanes
+    // accumulator element (row g [+8], column 2 t [+1]) of every n8 tile goes to this slice's partial result
     float* out = partial + (int64_t)blockIdx.y * M * N;
-    __syncthreads();                              // every warp is done with the rows of B: their memory is reused
-    float* rs = b_f + warp * 32 * (NP + 1);
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-        __syncwarp();
-#pragma unroll
-        for (int j = 0; j < NP; ++j) rs[lane * (NP + 1) + j] = acc[r][j];
-        __syncwarp();
-        if (lane < N && m0 + r < M) {
-            float s = 0.0f;
-#pragma unroll 8
-            for (int l = 0; l < 32; ++l) s += rs[l * (NP + 1) + lane];
-            out[(int64_t)(m0 + r) * N + lane] = s;
+    for (int n = 0; n < NT; ++n) {
+        const int c0 = n * 8 + 2 * t;
+        if (lo_ok) {
+            if (c0 < N) out[(int64_t)(m0 + g) * N + c0] = acc[n][0];
+            if (c0 + 1 < N) out[(int64_t)(m0 + g) * N + c0 + 1] = acc[n][1];
+        }
+        if (hi_ok) {
+            if (c0 < N) out[(int64_t)(m0 + g + 8) * N + c0] = acc[n][2];
+            if (c0 + 1 < N) out[(int64_t)(m0 + g + 8) * N + c0 + 1] = acc[n][3];
         }
     }
-    // ---- the block that finishes last for this group of 32 rows folds the k slices, in ascending order
+    // ---- the block that finishes last for this group of 128 rows folds the k slices, in ascending order
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) s_last = atomicAdd(&tickets[blockIdx.x], 1) == (int)gridDim.y - 1;
@@ -135,15 +173,47 @@ __global__ void __launch_bounds__(256, 2) k_linear_fwd(float* __restrict__ C, fl
     if (!s_last) return;
     __threadfence();
     const int nsplit = gridDim.y;
-    for (int idx = threadIdx.x; idx < 32 * N; idx += 256) {
-        const int row = idx / N, col = idx - row * N;
-        const int m = blockIdx.x * 32 + row;
-        if (m >= M) continue;
-        float s = 0.0f;
-        for (int sp = 0; sp < nsplit; ++sp) s += __ldcg(partial + ((int64_t)sp * M + m) * N + col);
-        if (bias) s += __ldg(bias + col);         // ADD.forward after DOT.forward
-        float* c = C + (int64_t)m * N + col;
-        *c = accumulate ? *c + s : s;
+    const int rows = min(128, M - (int)blockIdx.x * 128);
+    const int64_t base = (int64_t)blockIdx.x * 128 * N;      // the group's rows are rows * N contiguous floats per slice
+    const int64_t slice = (int64_t)M * N;
+    if ((slice & 3) == 0 && ((rows * N) & 3) == 0) {
+        // 16-byte pieces, eight slices in flight per thread, slices added in ascending order
+        const float4* p4 = reinterpret_cast<const float4*>(partial + base);
+        const int64_t slice4 = slice >> 2;
+        for (int i4 = threadIdx.x; i4 < (rows * N) >> 2; i4 += 256) {
+            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            int sp = 0;
+            for (; sp + 8 <= nsplit; sp += 8) {
+                float4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = __ldcg(p4 + (int64_t)(sp + u) * slice4 + i4);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { sum.x += v[u].x; sum.y += v[u].y; sum.z += v[u].z; sum.w += v[u].w; }
+            }
+            for (; sp < nsplit; ++sp) {
+                const float4 v = __ldcg(p4 + (int64_t)sp * slice4 + i4);
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+            }
+            const float sv[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int idx = i4 * 4 + e;
+                const int col = idx % N;
+                float r = sv[e];
+                if (bias) r += __ldg(bias + col);     // ADD.forward after DOT.forward
+                float* c = C + base + idx;
+                *c = accumulate ? *c + r : r;
+            }
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < rows * N; idx += 256) {
+            const int col = idx % N;
+            float sum = 0.0f;
+            for (int sp = 0; sp < nsplit; ++sp) sum += __ldcg(partial + (int64_t)sp * slice + base + idx);
+            if (bias) sum += __ldg(bias + col);       // ADD.forward after DOT.forward
+            float* c = C + base + idx;
+            *c = accumulate ? *c + sum : sum;
+        }
     }
     if (threadIdx.x == 0) tickets[blockIdx.x] = 0;   // ready for the next launch
 }
@@ -286,11 +356,39 @@ __device__ __forceinline__ void role_db(const LinBwd& p, int b, float* smem, int
     if (!*s_last) return;
     __threadfence();
     const int kn = min(256, p.K - kg * 256);
-    for (int idx = threadIdx.x; idx < kn * p.N; idx += 256) {   // consecutive threads, consecutive floats
-        const int64_t off = (int64_t)kg * 256 * p.N + idx;
-        float s = 0.0f;
-        for (int q = 0; q < p.msplit; ++q) s += __ldcg(p.partial + (int64_t)q * p.K * p.N + off);
-        p.dB[off] = p.acc_db ? p.dB[off] + s : s;
+    const int64_t slice = (int64_t)p.K * p.N, base = (int64_t)kg * 256 * p.N;
+    if ((slice & 3) == 0 && ((kn * p.N) & 3) == 0 && (reinterpret_cast<uintptr_t>(p.dB) & 15u) == 0) {
+        // 16-byte pieces, eight slices in flight per thread, slices added in ascending order
+        const float4* p4 = reinterpret_cast<const float4*>(p.partial + base);
+        float4* d4 = reinterpret_cast<float4*>(p.dB + base);
+        const int64_t slice4 = slice >> 2;
+        for (int i4 = threadIdx.x; i4 < (kn * p.N) >> 2; i4 += 256) {
+            float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            int q = 0;
+            for (; q + 8 <= p.msplit; q += 8) {
+                float4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = __ldcg(p4 + (int64_t)(q + u) * slice4 + i4);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) { s.x += v[u].x; s.y += v[u].y; s.z += v[u].z; s.w += v[u].w; }
+            }
+            for (; q < p.msplit; ++q) {
+                const float4 v = __ldcg(p4 + (int64_t)q * slice4 + i4);
+                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            }
+            if (p.acc_db) {
+                const float4 old = d4[i4];
+                s.x += old.x; s.y += old.y; s.z += old.z; s.w += old.w;
+            }
+            d4[i4] = s;
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < kn * p.N; idx += 256) {   // consecutive threads, consecutive floats
+            const int64_t off = base + idx;
+            float s = 0.0f;
+            for (int q = 0; q < p.msplit; ++q) s += __ldcg(p.partial + (int64_t)q * slice + off);
+            p.dB[off] = p.acc_db ? p.dB[off] + s : s;
+        }
     }
     if (threadIdx.x == 0) p.tickets[kg] = 0;
 }
@@ -344,23 +442,22 @@ int32_t mtl_linear_fwd(mtl_ctx* ctx, float* C, const float* A, const float* B, c
         const int64_t cs[2] = {M, N}, bs[1] = {N};
         return mtl_binary_fwd(ctx, MTL_OP_ADD, C, C, bias, 2, cs, 1, bs);
     }
-    // k extent per block: enough blocks (two fit an SM) to fill the machine
-    const int rb = (int)((M + 31) / 32);
-    int kc = kKC;
-    while (kc > 128 && (int64_t)rb * ((K + kc - 1) / kc) < 2ll * ctx->sm_count) kc >>= 1;
+    // 128 rows and one k slice per block.  Shorter slices mean more blocks but also more slices for the last
+    // block of a row group to fold (measured at 256 rows: 98 slices of 64 cost more in the fold than they
+    // gain in parallelism), so slices shrink only until half the SMs have a block.
+    const int rb = (int)((M + 127) / 128);
+    int kc = kMmaKC;
+    while (kc > 64 && (int64_t)rb * ((K + kc - 1) / kc) < ctx->sm_count / 2) kc >>= 1;
     const int nsplit = (int)((K + kc - 1) / kc);
     void* ws;
     int32_t rc = mtl_workspace(ctx, (size_t)nsplit * M * N * 4, &ws);
     if (rc) return rc;
     dim3 grid((unsigned)rb, (unsigned)nsplit);
     MTL_REQUIRE(ctx, nsplit <= 65535, "Linear: reduction too long");
-#define MTL_LIN_FWD(NQ_) mtl_launch_pdl(ctx, k_linear_fwd<NQ_>, grid, dim3(256), (size_t)0, C, (float*)ws, ctx->tickets, A, B, bias, \
-                                        (int)M, (int)N, (int)K, kc, 0)
-    if (N <= 4) MTL_LIN_FWD(1);
-    else if (N <= 8) MTL_LIN_FWD(2);
-    else if (N <= 12) MTL_LIN_FWD(3);
-    else MTL_LIN_FWD(4);
-#undef MTL_LIN_FWD
+    if (N <= 8)
+        mtl_launch_pdl(ctx, k_linear_fwd_mma<1>, grid, dim3(256), (size_t)0, C, (float*)ws, ctx->tickets, A, B, bias, (int)M, (int)N, (int)K, kc, 0);
+    else
+        mtl_launch_pdl(ctx, k_linear_fwd_mma<2>, grid, dim3(256), (size_t)0, C, (float*)ws, ctx->tickets, A, B, bias, (int)M, (int)N, (int)K, kc, 0);
     MTL_LAUNCHED(ctx);
     return MTL_OK;
 }
