@@ -778,15 +778,20 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                 int folder = *split_flag;
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (!folder) {
-                    for (int c = 0; c < nchunk; ++c) {
-                        uint32_t v[16];
-                        tmem_ld_32x16(half_addr + (uint32_t)(c * 16), v);
-                        tmem_ld_wait();
-                        float4* dst = mine + ((size_t)(c * 4 + quad) * 4) * 32 + lane;
+                    // the read of the next 16 columns is issued before the current ones are stored
+                    uint32_t v[2][16];
+                    tmem_ld_32x16(half_addr, v[0]);
 #pragma unroll
-                        for (int g = 0; g < 4; ++g)
-                            __stcg(dst + g * 32, make_float4(__uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
-                                                             __uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3])));
+                    for (int c = 0; c < 16; ++c) {
+                        if (c < nchunk) {
+                            tmem_ld_wait();
+                            if (c + 1 < nchunk) tmem_ld_32x16(half_addr + (uint32_t)((c + 1) * 16), v[(c + 1) & 1]);
+                            float4* dst = mine + ((size_t)(c * 4 + quad) * 4) * 32 + lane;
+#pragma unroll
+                            for (int g = 0; g < 4; ++g)
+                                __stcg(dst + g * 32, make_float4(__uint_as_float(v[c & 1][g * 4]), __uint_as_float(v[c & 1][g * 4 + 1]),
+                                                                 __uint_as_float(v[c & 1][g * 4 + 2]), __uint_as_float(v[c & 1][g * 4 + 3])));
+                        }
                     }
                     __threadfence();
                     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -801,22 +806,36 @@ k_conv_igemm_t(const __grid_constant__ CUtensorMap mapX0, const __grid_constant_
                     continue;
                 }
                 __threadfence();
-                for (int c = 0; c < nchunk; ++c) {
-                    uint32_t v[16];
-                    tmem_ld_32x16(half_addr + (uint32_t)(c * 16), v);
-                    const float4* src = other + ((size_t)(c * 4 + quad) * 4) * 32 + lane;
-                    float4 o[4];
+                {
+                    // The parked half comes from L2 (most of a microsecond per round trip): the loads of four
+                    // 16-column chunks are kept in flight, a chunk's registers being refilled as soon as it has
+                    // been added into tensor memory.
+                    float4 o[4][4];
+                    auto fetch_chunk = [&](int c, float4 (&dst)[4]) {
+                        const float4* src = other + ((size_t)(c * 4 + quad) * 4) * 32 + lane;
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) o[g] = __ldcg(src + g * 32);
-                    tmem_ld_wait();
+                        for (int g = 0; g < 4; ++g) dst[g] = __ldcg(src + g * 32);
+                    };
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        v[g * 4] = __float_as_uint(__uint_as_float(v[g * 4]) + o[g].x);
-                        v[g * 4 + 1] = __float_as_uint(__uint_as_float(v[g * 4 + 1]) + o[g].y);
-                        v[g * 4 + 2] = __float_as_uint(__uint_as_float(v[g * 4 + 2]) + o[g].z);
-                        v[g * 4 + 3] = __float_as_uint(__uint_as_float(v[g * 4 + 3]) + o[g].w);
+                    for (int c = 0; c < 4; ++c)
+                        if (c < nchunk) fetch_chunk(c, o[c]);
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        if (c < nchunk) {
+                            uint32_t v[16];
+                            tmem_ld_32x16(half_addr + (uint32_t)(c * 16), v);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                v[g * 4] = __float_as_uint(__uint_as_float(v[g * 4]) + o[c & 3][g].x);
+                                v[g * 4 + 1] = __float_as_uint(__uint_as_float(v[g * 4 + 1]) + o[c & 3][g].y);
+                                v[g * 4 + 2] = __float_as_uint(__uint_as_float(v[g * 4 + 2]) + o[c & 3][g].z);
+                                v[g * 4 + 3] = __float_as_uint(__uint_as_float(v[g * 4 + 3]) + o[c & 3][g].w);
+                            }
+                            tmem_st_32x16(half_addr + (uint32_t)(c * 16), v);
+                            if (c + 4 < nchunk) fetch_chunk(c + 4, o[c & 3]);
+                        }
                     }
-                    tmem_st_32x16(half_addr + (uint32_t)(c * 16), v);
                 }
                 tmem_st_wait();
                 if (threadIdx.x == 64) *ticket = 0;   // ready for the next launch
@@ -1258,7 +1277,7 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
             q.kb_half = (kblocks + 1) / 2;
             ctx->conv_split_tiles += rem;
         }
-        int grid = q.n_items < ctx->sm_count ? q.n_items : ctx->sm_count;
+        int grid = q.split_scratch ? (q.n_items < ctx->sm_count ? q.n_items : ctx->sm_count) : mtl_persistent_grid(ctx, q.n_items);
         {
             mtl_prof_scope prof(ctx, MTL_PROF_CONV_IGEMM);
             mtl_launch_pdl(ctx, k_conv_igemm_t, dim3(grid), dim3(kThreads), (size_t)(kTSmemBytes), tm[0], tm[1], tm[2], tm[3], q);
