@@ -43,11 +43,6 @@ struct mtl_ctx {
     int math_mode = MTL_MATH_TF32X3;
     int sm_count = 148;        // SMs the persistent grids may use (a data-parallel group takes some off)
     int sm_count_total = 148;  // SMs of the device
-    // Data parallel: while a gradient exchange is in flight on the communication stream (comm_pending), a
-    // persistent grid leaves comm_overlap_sms SMs to it when that costs the grid no extra wave of tiles
-    // (mtl_persistent_grid); the collective is limited to as many CTAs.
-    int comm_pending = 0;
-    int comm_overlap_sms = 0;
     // scratch workspace, grown on demand outside capture
     void* ws = nullptr;
     size_t ws_bytes = 0;
@@ -209,17 +204,6 @@ static inline int64_t mtl_numel(int32_t rank, const int64_t* shape) {
     int64_t n = 1;
     for (int i = 0; i < rank; ++i) n *= shape[i];
     return n;
-}
-
-// CTAs of a persistent kernel (one per SM) that walks `tiles` equal tiles.
-static inline int mtl_persistent_grid(const mtl_ctx* ctx, int64_t tiles) {
-    const int all = ctx->sm_count;
-    if (tiles <= 0) return 1;
-    if (ctx->comm_pending && ctx->comm_overlap_sms > 0 && all > 2 * ctx->comm_overlap_sms) {
-        const int fewer = all - ctx->comm_overlap_sms;
-        if (tiles >= all && (tiles + fewer - 1) / fewer == (tiles + all - 1) / all) return fewer;
-    }
-    return tiles < all ? (int)tiles : all;
 }
 
 static inline int mtl_grid_for(int64_t work_items, int block, int sm_count, int ctas_per_sm) {

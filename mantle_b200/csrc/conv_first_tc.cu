@@ -740,7 +740,7 @@ int32_t launch_first_wgrad(mtl_ctx* ctx, float* dW, float* db, const float* pg, 
     if (p.xw > Cfg::XW_MAX)
         return mtl_set_error(ctx, MTL_ERR_UNSUPPORTED, "first-layer tensor-core gradient: input box too wide");
     const int kgroups = (g.K + 63) / 64;
-    int gx = (kgroups == 1 ? mtl_persistent_grid(ctx, p.tiles) : ctx->sm_count / kgroups);
+    int gx = ctx->sm_count / kgroups;
     if (gx < 1) gx = 1;
     if (gx > p.tiles) gx = p.tiles;
     void* ws;

@@ -1277,7 +1277,7 @@ int32_t run_igemm_core(mtl_ctx* ctx, const IgemmCall& c, int x3, float* a_hi, fl
             q.kb_half = (kblocks + 1) / 2;
             ctx->conv_split_tiles += rem;
         }
-        int grid = q.split_scratch ? (q.n_items < ctx->sm_count ? q.n_items : ctx->sm_count) : mtl_persistent_grid(ctx, q.n_items);
+        int grid = q.n_items < ctx->sm_count ? q.n_items : ctx->sm_count;
         {
             mtl_prof_scope prof(ctx, MTL_PROF_CONV_IGEMM);
             mtl_launch_pdl(ctx, k_conv_igemm_t, dim3(grid), dim3(kThreads), (size_t)(kTSmemBytes), tm[0], tm[1], tm[2], tm[3], q);

@@ -382,19 +382,15 @@ int32_t mtl_dp_init(mtl_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world
     int reserve = 0;
     if (const char* e = getenv("MANTLE_DP_RESERVE_SMS")) reserve = atoi(e);
     if (reserve < 0) reserve = 0;
-    // MANTLE_DP_OVERLAP_SMS = n (default 0) reserves only where it is free: a persistent grid launched WHILE an
-    // exchange is in flight leaves n SMs to it when its tiles need no extra wave for that (mtl_persistent_grid;
-    // at 256 images per GPU conv2's input gradient has 256 tiles: two waves on 148 SMs and on 140).  Measured
-    // with n = 8 it still loses -- 4 GPUs 0.428 against 0.407 ms per step, 4 ranks at 256 images each 0.289
-    // against 0.273: an all-reduce squeezed into 8 CTAs beside a tensor-core kernel takes longer than one
-    // that waits for the kernel's end and then has the machine.
-    int overlap = 0;
-    if (const char* e = getenv("MANTLE_DP_OVERLAP_SMS")) overlap = atoi(e);
-    if (overlap < 0) overlap = 0;
-    if (world > 1 && (reserve > 0 || overlap > 0)) {
+    // Reserving only where it is free was measured too: a persistent grid launched WHILE an exchange is in
+    // flight left 8 SMs to it when its tiles needed no extra wave for that (at 256 images per GPU conv2's input
+    // gradient has 256 tiles: two waves on 148 SMs and on 140).  It lost as well -- 4 GPUs 0.428 against 0.407 ms
+    // per step, 4 ranks at 256 images each 0.289 against 0.273: an all-reduce squeezed into 8 CTAs beside a
+    // tensor-core kernel takes longer than one that waits for the kernel's end and then has the machine.
+    if (reserve > 0 && world > 1) {
         char buf[16];
-        int ctas = reserve > overlap ? reserve : overlap;
-        if (const char* e = getenv("MANTLE_DP_NCCL_CTAS")) ctas = atoi(e) > 0 ? atoi(e) : ctas;
+        int ctas = reserve;
+        if (const char* e = getenv("MANTLE_DP_NCCL_CTAS")) ctas = atoi(e) > 0 ? atoi(e) : reserve;
         snprintf(buf, sizeof(buf), "%d", ctas);
         setenv("NCCL_MAX_CTAS", buf, 0);   // a value set by the user wins
     }
@@ -412,8 +408,6 @@ int32_t mtl_dp_init(mtl_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world
         return mtl_set_error(ctx, MTL_ERR_CUDA, "could not create the communication stream");
     }
     ctx->dp = st;
-    ctx->comm_overlap_sms = world > 1 ? overlap : 0;
-    ctx->comm_pending = 0;
     if (world > 1 && reserve > 0 && ctx->sm_count > 2 * reserve) {
         st->reserved_sms = reserve;
         ctx->sm_count -= reserve;          // persistent grids are sized from this
@@ -444,7 +438,6 @@ int32_t mtl_dp_allreduce_async(mtl_ctx* ctx, float* buf, int64_t n) {
     } else
         MTL_NCCL(ctx, g_nccl.AllReduce(buf, buf, (size_t)n, ncclFloat32, ncclSum, st->comm, st->comm_stream));
     st->pending = true;
-    ctx->comm_pending = 1;
     return MTL_OK;
 }
 
@@ -508,7 +501,6 @@ int32_t mtl_dp_wait(mtl_ctx* ctx) {
     MTL_CUDA(ctx, cudaEventRecord(st->done, st->comm_stream));
     MTL_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, st->done, 0));
     st->pending = false;
-    ctx->comm_pending = 0;
     return MTL_OK;
 }
 
@@ -581,8 +573,6 @@ int32_t mtl_dp_destroy(mtl_ctx* ctx) {
     cudaEventDestroy(st->done);
     cudaStreamDestroy(st->comm_stream);
     ctx->sm_count += st->reserved_sms;
-    ctx->comm_pending = 0;
-    ctx->comm_overlap_sms = 0;
     delete st;
     ctx->dp = nullptr;
     return MTL_OK;
