@@ -59,7 +59,7 @@ class Model {
     // overwrites it and later ones add, which equals zero_grad() followed by accumulation without
     // touching the buffers twice; zero_grads() then only zeroes buffers no node writes.
     // Off: every contribution accumulates, exactly like backward_op (ops.mojo:405,463,498).
-    void set_overwrite_first(bool on) { overwrite_first_ = on; }
+    void set_overwrite_first(bool on) { overwrite_first_ = on; ce_grad_fresh_ = false; }
 
     // Chain fusion (off by default).  On: a CONV2D whose only consumer is a RELU writes the RELU's
     // output directly (mtl_conv2d_fwd_act) and the RELU node is not run -- and when a MAXPOOL2D is the
