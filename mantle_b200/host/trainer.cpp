@@ -40,7 +40,8 @@ void Trainer::map_final_nodes() {
 Trainer::~Trainer() {
     model_.after_backward_node = nullptr;
     model_.after_backward_user = nullptr;
-    if (graph_) mtl_graph_destroy(model_.ctx(), graph_);
+    for (mtl_graph* g : graphs_)
+        if (g) mtl_graph_destroy(model_.ctx(), g);
     for (int b = 0; b < 2; ++b)
         if (stage_[b]) mtl_free(model_.ctx(), stage_[b]);
     mtl_host_free(model_.ctx(), own_loss_);
@@ -118,9 +119,9 @@ void Trainer::enqueue_body() {
 }
 
 // Inputs travel host -> staging buffer on the copy stream (two buffers, used in turn) and staging
-// buffer -> input tensors on the compute stream, so a caller that enqueues step i + 1 while step i
-// is still running gets its copy overlapped with that step's kernels.
-void Trainer::stage_inputs(const std::vector<const float*>& host_inputs) {
+// buffer -> input tensors on the compute stream at the head of the step, so a caller that enqueues
+// step i + 1 while step i is still running gets its copy overlapped with that step's kernels.
+int Trainer::stage_inputs(const std::vector<const float*>& host_inputs) {
     mtl_ctx* ctx = model_.ctx();
     const Graph& g = model_.graph();
     if (host_inputs.size() != g.inputs.size()) throw Error(MTL_ERR_INVALID, "wrong number of inputs");
@@ -139,8 +140,16 @@ void Trainer::stage_inputs(const std::vector<const float*>& host_inputs) {
         off += (n + 63) / 64 * 64;
     }
     ck(ctx, mtl_stage_acquire(ctx, slot), "input copy wait");
-    off = 0;
-    for (size_t i = 0; i < host_inputs.size(); ++i) {
+    return slot;
+}
+
+// Staging buffer -> input tensors (a device copy; one-hot rows for an input declared with set_label_input).
+// Enqueued on the compute stream; inside a capture it becomes part of that slot's graph.
+void Trainer::place_inputs(int slot) {
+    mtl_ctx* ctx = model_.ctx();
+    const Graph& g = model_.graph();
+    int64_t off = 0;
+    for (size_t i = 0; i < g.inputs.size(); ++i) {
         const int64_t n = host_floats(i);
         if (i < label_classes_.size() && label_classes_[i])
             ck(ctx, mtl_one_hot_f32(ctx, model_.input_device((int)i), stage_[slot] + off, n, label_classes_[i]),
@@ -149,20 +158,22 @@ void Trainer::stage_inputs(const std::vector<const float*>& host_inputs) {
             ck(ctx, mtl_copy_f32(ctx, model_.input_device((int)i), stage_[slot] + off, n, 0), "input placement");
         off += (n + 63) / 64 * 64;
     }
-    ck(ctx, mtl_stage_release(ctx, slot), "input staging release");
 }
 
 void Trainer::step_async(const std::vector<const float*>& host_inputs, float* pinned_loss) {
     mtl_ctx* ctx = model_.ctx();
-    if (!host_inputs.empty()) stage_inputs(host_inputs);  // else: keep the inputs already resident
+    // which captured step this is: inputs from staging buffer 0 / 1, or already resident (2)
+    const int variant = host_inputs.empty() ? 2 : stage_inputs(host_inputs);
     ++steps_;
     if (!use_graph_ || steps_ == 1) {
         // the first step also sizes the scratch workspace, which must not grow during capture
+        if (variant < 2) place_inputs(variant);
         enqueue_body();
     } else {
-        if (!graph_) {
+        if (!graphs_[variant]) {
             ck(ctx, mtl_graph_begin(ctx), "graph capture begin");
             try {
+                if (variant < 2) place_inputs(variant);
                 enqueue_body();
             } catch (...) {
                 mtl_graph* dead = nullptr;
@@ -170,12 +181,14 @@ void Trainer::step_async(const std::vector<const float*>& host_inputs, float* pi
                 if (dead) mtl_graph_destroy(ctx, dead);
                 throw;
             }
-            ck(ctx, mtl_graph_end(ctx, &graph_), "graph capture end");
+            ck(ctx, mtl_graph_end(ctx, &graphs_[variant]), "graph capture end");
         } else {
             adam_.note_replayed_step();
         }
-        ck(ctx, mtl_graph_launch(ctx, graph_), "graph launch");
+        ck(ctx, mtl_graph_launch(ctx, graphs_[variant]), "graph launch");
     }
+    // the staging buffer may be overwritten once the step that read it is over
+    if (variant < 2) ck(ctx, mtl_stage_release(ctx, variant), "input staging release");
     // the loss tensor is not touched by the backward pass, so it is read after the whole step
     ck(ctx, mtl_d2h_async(ctx, pinned_loss, model_.loss_device(), 4), "loss read-back");
 }

@@ -36,11 +36,12 @@ class Trainer {
     void set_exchange(bool on) { exchange_ = on; }
 
     int64_t steps() const { return steps_; }
-    bool graph_active() const { return graph_ != nullptr; }
+    bool graph_active() const { return graphs_[0] || graphs_[1] || graphs_[2]; }
 
    private:
     void enqueue_body();
-    void stage_inputs(const std::vector<const float*>& host_inputs);
+    int stage_inputs(const std::vector<const float*>& host_inputs);   // returns the staging slot used
+    void place_inputs(int slot);
     static void node_done_thunk(void* self, int node);
     void node_done(int node);
     void flush_bucket(bool last = false);
@@ -53,7 +54,10 @@ class Trainer {
     bool use_graph_;
     int64_t bucket_bytes_;
     int world_ = 1;
-    mtl_graph* graph_ = nullptr;
+    // One captured step per source of the inputs: staging buffer 0, staging buffer 1 (the placement of the
+    // batch -- a device copy per input, one-hot rows for label inputs -- is part of those two graphs), and
+    // inputs already resident in the arena.
+    mtl_graph* graphs_[3] = {nullptr, nullptr, nullptr};
     float* stage_[2] = {nullptr, nullptr};  // device staging buffers for the inputs, used in turn
     int64_t stage_floats_ = 0;
     std::vector<int> label_classes_;        // per graph input: 0 = dense tensor, C = labels expanded to C classes
